@@ -1,0 +1,397 @@
+"""Benchmark of the fused CSR message-passing path (forward + backward).
+
+    python bench.py --gpus 1 --steps K --warmup W           # this build, on B200
+    python bench.py --impl reference --steps K --warmup W   # the CPU arm
+
+Workload at one GPU: the "GCN layer" configuration -- an R-MAT graph
+(a, b, c, d = 0.57, 0.19, 0.19, 0.05) with 2^20 nodes and 32 * 2^20 generated
+edges, symmetrised and de-duplicated, CSR by destination; edge weight
+1/sqrt(deg_i * deg_j); float32 features [N, 128]; sum reducer followed by a
+dense 128x128 float32 linear.  One step = forward plus the backward of
+out.sum() with respect to the features, the edge weights and the linear
+weights.  Metric: directed edges per second for forward + backward.
+
+The JSON line carries, besides the base fields:
+  roofline     achieved algorithmic GB/s of the dominant gather kernel, timed
+               with CUDA events inside the timed region, against the measured
+               HBM copy bandwidth of MEASURED_PEAKS.json
+  e2e          the same step through the public API with host (pinned) inputs
+               copied to the device and gradients copied back every step
+  cpu_baseline the CPU oracle port (test infrastructure, OpenMP over rows)
+               timed on a bounded sample of the same workload
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "tiga-lang_b200"))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "GEdges/s fwd+bwd for fused CSR message passing"
+UNIT = "GEdges/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=10)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="native", choices=("native", "reference"))
+    p.add_argument("--scale", type=int, default=20, help="log2 of the node count")
+    p.add_argument("--edge-factor", type=int, default=32)
+    p.add_argument("--features", type=int, default=128)
+    p.add_argument("--seed", type=int, default=20261125)
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--cpu-sample-seconds", type=float, default=15.0)
+    return p.parse_args()
+
+
+def hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as handle:
+            return float(json.load(handle)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def workload_name(args):
+    return (f"gcn-layer rmat scale={args.scale} edge_factor={args.edge_factor} symmetrized dedup "
+            f"F={args.features} fp32 sum+linear fwd+bwd")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while timing."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.lines = []
+        self.process = None
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.process = None
+
+    def _pump(self):
+        for line in self.process.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.process.terminate()
+        clocks, reasons, max_clock = [], set(), None
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                max_clock = float(parts[2])
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": max_clock,
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- GPU arm
+def build_inputs(args, device):
+    from tiga import synthetic as syn
+
+    row_ptr, col = syn.rmat_csr(args.scale, args.edge_factor, seed=args.seed, symmetrize=True, device=device)
+    n = row_ptr.numel() - 1
+    weight = syn.gcn_norm_weights(row_ptr, col)
+    x = syn.normal((n, args.features), seed=args.seed + 1, device=device)
+    lin = syn.normal((args.features, args.features), seed=args.seed + 2, device=device, std=args.features ** -0.5)
+    return row_ptr, col, weight, x, lin
+
+
+def algorithmic_bytes(E, N, F):
+    """No-reuse algorithmic traffic per launch: 8-byte indices as given by the
+    API, 4-byte weights, one F*4-byte row per edge, pointer + one row per node."""
+    row = 4 * F
+    return {
+        "fwd": E * (8 + 4 + row) + N * (8 + row),
+        "dx": E * (8 + 8 + 4 + row) + N * (8 + row),
+        "dw": E * (8 + row + 4) + N * (8 + row),
+    }
+
+
+def run_native(args):
+    import torch.distributed as dist
+
+    import tiga as tg
+    from tiga import _native, ops
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    if world > 1:
+        from tiga.distributed import bench_halo
+
+        return bench_halo.run(args, rank, world, device)
+
+    _native.lib()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    row_ptr, col, weight, x, lin = build_inputs(args, device)
+    N, E, F = row_ptr.numel() - 1, col.numel(), args.features
+    graph = tg.Graph.from_csr(row_ptr, col, num_src=N)
+
+    class GCNLayer(tg.MessagePassing):
+        reducer = tg.sum()
+
+        def edge(self, src, dst, edge):
+            return edge.weight * src.x
+
+    layer = GCNLayer()
+    x.requires_grad_()
+    weight.requires_grad_()
+    lin.requires_grad_()
+
+    # per-kernel CUDA-event timing inside the step (events on the launching stream)
+    timings = {"fwd": [], "dx": [], "dw": []}
+    recording = {"on": False}
+
+    def timed(name, function):
+        def wrapper(*a, **k):
+            if not recording["on"]:
+                return function(*a, **k)
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            result = function(*a, **k)
+            stop.record()
+            timings[name].append((start, stop))
+            return result
+        return wrapper
+
+    ops.csr_reduce_forward = timed("fwd", ops.csr_reduce_forward)
+    ops.csr_reduce_backward_dx = timed("dx", ops.csr_reduce_backward_dx)
+    ops.csr_reduce_backward_dw = timed("dw", ops.csr_reduce_backward_dw)
+
+    def step(xs, ws, ls):
+        agg = layer(graph=graph, src={"x": xs}, dst={}, edge={"weight": ws})
+        out = agg @ ls
+        return torch.autograd.grad(out.sum(), (xs, ws, ls))
+
+    plan_start = time.perf_counter()
+    graph.native_plan(transpose=True)
+    torch.cuda.synchronize()
+    plan_ms = (time.perf_counter() - plan_start) * 1e3
+
+    for _ in range(max(args.warmup, 3)):
+        step(x, weight, lin)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches_before = _native.launch_count()
+    recording["on"] = True
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    begin.record()
+    for _ in range(args.steps):
+        grads = step(x, weight, lin)
+    end.record()
+    torch.cuda.synchronize()
+    recording["on"] = False
+    launches = _native.launch_count() - launches_before
+    clocks = sampler.stop()
+    ms_per_step = begin.elapsed_time(end) / args.steps
+    value = E / (ms_per_step * 1e-3) / 1e9
+
+    bytes_per = algorithmic_bytes(E, N, F)
+    kernel_ms = {k: sum(a.elapsed_time(b) for a, b in v) / max(len(v), 1) for k, v in timings.items()}
+    dominant = max(kernel_ms, key=kernel_ms.get)
+    peak, peak_kind = hbm_peak()
+    achieved = bytes_per[dominant] / (kernel_ms[dominant] * 1e-3) / 1e9
+    total_alg = sum(bytes_per.values())
+    total_kernel_ms = sum(kernel_ms.values())
+    roofline = {
+        "bound": "hbm", "kernel": {"fwd": "k_gather_vec (forward)", "dx": "k_gather_vec (transposed, dx)",
+                                   "dw": "k_edge_dot_vec (dw)"}[dominant],
+        "achieved": round(achieved, 1), "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+        "frac": round(achieved / peak, 4), "traffic": None,
+        "algorithmic_bytes_per_launch": bytes_per[dominant],
+        "kernel_ms": {k: round(v, 4) for k, v in kernel_ms.items()},
+        "kernel_gbs": {k: round(bytes_per[k] / (kernel_ms[k] * 1e-3) / 1e9, 1) for k in kernel_ms},
+        "fwd_bwd_frac": round(total_alg / (total_kernel_ms * 1e-3) / 1e9 / peak, 4),
+    }
+
+    result = {
+        "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args), "num_nodes": N, "num_edges": E, "features": F,
+                   "index_dtype": "int64", "max_degree": int(graph.native_plan(transpose=True).info["max_degree"]),
+                   "l2": "inputs exceed L2 (features and indices are each > 126 MB)", "plan_ms": round(plan_ms, 2)},
+        "roofline": roofline, "gpu_launches": int(launches), "clocks": clocks,
+    }
+
+    if not args.no_e2e:
+        result["e2e"] = run_e2e(args, step, x, weight, lin, E)
+    if not args.no_cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline(args, row_ptr.cpu(), col.cpu(), weight.detach().cpu(),
+                                              x.detach().cpu(), lin.detach().cpu(), steps=1, warmup=0)
+    print(json.dumps(result), flush=True)
+
+
+def run_e2e(args, step, x, weight, lin, E):
+    """Host buffers in, host gradients out, every step."""
+    host_in = [t.detach().cpu().pin_memory() for t in (x, weight, lin)]
+    host_out = [torch.empty_like(t).pin_memory() for t in host_in]
+    dev_in = [torch.empty_like(t, device=x.device) for t in host_in]
+    h2d = sum(t.numel() * t.element_size() for t in host_in)
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+
+    def once():
+        for d, h in zip(dev_in, host_in):
+            d.copy_(h, non_blocking=True)
+        leaves = [d.detach().requires_grad_() for d in dev_in]
+        grads = step(*leaves)
+        for h, g in zip(host_out, grads):
+            h.copy_(g, non_blocking=True)
+
+    for _ in range(2):
+        once()
+    torch.cuda.synchronize()
+    steps = max(3, min(args.steps, 10))
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(steps):
+        once()
+    end.record()
+    torch.cuda.synchronize()
+    ms = begin.elapsed_time(end) / steps
+    return {"value": round(E / (ms * 1e-3) / 1e9, 4), "unit": UNIT, "ms_per_step": round(ms, 3),
+            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": steps}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_step_factory(row_ptr, col, weight, x, lin, rows):
+    """One forward+backward of the GCN layer on the first `rows` destination
+    rows, evaluated by the CPU oracle port (aggregation, dx, dw) and torch.mm
+    (the linear, which is ordinary Torch user code in the reference)."""
+    import numpy as np
+
+    from oracle import oracle
+
+    rp = row_ptr[: rows + 1].numpy().copy()
+    edges = int(rp[-1])
+    ci = col[:edges].numpy().copy()
+    w = weight[:edges].numpy().copy()
+    xn = x.numpy()
+    n_src = x.shape[0]
+    t_ptr, t_col, order = oracle.csr_transpose(rp, ci, n_src)
+    ones = torch.ones(rows, lin.shape[1])
+
+    def step():
+        agg = oracle.wsum_fwd(rp, ci, xn, w)
+        agg_t = torch.from_numpy(agg)
+        out = agg_t @ lin
+        d_agg = ones @ lin.t()
+        d_lin = agg_t.t() @ ones
+        d_agg_n = d_agg.numpy()
+        dx = oracle.wsum_bwd_dx_pre(rp, t_ptr, t_col, order, n_src, d_agg_n, w)
+        dw = oracle.wsum_bwd_dw(rp, ci, d_agg_n, xn)
+        return out, dx, dw, d_lin
+
+    return step, edges
+
+
+def cpu_baseline(args, row_ptr, col, weight, x, lin, steps, warmup):
+    from oracle import oracle
+
+    oracle.build()
+    cores = oracle.num_threads()
+    torch.set_num_threads(max(cores, 1))
+    N = row_ptr.numel() - 1
+    # size the sample from a small probe so the whole leg stays bounded
+    probe_rows = max(N // 64, 1)
+    probe, probe_edges = cpu_step_factory(row_ptr, col, weight, x, lin, probe_rows)
+    t0 = time.perf_counter()
+    probe()
+    probe_s = time.perf_counter() - t0
+    budget = args.cpu_sample_seconds / max(steps + warmup, 1)
+    E = col.numel()
+    target_edges = min(E, int(probe_edges * budget / max(probe_s, 1e-6)))
+    rows = int(torch.searchsorted(row_ptr, torch.tensor(target_edges), right=True).item()) - 1
+    rows = max(min(rows, N), probe_rows)
+    step, edges = cpu_step_factory(row_ptr, col, weight, x, lin, rows)
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    seconds = (time.perf_counter() - t0) / steps
+    return {"value": round(edges / seconds / 1e9, 5), "unit": UNIT, "cores": cores, "kind": "port",
+            "seconds_per_step": round(seconds, 3),
+            "sample": f"first {rows} of {N} destination rows ({edges} of {E} edges), full feature matrix"}
+
+
+def run_reference(args):
+    """CPU arm: the oracle port on the host cores, same workload and metric."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from tiga import synthetic as syn
+
+    row_ptr, col = syn.rmat_csr(args.scale, args.edge_factor, seed=args.seed, symmetrize=True, device="cpu")
+    n = row_ptr.numel() - 1
+    weight = syn.gcn_norm_weights(row_ptr, col)
+    x = syn.normal((n, args.features), seed=args.seed + 1)
+    lin = syn.normal((args.features, args.features), seed=args.seed + 2, std=args.features ** -0.5)
+    args.cpu_sample_seconds = 60.0
+    base = cpu_baseline(args, row_ptr, col, weight, x, lin, steps=args.steps, warmup=args.warmup)
+    value = base["value"]
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(base["seconds_per_step"] * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args), "num_nodes": n, "num_edges": col.numel(),
+                   "features": args.features},
+        "cpu_baseline": base,
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_native(args)
+
+
+if __name__ == "__main__":
+    main()

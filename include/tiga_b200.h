@@ -1,0 +1,179 @@
+/*
+ * tiga_b200.h -- C ABI of libtiga_b200.so: hand-written sm_100a CUDA kernels
+ * for Tiga's fused CSR message-passing path (forward and autograd backward).
+ *
+ * This boundary replaces, for that one path, the reference's native C ABI
+ * `gfrt_*` (include/tiga/Runtime/CAPI.h:50-114 of walkerchi/TIGA-lang: module
+ * load + kernel launch of Triton-compiled images) together with the launch
+ * ABI of those images (python/tiga/codegen/ttir.py:103-121: positional device
+ * pointers `(row_ptr, col_idx, *fields, out)`, scalars, then scratch
+ * pointers).  The same discipline is kept:
+ *
+ *   - every function returns an int32 status with the reference's codes
+ *     (CAPI.h:21-27) and never throws or aborts; tgb_last_error() gives the
+ *     thread-local message of the last non-zero status;
+ *   - the caller passes raw device addresses, element counts and the CUDA
+ *     stream handle to launch on (CAPI.h:78-80 wraps an external stream the
+ *     same way); nothing here allocates or frees device memory, and no call
+ *     synchronises the device except tgb_csr_plan_create (documented there);
+ *   - a plan is an opaque host handle over caller-owned device memory.
+ *
+ * Functions are re-entrant; the only mutable global state is the thread-local
+ * error string.  One process drives one GPU at a time (the current device of
+ * the calling thread must be the one that owns the pointers).
+ */
+#ifndef TIGA_B200_H
+#define TIGA_B200_H
+
+#include <stdint.h>
+
+#if defined(_WIN32)
+#define TGB_API __declspec(dllexport)
+#else
+#define TGB_API __attribute__((visibility("default")))
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes: identical to GFRTStatus (include/tiga/Runtime/CAPI.h:21-27). */
+enum {
+  TGB_STATUS_OK = 0,
+  TGB_STATUS_INVALID_ARGUMENT = 1,
+  TGB_STATUS_UNSUPPORTED = 2,
+  TGB_STATUS_OUT_OF_MEMORY = 3,
+  TGB_STATUS_INTERNAL = 4
+};
+
+/* Element types of feature buffers. */
+enum { TGB_DTYPE_F32 = 0, TGB_DTYPE_BF16 = 1 };
+
+/* Reducers.  SUM/MEAN: python/tiga/reducer/core.py:85-143.  MAX: a user
+ * Reducer whose combine is tg.math.maximum (the variadic-reduce algebra
+ * branch, lib/Target/Triton/Translate.cpp:3353-3402). */
+enum { TGB_REDUCER_SUM = 0, TGB_REDUCER_MEAN = 1, TGB_REDUCER_MAX = 2 };
+
+/* Plan flags. */
+enum {
+  TGB_PLAN_FORWARD = 1,   /* degree-bucket work lists over the CSR rows        */
+  TGB_PLAN_TRANSPOSE = 2  /* + transposed relation (stable), needed by *_bwd_dx */
+};
+
+/* replaces gfrt_status_string (CAPI.h:50) */
+TGB_API const char *tgb_status_string(int32_t status);
+/* replaces the message the reference raises after a non-zero status
+ * (python/tiga/runtime/__init__.py:279-284) */
+TGB_API const char *tgb_last_error(void);
+/* replaces gfrt_runtime_version (CAPI.h:51) */
+TGB_API const char *tgb_version(void);
+/* number of kernels this library has launched from the calling process */
+TGB_API int64_t tgb_launch_count(void);
+
+/* ------------------------------------------------------------------------
+ * Plans: the per-graph schedule.  Replaces the reference's schedule passes
+ * (lib/Transforms/SelectKernelSchedule.cpp:136-254, PlanDegreeBuckets.cpp:
+ * 32-143, PlanSplitRows.cpp:34-117) and its device work-list kernels
+ * gf_degree_reset/histogram/prefix/scatter (lib/Target/Triton/Translate.cpp:
+ * 4048-4210), and the transposed-relation build of the generated source VJP
+ * (python/tiga/interop/torch/relation_vjp.py:61-87).
+ *
+ * Rows are ordered by degree bucket (0, 1, 2, 3-4, 5-8, ... powers of two),
+ * heaviest bucket first, stable by row id inside a bucket.  Rows longer than
+ * the split threshold are cut into fixed-size edge segments that are reduced
+ * by separate thread groups and summed by a finalize kernel in segment order.
+ * ------------------------------------------------------------------------ */
+typedef struct tgb_csr_plan tgb_csr_plan;
+
+/* Bytes of device memory a plan needs: `persistent_bytes` lives as long as the
+ * plan, `temp_bytes` only during tgb_csr_plan_create.  index_bits is 32 or 64
+ * (row_ptr and col_idx share it, python/tiga/interop/torch/graph.py:594-601).
+ * Limits: num_dst, num_src < 2^31; num_edges < 2^32. */
+TGB_API int32_t tgb_csr_plan_sizes(int64_t num_dst, int64_t num_src,
+                                   int64_t num_edges, int32_t index_bits,
+                                   int32_t flags, uint64_t *persistent_bytes,
+                                   uint64_t *temp_bytes);
+
+/* Builds the plan into `persistent` (256-byte aligned device memory the caller
+ * keeps alive until tgb_csr_plan_destroy).  row_ptr/col_idx are device
+ * pointers that must stay valid and unchanged while the plan is used.
+ * This is the one call that synchronises `stream` (it reads three counters
+ * back to size the grids). */
+TGB_API int32_t tgb_csr_plan_create(const void *row_ptr, const void *col_idx,
+                                    int64_t num_dst, int64_t num_src,
+                                    int64_t num_edges, int32_t index_bits,
+                                    int32_t flags, void *persistent,
+                                    uint64_t persistent_bytes, void *temp,
+                                    uint64_t temp_bytes, uint64_t stream,
+                                    tgb_csr_plan **out_plan);
+
+/* Frees the host handle only (device memory belongs to the caller). */
+TGB_API int32_t tgb_csr_plan_destroy(tgb_csr_plan *plan);
+
+/* info[0]=num_dst [1]=num_src [2]=num_edges [3]=min_degree [4]=max_degree
+ * [5]=long rows (forward) [6]=segments (forward) [7]=long rows (transposed)
+ * [8]=segments (transposed) [9]=split threshold (edges) [10]=segment edges
+ * [11]=min in-degree of sources [12]=max in-degree of sources.
+ * Mirrors Graph.degree_bounds (python/tiga/interop/torch/graph.py:1224-1245)
+ * and the bucket summary of PlanDegreeBuckets.cpp:145-170. */
+TGB_API int32_t tgb_csr_plan_info(const tgb_csr_plan *plan, int64_t *info16);
+
+/* Device pointers of the plan's arrays, for tests and Graph.transpose():
+ * which = 0 forward row order (int32[num_dst]), 1 transposed row_ptr
+ * (int64[num_src+1]), 2 transposed destinations (int32[E]), 3 transposed edge
+ * ids (uint32[E], the stable argsort of col_idx), 4 transposed row order. */
+TGB_API int32_t tgb_csr_plan_array(const tgb_csr_plan *plan, int32_t which,
+                                   uint64_t *device_ptr, int64_t *count);
+
+/* Scratch bytes one reduce call needs for split rows (partial sums), for a
+ * feature row of `feature_elems` elements; direction 0 = forward/dw over the
+ * CSR rows, 1 = dx over the transposed rows. */
+TGB_API int32_t tgb_csr_plan_scratch_bytes(const tgb_csr_plan *plan,
+                                           int32_t direction, int32_t reducer,
+                                           int64_t feature_elems, int32_t dtype,
+                                           uint64_t *bytes);
+
+/* ------------------------------------------------------------------------
+ * Fused gather + reduce over CSR rows.
+ * ------------------------------------------------------------------------ */
+
+/* out[i,:] = reduce_{e in row i} (w ? w[e] : 1) * x[col[e],:]
+ * Replaces the generated gf_csr_weighted_sum / gf_csr_additive_tile /
+ * gf_csr_algebra_tile kernels and the row-split pair gf_row_split_partial /
+ * gf_row_split_finalize (lib/Target/Triton/Translate.cpp:776-1601,
+ * 2630-3450, 4212-4390) and the torch.sparse.mm fallback
+ * (python/tiga/interop/torch/message_passing.py:3287-3292).
+ *   x   [num_src, F] row-major contiguous, out [num_dst, F] (fully written)
+ *   w   [E] or NULL;  identity = start value of SUM / MAX rows
+ *   aux MAX only: int32 [num_dst, F] winning edge id per element (-1 = none)
+ * MEAN divides by the row length (empty row -> NaN). */
+TGB_API int32_t tgb_csr_reduce_fwd(const tgb_csr_plan *plan, int32_t reducer,
+                                   const void *x, const void *w, void *out,
+                                   void *aux, int64_t F, int32_t dtype,
+                                   float identity, void *scratch,
+                                   uint64_t scratch_bytes, uint64_t stream);
+
+/* dx[j,:] = sum_{e: col[e]=j} w[e] * dy[dst(e),:]  as a gather over the stable
+ * transposed relation (no atomics).  Replaces _CSRWeightedSumFunction.backward
+ * (python/tiga/interop/torch/message_passing.py:386-409) and
+ * compile_source_vjp (python/tiga/interop/torch/relation_vjp.py:45-105).
+ * MEAN: dy rows are divided by the destination's row length first (done into
+ * scratch).  MAX: only the winning edge of each (row, element) contributes. */
+TGB_API int32_t tgb_csr_reduce_bwd_dx(const tgb_csr_plan *plan, int32_t reducer,
+                                      const void *dy, const void *w,
+                                      const void *aux, void *dx, int64_t F,
+                                      int32_t dtype, void *scratch,
+                                      uint64_t scratch_bytes, uint64_t stream);
+
+/* dw[e] = <dy[dst(e),:], x[col[e],:]>  (per-edge dot product; the contract of
+ * benchmarks/autograd/message_passing_backward.py:346-353). */
+TGB_API int32_t tgb_csr_reduce_bwd_dw(const tgb_csr_plan *plan, int32_t reducer,
+                                      const void *dy, const void *x,
+                                      const void *aux, void *dw, int64_t F,
+                                      int32_t dtype, void *scratch,
+                                      uint64_t scratch_bytes, uint64_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TIGA_B200_H */

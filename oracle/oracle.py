@@ -161,6 +161,21 @@ def wsum_bwd_dx(row_ptr, col_idx, num_src, dy, w=None, mean=False):
     return dx.reshape((num_src,) + tuple(shape[1:]))
 
 
+def wsum_bwd_dx_pre(row_ptr, t_ptr, t_col, order, num_src, dy, w=None, mean=False):
+    """dx with a transposed relation built beforehand by csr_transpose."""
+    row_ptr, prow = _i64(row_ptr)
+    t_ptr, ptp = _i64(t_ptr)
+    t_col, ptc = _i64(t_col)
+    order, por = _i64(order)
+    dy2, shape = _as_2d(dy)
+    F = dy2.shape[1]
+    w, pw = _f32(None if w is None else np.asarray(w).reshape(-1))
+    dx = np.zeros((num_src, F), np.float32)
+    lib().orc_csr_wsum_bwd_dx_pre_f32(prow, ptp, ptc, por, _c64(num_src), dy2.ctypes.data_as(_f32p), _c64(F), pw,
+                                      ctypes.c_int(int(mean)), dx.ctypes.data_as(_f32p))
+    return dx.reshape((num_src,) + tuple(shape[1:]))
+
+
 def wsum_bwd_dw(row_ptr, col_idx, dy, x, mean=False):
     row_ptr, prow = _i64(row_ptr)
     col_idx, pcol = _i64(col_idx)

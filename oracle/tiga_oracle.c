@@ -174,17 +174,12 @@ ORC_API void orc_csr_wsum_fwd_f32(const int64_t *row_ptr, const int64_t *col_idx
  * `source[col_idx]` (python/tiga/interop/torch/message_passing.py:386-409) and
  * of the stable transposed relation (relation_vjp.py:61-87).  For the mean
  * reducer the cotangent of row i is first divided by the row length. */
-ORC_API int orc_csr_wsum_bwd_dx_f32(const int64_t *row_ptr,
-                                    const int64_t *col_idx, int64_t N,
-                                    int64_t num_src, const float *dy, int64_t F,
-                                    const float *w, int mean, float *dx) {
-  int64_t E = row_ptr[N];
-  int64_t *t_ptr = (int64_t *)malloc(sizeof(int64_t) * (size_t)(num_src + 1));
-  int64_t *t_col = (int64_t *)malloc(sizeof(int64_t) * (size_t)(E ? E : 1));
-  int64_t *order = (int64_t *)malloc(sizeof(int64_t) * (size_t)(E ? E : 1));
-  if (!t_ptr || !t_col || !order) return 3;
-  int rc = orc_csr_transpose(row_ptr, col_idx, N, num_src, t_ptr, t_col, order);
-  if (rc) return rc;
+ORC_API void orc_csr_wsum_bwd_dx_pre_f32(const int64_t *row_ptr,
+                                         const int64_t *t_ptr,
+                                         const int64_t *t_col,
+                                         const int64_t *order, int64_t num_src,
+                                         const float *dy, int64_t F,
+                                         const float *w, int mean, float *dx) {
 #pragma omp parallel for schedule(dynamic, 256)
   for (int64_t j = 0; j < num_src; ++j) {
     float *o = dx + j * F;
@@ -201,10 +196,25 @@ ORC_API int orc_csr_wsum_bwd_dx_f32(const int64_t *row_ptr,
       }
     }
   }
+}
+
+ORC_API int orc_csr_wsum_bwd_dx_f32(const int64_t *row_ptr,
+                                    const int64_t *col_idx, int64_t N,
+                                    int64_t num_src, const float *dy, int64_t F,
+                                    const float *w, int mean, float *dx) {
+  int64_t E = row_ptr[N];
+  int64_t *t_ptr = (int64_t *)malloc(sizeof(int64_t) * (size_t)(num_src + 1));
+  int64_t *t_col = (int64_t *)malloc(sizeof(int64_t) * (size_t)(E ? E : 1));
+  int64_t *order = (int64_t *)malloc(sizeof(int64_t) * (size_t)(E ? E : 1));
+  if (!t_ptr || !t_col || !order) return 3;
+  int rc = orc_csr_transpose(row_ptr, col_idx, N, num_src, t_ptr, t_col, order);
+  if (!rc)
+    orc_csr_wsum_bwd_dx_pre_f32(row_ptr, t_ptr, t_col, order, num_src, dy, F, w,
+                                mean, dx);
   free(t_ptr);
   free(t_col);
   free(order);
-  return 0;
+  return rc;
 }
 
 /* dw[e] = <dy[dst(e),:], x[col[e],:]>  (benchmark contract,

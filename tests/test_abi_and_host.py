@@ -1,0 +1,198 @@
+"""CPU-side checks: the C-ABI library loads and exports every declared symbol,
+and the host-side mirror of the reference API behaves like the reference
+(golden fixtures made by the reference itself)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import tiga as tg
+from tiga import _native
+from tiga import capture as cap
+from tiga.distributed import model as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "tiga_b200.h")).read()
+    return sorted(set(re.findall(r"TGB_API[^;]*?\b(tgb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    declared = _declared_symbols()
+    assert len(declared) >= 12
+    handle = ctypes.CDLL(_native.library_path())
+    for name in declared:
+        assert hasattr(handle, name), f"{name} declared in include/tiga_b200.h but not exported"
+    assert set(declared) == set(_native.exported_symbols())
+
+
+def test_status_strings_follow_reference_codes():
+    lib = _native.lib()
+    assert lib.tgb_status_string(0) == b"ok"
+    assert lib.tgb_status_string(1) == b"invalid argument"
+    assert lib.tgb_status_string(2) == b"unsupported"
+    assert lib.tgb_status_string(3) == b"out of memory"
+    assert lib.tgb_status_string(4) == b"internal error"
+    assert b"sm_100a" in lib.tgb_version()
+
+
+def test_argument_errors_without_gpu():
+    lib = _native.lib()
+    size = ctypes.c_uint64()
+    assert lib.tgb_csr_plan_sizes(4, 4, 4, 16, 1, ctypes.byref(size), ctypes.byref(size)) == _native.INVALID_ARGUMENT
+    assert b"index_bits" in lib.tgb_last_error()
+    assert lib.tgb_csr_plan_sizes(1 << 31, 4, 4, 64, 1, ctypes.byref(size), ctypes.byref(size)) == _native.UNSUPPORTED
+    assert lib.tgb_csr_reduce_fwd(None, 0, None, None, None, None, 4, 0, 0.0, None, 0, 0) == _native.INVALID_ARGUMENT
+    with pytest.raises(ValueError):
+        _native.check(_native.INVALID_ARGUMENT, "probe")
+
+
+def test_cpu_call_is_refused_not_emulated():
+    class WeightedSum(tg.MessagePassing):
+        reducer = tg.sum()
+
+        def edge(self, src, dst, edge):
+            return edge.weight * src.x
+
+    g = tg.Graph.from_csr(torch.tensor([0, 2, 3, 5]), torch.tensor([0, 2, 1, 0, 1]), num_src=3)
+    with pytest.raises(NotImplementedError):
+        WeightedSum()(graph=g, src={"x": torch.ones(3)}, dst={}, edge={"weight": torch.ones(5)})
+
+
+def test_reference_evaluator_matches_readme():
+    class WeightedSum(tg.MessagePassing):
+        reducer = tg.sum()
+
+        def edge(self, src, dst, edge):
+            return edge.weight * src.x
+
+    g = tg.Graph.from_csr(torch.tensor([0, 2, 3, 5]), torch.tensor([0, 2, 1, 0, 1]), num_src=3)
+    x = torch.tensor([1.0, 2.0, 3.0], requires_grad=True)
+    w = torch.tensor([2.0, 3.0, 4.0, 5.0, 6.0], requires_grad=True)
+    out = WeightedSum().reference(graph=g, src={"x": x}, dst={}, edge={"weight": w})
+    dx, dw = torch.autograd.grad(out.sum(), (x, w))
+    assert out.tolist() == [11.0, 8.0, 17.0] and dx.tolist() == [7.0, 10.0, 3.0]
+    assert dw.tolist() == [1.0, 3.0, 2.0, 1.0, 2.0]
+
+
+def test_capture_recognisers():
+    class Plain(tg.MessagePassing):
+        def edge(self, src, dst, edge):
+            return src.h
+
+    class Weighted(tg.MessagePassing):
+        def edge(self, src, dst, edge):
+            return src.x * edge.w
+
+    class GAT(tg.MessagePassing):
+        reducer = tg.online_softmax()
+
+        def edge(self, src, dst, edge, a_src, a_dst):
+            s = (src.x * a_src).sum(dim=-1) + (a_dst * dst.x).sum(dim=-1)
+            return self.reducer(tg.math.maximum(s, 0.2 * s), src.x)
+
+    class Attention(tg.MessagePassing):
+        reducer = tg.online_softmax()
+
+        def edge(self, src, dst, edge, scale):
+            return self.reducer((src.key * dst.query).sum(dim=-1) * scale, src.value)
+
+    class Opaque(tg.MessagePassing):
+        def edge(self, src, dst, edge):
+            return torch.relu(src.x)
+
+    assert cap.recognize_weighted_sum(cap.capture_edge(Plain().edge, {})) == cap.WeightedSumPattern("h", None)
+    assert cap.recognize_weighted_sum(cap.capture_edge(Weighted().edge, {})) == cap.WeightedSumPattern("x", "w")
+    gat = cap.recognize_gat(cap.capture_edge(GAT().edge, {"a_src": torch.zeros(2), "a_dst": torch.zeros(2)}))
+    assert gat == cap.GATPattern("x", "x", "a_src", "a_dst", 0.2)
+    dense = cap.recognize_dense_attention(cap.capture_edge(Attention().edge, {"scale": 0.25}))
+    assert dense == cap.DenseAttentionPattern("key", "query", "value", 0.25)
+    assert cap.capture_edge(Opaque().edge, {}) is None
+
+    class UserMax(tg.Reducer):
+        associative = commutative = True
+
+        def identity(self):
+            return float("-inf")
+
+        def combine(self, left, right):
+            return tg.math.maximum(left, right)
+
+    assert cap.reducer_algebra(UserMax()) == "max"
+    assert cap.reducer_algebra(tg.sum()) == "sum"
+    assert cap.reducer_algebra(tg.mean()) is None
+
+
+def test_graph_constructors_match_reference(golden):
+    src = torch.from_numpy(golden["coo_src"])
+    dst = torch.from_numpy(golden["coo_dst"])
+    g = tg.Graph.from_coo(src, dst, num_src=23, num_dst=17)
+    row_ptr, col = g.resolve_csr()
+    assert np.array_equal(row_ptr.numpy(), golden["coo_row_ptr"])
+    assert np.array_equal(col.numpy(), golden["coo_col"])
+    assert np.array_equal(g.destination_index().numpy(), golden["coo_destination"])
+    assert list(g.degree_bounds()) == golden["coo_degree_bounds"].tolist()
+    t = g.transpose()
+    t_ptr, t_col = t.resolve_csr()
+    assert np.array_equal(t_ptr.numpy(), golden["coo_t_ptr"])
+    assert np.array_equal(t_col.numpy(), golden["coo_t_col"])
+    # packed causal relation: cu_seqlens == cat of triangular blocks
+    cu = torch.from_numpy(golden["attn_cu"])
+    a = tg.Graph.cu_seqlens(cu, causal=True)
+    b = tg.Graph.cat([tg.Graph.triangular(int(n)) for n in cu.diff()])
+    for graph in (a, b):
+        rp, ci = graph.resolve_csr()
+        assert np.array_equal(rp.numpy(), golden["attn_row_ptr"])
+        assert np.array_equal(ci.numpy(), golden["attn_col"])
+    assert tg.Graph.triangular(4).resolve_csr()[0].tolist() == [0, 1, 3, 6, 10]
+    r = tg.Graph.regular(5, 2)
+    assert r.resolve_csr()[1].tolist() == [0, 1, 2, 3, 4, 0, 1, 2, 3, 4]
+    with pytest.raises(ValueError):
+        tg.Graph.from_csr(torch.tensor([0, 2]), torch.tensor([0, 5]), num_src=3, validate="full")
+    with pytest.raises(TypeError):
+        tg.Graph.from_csr(torch.tensor([0.0, 1.0]), torch.tensor([0]))
+
+
+def test_partition_model_matches_reference(golden):
+    for entities, world, rank, b, e in golden["owned_range_table"].tolist():
+        assert dist.owned_range(entities, world, rank) == (b, e)
+    for entity, entities, world, owner in golden["destination_owner_table"].tolist():
+        assert dist.destination_owner(entity, entities, world) == owner
+    row_ptr, col = golden["halo_row_ptr"], golden["halo_col"]
+    n = row_ptr.size - 1
+    for world in (2, 3, 4):
+        maps = [dist.derive_halo_map(row_ptr, col, num_entities=n, world_size=world, rank=r) for r in range(world)]
+        for r, m in enumerate(maps):
+            requests = [[i for i in maps[p].ghost_ids if m.owned_begin <= i < m.owned_end] for p in range(world)]
+            full = dist.derive_halo_map(row_ptr, col, num_entities=n, world_size=world, rank=r,
+                                        peer_requests=requests)
+            assert list(full.ghost_ids) == golden[f"halo_w{world}_r{r}_ghosts"].tolist()
+            assert [full.owned_begin, full.owned_end] == golden[f"halo_w{world}_r{r}_range"].tolist()
+            assert full.bytes_for(4, 64) == int(golden[f"halo_w{world}_r{r}_bytes"])
+            for peer, ids in full.receive_from:
+                assert list(ids) == golden[f"halo_w{world}_r{r}_recv{peer}"].tolist()
+            for peer, ids in full.send_to:
+                assert list(ids) == golden[f"halo_w{world}_r{r}_send{peer}"].tolist()
+            assert len(full.receive_from) == sum(f"halo_w{world}_r{r}_recv{p}" in golden for p in range(world))
+    assert dist.partition_bounds(10, 3) == [0, 4, 7, 10]
+    rp = torch.tensor([0, 90, 95, 96, 98, 100])
+    assert dist.partition_bounds(5, 2, row_ptr=rp, balance="edges") == [0, 1, 5]
+
+
+def test_synthetic_rmat_is_deterministic():
+    from tiga import synthetic as syn
+
+    a = syn.rmat_csr(10, 8, seed=7)
+    b = syn.rmat_csr(10, 8, seed=7)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    row_ptr, col = a
+    dst = torch.repeat_interleave(torch.arange(1024), row_ptr.diff())
+    key = dst * 1024 + col
+    assert torch.equal(key, torch.unique(key))            # sorted by (dst, src), no duplicates
+    rev = col * 1024 + dst
+    assert torch.equal(torch.sort(rev).values, key)        # symmetric

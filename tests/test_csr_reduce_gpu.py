@@ -1,0 +1,288 @@
+"""GPU parity: the CUDA path (through the C ABI) against the CPU oracle and the
+reference-generated fixtures.  Tolerances: float32 sums rel 1e-5 / abs 1e-6
+(bit-exact for rows that are not split); integer work and the max reducer's
+values and winners bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+import tiga as tg
+from tiga import ops
+from tiga import synthetic as syn
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-5, 1e-6
+
+
+class WeightedSum(tg.MessagePassing):
+    reducer = tg.sum()
+
+    def edge(self, src, dst, edge):
+        return edge.weight * src.x
+
+
+class PlainSum(tg.MessagePassing):
+    reducer = tg.sum(identity=0.5)
+
+    def edge(self, src, dst, edge):
+        return src.x
+
+
+class WeightedMean(tg.MessagePassing):
+    reducer = tg.mean()
+
+    def edge(self, src, dst, edge):
+        return edge.weight * src.x
+
+
+class PlainMean(tg.MessagePassing):
+    reducer = tg.mean()
+
+    def edge(self, src, dst, edge):
+        return src.x
+
+
+class UserMax(tg.Reducer):
+    associative = commutative = True
+
+    def identity(self):
+        return float("-inf")
+
+    def combine(self, left, right):
+        return tg.math.maximum(left, right)
+
+
+class WeightedMax(tg.MessagePassing):
+    reducer = UserMax()
+
+    def edge(self, src, dst, edge):
+        return self.reducer(edge.weight * src.x)
+
+
+KERNELS = {"wsum": WeightedSum, "psum": PlainSum, "wmean": WeightedMean, "pmean": PlainMean}
+
+
+def cuda(array, **kw):
+    return torch.from_numpy(np.ascontiguousarray(array)).cuda().requires_grad_(kw.get("grad", False))
+
+
+def test_readme_example_on_gpu():
+    g = tg.Graph.from_csr(torch.tensor([0, 2, 3, 5]).cuda(), torch.tensor([0, 2, 1, 0, 1]).cuda(), num_src=3)
+    x = torch.tensor([1.0, 2.0, 3.0], device="cuda", requires_grad=True)
+    w = torch.tensor([2.0, 3.0, 4.0, 5.0, 6.0], device="cuda", requires_grad=True)
+    kernel = WeightedSum()
+    out = kernel(graph=g, src={"x": x}, dst={}, edge={"weight": w})
+    dx, dw = torch.autograd.grad(out.sum(), (x, w))
+    assert out.tolist() == [11.0, 8.0, 17.0]
+    assert dx.tolist() == [7.0, 10.0, 3.0]
+    assert dw.tolist() == [1.0, 3.0, 2.0, 1.0, 2.0]
+    assert "weighted-sum" in kernel.last_variant.lowering
+    assert kernel.last_variant.provider == "b200-native"
+    assert "variant cache" in kernel.explain()
+
+
+@pytest.mark.parametrize("graph", ("fixed16", "ragged", "hub", "empty"))
+@pytest.mark.parametrize("F", (1, 3, 64))
+@pytest.mark.parametrize("tag", ("wsum", "psum", "wmean", "pmean"))
+def test_against_reference_fixtures(golden, graph, F, tag):
+    key = f"{tag}_{graph}_f{F}"
+    row_ptr, col = cuda(golden[key + "_row_ptr"]), cuda(golden[key + "_col"])
+    x = cuda(golden[key + "_x"], grad=True)
+    weighted = key + "_w" in golden
+    edge = {"weight": cuda(golden[key + "_w"], grad=True)} if weighted else {}
+    g = tg.Graph.from_csr(row_ptr, col, num_src=x.shape[0])
+    out = KERNELS[tag]()(graph=g, src={"x": x}, dst={}, edge=edge)
+    ref = golden[key + "_out"]
+    got = out.detach().cpu().numpy()
+    assert got.shape == ref.shape
+    if graph == "hub":  # split rows add partial sums in segment order
+        np.testing.assert_allclose(got, ref, rtol=RTOL, atol=ATOL)
+    else:
+        np.testing.assert_array_equal(got, ref)
+    if col.numel() == 0:
+        return
+    dy = golden[key + "_dy"].copy()
+    if "mean" in tag:
+        dy[np.diff(golden[key + "_row_ptr"]) == 0] = 0
+    inputs = (x, edge["weight"]) if weighted else (x,)
+    grads = torch.autograd.grad(out, inputs, cuda(dy))
+    np.testing.assert_allclose(grads[0].cpu().numpy(), golden[key + "_dx"], rtol=RTOL, atol=2 * ATOL)
+    if weighted:
+        np.testing.assert_allclose(grads[1].cpu().numpy(), golden[key + "_dw"], rtol=RTOL, atol=4 * ATOL)
+
+
+@pytest.mark.parametrize("index_dtype", (torch.int32, torch.int64))
+@pytest.mark.parametrize("F", (4, 8, 12, 32, 64, 96, 128, 256, 512, 5, 130))
+def test_feature_widths_against_oracle(oracle, index_dtype, F):
+    row_ptr, col = syn.rmat_csr(9, 12, seed=5)           # 512 nodes, hubs above the split threshold
+    n = row_ptr.numel() - 1
+    gen = torch.Generator().manual_seed(F)
+    x = torch.randn(n, F, generator=gen)
+    w = torch.rand(col.numel(), generator=gen)
+    dy = torch.randn(n, F, generator=gen)
+    g = tg.Graph.from_csr(row_ptr.to(index_dtype).cuda(), col.to(index_dtype).cuda(), num_src=n)
+    xg, wg = x.cuda().requires_grad_(), w.cuda().requires_grad_()
+    out = WeightedSum()(graph=g, src={"x": xg}, dst={}, edge={"weight": wg})
+    dx, dw = torch.autograd.grad(out, (xg, wg), dy.cuda())
+    ref = oracle.wsum_fwd(row_ptr.numpy(), col.numpy(), x.numpy(), w.numpy())
+    deg = np.diff(row_ptr.numpy())
+    got = out.detach().cpu().numpy()
+    unsplit = deg <= 512
+    np.testing.assert_array_equal(got[unsplit], ref[unsplit])
+    np.testing.assert_allclose(got, ref, rtol=RTOL, atol=ATOL)
+    ref_dx = oracle.wsum_bwd_dx(row_ptr.numpy(), col.numpy(), n, dy.numpy(), w.numpy())
+    np.testing.assert_allclose(dx.cpu().numpy(), ref_dx, rtol=RTOL, atol=2 * ATOL)
+    ref_dw = oracle.wsum_bwd_dw(row_ptr.numpy(), col.numpy(), dy.numpy(), x.numpy())
+    np.testing.assert_allclose(dw.cpu().numpy(), ref_dw, rtol=RTOL, atol=8 * ATOL)
+
+
+def test_config1_weighted_sum_full_size(oracle):
+    # N=16384, exactly 16 in-edges per row, F=64: the CPU-runnable configuration
+    n, degree, F = 16384, 16, 64
+    row_ptr, col = syn.fixed_degree_graph(n, degree, seed=1234)
+    gen = torch.Generator().manual_seed(1234)
+    x = torch.randn(n, F, generator=gen)
+    w = torch.rand(n * degree, generator=gen)
+    g = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=n)
+    xg, wg = x.cuda().requires_grad_(), w.cuda()[:, None].requires_grad_()
+    out = WeightedSum()(graph=g, src={"x": xg}, dst={}, edge={"weight": wg})
+    dx, dw = torch.autograd.grad(out.sum(), (xg, wg))
+    ref = oracle.wsum_fwd(row_ptr.numpy(), col.numpy(), x.numpy(), w.numpy())
+    np.testing.assert_array_equal(out.detach().cpu().numpy(), ref)
+    ones = np.ones((n, F), np.float32)
+    ref_dx = oracle.wsum_bwd_dx(row_ptr.numpy(), col.numpy(), n, ones, w.numpy())
+    np.testing.assert_array_equal(dx.cpu().numpy(), ref_dx)   # same per-source order => same bits
+    ref_dw = oracle.wsum_bwd_dw(row_ptr.numpy(), col.numpy(), ones, x.numpy())
+    assert dw.shape == (n * degree, 1)
+    np.testing.assert_allclose(dw.cpu().numpy()[:, 0], ref_dw, rtol=RTOL, atol=8 * ATOL)
+
+
+@pytest.mark.parametrize("F", (1, 7, 64, 128))
+@pytest.mark.parametrize("weighted", (True, False))
+def test_max_reducer_bit_exact(oracle, F, weighted):
+    row_ptr, col = syn.rmat_csr(9, 12, seed=11)
+    n = row_ptr.numel() - 1
+    gen = torch.Generator().manual_seed(3 + F)
+    x = torch.randn(n, F, generator=gen)
+    x[5] = float("nan")                       # NaN propagates through maximumf
+    x[7] = x[9]                               # ties: first edge wins
+    w = torch.rand(col.numel(), generator=gen) - 0.3
+    dy = torch.randn(n, F, generator=gen)
+    g = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=n)
+    xg = x.cuda().requires_grad_()
+    wg = w.cuda().requires_grad_()
+    if weighted:
+        out = WeightedMax()(graph=g, src={"x": xg}, dst={}, edge={"weight": wg})
+    else:
+        class PlainMax(tg.MessagePassing):
+            reducer = tg.max()
+
+            def edge(self, src, dst, edge):
+                return src.x
+        out = PlainMax()(graph=g, src={"x": xg}, dst={}, edge={})
+    ref, arg = oracle.max_fwd(row_ptr.numpy(), col.numpy(), x.numpy(), w.numpy() if weighted else None)
+    np.testing.assert_array_equal(out.detach().cpu().numpy(), ref)
+    plan = g.native_plan(transpose=True)
+    got, aux = ops.csr_reduce_forward(plan, "max", x.cuda(), wg.detach() if weighted else None, float("-inf"))
+    np.testing.assert_array_equal(aux.cpu().numpy().astype(np.int64), arg)
+    grads = torch.autograd.grad(out, (xg, wg) if weighted else (xg,), dy.cuda())
+    ref_dx, ref_dw = oracle.max_bwd(row_ptr.numpy(), col.numpy(), n, dy.numpy(), x.numpy(), arg,
+                                    w.numpy() if weighted else None)
+    # sources above the split threshold add partial rows, hence a tolerance
+    np.testing.assert_allclose(grads[0].cpu().numpy(), ref_dx, rtol=RTOL, atol=2 * ATOL, equal_nan=True)
+    if weighted:
+        np.testing.assert_allclose(grads[1].cpu().numpy(), ref_dw, rtol=RTOL, atol=8 * ATOL, equal_nan=True)
+
+
+def test_plan_matches_reference_transpose_and_buckets(oracle):
+    row_ptr, col = syn.rmat_csr(10, 10, seed=2)
+    n = row_ptr.numel() - 1
+    g = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=n)
+    plan = g.native_plan(transpose=True)
+    t_ptr, t_col, order = oracle.csr_transpose(row_ptr.numpy(), col.numpy(), n)
+    np.testing.assert_array_equal(plan.array(1).cpu().numpy(), t_ptr)
+    np.testing.assert_array_equal(plan.array(2).cpu().numpy().astype(np.int64), t_col)
+    np.testing.assert_array_equal(plan.array(3).cpu().numpy().astype(np.int64), order)
+    # Graph.transpose (torch stable argsort recipe of the reference) agrees
+    tp, tc = g.transpose().resolve_csr()
+    np.testing.assert_array_equal(tp.cpu().numpy(), t_ptr)
+    np.testing.assert_array_equal(tc.cpu().numpy(), t_col)
+    deg = np.diff(row_ptr.numpy())
+    lo, hi, total = oracle.degree_stats(row_ptr.numpy())
+    assert (plan.info["min_degree"], plan.info["max_degree"]) == (lo, hi)
+    assert g.degree_bounds() == (lo, hi)
+    assert plan.info["long_rows"] == int((deg > plan.info["split_threshold"]).sum())
+    seg = plan.info["segment_edges"]
+    assert plan.info["segments"] == int(np.ceil(deg[deg > plan.info["split_threshold"]] / seg).sum())
+    rows = plan.array(0).cpu().numpy()
+    assert sorted(rows.tolist()) == list(range(n))            # a permutation of the rows
+    # bucket membership: long rows first, then non-increasing power-of-two buckets, stable by id
+    def bucket(d):
+        if d > plan.info["split_threshold"]:
+            return 0
+        if d == 0:
+            return 11
+        return 10 - (0 if d == 1 else int(np.ceil(np.log2(d))))
+    keys = np.array([bucket(deg[r]) for r in rows])
+    assert np.all(np.diff(keys) >= 0)
+    for k in np.unique(keys):
+        members = rows[keys == k]
+        assert np.all(np.diff(members) > 0)
+
+
+def test_outputs_are_fresh_and_inputs_may_be_strided():
+    # tests/python/test_torch_default.py:147-162 of the reference: strided fields are accepted
+    row_ptr, col = syn.fixed_degree_graph(64, 4, seed=9)
+    g = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=64)
+    base = torch.randn(64, 16, device="cuda")
+    x = base[:, ::2]
+    w = torch.rand(256, 2, device="cuda")[:, 0]
+    kernel = WeightedSum()
+    a = kernel(graph=g, src={"x": x}, dst={}, edge={"weight": w})
+    b = kernel(graph=g, src={"x": x.contiguous()}, dst={}, edge={"weight": w.contiguous()})
+    assert torch.equal(a, b) and a.data_ptr() != b.data_ptr()
+    assert kernel.cache_info["hits"] >= 1
+
+
+def test_node_epilogue_and_params():
+    # tests/python/test_torch_default.py:64-87 of the reference
+    class BiasedSum(tg.MessagePassing):
+        def edge(self, src, dst, edge):
+            return src.x * edge.w
+
+        def node(self, dst, incoming):
+            return incoming + dst.bias
+
+    g = tg.Graph.from_csr(torch.tensor([0, 2, 3, 3]).cuda(), torch.tensor([0, 1, 1]).cuda(), num_src=2)
+    x = torch.tensor([2.0, 3.0], device="cuda", requires_grad=True)
+    w = torch.tensor([4.0, 5.0, 2.0], device="cuda", requires_grad=True)
+    bias = torch.tensor([0.1, 0.2, 0.3], device="cuda", requires_grad=True)
+    out = BiasedSum()(graph=g, src={"x": x}, dst={"bias": bias}, edge={"w": w})
+    torch.testing.assert_close(out, x.new_tensor([23.1, 6.2, 0.3]))
+    dx, dw, db = torch.autograd.grad(out.sum(), (x, w, bias))
+    assert dx.tolist() == [4.0, 7.0] and dw.tolist() == [2.0, 3.0, 3.0] and db.tolist() == [1.0, 1.0, 1.0]
+
+
+def test_in_place_change_of_saved_input_is_detected():
+    # tests/python/test_torch_default.py:90-100 of the reference
+    row_ptr, col = syn.fixed_degree_graph(32, 4, seed=1)
+    g = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=32)
+    x = torch.randn(32, 8, device="cuda", requires_grad=True)
+    w = torch.rand(128, device="cuda", requires_grad=True)
+    xx = x * 1.0
+    out = WeightedSum()(graph=g, src={"x": xx}, dst={}, edge={"weight": w})
+    xx.add_(1.0)
+    with pytest.raises(RuntimeError, match="modified by an inplace operation"):
+        out.sum().backward()
+
+
+def test_unsupported_inputs_raise():
+    row_ptr, col = syn.fixed_degree_graph(8, 2, seed=1)
+    g = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=8)
+    with pytest.raises(NotImplementedError):
+        WeightedSum()(graph=g, src={"x": torch.randn(8, 4, device="cuda", dtype=torch.float64)}, dst={},
+                      edge={"weight": torch.rand(16, device="cuda", dtype=torch.float64)})
+    with pytest.raises(ValueError):
+        WeightedSum()(graph=g, src={"x": torch.randn(7, 4, device="cuda")}, dst={},
+                      edge={"weight": torch.rand(16, device="cuda")})

@@ -1,0 +1,381 @@
+"""Logical relation object over torch tensors: ``tg.Graph``.
+
+Mirrors the Torch-facing behaviour of the reference's ``Graph``
+(python/tiga/graph/core.py:157-709,1271-1299 and its Torch twin
+python/tiga/interop/torch/graph.py:152-340,1212-1245 of walkerchi/TIGA-lang):
+the constructors ``from_csr / from_coo / regular / cu_seqlens / cat /
+triangular / dense``, ``transpose()``, ``halo()``, ``resolve_csr()``,
+``destination_index()``, the degree statistics and ``planning_key()``.
+
+CSR construction is integer work done with the same stable-sort / bincount /
+cumsum recipe as the reference, so results are bit-identical.  The per-graph
+launch plan of the CUDA library (degree buckets, split rows, transposed
+relation) is built lazily and cached on the graph.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Literal
+
+import torch
+
+from .distributed.model import ByDestination, DeviceMesh, GraphPlacement
+
+_INDEX_DTYPES = (torch.int32, torch.int64)
+_DENSE_EDGE_LIMIT = 1 << 22  # resolve_csr guard of the reference (interop/torch/graph.py:899-904)
+
+
+@dataclass(frozen=True)
+class GraphSchema:
+    num_src: int
+    num_dst: int
+    origin: str
+    lifecycle: str
+    realization: str
+    index_dtype: torch.dtype
+    sorted_by_dst: bool
+
+    def specialization_key(self) -> tuple[object, ...]:
+        return (self.num_src, self.num_dst, self.origin, self.lifecycle, self.realization,
+                str(self.index_dtype), self.sorted_by_dst)
+
+
+class Graph:
+    """Immutable relation; static CSR owns two index tensors, dense/triangular
+    and packed-sequence relations stay implicit."""
+
+    _tiga_graph = True
+
+    def __init__(self, schema: GraphSchema, *, row_ptr=None, col_idx=None, dense_boundary: str = "full",
+                 device=None, placement: GraphPlacement | None = None, cu_seqlens=None, causal: bool = True):
+        self._schema = schema
+        self._row_ptr = row_ptr
+        self._col_idx = col_idx
+        self._dense_boundary = dense_boundary
+        self._device = torch.device(device) if device is not None else (
+            row_ptr.device if row_ptr is not None else torch.device("cpu"))
+        self._placement = placement
+        self._cu_seqlens = cu_seqlens  # packed block-diagonal relation kept implicit
+        self._causal = causal
+        self._degree_bounds_cache = None
+        self._destination_cache = None
+        self._plans = {}
+        self._transpose_cache = None
+
+    # ------------------------------------------------------------ properties
+    @property
+    def schema(self) -> GraphSchema:
+        return self._schema
+
+    @property
+    def device(self) -> torch.device:
+        return self._device
+
+    @property
+    def placement(self):
+        return self._placement
+
+    @property
+    def is_distributed(self) -> bool:
+        return self._placement is not None
+
+    @property
+    def num_src(self) -> int:
+        return self._schema.num_src
+
+    @property
+    def num_dst(self) -> int:
+        return self._schema.num_dst
+
+    @property
+    def cu_seqlens_tensor(self):
+        return self._cu_seqlens
+
+    @property
+    def causal(self) -> bool:
+        return self._causal
+
+    # ---------------------------------------------------------- constructors
+    @staticmethod
+    def _validate_index_tensor(name: str, value) -> None:
+        if not isinstance(value, torch.Tensor):
+            raise TypeError(f"{name} must be a torch.Tensor")
+        if value.dtype not in _INDEX_DTYPES:
+            raise TypeError(f"{name} must have dtype int32 or int64")
+        if value.ndim != 1:
+            raise ValueError(f"{name} must be one-dimensional")
+
+    @staticmethod
+    def _validate_csr_values(row_ptr, col_idx, num_src: int) -> None:
+        if int(row_ptr[0].item()) != 0:
+            raise ValueError("row_ptr must start at zero")
+        if int(row_ptr[-1].item()) != col_idx.numel():
+            raise ValueError("row_ptr[-1] must equal the number of edges")
+        if bool(torch.any(row_ptr[1:] < row_ptr[:-1]).item()):
+            raise ValueError("row_ptr must be monotonic")
+        if col_idx.numel() and (int(col_idx.min().item()) < 0 or int(col_idx.max().item()) >= num_src):
+            raise ValueError("col_idx contains an out-of-range source index")
+
+    @classmethod
+    def from_csr(cls, row_ptr, col_idx, *, num_src: int | None = None, sorted_by_dst: bool = True,
+                 validate: Literal["basic", "full"] = "basic") -> "Graph":
+        cls._validate_index_tensor("row_ptr", row_ptr)
+        cls._validate_index_tensor("col_idx", col_idx)
+        if row_ptr.device != col_idx.device:
+            raise ValueError("row_ptr and col_idx must be on the same device")
+        if row_ptr.numel() == 0:
+            raise ValueError("row_ptr must contain at least the initial zero")
+        num_dst = row_ptr.numel() - 1
+        if num_src is None:
+            num_src = num_dst if col_idx.numel() == 0 else int(col_idx.max().item()) + 1
+        if num_src < 0:
+            raise ValueError("num_src must be non-negative")
+        if validate == "full":
+            cls._validate_csr_values(row_ptr, col_idx, num_src)
+        elif validate != "basic":
+            raise ValueError("validate must be 'basic' or 'full'")
+        schema = GraphSchema(num_src=num_src, num_dst=num_dst, origin="explicit", lifecycle="static",
+                             realization="materialized_csr", index_dtype=col_idx.dtype,
+                             sorted_by_dst=sorted_by_dst)
+        return cls(schema, row_ptr=row_ptr, col_idx=col_idx)
+
+    @classmethod
+    def from_coo(cls, src, dst, *, num_src: int | None = None, num_dst: int | None = None) -> "Graph":
+        cls._validate_index_tensor("src", src)
+        cls._validate_index_tensor("dst", dst)
+        if src.shape != dst.shape:
+            raise ValueError("src and dst must have identical shapes")
+        if src.device != dst.device:
+            raise ValueError("src and dst must be on the same device")
+        if num_src is None:
+            num_src = int(src.max().item()) + 1 if src.numel() else 0
+        if num_dst is None:
+            num_dst = int(dst.max().item()) + 1 if dst.numel() else 0
+        if not isinstance(num_src, int) or num_src < 0:
+            raise ValueError("num_src must be a non-negative integer")
+        if not isinstance(num_dst, int) or num_dst < 0:
+            raise ValueError("num_dst must be a non-negative integer")
+        if src.numel():
+            if int(src.min().item()) < 0 or int(src.max().item()) >= num_src:
+                raise ValueError("src contains an out-of-range source index")
+            if int(dst.min().item()) < 0 or int(dst.max().item()) >= num_dst:
+                raise ValueError("dst contains an out-of-range destination index")
+        order = torch.argsort(dst, stable=True)
+        sorted_dst = dst[order]
+        col_idx = src[order]
+        counts = torch.bincount(sorted_dst.to(torch.int64), minlength=num_dst)
+        row_ptr = torch.empty(num_dst + 1, device=dst.device, dtype=dst.dtype)
+        row_ptr[0] = 0
+        torch.cumsum(counts, dim=0, out=row_ptr[1:])
+        return cls.from_csr(row_ptr, col_idx, num_src=num_src, sorted_by_dst=True, validate="basic")
+
+    @classmethod
+    def regular(cls, num_nodes: int, degree: int, *, device="cpu") -> "Graph":
+        if not isinstance(num_nodes, int) or num_nodes < 1:
+            raise ValueError("num_nodes must be a positive integer")
+        if not isinstance(degree, int) or degree < 0:
+            raise ValueError("degree must be a non-negative integer")
+        row_ptr = torch.arange(num_nodes + 1, device=device, dtype=torch.int64) * degree
+        col_idx = torch.arange(num_nodes * degree, device=device, dtype=torch.int64) % num_nodes
+        return cls.from_csr(row_ptr, col_idx, num_src=num_nodes)
+
+    @classmethod
+    def cu_seqlens(cls, cu_seqlens, *, causal: bool = True) -> "Graph":
+        """Block-diagonal packed variable-length relation (flash-attn varlen
+        style).  Position i of sequence k gathers from [s_k, i] (causal) or its
+        whole sequence.  Kept implicit; ``resolve_csr()`` materialises it."""
+        cls._validate_index_tensor("cu_seqlens", cu_seqlens)
+        if not isinstance(causal, bool):
+            raise TypeError("causal must be bool")
+        if cu_seqlens.numel() == 0 or int(cu_seqlens[0].item()) != 0:
+            raise ValueError("cu_seqlens must start at zero")
+        if bool(torch.any(cu_seqlens[1:] < cu_seqlens[:-1]).item()):
+            raise ValueError("cu_seqlens must be monotonic")
+        total = int(cu_seqlens[-1].item())
+        schema = GraphSchema(num_src=total, num_dst=total, origin="packed_sequences", lifecycle="static",
+                             realization="implicit_block_dense", index_dtype=cu_seqlens.dtype,
+                             sorted_by_dst=True)
+        return cls(schema, device=cu_seqlens.device, cu_seqlens=cu_seqlens, causal=causal,
+                   dense_boundary="lower_inclusive" if causal else "full")
+
+    @classmethod
+    def dense(cls, num_src: int, num_dst: int | None = None, *, device=None, index_dtype=torch.int64) -> "Graph":
+        if num_dst is None:
+            num_dst = num_src
+        if not isinstance(num_src, int) or num_src < 0:
+            raise ValueError("num_src must be non-negative")
+        if not isinstance(num_dst, int) or num_dst < 0:
+            raise ValueError("num_dst must be non-negative")
+        if index_dtype not in _INDEX_DTYPES:
+            raise TypeError("index_dtype must be int32 or int64")
+        schema = GraphSchema(num_src=num_src, num_dst=num_dst, origin="cartesian", lifecycle="static",
+                             realization="implicit_dense", index_dtype=index_dtype, sorted_by_dst=True)
+        return cls(schema, device=device or "cpu")
+
+    @classmethod
+    def triangular(cls, num_entities: int, *, device=None, index_dtype=torch.int64) -> "Graph":
+        graph = cls.dense(num_entities, num_entities, device=device, index_dtype=index_dtype)
+        graph._schema = GraphSchema(num_src=num_entities, num_dst=num_entities, origin="lower_triangular",
+                                    lifecycle="static", realization="implicit_dense", index_dtype=index_dtype,
+                                    sorted_by_dst=True)
+        graph._dense_boundary = "lower_inclusive"
+        return graph
+
+    @classmethod
+    def cat(cls, graphs) -> "Graph":
+        """Block-diagonal composition.  A list of square triangular (or square
+        dense) blocks stays implicit as a packed-sequence relation, which is
+        what ``cat([triangular(n) for n in lengths])`` means in the reference
+        (python/tiga/graph/core.py:650-709); anything else is assembled as CSR."""
+        blocks = list(graphs)
+        if not blocks:
+            raise ValueError("graphs must be a non-empty sequence")
+        for block in blocks:
+            if not isinstance(block, Graph):
+                raise TypeError("graphs must contain only Graph instances")
+        device = blocks[0].device
+        if any(str(block.device) != str(device) for block in blocks):
+            raise ValueError("all blocks must share a device")
+        dtype = (torch.int64 if any(block.schema.index_dtype == torch.int64 for block in blocks)
+                 else torch.int32)
+        implicit = all(block.schema.realization == "implicit_dense" and block.num_src == block.num_dst
+                       for block in blocks)
+        boundaries = {block._dense_boundary for block in blocks}
+        if implicit and len(boundaries) == 1:
+            lengths = torch.tensor([0] + [block.num_dst for block in blocks], dtype=dtype)
+            cu = torch.cumsum(lengths, 0).to(dtype).to(device)
+            return cls.cu_seqlens(cu, causal=boundaries == {"lower_inclusive"})
+        row_parts = [torch.zeros(1, device=device, dtype=dtype)]
+        col_parts = []
+        edge_offset = 0
+        src_offset = 0
+        for block in blocks:
+            block_rows, block_cols = block.resolve_csr()
+            block_rows = block_rows.to(dtype)
+            col_parts.append(block_cols.to(dtype) + src_offset)
+            row_parts.append(block_rows[1:] + edge_offset)
+            edge_offset += int(block_rows[-1].item())
+            src_offset += block.schema.num_src
+        row_ptr = torch.cat(row_parts)
+        col_idx = (torch.cat(col_parts) if any(part.numel() for part in col_parts)
+                   else torch.empty(0, device=device, dtype=dtype))
+        return cls.from_csr(row_ptr, col_idx, num_src=src_offset)
+
+    # --------------------------------------------------------------- queries
+    def sequence_boundaries(self):
+        """cu_seqlens of an implicit dense / triangular / packed relation, or
+        None for a stored CSR."""
+        if self._cu_seqlens is not None:
+            return self._cu_seqlens
+        if self._schema.realization == "implicit_dense" and self.num_src == self.num_dst:
+            return torch.tensor([0, self.num_dst], dtype=self._schema.index_dtype, device=self._device)
+        return None
+
+    def resolve_csr(self):
+        if self._row_ptr is not None:
+            return self._row_ptr, self._col_idx
+        dtype = self._schema.index_dtype
+        device = self._device
+        if self._cu_seqlens is not None:
+            # Graph.cu_seqlens of the reference (interop/torch/graph.py:259-294)
+            cu = self._cu_seqlens
+            lengths = cu.diff()
+            total = int(cu[-1].item())
+            positions = torch.arange(total, device=device, dtype=dtype)
+            sequence = torch.repeat_interleave(
+                torch.arange(lengths.numel(), device=device, dtype=dtype), lengths.to(torch.int64))
+            start = cu[:-1][sequence]
+            degree = positions - start + 1 if self._causal else lengths[sequence]
+            if int(degree.sum().item()) > _DENSE_EDGE_LIMIT:
+                raise RuntimeError("refusing to materialise more than 2^22 edges of an implicit relation")
+            row_ptr = torch.cat([cu.new_zeros(1), degree.cumsum(0, dtype=dtype)])
+            repeats = degree.to(torch.int64)
+            offset = torch.arange(int(row_ptr[-1].item()), device=device, dtype=dtype)
+            col_idx = start.repeat_interleave(repeats) + (offset - row_ptr[:-1].repeat_interleave(repeats))
+        else:
+            n_src, n_dst = self.num_src, self.num_dst
+            if self._dense_boundary == "lower_inclusive":
+                degree = torch.arange(1, n_dst + 1, device=device, dtype=dtype).clamp(max=n_src)
+            else:
+                degree = torch.full((n_dst,), n_src, device=device, dtype=dtype)
+            if int(degree.sum().item()) > _DENSE_EDGE_LIMIT:
+                raise RuntimeError("refusing to materialise more than 2^22 edges of an implicit relation")
+            row_ptr = torch.cat([degree.new_zeros(1), degree.cumsum(0, dtype=dtype)])
+            offset = torch.arange(int(row_ptr[-1].item()), device=device, dtype=dtype)
+            col_idx = offset - row_ptr[:-1].repeat_interleave(degree.to(torch.int64))
+        self._row_ptr, self._col_idx = row_ptr, col_idx
+        return row_ptr, col_idx
+
+    def destination_index(self, row_ptr=None):
+        if row_ptr is None:
+            row_ptr = self.resolve_csr()[0]
+        if self._destination_cache is None or self._destination_cache[0] is not row_ptr:
+            rows = row_ptr.numel() - 1
+            destination = torch.repeat_interleave(
+                torch.arange(rows, device=row_ptr.device, dtype=row_ptr.dtype),
+                (row_ptr[1:] - row_ptr[:-1]).to(torch.int64))
+            self._destination_cache = (row_ptr, destination)
+        return self._destination_cache[1]
+
+    def implicit_edge_fields(self, row_ptr, col_idx):
+        return {}
+
+    def degree_bounds(self) -> tuple[int, int]:
+        if self._degree_bounds_cache is None:
+            row_ptr = self.resolve_csr()[0]
+            if row_ptr.numel() <= 1:
+                self._degree_bounds_cache = (0, 0)
+            else:
+                degree = row_ptr[1:] - row_ptr[:-1]
+                self._degree_bounds_cache = (int(degree.min().item()), int(degree.max().item()))
+        return self._degree_bounds_cache
+
+    def degree_statistics(self) -> tuple[int, int, int]:
+        lo, hi = self.degree_bounds()
+        row_ptr = self.resolve_csr()[0]
+        return lo, hi, int(row_ptr[-1].item()) if row_ptr.numel() else 0
+
+    def fixed_degree(self) -> int | None:
+        lo, hi = self.degree_bounds()
+        return lo if lo == hi else None
+
+    def specialization_key(self) -> tuple[object, ...]:
+        placement = self._placement.specialization_key() if self._placement is not None else ()
+        return (*self._schema.specialization_key(), self._dense_boundary, placement)
+
+    def planning_key(self) -> tuple[object, ...]:
+        if self._row_ptr is None:
+            return (*self.specialization_key(), "implicit")
+        return (*self.specialization_key(), self.degree_statistics())
+
+    def transpose(self) -> "Graph":
+        """Materialised snapshot with endpoint roles swapped (stable order)."""
+        if self._transpose_cache is None:
+            row_ptr, col_idx = self.resolve_csr()
+            destination = self.destination_index(row_ptr)
+            self._transpose_cache = type(self).from_coo(
+                destination, col_idx, num_src=self._schema.num_dst, num_dst=self._schema.num_src)
+        return self._transpose_cache
+
+    def halo(self, mesh: DeviceMesh, *, partition: ByDestination | None = None, depth="auto") -> "Graph":
+        placement = GraphPlacement(mesh, partition or ByDestination(), depth)
+        clone = object.__new__(Graph)
+        clone.__dict__ = self.__dict__.copy()
+        clone._placement = placement
+        clone._plans = {}
+        return clone
+
+    # ------------------------------------------------------------ native plan
+    def native_plan(self, *, transpose: bool):
+        """Launch plan of the CUDA library for this CSR, cached per graph."""
+        from .plan import CSRPlan
+
+        plan = self._plans.get(True) or (None if transpose else self._plans.get(False))
+        if plan is None:
+            row_ptr, col_idx = self.resolve_csr()
+            plan = CSRPlan(row_ptr, col_idx, self.num_src, transpose=transpose)
+            self._plans[transpose] = plan
+        return plan
+
+
+__all__ = ["Graph", "GraphSchema"]

@@ -1,0 +1,125 @@
+"""Thin tensor-level wrappers of the C-ABI kernels plus their autograd glue.
+
+Each wrapper passes raw device addresses and Torch's current CUDA stream to
+the library (the provider discipline of python/tiga/interop/torch/provider.py:
+8-14,170-198 of the reference: run on the caller's current stream, return a
+fresh output tensor with its own storage).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _native
+from .plan import CSRPlan
+
+_REDUCER_IDS = {"sum": _native.REDUCER_SUM, "mean": _native.REDUCER_MEAN, "max": _native.REDUCER_MAX}
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _ptr(tensor) -> int:
+    return 0 if tensor is None else tensor.data_ptr()
+
+
+def _as_rows(tensor: torch.Tensor, rows: int) -> torch.Tensor:
+    """[rows, F] contiguous float32 view of a field with arbitrary trailing dims."""
+    if tensor.dtype != torch.float32:
+        raise NotImplementedError(
+            f"the CSR reduce kernels take float32 fields, got {tensor.dtype}")
+    return tensor.contiguous().reshape(rows, -1)
+
+
+def csr_reduce_forward(plan: CSRPlan, reducer: str, x: torch.Tensor, w: torch.Tensor | None,
+                       identity: float = 0.0):
+    """out[i] = reduce over row i of w[e]*x[col[e]]; returns (out2d, argmax or None)."""
+    lib = _native.lib()
+    rid = _REDUCER_IDS[reducer]
+    F = x.shape[1]
+    out = torch.empty((plan.num_dst, F), dtype=torch.float32, device=x.device)
+    aux = torch.empty((plan.num_dst, F), dtype=torch.int32, device=x.device) if reducer == "max" else None
+    keep, scratch, scratch_bytes = plan.scratch(0, rid, F)
+    with torch.cuda.device(x.device):
+        _native.check(lib.tgb_csr_reduce_fwd(plan.handle, rid, _ptr(x), _ptr(w), _ptr(out), _ptr(aux), F,
+                                             _native.DTYPE_F32, float(identity), scratch, scratch_bytes,
+                                             _stream(x.device)), "tgb_csr_reduce_fwd")
+    return out, aux
+
+
+def csr_reduce_backward_dx(plan: CSRPlan, reducer: str, dy: torch.Tensor, w: torch.Tensor | None, aux=None):
+    lib = _native.lib()
+    rid = _REDUCER_IDS[reducer]
+    F = dy.shape[1]
+    dx = torch.empty((plan.num_src, F), dtype=torch.float32, device=dy.device)
+    keep, scratch, scratch_bytes = plan.scratch(1, rid, F)
+    with torch.cuda.device(dy.device):
+        _native.check(lib.tgb_csr_reduce_bwd_dx(plan.handle, rid, _ptr(dy), _ptr(w), _ptr(aux), _ptr(dx), F,
+                                                _native.DTYPE_F32, scratch, scratch_bytes,
+                                                _stream(dy.device)), "tgb_csr_reduce_bwd_dx")
+    return dx
+
+
+def csr_reduce_backward_dw(plan: CSRPlan, reducer: str, dy: torch.Tensor, x: torch.Tensor, aux=None):
+    lib = _native.lib()
+    rid = _REDUCER_IDS[reducer]
+    F = dy.shape[1]
+    dw = torch.empty((plan.num_edges,), dtype=torch.float32, device=dy.device)
+    keep, scratch, scratch_bytes = plan.scratch(0, rid, F)
+    with torch.cuda.device(dy.device):
+        _native.check(lib.tgb_csr_reduce_bwd_dw(plan.handle, rid, _ptr(dy), _ptr(x), _ptr(aux), _ptr(dw), F,
+                                                _native.DTYPE_F32, scratch, scratch_bytes,
+                                                _stream(dy.device)), "tgb_csr_reduce_bwd_dw")
+    return dw
+
+
+class CSRReduceFunction(torch.autograd.Function):
+    """Fused CSR gather+reduce with a native backward.
+
+    Replaces ``_CSRWeightedSumFunction`` of the reference
+    (python/tiga/interop/torch/message_passing.py:378-409), whose backward
+    replays Torch gather / mul / index_add: here dx is one gather kernel over
+    the cached transposed relation and dw one per-edge dot kernel.  Only the
+    inputs are saved (plus the winning-edge table for the max reducer)."""
+
+    @staticmethod
+    def forward(ctx, x, w, graph, reducer: str, identity: float):
+        rows_x = _as_rows(x, graph.num_src)
+        w_flat = None
+        if w is not None:
+            if w.dtype != torch.float32:
+                raise NotImplementedError(f"edge weights must be float32, got {w.dtype}")
+            w_flat = w.contiguous().reshape(-1)
+        needs_grad = x.requires_grad or (w is not None and w.requires_grad)
+        plan = graph.native_plan(transpose=bool(needs_grad and x.requires_grad))
+        out, aux = csr_reduce_forward(plan, reducer, rows_x, w_flat, identity)
+        ctx.graph = graph
+        ctx.reducer = reducer
+        ctx.x_shape = x.shape
+        ctx.w_shape = None if w is None else w.shape
+        ctx.save_for_backward(x, w, aux)
+        return out.reshape((graph.num_dst,) + tuple(x.shape[1:]))
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, w, aux = ctx.saved_tensors
+        graph = ctx.graph
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        dy = _as_rows(grad_output, graph.num_dst)
+        w_flat = None if w is None else w.contiguous().reshape(-1)
+        dx = dw = None
+        if need_x:
+            plan = graph.native_plan(transpose=True)
+            dx = csr_reduce_backward_dx(plan, ctx.reducer, dy, w_flat, aux).reshape(ctx.x_shape)
+        if need_w and w is not None:
+            plan = graph.native_plan(transpose=False)
+            dw = csr_reduce_backward_dw(plan, ctx.reducer, dy, _as_rows(x, graph.num_src), aux)
+            dw = dw.reshape(ctx.w_shape)
+        return dx, dw, None, None, None
+
+
+def csr_reduce(graph, reducer: str, x: torch.Tensor, w: torch.Tensor | None, identity: float = 0.0):
+    """Differentiable ``reduce_{e in row i} w[e] * x[col[e]]`` on the GPU."""
+    if not x.is_cuda:
+        raise RuntimeError("csr_reduce runs on CUDA tensors only (no CPU fallback)")
+    return CSRReduceFunction.apply(x, w, graph, reducer, float(identity))

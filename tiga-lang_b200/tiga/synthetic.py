@@ -1,0 +1,101 @@
+"""Seeded synthetic inputs with the shapes of the benchmark configurations.
+
+Everything is generated with integer torch ops from a counter-based hash, so
+the CPU and the GPU produce bit-identical graphs for the same seed.  The
+R-MAT generator follows the published recursive-quadrant definition
+(probabilities a, b, c, d for the (0,0), (0,1), (1,0), (1,1) quadrants of the
+(source, destination) bit pair at every level); no vertex relabelling, so hubs
+sit at low ids.  These graphs stand in for the Graph500-style cases the
+reference only plans (benchmarks/large_graphs/suite.json of the reference);
+no external generator or data set is used.
+"""
+from __future__ import annotations
+
+import torch
+
+_MASK63 = (1 << 63) - 1
+
+
+def _mix(x: torch.Tensor) -> torch.Tensor:
+    """splitmix64-style finaliser on int64 tensors (wrapping arithmetic)."""
+    def lsr(v, s):
+        return (v >> s) & ((1 << (64 - s)) - 1)
+
+    x = x + (-7046029254386353131)            # 0x9E3779B97F4A7C15 as signed
+    x = (x ^ lsr(x, 30)) * (-4658895280553007687)   # 0xBF58476D1CE4E5B9
+    x = (x ^ lsr(x, 27)) * (-7723592293110705685)   # 0x94D049BB133111EB
+    return x ^ lsr(x, 31)
+
+
+def uniform_u16(seed: int, counter: torch.Tensor, stream: int) -> torch.Tensor:
+    """Four 16-bit uniform integers per counter value: returns [4, n] int64."""
+    salt = ((seed * 1000003 + stream) * 2654435761) & _MASK63
+    h = _mix(_mix(counter + salt))
+    return torch.stack([(h >> (16 * k)) & 0xFFFF for k in range(4)])
+
+
+def rmat_edges(scale: int, num_edges: int, *, seed: int = 1, a=0.57, b=0.19, c=0.19, d=0.05, device="cpu",
+               chunk: int = 1 << 24):
+    """Directed R-MAT edge list (src, dst) as int64 tensors of length num_edges."""
+    ta = int(round(a * 65536))
+    tb = ta + int(round(b * 65536))
+    tc = tb + int(round(c * 65536))
+    srcs, dsts = [], []
+    for start in range(0, num_edges, chunk):
+        n = min(chunk, num_edges - start)
+        counter = torch.arange(start, start + n, dtype=torch.int64, device=device)
+        src = torch.zeros(n, dtype=torch.int64, device=device)
+        dst = torch.zeros(n, dtype=torch.int64, device=device)
+        for level in range(scale):
+            if level % 4 == 0:
+                draws = uniform_u16(seed, counter, level // 4)
+            r = draws[level % 4]
+            src_bit = (r >= tb).to(torch.int64)                      # quadrants c, d
+            dst_bit = (((r >= ta) & (r < tb)) | (r >= tc)).to(torch.int64)  # quadrants b, d
+            src = (src << 1) | src_bit
+            dst = (dst << 1) | dst_bit
+        srcs.append(src)
+        dsts.append(dst)
+    return torch.cat(srcs), torch.cat(dsts)
+
+
+def csr_from_pairs(src: torch.Tensor, dst: torch.Tensor, num_nodes: int, *, symmetrize: bool, dedup: bool = True):
+    """CSR by destination, sources ascending inside a row.  Self loops are kept
+    as generated."""
+    if symmetrize:
+        src, dst = torch.cat((src, dst)), torch.cat((dst, src))
+    key = dst * num_nodes + src
+    key = torch.unique(key) if dedup else torch.sort(key).values
+    dst = key // num_nodes
+    src = key - dst * num_nodes
+    counts = torch.bincount(dst, minlength=num_nodes)
+    row_ptr = torch.zeros(num_nodes + 1, dtype=torch.int64, device=key.device)
+    torch.cumsum(counts, 0, out=row_ptr[1:])
+    return row_ptr, src
+
+
+def rmat_csr(scale: int, edge_factor: int, *, seed: int = 1, symmetrize: bool = True, device="cpu"):
+    n = 1 << scale
+    src, dst = rmat_edges(scale, n * edge_factor, seed=seed, device=device)
+    return csr_from_pairs(src, dst, n, symmetrize=symmetrize)
+
+
+def gcn_norm_weights(row_ptr: torch.Tensor, col_idx: torch.Tensor) -> torch.Tensor:
+    """Symmetric GCN normalisation 1/sqrt(deg_i * deg_j), deg = CSR row length."""
+    deg = (row_ptr[1:] - row_ptr[:-1]).to(torch.float32)
+    dst = torch.repeat_interleave(torch.arange(deg.numel(), device=row_ptr.device), (row_ptr[1:] - row_ptr[:-1]))
+    return torch.rsqrt(deg[dst] * deg[col_idx])
+
+
+def normal(shape, *, seed: int, device="cpu", dtype=torch.float32, std: float = 1.0):
+    """N(0, std^2) values from a seeded CPU-or-GPU generator of that device."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    return (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std).to(dtype)
+
+
+def fixed_degree_graph(num_nodes: int, degree: int, *, seed: int = 1234, device="cpu"):
+    """Config-1 shape: exactly `degree` in-edges per row, uniform random sources."""
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    row_ptr = torch.arange(0, num_nodes * degree + 1, degree, dtype=torch.int64)
+    col_idx = torch.randint(0, num_nodes, (num_nodes * degree,), generator=gen, dtype=torch.int64)
+    return row_ptr.to(device), col_idx.to(device)
