@@ -219,11 +219,13 @@ def run_native(args):
     recording["on"] = True
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
+    torch.cuda.profiler.start()   # lets a profiler started with --profile-from-start off see only the timed steps
     begin.record()
     for _ in range(args.steps):
         grads = step(x, weight, lin)
     end.record()
     torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     recording["on"] = False
     launches = _native.launch_count() - launches_before
     clocks = sampler.stop()

@@ -134,7 +134,17 @@ def test_feature_widths_against_oracle(oracle, index_dtype, F):
     ref_dx = oracle.wsum_bwd_dx(row_ptr.numpy(), col.numpy(), n, dy.numpy(), w.numpy())
     np.testing.assert_allclose(dx.cpu().numpy(), ref_dx, rtol=RTOL, atol=2 * ATOL)
     ref_dw = oracle.wsum_bwd_dw(row_ptr.numpy(), col.numpy(), dy.numpy(), x.numpy())
-    np.testing.assert_allclose(dw.cpu().numpy(), ref_dw, rtol=RTOL, atol=8 * ATOL)
+    assert_dot_close(oracle, dw.cpu().numpy(), ref_dw, row_ptr, col, dy, x)
+
+
+def assert_dot_close(oracle, got, ref, row_ptr, col, dy, x):
+    """Per-edge dot products: rel 1e-5 / abs 1e-6 plus the rounding a different
+    summation order may introduce, 4 ulp of sum_f |dy_f * x_f| (the oracle adds
+    the F products left to right, the kernel as a tree)."""
+    magnitude = oracle.wsum_bwd_dw(row_ptr.numpy(), col.numpy(), dy.abs().numpy(), x.abs().numpy())
+    bound = RTOL * np.abs(ref) + ATOL + 4 * np.finfo(np.float32).eps * magnitude
+    error = np.abs(got - ref)
+    assert np.all(error <= bound), f"max excess {np.max(error - bound)}"
 
 
 def test_config1_weighted_sum_full_size(oracle):
@@ -155,7 +165,7 @@ def test_config1_weighted_sum_full_size(oracle):
     np.testing.assert_array_equal(dx.cpu().numpy(), ref_dx)   # same per-source order => same bits
     ref_dw = oracle.wsum_bwd_dw(row_ptr.numpy(), col.numpy(), ones, x.numpy())
     assert dw.shape == (n * degree, 1)
-    np.testing.assert_allclose(dw.cpu().numpy()[:, 0], ref_dw, rtol=RTOL, atol=8 * ATOL)
+    assert_dot_close(oracle, dw.cpu().numpy()[:, 0], ref_dw, row_ptr, col, torch.ones(n, F), x)
 
 
 @pytest.mark.parametrize("F", (1, 7, 64, 128))

@@ -22,7 +22,20 @@
 namespace tgb {
 namespace {
 
-constexpr int kBlock = 256;
+// Tunables (overridable at build time for sweeps).  Measured on B200 with the
+// GCN-layer workload: 128-thread CTAs and 4 rows in flight per lane were the
+// fastest of {128, 256} x {2, 4, 6, 8}; forcing fewer registers or a rolling
+// software pipeline was slower.
+#ifndef TGB_BLOCK
+#define TGB_BLOCK 128
+#endif
+#ifndef TGB_MIN_BLOCKS
+#define TGB_MIN_BLOCKS 1
+#endif
+#ifndef TGB_U32
+#define TGB_U32 4
+#endif
+constexpr int kBlock = TGB_BLOCK;
 
 enum Mode { kSum = 0, kMax = 2 };
 
@@ -93,7 +106,7 @@ __device__ __forceinline__ void max_update(float m, int32_t e, float &acc,
 // ---------------------------------------------------------------------------
 template <typename PtrT, typename IdxT, int G, int VPL, int U, int MODE,
           bool HAS_W, bool W_BY_EID, bool ARG_FILTER>
-__global__ void __launch_bounds__(kBlock)
+__global__ void __launch_bounds__(kBlock, TGB_MIN_BLOCKS)
 k_gather_vec(const GatherArgs a) {
   const int lane = threadIdx.x & (G - 1);
   const int64_t gid = ((int64_t)blockIdx.x * kBlock + threadIdx.x) / G;
@@ -285,7 +298,7 @@ __global__ void k_scale_by_degree(const PtrT *ptr, const float *dy, int64_t N,
 // to G results per step.  MAX keeps only elements whose winner is the edge.
 // ---------------------------------------------------------------------------
 template <typename PtrT, typename IdxT, int G, int VPL, int U, bool ARG_FILTER>
-__global__ void __launch_bounds__(kBlock)
+__global__ void __launch_bounds__(kBlock, TGB_MIN_BLOCKS)
 k_edge_dot_vec(const GatherArgs a, const float *dy, float *dw) {
   const int lane = threadIdx.x & (G - 1);
   const int64_t gid = ((int64_t)blockIdx.x * kBlock + threadIdx.x) / G;
@@ -432,7 +445,7 @@ int32_t launch_gather(const GatherArgs &a, const Shape &s, cudaStream_t stream) 
         case 4: TGB_VEC(4, 1, 4); break;
         case 8: TGB_VEC(8, 1, 4); break;
         case 16: TGB_VEC(16, 1, 4); break;
-        default: TGB_VEC(32, 1, 4); break;
+        default: TGB_VEC(32, 1, TGB_U32); break;
       }
     } else if (s.VPL == 2) {
       TGB_VEC(32, 2, 2);
@@ -475,7 +488,7 @@ int32_t launch_edge_dot(const GatherArgs &a, const Shape &s, const float *dy,
         case 4: TGB_DOT(4, 1, 4); break;
         case 8: TGB_DOT(8, 1, 4); break;
         case 16: TGB_DOT(16, 1, 4); break;
-        default: TGB_DOT(32, 1, 4); break;
+        default: TGB_DOT(32, 1, TGB_U32); break;
       }
     } else if (s.VPL == 2) {
       TGB_DOT(32, 2, 2);
