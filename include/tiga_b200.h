@@ -173,6 +173,53 @@ TGB_API int32_t tgb_csr_reduce_bwd_dw(const tgb_csr_plan *plan, int32_t reducer,
                                       int32_t dtype, void *scratch,
                                       uint64_t scratch_bytes, uint64_t stream);
 
+/* ------------------------------------------------------------------------
+ * Edge attention over CSR rows (online-softmax reducer), bf16 features.
+ *
+ * Program: s = (src.x*a_src).sum(-1) + (dst.x*a_dst).sum(-1) per head,
+ * score = maximum(s, slope*s), out = online_softmax(score, src.x).
+ * Replaces, for this program, the reference's gf_edge_nn_attention /
+ * gf_edge_nn_attention_vjp kernels (python/tiga/compiler/edge_nn_attention.py:
+ * 127-338, 344-611) and the eager evaluator it falls back to for bf16
+ * multi-head scores (python/tiga/interop/torch/message_passing.py:2848-2894,
+ * reducer_oracle.py:60-137).  x [rows, H, D] bf16 contiguous, 16-byte aligned;
+ * H*D/8 a power of two <= 32 and D/8 a power of two.
+ * ------------------------------------------------------------------------ */
+
+/* scores[n,h] = bf16(sum_d bf16(x[n,h,d]*a[h,d])) as float32 [n, H]. */
+TGB_API int32_t tgb_gat_node_scores(const void *x, const void *a, int64_t n,
+                                    int32_t H, int32_t D, void *scores,
+                                    uint64_t stream);
+
+/* Scratch bytes of tgb_gat_fwd (backward = 0) or tgb_gat_bwd (backward = 1). */
+TGB_API int32_t tgb_gat_scratch_bytes(const tgb_csr_plan *plan, int32_t H,
+                                      int32_t D, int32_t backward,
+                                      uint64_t *bytes);
+
+/* out [num_dst,H,D] bf16 (0 for an empty row, reducer_oracle.py:132-136);
+ * m, l [num_dst,H] float32 = row maximum and denominator, saved for the
+ * backward like the reference does (edge_nn_attention.py:330-334). */
+TGB_API int32_t tgb_gat_fwd(const tgb_csr_plan *plan, const void *x_src,
+                            const void *s_src, const void *s_dst, void *out,
+                            void *m, void *l, int32_t H, int32_t D, float slope,
+                            void *scratch, uint64_t scratch_bytes,
+                            uint64_t stream);
+
+/* Gradients of the program: dx_src [num_src,H,D] and dx_dst [num_dst,H,D] in
+ * bf16 (add them when one tensor plays both roles), da_src/da_dst [H,D] in
+ * float32.  No atomics: a destination-major pass writes the per-edge softmax
+ * weight and pre-activation cotangent, a source-major pass over the plan's
+ * transposed relation gathers them. */
+TGB_API int32_t tgb_gat_bwd(const tgb_csr_plan *plan, const void *x_src,
+                            const void *x_dst, const void *a_src,
+                            const void *a_dst, const void *s_src,
+                            const void *s_dst, const void *out,
+                            const void *dout, const void *m, const void *l,
+                            int32_t H, int32_t D, float slope, void *dx_src,
+                            void *dx_dst, void *da_src, void *da_dst,
+                            void *scratch, uint64_t scratch_bytes,
+                            uint64_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,124 @@
+"""GPU parity of the GAT edge-attention path (bf16, online softmax) against the
+CPU oracle and the reference-generated fixtures.  Tolerance: bf16 attention
+within rel 2e-2 (plus one bf16 ulp of the value scale, abs 2e-2)."""
+import numpy as np
+import pytest
+import torch
+
+import tiga as tg
+from tiga import synthetic as syn
+
+pytestmark = pytest.mark.gpu
+
+
+class GAT(tg.MessagePassing):
+    reducer = tg.online_softmax()
+
+    def edge(self, src, dst, edge, a_src, a_dst):
+        s = (src.x * a_src).sum(dim=-1) + (dst.x * a_dst).sum(dim=-1)
+        return self.reducer(tg.math.maximum(s, 0.2 * s), src.x)
+
+
+def bf16_tensor(bits):
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).view(torch.bfloat16).cuda()
+
+
+def to_f32(t):
+    return t.detach().float().cpu().numpy()
+
+
+def bits_of(t):
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+@pytest.mark.parametrize("graph", ("fixed16", "ragged", "hub"))
+def test_against_reference_fixtures(golden, oracle, graph):
+    key = f"gat_{graph}"
+    row_ptr = torch.from_numpy(golden[key + "_row_ptr"]).cuda()
+    col = torch.from_numpy(golden[key + "_col"]).cuda()
+    x = bf16_tensor(golden[key + "_x"]).requires_grad_()
+    a_src = bf16_tensor(golden[key + "_a_src"]).requires_grad_()
+    a_dst = bf16_tensor(golden[key + "_a_dst"]).requires_grad_()
+    g = tg.Graph.from_csr(row_ptr, col, num_src=x.shape[0])
+    kernel = GAT()
+    out = kernel(graph=g, ndata={"x": x}, a_src=a_src, a_dst=a_dst)
+    assert out.dtype == torch.bfloat16 and out.shape == x.shape
+    ref = oracle.bf16_to_f32(golden[key + "_out"])
+    np.testing.assert_allclose(to_f32(out), ref, rtol=2e-2, atol=2e-2)
+    deg = np.diff(golden[key + "_row_ptr"])
+    assert np.all(to_f32(out)[deg == 0] == 0)           # empty rows are exact zeros
+    assert "online-softmax" in kernel.last_variant.lowering
+    dy = bf16_tensor(golden[key + "_dy"])
+    dx, das, dad = torch.autograd.grad(out, (x, a_src, a_dst), dy)
+    # the fixture's gradients ran through bf16 autograd; compare with the float oracle and the fixture
+    dxs, dxd, o_das, o_dad = oracle.gat_bwd(golden[key + "_row_ptr"], golden[key + "_col"], golden[key + "_x"],
+                                            golden[key + "_x"], golden[key + "_a_src"], golden[key + "_a_dst"],
+                                            golden[key + "_dy"])
+    scale = np.abs(dxs + dxd).max()
+    np.testing.assert_allclose(to_f32(dx), dxs + dxd, rtol=2e-2, atol=2e-2 * scale)
+    np.testing.assert_allclose(to_f32(das), o_das, rtol=2e-2, atol=2e-2 * np.abs(o_das).max())
+    np.testing.assert_allclose(to_f32(dad), o_dad, rtol=2e-2, atol=2e-2 * np.abs(o_dad).max())
+    ref_dx = oracle.bf16_to_f32(golden[key + "_dx"])
+    assert np.median(np.abs(to_f32(dx) - ref_dx)) < 2e-2 * np.abs(ref_dx).mean() + 1e-3
+
+
+@pytest.mark.parametrize("H,D", ((8, 32), (4, 64), (1, 64), (8, 16), (2, 8)))
+@pytest.mark.parametrize("index_dtype", (torch.int32, torch.int64))
+def test_head_shapes_against_oracle(oracle, H, D, index_dtype):
+    row_ptr, col = syn.rmat_csr(9, 12, seed=21, symmetrize=False)   # directed, with empty rows and hubs
+    n = row_ptr.numel() - 1
+    gen = torch.Generator().manual_seed(H * 100 + D)
+    x = torch.randn(n, H, D, generator=gen).to(torch.bfloat16)
+    a_src = (0.1 * torch.randn(H, D, generator=gen)).to(torch.bfloat16)
+    a_dst = (0.1 * torch.randn(H, D, generator=gen)).to(torch.bfloat16)
+    dy = torch.randn(n, H, D, generator=gen).to(torch.bfloat16)
+    g = tg.Graph.from_csr(row_ptr.to(index_dtype).cuda(), col.to(index_dtype).cuda(), num_src=n)
+    xg = x.cuda().requires_grad_()
+    asg, adg = a_src.cuda().requires_grad_(), a_dst.cuda().requires_grad_()
+    out = GAT()(graph=g, src={"x": xg}, dst={"x": xg}, a_src=asg, a_dst=adg)
+    ref_out, m, l, score = oracle.gat_fwd(row_ptr.numpy(), col.numpy(), bits_of(x), bits_of(x), bits_of(a_src),
+                                          bits_of(a_dst))
+    np.testing.assert_allclose(to_f32(out), oracle.bf16_to_f32(ref_out), rtol=2e-2, atol=2e-2)
+    dx, das, dad = torch.autograd.grad(out, (xg, asg, adg), dy.cuda())
+    dxs, dxd, o_das, o_dad = oracle.gat_bwd(row_ptr.numpy(), col.numpy(), bits_of(x), bits_of(x), bits_of(a_src),
+                                            bits_of(a_dst), bits_of(dy))
+    want = dxs + dxd
+    np.testing.assert_allclose(to_f32(dx), want, rtol=2e-2, atol=2e-2 * np.abs(want).max())
+    np.testing.assert_allclose(to_f32(das), o_das, rtol=2e-2, atol=2e-2 * np.abs(o_das).max())
+    np.testing.assert_allclose(to_f32(dad), o_dad, rtol=2e-2, atol=2e-2 * np.abs(o_dad).max())
+
+
+def test_bipartite_roles_and_saved_state(oracle):
+    # distinct source / destination node sets, features given separately
+    n_dst, n_src, H, D = 50, 70, 8, 32
+    gen = torch.Generator().manual_seed(5)
+    deg = torch.randint(0, 9, (n_dst,), generator=gen)
+    row_ptr = torch.cat((torch.zeros(1, dtype=torch.int64), deg.cumsum(0)))
+    col = torch.randint(0, n_src, (int(row_ptr[-1]),), generator=gen)
+    xs = torch.randn(n_src, H, D, generator=gen).to(torch.bfloat16)
+    xd = torch.randn(n_dst, H, D, generator=gen).to(torch.bfloat16)
+    a_src = (0.1 * torch.randn(H, D, generator=gen)).to(torch.bfloat16)
+    a_dst = (0.1 * torch.randn(H, D, generator=gen)).to(torch.bfloat16)
+    g = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=n_src)
+    xsg, xdg = xs.cuda().requires_grad_(), xd.cuda().requires_grad_()
+    out = GAT()(graph=g, src={"x": xsg}, dst={"x": xdg}, a_src=a_src.cuda(), a_dst=a_dst.cuda())
+    ref_out, m, l, score = oracle.gat_fwd(row_ptr.numpy(), col.numpy(), bits_of(xs), bits_of(xd), bits_of(a_src),
+                                          bits_of(a_dst))
+    np.testing.assert_allclose(to_f32(out), oracle.bf16_to_f32(ref_out), rtol=2e-2, atol=2e-2)
+    dy = torch.randn(n_dst, H, D, generator=gen).to(torch.bfloat16)
+    dxs_g, dxd_g = torch.autograd.grad(out, (xsg, xdg), dy.cuda())
+    dxs, dxd, _, _ = oracle.gat_bwd(row_ptr.numpy(), col.numpy(), bits_of(xs), bits_of(xd), bits_of(a_src),
+                                    bits_of(a_dst), bits_of(dy))
+    np.testing.assert_allclose(to_f32(dxs_g), dxs, rtol=2e-2, atol=2e-2 * np.abs(dxs).max())
+    np.testing.assert_allclose(to_f32(dxd_g), dxd, rtol=2e-2, atol=2e-2 * np.abs(dxd).max() + 1e-6)
+
+
+def test_unsupported_shapes_raise():
+    row_ptr, col = syn.fixed_degree_graph(16, 2, seed=1)
+    g = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=16)
+    x = torch.randn(16, 3, 8, device="cuda").to(torch.bfloat16)     # 3 heads: not a power of two
+    a = torch.randn(3, 8, device="cuda").to(torch.bfloat16)
+    with pytest.raises(NotImplementedError):
+        GAT()(graph=g, ndata={"x": x}, a_src=a, a_dst=a)
+    with pytest.raises(NotImplementedError):
+        GAT()(graph=g, ndata={"x": x.float()}, a_src=a.float(), a_dst=a.float())

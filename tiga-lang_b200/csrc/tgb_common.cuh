@@ -99,6 +99,43 @@ __device__ __forceinline__ float mul_add_rn(float a, float b, float acc) {
   return __fadd_rn(acc, __fmul_rn(a, b));
 }
 
+// Work list of one traversal side as the kernels see it.  Thread groups
+// [0, n_seg) own segments of split rows, the rest own whole rows in bucket order.
+struct WorkList {
+  const void *ptr;
+  const void *idx;
+  const uint32_t *eid;
+  const int32_t *order;
+  const int32_t *seg_row;
+  const int32_t *seg_ptr;
+  int64_t n_rows, n_long, n_seg;
+};
+
+inline WorkList work_list(const Side &side) {
+  return WorkList{side.ptr, side.idx, side.eid, side.order, side.seg_row, side.seg_ptr,
+                  side.n_rows, side.n_long, side.n_seg};
+}
+
+template <typename PtrT>
+__device__ __forceinline__ void decode_group(const WorkList &w, int64_t gid, int64_t &row,
+                                             int64_t &beg, int64_t &end, int64_t &seg) {
+  const PtrT *ptr = static_cast<const PtrT *>(w.ptr);
+  if (gid < w.n_seg) {
+    const int32_t lr = w.seg_row[gid];
+    row = w.order[lr];
+    const int64_t k = gid - w.seg_ptr[lr];
+    const int64_t rb = (int64_t)ptr[row], re = (int64_t)ptr[row + 1];
+    beg = rb + k * kSegmentEdges;
+    end = beg + kSegmentEdges < re ? beg + kSegmentEdges : re;
+    seg = gid;
+  } else {
+    row = w.order[w.n_long + (gid - w.n_seg)];
+    beg = (int64_t)ptr[row];
+    end = (int64_t)ptr[row + 1];
+    seg = -1;
+  }
+}
+
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 

@@ -1,0 +1,101 @@
+"""Online-softmax programs on the native kernels: GAT edge attention over CSR
+rows and (dense / packed causal) relation attention.
+
+The autograd Functions save only inputs, the output and the per-row softmax
+state (m, l), like the reference's ``_EdgeNNAttentionFunction``
+(python/tiga/interop/torch/message_passing.py:193-277), and recompute per-edge
+quantities in the backward.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _native
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _gat_scratch(plan, H, D, backward, device):
+    size = ctypes.c_uint64()
+    _native.check(_native.lib().tgb_gat_scratch_bytes(plan.handle, H, D, int(backward), ctypes.byref(size)),
+                  "tgb_gat_scratch_bytes")
+    buffer = torch.empty(max(int(size.value), 256), dtype=torch.uint8, device=device)
+    return buffer, int(size.value)
+
+
+def _node_scores(x, a, H, D):
+    scores = torch.empty((x.shape[0], H), dtype=torch.float32, device=x.device)
+    _native.check(_native.lib().tgb_gat_node_scores(x.data_ptr(), a.data_ptr(), x.shape[0], H, D,
+                                                    scores.data_ptr(), _stream(x.device)), "tgb_gat_node_scores")
+    return scores
+
+
+class GATFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_src, x_dst, a_src, a_dst, graph, slope):
+        for name, t in (("src feature", x_src), ("dst feature", x_dst), ("a_src", a_src), ("a_dst", a_dst)):
+            if t.dtype != torch.bfloat16:
+                raise NotImplementedError(f"edge attention kernels take bfloat16 inputs; {name} is {t.dtype}")
+        if x_src.ndim != 3 or x_dst.shape[1:] != x_src.shape[1:] or a_src.shape != x_src.shape[1:] \
+                or a_dst.shape != x_src.shape[1:]:
+            raise NotImplementedError("edge attention expects x [N, H, D] and a_src, a_dst [H, D]")
+        H, D = x_src.shape[1], x_src.shape[2]
+        xs, xd = x_src.contiguous(), x_dst.contiguous()
+        a_s, a_d = a_src.contiguous(), a_dst.contiguous()
+        needs_grad = any(t.requires_grad for t in (x_src, x_dst, a_src, a_dst))
+        plan = graph.native_plan(transpose=needs_grad)
+        lib = _native.lib()
+        with torch.cuda.device(xs.device):
+            s_src = _node_scores(xs, a_s, H, D)
+            s_dst = s_src if (xd is xs or xd.data_ptr() == xs.data_ptr()) and a_d.data_ptr() == a_s.data_ptr() \
+                else _node_scores(xd, a_d, H, D)
+            out = torch.empty((graph.num_dst, H, D), dtype=torch.bfloat16, device=xs.device)
+            m = torch.empty((graph.num_dst, H), dtype=torch.float32, device=xs.device)
+            l = torch.empty_like(m)
+            scratch, size = _gat_scratch(plan, H, D, False, xs.device)
+            _native.check(lib.tgb_gat_fwd(plan.handle, xs.data_ptr(), s_src.data_ptr(), s_dst.data_ptr(),
+                                          out.data_ptr(), m.data_ptr(), l.data_ptr(), H, D, float(slope),
+                                          scratch.data_ptr(), size, _stream(xs.device)), "tgb_gat_fwd")
+        ctx.graph, ctx.slope = graph, float(slope)
+        ctx.save_for_backward(x_src, x_dst, a_src, a_dst, s_src, s_dst, out, m, l)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x_src, x_dst, a_src, a_dst, s_src, s_dst, out, m, l = ctx.saved_tensors
+        graph = ctx.graph
+        H, D = x_src.shape[1], x_src.shape[2]
+        plan = graph.native_plan(transpose=True)
+        xs, xd = x_src.contiguous(), x_dst.contiguous()
+        a_s, a_d = a_src.contiguous(), a_dst.contiguous()
+        dout = grad_output.contiguous().to(torch.bfloat16)
+        device = xs.device
+        dx_src = torch.empty_like(xs)
+        dx_dst = torch.empty_like(xd)
+        da_src = torch.empty((H, D), dtype=torch.float32, device=device)
+        da_dst = torch.empty_like(da_src)
+        with torch.cuda.device(device):
+            scratch, size = _gat_scratch(plan, H, D, True, device)
+            _native.check(_native.lib().tgb_gat_bwd(
+                plan.handle, xs.data_ptr(), xd.data_ptr(), a_s.data_ptr(), a_d.data_ptr(), s_src.data_ptr(),
+                s_dst.data_ptr(), out.data_ptr(), dout.data_ptr(), m.data_ptr(), l.data_ptr(), H, D, ctx.slope,
+                dx_src.data_ptr(), dx_dst.data_ptr(), da_src.data_ptr(), da_dst.data_ptr(), scratch.data_ptr(),
+                size, _stream(device)), "tgb_gat_bwd")
+        needs = ctx.needs_input_grad
+        return (dx_src if needs[0] else None, dx_dst if needs[1] else None,
+                da_src.to(a_src.dtype) if needs[2] else None, da_dst.to(a_dst.dtype) if needs[3] else None,
+                None, None)
+
+
+def gat_attention(graph, x_src, x_dst, a_src, a_dst, slope: float):
+    if not x_src.is_cuda:
+        raise RuntimeError("edge attention runs on CUDA tensors only (no CPU fallback)")
+    return GATFunction.apply(x_src, x_dst, a_src, a_dst, graph, slope)
+
+
+def varlen_attention(graph, query, key, value, scale):
+    raise NotImplementedError("the dense-relation attention kernel is not built yet")
