@@ -54,6 +54,14 @@ enum { TGB_DTYPE_F32 = 0, TGB_DTYPE_BF16 = 1 };
  * branch, lib/Target/Triton/Translate.cpp:3353-3402). */
 enum { TGB_REDUCER_SUM = 0, TGB_REDUCER_MEAN = 1, TGB_REDUCER_MAX = 2 };
 
+/* Flags of tgb_csr_reduce_fwd. */
+enum {
+  TGB_REDUCE_ACCUMULATE = 1 /* SUM only: out[i,:] += row sum; rows without edges
+                               are left untouched (second pass of a relation
+                               whose edges were split in two parts, e.g. owned
+                               and ghost sources of a halo partition) */
+};
+
 /* Plan flags. */
 enum {
   TGB_PLAN_FORWARD = 1,   /* degree-bucket work lists over the CSR rows        */
@@ -150,7 +158,7 @@ TGB_API int32_t tgb_csr_plan_scratch_bytes(const tgb_csr_plan *plan,
 TGB_API int32_t tgb_csr_reduce_fwd(const tgb_csr_plan *plan, int32_t reducer,
                                    const void *x, const void *w, void *out,
                                    void *aux, int64_t F, int32_t dtype,
-                                   float identity, void *scratch,
+                                   float identity, int32_t flags, void *scratch,
                                    uint64_t scratch_bytes, uint64_t stream);
 
 /* dx[j,:] = sum_{e: col[e]=j} w[e] * dy[dst(e),:]  as a gather over the stable

@@ -47,7 +47,7 @@ def test_argument_errors_without_gpu():
     assert lib.tgb_csr_plan_sizes(4, 4, 4, 16, 1, ctypes.byref(size), ctypes.byref(size)) == _native.INVALID_ARGUMENT
     assert b"index_bits" in lib.tgb_last_error()
     assert lib.tgb_csr_plan_sizes(1 << 31, 4, 4, 64, 1, ctypes.byref(size), ctypes.byref(size)) == _native.UNSUPPORTED
-    assert lib.tgb_csr_reduce_fwd(None, 0, None, None, None, None, 4, 0, 0.0, None, 0, 0) == _native.INVALID_ARGUMENT
+    assert lib.tgb_csr_reduce_fwd(None, 0, None, None, None, None, 4, 0, 0.0, 0, None, 0, 0) == _native.INVALID_ARGUMENT
     with pytest.raises(ValueError):
         _native.check(_native.INVALID_ARGUMENT, "probe")
 

@@ -58,6 +58,7 @@ struct GatherArgs {
   int64_t F;
   float identity;
   int mean;               // divide finished rows by their length
+  int accumulate;         // add to the rows already in `out`; rows without edges stay untouched
 };
 
 template <typename T>
@@ -122,12 +123,14 @@ k_gather_vec(const GatherArgs a) {
   const bool active = lane < vecs;           // G may exceed the row's vectors
   const float start = (seg >= 0 || a.mean) ? (MODE == kMax ? a.identity : 0.0f)
                                            : a.identity;
+  if (a.accumulate && beg == end) return;
 
   float4 acc[VPL];
   int4 arg[MODE == kMax ? VPL : 1];
 #pragma unroll
   for (int v = 0; v < VPL; ++v) {
     acc[v] = make_float4(start, start, start, start);
+    if (a.accumulate && seg < 0 && active) acc[v] = *reinterpret_cast<const float4 *>(a.out + row * F + 4 * (lane + v * G));
     if constexpr (MODE == kMax) arg[v] = make_int4(-1, -1, -1, -1);
   }
 
@@ -231,8 +234,9 @@ k_gather_scalar(const GatherArgs a) {
   const int64_t F = a.F;
   const float start = (seg >= 0 || a.mean) ? (MODE == kMax ? a.identity : 0.0f)
                                            : a.identity;
+  if (a.accumulate && beg == end) return;
   for (int64_t f = lane; f < F; f += G) {
-    float acc = start;
+    float acc = (a.accumulate && seg < 0) ? a.out[row * F + f] : start;
     int32_t arg = -1;
     for (int64_t e = beg; e < end; ++e) {
       const int64_t c = (int64_t)idx[e];
@@ -269,7 +273,7 @@ k_finalize_split(const GatherArgs a) {
   const PtrT *ptr = static_cast<const PtrT *>(a.ptr);
   const float count = (float)((int64_t)ptr[row + 1] - (int64_t)ptr[row]);
   for (int64_t f = threadIdx.x; f < a.F; f += kBlock) {
-    float acc = a.mean ? 0.0f : a.identity;
+    float acc = a.accumulate ? a.out[row * a.F + f] : (a.mean ? 0.0f : a.identity);
     int32_t arg = -1;
     for (int32_t s = s0; s < s1; ++s) {
       const float p = a.partial[(int64_t)s * a.F + f];
@@ -562,10 +566,12 @@ int32_t tgb_csr_plan_scratch_bytes(const tgb_csr_plan *plan, int32_t direction,
 int32_t tgb_csr_reduce_fwd(const tgb_csr_plan *plan, int32_t reducer,
                            const void *x, const void *w, void *out, void *aux,
                            int64_t F, int32_t dtype, float identity,
-                           void *scratch, uint64_t scratch_bytes,
+                           int32_t flags, void *scratch, uint64_t scratch_bytes,
                            uint64_t stream) {
   int32_t rc = check_common(plan, reducer, F, dtype);
   if (rc) return rc;
+  if ((flags & TGB_REDUCE_ACCUMULATE) && reducer != TGB_REDUCER_SUM)
+    TGB_FAIL(TGB_STATUS_UNSUPPORTED, "accumulation into existing rows is defined for the sum reducer only");
   if ((!x && plan->num_src > 0 && plan->num_edges > 0) || (!out && plan->num_dst > 0))
     TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null feature pointer");
   if (reducer == TGB_REDUCER_MAX && !aux && plan->num_dst > 0)
@@ -587,6 +593,7 @@ int32_t tgb_csr_reduce_fwd(const tgb_csr_plan *plan, int32_t reducer,
   a.F = F;
   a.identity = identity;
   a.mean = reducer == TGB_REDUCER_MEAN;
+  a.accumulate = (flags & TGB_REDUCE_ACCUMULATE) != 0;
   Shape s = pick_shape(F, x, out);
   if (reducer == TGB_REDUCER_MAX && s.vec && (((uintptr_t)aux | (uintptr_t)a.arg_partial) & 15u))
     s = scalar_shape(F);

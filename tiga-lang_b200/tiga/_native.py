@@ -22,6 +22,7 @@ OK, INVALID_ARGUMENT, UNSUPPORTED, OUT_OF_MEMORY, INTERNAL = range(5)
 DTYPE_F32, DTYPE_BF16 = 0, 1
 REDUCER_SUM, REDUCER_MEAN, REDUCER_MAX = 0, 1, 2
 PLAN_FORWARD, PLAN_TRANSPOSE = 1, 2
+REDUCE_ACCUMULATE = 1
 
 _u64 = ctypes.c_uint64
 _i64 = ctypes.c_int64
@@ -42,7 +43,7 @@ _SIGNATURES = {
     "tgb_csr_plan_info": (_i32, [_vp, ctypes.POINTER(_i64)]),
     "tgb_csr_plan_array": (_i32, [_vp, _i32, ctypes.POINTER(_u64), ctypes.POINTER(_i64)]),
     "tgb_csr_plan_scratch_bytes": (_i32, [_vp, _i32, _i32, _i64, _i32, ctypes.POINTER(_u64)]),
-    "tgb_csr_reduce_fwd": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _vp, _u64, _u64]),
+    "tgb_csr_reduce_fwd": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _i32, _vp, _u64, _u64]),
     "tgb_csr_reduce_bwd_dx": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i32, _vp, _u64, _u64]),
     "tgb_csr_reduce_bwd_dw": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i32, _vp, _u64, _u64]),
     "tgb_gat_node_scores": (_i32, [_vp, _vp, _i64, _i32, _i32, _vp, _u64]),

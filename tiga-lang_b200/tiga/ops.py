@@ -32,17 +32,20 @@ def _as_rows(tensor: torch.Tensor, rows: int) -> torch.Tensor:
 
 
 def csr_reduce_forward(plan: CSRPlan, reducer: str, x: torch.Tensor, w: torch.Tensor | None,
-                       identity: float = 0.0):
-    """out[i] = reduce over row i of w[e]*x[col[e]]; returns (out2d, argmax or None)."""
+                       identity: float = 0.0, accumulate_into: torch.Tensor | None = None):
+    """out[i] = reduce over row i of w[e]*x[col[e]]; returns (out2d, argmax or None).
+    With ``accumulate_into`` (sum only) the row sums are added to that tensor in place."""
     lib = _native.lib()
     rid = _REDUCER_IDS[reducer]
     F = x.shape[1]
-    out = torch.empty((plan.num_dst, F), dtype=torch.float32, device=x.device)
+    out = accumulate_into if accumulate_into is not None else torch.empty(
+        (plan.num_dst, F), dtype=torch.float32, device=x.device)
+    flags = _native.REDUCE_ACCUMULATE if accumulate_into is not None else 0
     aux = torch.empty((plan.num_dst, F), dtype=torch.int32, device=x.device) if reducer == "max" else None
     keep, scratch, scratch_bytes = plan.scratch(0, rid, F)
     with torch.cuda.device(x.device):
         _native.check(lib.tgb_csr_reduce_fwd(plan.handle, rid, _ptr(x), _ptr(w), _ptr(out), _ptr(aux), F,
-                                             _native.DTYPE_F32, float(identity), scratch, scratch_bytes,
+                                             _native.DTYPE_F32, float(identity), flags, scratch, scratch_bytes,
                                              _stream(x.device)), "tgb_csr_reduce_fwd")
     return out, aux
 
