@@ -54,6 +54,8 @@ def parse_args():
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--cpu-sample-seconds", type=float, default=15.0)
+    p.add_argument("--kernel-table", action="store_true",
+                   help="after the timed run, print a per-kernel device-time table of two more steps to stderr")
     return p.parse_args()
 
 
@@ -246,12 +248,26 @@ def run_native(args):
         "roofline": roofline, "gpu_launches": int(launches), "clocks": clocks,
     }
 
+    if args.kernel_table:
+        kernel_table(lambda: step(x, weight, lin), 0)
     if not args.no_e2e:
         result["e2e"] = run_e2e(args, step, x, weight, lin, E)
     if not args.no_cpu_baseline:
         result["cpu_baseline"] = cpu_baseline(args, row_ptr.cpu(), col.cpu(), weight.detach().cpu(),
                                               x.detach().cpu(), lin.detach().cpu(), steps=1, warmup=0)
     print(json.dumps(result), flush=True)
+
+
+def kernel_table(run, rank, steps=2):
+    """Device time per kernel over a few steps (torch profiler), for analysis only."""
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        for _ in range(steps):
+            run()
+        torch.cuda.synchronize()
+    table = prof.key_averages().table(sort_by="cuda_time_total", row_limit=28, max_name_column_width=70)
+    print(f"---- rank {rank}: device time over {steps} steps\n{table}", file=sys.stderr, flush=True)
 
 
 def instrument(ops, timings, recording):
@@ -276,7 +292,7 @@ def instrument(ops, timings, recording):
 def run_native_multi(args, rank, world, device):
     """N > 1: the same GCN layer on a graph that grows with N (weak scaling:
     2^scale * N nodes), partitioned into N contiguous destination ranges with
-    balanced edge counts; features of ghost rows are exchanged with NCCL
+    balanced cost (edges + 32 per row); features of ghost rows are exchanged with NCCL
     send/recv every step (forward) and their cotangents sent back (backward);
     the linear weights are replicated and their gradient all-reduced."""
     import math
@@ -295,7 +311,7 @@ def run_native_multi(args, rank, world, device):
     row_ptr, col = syn.rmat_csr(scale, args.edge_factor, seed=args.seed, symmetrize=True, device=device)
     N, E = row_ptr.numel() - 1, col.numel()
     graph = tg.Graph.from_csr(row_ptr, col, num_src=N).halo(
-        tg.DeviceMesh("cuda", world), partition=tg.ByDestination(balance="edges"))
+        tg.DeviceMesh("cuda", world), partition=tg.ByDestination(balance="cost"))
     runtime = DistributedRuntime(NCCLTransport(device=device))
 
     class GCNLayer(tg.MessagePassing):
@@ -354,6 +370,8 @@ def run_native_multi(args, rank, world, device):
     ms_per_step = float(elapsed.item()) / args.steps
     value = E / (ms_per_step * 1e-3) / 1e9
 
+    if args.kernel_table:
+        kernel_table(lambda: step(x, weight, lin), rank)
     stats = torch.tensor([hi - lo, e - b, int(shard.ghosts.numel()), int(shard.edges_ghost.numel())],
                          device=device, dtype=torch.int64)
     gathered = [torch.empty_like(stats) for _ in range(world)]
@@ -374,7 +392,7 @@ def run_native_multi(args, rank, world, device):
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"halo gcn-layer rmat scale={scale} (2^{args.scale} nodes per GPU) "
                                    f"edge_factor={args.edge_factor} symmetrized dedup F={F} fp32 sum+linear fwd+bwd",
-                       "num_nodes": N, "num_edges": E, "features": F, "partition": "contiguous ranges, edge-balanced",
+                       "num_nodes": N, "num_edges": E, "features": F, "partition": "contiguous ranges balancing edges + 32 per row",
                        "per_rank_edges_rows_ghosts_ghostedges": per_rank,
                        "halo_bytes_per_step_rank0": int(shard.ghosts.numel()) * F * 4 * 2,
                        "l2": "inputs exceed L2"},

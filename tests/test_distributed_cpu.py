@@ -90,7 +90,7 @@ def _worker(rank, world, port, balance, result_dir):
             out = WeightedSum()(graph=graph, src={"x": xs}, dst={}, edge={"weight": ws})
             dx, dw = torch.autograd.grad(out, (xs, ws), dy[b:e])
         halo = shard.halo_map()
-        if balance != "edges":
+        if balance == "auto":
             peers = [model.derive_halo_map(row_ptr, col, num_entities=n, world_size=world, rank=r)
                      for r in range(world)]
             requests = [[i for i in peers[p].ghost_ids if b <= i < e] for p in range(world)]
@@ -104,7 +104,7 @@ def _worker(rank, world, port, balance, result_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,balance", ((2, "auto"), (3, "auto"), (2, "edges")))
+@pytest.mark.parametrize("world,balance", ((2, "auto"), (3, "auto"), (2, "edges"), (3, "cost")))
 def test_sharded_weighted_sum_matches_single_process(tmp_path, oracle, world, balance):
     port = _free_port()
     mp.start_processes(_worker, args=(world, port, balance, str(tmp_path)), nprocs=world, join=True,
@@ -130,6 +130,6 @@ def test_sharded_weighted_sum_matches_single_process(tmp_path, oracle, world, ba
         np.testing.assert_allclose(data["dx"], ref_dx[b:e], rtol=1e-5, atol=2e-6)
         np.testing.assert_allclose(data["dw"], ref_dw[lo:hi], rtol=1e-5, atol=2e-6)
         expect_ghosts = oracle.derive_ghosts(row_ptr.numpy(), col.numpy(), n, world, rank)
-        if balance != "edges":
+        if balance == "auto":
             np.testing.assert_array_equal(data["ghosts"], expect_ghosts)
     assert covered == n

@@ -68,8 +68,8 @@ class ByDestination:
     def __post_init__(self) -> None:
         if not isinstance(self.mesh_axis, (int, str)):
             raise TypeError("mesh_axis must be an integer or a named mesh axis")
-        if self.balance not in {"edges", "entities", "auto"}:
-            raise ValueError("balance must be 'edges', 'entities', or 'auto'")
+        if self.balance not in {"edges", "entities", "auto", "cost"}:
+            raise ValueError("balance must be 'edges', 'entities', 'auto' or 'cost'")
 
     def specialization_key(self) -> tuple[object, ...]:
         return "by_destination", self.mesh_axis, self.balance
@@ -138,18 +138,29 @@ def destination_owner(entity: int, entities: int, world_size: int) -> int:
     return extra + (entity - boundary) // base if base else extra
 
 
+ROW_COST_IN_EDGES = 32  # balance="cost": one destination row weighs as much as this many edges
+
+
 def partition_bounds(entities: int, world_size: int, *, row_ptr=None, balance: str = "auto"):
     """Begin offsets of every rank plus the end: ``bounds[r]..bounds[r+1]``.
 
     ``balance='edges'`` needs ``row_ptr`` (a torch tensor) and places the cut
-    for rank r at the first row whose prefix edge count reaches r*E/W."""
-    if balance == "edges" and row_ptr is not None and entities > 0:
+    for rank r at the first row whose prefix edge count reaches r*E/W.
+    ``balance='cost'`` (an addition of this package) balances edges plus
+    ROW_COST_IN_EDGES per row: a destination row costs a pointer read, an
+    output row and its share of the node epilogue whatever its degree, which on
+    power-law graphs is what an edge-only balance gets wrong."""
+    if balance in ("edges", "cost") and row_ptr is not None and entities > 0:
         import torch
 
+        prefix = row_ptr[:-1].to(torch.int64)
         total = int(row_ptr[-1].item())
+        if balance == "cost":
+            prefix = prefix + ROW_COST_IN_EDGES * torch.arange(entities, device=row_ptr.device, dtype=torch.int64)
+            total += ROW_COST_IN_EDGES * entities
         targets = torch.tensor([(total * r) // world_size for r in range(1, world_size)],
-                               dtype=row_ptr.dtype, device=row_ptr.device)
-        cuts = torch.searchsorted(row_ptr[:-1].contiguous(), targets, right=False).tolist()
+                               dtype=torch.int64, device=row_ptr.device)
+        cuts = torch.searchsorted(prefix.contiguous(), targets, right=False).tolist()
         bounds = [0]
         for cut in cuts:
             bounds.append(min(max(int(cut), bounds[-1]), entities))
