@@ -181,6 +181,27 @@ TGB_API int32_t tgb_csr_reduce_bwd_dw(const tgb_csr_plan *plan, int32_t reducer,
                                       int32_t dtype, void *scratch,
                                       uint64_t scratch_bytes, uint64_t stream);
 
+/* Forward sum that needs no scratch buffer from the caller and performs no
+ * allocation of any kind (no counterpart in the reference: its runtime always
+ * allocates outputs and scratch itself).  Meant for callers that cannot call
+ * cudaMalloc where they need the result -- code inside a region that must not
+ * synchronise or take the allocator lock, or a host that gives a plug-in no
+ * allocator.  Computes exactly what tgb_csr_reduce_fwd(TGB_REDUCER_SUM) does.
+ *
+ * The partial rows of split rows live in an 8 MiB array inside the library
+ * image (held by every GPU that loads the library until exit), so the graph
+ * must satisfy  split-row segments x F <= 2 097 152  (tgb_csr_plan_info
+ * info[6] gives the segments); larger calls fail with TGB_STATUS_UNSUPPORTED
+ * and a message naming both numbers.  The first call on each device looks up
+ * the array's device address (cudaGetSymbolAddress); make that first call
+ * outside any stream capture.  All calls share the one array: nothing in it
+ * has to be cleared between calls (every segment rewrites its row before it is
+ * read), but two calls that overlap on the GPU, e.g. on different streams,
+ * race on it -- serialise them. */
+TGB_API int32_t tgb_csr_wsum_fwd_noalloc(const tgb_csr_plan *plan, const void *x,
+                                         const void *w, void *out, int64_t F,
+                                         float identity, uint64_t stream);
+
 /* ------------------------------------------------------------------------
  * Edge attention over CSR rows (online-softmax reducer), bf16 features.
  *

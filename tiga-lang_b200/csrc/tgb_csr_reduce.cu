@@ -708,3 +708,83 @@ int32_t tgb_csr_reduce_bwd_dw(const tgb_csr_plan *plan, int32_t reducer,
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Allocation-free forward sum.
+//
+// Some callers may not allocate device memory at the point where they need the
+// aggregation: code running inside a region where cudaMalloc is forbidden or
+// would synchronise the device (a real-time control loop, a section that holds
+// a driver-level lock, a plug-in host that hands out no allocator).  The
+// regular entry point needs a scratch buffer for the partial rows of split
+// (long) rows; this variant keeps that scratch in a fixed array that is part
+// of the library image, so the call needs nothing but its inputs and outputs.
+// ---------------------------------------------------------------------------
+#include <mutex>
+
+namespace {
+// 2 Mi floats = 8 MiB, resident on every GPU that loads the library until the
+// process exits.  Bounds (split-row segments) x (feature width).
+constexpr size_t kNoAllocScratchFloats = size_t(2) << 20;
+constexpr int kNoAllocMaxDevices = 64;
+}  // namespace
+
+static __device__ __align__(256) float g_noalloc_partials[kNoAllocScratchFloats];
+
+namespace {
+std::mutex g_noalloc_mutex;
+float *g_noalloc_address[kNoAllocMaxDevices] = {};
+
+// The array's name is only a host-side handle; the device address has to be
+// asked for, once per device, with that device current.
+int32_t noalloc_scratch_address(float **address) {
+  int device = -1;
+  TGB_CUDA(cudaGetDevice(&device));
+  if (device < 0 || device >= kNoAllocMaxDevices)
+    TGB_FAIL(TGB_STATUS_UNSUPPORTED, "device ordinal %d is outside the supported range", device);
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_address[device]) {
+    void *pointer = nullptr;
+    cudaError_t err = cudaGetSymbolAddress(&pointer, g_noalloc_partials);
+    if (err != cudaSuccess || !pointer)
+      TGB_FAIL(TGB_STATUS_INTERNAL, "cudaGetSymbolAddress(scratch) failed: %s", cudaGetErrorString(err));
+    g_noalloc_address[device] = static_cast<float *>(pointer);
+  }
+  *address = g_noalloc_address[device];
+  return TGB_STATUS_OK;
+}
+}  // namespace
+
+extern "C" int32_t tgb_csr_wsum_fwd_noalloc(const tgb_csr_plan *plan, const void *x, const void *w,
+                                            void *out, int64_t F, float identity, uint64_t stream) {
+  int32_t rc = check_common(plan, TGB_REDUCER_SUM, F, TGB_DTYPE_F32);
+  if (rc) return rc;
+  if ((!x && plan->num_src > 0 && plan->num_edges > 0) || (!out && plan->num_dst > 0))
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null feature pointer");
+  const Side &side = plan->fwd;
+  const uint64_t need = (uint64_t)side.n_seg * (uint64_t)F;
+  if (need > kNoAllocScratchFloats)
+    TGB_FAIL(TGB_STATUS_UNSUPPORTED,
+             "graph too large for the built-in scratch: %lld split-row segments x %lld features = %llu floats, "
+             "the limit is %llu (use tgb_csr_reduce_fwd with a caller-provided scratch buffer)",
+             (long long)side.n_seg, (long long)F, (unsigned long long)need,
+             (unsigned long long)kNoAllocScratchFloats);
+  float *scratch = nullptr;
+  rc = noalloc_scratch_address(&scratch);
+  if (rc) return rc;
+  GatherArgs a{};
+  fill_side(a, side);
+  a.x = (const float *)x;
+  a.w = (const float *)w;
+  a.out = (float *)out;
+  a.partial = scratch;   // every segment overwrites its whole partial row before the finalize kernel reads it
+  a.F = F;
+  a.identity = identity;
+  Shape s = pick_shape(F, x, out);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (plan->index_bits == 32)
+    return w ? launch_gather<int32_t, int32_t, kSum, true, false, false>(a, s, st)
+             : launch_gather<int32_t, int32_t, kSum, false, false, false>(a, s, st);
+  return w ? launch_gather<int64_t, int64_t, kSum, true, false, false>(a, s, st)
+           : launch_gather<int64_t, int64_t, kSum, false, false, false>(a, s, st);
+}
