@@ -190,7 +190,7 @@ def run_native(args):
 
     def step(xs, ws, ls):
         agg = layer(graph=graph, src={"x": xs}, dst={}, edge={"weight": ws})
-        out = agg @ ls
+        out = ops.dense_linear(agg, ls)
         return torch.autograd.grad(out.sum(), (xs, ws, ls))
 
     plan_start = time.perf_counter()
@@ -217,6 +217,7 @@ def run_native(args):
     recording["on"] = False
     launches = _native.launch_count() - launches_before
     clocks = sampler.stop()
+    ops.check_async_errors()
     ms_per_step = begin.elapsed_time(end) / args.steps
     value = E / (ms_per_step * 1e-3) / 1e9
 
@@ -341,7 +342,7 @@ def run_native_multi(args, rank, world, device):
     def step(xs, ws, ls):
         with runtime:
             agg = layer(graph=graph, src={"x": xs}, dst={}, edge={"weight": ws})
-        out = agg @ ls
+        out = ops.dense_linear(agg, ls)
         dx, dw, dl = torch.autograd.grad(out.sum(), (xs, ws, ls))
         dist.all_reduce(dl)
         return dx, dw, dl

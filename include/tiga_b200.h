@@ -249,6 +249,22 @@ TGB_API int32_t tgb_gat_bwd(const tgb_csr_plan *plan, const void *x_src,
                             void *scratch, uint64_t scratch_bytes,
                             uint64_t stream);
 
+/* ------------------------------------------------------------------------
+ * Dense float32 linear on the tensor cores (tcgen05, 3xTF32 split):
+ *   out[M, N] = a[M, K] @ b_t[N, K]^T
+ * The GCN layer's `aggregate @ W`, which the reference leaves to Torch user
+ * code after its kernel (SURVEY note on examples/gcn.py:20-30; the reference's
+ * own GEMM is f16-only, lib/Target/Triton/Translate.cpp:6306-6322).  b_t is
+ * the weight stored [N, K] (pass W^T for a @ W, W itself for dout @ W^T).
+ * N in {64, 128}, K in {32, 64, 96, 128}; 16-byte aligned row-major inputs.
+ * `error_flag` is one int32 in device memory (zero-initialised by the caller):
+ * every wait in the kernel is bounded, and a wait that gives up stores a
+ * non-zero code there instead of hanging.
+ * ------------------------------------------------------------------------ */
+TGB_API int32_t tgb_linear_f32(const void *a, const void *b_t, void *out,
+                               int64_t M, int32_t K, int32_t N,
+                               void *error_flag, uint64_t stream);
+
 #ifdef __cplusplus
 }
 #endif

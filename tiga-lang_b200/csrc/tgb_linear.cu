@@ -1,0 +1,256 @@
+// Dense float32 linear  out[M, N] = a[M, K] @ b_t[N, K]^T  on the 5th-generation
+// tensor cores (tcgen05.mma kind::tf32, accumulators in tensor memory) with an
+// error-compensated 3xTF32 split, so results stay within float32 tolerance:
+//   a = a_hi + a_lo (a_hi = a rounded to tf32), same for b,
+//   a*b ~= a_hi*b_hi + a_lo*b_hi + a_hi*b_lo      (dropped term <= 2^-22 |a||b|).
+// This is the GCN layer's dense linear (the reference leaves it to user Torch
+// code after the kernel; its own f16-only tt.dot GEMM is
+// lib/Target/Triton/Translate.cpp:6306-6322).
+//
+// One persistent CTA per SM.  b_t (N x K, at most 128 x 128) is loaded once,
+// split into hi/lo and kept in shared memory.  Tiles of 128 rows of `a` stream
+// through a two-stage ring: TMA loads a [128 x 32] float chunk (128-byte rows,
+// 128-byte swizzle), the CTA splits it into hi/lo in shared memory, one thread
+// issues 12 MMAs (M=128, N, K=8) per chunk, and after the last chunk the four
+// warps read the accumulator from tensor memory and store their rows.
+// Tensor-core bound in flops but HBM bound in practice: 2*M*K*4 bytes per call.
+#include "tgb_common.cuh"
+#include "tgb_tcgen05.cuh"
+
+namespace tgb {
+
+int32_t make_tensor_map_2d(CUtensorMap *map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void *base,
+                           uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
+                           uint32_t box_rows) {
+  static EncodeTiledFn encode = nullptr;
+  if (!encode) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &query);
+    if (err != cudaSuccess || query != cudaDriverEntryPointSuccess || !fn)
+      TGB_FAIL(TGB_STATUS_INTERNAL, "cuTensorMapEncodeTiled is not available from the driver");
+    encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  // The encoder is a driver call and needs the primary context bound to this
+  // thread; a thread that has made no runtime call yet (an autograd worker) has none.
+  TGB_CUDA(cudaFree(nullptr));
+  if (((uintptr_t)base & 15u) || (pitch_bytes & 15u) || box_cols * elem_bytes != 128)
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "tensor map needs a 16-byte aligned base and pitch and a 128-byte box row");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t elem_strides[2] = {1, 1};
+  CUresult rc = encode(map, dtype, 2, const_cast<void *>(base), dims, strides, box, elem_strides,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) TGB_FAIL(TGB_STATUS_INTERNAL, "cuTensorMapEncodeTiled failed with code %d", (int)rc);
+  return TGB_STATUS_OK;
+}
+
+namespace {
+
+using namespace sm100;
+
+constexpr int kTileM = 128;
+constexpr int kChunkK = 32;                       // floats per 128-byte row
+constexpr int kChunkBytes = kTileM * 128;         // [128 rows x 128 bytes]
+constexpr int kMaxChunks = 4;                     // K <= 128
+
+struct LinearSmem {
+  alignas(1024) uint8_t b_hi[kMaxChunks][kChunkBytes];
+  alignas(1024) uint8_t b_lo[kMaxChunks][kChunkBytes];
+  alignas(1024) uint8_t a_hi[2][kChunkBytes];
+  alignas(1024) uint8_t a_lo[2][kChunkBytes];
+  uint64_t full[2];       // TMA chunk landed
+  uint64_t mma_done[2];   // MMAs that read ring slot s have finished
+  uint64_t acc_done;      // accumulator of the current tile is complete
+  uint64_t b_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// hi = x rounded to tf32 (low 13 mantissa bits zero), lo = x - hi (exact)
+__device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
+  uint32_t h;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+  hi = __uint_as_float(h);
+  lo = x - hi;
+}
+
+// Element-wise split of one [rows x 128 B] chunk; the swizzle only permutes
+// 16-byte units, so the same unit index is used for the hi and the lo copy.
+__device__ __forceinline__ void split_chunk(uint8_t *hi_inplace, uint8_t *lo_out, int bytes, int tid, int threads) {
+  float4 *hi = reinterpret_cast<float4 *>(hi_inplace);
+  float4 *lo = reinterpret_cast<float4 *>(lo_out);
+  for (int i = tid; i < bytes / 16; i += threads) {
+    float4 v = hi[i], h, l;
+    split_tf32(v.x, h.x, l.x);
+    split_tf32(v.y, h.y, l.y);
+    split_tf32(v.z, h.z, l.z);
+    split_tf32(v.w, h.w, l.w);
+    hi[i] = h;
+    lo[i] = l;
+  }
+}
+
+template <int N>
+__global__ void __launch_bounds__(128, 1)
+k_linear_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                float *__restrict__ out, int64_t M, int k_chunks, int *error) {
+  extern __shared__ uint8_t smem_raw[];
+  LinearSmem &sm = *reinterpret_cast<LinearSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b_bytes = N * 128;                       // one chunk of b_t: [N rows x 128 B]
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    mbar_init(&sm.full[0], 1);
+    mbar_init(&sm.full[1], 1);
+    mbar_init(&sm.mma_done[0], 1);
+    mbar_init(&sm.mma_done[1], 1);
+    mbar_init(&sm.acc_done, 1);
+    mbar_init(&sm.b_full, 1);
+    mbar_fence_init();
+    tma_prefetch_descriptor(&map_a);
+    tma_prefetch_descriptor(&map_b);
+  }
+  __syncthreads();
+  if (warp == 0) tmem_alloc(&sm.tmem_base, N);       // N float32 columns x 128 lanes
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = sm.tmem_base;
+  volatile int *abort_flag = &sm.abort_flag;
+
+  const int64_t n_tiles = (M + kTileM - 1) / kTileM;
+  const int64_t my_tiles = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int64_t total_chunks = my_tiles * k_chunks;
+
+  // b_t: load every chunk, split once
+  if (tid == 0) {
+    mbar_arrive_expect_tx(&sm.b_full, (uint32_t)(b_bytes * k_chunks));
+    for (int kc = 0; kc < k_chunks; ++kc) tma_load_2d(sm.b_hi[kc], &map_b, kc * kChunkK, 0, &sm.b_full);
+    if (total_chunks > 0) {   // first chunk of the first tile
+      mbar_arrive_expect_tx(&sm.full[0], kChunkBytes);
+      tma_load_2d(sm.a_hi[0], &map_a, 0, (int32_t)(blockIdx.x * kTileM), &sm.full[0]);
+    }
+  }
+  mbar_wait(&sm.b_full, 0, abort_flag, error, 1);
+  for (int kc = 0; kc < k_chunks; ++kc) split_chunk(sm.b_hi[kc], sm.b_lo[kc], b_bytes, tid, 128);
+  fence_proxy_async_smem();
+  __syncthreads();
+
+  constexpr uint32_t idesc = instr_desc(kFmtTF32, kFmtTF32, kTileM, N, 0, 0);
+  int64_t it = 0;
+  for (int64_t t = 0; t < my_tiles; ++t) {
+    const int64_t row0 = (blockIdx.x + t * gridDim.x) * kTileM;
+    for (int kc = 0; kc < k_chunks; ++kc, ++it) {
+      const int s = (int)(it & 1);
+      const uint32_t use = (uint32_t)(it >> 1);
+      if (tid == 0 && it + 1 < total_chunks) {        // prefetch the next chunk into the other slot
+        const int64_t nx = it + 1;
+        const int s1 = (int)(nx & 1);
+        const uint32_t use1 = (uint32_t)(nx >> 1);
+        if (use1 >= 1) mbar_wait(&sm.mma_done[s1], (use1 - 1) & 1, abort_flag, error, 2);
+        const int kc1 = (int)(nx % k_chunks);
+        const int64_t row1 = (blockIdx.x + (nx / k_chunks) * gridDim.x) * kTileM;
+        mbar_arrive_expect_tx(&sm.full[s1], kChunkBytes);
+        tma_load_2d(sm.a_hi[s1], &map_a, kc1 * kChunkK, (int32_t)row1, &sm.full[s1]);
+      }
+      mbar_wait(&sm.full[s], use & 1, abort_flag, error, 3);
+      split_chunk(sm.a_hi[s], sm.a_lo[s], kChunkBytes, tid, 128);
+      fence_proxy_async_smem();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after_sync();
+        const uint32_t a_hi = smem_u32(sm.a_hi[s]), a_lo = smem_u32(sm.a_lo[s]);
+        const uint32_t b_hi = smem_u32(sm.b_hi[kc]), b_lo = smem_u32(sm.b_lo[kc]);
+#pragma unroll
+        for (int k = 0; k < kChunkK / 8; ++k) {       // K = 8 per MMA: 32 bytes along the row
+          const uint32_t off = k * 32;
+          const uint64_t ah = smem_desc_k_major_sw128(a_hi + off), al = smem_desc_k_major_sw128(a_lo + off);
+          const uint64_t bh = smem_desc_k_major_sw128(b_hi + off), bl = smem_desc_k_major_sw128(b_lo + off);
+          mma_tf32(tmem, al, bh, idesc, (kc | k) != 0);   // small terms first
+          mma_tf32(tmem, ah, bl, idesc, 1);
+          mma_tf32(tmem, ah, bh, idesc, 1);
+        }
+        mma_commit(&sm.mma_done[s]);
+        if (kc == k_chunks - 1) mma_commit(&sm.acc_done);
+      }
+    }
+    // epilogue: every warp reads its 32 lanes (rows) of the accumulator
+    mbar_wait(&sm.acc_done, (uint32_t)(t & 1), abort_flag, error, 4);
+    tc_fence_after_sync();
+    const int64_t row = row0 + warp * 32 + lane;
+#pragma unroll 1
+    for (int c0 = 0; c0 < N; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + c0, r);
+      tmem_ld_wait();
+      if (row < M && !*abort_flag) {
+        float4 *dst = reinterpret_cast<float4 *>(out + row * N + c0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                               __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+      }
+    }
+    tc_fence_before_sync();
+    __syncthreads();     // the next tile's first MMA overwrites the accumulator
+  }
+  // teardown: drain the ring so no TMA or MMA is in flight, then free tensor memory
+  if (tid == 0 && total_chunks > 0) {
+    const int64_t last = total_chunks - 1;
+    mbar_wait(&sm.mma_done[last & 1], (uint32_t)((last >> 1) & 1), abort_flag, error, 5);
+    if (total_chunks > 1) mbar_wait(&sm.mma_done[(last - 1) & 1], (uint32_t)(((last - 1) >> 1) & 1), abort_flag, error, 6);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, N);
+}
+
+}  // namespace
+}  // namespace tgb
+
+using namespace tgb;
+
+extern "C" int32_t tgb_linear_f32(const void *a, const void *b_t, void *out, int64_t M, int32_t K, int32_t N,
+                                  void *error_flag, uint64_t stream) {
+  if (M < 0) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "negative row count");
+  if (M == 0) return TGB_STATUS_OK;
+  if (!a || !b_t || !out || !error_flag) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
+  if ((N != 64 && N != 128) || K % 32 != 0 || K <= 0 || K > 128)
+    TGB_FAIL(TGB_STATUS_UNSUPPORTED, "tensor-core linear supports N in {64, 128} and K in {32, 64, 96, 128} (got K=%d, N=%d)", K, N);
+  if (M > (int64_t)INT32_MAX - 256) TGB_FAIL(TGB_STATUS_UNSUPPORTED, "more than 2^31 rows");
+  if ((uintptr_t)out & 15u) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "output must be 16-byte aligned");
+  CUtensorMap map_a, map_b;
+  int32_t rc = make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)M, (uint64_t)K,
+                                  (uint64_t)K * 4, 32, 128);
+  if (rc) return rc;
+  rc = make_tensor_map_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, b_t, (uint64_t)N, (uint64_t)K, (uint64_t)K * 4,
+                          32, (uint32_t)N);
+  if (rc) return rc;
+  int device = 0, sms = 0;
+  TGB_CUDA(cudaGetDevice(&device));
+  TGB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  const int64_t tiles = ceil_div(M, kTileM);
+  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  const size_t smem = sizeof(LinearSmem) + 1024;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (N == 128) {
+    static bool configured = false;
+    if (!configured) {
+      TGB_CUDA(cudaFuncSetAttribute(k_linear_3xtf32<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured = true;
+    }
+    k_linear_3xtf32<128><<<grid, 128, smem, st>>>(map_a, map_b, (float *)out, M, K / 32, (int *)error_flag);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      TGB_CUDA(cudaFuncSetAttribute(k_linear_3xtf32<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured = true;
+    }
+    k_linear_3xtf32<64><<<grid, 128, smem, st>>>(map_a, map_b, (float *)out, M, K / 32, (int *)error_flag);
+  }
+  TGB_LAUNCHED();
+  return TGB_STATUS_OK;
+}

@@ -126,3 +126,75 @@ def csr_reduce(graph, reducer: str, x: torch.Tensor, w: torch.Tensor | None, ide
     if not x.is_cuda:
         raise RuntimeError("csr_reduce runs on CUDA tensors only (no CPU fallback)")
     return CSRReduceFunction.apply(x, w, graph, reducer, float(identity))
+
+
+# --------------------------------------------------------------------------- dense linear
+_error_flags = {}
+
+
+def error_flag(device) -> torch.Tensor:
+    """One int32 per device that tensor-core kernels set when a bounded wait gives up."""
+    key = torch.device(device).index
+    if key not in _error_flags:
+        _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_flags[key]
+
+
+def check_async_errors(device=None) -> None:
+    """Synchronises and raises if a tensor-core kernel reported a timed-out wait."""
+    for key, flag in list(_error_flags.items()):
+        if device is not None and torch.device(device).index != key:
+            continue
+        code = int(flag.item())
+        if code:
+            flag.zero_()
+            raise RuntimeError(f"a tensor-core kernel gave up on a bounded wait (code {code})")
+
+
+def linear_supported(a: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (a.is_cuda and a.dtype == torch.float32 and weight.dtype == torch.float32 and a.ndim == 2
+            and weight.ndim == 2 and weight.shape[0] in (32, 64, 96, 128) and weight.shape[1] in (64, 128))
+
+
+def _linear_raw(a: torch.Tensor, b_t: torch.Tensor) -> torch.Tensor:
+    """a [M, K] @ b_t[N, K]^T on the tensor cores (3xTF32)."""
+    a, b_t = a.contiguous(), b_t.contiguous()
+    M, K = a.shape
+    N = b_t.shape[0]
+    out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    with torch.cuda.device(a.device):
+        _native.check(_native.lib().tgb_linear_f32(a.data_ptr(), b_t.data_ptr(), out.data_ptr(), M, K, N,
+                                                   error_flag(a.device).data_ptr(), _stream(a.device)),
+                      "tgb_linear_f32")
+    return out
+
+
+class DenseLinearFunction(torch.autograd.Function):
+    """out = a @ W with W [K, N]; forward and d(a) run on tcgen05, d(W) = a^T @ dout is a
+    plain library GEMM (reduction over the rows)."""
+
+    @staticmethod
+    def forward(ctx, a, weight):
+        ctx.save_for_backward(a, weight)
+        return _linear_raw(a, weight.t())
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        a, weight = ctx.saved_tensors
+        grad_output = grad_output.contiguous()
+        da = dw = None
+        if ctx.needs_input_grad[0]:
+            if weight.shape[0] in (64, 128) and weight.shape[1] % 32 == 0:
+                da = _linear_raw(grad_output, weight)
+            else:
+                da = grad_output @ weight.t()
+        if ctx.needs_input_grad[1]:
+            dw = a.t() @ grad_output
+        return da, dw
+
+
+def dense_linear(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``a @ weight`` for float32 [M, K] x [K, N] with K, N <= 128 on the tensor cores."""
+    if not linear_supported(a, weight):
+        raise NotImplementedError("dense_linear takes float32 CUDA matrices with K in {32,64,96,128}, N in {64,128}")
+    return DenseLinearFunction.apply(a, weight)
