@@ -250,6 +250,29 @@ TGB_API int32_t tgb_gat_bwd(const tgb_csr_plan *plan, const void *x_src,
                             uint64_t stream);
 
 /* ------------------------------------------------------------------------
+ * Dense-relation attention (online-softmax reducer over an implicit dense or
+ * lower-triangular relation), packed variable-length sequences, bf16, on the
+ * tensor cores (tcgen05 + tensor memory, TMA loads).
+ * Replaces gf_dense_streaming_reduce (lib/Target/Triton/Translate.cpp:
+ * 1603-1912) and _execute_structured_dense (python/tiga/interop/torch/
+ * message_passing.py:1910-2020); the packed relation is Graph.cu_seqlens /
+ * Graph.cat of triangular blocks (python/tiga/graph/core.py:314-351,650-709),
+ * which the reference materialises edge by edge and evaluates eagerly.
+ *   q, k, v, out  [tokens, H, D] bf16 contiguous, D in {64, 128}
+ *   lse           [tokens, H] float32: log-sum-exp of the scaled scores
+ *   tiles         int32 [n_tiles, 4] = {first query, sequence begin, sequence
+ *                 end, 0}: the 128-query tiles of every sequence (heaviest
+ *                 first for load balance)
+ *   causal        1: query i attends keys seq_begin..i; 0: its whole sequence
+ * error_flag: one zero-initialised int32 in device memory (bounded waits).
+ * ------------------------------------------------------------------------ */
+TGB_API int32_t tgb_varlen_attn_fwd(const void *q, const void *k, const void *v,
+                                    void *out, void *lse, const void *tiles,
+                                    int64_t n_tiles, int64_t tokens, int32_t H,
+                                    int32_t D, float scale, int32_t causal,
+                                    void *error_flag, uint64_t stream);
+
+/* ------------------------------------------------------------------------
  * Dense float32 linear on the tensor cores (tcgen05, 3xTF32 split):
  *   out[M, N] = a[M, K] @ b_t[N, K]^T
  * The GCN layer's `aggregate @ W`, which the reference leaves to Torch user

@@ -1,0 +1,290 @@
+// Dense-relation attention with the online-softmax reducer over packed
+// variable-length sequences (causal or full inside each sequence), bf16 inputs,
+// float32 softmax state, on the 5th-generation tensor cores.
+//
+// It is the reference's streaming kernel gf_dense_streaming_reduce
+// (lib/Target/Triton/Translate.cpp:1603-1912: S = Q K^T * scale * log2e, causal
+// mask src <= row, online softmax with exp2, O += P V, O / l) rebuilt for
+// sm_100a, extended to bf16, to a block-diagonal (cu_seqlens) relation that is
+// never materialised (Graph.cu_seqlens / Graph.cat of triangular blocks,
+// python/tiga/graph/core.py:314-351,650-709), and to a backward pass, which the
+// reference does not have.
+//
+// Forward, one CTA (128 threads) per (128-query tile, head):
+//   TMA loads Q once and K/V blocks of 128 keys into a two-stage ring
+//   (128-byte rows, 128-byte swizzle; a 128-wide head is two 64-column boxes);
+//   one thread issues tcgen05.mma: S = Q K^T into tensor memory; the four warps
+//   read their 32 rows of S, keep the running max / denominator in registers,
+//   write P as bf16 into a swizzled shared-memory tile; a second MMA group
+//   computes P V into tensor memory (V is consumed MN-major as loaded) and the
+//   threads fold it into their float32 output row with the rescale factor.
+// Tensor-core bound: 4*D flops per (query, key) pair forward.
+#include <cuda_bf16.h>
+
+#include "tgb_common.cuh"
+#include "tgb_tcgen05.cuh"
+
+namespace tgb {
+namespace {
+
+using namespace sm100;
+
+constexpr int kTile = 128;                 // queries per CTA and keys per block
+constexpr int kBoxBytes = kTile * 128;     // one TMA box: 128 rows x 128 bytes (64 bf16)
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// Writes 8 consecutive bf16 of row `r`, 16-byte chunk `chunk` (0..7) of a
+// K-major tile of 128-byte rows with the 128-byte swizzle.
+__device__ __forceinline__ void store_swizzled_chunk(uint8_t *tile, int r, int chunk, uint4 value) {
+  *reinterpret_cast<uint4 *>(tile + r * 128 + ((chunk ^ (r & 7)) << 4)) = value;
+}
+
+struct Tile {           // one 128-query tile of one sequence
+  int32_t q_begin;      // first query (token index)
+  int32_t seq_begin;    // first token of the sequence
+  int32_t seq_end;      // one past the last token of the sequence
+  int32_t reserved;
+};
+
+template <int HALVES>   // head width = 64 * HALVES
+struct FwdSmem {
+  alignas(1024) uint8_t q[HALVES][kBoxBytes];
+  alignas(1024) uint8_t k[2][HALVES][kBoxBytes];
+  alignas(1024) uint8_t v[2][HALVES][kBoxBytes];
+  alignas(1024) uint8_t p[2][kBoxBytes];          // keys 0-63 and 64-127
+  uint64_t q_full, kv_full[2], s_done, o_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int HALVES>
+__global__ void __launch_bounds__(128, 1)
+k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+           const __grid_constant__ CUtensorMap map_v, const Tile *__restrict__ tiles, int H,
+           float scale_log2, int causal, __nv_bfloat16 *__restrict__ out, float *__restrict__ lse, int *error) {
+  constexpr int D = 64 * HALVES;
+  extern __shared__ uint8_t smem_raw[];
+  FwdSmem<HALVES> &sm =
+      *reinterpret_cast<FwdSmem<HALVES> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const Tile tile = tiles[blockIdx.x / H];
+  const int head = blockIdx.x % H;
+  const int row = warp * 32 + lane;                 // query row of this thread inside the tile
+  const int q_index = tile.q_begin + row;
+  const int key_limit = causal ? min(tile.q_begin + kTile, tile.seq_end) : tile.seq_end;
+  const int n_blocks = (key_limit - tile.seq_begin + kTile - 1) / kTile;
+
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    mbar_init(&sm.q_full, 1);
+    mbar_init(&sm.kv_full[0], 1);
+    mbar_init(&sm.kv_full[1], 1);
+    mbar_init(&sm.s_done, 1);
+    mbar_init(&sm.o_done, 1);
+    mbar_fence_init();
+    tma_prefetch_descriptor(&map_q);
+    tma_prefetch_descriptor(&map_k);
+    tma_prefetch_descriptor(&map_v);
+  }
+  __syncthreads();
+  if (warp == 0) tmem_alloc(&sm.tmem_base, 256);    // S: columns 0-127, P V: columns 128-255
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_s = sm.tmem_base, tmem_o = sm.tmem_base + 128;
+  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+  volatile int *abort_flag = &sm.abort_flag;
+
+  auto load_kv = [&](int block, int stage) {
+    const int y = tile.seq_begin + block * kTile;
+    mbar_arrive_expect_tx(&sm.kv_full[stage], 2 * HALVES * kBoxBytes);
+#pragma unroll
+    for (int j = 0; j < HALVES; ++j) {
+      tma_load_2d(sm.k[stage][j], &map_k, head * D + 64 * j, y, &sm.kv_full[stage]);
+      tma_load_2d(sm.v[stage][j], &map_v, head * D + 64 * j, y, &sm.kv_full[stage]);
+    }
+  };
+  if (tid == 0) {
+    mbar_arrive_expect_tx(&sm.q_full, HALVES * kBoxBytes);
+#pragma unroll
+    for (int j = 0; j < HALVES; ++j) tma_load_2d(sm.q[j], &map_q, head * D + 64 * j, tile.q_begin, &sm.q_full);
+    load_kv(0, 0);
+  }
+
+  constexpr uint32_t idesc_s = instr_desc(kFmtBF16, kFmtBF16, kTile, kTile, 0, 0);
+  constexpr uint32_t idesc_o = instr_desc(kFmtBF16, kFmtBF16, kTile, D, 0, 1);   // V is MN-major
+  float m = -INFINITY, l = 0.0f;
+  float o[D];
+#pragma unroll
+  for (int d = 0; d < D; ++d) o[d] = 0.0f;
+
+  mbar_wait(&sm.q_full, 0, abort_flag, error, 11);
+  for (int kb = 0; kb < n_blocks; ++kb) {
+    const int st = kb & 1;
+    const int key0 = tile.seq_begin + kb * kTile;
+    if (tid == 0 && kb + 1 < n_blocks) load_kv(kb + 1, st ^ 1);   // its previous reader finished last iteration
+    mbar_wait(&sm.kv_full[st], (uint32_t)((kb >> 1) & 1), abort_flag, error, 12);
+    if (tid == 0) {
+      tc_fence_after_sync();
+#pragma unroll
+      for (int k16 = 0; k16 < D / 16; ++k16) {       // 16 bf16 = 32 bytes of the 128-byte row per MMA
+        const int j = k16 >> 2;
+        const uint32_t off = (k16 & 3) * 32;
+        mma_f16(tmem_s, smem_desc_k_major_sw128(smem_u32(sm.q[j]) + off),
+                smem_desc_k_major_sw128(smem_u32(sm.k[st][j]) + off), idesc_s, k16 != 0);
+      }
+      mma_commit(&sm.s_done);
+    }
+    mbar_wait(&sm.s_done, (uint32_t)(kb & 1), abort_flag, error, 13);
+    tc_fence_after_sync();
+
+    const bool masked = (key0 + kTile > tile.seq_end) || (causal && key0 + kTile - 1 > tile.q_begin);
+    // pass A: row maximum
+    float block_max = -INFINITY;
+#pragma unroll 1
+    for (int c0 = 0; c0 < kTile; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld_32x32(tmem_s + lane_base + c0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const int key = key0 + c0 + c;
+        const bool valid = !masked || (key < tile.seq_end && (!causal || key <= q_index));
+        if (valid) block_max = fmaxf(block_max, __uint_as_float(r[c]));
+      }
+    }
+    const float m_new = fmaxf(m, block_max * scale_log2);
+    const float alpha = m == -INFINITY ? 0.0f : fast_exp2(m - m_new);
+    const float m_use = m_new == -INFINITY ? 0.0f : m_new;     // a fully masked row keeps p = 0
+    // pass B: p = 2^(s - m), written as bf16 for the second MMA
+    float block_sum = 0.0f;
+#pragma unroll 1
+    for (int c0 = 0; c0 < kTile; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld_32x32(tmem_s + lane_base + c0, r);
+      tmem_ld_wait();
+      float p[32];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const int key = key0 + c0 + c;
+        const bool valid = !masked || (key < tile.seq_end && (!causal || key <= q_index));
+        p[c] = valid ? fast_exp2(__uint_as_float(r[c]) * scale_log2 - m_use) : 0.0f;
+        block_sum += p[c];
+      }
+      uint8_t *half = sm.p[c0 >> 6];
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+        store_swizzled_chunk(half, row, ((c0 & 63) >> 3) + g,
+                             make_uint4(pack_bf16(p[8 * g], p[8 * g + 1]), pack_bf16(p[8 * g + 2], p[8 * g + 3]),
+                                        pack_bf16(p[8 * g + 4], p[8 * g + 5]), pack_bf16(p[8 * g + 6], p[8 * g + 7])));
+    }
+    l = l * alpha + block_sum;
+    m = m_new;
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+#pragma unroll
+      for (int k16 = 0; k16 < kTile / 16; ++k16) {   // 16 keys per MMA
+        const uint64_t a_desc = smem_desc_k_major_sw128(smem_u32(sm.p[k16 >> 2]) + (k16 & 3) * 32);
+        const uint64_t b_desc = smem_desc_mn_major_sw128(smem_u32(sm.v[st][0]) + k16 * 16 * 128, kBoxBytes);
+        mma_f16(tmem_o, a_desc, b_desc, idesc_o, k16 != 0);
+      }
+      mma_commit(&sm.o_done);
+    }
+#pragma unroll
+    for (int d = 0; d < D; ++d) o[d] *= alpha;       // overlaps the MMA
+    mbar_wait(&sm.o_done, (uint32_t)(kb & 1), abort_flag, error, 14);
+    tc_fence_after_sync();
+#pragma unroll
+    for (int c0 = 0; c0 < D; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld_32x32(tmem_o + lane_base + c0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 32; ++c) o[c0 + c] += __uint_as_float(r[c]);
+    }
+    tc_fence_before_sync();
+  }
+
+  if (q_index < tile.seq_end && !*abort_flag) {
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    __nv_bfloat16 *dst = out + ((int64_t)q_index * H + head) * D;
+#pragma unroll
+    for (int d = 0; d < D; d += 8)
+      *reinterpret_cast<uint4 *>(dst + d) =
+          make_uint4(pack_bf16(o[d] * inv, o[d + 1] * inv), pack_bf16(o[d + 2] * inv, o[d + 3] * inv),
+                     pack_bf16(o[d + 4] * inv, o[d + 5] * inv), pack_bf16(o[d + 6] * inv, o[d + 7] * inv));
+    lse[(int64_t)q_index * H + head] = l > 0.0f ? (m + log2f(l)) * kLn2 : -INFINITY;
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(sm.tmem_base, 256);
+}
+
+int32_t check_attn(const void *q, const void *k, const void *v, int64_t tokens, int32_t H, int32_t D) {
+  if (!q || !k || !v) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
+  if (H <= 0 || tokens < 0) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "invalid shape");
+  if (D != 64 && D != 128) TGB_FAIL(TGB_STATUS_UNSUPPORTED, "dense attention supports head widths 64 and 128 (got %d)", D);
+  if (tokens > (int64_t)INT32_MAX - 256) TGB_FAIL(TGB_STATUS_UNSUPPORTED, "too many tokens");
+  return TGB_STATUS_OK;
+}
+
+int32_t head_map(CUtensorMap *map, const void *base, int64_t tokens, int32_t H, int32_t D) {
+  return make_tensor_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, (uint64_t)tokens, (uint64_t)H * D,
+                            (uint64_t)H * D * 2, 64, kTile);
+}
+
+}  // namespace
+}  // namespace tgb
+
+using namespace tgb;
+
+extern "C" int32_t tgb_varlen_attn_fwd(const void *q, const void *k, const void *v, void *out, void *lse,
+                                       const void *tiles, int64_t n_tiles, int64_t tokens, int32_t H, int32_t D,
+                                       float scale, int32_t causal, void *error_flag, uint64_t stream) {
+  int32_t rc = check_attn(q, k, v, tokens, H, D);
+  if (rc) return rc;
+  if (n_tiles == 0) return TGB_STATUS_OK;
+  if (!out || !lse || !tiles || !error_flag) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
+  CUtensorMap map_q, map_k, map_v;
+  if ((rc = head_map(&map_q, q, tokens, H, D))) return rc;
+  if ((rc = head_map(&map_k, k, tokens, H, D))) return rc;
+  if ((rc = head_map(&map_v, v, tokens, H, D))) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const unsigned grid = (unsigned)(n_tiles * H);
+  const float scale_log2 = scale * kLog2e;
+  if (D == 128) {
+    const size_t smem = sizeof(FwdSmem<2>) + 1024;
+    static bool configured = false;
+    if (!configured) {
+      TGB_CUDA(cudaFuncSetAttribute(k_attn_fwd<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured = true;
+    }
+    k_attn_fwd<2><<<grid, 128, smem, st>>>(map_q, map_k, map_v, (const Tile *)tiles, H, scale_log2, causal,
+                                           (__nv_bfloat16 *)out, (float *)lse, (int *)error_flag);
+  } else {
+    const size_t smem = sizeof(FwdSmem<1>) + 1024;
+    static bool configured = false;
+    if (!configured) {
+      TGB_CUDA(cudaFuncSetAttribute(k_attn_fwd<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured = true;
+    }
+    k_attn_fwd<1><<<grid, 128, smem, st>>>(map_q, map_k, map_v, (const Tile *)tiles, H, scale_log2, causal,
+                                           (__nv_bfloat16 *)out, (float *)lse, (int *)error_flag);
+  }
+  TGB_LAUNCHED();
+  return TGB_STATUS_OK;
+}

@@ -97,5 +97,58 @@ def gat_attention(graph, x_src, x_dst, a_src, a_dst, slope: float):
     return GATFunction.apply(x_src, x_dst, a_src, a_dst, graph, slope)
 
 
+def _attention_tiles(graph, device):
+    """int32 [n_tiles, 4] = (first query, sequence begin, sequence end, 0) for every
+    128-query tile of every sequence, heaviest (most key blocks) first."""
+    cached = graph.__dict__.get("_attention_tiles")
+    if cached is not None and cached[0].device == device:
+        return cached
+    bounds = graph.sequence_boundaries().tolist()
+    causal = graph._dense_boundary == "lower_inclusive"
+    rows = []
+    for begin, end in zip(bounds[:-1], bounds[1:]):
+        for q0 in range(begin, end, 128):
+            blocks = ((min(q0 + 128, end) if causal else end) - begin + 127) // 128
+            rows.append((blocks, q0, begin, end))
+    rows.sort(key=lambda r: -r[0])
+    table = torch.tensor([[q0, b, e, 0] for _, q0, b, e in rows], dtype=torch.int32).reshape(-1, 4).to(device)
+    graph.__dict__["_attention_tiles"] = (table, causal)
+    return table, causal
+
+
+class VarlenAttentionFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, query, key, value, graph, scale):
+        from . import ops
+
+        for name, t in (("query", query), ("key", key), ("value", value)):
+            if t.dtype != torch.bfloat16:
+                raise NotImplementedError(f"dense attention kernels take bfloat16 inputs; {name} is {t.dtype}")
+            if t.ndim != 3 or t.shape != query.shape:
+                raise NotImplementedError("dense attention expects query, key, value of one shape [tokens, H, D]")
+        tokens, H, D = query.shape
+        if tokens != graph.num_dst:
+            raise ValueError(f"fields must have {graph.num_dst} rows, got {tokens}")
+        q, k, v = query.contiguous(), key.contiguous(), value.contiguous()
+        tiles, causal = _attention_tiles(graph, q.device)
+        out = torch.empty_like(q)
+        lse = torch.empty((tokens, H), dtype=torch.float32, device=q.device)
+        with torch.cuda.device(q.device):
+            _native.check(_native.lib().tgb_varlen_attn_fwd(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), tiles.data_ptr(),
+                tiles.shape[0], tokens, H, D, float(scale), int(causal), ops.error_flag(q.device).data_ptr(),
+                _stream(q.device)), "tgb_varlen_attn_fwd")
+        ctx.graph, ctx.scale = graph, float(scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        raise NotImplementedError("the dense attention backward kernel is not built yet")
+
+
 def varlen_attention(graph, query, key, value, scale):
-    raise NotImplementedError("the dense-relation attention kernel is not built yet")
+    """softmax(q k^T * scale [+ causal]) v inside every sequence of a packed batch."""
+    if not query.is_cuda:
+        raise RuntimeError("dense attention runs on CUDA tensors only (no CPU fallback)")
+    return VarlenAttentionFunction.apply(query, key, value, graph, scale)
