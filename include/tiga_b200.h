@@ -272,6 +272,23 @@ TGB_API int32_t tgb_varlen_attn_fwd(const void *q, const void *k, const void *v,
                                     int32_t D, float scale, int32_t causal,
                                     void *error_flag, uint64_t stream);
 
+/* Gradients of tgb_varlen_attn_fwd (no counterpart in the reference, whose
+ * dense path is forward only: python/tiga/interop/torch/message_passing.py:
+ * 1910-2020 returns without an autograd Function).  dq, dk, dv [tokens, H, D]
+ * bf16; delta is scratch, float32 [tokens, H]; query_tiles as in the forward,
+ * key_tiles the same tiles ordered for the key-major kernel (field 0 = first
+ * key of the tile).  No atomics: dK/dV are accumulated per key tile over the
+ * query blocks that see it, dQ per query tile over its key blocks. */
+TGB_API int32_t tgb_varlen_attn_bwd(const void *q, const void *k, const void *v,
+                                    const void *out, const void *dout,
+                                    const void *lse, void *dq, void *dk,
+                                    void *dv, void *delta,
+                                    const void *query_tiles,
+                                    const void *key_tiles, int64_t n_tiles,
+                                    int64_t tokens, int32_t H, int32_t D,
+                                    float scale, int32_t causal,
+                                    void *error_flag, uint64_t stream);
+
 /* ------------------------------------------------------------------------
  * Dense float32 linear on the tensor cores (tcgen05, 3xTF32 split):
  *   out[M, N] = a[M, K] @ b_t[N, K]^T

@@ -55,3 +55,26 @@ def test_cat_of_triangular_blocks_is_the_same_relation(oracle):
     ref, _ = oracle.varlen_attn_fwd(cu.numpy(), q.float().numpy(), k.float().numpy(), v.float().numpy(), 0.1)
     np.testing.assert_allclose(out.float().cpu().numpy(), ref, rtol=2e-2, atol=2e-2)
     ops.check_async_errors()
+
+
+@pytest.mark.parametrize("lengths,H,D", (
+    ([5, 1, 9, 16], 2, 128),
+    ([300, 129, 127, 513], 2, 128),
+    ([700, 40], 3, 64),
+))
+@pytest.mark.parametrize("causal", (True, False))
+def test_backward_matches_oracle(oracle, lengths, H, D, causal):
+    q, k, v, cu = make_inputs(lengths, H, D, seed=7 + D)
+    gen = torch.Generator().manual_seed(11)
+    dy = torch.randn(q.shape, generator=gen).to(torch.bfloat16)
+    scale = D ** -0.5
+    graph = tg.Graph.cu_seqlens(cu.cuda(), causal=causal)
+    qg, kg, vg = (t.cuda().requires_grad_() for t in (q, k, v))
+    out = Attention()(graph=graph, src={"key": kg, "value": vg}, dst={"query": qg}, scale=scale)
+    dq, dk, dv = torch.autograd.grad(out, (qg, kg, vg), dy.cuda())
+    ops.check_async_errors()
+    qf, kf, vf = q.float().numpy(), k.float().numpy(), v.float().numpy()
+    ref_out, _ = oracle.varlen_attn_fwd(cu.numpy(), qf, kf, vf, scale, causal=causal)
+    rq, rk, rv = oracle.varlen_attn_bwd(cu.numpy(), qf, kf, vf, ref_out, dy.float().numpy(), scale, causal=causal)
+    for got, ref in ((dq, rq), (dk, rk), (dv, rv)):
+        np.testing.assert_allclose(got.float().cpu().numpy(), ref, rtol=2e-2, atol=2e-2 * np.abs(ref).max())

@@ -234,6 +234,340 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   if (warp == 0) tmem_dealloc(sm.tmem_base, 256);
 }
 
+// ---------------------------------------------------------------------------
+// Backward.  delta[i,h] = <dO[i,h,:], O[i,h,:]>; with P = exp(S*scale - lse):
+//   dV = P^T dO,  dP = dO V^T,  dS = P o (dP - delta),  dQ = scale dS K,  dK = scale dS^T Q.
+// Two kernels, both without atomics:
+//   k_attn_bwd_dkv  one CTA per (128-key tile, head), loops over the query
+//                   blocks that see those keys; works on the TRANSPOSED score
+//                   tile (rows = keys), so every thread owns one key row of the
+//                   dV / dK accumulators in tensor memory (S^T, dP^T, dV, dK:
+//                   512 columns);
+//   k_attn_bwd_dq   one CTA per (128-query tile, head), loops over key blocks
+//                   (S, dP, dQ in tensor memory).
+// Every operand is used in the orientation TMA delivers it: [rows, D] tiles are
+// K-major for the score products and MN-major for the gradient products.
+// ---------------------------------------------------------------------------
+__global__ void k_attn_delta(const __nv_bfloat16 *__restrict__ o, const __nv_bfloat16 *__restrict__ d_o,
+                             int64_t rows, int D, float *__restrict__ delta) {
+  const int lane = threadIdx.x & 31;
+  const int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (r >= rows) return;
+  float acc = 0.0f;
+  for (int d = lane * 2; d < D; d += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(o + r * D + d));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(d_o + r * D + d));
+    acc = fmaf(a.x, b.x, fmaf(a.y, b.y, acc));
+  }
+  for (int s = 16; s; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (lane == 0) delta[r] = acc;
+}
+
+template <int HALVES>
+struct BwdSmem {
+  alignas(1024) uint8_t fixed_a[HALVES][kBoxBytes];   // dkv: K tile      dq: Q tile
+  alignas(1024) uint8_t fixed_b[HALVES][kBoxBytes];   // dkv: V tile      dq: dO tile
+  alignas(1024) uint8_t stream_a[HALVES][kBoxBytes];  // dkv: Q block     dq: K block
+  alignas(1024) uint8_t stream_b[HALVES][kBoxBytes];  // dkv: dO block    dq: V block
+  alignas(1024) uint8_t p[2][kBoxBytes];              // dkv: P^T         dq: unused
+  alignas(1024) uint8_t ds[2][kBoxBytes];             // dkv: dS^T        dq: dS
+  float lse2[kTile];
+  float delta[kTile];
+  uint64_t fixed_full, stream_full, s_done, acc_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// [128 x 128] score-like product of two K-major tiles of width D into `tmem`
+template <int HALVES>
+__device__ __forceinline__ void issue_scores(uint32_t tmem, uint8_t (*a)[kBoxBytes], uint8_t (*b)[kBoxBytes],
+                                             uint32_t idesc) {
+#pragma unroll
+  for (int k16 = 0; k16 < HALVES * 4; ++k16) {
+    const uint32_t off = (k16 & 3) * 32;
+    mma_f16(tmem, smem_desc_k_major_sw128(smem_u32(a[k16 >> 2]) + off),
+            smem_desc_k_major_sw128(smem_u32(b[k16 >> 2]) + off), idesc, k16 != 0);
+  }
+}
+
+// [128 x D] += A[128 x 128] (K-major halves of 64 columns) * B[128 rows x D] (MN-major as loaded)
+__device__ __forceinline__ void issue_gradient(uint32_t tmem, uint8_t (*a)[kBoxBytes], uint8_t *b, uint32_t idesc,
+                                               bool accumulate) {
+#pragma unroll
+  for (int k16 = 0; k16 < kTile / 16; ++k16)
+    mma_f16(tmem, smem_desc_k_major_sw128(smem_u32(a[k16 >> 2]) + (k16 & 3) * 32),
+            smem_desc_mn_major_sw128(smem_u32(b) + k16 * 16 * 128, kBoxBytes), idesc, accumulate || k16 != 0);
+}
+
+template <int HALVES>
+__global__ void __launch_bounds__(128, 1)
+k_attn_bwd_dkv(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+               const Tile *__restrict__ tiles, int H, float scale, int causal, const float *__restrict__ lse,
+               const float *__restrict__ delta, __nv_bfloat16 *__restrict__ dk, __nv_bfloat16 *__restrict__ dv,
+               int *error) {
+  constexpr int D = 64 * HALVES;
+  extern __shared__ uint8_t smem_raw[];
+  BwdSmem<HALVES> &sm =
+      *reinterpret_cast<BwdSmem<HALVES> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const Tile tile = tiles[blockIdx.x / H];           // q_begin holds the first key of this tile
+  const int head = blockIdx.x % H;
+  const int row = warp * 32 + lane;
+  const int key_index = tile.q_begin + row;
+  const int q_first = causal ? tile.q_begin : tile.seq_begin;
+  const int n_blocks = (tile.seq_end - q_first + kTile - 1) / kTile;
+  const float scale_log2 = scale * kLog2e;
+
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    mbar_init(&sm.fixed_full, 1);
+    mbar_init(&sm.stream_full, 1);
+    mbar_init(&sm.s_done, 1);
+    mbar_init(&sm.acc_done, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (warp == 0) tmem_alloc(&sm.tmem_base, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_st = sm.tmem_base, tmem_dpt = sm.tmem_base + 128, tmem_dv = sm.tmem_base + 256,
+                 tmem_dk = sm.tmem_base + 384;
+  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+  volatile int *abort_flag = &sm.abort_flag;
+
+  if (tid == 0) {
+    mbar_arrive_expect_tx(&sm.fixed_full, 2 * HALVES * kBoxBytes);
+#pragma unroll
+    for (int j = 0; j < HALVES; ++j) {
+      tma_load_2d(sm.fixed_a[j], &map_k, head * D + 64 * j, tile.q_begin, &sm.fixed_full);
+      tma_load_2d(sm.fixed_b[j], &map_v, head * D + 64 * j, tile.q_begin, &sm.fixed_full);
+    }
+  }
+  constexpr uint32_t idesc_s = instr_desc(kFmtBF16, kFmtBF16, kTile, kTile, 0, 0);
+  constexpr uint32_t idesc_g = instr_desc(kFmtBF16, kFmtBF16, kTile, D, 0, 1);
+  mbar_wait(&sm.fixed_full, 0, abort_flag, error, 21);
+
+  for (int qb = 0; qb < n_blocks; ++qb) {
+    const int q0 = q_first + qb * kTile;
+    if (tid == 0) {                                   // the previous block's readers finished (acc_done)
+      mbar_arrive_expect_tx(&sm.stream_full, 2 * HALVES * kBoxBytes);
+#pragma unroll
+      for (int j = 0; j < HALVES; ++j) {
+        tma_load_2d(sm.stream_a[j], &map_q, head * D + 64 * j, q0, &sm.stream_full);
+        tma_load_2d(sm.stream_b[j], &map_do, head * D + 64 * j, q0, &sm.stream_full);
+      }
+    }
+    {                                                 // per-query softmax statistics of this block
+      const int qi = q0 + tid;
+      const bool ok = qi < tile.seq_end;
+      sm.lse2[tid] = ok ? lse[(int64_t)qi * H + head] * kLog2e : INFINITY;
+      sm.delta[tid] = ok ? delta[(int64_t)qi * H + head] : 0.0f;
+    }
+    mbar_wait(&sm.stream_full, (uint32_t)(qb & 1), abort_flag, error, 22);
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+      issue_scores<HALVES>(tmem_st, sm.fixed_a, sm.stream_a, idesc_s);    // S^T  = K Q^T
+      issue_scores<HALVES>(tmem_dpt, sm.fixed_b, sm.stream_b, idesc_s);   // dP^T = V dO^T
+      mma_commit(&sm.s_done);
+    }
+    mbar_wait(&sm.s_done, (uint32_t)(qb & 1), abort_flag, error, 23);
+    tc_fence_after_sync();
+    const bool key_ok = key_index < tile.seq_end;
+#pragma unroll 1
+    for (int c0 = 0; c0 < kTile; c0 += 32) {
+      uint32_t rs[32], rp[32];
+      tmem_ld_32x32(tmem_st + lane_base + c0, rs);
+      tmem_ld_32x32(tmem_dpt + lane_base + c0, rp);
+      tmem_ld_wait();
+      float p[32], ds[32];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const int qi = q0 + c0 + c;
+        const bool valid = key_ok && (!causal || key_index <= qi);
+        p[c] = valid ? fast_exp2(__uint_as_float(rs[c]) * scale_log2 - sm.lse2[c0 + c]) : 0.0f;
+        ds[c] = p[c] * (__uint_as_float(rp[c]) - sm.delta[c0 + c]);
+      }
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const int chunk = ((c0 & 63) >> 3) + g;
+        store_swizzled_chunk(sm.p[c0 >> 6], row, chunk,
+                             make_uint4(pack_bf16(p[8 * g], p[8 * g + 1]), pack_bf16(p[8 * g + 2], p[8 * g + 3]),
+                                        pack_bf16(p[8 * g + 4], p[8 * g + 5]), pack_bf16(p[8 * g + 6], p[8 * g + 7])));
+        store_swizzled_chunk(sm.ds[c0 >> 6], row, chunk,
+                             make_uint4(pack_bf16(ds[8 * g], ds[8 * g + 1]), pack_bf16(ds[8 * g + 2], ds[8 * g + 3]),
+                                        pack_bf16(ds[8 * g + 4], ds[8 * g + 5]), pack_bf16(ds[8 * g + 6], ds[8 * g + 7])));
+      }
+    }
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+      issue_gradient(tmem_dv, sm.p, sm.stream_b[0], idesc_g, qb != 0);    // dV += P^T dO
+      issue_gradient(tmem_dk, sm.ds, sm.stream_a[0], idesc_g, qb != 0);   // dK += dS^T Q
+      mma_commit(&sm.acc_done);
+    }
+    mbar_wait(&sm.acc_done, (uint32_t)(qb & 1), abort_flag, error, 24);
+    tc_fence_after_sync();
+  }
+
+  const bool store = key_index < tile.seq_end && !*abort_flag;
+  __nv_bfloat16 *dst_v = dv + ((int64_t)key_index * H + head) * D;
+  __nv_bfloat16 *dst_k = dk + ((int64_t)key_index * H + head) * D;
+#pragma unroll 1
+  for (int c0 = 0; c0 < D; c0 += 32) {
+    uint32_t rv[32], rk[32];
+    tmem_ld_32x32(tmem_dv + lane_base + c0, rv);
+    tmem_ld_32x32(tmem_dk + lane_base + c0, rk);
+    tmem_ld_wait();
+    if (store) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        *reinterpret_cast<uint4 *>(dst_v + c0 + 8 * g) = make_uint4(
+            pack_bf16(__uint_as_float(rv[8 * g]), __uint_as_float(rv[8 * g + 1])),
+            pack_bf16(__uint_as_float(rv[8 * g + 2]), __uint_as_float(rv[8 * g + 3])),
+            pack_bf16(__uint_as_float(rv[8 * g + 4]), __uint_as_float(rv[8 * g + 5])),
+            pack_bf16(__uint_as_float(rv[8 * g + 6]), __uint_as_float(rv[8 * g + 7])));
+        *reinterpret_cast<uint4 *>(dst_k + c0 + 8 * g) = make_uint4(
+            pack_bf16(__uint_as_float(rk[8 * g]) * scale, __uint_as_float(rk[8 * g + 1]) * scale),
+            pack_bf16(__uint_as_float(rk[8 * g + 2]) * scale, __uint_as_float(rk[8 * g + 3]) * scale),
+            pack_bf16(__uint_as_float(rk[8 * g + 4]) * scale, __uint_as_float(rk[8 * g + 5]) * scale),
+            pack_bf16(__uint_as_float(rk[8 * g + 6]) * scale, __uint_as_float(rk[8 * g + 7]) * scale));
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(sm.tmem_base, 512);
+}
+
+template <int HALVES>
+__global__ void __launch_bounds__(128, 1)
+k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+              const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+              const Tile *__restrict__ tiles, int H, float scale, int causal, const float *__restrict__ lse,
+              const float *__restrict__ delta, __nv_bfloat16 *__restrict__ dq, int *error) {
+  constexpr int D = 64 * HALVES;
+  extern __shared__ uint8_t smem_raw[];
+  BwdSmem<HALVES> &sm =
+      *reinterpret_cast<BwdSmem<HALVES> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const Tile tile = tiles[blockIdx.x / H];
+  const int head = blockIdx.x % H;
+  const int row = warp * 32 + lane;
+  const int q_index = tile.q_begin + row;
+  const int key_limit = causal ? min(tile.q_begin + kTile, tile.seq_end) : tile.seq_end;
+  const int n_blocks = (key_limit - tile.seq_begin + kTile - 1) / kTile;
+  const float scale_log2 = scale * kLog2e;
+
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    mbar_init(&sm.fixed_full, 1);
+    mbar_init(&sm.stream_full, 1);
+    mbar_init(&sm.s_done, 1);
+    mbar_init(&sm.acc_done, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (warp == 0) tmem_alloc(&sm.tmem_base, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_s = sm.tmem_base, tmem_dp = sm.tmem_base + 128, tmem_dq = sm.tmem_base + 256;
+  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+  volatile int *abort_flag = &sm.abort_flag;
+
+  if (tid == 0) {
+    mbar_arrive_expect_tx(&sm.fixed_full, 2 * HALVES * kBoxBytes);
+#pragma unroll
+    for (int j = 0; j < HALVES; ++j) {
+      tma_load_2d(sm.fixed_a[j], &map_q, head * D + 64 * j, tile.q_begin, &sm.fixed_full);
+      tma_load_2d(sm.fixed_b[j], &map_do, head * D + 64 * j, tile.q_begin, &sm.fixed_full);
+    }
+  }
+  const bool q_ok = q_index < tile.seq_end;
+  const float lse2 = q_ok ? lse[(int64_t)q_index * H + head] * kLog2e : INFINITY;
+  const float my_delta = q_ok ? delta[(int64_t)q_index * H + head] : 0.0f;
+  constexpr uint32_t idesc_s = instr_desc(kFmtBF16, kFmtBF16, kTile, kTile, 0, 0);
+  constexpr uint32_t idesc_g = instr_desc(kFmtBF16, kFmtBF16, kTile, D, 0, 1);
+  mbar_wait(&sm.fixed_full, 0, abort_flag, error, 31);
+
+  for (int kb = 0; kb < n_blocks; ++kb) {
+    const int key0 = tile.seq_begin + kb * kTile;
+    if (tid == 0) {
+      mbar_arrive_expect_tx(&sm.stream_full, 2 * HALVES * kBoxBytes);
+#pragma unroll
+      for (int j = 0; j < HALVES; ++j) {
+        tma_load_2d(sm.stream_a[j], &map_k, head * D + 64 * j, key0, &sm.stream_full);
+        tma_load_2d(sm.stream_b[j], &map_v, head * D + 64 * j, key0, &sm.stream_full);
+      }
+    }
+    mbar_wait(&sm.stream_full, (uint32_t)(kb & 1), abort_flag, error, 32);
+    if (tid == 0) {
+      tc_fence_after_sync();
+      issue_scores<HALVES>(tmem_s, sm.fixed_a, sm.stream_a, idesc_s);     // S  = Q K^T
+      issue_scores<HALVES>(tmem_dp, sm.fixed_b, sm.stream_b, idesc_s);    // dP = dO V^T
+      mma_commit(&sm.s_done);
+    }
+    mbar_wait(&sm.s_done, (uint32_t)(kb & 1), abort_flag, error, 33);
+    tc_fence_after_sync();
+#pragma unroll 1
+    for (int c0 = 0; c0 < kTile; c0 += 32) {
+      uint32_t rs[32], rp[32];
+      tmem_ld_32x32(tmem_s + lane_base + c0, rs);
+      tmem_ld_32x32(tmem_dp + lane_base + c0, rp);
+      tmem_ld_wait();
+      float ds[32];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const int key = key0 + c0 + c;
+        const bool valid = key < tile.seq_end && (!causal || key <= q_index);
+        const float p = valid ? fast_exp2(__uint_as_float(rs[c]) * scale_log2 - lse2) : 0.0f;
+        ds[c] = p * (__uint_as_float(rp[c]) - my_delta);
+      }
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+        store_swizzled_chunk(sm.ds[c0 >> 6], row, ((c0 & 63) >> 3) + g,
+                             make_uint4(pack_bf16(ds[8 * g], ds[8 * g + 1]), pack_bf16(ds[8 * g + 2], ds[8 * g + 3]),
+                                        pack_bf16(ds[8 * g + 4], ds[8 * g + 5]), pack_bf16(ds[8 * g + 6], ds[8 * g + 7])));
+    }
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+      issue_gradient(tmem_dq, sm.ds, sm.stream_a[0], idesc_g, kb != 0);   // dQ += dS K
+      mma_commit(&sm.acc_done);
+    }
+    mbar_wait(&sm.acc_done, (uint32_t)(kb & 1), abort_flag, error, 34);
+    tc_fence_after_sync();
+  }
+
+  const bool store = q_ok && !*abort_flag;
+  __nv_bfloat16 *dst = dq + ((int64_t)q_index * H + head) * D;
+#pragma unroll 1
+  for (int c0 = 0; c0 < D; c0 += 32) {
+    uint32_t r[32];
+    tmem_ld_32x32(tmem_dq + lane_base + c0, r);
+    tmem_ld_wait();
+    if (store) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+        *reinterpret_cast<uint4 *>(dst + c0 + 8 * g) = make_uint4(
+            pack_bf16(__uint_as_float(r[8 * g]) * scale, __uint_as_float(r[8 * g + 1]) * scale),
+            pack_bf16(__uint_as_float(r[8 * g + 2]) * scale, __uint_as_float(r[8 * g + 3]) * scale),
+            pack_bf16(__uint_as_float(r[8 * g + 4]) * scale, __uint_as_float(r[8 * g + 5]) * scale),
+            pack_bf16(__uint_as_float(r[8 * g + 6]) * scale, __uint_as_float(r[8 * g + 7]) * scale));
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(sm.tmem_base, 512);
+}
+
 int32_t check_attn(const void *q, const void *k, const void *v, int64_t tokens, int32_t H, int32_t D) {
   if (!q || !k || !v) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
   if (H <= 0 || tokens < 0) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "invalid shape");
@@ -286,5 +620,50 @@ extern "C" int32_t tgb_varlen_attn_fwd(const void *q, const void *k, const void 
                                            (__nv_bfloat16 *)out, (float *)lse, (int *)error_flag);
   }
   TGB_LAUNCHED();
+  return TGB_STATUS_OK;
+}
+
+extern "C" int32_t tgb_varlen_attn_bwd(const void *q, const void *k, const void *v, const void *out,
+                                       const void *dout, const void *lse, void *dq, void *dk, void *dv,
+                                       void *delta, const void *query_tiles, const void *key_tiles,
+                                       int64_t n_tiles, int64_t tokens, int32_t H, int32_t D, float scale,
+                                       int32_t causal, void *error_flag, uint64_t stream) {
+  int32_t rc = check_attn(q, k, v, tokens, H, D);
+  if (rc) return rc;
+  if (n_tiles == 0) return TGB_STATUS_OK;
+  if (!out || !dout || !lse || !dq || !dk || !dv || !delta || !query_tiles || !key_tiles || !error_flag)
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
+  CUtensorMap map_q, map_k, map_v, map_do;
+  if ((rc = head_map(&map_q, q, tokens, H, D))) return rc;
+  if ((rc = head_map(&map_k, k, tokens, H, D))) return rc;
+  if ((rc = head_map(&map_v, v, tokens, H, D))) return rc;
+  if ((rc = head_map(&map_do, dout, tokens, H, D))) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int64_t rows = tokens * H;
+  k_attn_delta<<<(unsigned)ceil_div(rows * 32, 256), 256, 0, st>>>((const __nv_bfloat16 *)out,
+                                                                  (const __nv_bfloat16 *)dout, rows, D,
+                                                                  (float *)delta);
+  TGB_LAUNCHED();
+  const unsigned grid = (unsigned)(n_tiles * H);
+#define TGB_BWD(HV)                                                                                         \
+  {                                                                                                         \
+    const size_t smem = sizeof(BwdSmem<HV>) + 1024;                                                         \
+    static bool configured = false;                                                                         \
+    if (!configured) {                                                                                      \
+      TGB_CUDA(cudaFuncSetAttribute(k_attn_bwd_dkv<HV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      TGB_CUDA(cudaFuncSetAttribute(k_attn_bwd_dq<HV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
+      configured = true;                                                                                    \
+    }                                                                                                       \
+    k_attn_bwd_dkv<HV><<<grid, 128, smem, st>>>(map_q, map_k, map_v, map_do, (const Tile *)key_tiles, H, scale, \
+                                                causal, (const float *)lse, (const float *)delta,           \
+                                                (__nv_bfloat16 *)dk, (__nv_bfloat16 *)dv, (int *)error_flag); \
+    TGB_LAUNCHED();                                                                                         \
+    k_attn_bwd_dq<HV><<<grid, 128, smem, st>>>(map_q, map_k, map_v, map_do, (const Tile *)query_tiles, H, scale, \
+                                               causal, (const float *)lse, (const float *)delta,            \
+                                               (__nv_bfloat16 *)dq, (int *)error_flag);                     \
+    TGB_LAUNCHED();                                                                                         \
+  }
+  if (D == 128) TGB_BWD(2) else TGB_BWD(1)
+#undef TGB_BWD
   return TGB_STATUS_OK;
 }

@@ -110,10 +110,14 @@ def _attention_tiles(graph, device):
         for q0 in range(begin, end, 128):
             blocks = ((min(q0 + 128, end) if causal else end) - begin + 127) // 128
             rows.append((blocks, q0, begin, end))
-    rows.sort(key=lambda r: -r[0])
-    table = torch.tensor([[q0, b, e, 0] for _, q0, b, e in rows], dtype=torch.int32).reshape(-1, 4).to(device)
-    graph.__dict__["_attention_tiles"] = (table, causal)
-    return table, causal
+    def table(ordered):
+        return torch.tensor([[q0, b, e, 0] for _, q0, b, e in ordered], dtype=torch.int32).reshape(-1, 4).to(device)
+
+    by_query = sorted(rows, key=lambda r: -r[0])
+    # the key-major backward kernel loops over the query blocks that see a key tile
+    by_key = sorted(rows, key=lambda r: -(((r[3] - r[1]) if causal else (r[3] - r[2])) + 127) // 128)
+    graph.__dict__["_attention_tiles"] = (table(by_query), causal, table(by_key))
+    return graph.__dict__["_attention_tiles"]
 
 
 class VarlenAttentionFunction(torch.autograd.Function):
@@ -130,7 +134,7 @@ class VarlenAttentionFunction(torch.autograd.Function):
         if tokens != graph.num_dst:
             raise ValueError(f"fields must have {graph.num_dst} rows, got {tokens}")
         q, k, v = query.contiguous(), key.contiguous(), value.contiguous()
-        tiles, causal = _attention_tiles(graph, q.device)
+        tiles, causal, _ = _attention_tiles(graph, q.device)
         out = torch.empty_like(q)
         lse = torch.empty((tokens, H), dtype=torch.float32, device=q.device)
         with torch.cuda.device(q.device):
@@ -144,7 +148,21 @@ class VarlenAttentionFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
-        raise NotImplementedError("the dense attention backward kernel is not built yet")
+        from . import ops
+
+        q, k, v, out, lse = ctx.saved_tensors
+        tokens, H, D = q.shape
+        d_out = grad_output.contiguous().to(torch.bfloat16)
+        query_tiles, causal, key_tiles = _attention_tiles(ctx.graph, q.device)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        delta = torch.empty((tokens, H), dtype=torch.float32, device=q.device)
+        with torch.cuda.device(q.device):
+            _native.check(_native.lib().tgb_varlen_attn_bwd(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), d_out.data_ptr(), lse.data_ptr(),
+                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(), query_tiles.data_ptr(),
+                key_tiles.data_ptr(), query_tiles.shape[0], tokens, H, D, ctx.scale, int(causal),
+                ops.error_flag(q.device).data_ptr(), _stream(q.device)), "tgb_varlen_attn_bwd")
+        return dq, dk, dv, None, None
 
 
 def varlen_attention(graph, query, key, value, scale):
