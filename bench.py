@@ -54,6 +54,9 @@ def parse_args():
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--cpu-sample-seconds", type=float, default=15.0)
+    p.add_argument("--workload", default="gcn", choices=("gcn", "gat", "attention"),
+                   help="gcn = the headline GCN-layer configuration; gat / attention measure the edge-attention "
+                        "and dense-attention configurations (one GPU)")
     p.add_argument("--kernel-table", action="store_true",
                    help="after the timed run, print a per-kernel device-time table of two more steps to stderr")
     return p.parse_args()
@@ -145,6 +148,127 @@ def algorithmic_bytes(E, N, F):
     }
 
 
+def bf16_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as handle:
+            return float(json.load(handle)["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
+
+
+def time_steps(step, steps, warmup):
+    for _ in range(max(warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(steps):
+        step()
+    end.record()
+    torch.cuda.synchronize()
+    return begin.elapsed_time(end) / steps
+
+
+def run_gat(args, device):
+    """Edge-attention configuration: directed R-MAT (2^21 nodes, 64M generated edges, de-duplicated),
+    bf16 features [N, 8, 32], GAT logit, online-softmax reducer, forward + backward."""
+    import tiga as tg
+    from tiga import _native, ops
+    from tiga import synthetic as syn
+
+    scale = args.scale + 1 if args.scale == 20 else args.scale
+    row_ptr, col = syn.rmat_csr(scale, args.edge_factor, seed=args.seed, symmetrize=False, device=device)
+    N, E, H, D = row_ptr.numel() - 1, col.numel(), 8, 32
+    x = syn.normal((N, H, D), seed=args.seed + 1, device=device, dtype=torch.bfloat16).requires_grad_()
+    a_src = syn.normal((H, D), seed=args.seed + 2, device=device, dtype=torch.bfloat16, std=0.1).requires_grad_()
+    a_dst = syn.normal((H, D), seed=args.seed + 3, device=device, dtype=torch.bfloat16, std=0.1).requires_grad_()
+    graph = tg.Graph.from_csr(row_ptr, col, num_src=N)
+
+    class GAT(tg.MessagePassing):
+        reducer = tg.online_softmax()
+
+        def edge(self, src, dst, edge, a_src, a_dst):
+            s = (src.x * a_src).sum(dim=-1) + (dst.x * a_dst).sum(dim=-1)
+            return self.reducer(tg.math.maximum(s, 0.2 * s), src.x)
+
+    layer = GAT()
+    dy = syn.normal((N, H, D), seed=args.seed + 4, device=device, dtype=torch.bfloat16)
+    fwd_ms = time_steps(lambda: layer(graph=graph, ndata={"x": x.detach()}, a_src=a_src.detach(),
+                                      a_dst=a_dst.detach()), args.steps, args.warmup)
+
+    def step():
+        out = layer(graph=graph, ndata={"x": x}, a_src=a_src, a_dst=a_dst)
+        return torch.autograd.grad(out, (x, a_src, a_dst), dy)
+
+    before = _native.launch_count()
+    ms = time_steps(step, args.steps, args.warmup)
+    launches = (_native.launch_count() - before) // (args.steps + max(args.warmup, 3))
+    peak, kind = hbm_peak()
+    alg = 1696 * E + 3152 * N
+    alg_fwd = 520 * E + 1032 * N
+    print(json.dumps({
+        "metric": METRIC, "value": round(E / (ms * 1e-3) / 1e9, 4), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"gat edge attention rmat scale={scale} directed dedup bf16 [N,8,32] fwd+bwd",
+                   "num_nodes": N, "num_edges": E, "forward_ms": round(fwd_ms, 4), "l2": "inputs exceed L2"},
+        "roofline": {"bound": "hbm", "kernel": "k_gat_fwd + k_gat_bwd_dst + k_gat_bwd_src (whole step)",
+                     "achieved": round(alg / (ms * 1e-3) / 1e9, 1), "peak": peak, "peak_kind": f"of {kind}",
+                     "unit": "GB/s", "frac": round(alg / (ms * 1e-3) / 1e9 / peak, 4), "traffic": None,
+                     "forward_frac": round(alg_fwd / (fwd_ms * 1e-3) / 1e9 / peak, 4)},
+        "gpu_launches": int(launches)}), flush=True)
+
+
+def run_attention(args, device):
+    """Dense-relation configuration: 32 sequences with lengths uniform in [512, 8192], 16 heads,
+    head width 128, bf16, causal inside each sequence, forward + backward."""
+    import tiga as tg
+    from tiga import _native, ops
+    from tiga import synthetic as syn
+
+    gen = torch.Generator().manual_seed(20260821)
+    lengths = torch.randint(512, 8193, (32,), generator=gen)
+    cu = torch.cat((torch.zeros(1, dtype=torch.int64), lengths.cumsum(0)))
+    T, H, D = int(cu[-1]), 16, 128
+    q, k, v = (syn.normal((T, H, D), seed=args.seed + i, device=device, dtype=torch.bfloat16).requires_grad_()
+               for i in range(3))
+    dy = syn.normal((T, H, D), seed=args.seed + 9, device=device, dtype=torch.bfloat16)
+    graph = tg.Graph.cu_seqlens(cu.to(device), causal=True)
+
+    class Attention(tg.MessagePassing):
+        reducer = tg.online_softmax()
+
+        def edge(self, src, dst, edge, scale):
+            return self.reducer((src.key * dst.query).sum(dim=-1) * scale, src.value)
+
+    layer = Attention()
+    scale = D ** -0.5
+    fwd_ms = time_steps(lambda: layer(graph=graph, src={"key": k.detach(), "value": v.detach()},
+                                      dst={"query": q.detach()}, scale=scale), args.steps, args.warmup)
+
+    def step():
+        out = layer(graph=graph, src={"key": k, "value": v}, dst={"query": q}, scale=scale)
+        return torch.autograd.grad(out, (q, k, v), dy)
+
+    ms = time_steps(step, args.steps, args.warmup)
+    ops.check_async_errors()
+    pairs = float((lengths.double() * (lengths.double() + 1) / 2).sum())
+    fwd_flops = 4.0 * H * D * pairs
+    total_flops = 3.5 * fwd_flops
+    peak, kind = bf16_peak()
+    print(json.dumps({
+        "metric": "TFLOP/s fwd+bwd for varlen causal dense-relation attention", "value": round(total_flops / (ms * 1e-3) / 1e12, 2),
+        "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "varlen causal attention 32 sequences L~U[512,8192] H=16 D=128 bf16 fwd+bwd",
+                   "tokens": T, "forward_ms": round(fwd_ms, 4),
+                   "forward_tflops": round(fwd_flops / (fwd_ms * 1e-3) / 1e12, 2)},
+        "roofline": {"bound": "tensor", "kernel": "k_attn_fwd + k_attn_bwd_dkv + k_attn_bwd_dq",
+                     "achieved": round(total_flops / (ms * 1e-3) / 1e12, 2), "peak": peak, "peak_kind": f"of {kind}",
+                     "unit": "TFLOP/s", "frac": round(total_flops / (ms * 1e-3) / 1e12 / peak, 4), "traffic": None,
+                     "forward_frac": round(fwd_flops / (fwd_ms * 1e-3) / 1e12 / peak, 4)}}), flush=True)
+
+
 def run_native(args):
     import torch.distributed as dist
 
@@ -167,6 +291,10 @@ def run_native(args):
 
     _native.lib()
     torch.backends.cuda.matmul.allow_tf32 = False
+    if args.workload == "gat":
+        return run_gat(args, device)
+    if args.workload == "attention":
+        return run_attention(args, device)
     row_ptr, col, weight, x, lin = build_inputs(args, device)
     N, E, F = row_ptr.numel() - 1, col.numel(), args.features
     graph = tg.Graph.from_csr(row_ptr, col, num_src=N)
