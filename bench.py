@@ -161,11 +161,13 @@ def time_steps(step, steps, warmup):
         step()
     torch.cuda.synchronize()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()
     begin.record()
     for _ in range(steps):
         step()
     end.record()
     torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     return begin.elapsed_time(end) / steps
 
 
