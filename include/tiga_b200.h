@@ -261,8 +261,9 @@ TGB_API int32_t tgb_gat_bwd(const tgb_csr_plan *plan, const void *x_src,
  *   q, k, v, out  [tokens, H, D] bf16 contiguous, D in {64, 128}
  *   lse           [tokens, H] float32: log-sum-exp of the scaled scores
  *   tiles         int32 [n_tiles, 4] = {first query, sequence begin, sequence
- *                 end, 0}: the 128-query tiles of every sequence (heaviest
- *                 first for load balance)
+ *                 end, head}: one entry per (128-query tile, head); one CTA
+ *                 each, launched in table order (keep the entries of one
+ *                 (sequence, head) adjacent so they share K/V in L2)
  *   causal        1: query i attends keys seq_begin..i; 0: its whole sequence
  * error_flag: one zero-initialised int32 in device memory (bounded waits).
  * ------------------------------------------------------------------------ */

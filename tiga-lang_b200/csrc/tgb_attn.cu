@@ -51,40 +51,49 @@ __device__ __forceinline__ void store_swizzled_chunk(uint8_t *tile, int r, int c
   *reinterpret_cast<uint4 *>(tile + r * 128 + ((chunk ^ (r & 7)) << 4)) = value;
 }
 
-struct Tile {           // one 128-query tile of one sequence
-  int32_t q_begin;      // first query (token index)
+struct Tile {           // one 128-token tile of one sequence, for one head
+  int32_t q_begin;      // first query (or key) of the tile (token index)
   int32_t seq_begin;    // first token of the sequence
   int32_t seq_end;      // one past the last token of the sequence
-  int32_t reserved;
+  int32_t head;
 };
+
+// Keys per block of the forward and dQ kernels.  64 keeps a CTA at 112 KB of
+// shared memory, 256 registers x 128 threads and 256 tensor-memory columns, so
+// two CTAs share an SM and one CTA's softmax overlaps the other's MMAs.
+constexpr int kKeyBlock = 64;
+constexpr int kKeyBoxBytes = kKeyBlock * 128;
 
 template <int HALVES>   // head width = 64 * HALVES
 struct FwdSmem {
   alignas(1024) uint8_t q[HALVES][kBoxBytes];
-  alignas(1024) uint8_t k[2][HALVES][kBoxBytes];
-  alignas(1024) uint8_t v[2][HALVES][kBoxBytes];
-  alignas(1024) uint8_t p[2][kBoxBytes];          // keys 0-63 and 64-127
+  alignas(1024) uint8_t k[2][HALVES][kKeyBoxBytes];
+  alignas(1024) uint8_t v[2][HALVES][kKeyBoxBytes];
+  alignas(1024) uint8_t p[kBoxBytes];              // [128 queries x 64 keys] bf16
   uint64_t q_full, kv_full[2], s_done, o_done;
   uint32_t tmem_base;
   int abort_flag;
 };
 
 template <int HALVES>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(128, 2)
 k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
            const __grid_constant__ CUtensorMap map_v, const Tile *__restrict__ tiles, int H,
            float scale_log2, int causal, __nv_bfloat16 *__restrict__ out, float *__restrict__ lse, int *error) {
   constexpr int D = 64 * HALVES;
-  extern __shared__ uint8_t smem_raw[];
-  FwdSmem<HALVES> &sm =
-      *reinterpret_cast<FwdSmem<HALVES> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  FwdSmem<HALVES> &sm = *reinterpret_cast<FwdSmem<HALVES> *>(smem_raw);
+  if (smem_u32(smem_raw) & 1023u) {                  // swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicCAS(error, 0, 19);
+    return;
+  }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const Tile tile = tiles[blockIdx.x / H];
-  const int head = blockIdx.x % H;
+  const Tile tile = tiles[blockIdx.x];
+  const int head = tile.head;
   const int row = warp * 32 + lane;                 // query row of this thread inside the tile
   const int q_index = tile.q_begin + row;
   const int key_limit = causal ? min(tile.q_begin + kTile, tile.seq_end) : tile.seq_end;
-  const int n_blocks = (key_limit - tile.seq_begin + kTile - 1) / kTile;
+  const int n_blocks = (key_limit - tile.seq_begin + kKeyBlock - 1) / kKeyBlock;
 
   if (tid == 0) {
     sm.abort_flag = 0;
@@ -99,7 +108,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     tma_prefetch_descriptor(&map_v);
   }
   __syncthreads();
-  if (warp == 0) tmem_alloc(&sm.tmem_base, 256);    // S: columns 0-127, P V: columns 128-255
+  if (warp == 0) tmem_alloc(&sm.tmem_base, 256);    // S: columns 0-63, P V: columns 128-255
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -108,8 +117,8 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   volatile int *abort_flag = &sm.abort_flag;
 
   auto load_kv = [&](int block, int stage) {
-    const int y = tile.seq_begin + block * kTile;
-    mbar_arrive_expect_tx(&sm.kv_full[stage], 2 * HALVES * kBoxBytes);
+    const int y = tile.seq_begin + block * kKeyBlock;
+    mbar_arrive_expect_tx(&sm.kv_full[stage], 2 * HALVES * kKeyBoxBytes);
 #pragma unroll
     for (int j = 0; j < HALVES; ++j) {
       tma_load_2d(sm.k[stage][j], &map_k, head * D + 64 * j, y, &sm.kv_full[stage]);
@@ -123,7 +132,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     load_kv(0, 0);
   }
 
-  constexpr uint32_t idesc_s = instr_desc(kFmtBF16, kFmtBF16, kTile, kTile, 0, 0);
+  constexpr uint32_t idesc_s = instr_desc(kFmtBF16, kFmtBF16, kTile, kKeyBlock, 0, 0);
   constexpr uint32_t idesc_o = instr_desc(kFmtBF16, kFmtBF16, kTile, D, 0, 1);   // V is MN-major
   float m = -INFINITY, l = 0.0f;
   float o[D];
@@ -133,7 +142,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   mbar_wait(&sm.q_full, 0, abort_flag, error, 11);
   for (int kb = 0; kb < n_blocks; ++kb) {
     const int st = kb & 1;
-    const int key0 = tile.seq_begin + kb * kTile;
+    const int key0 = tile.seq_begin + kb * kKeyBlock;
     if (tid == 0 && kb + 1 < n_blocks) load_kv(kb + 1, st ^ 1);   // its previous reader finished last iteration
     mbar_wait(&sm.kv_full[st], (uint32_t)((kb >> 1) & 1), abort_flag, error, 12);
     if (tid == 0) {
@@ -150,11 +159,11 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     mbar_wait(&sm.s_done, (uint32_t)(kb & 1), abort_flag, error, 13);
     tc_fence_after_sync();
 
-    const bool masked = (key0 + kTile > tile.seq_end) || (causal && key0 + kTile - 1 > tile.q_begin);
+    const bool masked = (key0 + kKeyBlock > tile.seq_end) || (causal && key0 + kKeyBlock - 1 > tile.q_begin);
     // pass A: row maximum
     float block_max = -INFINITY;
 #pragma unroll 1
-    for (int c0 = 0; c0 < kTile; c0 += 32) {
+    for (int c0 = 0; c0 < kKeyBlock; c0 += 32) {
       uint32_t r[32];
       tmem_ld_32x32(tmem_s + lane_base + c0, r);
       tmem_ld_wait();
@@ -171,7 +180,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     // pass B: p = 2^(s - m), written as bf16 for the second MMA
     float block_sum = 0.0f;
 #pragma unroll 1
-    for (int c0 = 0; c0 < kTile; c0 += 32) {
+    for (int c0 = 0; c0 < kKeyBlock; c0 += 32) {
       uint32_t r[32];
       tmem_ld_32x32(tmem_s + lane_base + c0, r);
       tmem_ld_wait();
@@ -183,7 +192,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         p[c] = valid ? fast_exp2(__uint_as_float(r[c]) * scale_log2 - m_use) : 0.0f;
         block_sum += p[c];
       }
-      uint8_t *half = sm.p[c0 >> 6];
+      uint8_t *half = sm.p;
 #pragma unroll
       for (int g = 0; g < 4; ++g)
         store_swizzled_chunk(half, row, ((c0 & 63) >> 3) + g,
@@ -198,9 +207,9 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     if (tid == 0) {
       tc_fence_after_sync();
 #pragma unroll
-      for (int k16 = 0; k16 < kTile / 16; ++k16) {   // 16 keys per MMA
-        const uint64_t a_desc = smem_desc_k_major_sw128(smem_u32(sm.p[k16 >> 2]) + (k16 & 3) * 32);
-        const uint64_t b_desc = smem_desc_mn_major_sw128(smem_u32(sm.v[st][0]) + k16 * 16 * 128, kBoxBytes);
+      for (int k16 = 0; k16 < kKeyBlock / 16; ++k16) {   // 16 keys per MMA
+        const uint64_t a_desc = smem_desc_k_major_sw128(smem_u32(sm.p) + k16 * 32);
+        const uint64_t b_desc = smem_desc_mn_major_sw128(smem_u32(sm.v[st][0]) + k16 * 16 * 128, kKeyBoxBytes);
         mma_f16(tmem_o, a_desc, b_desc, idesc_o, k16 != 0);
       }
       mma_commit(&sm.o_done);
@@ -279,8 +288,8 @@ struct BwdSmem {
 };
 
 // [128 x 128] score-like product of two K-major tiles of width D into `tmem`
-template <int HALVES>
-__device__ __forceinline__ void issue_scores(uint32_t tmem, uint8_t (*a)[kBoxBytes], uint8_t (*b)[kBoxBytes],
+template <int HALVES, int BOX_A, int BOX_B>
+__device__ __forceinline__ void issue_scores(uint32_t tmem, uint8_t (*a)[BOX_A], uint8_t (*b)[BOX_B],
                                              uint32_t idesc) {
 #pragma unroll
   for (int k16 = 0; k16 < HALVES * 4; ++k16) {
@@ -311,8 +320,8 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   BwdSmem<HALVES> &sm =
       *reinterpret_cast<BwdSmem<HALVES> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const Tile tile = tiles[blockIdx.x / H];           // q_begin holds the first key of this tile
-  const int head = blockIdx.x % H;
+  const Tile tile = tiles[blockIdx.x];               // q_begin holds the first key of this tile
+  const int head = tile.head;
   const int row = warp * 32 + lane;
   const int key_index = tile.q_begin + row;
   const int q_first = causal ? tile.q_begin : tile.seq_begin;
@@ -369,8 +378,8 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     __syncthreads();
     if (tid == 0) {
       tc_fence_after_sync();
-      issue_scores<HALVES>(tmem_st, sm.fixed_a, sm.stream_a, idesc_s);    // S^T  = K Q^T
-      issue_scores<HALVES>(tmem_dpt, sm.fixed_b, sm.stream_b, idesc_s);   // dP^T = V dO^T
+      issue_scores<HALVES, kBoxBytes, kBoxBytes>(tmem_st, sm.fixed_a, sm.stream_a, idesc_s);    // S^T  = K Q^T
+      issue_scores<HALVES, kBoxBytes, kBoxBytes>(tmem_dpt, sm.fixed_b, sm.stream_b, idesc_s);   // dP^T = V dO^T
       mma_commit(&sm.s_done);
     }
     mbar_wait(&sm.s_done, (uint32_t)(qb & 1), abort_flag, error, 23);
@@ -445,22 +454,39 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 }
 
 template <int HALVES>
-__global__ void __launch_bounds__(128, 1)
+struct DqSmem {
+  alignas(1024) uint8_t q[HALVES][kBoxBytes];
+  alignas(1024) uint8_t d_o[HALVES][kBoxBytes];
+  alignas(1024) uint8_t k[HALVES][kKeyBoxBytes];
+  alignas(1024) uint8_t v[HALVES][kKeyBoxBytes];
+  alignas(1024) uint8_t ds[kBoxBytes];              // [128 queries x 64 keys] bf16
+  uint64_t fixed_full, stream_full, s_done, acc_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// 64-key blocks: 112 KB of shared memory and 256 tensor-memory columns per CTA,
+// two CTAs per SM.
+template <int HALVES>
+__global__ void __launch_bounds__(128, 2)
 k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
               const Tile *__restrict__ tiles, int H, float scale, int causal, const float *__restrict__ lse,
               const float *__restrict__ delta, __nv_bfloat16 *__restrict__ dq, int *error) {
   constexpr int D = 64 * HALVES;
-  extern __shared__ uint8_t smem_raw[];
-  BwdSmem<HALVES> &sm =
-      *reinterpret_cast<BwdSmem<HALVES> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  DqSmem<HALVES> &sm = *reinterpret_cast<DqSmem<HALVES> *>(smem_raw);
+  if (smem_u32(smem_raw) & 1023u) {
+    if (threadIdx.x == 0) atomicCAS(error, 0, 39);
+    return;
+  }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const Tile tile = tiles[blockIdx.x / H];
-  const int head = blockIdx.x % H;
+  const Tile tile = tiles[blockIdx.x];
+  const int head = tile.head;
   const int row = warp * 32 + lane;
   const int q_index = tile.q_begin + row;
   const int key_limit = causal ? min(tile.q_begin + kTile, tile.seq_end) : tile.seq_end;
-  const int n_blocks = (key_limit - tile.seq_begin + kTile - 1) / kTile;
+  const int n_blocks = (key_limit - tile.seq_begin + kKeyBlock - 1) / kKeyBlock;
   const float scale_log2 = scale * kLog2e;
 
   if (tid == 0) {
@@ -472,11 +498,11 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     mbar_fence_init();
   }
   __syncthreads();
-  if (warp == 0) tmem_alloc(&sm.tmem_base, 512);
+  if (warp == 0) tmem_alloc(&sm.tmem_base, 256);     // S: 0-63, dP: 64-127, dQ: 128-255
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_s = sm.tmem_base, tmem_dp = sm.tmem_base + 128, tmem_dq = sm.tmem_base + 256;
+  const uint32_t tmem_s = sm.tmem_base, tmem_dp = sm.tmem_base + 64, tmem_dq = sm.tmem_base + 128;
   const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
   volatile int *abort_flag = &sm.abort_flag;
 
@@ -484,38 +510,38 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     mbar_arrive_expect_tx(&sm.fixed_full, 2 * HALVES * kBoxBytes);
 #pragma unroll
     for (int j = 0; j < HALVES; ++j) {
-      tma_load_2d(sm.fixed_a[j], &map_q, head * D + 64 * j, tile.q_begin, &sm.fixed_full);
-      tma_load_2d(sm.fixed_b[j], &map_do, head * D + 64 * j, tile.q_begin, &sm.fixed_full);
+      tma_load_2d(sm.q[j], &map_q, head * D + 64 * j, tile.q_begin, &sm.fixed_full);
+      tma_load_2d(sm.d_o[j], &map_do, head * D + 64 * j, tile.q_begin, &sm.fixed_full);
     }
   }
   const bool q_ok = q_index < tile.seq_end;
   const float lse2 = q_ok ? lse[(int64_t)q_index * H + head] * kLog2e : INFINITY;
   const float my_delta = q_ok ? delta[(int64_t)q_index * H + head] : 0.0f;
-  constexpr uint32_t idesc_s = instr_desc(kFmtBF16, kFmtBF16, kTile, kTile, 0, 0);
+  constexpr uint32_t idesc_s = instr_desc(kFmtBF16, kFmtBF16, kTile, kKeyBlock, 0, 0);
   constexpr uint32_t idesc_g = instr_desc(kFmtBF16, kFmtBF16, kTile, D, 0, 1);
   mbar_wait(&sm.fixed_full, 0, abort_flag, error, 31);
 
   for (int kb = 0; kb < n_blocks; ++kb) {
-    const int key0 = tile.seq_begin + kb * kTile;
-    if (tid == 0) {
-      mbar_arrive_expect_tx(&sm.stream_full, 2 * HALVES * kBoxBytes);
+    const int key0 = tile.seq_begin + kb * kKeyBlock;
+    if (tid == 0) {                                   // the previous block's readers finished (acc_done)
+      mbar_arrive_expect_tx(&sm.stream_full, 2 * HALVES * kKeyBoxBytes);
 #pragma unroll
       for (int j = 0; j < HALVES; ++j) {
-        tma_load_2d(sm.stream_a[j], &map_k, head * D + 64 * j, key0, &sm.stream_full);
-        tma_load_2d(sm.stream_b[j], &map_v, head * D + 64 * j, key0, &sm.stream_full);
+        tma_load_2d(sm.k[j], &map_k, head * D + 64 * j, key0, &sm.stream_full);
+        tma_load_2d(sm.v[j], &map_v, head * D + 64 * j, key0, &sm.stream_full);
       }
     }
     mbar_wait(&sm.stream_full, (uint32_t)(kb & 1), abort_flag, error, 32);
     if (tid == 0) {
       tc_fence_after_sync();
-      issue_scores<HALVES>(tmem_s, sm.fixed_a, sm.stream_a, idesc_s);     // S  = Q K^T
-      issue_scores<HALVES>(tmem_dp, sm.fixed_b, sm.stream_b, idesc_s);    // dP = dO V^T
+      issue_scores<HALVES, kBoxBytes, kKeyBoxBytes>(tmem_s, sm.q, sm.k, idesc_s);      // S  = Q K^T
+      issue_scores<HALVES, kBoxBytes, kKeyBoxBytes>(tmem_dp, sm.d_o, sm.v, idesc_s);   // dP = dO V^T
       mma_commit(&sm.s_done);
     }
     mbar_wait(&sm.s_done, (uint32_t)(kb & 1), abort_flag, error, 33);
     tc_fence_after_sync();
 #pragma unroll 1
-    for (int c0 = 0; c0 < kTile; c0 += 32) {
+    for (int c0 = 0; c0 < kKeyBlock; c0 += 32) {
       uint32_t rs[32], rp[32];
       tmem_ld_32x32(tmem_s + lane_base + c0, rs);
       tmem_ld_32x32(tmem_dp + lane_base + c0, rp);
@@ -530,7 +556,7 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       }
 #pragma unroll
       for (int g = 0; g < 4; ++g)
-        store_swizzled_chunk(sm.ds[c0 >> 6], row, ((c0 & 63) >> 3) + g,
+        store_swizzled_chunk(sm.ds, row, (c0 >> 3) + g,
                              make_uint4(pack_bf16(ds[8 * g], ds[8 * g + 1]), pack_bf16(ds[8 * g + 2], ds[8 * g + 3]),
                                         pack_bf16(ds[8 * g + 4], ds[8 * g + 5]), pack_bf16(ds[8 * g + 6], ds[8 * g + 7])));
     }
@@ -539,7 +565,11 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     __syncthreads();
     if (tid == 0) {
       tc_fence_after_sync();
-      issue_gradient(tmem_dq, sm.ds, sm.stream_a[0], idesc_g, kb != 0);   // dQ += dS K
+#pragma unroll
+      for (int k16 = 0; k16 < kKeyBlock / 16; ++k16)   // dQ += dS K, 16 keys per MMA, K consumed MN-major
+        mma_f16(tmem_dq, smem_desc_k_major_sw128(smem_u32(sm.ds) + k16 * 32),
+                smem_desc_mn_major_sw128(smem_u32(sm.k[0]) + k16 * 16 * 128, kKeyBoxBytes), idesc_g,
+                kb != 0 || k16 != 0);
       mma_commit(&sm.acc_done);
     }
     mbar_wait(&sm.acc_done, (uint32_t)(kb & 1), abort_flag, error, 34);
@@ -565,7 +595,7 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(sm.tmem_base, 512);
+  if (warp == 0) tmem_dealloc(sm.tmem_base, 256);
 }
 
 int32_t check_attn(const void *q, const void *k, const void *v, int64_t tokens, int32_t H, int32_t D) {
@@ -576,9 +606,9 @@ int32_t check_attn(const void *q, const void *k, const void *v, int64_t tokens, 
   return TGB_STATUS_OK;
 }
 
-int32_t head_map(CUtensorMap *map, const void *base, int64_t tokens, int32_t H, int32_t D) {
+int32_t head_map(CUtensorMap *map, const void *base, int64_t tokens, int32_t H, int32_t D, int box_rows = kTile) {
   return make_tensor_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, (uint64_t)tokens, (uint64_t)H * D,
-                            (uint64_t)H * D * 2, 64, kTile);
+                            (uint64_t)H * D * 2, 64, (uint32_t)box_rows);
 }
 
 }  // namespace
@@ -595,13 +625,13 @@ extern "C" int32_t tgb_varlen_attn_fwd(const void *q, const void *k, const void 
   if (!out || !lse || !tiles || !error_flag) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
   CUtensorMap map_q, map_k, map_v;
   if ((rc = head_map(&map_q, q, tokens, H, D))) return rc;
-  if ((rc = head_map(&map_k, k, tokens, H, D))) return rc;
-  if ((rc = head_map(&map_v, v, tokens, H, D))) return rc;
+  if ((rc = head_map(&map_k, k, tokens, H, D, kKeyBlock))) return rc;
+  if ((rc = head_map(&map_v, v, tokens, H, D, kKeyBlock))) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const unsigned grid = (unsigned)(n_tiles * H);
+  const unsigned grid = (unsigned)n_tiles;
   const float scale_log2 = scale * kLog2e;
   if (D == 128) {
-    const size_t smem = sizeof(FwdSmem<2>) + 1024;
+    const size_t smem = sizeof(FwdSmem<2>);
     static bool configured = false;
     if (!configured) {
       TGB_CUDA(cudaFuncSetAttribute(k_attn_fwd<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -610,7 +640,7 @@ extern "C" int32_t tgb_varlen_attn_fwd(const void *q, const void *k, const void 
     k_attn_fwd<2><<<grid, 128, smem, st>>>(map_q, map_k, map_v, (const Tile *)tiles, H, scale_log2, causal,
                                            (__nv_bfloat16 *)out, (float *)lse, (int *)error_flag);
   } else {
-    const size_t smem = sizeof(FwdSmem<1>) + 1024;
+    const size_t smem = sizeof(FwdSmem<1>);
     static bool configured = false;
     if (!configured) {
       TGB_CUDA(cudaFuncSetAttribute(k_attn_fwd<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -638,27 +668,31 @@ extern "C" int32_t tgb_varlen_attn_bwd(const void *q, const void *k, const void 
   if ((rc = head_map(&map_k, k, tokens, H, D))) return rc;
   if ((rc = head_map(&map_v, v, tokens, H, D))) return rc;
   if ((rc = head_map(&map_do, dout, tokens, H, D))) return rc;
+  CUtensorMap map_k64, map_v64;
+  if ((rc = head_map(&map_k64, k, tokens, H, D, kKeyBlock))) return rc;
+  if ((rc = head_map(&map_v64, v, tokens, H, D, kKeyBlock))) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int64_t rows = tokens * H;
   k_attn_delta<<<(unsigned)ceil_div(rows * 32, 256), 256, 0, st>>>((const __nv_bfloat16 *)out,
                                                                   (const __nv_bfloat16 *)dout, rows, D,
                                                                   (float *)delta);
   TGB_LAUNCHED();
-  const unsigned grid = (unsigned)(n_tiles * H);
+  const unsigned grid = (unsigned)n_tiles;
 #define TGB_BWD(HV)                                                                                         \
   {                                                                                                         \
     const size_t smem = sizeof(BwdSmem<HV>) + 1024;                                                         \
+    const size_t smem_dq = sizeof(DqSmem<HV>);                                                              \
     static bool configured = false;                                                                         \
     if (!configured) {                                                                                      \
       TGB_CUDA(cudaFuncSetAttribute(k_attn_bwd_dkv<HV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-      TGB_CUDA(cudaFuncSetAttribute(k_attn_bwd_dq<HV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
+      TGB_CUDA(cudaFuncSetAttribute(k_attn_bwd_dq<HV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq)); \
       configured = true;                                                                                    \
     }                                                                                                       \
     k_attn_bwd_dkv<HV><<<grid, 128, smem, st>>>(map_q, map_k, map_v, map_do, (const Tile *)key_tiles, H, scale, \
                                                 causal, (const float *)lse, (const float *)delta,           \
                                                 (__nv_bfloat16 *)dk, (__nv_bfloat16 *)dv, (int *)error_flag); \
     TGB_LAUNCHED();                                                                                         \
-    k_attn_bwd_dq<HV><<<grid, 128, smem, st>>>(map_q, map_k, map_v, map_do, (const Tile *)query_tiles, H, scale, \
+    k_attn_bwd_dq<HV><<<grid, 128, smem_dq, st>>>(map_q, map_k64, map_v64, map_do, (const Tile *)query_tiles, H, scale, \
                                                causal, (const float *)lse, (const float *)delta,            \
                                                (__nv_bfloat16 *)dq, (int *)error_flag);                     \
     TGB_LAUNCHED();                                                                                         \

@@ -97,26 +97,31 @@ def gat_attention(graph, x_src, x_dst, a_src, a_dst, slope: float):
     return GATFunction.apply(x_src, x_dst, a_src, a_dst, graph, slope)
 
 
-def _attention_tiles(graph, device):
-    """int32 [n_tiles, 4] = (first query, sequence begin, sequence end, 0) for every
-    128-query tile of every sequence, heaviest (most key blocks) first."""
+def _attention_tiles(graph, device, heads):
+    """int32 [n, 4] = (first token of the tile, sequence begin, sequence end, head) for every
+    (128-token tile, head).  Order: longest sequence first, then head, then the heaviest tile of
+    that (sequence, head) first -- CTAs that are resident together then read the same K/V (or
+    Q/dO) stream, which keeps it in L2, while the long tiles still start early.  Returns the
+    table for the query-major kernels, the causal flag and the table for the key-major kernel."""
     cached = graph.__dict__.get("_attention_tiles")
-    if cached is not None and cached[0].device == device:
+    if cached is not None and cached[0].device == device and cached[3] == heads:
         return cached
     bounds = graph.sequence_boundaries().tolist()
     causal = graph._dense_boundary == "lower_inclusive"
-    rows = []
-    for begin, end in zip(bounds[:-1], bounds[1:]):
-        for q0 in range(begin, end, 128):
-            blocks = ((min(q0 + 128, end) if causal else end) - begin + 127) // 128
-            rows.append((blocks, q0, begin, end))
-    def table(ordered):
-        return torch.tensor([[q0, b, e, 0] for _, q0, b, e in ordered], dtype=torch.int32).reshape(-1, 4).to(device)
+    sequences = sorted(zip(bounds[:-1], bounds[1:]), key=lambda be: be[0] - be[1])
 
-    by_query = sorted(rows, key=lambda r: -r[0])
-    # the key-major backward kernel loops over the query blocks that see a key tile
-    by_key = sorted(rows, key=lambda r: -(((r[3] - r[1]) if causal else (r[3] - r[2])) + 127) // 128)
-    graph.__dict__["_attention_tiles"] = (table(by_query), causal, table(by_key))
+    def table(key_major):
+        rows = []
+        for begin, end in sequences:
+            starts = list(range(begin, end, 128))
+            # query-major + causal: later tiles see more keys; key-major + causal: earlier tiles see more queries
+            if causal and not key_major:
+                starts.reverse()
+            for head in range(heads):
+                rows.extend((t0, begin, end, head) for t0 in starts)
+        return torch.tensor(rows, dtype=torch.int32).reshape(-1, 4).to(device)
+
+    graph.__dict__["_attention_tiles"] = (table(False), causal, table(True), heads)
     return graph.__dict__["_attention_tiles"]
 
 
@@ -134,7 +139,7 @@ class VarlenAttentionFunction(torch.autograd.Function):
         if tokens != graph.num_dst:
             raise ValueError(f"fields must have {graph.num_dst} rows, got {tokens}")
         q, k, v = query.contiguous(), key.contiguous(), value.contiguous()
-        tiles, causal, _ = _attention_tiles(graph, q.device)
+        tiles, causal, _, _ = _attention_tiles(graph, q.device, H)
         out = torch.empty_like(q)
         lse = torch.empty((tokens, H), dtype=torch.float32, device=q.device)
         with torch.cuda.device(q.device):
@@ -153,7 +158,7 @@ class VarlenAttentionFunction(torch.autograd.Function):
         q, k, v, out, lse = ctx.saved_tensors
         tokens, H, D = q.shape
         d_out = grad_output.contiguous().to(torch.bfloat16)
-        query_tiles, causal, key_tiles = _attention_tiles(ctx.graph, q.device)
+        query_tiles, causal, key_tiles, _ = _attention_tiles(ctx.graph, q.device, H)
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         delta = torch.empty((tokens, H), dtype=torch.float32, device=q.device)
         with torch.cuda.device(q.device):
