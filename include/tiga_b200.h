@@ -126,6 +126,16 @@ TGB_API int32_t tgb_csr_plan_destroy(tgb_csr_plan *plan);
  * and the bucket summary of PlanDegreeBuckets.cpp:145-170. */
 TGB_API int32_t tgb_csr_plan_info(const tgb_csr_plan *plan, int64_t *info16);
 
+/* Edge map: this CSR is a sub-relation of a larger edge list (the owned-source
+ * or ghost-source part of a halo partition, python/tiga/distributed/
+ * transport.py:790-895 splits rows the same way), and edge e of the CSR is
+ * entry edge_map[e] (uint32, device memory kept alive by the caller) of the
+ * weight array passed to *_fwd / *_bwd_dx and of the dw array written by
+ * *_bwd_dw.  Saves the gather/scatter passes that would otherwise permute the
+ * weights and their gradients on every call.  Set once, right after create. */
+TGB_API int32_t tgb_csr_plan_set_edge_map(tgb_csr_plan *plan,
+                                          const void *edge_map, uint64_t stream);
+
 /* Device pointers of the plan's arrays, for tests and Graph.transpose():
  * which = 0 forward row order (int32[num_dst]), 1 transposed row_ptr
  * (int64[num_src+1]), 2 transposed destinations (int32[E]), 3 transposed edge

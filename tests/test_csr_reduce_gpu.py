@@ -296,3 +296,35 @@ def test_unsupported_inputs_raise():
     with pytest.raises(ValueError):
         WeightedSum()(graph=g, src={"x": torch.randn(7, 4, device="cuda")}, dst={},
                       edge={"weight": torch.rand(16, device="cuda")})
+
+
+@pytest.mark.parametrize("F", (3, 64, 128))
+def test_edge_map_addresses_weights_and_dw_in_a_larger_edge_list(oracle, F):
+    # a CSR whose edges are a subset (in order) of a longer per-edge array, as the halo runtime builds them
+    row_ptr, col = syn.rmat_csr(9, 10, seed=17)
+    n, E = row_ptr.numel() - 1, col.numel()
+    gen = torch.Generator().manual_seed(F)
+    total = 2 * E + 5
+    positions = torch.sort(torch.randperm(total, generator=gen)[:E]).values
+    w_all = torch.rand(total, generator=gen)
+    x = torch.randn(n, F, generator=gen)
+    dy = torch.randn(n, F, generator=gen)
+    g = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=n)
+    g._edge_map = positions.to(torch.int32)
+    plan = g.native_plan(transpose=True)
+    w_sub = w_all[positions].numpy()
+    out, _ = ops.csr_reduce_forward(plan, "sum", x.cuda(), w_all.cuda(), 0.0)
+    ref = oracle.wsum_fwd(row_ptr.numpy(), col.numpy(), x.numpy(), w_sub)
+    assert_sum_close(out.cpu().numpy(), ref, oracle.wsum_fwd(row_ptr.numpy(), col.numpy(), x.abs().numpy(), w_sub))
+    dx = ops.csr_reduce_backward_dx(plan, "sum", dy.cuda(), w_all.cuda())
+    ref_dx = oracle.wsum_bwd_dx(row_ptr.numpy(), col.numpy(), n, dy.numpy(), w_sub)
+    assert_sum_close(dx.cpu().numpy(), ref_dx,
+                     oracle.wsum_bwd_dx(row_ptr.numpy(), col.numpy(), n, dy.abs().numpy(), w_sub))
+    dw_all = torch.full((total,), -7.0, device="cuda")
+    ops.csr_reduce_backward_dw(plan, "sum", dy.cuda(), x.cuda(), out=dw_all)
+    ref_dw = oracle.wsum_bwd_dw(row_ptr.numpy(), col.numpy(), dy.numpy(), x.numpy())
+    got = dw_all.cpu()
+    assert_dot_close(oracle, got[positions].numpy(), ref_dw, row_ptr, col, dy, x)
+    untouched = torch.ones(total, dtype=torch.bool)
+    untouched[positions] = False
+    assert torch.all(got[untouched] == -7.0)

@@ -28,6 +28,8 @@ class OracleBackend:
         from oracle import oracle
 
         row_ptr, col = self._csr(graph)
+        if w is not None and graph._edge_map is not None:
+            w = w[graph._edge_map.long()]
         out = torch.from_numpy(oracle.wsum_fwd(row_ptr, col, x.numpy(), None if w is None else w.numpy()))
         if accumulate_into is not None:
             accumulate_into += out
@@ -38,14 +40,17 @@ class OracleBackend:
         from oracle import oracle
 
         row_ptr, col = self._csr(graph)
+        if w is not None and graph._edge_map is not None:
+            w = w[graph._edge_map.long()]
         return torch.from_numpy(oracle.wsum_bwd_dx(row_ptr, col, graph.num_src, dy.numpy(),
                                                    None if w is None else w.numpy()))
 
-    def backward_dw(self, graph, dy, x):
+    def backward_dw(self, graph, dy, x, out):
         from oracle import oracle
 
         row_ptr, col = self._csr(graph)
-        return torch.from_numpy(oracle.wsum_bwd_dw(row_ptr, col, dy.numpy(), x.numpy()))
+        out[graph._edge_map.long()] = torch.from_numpy(oracle.wsum_bwd_dw(row_ptr, col, dy.numpy(), x.numpy()))
+        return out
 
 
 def _free_port():

@@ -361,7 +361,7 @@ k_edge_dot_vec(const GatherArgs a, const float *dy, float *dw) {
         if (lane == k0 + u) mine = p;
       }
     }
-    if (e < end) dw[e] = mine;
+    if (e < end) dw[a.eid ? (int64_t)a.eid[e] : e] = mine;
   }
 }
 
@@ -382,7 +382,7 @@ k_edge_dot_scalar(const GatherArgs a, const float *dy, float *dw) {
       if (ARG_FILTER && a.arg_in[row * F + f] != (int32_t)e) continue;
       p = __fadd_rn(p, __fmul_rn(dy[row * F + f], a.x[c * F + f]));
     }
-    dw[e] = p;
+    dw[a.eid ? (int64_t)a.eid[e] : e] = p;
   }
 }
 
@@ -598,6 +598,12 @@ int32_t tgb_csr_reduce_fwd(const tgb_csr_plan *plan, int32_t reducer,
   if (reducer == TGB_REDUCER_MAX && s.vec && (((uintptr_t)aux | (uintptr_t)a.arg_partial) & 15u))
     s = scalar_shape(F);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (side.eid && w) {   // weights are addressed through the plan's edge map
+    if (reducer == TGB_REDUCER_MAX)
+      TGB_FAIL(TGB_STATUS_UNSUPPORTED, "the max reducer does not take an edge map");
+    return plan->index_bits == 32 ? launch_gather<int32_t, int32_t, kSum, true, true, false>(a, s, st)
+                                  : launch_gather<int64_t, int64_t, kSum, true, true, false>(a, s, st);
+  }
 #define TGB_FWD(PT, MODE, HW) launch_gather<PT, PT, MODE, HW, false, false>(a, s, st)
   if (plan->index_bits == 32) {
     if (reducer == TGB_REDUCER_MAX) return w ? TGB_FWD(int32_t, kMax, true) : TGB_FWD(int32_t, kMax, false);

@@ -437,6 +437,29 @@ int32_t tgb_csr_plan_destroy(tgb_csr_plan *plan) {
   return TGB_STATUS_OK;
 }
 
+namespace tgb {
+namespace {
+// eid_t[k] <- map[eid_t[k]]: the transposed side then addresses weights directly
+__global__ void k_compose_edge_map(uint32_t *eid_t, const uint32_t *map, int64_t E) {
+  int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (k < E) eid_t[k] = map[eid_t[k]];
+}
+}  // namespace
+}  // namespace tgb
+
+int32_t tgb_csr_plan_set_edge_map(tgb_csr_plan *plan, const void *edge_map, uint64_t stream) {
+  if (!plan || !edge_map) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null plan or edge map");
+  if (plan->fwd.eid) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "the plan already has an edge map");
+  plan->fwd.eid = static_cast<const uint32_t *>(edge_map);
+  if ((plan->flags & TGB_PLAN_TRANSPOSE) && plan->num_edges > 0) {
+    tgb::k_compose_edge_map<<<tgb::grid_for(plan->num_edges), tgb::kThreads, 0,
+                              reinterpret_cast<cudaStream_t>(stream)>>>(
+        const_cast<uint32_t *>(plan->bwd.eid), plan->fwd.eid, plan->num_edges);
+    TGB_LAUNCHED();
+  }
+  return TGB_STATUS_OK;
+}
+
 int32_t tgb_csr_plan_info(const tgb_csr_plan *plan, int64_t *info) {
   if (!plan || !info) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null plan or output");
   for (int i = 0; i < 16; ++i) info[i] = 0;

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "tgb_csr_plan_create": (_i32, [_vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp, _u64, _vp, _u64, _u64,
                                    ctypes.POINTER(_vp)]),
     "tgb_csr_plan_destroy": (_i32, [_vp]),
+    "tgb_csr_plan_set_edge_map": (_i32, [_vp, _vp, _u64]),
     "tgb_csr_plan_info": (_i32, [_vp, ctypes.POINTER(_i64)]),
     "tgb_csr_plan_array": (_i32, [_vp, _i32, ctypes.POINTER(_u64), ctypes.POINTER(_i64)]),
     "tgb_csr_plan_scratch_bytes": (_i32, [_vp, _i32, _i32, _i64, _i32, ctypes.POINTER(_u64)]),

@@ -114,10 +114,10 @@ class NativeBackend:
         return ops.csr_reduce_backward_dx(graph.native_plan(transpose=True), "sum", dy, w)
 
     @staticmethod
-    def backward_dw(graph, dy, x):
+    def backward_dw(graph, dy, x, out):
         from .. import ops
 
-        return ops.csr_reduce_backward_dw(graph.native_plan(transpose=False), "sum", dy, x)
+        return ops.csr_reduce_backward_dw(graph.native_plan(transpose=False), "sum", dy, x, out=out)
 
 
 class DistributedRuntime:
@@ -201,12 +201,17 @@ def build_shard_plan(graph: Graph, transport: ProcessGroupTransport) -> ShardPla
         torch.cumsum(counts, 0, out=ptr[1:])
         return Graph.from_csr(ptr.to(index_dtype), columns.to(index_dtype).contiguous(), num_src=num_src)
 
+    if local_col.numel() >= 1 << 31:
+        raise NotImplementedError("more than 2^31 local edges per rank")
     edges_own = torch.nonzero(is_own).reshape(-1)
     edges_ghost = torch.nonzero(~is_own).reshape(-1)
     ghost_cols = local_col[edges_ghost]
     ghosts = torch.unique(ghost_cols, sorted=True)
     graph_own = sub_relation(is_own, local_col[edges_own] - begin, owned)
     graph_ghost = sub_relation(~is_own, torch.searchsorted(ghosts, ghost_cols), max(int(ghosts.numel()), 0))
+    # the two sub-relations address the caller's per-edge arrays through their positions
+    graph_own._edge_map = edges_own.to(torch.int32)
+    graph_ghost._edge_map = edges_ghost.to(torch.int32)
 
     # ghosts are sorted, owners are contiguous ranges => each owner's ids are one slice
     bound_t = torch.tensor(bounds, dtype=torch.int64, device=device)
@@ -248,8 +253,7 @@ class _HaloWeightedSum(torch.autograd.Function):
         rows = x.contiguous().reshape(shard.owned, -1)
         F = rows.shape[1]
         w_flat = None if w is None else w.contiguous().reshape(-1)
-        w_own = None if w_flat is None else w_flat[shard.edges_own]
-        w_ghost = None if w_flat is None else w_flat[shard.edges_ghost]
+        w_own = w_ghost = w_flat        # the sub-relations read it through their edge maps
         ghost_x = torch.empty((int(shard.ghosts.numel()), F), dtype=rows.dtype, device=rows.device)
         packed = [(p, rows.index_select(0, ids)) for p, ids in enumerate(shard.send_ids) if ids.numel()]
         receives = [(p, ghost_x[o:o + c]) for p, (o, c) in enumerate(shard.recv_offsets) if c and p != shard.rank]
@@ -260,22 +264,23 @@ class _HaloWeightedSum(torch.autograd.Function):
             out = backend.forward(shard.graph_ghost, ghost_x, w_ghost, accumulate_into=out)
         ctx.shard, ctx.runtime = shard, runtime
         ctx.x_shape, ctx.w_shape = x.shape, None if w is None else w.shape
-        ctx.save_for_backward(rows, w_own, w_ghost, ghost_x)
+        ctx.save_for_backward(rows, w_flat, ghost_x)
         ctx.halo_bytes = ghost_x.numel() * ghost_x.element_size()
         return out.reshape((shard.owned,) + tuple(x.shape[1:]))
 
     @staticmethod
     def backward(ctx, grad_output):
-        rows, w_own, w_ghost, ghost_x = ctx.saved_tensors
+        rows, w_flat, ghost_x = ctx.saved_tensors
+        w_own = w_ghost = w_flat
         shard, runtime = ctx.shard, ctx.runtime
         transport, backend = runtime.transport, runtime.backend
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         dy = grad_output.contiguous().reshape(shard.owned, -1)
         F = dy.shape[1]
         dx = dw = None
+        works, landed = [], []
         if need_x:
-            # ghost cotangents go back to their owners while the owned part is computed
-            works, landed = [], []
+            # ghost cotangents go back to their owners while everything else of the backward runs
             if shard.edges_ghost.numel() or any(ids.numel() for ids in shard.send_ids):
                 d_ghost = (backend.backward_dx(shard.graph_ghost, dy, w_ghost) if shard.ghosts.numel()
                            else dy.new_zeros((0, F)))
@@ -286,17 +291,18 @@ class _HaloWeightedSum(torch.autograd.Function):
                            if c and p != shard.rank],
                     receives=[(p, buffer) for p, _, buffer in landed])
             dx = backend.backward_dx(shard.graph_own, dy, w_own)
+        if need_w and ctx.w_shape is not None:
+            dw = torch.empty(shard.num_local_edges, dtype=dy.dtype, device=dy.device)
+            if shard.edges_own.numel():      # each part writes its own entries of dw through its edge map
+                backend.backward_dw(shard.graph_own, dy, rows, dw)
+            if shard.edges_ghost.numel():
+                backend.backward_dw(shard.graph_ghost, dy, ghost_x, dw)
+            dw = dw.reshape(ctx.w_shape)
+        if need_x:
             transport.wait(works)
             for _, ids, buffer in landed:            # fixed peer order: deterministic
                 dx.index_add_(0, ids, buffer)
             dx = dx.reshape(ctx.x_shape)
-        if need_w and ctx.w_shape is not None:
-            dw = torch.empty(shard.num_local_edges, dtype=dy.dtype, device=dy.device)
-            if shard.edges_own.numel():
-                dw[shard.edges_own] = backend.backward_dw(shard.graph_own, dy, rows)
-            if shard.edges_ghost.numel():
-                dw[shard.edges_ghost] = backend.backward_dw(shard.graph_ghost, dy, ghost_x)
-            dw = dw.reshape(ctx.w_shape)
         return dx, dw, None, None
 
 

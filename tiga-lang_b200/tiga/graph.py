@@ -61,6 +61,7 @@ class Graph:
         self._destination_cache = None
         self._plans = {}
         self._transpose_cache = None
+        self._edge_map = None   # set for sub-relations whose weights live in a larger edge list
 
     # ------------------------------------------------------------ properties
     @property
@@ -373,7 +374,7 @@ class Graph:
         plan = self._plans.get(True) or (None if transpose else self._plans.get(False))
         if plan is None:
             row_ptr, col_idx = self.resolve_csr()
-            plan = CSRPlan(row_ptr, col_idx, self.num_src, transpose=transpose)
+            plan = CSRPlan(row_ptr, col_idx, self.num_src, transpose=transpose, edge_map=self._edge_map)
             self._plans[transpose] = plan
         return plan
 

@@ -63,11 +63,14 @@ def csr_reduce_backward_dx(plan: CSRPlan, reducer: str, dy: torch.Tensor, w: tor
     return dx
 
 
-def csr_reduce_backward_dw(plan: CSRPlan, reducer: str, dy: torch.Tensor, x: torch.Tensor, aux=None):
+def csr_reduce_backward_dw(plan: CSRPlan, reducer: str, dy: torch.Tensor, x: torch.Tensor, aux=None, out=None):
+    """dw per edge; with a plan that has an edge map the results are written to out[edge_map[e]]."""
     lib = _native.lib()
     rid = _REDUCER_IDS[reducer]
     F = dy.shape[1]
-    dw = torch.empty((plan.num_edges,), dtype=torch.float32, device=dy.device)
+    if plan.edge_map is not None and out is None:
+        raise ValueError("a plan with an edge map writes dw into the caller's full-length array: pass out=")
+    dw = out if out is not None else torch.empty((plan.num_edges,), dtype=torch.float32, device=dy.device)
     keep, scratch, scratch_bytes = plan.scratch(0, rid, F)
     with torch.cuda.device(dy.device):
         _native.check(lib.tgb_csr_reduce_bwd_dw(plan.handle, rid, _ptr(dy), _ptr(x), _ptr(aux), _ptr(dw), F,

@@ -14,7 +14,8 @@ class CSRPlan:
     device memory is a torch uint8 tensor owned by this object; the library
     only holds pointers into it."""
 
-    def __init__(self, row_ptr: torch.Tensor, col_idx: torch.Tensor, num_src: int, *, transpose: bool):
+    def __init__(self, row_ptr: torch.Tensor, col_idx: torch.Tensor, num_src: int, *, transpose: bool,
+                 edge_map: torch.Tensor | None = None):
         if not row_ptr.is_cuda:
             raise RuntimeError("native plans exist for CUDA graphs only")
         if row_ptr.dtype != col_idx.dtype:
@@ -44,6 +45,13 @@ class CSRPlan:
                 self.index_bits, flags, self._persistent.data_ptr(), self._persistent.numel(),
                 scratch.data_ptr(), scratch.numel(), stream, ctypes.byref(handle)), "tgb_csr_plan_create")
         self._handle = handle
+        self.edge_map = None
+        if edge_map is not None:
+            # edge e of this CSR is entry edge_map[e] of the caller's weight / dw arrays
+            self.edge_map = edge_map.to(device=self.device, dtype=torch.int32).contiguous()
+            with torch.cuda.device(self.device):
+                _native.check(lib.tgb_csr_plan_set_edge_map(self._handle, self.edge_map.data_ptr(), stream),
+                              "tgb_csr_plan_set_edge_map")
         info = (ctypes.c_int64 * 16)()
         _native.check(lib.tgb_csr_plan_info(self._handle, info), "tgb_csr_plan_info")
         self.info = {
