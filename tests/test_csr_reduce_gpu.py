@@ -7,6 +7,7 @@ import pytest
 import torch
 
 import tiga as tg
+from conftest import assert_sum_close
 from tiga import ops
 from tiga import synthetic as syn
 
