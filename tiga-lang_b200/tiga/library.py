@@ -108,28 +108,44 @@ def register_message_passing(kernel, *, graph, src: Mapping[str, Any], dst: Mapp
     torch.library.register_fake(qualified, lambda *flat: flat[2].new_empty(output_shape, dtype=output_dtype),
                                 lib=library)
 
-    def setup_context(ctx, inputs, output):
-        ctx.save_for_backward(*inputs)
+    # The backward is a dispatcher op of its own (opaque to tracing, with a fake implementation), so
+    # compiled / exported graphs can differentiate through the forward op.
+    float_positions = tuple(i for i, v in enumerate(values) if v.is_floating_point())
+    backward_name = f"{op_name}_backward"
+    library.define(f"{backward_name}(Tensor grad_output, {arguments}) -> Tensor[]")
 
-    def backward(ctx, grad_output):
-        replay, wanted, positions = [], [], []
-        for index, (value, needed) in enumerate(zip(ctx.saved_tensors, ctx.needs_input_grad)):
-            local = value.detach()
-            if needed and local.is_floating_point():
-                local.requires_grad_(True)
-                wanted.append(local)
-                positions.append(index)
-            replay.append(local)
-        if not wanted:
-            return (None,) * len(replay)
+    def backward_implementation(grad_output, *flat):
+        replay = [value.detach() for value in flat]
+        wanted = []
+        for position in float_positions:
+            replay[2 + position].requires_grad_(True)
+            wanted.append(replay[2 + position])
         fields = unpack(replay[2:])
         with torch.enable_grad():
             output = kernel(graph=runtime_graph(replay), src=fields["src"], dst=fields["dst"],
                             edge=fields["edge"], **params)
             computed = torch.autograd.grad(output, wanted, grad_output.contiguous(), allow_unused=True)
-        gradients = [None] * len(replay)
-        for position, gradient in zip(positions, computed):
-            gradients[position] = gradient
+        return [g if g is not None else torch.zeros_like(w) for g, w in zip(computed, wanted)]
+
+    library.impl(backward_name, backward_implementation, "CompositeExplicitAutograd")
+    torch.library.register_fake(
+        f"tiga::{backward_name}",
+        lambda grad_output, *flat: [torch.empty_like(flat[2 + position]) for position in float_positions],
+        lib=library)
+    backward_operation = getattr(getattr(torch.ops.tiga, backward_name), "default")
+
+    def setup_context(ctx, inputs, output):
+        ctx.save_for_backward(*inputs)
+
+    def backward(ctx, grad_output):
+        saved = ctx.saved_tensors
+        if not any(ctx.needs_input_grad[2 + position] for position in float_positions):
+            return (None,) * len(saved)
+        computed = backward_operation(grad_output, *saved)
+        gradients = [None] * len(saved)
+        for position, gradient in zip(float_positions, computed):
+            if ctx.needs_input_grad[2 + position]:
+                gradients[2 + position] = gradient
         return tuple(gradients)
 
     torch.library.register_autograd(qualified, backward, setup_context=setup_context, lib=library)
