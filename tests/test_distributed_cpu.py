@@ -138,3 +138,47 @@ def test_sharded_weighted_sum_matches_single_process(tmp_path, oracle, world, ba
         if balance == "auto":
             np.testing.assert_array_equal(data["ghosts"], expect_ghosts)
     assert covered == n
+
+
+def _failing_worker(rank, world, port, result_dir):
+    """Rank 1 leaves before the halo exchange (a host-side failure between steps);
+    rank 0 must get an exception from its exchange instead of waiting forever."""
+    import datetime
+
+    for path in (ROOT, os.path.join(ROOT, "tiga-lang_b200")):
+        sys.path.insert(0, path)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    import tiga as tg
+    from tiga import synthetic as syn
+    from tiga.distributed.runtime import DistributedRuntime, ProcessGroupTransport, halo_weighted_sum, shard_plan_for
+
+    row_ptr, col = syn.rmat_csr(7, 6, seed=13)
+    n = row_ptr.numel() - 1
+    graph = tg.Graph.from_csr(row_ptr, col, num_src=n).halo(tg.DeviceMesh("cpu", world))
+    runtime = DistributedRuntime(ProcessGroupTransport(), backend=OracleBackend())
+    with runtime:
+        shard = shard_plan_for(graph, runtime)          # both ranks take part in the plan
+        dist.barrier()
+        if rank == 1:
+            os._exit(0)                                  # leaves between steps, nothing in flight
+        x = torch.randn(shard.owned, 4)
+        try:
+            halo_weighted_sum(graph, x, None, runtime)
+            outcome = "no error"
+        except Exception as error:                       # the exchange must fail, not hang
+            outcome = f"raised {type(error).__name__}"
+    with open(os.path.join(result_dir, "rank0.txt"), "w") as handle:
+        handle.write(outcome)
+    os._exit(0)
+
+
+def test_peer_leaving_between_steps_surfaces_as_an_error(tmp_path):
+    port = _free_port()
+    context = mp.start_processes(_failing_worker, args=(2, port, str(tmp_path)), nprocs=2, join=False,
+                                 start_method="spawn")
+    for process in context.processes:
+        process.join(90)
+        assert not process.is_alive(), "a rank is still waiting: the failure did not surface"
+    assert (tmp_path / "rank0.txt").read_text().startswith("raised")
