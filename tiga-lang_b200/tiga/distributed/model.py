@@ -138,7 +138,13 @@ def destination_owner(entity: int, entities: int, world_size: int) -> int:
     return extra + (entity - boundary) // base if base else extra
 
 
-ROW_COST_IN_EDGES = 32  # balance="cost": one destination row weighs as much as this many edges
+import os
+
+# balance="cost": one destination row weighs as much as this many edges.  Measured on 4 B200s with the
+# GCN layer (R-MAT, 2^20 nodes per GPU), ms per step for 8 / 16 / 24 / 32 / 64: 22.6 / 21.2 / 20.2 /
+# 19.0 / 21.2 -- a row costs its pointer reads, two output-row passes (owned and ghost part), its
+# share of the dense linear and of the halo traffic.
+ROW_COST_IN_EDGES = int(os.environ.get("TIGA_B200_ROW_COST", "32"))
 
 
 def partition_bounds(entities: int, world_size: int, *, row_ptr=None, balance: str = "auto"):
