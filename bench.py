@@ -443,7 +443,7 @@ def run_native_multi(args, rank, world, device):
     N, E = row_ptr.numel() - 1, col.numel()
     graph = tg.Graph.from_csr(row_ptr, col, num_src=N).halo(
         tg.DeviceMesh("cuda", world), partition=tg.ByDestination(balance="cost"))
-    runtime = DistributedRuntime(NCCLTransport(device=device))
+    runtime = DistributedRuntime(NCCLTransport(device=device), trace=True)
 
     class GCNLayer(tg.MessagePassing):
         reducer = tg.sum()
@@ -480,6 +480,7 @@ def run_native_multi(args, rank, world, device):
     for _ in range(max(args.warmup, 3)):
         step(x, weight, lin)
     torch.cuda.synchronize()
+    runtime.reset_trace()
     dist.barrier()
     sampler = ClockSampler(device.index)
     sampler.start()
@@ -496,6 +497,13 @@ def run_native_multi(args, rank, world, device):
     recording["on"] = False
     launches = _native.launch_count() - launches_before
     clocks = sampler.stop()
+    phases = runtime.phase_times()
+    runtime.trace = False
+    phase_names = sorted(phases)
+    mine = torch.tensor([phases[k] / args.steps for k in phase_names] + [begin.elapsed_time(end) / args.steps],
+                        device=device, dtype=torch.float64)
+    all_phases = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(all_phases, mine)
     elapsed = torch.tensor([begin.elapsed_time(end)], device=device, dtype=torch.float64)
     dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
     ms_per_step = float(elapsed.item()) / args.steps
@@ -526,6 +534,8 @@ def run_native_multi(args, rank, world, device):
                        "num_nodes": N, "num_edges": E, "features": F, "partition": "contiguous ranges balancing edges + 32 per row",
                        "per_rank_edges_rows_ghosts_ghostedges": per_rank,
                        "halo_bytes_per_step_rank0": int(shard.ghosts.numel()) * F * 4 * 2,
+                       "phase_ms_per_rank": {name: [round(float(r[i]), 3) for r in all_phases]
+                                             for i, name in enumerate(phase_names + ["step (own clock)"])},
                        "l2": "inputs exceed L2"},
             "roofline": {"bound": "hbm", "kernel": f"rank 0 {dominant} (owned + ghost parts)",
                          "achieved": round(achieved, 1), "peak": peak, "peak_kind": f"of {peak_kind}",

@@ -121,11 +121,43 @@ class NativeBackend:
 
 
 class DistributedRuntime:
-    def __init__(self, transport: ProcessGroupTransport, *, backend=None):
+    """``with DistributedRuntime(transport): kernel(graph=g.halo(mesh), ...)``.
+
+    ``trace=True`` records a CUDA event on the compute stream at every phase boundary of a sharded call
+    (pack + start exchange, owned-source part, exposed wait for the halo, ghost-source part, ...);
+    ``phase_times()`` turns the marks of the calls since the last ``reset_trace()`` into milliseconds
+    per phase.  Device timestamps, not host clocks, so an exposed wait is what the stream really waited
+    (the reference's ``last_execution_trace`` keeps host nanoseconds and declines to claim overlap,
+    python/tiga/distributed/transport.py:1311-1370)."""
+
+    def __init__(self, transport: ProcessGroupTransport, *, backend=None, trace: bool = False):
         self.transport = transport
         self.backend = backend or NativeBackend()
         self._token = None
-        self.last_execution_trace = None
+        self.trace = bool(trace)
+        self.last_execution_trace = []
+
+    def reset_trace(self) -> None:
+        self.last_execution_trace = []
+
+    def mark(self, name: str, device) -> None:
+        if self.trace and torch.device(device).type == "cuda":
+            event = torch.cuda.Event(enable_timing=True)
+            event.record(torch.cuda.current_stream(device))
+            self.last_execution_trace.append((name, event))
+
+    def phase_times(self) -> dict:
+        """Milliseconds between consecutive marks, summed per phase name (the name of a mark is the
+        phase that ENDS there).  Synchronises."""
+        totals = {}
+        marks = self.last_execution_trace
+        if marks:
+            marks[-1][1].synchronize()
+        for (_, before), (name, after) in zip(marks[:-1], marks[1:]):
+            if name.endswith(":begin"):
+                continue
+            totals[name] = totals.get(name, 0.0) + before.elapsed_time(after)
+        return totals
 
     def __enter__(self):
         self._token = _ACTIVE.set(self)
@@ -254,14 +286,20 @@ class _HaloWeightedSum(torch.autograd.Function):
         F = rows.shape[1]
         w_flat = None if w is None else w.contiguous().reshape(-1)
         w_own = w_ghost = w_flat        # the sub-relations read it through their edge maps
+        device = rows.device
+        runtime.mark("forward:begin", device)
         ghost_x = torch.empty((int(shard.ghosts.numel()), F), dtype=rows.dtype, device=rows.device)
         packed = [(p, rows.index_select(0, ids)) for p, ids in enumerate(shard.send_ids) if ids.numel()]
         receives = [(p, ghost_x[o:o + c]) for p, (o, c) in enumerate(shard.recv_offsets) if c and p != shard.rank]
         works = transport.exchange(sends=packed, receives=receives)      # halo in flight ...
+        runtime.mark("forward pack + start exchange", device)
         out = backend.forward(shard.graph_own, rows, w_own)              # ... while owned-source edges reduce
+        runtime.mark("forward owned-source part", device)
         transport.wait(works)
+        runtime.mark("forward exposed halo wait", device)
         if shard.edges_ghost.numel():
             out = backend.forward(shard.graph_ghost, ghost_x, w_ghost, accumulate_into=out)
+        runtime.mark("forward ghost-source part", device)
         ctx.shard, ctx.runtime = shard, runtime
         ctx.x_shape, ctx.w_shape = x.shape, None if w is None else w.shape
         ctx.save_for_backward(rows, w_flat, ghost_x)
@@ -279,6 +317,8 @@ class _HaloWeightedSum(torch.autograd.Function):
         F = dy.shape[1]
         dx = dw = None
         works, landed = [], []
+        device = dy.device
+        runtime.mark("backward:begin", device)
         if need_x:
             # ghost cotangents go back to their owners while everything else of the backward runs
             if shard.edges_ghost.numel() or any(ids.numel() for ids in shard.send_ids):
@@ -290,7 +330,9 @@ class _HaloWeightedSum(torch.autograd.Function):
                     sends=[(p, d_ghost[o:o + c]) for p, (o, c) in enumerate(shard.recv_offsets)
                            if c and p != shard.rank],
                     receives=[(p, buffer) for p, _, buffer in landed])
+            runtime.mark("backward ghost cotangents + start exchange", device)
             dx = backend.backward_dx(shard.graph_own, dy, w_own)
+            runtime.mark("backward dx owned part", device)
         if need_w and ctx.w_shape is not None:
             dw = torch.empty(shard.num_local_edges, dtype=dy.dtype, device=dy.device)
             if shard.edges_own.numel():      # each part writes its own entries of dw through its edge map
@@ -298,11 +340,14 @@ class _HaloWeightedSum(torch.autograd.Function):
             if shard.edges_ghost.numel():
                 backend.backward_dw(shard.graph_ghost, dy, ghost_x, dw)
             dw = dw.reshape(ctx.w_shape)
+            runtime.mark("backward dw", device)
         if need_x:
             transport.wait(works)
+            runtime.mark("backward exposed cotangent wait", device)
             for _, ids, buffer in landed:            # fixed peer order: deterministic
                 dx.index_add_(0, ids, buffer)
             dx = dx.reshape(ctx.x_shape)
+            runtime.mark("backward add received cotangents", device)
         return dx, dw, None, None
 
 
