@@ -260,6 +260,20 @@ TGB_API int32_t tgb_gat_bwd(const tgb_csr_plan *plan, const void *x_src,
                             uint64_t stream);
 
 /* ------------------------------------------------------------------------
+ * Row movers of the halo exchange (float32 rows of F elements, int64 ids that
+ * are unique within one call).  Replace the pack / unpack / reverse-halo
+ * segment-sum of the reference's device halo path
+ * (python/tiga/distributed/transport.py:1060-1133, 446-574).
+ * ------------------------------------------------------------------------ */
+/* packed[i, :] = rows[ids[i], :] */
+TGB_API int32_t tgb_rows_gather(const void *rows, const void *ids, void *packed,
+                                int64_t n, int64_t F, uint64_t stream);
+/* rows[ids[i], :] += packed[i, :]   (no atomics: ids are unique) */
+TGB_API int32_t tgb_rows_scatter_add(void *rows, const void *ids,
+                                     const void *packed, int64_t n, int64_t F,
+                                     uint64_t stream);
+
+/* ------------------------------------------------------------------------
  * Dense-relation attention (online-softmax reducer over an implicit dense or
  * lower-triangular relation), packed variable-length sequences, bf16, on the
  * tensor cores (tcgen05 + tensor memory, TMA loads).
@@ -315,6 +329,17 @@ TGB_API int32_t tgb_varlen_attn_bwd(const void *q, const void *k, const void *v,
 TGB_API int32_t tgb_linear_f32(const void *a, const void *b_t, void *out,
                                int64_t M, int32_t K, int32_t N,
                                void *error_flag, uint64_t stream);
+
+/* Weight gradient of the linear: dw[K, N] = a[M, K]^T @ dout[M, N], tensor
+ * cores (tcgen05, 3xTF32), deterministic split over the M rows: every
+ * persistent CTA accumulates its row tiles in tensor memory and writes one
+ * partial [K, N] matrix into `partial` (tgb_linear_dw_partials(M) matrices of
+ * K*N floats), a second kernel adds them in CTA order.  K = 128, N in {64,128}. */
+TGB_API int32_t tgb_linear_dw_f32(const void *a, const void *dout, void *dw,
+                                  void *partial, uint64_t partial_bytes,
+                                  int64_t M, int32_t K, int32_t N,
+                                  void *error_flag, uint64_t stream);
+TGB_API int32_t tgb_linear_dw_partials(int64_t M, int32_t *count);
 
 #ifdef __cplusplus
 }

@@ -329,3 +329,17 @@ def test_edge_map_addresses_weights_and_dw_in_a_larger_edge_list(oracle, F):
     untouched = torch.ones(total, dtype=torch.bool)
     untouched[positions] = False
     assert torch.all(got[untouched] == -7.0)
+
+
+@pytest.mark.parametrize("F", (5, 64, 128))
+def test_halo_row_movers(F):
+    gen = torch.Generator().manual_seed(F)
+    rows = torch.randn(500, F, generator=gen).cuda()
+    ids = torch.randperm(500, generator=gen)[:123].sort().values.cuda()
+    packed = ops.rows_gather(rows, ids)
+    assert torch.equal(packed, rows[ids])
+    update = torch.randn(123, F, generator=gen).cuda()
+    expect = rows.clone()
+    expect[ids] += update
+    ops.rows_scatter_add(rows, ids, update)
+    assert torch.equal(rows, expect)

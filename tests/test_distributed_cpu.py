@@ -36,6 +36,14 @@ class OracleBackend:
             return accumulate_into
         return out
 
+    @staticmethod
+    def pack_rows(rows, ids):
+        return rows.index_select(0, ids)
+
+    @staticmethod
+    def add_rows(rows, ids, packed):
+        rows.index_add_(0, ids, packed)
+
     def backward_dx(self, graph, dy, w):
         from oracle import oracle
 

@@ -58,7 +58,20 @@ def test_backward_matches_oracle(oracle):
     wt = w.t().contiguous().numpy()
     assert_gemm_close(da.cpu().numpy(), dy.numpy(), wt, oracle.linear(dy.numpy(), wt))
     ref_dw = oracle.linear(a.t().contiguous().numpy(), dy.numpy())
-    np.testing.assert_allclose(dw.cpu().numpy(), ref_dw, rtol=1e-4, atol=1e-3)
+    assert_gemm_close(dw.cpu().numpy(), a.t().contiguous().numpy(), dy.numpy(), ref_dw)
+
+
+@pytest.mark.parametrize("M", (1, 31, 32, 33, 4777, 200000))
+@pytest.mark.parametrize("N", (64, 128))
+def test_weight_gradient_kernel(oracle, M, N):
+    a = syn.normal((M, 128), seed=M)
+    dy = syn.normal((M, N), seed=M + 1)
+    dw = ops._linear_dw_raw(a.cuda(), dy.cuda())
+    again = ops._linear_dw_raw(a.cuda(), dy.cuda())
+    ops.check_async_errors()
+    assert torch.equal(dw, again)                      # deterministic split-K
+    ref = oracle.linear(a.t().contiguous().numpy(), dy.numpy())
+    assert_gemm_close(dw.cpu().numpy(), a.t().contiguous().numpy(), dy.numpy(), ref)
 
 
 def test_unsupported_shapes_raise():

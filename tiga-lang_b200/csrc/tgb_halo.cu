@@ -1,0 +1,71 @@
+// Row movers of the halo exchange.
+//   tgb_rows_gather       packed[i, :]  = rows[ids[i], :]     (pack the rows a peer asked for)
+//   tgb_rows_scatter_add  rows[ids[i], :] += packed[i, :]     (add the cotangents a peer sent back)
+// They replace the reference's pack / unpack / segment-sum steps of the device halo path
+// (python/tiga/distributed/transport.py:1060-1133 pack and per-run copies, :446-574
+// reverse_halo_device).  The ids of one call are unique (a peer asks for / returns each row
+// once), so the add is a plain read-modify-write: no atomics, deterministic.
+// HBM bound: F*4 bytes read + written (gather), read + read + written (scatter-add) per row.
+#include "tgb_common.cuh"
+
+namespace tgb {
+namespace {
+
+constexpr int kBlock = 256;
+
+template <bool ADD>
+__global__ void __launch_bounds__(kBlock)
+k_move_rows(float *__restrict__ rows, const int64_t *__restrict__ ids, float *__restrict__ packed, int64_t n,
+            int64_t F) {
+  // one warp per row, 128-bit accesses when the row allows it
+  const int lane = threadIdx.x & 31;
+  const int64_t i = ((int64_t)blockIdx.x * kBlock + threadIdx.x) >> 5;
+  if (i >= n) return;
+  float *row = rows + ids[i] * F;
+  float *pack = packed + i * F;
+  const bool vec = (F & 3) == 0 && ((((uintptr_t)rows | (uintptr_t)packed) & 15u) == 0);
+  if (vec) {
+    for (int64_t f = 4 * lane; f < F; f += 128) {
+      if (ADD) {
+        float4 a = *reinterpret_cast<float4 *>(row + f);
+        const float4 b = __ldcs(reinterpret_cast<const float4 *>(pack + f));
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        *reinterpret_cast<float4 *>(row + f) = a;
+      } else {
+        __stcs(reinterpret_cast<float4 *>(pack + f), *reinterpret_cast<const float4 *>(row + f));
+      }
+    }
+  } else {
+    for (int64_t f = lane; f < F; f += 32) {
+      if (ADD) row[f] += pack[f];
+      else pack[f] = row[f];
+    }
+  }
+}
+
+int32_t move_rows(bool add, void *rows, const void *ids, void *packed, int64_t n, int64_t F, uint64_t stream) {
+  if (n < 0 || F <= 0) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "invalid row count or width");
+  if (n == 0) return TGB_STATUS_OK;
+  if (!rows || !ids || !packed) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const unsigned blocks = (unsigned)ceil_div(n * 32, kBlock);
+  if (add)
+    k_move_rows<true><<<blocks, kBlock, 0, st>>>((float *)rows, (const int64_t *)ids, (float *)packed, n, F);
+  else
+    k_move_rows<false><<<blocks, kBlock, 0, st>>>((float *)rows, (const int64_t *)ids, (float *)packed, n, F);
+  TGB_LAUNCHED();
+  return TGB_STATUS_OK;
+}
+
+}  // namespace
+}  // namespace tgb
+
+extern "C" int32_t tgb_rows_gather(const void *rows, const void *ids, void *packed, int64_t n, int64_t F,
+                                   uint64_t stream) {
+  return tgb::move_rows(false, const_cast<void *>(rows), ids, packed, n, F, stream);
+}
+
+extern "C" int32_t tgb_rows_scatter_add(void *rows, const void *ids, const void *packed, int64_t n, int64_t F,
+                                        uint64_t stream) {
+  return tgb::move_rows(true, rows, ids, const_cast<void *>(packed), n, F, stream);
+}

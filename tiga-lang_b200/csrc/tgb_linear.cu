@@ -21,7 +21,7 @@ namespace tgb {
 
 int32_t make_tensor_map_2d(CUtensorMap *map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void *base,
                            uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
-                           uint32_t box_rows) {
+                           uint32_t box_rows, bool swizzle_base32) {
   static EncodeTiledFn encode = nullptr;
   if (!encode) {
     void *fn = nullptr;
@@ -41,7 +41,9 @@ int32_t make_tensor_map_2d(CUtensorMap *map, CUtensorMapDataType dtype, uint32_t
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t elem_strides[2] = {1, 1};
   CUresult rc = encode(map, dtype, 2, const_cast<void *>(base), dims, strides, box, elem_strides,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       swizzle_base32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) TGB_FAIL(TGB_STATUS_INTERNAL, "cuTensorMapEncodeTiled failed with code %d", (int)rc);
   return TGB_STATUS_OK;
@@ -208,6 +210,140 @@ k_linear_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (warp == 0) tmem_dealloc(tmem, N);
 }
 
+
+// ---------------------------------------------------------------------------
+// Weight gradient  dw[K, N] = a[M, K]^T @ dout[M, N]  (a reduction over the M rows).
+// Both operands are used MN-major exactly as TMA delivers them: a tile of 32
+// rows is, per block of 32 columns, a [32 rows x 128 bytes] box whose rows are
+// the reduction index (32-byte-base swizzle, the layout tf32 needs MN-major).  Persistent CTAs stride over the row tiles and keep one
+// [K x N] accumulator in tensor memory for all of them (3xTF32 split as above);
+// each CTA then writes its partial matrix and a second kernel adds the partials
+// in CTA order (deterministic split-K, no atomics).
+// ---------------------------------------------------------------------------
+constexpr int kDwRows = 32;                        // rows (reduction) per tile
+constexpr int kDwBoxBytes = kDwRows * 128;         // one [32 rows x 32 floats] box
+constexpr int kDwMaxBoxes = 8;                     // (K + N) / 32 <= 8
+
+struct DwSmem {
+  alignas(1024) uint8_t hi[2][kDwMaxBoxes][kDwBoxBytes];   // a blocks first, then dout blocks
+  alignas(1024) uint8_t lo[2][kDwMaxBoxes][kDwBoxBytes];
+  uint64_t full[2];
+  uint64_t mma_done[2];
+  uint64_t acc_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int N>
+__global__ void __launch_bounds__(128, 1)
+k_linear_dw_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_d,
+                   float *__restrict__ partial, int64_t M, int *error) {
+  constexpr int K = 128;                             // rows of dw = M dimension of the MMA
+  constexpr int kABoxes = K / 32, kDBoxes = N / 32, kBoxes = kABoxes + kDBoxes;
+  extern __shared__ uint8_t smem_raw[];
+  DwSmem &sm = *reinterpret_cast<DwSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    mbar_init(&sm.full[0], 1);
+    mbar_init(&sm.full[1], 1);
+    mbar_init(&sm.mma_done[0], 1);
+    mbar_init(&sm.mma_done[1], 1);
+    mbar_init(&sm.acc_done, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (warp == 0) tmem_alloc(&sm.tmem_base, N);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = sm.tmem_base;
+  volatile int *abort_flag = &sm.abort_flag;
+
+  const int64_t n_tiles = (M + kDwRows - 1) / kDwRows;
+  const int64_t my_tiles = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  auto load_tile = [&](int64_t t, int slot) {
+    const int32_t row0 = (int32_t)((blockIdx.x + t * gridDim.x) * kDwRows);
+    mbar_arrive_expect_tx(&sm.full[slot], kBoxes * kDwBoxBytes);
+#pragma unroll
+    for (int j = 0; j < kABoxes; ++j) tma_load_2d(sm.hi[slot][j], &map_a, 32 * j, row0, &sm.full[slot]);
+#pragma unroll
+    for (int j = 0; j < kDBoxes; ++j) tma_load_2d(sm.hi[slot][kABoxes + j], &map_d, 32 * j, row0, &sm.full[slot]);
+  };
+  if (tid == 0 && my_tiles > 0) load_tile(0, 0);
+
+  constexpr uint32_t idesc = instr_desc(kFmtTF32, kFmtTF32, K, N, 1, 1);    // both operands MN-major
+  for (int64_t t = 0; t < my_tiles; ++t) {
+    const int s = (int)(t & 1);
+    const uint32_t use = (uint32_t)(t >> 1);
+    if (tid == 0 && t + 1 < my_tiles) {
+      const int s1 = (int)((t + 1) & 1);
+      const uint32_t use1 = (uint32_t)((t + 1) >> 1);
+      if (use1 >= 1) mbar_wait(&sm.mma_done[s1], (use1 - 1) & 1, abort_flag, error, 51);
+      load_tile(t + 1, s1);
+    }
+    mbar_wait(&sm.full[s], use & 1, abort_flag, error, 52);
+    split_chunk(sm.hi[s][0], sm.lo[s][0], kBoxes * kDwBoxBytes, tid, 128);
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after_sync();
+      const uint32_t a_hi = smem_u32(sm.hi[s][0]), a_lo = smem_u32(sm.lo[s][0]);
+      const uint32_t d_hi = smem_u32(sm.hi[s][kABoxes]), d_lo = smem_u32(sm.lo[s][kABoxes]);
+#pragma unroll
+      for (int k = 0; k < kDwRows / 8; ++k) {          // 8 reduction rows = one 1024-byte swizzle atom per MMA
+        const uint32_t off = k * 1024;
+        const uint64_t ah = smem_desc_mn_major_sw128_base32(a_hi + off, kDwBoxBytes);
+        const uint64_t al = smem_desc_mn_major_sw128_base32(a_lo + off, kDwBoxBytes);
+        const uint64_t dh = smem_desc_mn_major_sw128_base32(d_hi + off, kDwBoxBytes);
+        const uint64_t dl = smem_desc_mn_major_sw128_base32(d_lo + off, kDwBoxBytes);
+        mma_tf32(tmem, al, dh, idesc, (t | k) != 0);
+        mma_tf32(tmem, ah, dl, idesc, 1);
+        mma_tf32(tmem, ah, dh, idesc, 1);
+      }
+      mma_commit(&sm.mma_done[s]);
+      if (t == my_tiles - 1) mma_commit(&sm.acc_done);
+    }
+  }
+  float *mine = partial + (int64_t)blockIdx.x * K * N;
+  if (my_tiles > 0) {
+    mbar_wait(&sm.acc_done, 0, abort_flag, error, 53);
+    tc_fence_after_sync();
+  }
+  const int row = warp * 32 + lane;                    // row of dw = column of a
+#pragma unroll 1
+  for (int c0 = 0; c0 < N; c0 += 32) {
+    uint32_t r[32];
+    if (my_tiles > 0) {
+      tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + c0, r);
+      tmem_ld_wait();
+    } else {
+#pragma unroll
+      for (int q = 0; q < 32; ++q) r[q] = 0u;
+    }
+    float4 *dst = reinterpret_cast<float4 *>(mine + (int64_t)row * N + c0);
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                           __uint_as_float(r[4 * q + 3]));
+  }
+  if (tid == 0 && my_tiles > 1) {
+    const int64_t prev = my_tiles - 2;
+    mbar_wait(&sm.mma_done[prev & 1], (uint32_t)((prev >> 1) & 1), abort_flag, error, 54);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, N);
+}
+
+__global__ void k_sum_dw_partials(const float *__restrict__ partial, int blocks, int elems, float *__restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= elems) return;
+  float acc = 0.0f;
+  for (int b = 0; b < blocks; ++b) acc += partial[(int64_t)b * elems + i];
+  out[i] = acc;
+}
+
 }  // namespace
 }  // namespace tgb
 
@@ -252,5 +388,68 @@ extern "C" int32_t tgb_linear_f32(const void *a, const void *b_t, void *out, int
     k_linear_3xtf32<64><<<grid, 128, smem, st>>>(map_a, map_b, (float *)out, M, K / 32, (int *)error_flag);
   }
   TGB_LAUNCHED();
+  return TGB_STATUS_OK;
+}
+
+extern "C" int32_t tgb_linear_dw_f32(const void *a, const void *dout, void *dw, void *partial,
+                                     uint64_t partial_bytes, int64_t M, int32_t K, int32_t N, void *error_flag,
+                                     uint64_t stream) {
+  if (M < 0) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "negative row count");
+  if (K != 128 || (N != 64 && N != 128))
+    TGB_FAIL(TGB_STATUS_UNSUPPORTED, "tensor-core weight gradient supports K = 128 and N in {64, 128} (got K=%d, N=%d)", K, N);
+  if (!a || !dout || !dw || !partial || !error_flag) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
+  if (M > (int64_t)INT32_MAX - 256) TGB_FAIL(TGB_STATUS_UNSUPPORTED, "more than 2^31 rows");
+  if (M == 0) {
+    TGB_CUDA(cudaMemsetAsync(dw, 0, (size_t)K * N * 4, reinterpret_cast<cudaStream_t>(stream)));
+    return TGB_STATUS_OK;
+  }
+  int device = 0, sms = 0;
+  TGB_CUDA(cudaGetDevice(&device));
+  TGB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  const int64_t tiles = ceil_div(M > 0 ? M : 1, kDwRows);
+  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  const uint64_t need = (uint64_t)grid * K * N * 4;
+  if (partial_bytes < need)
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "partial buffer too small: %llu < %llu bytes",
+             (unsigned long long)partial_bytes, (unsigned long long)need);
+  CUtensorMap map_a, map_d;
+  int32_t rc = make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)(M > 0 ? M : 1), (uint64_t)K,
+                                  (uint64_t)K * 4, 32, kDwRows, true);
+  if (rc) return rc;
+  rc = make_tensor_map_2d(&map_d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dout, (uint64_t)(M > 0 ? M : 1), (uint64_t)N,
+                          (uint64_t)N * 4, 32, kDwRows, true);
+  if (rc) return rc;
+  const size_t smem = sizeof(DwSmem) + 1024;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (N == 128) {
+    static bool configured = false;
+    if (!configured) {
+      TGB_CUDA(cudaFuncSetAttribute(k_linear_dw_3xtf32<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured = true;
+    }
+    k_linear_dw_3xtf32<128><<<grid, 128, smem, st>>>(map_a, map_d, (float *)partial, M, (int *)error_flag);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      TGB_CUDA(cudaFuncSetAttribute(k_linear_dw_3xtf32<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured = true;
+    }
+    k_linear_dw_3xtf32<64><<<grid, 128, smem, st>>>(map_a, map_d, (float *)partial, M, (int *)error_flag);
+  }
+  TGB_LAUNCHED();
+  k_sum_dw_partials<<<(unsigned)ceil_div((int64_t)K * N, 256), 256, 0, st>>>((const float *)partial, (int)grid, K * N,
+                                                                            (float *)dw);
+  TGB_LAUNCHED();
+  return TGB_STATUS_OK;
+}
+
+/* number of persistent CTAs (= partial matrices) tgb_linear_dw_f32 uses for M rows */
+extern "C" int32_t tgb_linear_dw_partials(int64_t M, int32_t *count) {
+  if (!count) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null output");
+  int device = 0, sms = 0;
+  TGB_CUDA(cudaGetDevice(&device));
+  TGB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  const int64_t tiles = ceil_div(M > 0 ? M : 1, kDwRows);
+  *count = (int32_t)(tiles < sms ? tiles : sms);
   return TGB_STATUS_OK;
 }

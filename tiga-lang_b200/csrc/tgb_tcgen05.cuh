@@ -134,6 +134,21 @@ __device__ __forceinline__ uint64_t smem_desc_mn_major_sw128(uint32_t smem_addr,
   return desc;
 }
 
+// MN-major operand of 32-bit elements (tf32): the only layout the tensor core
+// accepts is the 128-byte swizzle with a 32-byte base -- 128-byte rows (32
+// floats along MN, consecutive rows = consecutive K), 32-byte chunks permuted
+// inside groups of 4 rows (512 bytes).  It is what TMA writes with
+// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.
+__device__ __forceinline__ uint64_t smem_desc_mn_major_sw128_base32(uint32_t smem_addr, uint32_t mn_atom_stride) {
+  uint64_t desc = 0;
+  desc |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  desc |= (uint64_t)((mn_atom_stride >> 4) & 0x3FFFu) << 16;   // leading byte offset: next block of 32 floats
+  desc |= (uint64_t)(512 >> 4) << 32;                          // stride byte offset: next 4 rows of K
+  desc |= (uint64_t)1 << 46;
+  desc |= (uint64_t)1 << 61;                                   // SWIZZLE_128B_BASE32B
+  return desc;
+}
+
 enum : uint32_t { kFmtF16 = 0, kFmtBF16 = 1, kFmtTF32 = 2 };
 
 // Instruction descriptor of tcgen05.mma kind::f16 / kind::tf32 with float32
@@ -203,6 +218,6 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 // elem_bytes must be 128).  Returns a TGB status.
 int32_t make_tensor_map_2d(CUtensorMap *map, CUtensorMapDataType dtype, uint32_t elem_bytes, const void *base,
                            uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
-                           uint32_t box_rows);
+                           uint32_t box_rows, bool swizzle_base32 = false);
 
 }  // namespace tgb

@@ -114,6 +114,18 @@ class NativeBackend:
         return ops.csr_reduce_backward_dx(graph.native_plan(transpose=True), "sum", dy, w)
 
     @staticmethod
+    def pack_rows(rows, ids):
+        from .. import ops
+
+        return ops.rows_gather(rows, ids)
+
+    @staticmethod
+    def add_rows(rows, ids, packed):
+        from .. import ops
+
+        ops.rows_scatter_add(rows, ids, packed)
+
+    @staticmethod
     def backward_dw(graph, dy, x, out):
         from .. import ops
 
@@ -289,7 +301,7 @@ class _HaloWeightedSum(torch.autograd.Function):
         device = rows.device
         runtime.mark("forward:begin", device)
         ghost_x = torch.empty((int(shard.ghosts.numel()), F), dtype=rows.dtype, device=rows.device)
-        packed = [(p, rows.index_select(0, ids)) for p, ids in enumerate(shard.send_ids) if ids.numel()]
+        packed = [(p, backend.pack_rows(rows, ids)) for p, ids in enumerate(shard.send_ids) if ids.numel()]
         receives = [(p, ghost_x[o:o + c]) for p, (o, c) in enumerate(shard.recv_offsets) if c and p != shard.rank]
         works = transport.exchange(sends=packed, receives=receives)      # halo in flight ...
         runtime.mark("forward pack + start exchange", device)
@@ -345,7 +357,7 @@ class _HaloWeightedSum(torch.autograd.Function):
             transport.wait(works)
             runtime.mark("backward exposed cotangent wait", device)
             for _, ids, buffer in landed:            # fixed peer order: deterministic
-                dx.index_add_(0, ids, buffer)
+                backend.add_rows(dx, ids, buffer)
             dx = dx.reshape(ctx.x_shape)
             runtime.mark("backward add received cotangents", device)
         return dx, dw, None, None

@@ -172,9 +172,27 @@ def _linear_raw(a: torch.Tensor, b_t: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def _linear_dw_raw(a: torch.Tensor, d_out: torch.Tensor) -> torch.Tensor:
+    """a[M, K]^T @ d_out[M, N] on the tensor cores (3xTF32, deterministic split over the rows)."""
+    import ctypes
+
+    a, d_out = a.contiguous(), d_out.contiguous()
+    M, K = a.shape
+    N = d_out.shape[1]
+    lib = _native.lib()
+    count = ctypes.c_int32()
+    with torch.cuda.device(a.device):
+        _native.check(lib.tgb_linear_dw_partials(M, ctypes.byref(count)), "tgb_linear_dw_partials")
+        partial = torch.empty((count.value, K, N), dtype=torch.float32, device=a.device)
+        dw = torch.empty((K, N), dtype=torch.float32, device=a.device)
+        _native.check(lib.tgb_linear_dw_f32(a.data_ptr(), d_out.data_ptr(), dw.data_ptr(), partial.data_ptr(),
+                                            partial.numel() * 4, M, K, N, error_flag(a.device).data_ptr(),
+                                            _stream(a.device)), "tgb_linear_dw_f32")
+    return dw
+
+
 class DenseLinearFunction(torch.autograd.Function):
-    """out = a @ W with W [K, N]; forward and d(a) run on tcgen05, d(W) = a^T @ dout is a
-    plain library GEMM (reduction over the rows)."""
+    """out = a @ W with W [K, N]; forward, d(a) and (for K = 128) d(W) = a^T @ dout run on tcgen05."""
 
     @staticmethod
     def forward(ctx, a, weight):
@@ -192,7 +210,10 @@ class DenseLinearFunction(torch.autograd.Function):
             else:
                 da = grad_output @ weight.t()
         if ctx.needs_input_grad[1]:
-            dw = a.t() @ grad_output
+            if weight.shape[0] == 128 and weight.shape[1] in (64, 128):
+                dw = _linear_dw_raw(a, grad_output)
+            else:
+                dw = a.t() @ grad_output
         return da, dw
 
 
@@ -201,3 +222,21 @@ def dense_linear(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     if not linear_supported(a, weight):
         raise NotImplementedError("dense_linear takes float32 CUDA matrices with K in {32,64,96,128}, N in {64,128}")
     return DenseLinearFunction.apply(a, weight)
+
+
+# --------------------------------------------------------------------------- halo row movers
+def rows_gather(rows: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """packed[i] = rows[ids[i]] for float32 rows and int64 ids."""
+    packed = torch.empty((ids.numel(), rows.shape[1]), dtype=rows.dtype, device=rows.device)
+    with torch.cuda.device(rows.device):
+        _native.check(_native.lib().tgb_rows_gather(rows.data_ptr(), ids.data_ptr(), packed.data_ptr(), ids.numel(),
+                                                    rows.shape[1], _stream(rows.device)), "tgb_rows_gather")
+    return packed
+
+
+def rows_scatter_add(rows: torch.Tensor, ids: torch.Tensor, packed: torch.Tensor) -> None:
+    """rows[ids[i]] += packed[i] in place; the ids must be unique."""
+    with torch.cuda.device(rows.device):
+        _native.check(_native.lib().tgb_rows_scatter_add(rows.data_ptr(), ids.data_ptr(), packed.data_ptr(),
+                                                         ids.numel(), rows.shape[1], _stream(rows.device)),
+                      "tgb_rows_scatter_add")
