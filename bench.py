@@ -51,6 +51,8 @@ def parse_args():
     p.add_argument("--edge-factor", type=int, default=32)
     p.add_argument("--features", type=int, default=128)
     p.add_argument("--seed", type=int, default=20261125)
+    p.add_argument("--labels", default="natural", choices=("natural", "random"),
+                   help="multi-GPU workload: keep the generator's vertex ids or relabel them at random")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--cpu-sample-seconds", type=float, default=15.0)
@@ -271,6 +273,19 @@ def run_attention(args, device):
                      "forward_frac": round(fwd_flops / (fwd_ms * 1e-3) / 1e12 / peak, 4)}}), flush=True)
 
 
+def measured_dram_traffic(args, kernel):
+    """DRAM bytes (read + write) of one launch of `kernel` ("fwd", "dx" or
+    "dw"), taken from a one-pass ncu capture of dram__bytes_read.sum and
+    dram__bytes_write.sum on this exact workload (the table is in
+    profiles/csr_reduce_gcn_layer_ncu.md).  The
+    figure is a recorded measurement, not something this run can observe, so it
+    is reported only for the workload it was captured on."""
+    if getattr(args, "workload", "gcn") == "gcn" and args.scale == 20 and args.features == 128 \
+            and args.edge_factor == 32:
+        return {"fwd": 6.55e9, "dx": 10.36e9, "dw": 6.52e9}[kernel]
+    return None
+
+
 def run_native(args):
     import torch.distributed as dist
 
@@ -439,7 +454,8 @@ def run_native_multi(args, rank, world, device):
     torch.backends.cuda.matmul.allow_tf32 = False
     scale = args.scale + int(round(math.log2(world)))
     F = args.features
-    row_ptr, col = syn.rmat_csr(scale, args.edge_factor, seed=args.seed, symmetrize=True, device=device)
+    row_ptr, col = syn.rmat_csr(scale, args.edge_factor, seed=args.seed, symmetrize=True, device=device,
+                                relabel=args.labels == "random")
     N, E = row_ptr.numel() - 1, col.numel()
     graph = tg.Graph.from_csr(row_ptr, col, num_src=N).halo(
         tg.DeviceMesh("cuda", world), partition=tg.ByDestination(balance="cost"))
@@ -531,7 +547,8 @@ def run_native_multi(args, rank, world, device):
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"halo gcn-layer rmat scale={scale} (2^{args.scale} nodes per GPU) "
                                    f"edge_factor={args.edge_factor} symmetrized dedup F={F} fp32 sum+linear fwd+bwd",
-                       "num_nodes": N, "num_edges": E, "features": F, "partition": "contiguous ranges balancing edges + 32 per row",
+                       "num_nodes": N, "num_edges": E, "features": F, "vertex_labels": args.labels,
+                       "partition": "contiguous ranges balancing edges + 32 per row",
                        "per_rank_edges_rows_ghosts_ghostedges": per_rank,
                        "halo_bytes_per_step_rank0": int(shard.ghosts.numel()) * F * 4 * 2,
                        "phase_ms_per_rank": {name: [round(float(r[i]), 3) for r in all_phases]

@@ -57,7 +57,11 @@ class OracleBackend:
         from oracle import oracle
 
         row_ptr, col = self._csr(graph)
-        out[graph._edge_map.long()] = torch.from_numpy(oracle.wsum_bwd_dw(row_ptr, col, dy.numpy(), x.numpy()))
+        dw = torch.from_numpy(oracle.wsum_bwd_dw(row_ptr, col, dy.numpy(), x.numpy()))
+        if graph._edge_map is not None:
+            out[graph._edge_map.long()] = dw
+        else:
+            out.copy_(dw)
         return out
 
 
@@ -102,6 +106,16 @@ def _worker(rank, world, port, balance, result_dir):
             ws = w[lo:hi].clone().requires_grad_()
             out = WeightedSum()(graph=graph, src={"x": xs}, dst={}, edge={"weight": ws})
             dx, dw = torch.autograd.grad(out, (xs, ws), dy[b:e])
+            # only one gradient wanted: the backward runs per sub-relation instead of over the whole
+            # local relation; every rank takes part in both exchanges
+            xs1 = x[b:e].clone().requires_grad_()
+            out1 = WeightedSum()(graph=graph, src={"x": xs1}, dst={}, edge={"weight": w[lo:hi].clone()})
+            (dx_only,) = torch.autograd.grad(out1, (xs1,), dy[b:e])
+            ws1 = w[lo:hi].clone().requires_grad_()
+            out2 = WeightedSum()(graph=graph, src={"x": x[b:e].clone()}, dst={}, edge={"weight": ws1})
+            (dw_only,) = torch.autograd.grad(out2, (ws1,), dy[b:e])
+        np.testing.assert_allclose(dx_only.numpy(), dx.numpy(), rtol=1e-5, atol=2e-6)
+        np.testing.assert_allclose(dw_only.numpy(), dw.numpy(), rtol=1e-5, atol=2e-6)
         halo = shard.halo_map()
         if balance == "auto":
             peers = [model.derive_halo_map(row_ptr, col, num_entities=n, world_size=world, rank=r)

@@ -4,8 +4,8 @@ Everything is generated with integer torch ops from a counter-based hash, so
 the CPU and the GPU produce bit-identical graphs for the same seed.  The
 R-MAT generator follows the published recursive-quadrant definition
 (probabilities a, b, c, d for the (0,0), (0,1), (1,0), (1,1) quadrants of the
-(source, destination) bit pair at every level); no vertex relabelling, so hubs
-sit at low ids.  These graphs stand in for the Graph500-style cases the
+(source, destination) bit pair at every level); by default no vertex
+relabelling, so hubs sit at low ids (`relabel=True` permutes the ids).  These graphs stand in for the Graph500-style cases the
 reference only plans (benchmarks/large_graphs/suite.json of the reference);
 no external generator or data set is used.
 """
@@ -74,9 +74,28 @@ def csr_from_pairs(src: torch.Tensor, dst: torch.Tensor, num_nodes: int, *, symm
     return row_ptr, src
 
 
-def rmat_csr(scale: int, edge_factor: int, *, seed: int = 1, symmetrize: bool = True, device="cpu"):
+def random_relabelling(num_nodes: int, *, seed: int, device="cpu") -> torch.Tensor:
+    """A seeded random permutation of the vertex ids (new id of old id i is
+    perm[i]): the order of a 63-bit hash of the ids, ties broken by id."""
+    ids = torch.arange(num_nodes, dtype=torch.int64, device=device)
+    key = _mix(ids + ((seed * 2862933555777941757 + 3037000493) & _MASK63)) & _MASK63
+    order = torch.argsort(key, stable=True)
+    perm = torch.empty_like(order)
+    perm[order] = ids
+    return perm
+
+
+def rmat_csr(scale: int, edge_factor: int, *, seed: int = 1, symmetrize: bool = True, device="cpu",
+             relabel: bool = False):
+    """R-MAT graph as CSR by destination.  `relabel=True` applies the random
+    vertex relabelling that Graph500-style generators prescribe, which spreads
+    the hubs over the whole id range (contiguous id ranges then hold the same
+    mix of degrees); the default keeps the generator's natural ids."""
     n = 1 << scale
     src, dst = rmat_edges(scale, n * edge_factor, seed=seed, device=device)
+    if relabel:
+        perm = random_relabelling(n, seed=seed, device=device)
+        src, dst = perm[src], perm[dst]
     return csr_from_pairs(src, dst, n, symmetrize=symmetrize)
 
 
