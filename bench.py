@@ -51,8 +51,10 @@ def parse_args():
     p.add_argument("--edge-factor", type=int, default=32)
     p.add_argument("--features", type=int, default=128)
     p.add_argument("--seed", type=int, default=20261125)
-    p.add_argument("--labels", default="natural", choices=("natural", "random"),
-                   help="multi-GPU workload: keep the generator's vertex ids or relabel them at random")
+    p.add_argument("--labels", default="random", choices=("natural", "random"),
+                   help="multi-GPU workload: relabel the vertices at random as Graph500-style generators "
+                        "prescribe (default), or keep the generator's ids with the hubs at low ids; the "
+                        "single-GPU workload always keeps the generator's ids")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--cpu-sample-seconds", type=float, default=15.0)
