@@ -16,8 +16,9 @@
 //   one thread issues tcgen05.mma: S = Q K^T into tensor memory; the four warps
 //   read their 32 rows of S, keep the running max / denominator in registers,
 //   write P as bf16 into a swizzled shared-memory tile; a second MMA group
-//   computes P V into tensor memory (V is consumed MN-major as loaded) and the
-//   threads fold it into their float32 output row with the rescale factor.
+//   accumulates P V in tensor memory over all key blocks (V is consumed
+//   MN-major as loaded).  The accumulator is rescaled in place only when a
+//   row's maximum has grown by more than 2^8 since its reference was set.
 // Tensor-core bound: 4*D flops per (query, key) pair forward.
 #include <cuda_bf16.h>
 
@@ -70,10 +71,16 @@ struct FwdSmem {
   alignas(1024) uint8_t k[2][HALVES][kKeyBoxBytes];
   alignas(1024) uint8_t v[2][HALVES][kKeyBoxBytes];
   alignas(1024) uint8_t p[kBoxBytes];              // [128 queries x 64 keys] bf16
-  uint64_t q_full, kv_full[2], s_done, o_done;
+  uint64_t q_full, k_full[2], v_full[2], s_done, o_done;
   uint32_t tmem_base;
   int abort_flag;
 };
+
+// The output accumulates in tensor memory against a reference maximum that is
+// only moved (and the accumulator rescaled) when the running maximum has grown
+// by more than this many powers of two; p = 2^(s - reference) then stays below
+// 2^8 and the final O / l is the same quotient as with the exact maximum.
+constexpr float kRescaleGap = 8.0f;
 
 template <int HALVES>
 __global__ void __launch_bounds__(128, 2)
@@ -98,8 +105,10 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   if (tid == 0) {
     sm.abort_flag = 0;
     mbar_init(&sm.q_full, 1);
-    mbar_init(&sm.kv_full[0], 1);
-    mbar_init(&sm.kv_full[1], 1);
+    mbar_init(&sm.k_full[0], 1);
+    mbar_init(&sm.k_full[1], 1);
+    mbar_init(&sm.v_full[0], 1);
+    mbar_init(&sm.v_full[1], 1);
     mbar_init(&sm.s_done, 1);
     mbar_init(&sm.o_done, 1);
     mbar_fence_init();
@@ -116,35 +125,36 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
   volatile int *abort_flag = &sm.abort_flag;
 
-  auto load_kv = [&](int block, int stage) {
+  auto load_k = [&](int block, int stage) {
     const int y = tile.seq_begin + block * kKeyBlock;
-    mbar_arrive_expect_tx(&sm.kv_full[stage], 2 * HALVES * kKeyBoxBytes);
+    mbar_arrive_expect_tx(&sm.k_full[stage], HALVES * kKeyBoxBytes);
 #pragma unroll
-    for (int j = 0; j < HALVES; ++j) {
-      tma_load_2d(sm.k[stage][j], &map_k, head * D + 64 * j, y, &sm.kv_full[stage]);
-      tma_load_2d(sm.v[stage][j], &map_v, head * D + 64 * j, y, &sm.kv_full[stage]);
-    }
+    for (int j = 0; j < HALVES; ++j) tma_load_2d(sm.k[stage][j], &map_k, head * D + 64 * j, y, &sm.k_full[stage]);
+  };
+  auto load_v = [&](int block, int stage) {
+    const int y = tile.seq_begin + block * kKeyBlock;
+    mbar_arrive_expect_tx(&sm.v_full[stage], HALVES * kKeyBoxBytes);
+#pragma unroll
+    for (int j = 0; j < HALVES; ++j) tma_load_2d(sm.v[stage][j], &map_v, head * D + 64 * j, y, &sm.v_full[stage]);
   };
   if (tid == 0) {
     mbar_arrive_expect_tx(&sm.q_full, HALVES * kBoxBytes);
 #pragma unroll
     for (int j = 0; j < HALVES; ++j) tma_load_2d(sm.q[j], &map_q, head * D + 64 * j, tile.q_begin, &sm.q_full);
-    load_kv(0, 0);
+    load_k(0, 0);
+    load_v(0, 0);
   }
 
   constexpr uint32_t idesc_s = instr_desc(kFmtBF16, kFmtBF16, kTile, kKeyBlock, 0, 0);
   constexpr uint32_t idesc_o = instr_desc(kFmtBF16, kFmtBF16, kTile, D, 0, 1);   // V is MN-major
-  float m = -INFINITY, l = 0.0f;
-  float o[D];
-#pragma unroll
-  for (int d = 0; d < D; ++d) o[d] = 0.0f;
+  float m = -INFINITY, l = 0.0f;                    // reference maximum (log2 domain) and denominator
 
   mbar_wait(&sm.q_full, 0, abort_flag, error, 11);
   for (int kb = 0; kb < n_blocks; ++kb) {
     const int st = kb & 1;
     const int key0 = tile.seq_begin + kb * kKeyBlock;
-    if (tid == 0 && kb + 1 < n_blocks) load_kv(kb + 1, st ^ 1);   // its previous reader finished last iteration
-    mbar_wait(&sm.kv_full[st], (uint32_t)((kb >> 1) & 1), abort_flag, error, 12);
+    if (tid == 0 && kb + 1 < n_blocks) load_k(kb + 1, st ^ 1);    // S of block kb-1 was waited for last iteration
+    mbar_wait(&sm.k_full[st], (uint32_t)((kb >> 1) & 1), abort_flag, error, 12);
     if (tid == 0) {
       tc_fence_after_sync();
 #pragma unroll
@@ -160,7 +170,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     tc_fence_after_sync();
 
     const bool masked = (key0 + kKeyBlock > tile.seq_end) || (causal && key0 + kKeyBlock - 1 > tile.q_begin);
-    // pass A: row maximum
+    // pass A: row maximum (overlaps P V of the previous block)
     float block_max = -INFINITY;
 #pragma unroll 1
     for (int c0 = 0; c0 < kKeyBlock; c0 += 32) {
@@ -174,9 +184,34 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         if (valid) block_max = fmaxf(block_max, __uint_as_float(r[c]));
       }
     }
-    const float m_new = fmaxf(m, block_max * scale_log2);
-    const float alpha = m == -INFINITY ? 0.0f : fast_exp2(m - m_new);
-    const float m_use = m_new == -INFINITY ? 0.0f : m_new;     // a fully masked row keeps p = 0
+    const float m_blk = fmaxf(m, block_max * scale_log2);
+    float alpha = 1.0f;
+    if (m == -INFINITY) {
+      m = m_blk;                                     // nothing accumulated for this row yet
+    } else if (m_blk - m > kRescaleGap) {
+      alpha = fast_exp2(m - m_blk);
+      m = m_blk;
+    }
+    const float m_use = m == -INFINITY ? 0.0f : m;   // a fully masked row keeps p = 0
+    if (kb > 0) {
+      // P V of the previous block read the P tile, the other V stage and the accumulator
+      mbar_wait(&sm.o_done, (uint32_t)((kb - 1) & 1), abort_flag, error, 14);
+      tc_fence_after_sync();
+    }
+    if (tid == 0 && kb + 1 < n_blocks) load_v(kb + 1, st ^ 1);
+    if (__any_sync(0xffffffffu, alpha != 1.0f)) {    // rare: move the reference maximum of these 32 rows
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_o + lane_base + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+        tmem_st_32x32(tmem_o + lane_base + c0, r);
+      }
+      tmem_st_wait();
+      l *= alpha;
+    }
     // pass B: p = 2^(s - m), written as bf16 for the second MMA
     float block_sum = 0.0f;
 #pragma unroll 1
@@ -199,46 +234,52 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                              make_uint4(pack_bf16(p[8 * g], p[8 * g + 1]), pack_bf16(p[8 * g + 2], p[8 * g + 3]),
                                         pack_bf16(p[8 * g + 4], p[8 * g + 5]), pack_bf16(p[8 * g + 6], p[8 * g + 7])));
     }
-    l = l * alpha + block_sum;
-    m = m_new;
+    l += block_sum;
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     if (tid == 0) {
       tc_fence_after_sync();
+      mbar_wait(&sm.v_full[st], (uint32_t)((kb >> 1) & 1), abort_flag, error, 15);
 #pragma unroll
-      for (int k16 = 0; k16 < kKeyBlock / 16; ++k16) {   // 16 keys per MMA
+      for (int k16 = 0; k16 < kKeyBlock / 16; ++k16) {   // 16 keys per MMA, accumulated over all blocks
         const uint64_t a_desc = smem_desc_k_major_sw128(smem_u32(sm.p) + k16 * 32);
         const uint64_t b_desc = smem_desc_mn_major_sw128(smem_u32(sm.v[st][0]) + k16 * 16 * 128, kKeyBoxBytes);
-        mma_f16(tmem_o, a_desc, b_desc, idesc_o, k16 != 0);
+        mma_f16(tmem_o, a_desc, b_desc, idesc_o, (kb | k16) != 0);
       }
       mma_commit(&sm.o_done);
     }
-#pragma unroll
-    for (int d = 0; d < D; ++d) o[d] *= alpha;       // overlaps the MMA
-    mbar_wait(&sm.o_done, (uint32_t)(kb & 1), abort_flag, error, 14);
+  }
+  if (n_blocks > 0) {
+    mbar_wait(&sm.o_done, (uint32_t)((n_blocks - 1) & 1), abort_flag, error, 16);
     tc_fence_after_sync();
-#pragma unroll
-    for (int c0 = 0; c0 < D; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld_32x32(tmem_o + lane_base + c0, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int c = 0; c < 32; ++c) o[c0 + c] += __uint_as_float(r[c]);
-    }
-    tc_fence_before_sync();
   }
 
-  if (q_index < tile.seq_end && !*abort_flag) {
-    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    __nv_bfloat16 *dst = out + ((int64_t)q_index * H + head) * D;
+  const bool writes = q_index < tile.seq_end && !*abort_flag;
+  const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+  __nv_bfloat16 *dst = out + ((int64_t)q_index * H + head) * D;
+#pragma unroll 1
+  for (int c0 = 0; c0 < D; c0 += 32) {
+    uint32_t r[32];
+    if (n_blocks > 0) {
+      tmem_ld_32x32(tmem_o + lane_base + c0, r);
+      tmem_ld_wait();
+    } else {
 #pragma unroll
-    for (int d = 0; d < D; d += 8)
-      *reinterpret_cast<uint4 *>(dst + d) =
-          make_uint4(pack_bf16(o[d] * inv, o[d + 1] * inv), pack_bf16(o[d + 2] * inv, o[d + 3] * inv),
-                     pack_bf16(o[d + 4] * inv, o[d + 5] * inv), pack_bf16(o[d + 6] * inv, o[d + 7] * inv));
-    lse[(int64_t)q_index * H + head] = l > 0.0f ? (m + log2f(l)) * kLn2 : -INFINITY;
+      for (int c = 0; c < 32; ++c) r[c] = 0u;
+    }
+    if (writes) {
+#pragma unroll
+      for (int d = 0; d < 32; d += 8)
+        *reinterpret_cast<uint4 *>(dst + c0 + d) = make_uint4(
+            pack_bf16(__uint_as_float(r[d]) * inv, __uint_as_float(r[d + 1]) * inv),
+            pack_bf16(__uint_as_float(r[d + 2]) * inv, __uint_as_float(r[d + 3]) * inv),
+            pack_bf16(__uint_as_float(r[d + 4]) * inv, __uint_as_float(r[d + 5]) * inv),
+            pack_bf16(__uint_as_float(r[d + 6]) * inv, __uint_as_float(r[d + 7]) * inv));
+    }
   }
+  if (writes) lse[(int64_t)q_index * H + head] = l > 0.0f ? (m + log2f(l)) * kLn2 : -INFINITY;
+  tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(sm.tmem_base, 256);
 }
