@@ -212,10 +212,213 @@ k_linear_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
 
 // ---------------------------------------------------------------------------
+// N = 128: the same product with the operand roles swapped, out^T = b_t a^T.
+// The resident matrix b_t (hi and lo parts, 2 x 128 columns) lives in tensor
+// memory as the A operand of the MMA, so shared memory holds nothing but the
+// streamed rows of `a`: a ring of six TMA slots (96 KB in flight per SM) and
+// two hi/lo operand slots.  The accumulator is the transposed tile (lane =
+// output feature, column = row of the tile), which makes the epilogue's
+// stores full 128-byte lines: 32 lanes write 32 consecutive features of a row.
+// Tensor memory: b_t hi [0,128), lo [128,256), two accumulators [256,512).
+// ---------------------------------------------------------------------------
+constexpr int kWtRing = 6;
+constexpr int kWtThreads = 288;   // warps 0-3: split; warps 4-7: epilogue; warp 8: TMA + MMA issue
+
+struct LinearWtSmem {
+  alignas(1024) uint8_t raw[kWtRing][kChunkBytes];   // TMA destination ring
+  alignas(1024) uint8_t a_hi[2][kChunkBytes];
+  alignas(1024) uint8_t a_lo[2][kChunkBytes];
+  uint64_t raw_full[kWtRing];   // TMA chunk landed in raw[r]
+  uint64_t op_full[2];          // operand slot s holds the split chunk (and its TMA slot has been read)
+  uint64_t mma_done[2];         // MMAs that read operand slot s have finished
+  uint64_t acc_full[2];         // accumulator b of a tile is complete
+  uint64_t acc_empty[2];        // the epilogue warps have read accumulator b
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// Same split from a separate source buffer (the TMA ring) into an operand slot.
+__device__ __forceinline__ void split_chunk_from(const uint8_t *raw, uint8_t *hi_out, uint8_t *lo_out, int bytes,
+                                                 int tid, int threads) {
+  const float4 *src = reinterpret_cast<const float4 *>(raw);
+  float4 *hi = reinterpret_cast<float4 *>(hi_out);
+  float4 *lo = reinterpret_cast<float4 *>(lo_out);
+#pragma unroll 4
+  for (int i = tid; i < bytes / 16; i += threads) {
+    float4 v = src[i], h, l;
+    split_tf32(v.x, h.x, l.x);
+    split_tf32(v.y, h.y, l.y);
+    split_tf32(v.z, h.z, l.z);
+    split_tf32(v.w, h.w, l.w);
+    hi[i] = h;
+    lo[i] = l;
+  }
+}
+
+// Bounded wait used only while tearing down: it ignores the abort flag (copies
+// or MMAs still in flight must land before shared and tensor memory go away)
+// and records nothing.
+__device__ __forceinline__ void mbar_wait_teardown(uint64_t *bar, uint32_t parity) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+    if (mbar_try_wait(bar, parity)) return;
+}
+
+__global__ void __launch_bounds__(kWtThreads, 1)
+k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__restrict__ b_t,
+                   float *__restrict__ out, int64_t M, int k_chunks, int *error) {
+  constexpr int N = 128;
+  extern __shared__ uint8_t smem_raw[];
+  LinearWtSmem &sm =
+      *reinterpret_cast<LinearWtSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    for (int i = 0; i < kWtRing; ++i) mbar_init(&sm.raw_full[i], 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.op_full[i], 128);
+      mbar_init(&sm.mma_done[i], 1);
+      mbar_init(&sm.acc_full[i], 1);
+      mbar_init(&sm.acc_empty[i], 128);
+    }
+    mbar_fence_init();
+    tma_prefetch_descriptor(&map_a);
+  }
+  __syncthreads();
+  if (warp == 0) tmem_alloc(&sm.tmem_base, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t w_hi = tmem, w_lo = tmem + 128, acc0 = tmem + 256;
+  volatile int *abort_flag = &sm.abort_flag;
+
+  const int64_t n_tiles = (M + kTileM - 1) / kTileM;
+  const int64_t my_tiles = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int64_t total_chunks = my_tiles * k_chunks;
+  auto load_chunk = [&](int64_t chunk) {             // thread 0 only
+    const int r = (int)(chunk % kWtRing);
+    const int kc = (int)(chunk % k_chunks);
+    const int64_t row = (blockIdx.x + (chunk / k_chunks) * gridDim.x) * kTileM;
+    mbar_arrive_expect_tx(&sm.raw_full[r], kChunkBytes);
+    tma_load_2d(sm.raw[r], &map_a, kc * kChunkK, (int32_t)row, &sm.raw_full[r]);
+  };
+  if (tid == 0)
+    for (int64_t c = 0; c < kWtRing && c < total_chunks; ++c) load_chunk(c);
+
+  if (warp < 4) {
+    // b_t row `tid` (an output feature) -> hi/lo -> this thread's lane of tensor memory
+    const int K = k_chunks * kChunkK;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+#pragma unroll 1
+    for (int kc = 0; kc < k_chunks; ++kc) {
+      uint32_t hi[32], lo[32];
+      const float4 *src = reinterpret_cast<const float4 *>(b_t + (int64_t)tid * K + kc * kChunkK);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float4 v = __ldg(src + q);
+        float h, l;
+        split_tf32(v.x, h, l); hi[4 * q] = __float_as_uint(h); lo[4 * q] = __float_as_uint(l);
+        split_tf32(v.y, h, l); hi[4 * q + 1] = __float_as_uint(h); lo[4 * q + 1] = __float_as_uint(l);
+        split_tf32(v.z, h, l); hi[4 * q + 2] = __float_as_uint(h); lo[4 * q + 2] = __float_as_uint(l);
+        split_tf32(v.w, h, l); hi[4 * q + 3] = __float_as_uint(h); lo[4 * q + 3] = __float_as_uint(l);
+      }
+      tmem_st_32x32(w_hi + lane_base + kc * kChunkK, hi);
+      tmem_st_32x32(w_lo + lane_base + kc * kChunkK, lo);
+    }
+    tmem_st_wait();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  if (warp < 4) {
+    // ---- split warps: raw chunk -> hi/lo operand slot --------------------------------------------
+    for (int64_t it = 0; it < total_chunks; ++it) {
+      const int r = (int)(it % kWtRing);
+      const uint32_t use_r = (uint32_t)(it / kWtRing);
+      const int s = (int)(it & 1);
+      const uint32_t use_s = (uint32_t)(it >> 1);
+      mbar_wait(&sm.raw_full[r], use_r & 1, abort_flag, error, 3);
+      if (use_s >= 1) mbar_wait(&sm.mma_done[s], (use_s - 1) & 1, abort_flag, error, 2);   // operand slot free
+      split_chunk_from(sm.raw[r], sm.a_hi[s], sm.a_lo[s], kChunkBytes, tid, 128);
+      fence_proxy_async_smem();
+      mbar_arrive(&sm.op_full[s]);                    // 128 arrivals: operands written, raw[r] read
+    }
+  } else if (warp == 8) {
+    // ---- issue warp: one thread refills the TMA ring and issues the MMAs; issuing can stall on the
+    // tensor pipe, so this thread does nothing else -------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(kFmtTF32, kFmtTF32, N, kTileM, 0, 0);   // M = features, N = rows of the tile
+      int64_t it = 0;
+      for (int64_t t = 0; t < my_tiles; ++t) {
+        const uint32_t acc = acc0 + (uint32_t)(t & 1) * kTileM;
+        for (int kc = 0; kc < k_chunks; ++kc, ++it) {
+          const int s = (int)(it & 1);
+          mbar_wait(&sm.op_full[s], (uint32_t)((it >> 1) & 1), abort_flag, error, 8);
+          if (it + kWtRing < total_chunks) load_chunk(it + kWtRing);   // its slot raw[it % ring] has been read
+          if (kc == 0 && t >= 2)                              // the epilogue of tile t-2 has drained this accumulator
+            mbar_wait(&sm.acc_empty[t & 1], (uint32_t)(((t >> 1) - 1) & 1), abort_flag, error, 7);
+          tc_fence_after_sync();
+          const uint32_t a_hi = smem_u32(sm.a_hi[s]), a_lo = smem_u32(sm.a_lo[s]);
+#pragma unroll
+          for (int k = 0; k < kChunkK / 8; ++k) {       // K = 8 per MMA: 8 columns of b_t, 32 bytes of the row of a
+            const uint32_t col = (uint32_t)(kc * kChunkK + k * 8);
+            const uint64_t ah = smem_desc_k_major_sw128(a_hi + k * 32), al = smem_desc_k_major_sw128(a_lo + k * 32);
+            mma_tf32_a_tmem(acc, w_lo + col, ah, idesc, (kc | k) != 0);   // small terms first
+            mma_tf32_a_tmem(acc, w_hi + col, al, idesc, 1);
+            mma_tf32_a_tmem(acc, w_hi + col, ah, idesc, 1);
+          }
+          mma_commit(&sm.mma_done[s]);
+          if (kc == k_chunks - 1) mma_commit(&sm.acc_full[t & 1]);
+        }
+      }
+      // no TMA or MMA may be in flight when shared and tensor memory go away
+      if (total_chunks > 0) {
+        const int64_t last = total_chunks - 1;
+        mbar_wait_teardown(&sm.mma_done[last & 1], (uint32_t)((last >> 1) & 1));
+        if (total_chunks > 1) mbar_wait_teardown(&sm.mma_done[(last - 1) & 1], (uint32_t)(((last - 1) >> 1) & 1));
+        // after an abort some chunk may still be on its way into the ring: give it a bounded 2 ms to land
+        if (*abort_flag)
+          for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+      }
+    }
+  } else {
+    // ---- epilogue warps (4-7): lane = output feature, column = row of the tile ------------------------
+    const int ew = warp - 4;
+    const int n = ew * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(ew * 32) << 16;
+    for (int64_t t = 0; t < my_tiles; ++t) {
+      const int b = (int)(t & 1);
+      mbar_wait(&sm.acc_full[b], (uint32_t)((t >> 1) & 1), abort_flag, error, 4);
+      tc_fence_after_sync();
+      const int64_t row0 = (blockIdx.x + t * gridDim.x) * kTileM;
+      const bool live = !*abort_flag;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kTileM; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(acc0 + (uint32_t)(b * kTileM) + lane_base + c0, r);
+        tmem_ld_wait();
+        float *dst = out + (row0 + c0) * N + n;
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          if (live && row0 + c0 + c < M) __stcs(dst + (int64_t)c * N, __uint_as_float(r[c]));
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&sm.acc_empty[b]);                    // 128 arrivals complete the phase
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------
 // Weight gradient  dw[K, N] = a[M, K]^T @ dout[M, N]  (a reduction over the M rows).
 // Both operands are used MN-major exactly as TMA delivers them: a tile of 32
 // rows is, per block of 32 columns, a [32 rows x 128 bytes] box whose rows are
-// the reduction index (32-byte-base swizzle, the layout tf32 needs MN-major).  Persistent CTAs stride over the row tiles and keep one
+// the reduction index (32-byte-base swizzle, the layout tf32 needs MN-major).
+// Two TMA slots stay in flight while the tile before them is split into one of
+// two hi/lo operand slots.  Persistent CTAs stride over the row tiles and keep one
 // [K x N] accumulator in tensor memory for all of them (3xTF32 split as above);
 // each CTA then writes its partial matrix and a second kernel adds the partials
 // in CTA order (deterministic split-K, no atomics).
@@ -227,6 +430,7 @@ constexpr int kDwMaxBoxes = 8;                     // (K + N) / 32 <= 8
 struct DwSmem {
   alignas(1024) uint8_t hi[2][kDwMaxBoxes][kDwBoxBytes];   // a blocks first, then dout blocks
   alignas(1024) uint8_t lo[2][kDwMaxBoxes][kDwBoxBytes];
+  alignas(1024) uint8_t raw[2][kDwMaxBoxes][kDwBoxBytes];  // TMA destination ring
   uint64_t full[2];
   uint64_t mma_done[2];
   uint64_t acc_done;
@@ -266,27 +470,24 @@ k_linear_dw_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const int32_t row0 = (int32_t)((blockIdx.x + t * gridDim.x) * kDwRows);
     mbar_arrive_expect_tx(&sm.full[slot], kBoxes * kDwBoxBytes);
 #pragma unroll
-    for (int j = 0; j < kABoxes; ++j) tma_load_2d(sm.hi[slot][j], &map_a, 32 * j, row0, &sm.full[slot]);
+    for (int j = 0; j < kABoxes; ++j) tma_load_2d(sm.raw[slot][j], &map_a, 32 * j, row0, &sm.full[slot]);
 #pragma unroll
-    for (int j = 0; j < kDBoxes; ++j) tma_load_2d(sm.hi[slot][kABoxes + j], &map_d, 32 * j, row0, &sm.full[slot]);
+    for (int j = 0; j < kDBoxes; ++j) tma_load_2d(sm.raw[slot][kABoxes + j], &map_d, 32 * j, row0, &sm.full[slot]);
   };
   if (tid == 0 && my_tiles > 0) load_tile(0, 0);
+  if (tid == 0 && my_tiles > 1) load_tile(1, 1);
 
   constexpr uint32_t idesc = instr_desc(kFmtTF32, kFmtTF32, K, N, 1, 1);    // both operands MN-major
   for (int64_t t = 0; t < my_tiles; ++t) {
     const int s = (int)(t & 1);
     const uint32_t use = (uint32_t)(t >> 1);
-    if (tid == 0 && t + 1 < my_tiles) {
-      const int s1 = (int)((t + 1) & 1);
-      const uint32_t use1 = (uint32_t)((t + 1) >> 1);
-      if (use1 >= 1) mbar_wait(&sm.mma_done[s1], (use1 - 1) & 1, abort_flag, error, 51);
-      load_tile(t + 1, s1);
-    }
     mbar_wait(&sm.full[s], use & 1, abort_flag, error, 52);
-    split_chunk(sm.hi[s][0], sm.lo[s][0], kBoxes * kDwBoxBytes, tid, 128);
+    if (use >= 1) mbar_wait(&sm.mma_done[s], (use - 1) & 1, abort_flag, error, 51);   // operand slot free
+    split_chunk_from(sm.raw[s][0], sm.hi[s][0], sm.lo[s][0], kBoxes * kDwBoxBytes, tid, 128);
     fence_proxy_async_smem();
     __syncthreads();
     if (tid == 0) {
+      if (t + 2 < my_tiles) load_tile(t + 2, s);      // every thread has read raw[s]
       tc_fence_after_sync();
       const uint32_t a_hi = smem_u32(sm.hi[s][0]), a_lo = smem_u32(sm.lo[s][0]);
       const uint32_t d_hi = smem_u32(sm.hi[s][kABoxes]), d_lo = smem_u32(sm.lo[s][kABoxes]);
@@ -372,7 +573,17 @@ extern "C" int32_t tgb_linear_f32(const void *a, const void *b_t, void *out, int
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
   const size_t smem = sizeof(LinearSmem) + 1024;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (N == 128) {
+  if (N == 128 && ((uintptr_t)b_t & 15u) == 0) {
+    // resident matrix in tensor memory, rows of `a` through a six-slot TMA ring
+    const size_t smem_wt = sizeof(LinearWtSmem) + 1024;
+    static bool configured = false;
+    if (!configured) {
+      TGB_CUDA(cudaFuncSetAttribute(k_linear_wt_3xtf32, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_wt));
+      configured = true;
+    }
+    k_linear_wt_3xtf32<<<grid, kWtThreads, smem_wt, st>>>(map_a, (const float *)b_t, (float *)out, M, K / 32,
+                                                         (int *)error_flag);
+  } else if (N == 128) {
     static bool configured = false;
     if (!configured) {
       TGB_CUDA(cudaFuncSetAttribute(k_linear_3xtf32<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
