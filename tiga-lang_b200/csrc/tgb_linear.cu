@@ -216,21 +216,25 @@ k_linear_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 // The resident matrix b_t (hi and lo parts, 2 x 128 columns) lives in tensor
 // memory as the A operand of the MMA, so shared memory holds nothing but the
 // streamed rows of `a`: a ring of six TMA slots (96 KB in flight per SM) and
-// two hi/lo operand slots.  The accumulator is the transposed tile (lane =
+// three hi/lo operand slots.  One thread of a warp of its own refills the ring
+// and issues the MMAs: issuing stalls while the tensor pipe is busy, and a
+// thread that also splits would hold the other split threads at their barrier
+// (measured: 365 us with a shared thread, 253 us with the dedicated one).  The accumulator is the transposed tile (lane =
 // output feature, column = row of the tile), which makes the epilogue's
 // stores full 128-byte lines: 32 lanes write 32 consecutive features of a row.
 // Tensor memory: b_t hi [0,128), lo [128,256), two accumulators [256,512).
 // ---------------------------------------------------------------------------
 constexpr int kWtRing = 6;
+constexpr int kWtOps = 3;         // hi/lo operand slots
 constexpr int kWtThreads = 288;   // warps 0-3: split; warps 4-7: epilogue; warp 8: TMA + MMA issue
 
 struct LinearWtSmem {
   alignas(1024) uint8_t raw[kWtRing][kChunkBytes];   // TMA destination ring
-  alignas(1024) uint8_t a_hi[2][kChunkBytes];
-  alignas(1024) uint8_t a_lo[2][kChunkBytes];
+  alignas(1024) uint8_t a_hi[kWtOps][kChunkBytes];
+  alignas(1024) uint8_t a_lo[kWtOps][kChunkBytes];
   uint64_t raw_full[kWtRing];   // TMA chunk landed in raw[r]
-  uint64_t op_full[2];          // operand slot s holds the split chunk (and its TMA slot has been read)
-  uint64_t mma_done[2];         // MMAs that read operand slot s have finished
+  uint64_t op_full[kWtOps];     // operand slot s holds the split chunk (and its TMA slot has been read)
+  uint64_t mma_done[kWtOps];    // MMAs that read operand slot s have finished
   uint64_t acc_full[2];         // accumulator b of a tile is complete
   uint64_t acc_empty[2];        // the epilogue warps have read accumulator b
   uint32_t tmem_base;
@@ -274,9 +278,11 @@ k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__res
   if (tid == 0) {
     sm.abort_flag = 0;
     for (int i = 0; i < kWtRing; ++i) mbar_init(&sm.raw_full[i], 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kWtOps; ++i) {
       mbar_init(&sm.op_full[i], 128);
       mbar_init(&sm.mma_done[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&sm.acc_full[i], 1);
       mbar_init(&sm.acc_empty[i], 128);
     }
@@ -336,8 +342,8 @@ k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__res
     for (int64_t it = 0; it < total_chunks; ++it) {
       const int r = (int)(it % kWtRing);
       const uint32_t use_r = (uint32_t)(it / kWtRing);
-      const int s = (int)(it & 1);
-      const uint32_t use_s = (uint32_t)(it >> 1);
+      const int s = (int)(it % kWtOps);
+      const uint32_t use_s = (uint32_t)(it / kWtOps);
       mbar_wait(&sm.raw_full[r], use_r & 1, abort_flag, error, 3);
       if (use_s >= 1) mbar_wait(&sm.mma_done[s], (use_s - 1) & 1, abort_flag, error, 2);   // operand slot free
       split_chunk_from(sm.raw[r], sm.a_hi[s], sm.a_lo[s], kChunkBytes, tid, 128);
@@ -353,8 +359,8 @@ k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__res
       for (int64_t t = 0; t < my_tiles; ++t) {
         const uint32_t acc = acc0 + (uint32_t)(t & 1) * kTileM;
         for (int kc = 0; kc < k_chunks; ++kc, ++it) {
-          const int s = (int)(it & 1);
-          mbar_wait(&sm.op_full[s], (uint32_t)((it >> 1) & 1), abort_flag, error, 8);
+          const int s = (int)(it % kWtOps);
+          mbar_wait(&sm.op_full[s], (uint32_t)((it / kWtOps) & 1), abort_flag, error, 8);
           if (it + kWtRing < total_chunks) load_chunk(it + kWtRing);   // its slot raw[it % ring] has been read
           if (kc == 0 && t >= 2)                              // the epilogue of tile t-2 has drained this accumulator
             mbar_wait(&sm.acc_empty[t & 1], (uint32_t)(((t >> 1) - 1) & 1), abort_flag, error, 7);
@@ -374,9 +380,8 @@ k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__res
       }
       // no TMA or MMA may be in flight when shared and tensor memory go away
       if (total_chunks > 0) {
-        const int64_t last = total_chunks - 1;
-        mbar_wait_teardown(&sm.mma_done[last & 1], (uint32_t)((last >> 1) & 1));
-        if (total_chunks > 1) mbar_wait_teardown(&sm.mma_done[(last - 1) & 1], (uint32_t)(((last - 1) >> 1) & 1));
+        for (int64_t c = total_chunks - 1; c >= 0 && c > total_chunks - 1 - kWtOps; --c)
+          mbar_wait_teardown(&sm.mma_done[c % kWtOps], (uint32_t)((c / kWtOps) & 1));
         // after an abort some chunk may still be on its way into the ring: give it a bounded 2 ms to land
         if (*abort_flag)
           for (int i = 0; i < 2000; ++i) __nanosleep(1000);
@@ -431,6 +436,7 @@ struct DwSmem {
   alignas(1024) uint8_t hi[2][kDwMaxBoxes][kDwBoxBytes];   // a blocks first, then dout blocks
   alignas(1024) uint8_t lo[2][kDwMaxBoxes][kDwBoxBytes];
   alignas(1024) uint8_t raw[2][kDwMaxBoxes][kDwBoxBytes];  // TMA destination ring
+  uint64_t op_full[2];
   uint64_t full[2];
   uint64_t mma_done[2];
   uint64_t acc_done;
@@ -438,8 +444,11 @@ struct DwSmem {
   int abort_flag;
 };
 
+constexpr int kDwSplitWarps = 8;
+constexpr int kDwThreads = (kDwSplitWarps + 1) * 32;   // warps 0-7 split, warp 8 issues TMA and MMAs
+
 template <int N>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(kDwThreads, 1)
 k_linear_dw_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_d,
                    float *__restrict__ partial, int64_t M, int *error) {
   constexpr int K = 128;                             // rows of dw = M dimension of the MMA
@@ -449,12 +458,15 @@ k_linear_dw_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     sm.abort_flag = 0;
-    mbar_init(&sm.full[0], 1);
-    mbar_init(&sm.full[1], 1);
-    mbar_init(&sm.mma_done[0], 1);
-    mbar_init(&sm.mma_done[1], 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.full[i], 1);
+      mbar_init(&sm.op_full[i], kDwSplitWarps * 32);
+      mbar_init(&sm.mma_done[i], 1);
+    }
     mbar_init(&sm.acc_done, 1);
     mbar_fence_init();
+    tma_prefetch_descriptor(&map_a);
+    tma_prefetch_descriptor(&map_d);
   }
   __syncthreads();
   if (warp == 0) tmem_alloc(&sm.tmem_base, N);
@@ -474,20 +486,27 @@ k_linear_dw_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll
     for (int j = 0; j < kDBoxes; ++j) tma_load_2d(sm.raw[slot][kABoxes + j], &map_d, 32 * j, row0, &sm.full[slot]);
   };
-  if (tid == 0 && my_tiles > 0) load_tile(0, 0);
-  if (tid == 0 && my_tiles > 1) load_tile(1, 1);
 
-  constexpr uint32_t idesc = instr_desc(kFmtTF32, kFmtTF32, K, N, 1, 1);    // both operands MN-major
-  for (int64_t t = 0; t < my_tiles; ++t) {
-    const int s = (int)(t & 1);
-    const uint32_t use = (uint32_t)(t >> 1);
-    mbar_wait(&sm.full[s], use & 1, abort_flag, error, 52);
-    if (use >= 1) mbar_wait(&sm.mma_done[s], (use - 1) & 1, abort_flag, error, 51);   // operand slot free
-    split_chunk_from(sm.raw[s][0], sm.hi[s][0], sm.lo[s][0], kBoxes * kDwBoxBytes, tid, 128);
-    fence_proxy_async_smem();
-    __syncthreads();
-    if (tid == 0) {
-      if (t + 2 < my_tiles) load_tile(t + 2, s);      // every thread has read raw[s]
+  if (warp < kDwSplitWarps) {
+    // ---- split warps: raw tile -> hi/lo operand slot ------------------------------------------
+    for (int64_t t = 0; t < my_tiles; ++t) {
+      const int s = (int)(t & 1);
+      const uint32_t use = (uint32_t)(t >> 1);
+      mbar_wait(&sm.full[s], use & 1, abort_flag, error, 52);
+      if (use >= 1) mbar_wait(&sm.mma_done[s], (use - 1) & 1, abort_flag, error, 51);   // operand slot free
+      split_chunk_from(sm.raw[s][0], sm.hi[s][0], sm.lo[s][0], kBoxes * kDwBoxBytes, tid, kDwSplitWarps * 32);
+      fence_proxy_async_smem();
+      mbar_arrive(&sm.op_full[s]);                    // operands written, raw[s] read
+    }
+  } else if (lane == 0) {
+    // ---- issue thread: refills the TMA slots and issues the MMAs, nothing else ----------------
+    constexpr uint32_t idesc = instr_desc(kFmtTF32, kFmtTF32, K, N, 1, 1);    // both operands MN-major
+    if (my_tiles > 0) load_tile(0, 0);
+    if (my_tiles > 1) load_tile(1, 1);
+    for (int64_t t = 0; t < my_tiles; ++t) {
+      const int s = (int)(t & 1);
+      mbar_wait(&sm.op_full[s], (uint32_t)((t >> 1) & 1), abort_flag, error, 55);
+      if (t + 2 < my_tiles) load_tile(t + 2, s);      // every split thread has read raw[s]
       tc_fence_after_sync();
       const uint32_t a_hi = smem_u32(sm.hi[s][0]), a_lo = smem_u32(sm.lo[s][0]);
       const uint32_t d_hi = smem_u32(sm.hi[s][kABoxes]), d_lo = smem_u32(sm.lo[s][kABoxes]);
@@ -505,32 +524,35 @@ k_linear_dw_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_const
       mma_commit(&sm.mma_done[s]);
       if (t == my_tiles - 1) mma_commit(&sm.acc_done);
     }
-  }
-  float *mine = partial + (int64_t)blockIdx.x * K * N;
-  if (my_tiles > 0) {
-    mbar_wait(&sm.acc_done, 0, abort_flag, error, 53);
-    tc_fence_after_sync();
-  }
-  const int row = warp * 32 + lane;                    // row of dw = column of a
-#pragma unroll 1
-  for (int c0 = 0; c0 < N; c0 += 32) {
-    uint32_t r[32];
-    if (my_tiles > 0) {
-      tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + c0, r);
-      tmem_ld_wait();
-    } else {
-#pragma unroll
-      for (int q = 0; q < 32; ++q) r[q] = 0u;
+    if (my_tiles > 1) {                                // the tile before the last: its MMAs must be complete too
+      const int64_t prev = my_tiles - 2;
+      mbar_wait_teardown(&sm.mma_done[prev & 1], (uint32_t)((prev >> 1) & 1));
     }
-    float4 *dst = reinterpret_cast<float4 *>(mine + (int64_t)row * N + c0);
-#pragma unroll
-    for (int q = 0; q < 8; ++q)
-      dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
-                           __uint_as_float(r[4 * q + 3]));
   }
-  if (tid == 0 && my_tiles > 1) {
-    const int64_t prev = my_tiles - 2;
-    mbar_wait(&sm.mma_done[prev & 1], (uint32_t)((prev >> 1) & 1), abort_flag, error, 54);
+  // epilogue: warps 0-3 write this CTA's partial matrix (row of dw = column of a = tensor-memory lane)
+  float *mine = partial + (int64_t)blockIdx.x * K * N;
+  if (warp < 4) {
+    if (my_tiles > 0) {
+      mbar_wait(&sm.acc_done, 0, abort_flag, error, 53);
+      tc_fence_after_sync();
+    }
+    const int row = warp * 32 + lane;
+#pragma unroll 1
+    for (int c0 = 0; c0 < N; c0 += 32) {
+      uint32_t r[32];
+      if (my_tiles > 0) {
+        tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + c0, r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int q = 0; q < 32; ++q) r[q] = 0u;
+      }
+      float4 *dst = reinterpret_cast<float4 *>(mine + (int64_t)row * N + c0);
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                             __uint_as_float(r[4 * q + 3]));
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -638,14 +660,14 @@ extern "C" int32_t tgb_linear_dw_f32(const void *a, const void *dout, void *dw, 
       TGB_CUDA(cudaFuncSetAttribute(k_linear_dw_3xtf32<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       configured = true;
     }
-    k_linear_dw_3xtf32<128><<<grid, 128, smem, st>>>(map_a, map_d, (float *)partial, M, (int *)error_flag);
+    k_linear_dw_3xtf32<128><<<grid, kDwThreads, smem, st>>>(map_a, map_d, (float *)partial, M, (int *)error_flag);
   } else {
     static bool configured = false;
     if (!configured) {
       TGB_CUDA(cudaFuncSetAttribute(k_linear_dw_3xtf32<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       configured = true;
     }
-    k_linear_dw_3xtf32<64><<<grid, 128, smem, st>>>(map_a, map_d, (float *)partial, M, (int *)error_flag);
+    k_linear_dw_3xtf32<64><<<grid, kDwThreads, smem, st>>>(map_a, map_d, (float *)partial, M, (int *)error_flag);
   }
   TGB_LAUNCHED();
   k_sum_dw_partials<<<(unsigned)ceil_div((int64_t)K * N, 256), 256, 0, st>>>((const float *)partial, (int)grid, K * N,
