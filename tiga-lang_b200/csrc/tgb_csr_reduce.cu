@@ -275,10 +275,24 @@ k_finalize_split(const GatherArgs a) {
   for (int64_t f = threadIdx.x; f < a.F; f += kBlock) {
     float acc = a.accumulate ? a.out[row * a.F + f] : (a.mean ? 0.0f : a.identity);
     int32_t arg = -1;
-    for (int32_t s = s0; s < s1; ++s) {
-      const float p = a.partial[(int64_t)s * a.F + f];
-      if (MODE == kMax) max_update(p, a.arg_partial[(int64_t)s * a.F + f], acc, arg);
-      else acc = __fadd_rn(acc, p);
+    // 16 partial rows are fetched at once (the longest row of a power-law graph
+    // has hundreds of segments and one CTA walks them), then folded in order
+    for (int32_t s = s0; s < s1; s += 16) {
+      float p[16];
+      int32_t q[MODE == kMax ? 16 : 1];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const bool in = s + j < s1;
+        p[j] = in ? __ldcs(a.partial + (int64_t)(s + j) * a.F + f) : 0.0f;
+        if constexpr (MODE == kMax) q[j] = in ? __ldcs(a.arg_partial + (int64_t)(s + j) * a.F + f) : -1;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (s + j < s1) {
+          if constexpr (MODE == kMax) max_update(p[j], q[j], acc, arg);
+          else acc = __fadd_rn(acc, p[j]);
+        }
+      }
     }
     if (a.mean) acc = __fdiv_rn(acc, count);
     a.out[row * a.F + f] = acc;

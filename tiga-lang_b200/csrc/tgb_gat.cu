@@ -414,6 +414,113 @@ k_gat_bwd_src_finalize(const GatArgs a) {
 }
 
 // ---------------------------------------------------------------------------
+// Rows of 32 vectors (H*D = 256 bf16) with heads of at most 8 vectors: the
+// forward pass with 8 lanes per row and 4 vectors per lane (lane l holds
+// vectors l, l+8, l+16, l+24, each of a different head), so a warp keeps four
+// rows in flight and broadcasts an edge's source id once per 512 bytes
+// gathered.  The running maximum moves only when an edge exceeds it.  Partial
+// rows of split rows keep the layout of the one-vector-per-lane kernel, so the
+// finalize kernel is shared.  Measured on the 2^21-node R-MAT case: forward
+// 7.23 -> 6.54 ms.  The same shape for the two backward passes was slower
+// (step 23.8 -> 31.9 ms: four per-head scalars per lane and edge instead of
+// one) and is not used.
+// ---------------------------------------------------------------------------
+constexpr int kQG = 8, kQV = 4, kQVecs = kQG * kQV;
+
+template <typename PtrT, typename IdxT, int U>
+__global__ void __launch_bounds__(kBlock)
+k_gat_fwd_q(const GatArgs a) {
+  const int lane = threadIdx.x & (kQG - 1);
+  const int64_t gid = ((int64_t)blockIdx.x * kBlock + threadIdx.x) / kQG;
+  if (gid >= a.work.n_seg + (a.work.n_rows - a.work.n_long)) return;
+  const unsigned gmask = 0xffu << ((threadIdx.x & 31) & ~(kQG - 1));
+  int64_t row, beg, end, seg;
+  decode_group<PtrT>(a.work, gid, row, beg, end, seg);
+  const IdxT *idx = static_cast<const IdxT *>(a.work.idx);
+  const int H = a.H, sh = __ffs(a.lph) - 1;
+  const uint4 *xs = reinterpret_cast<const uint4 *>(a.x_src);
+  int hv[kQV];
+  float sd[kQV], m[kQV], l[kQV], acc[kQV][8];
+#pragma unroll
+  for (int v = 0; v < kQV; ++v) {
+    hv[v] = (lane + v * kQG) >> sh;
+    sd[v] = __ldg(a.s_dst + row * H + hv[v]);
+    m[v] = -INFINITY;
+    l[v] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[v][i] = 0.0f;
+  }
+  for (int64_t base = beg; base < end; base += kQG) {
+    const int64_t e = base + lane;
+    const int32_t c = e < end ? (int32_t)ld_stream(idx + e) : 0;
+    const int n = (int)(end - base < kQG ? end - base : kQG);
+    for (int k0 = 0; k0 < n; k0 += U) {
+      uint4 raw[U][kQV];
+      float ss[U][kQV];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int k = k0 + u;
+        const int32_t cc = __shfl_sync(gmask, c, k < n ? k : n - 1, kQG);
+        if (k < n) {
+#pragma unroll
+          for (int v = 0; v < kQV; ++v) {
+            raw[u][v] = __ldg(xs + (int64_t)cc * kQVecs + lane + v * kQG);
+            ss[u][v] = __ldg(a.s_src + (int64_t)cc * H + hv[v]);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (k0 + u < n) {
+#pragma unroll
+          for (int v = 0; v < kQV; ++v) {
+            float pre;
+            const float logit = logit_of(ss[u][v], sd[v], a.slope_bf, pre);
+            if (logit > m[v]) {                       // rare after the first edges of a row
+              const float scale = m[v] == -INFINITY ? 0.0f : __expf(m[v] - logit);
+              l[v] *= scale;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc[v][i] *= scale;
+              m[v] = logit;
+            }
+            const float p = __expf(logit - m[v]);
+            float val[8];
+            unpack8(raw[u][v], val);
+            l[v] += p;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[v][i] = fmaf(p, val[i], acc[v][i]);
+          }
+        }
+      }
+    }
+  }
+  const bool writer = (lane & (a.lph - 1)) == 0;
+#pragma unroll
+  for (int v = 0; v < kQV; ++v) {
+    const int j = lane + v * kQG;
+    if (seg >= 0) {
+      float *pa = a.part_acc + (seg * kQVecs + j) * 8;
+      *reinterpret_cast<float4 *>(pa) = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+      *reinterpret_cast<float4 *>(pa + 4) = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
+      if (writer) {
+        a.part_ml[seg * 2 * H + hv[v]] = m[v];
+        a.part_ml[seg * 2 * H + H + hv[v]] = l[v];
+      }
+    } else {
+      float o[8];
+      const float inv = l[v] > 0.0f ? 1.0f / l[v] : 0.0f;   // empty row -> exact zeros
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = acc[v][i] * inv;
+      *reinterpret_cast<uint4 *>(a.out + (row * kQVecs + j) * 8) = pack8(o);
+      if (writer) {
+        a.m[row * H + hv[v]] = m[v];
+        a.l[row * H + hv[v]] = l[v];
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // backward pass 3: dx_dst rows and the two parameter gradients
 //   dx_dst[r] = d_sdst[r,h] * a_dst ;  partial[b] = sum_{rows of CTA b} d_s[r,h] * x[r]
 // One thread per 8-element vector of the row; CTAs stride over rows.
@@ -482,6 +589,11 @@ int32_t gat_shape(int32_t H, int32_t D, GatShape *s) {
   s->lph = lph;
   return TGB_STATUS_OK;
 }
+
+constexpr int kQU = 1;   // gathered rows in flight per lane of the 8-lane forward kernel
+
+// rows of 32 vectors whose heads span at most 8 of them take the 8-lane forward kernel
+inline bool quarter_shape(const GatShape &s) { return s.G == kQVecs && s.lph <= kQG; }
 
 struct GatScratch {
   uint64_t part_acc, part_ml, part_h, P, Q, d_sdst, d_ssrc, red, total;
@@ -585,7 +697,10 @@ int32_t tgb_gat_fwd(const tgb_csr_plan *plan, const void *x_src, const void *s_s
   a.slope_bf = __bfloat162float(__float2bfloat16_rn(slope));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int64_t groups = a.work.n_seg + (a.work.n_rows - a.work.n_long);
-  if (plan->index_bits == 32) {
+  if (quarter_shape(shape)) {
+    if (plan->index_bits == 32) k_gat_fwd_q<int32_t, int32_t, kQU><<<blocks_for(groups, kQG), kBlock, 0, st>>>(a);
+    else k_gat_fwd_q<int64_t, int64_t, kQU><<<blocks_for(groups, kQG), kBlock, 0, st>>>(a);
+  } else if (plan->index_bits == 32) {
     TGB_DISPATCH_G(shape.G, k_gat_fwd<int32_t, int32_t, GG><<<blocks_for(groups, GG), kBlock, 0, st>>>(a));
   } else {
     TGB_DISPATCH_G(shape.G, k_gat_fwd<int64_t, int64_t, GG><<<blocks_for(groups, GG), kBlock, 0, st>>>(a));
