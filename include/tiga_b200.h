@@ -318,7 +318,7 @@ TGB_API int32_t tgb_varlen_attn_bwd(const void *q, const void *k, const void *v,
  * Dense float32 linear on the tensor cores (tcgen05, 3xTF32 split):
  *   out[M, N] = a[M, K] @ b_t[N, K]^T
  * The GCN layer's `aggregate @ W`, which the reference leaves to Torch user
- * code after its kernel (SURVEY note on examples/gcn.py:20-30; the reference's
+ * code after its kernel (examples/gcn.py:20-30 of the reference; the reference's
  * own GEMM is f16-only, lib/Target/Triton/Translate.cpp:6306-6322).  b_t is
  * the weight stored [N, K] (pass W^T for a @ W, W itself for dout @ W^T).
  * N in {64, 128}, K in {32, 64, 96, 128}; 16-byte aligned row-major inputs.

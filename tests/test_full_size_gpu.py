@@ -1,4 +1,4 @@
-"""Parity at the BASELINE configurations' full sizes through size-independent
+"""Parity at the benchmark configurations' full sizes through size-independent
 properties (the CPU oracle would take minutes there): adjoint identities that
 tie forward, dx and dw together, column-sum checksums computed independently in
 float64, the CPU oracle on sampled rows, and softmax rows that must sum to one."""

@@ -1,7 +1,7 @@
 // GAT-style edge attention over CSR rows with the online-softmax reducer,
 // bf16 features, float32 state, and its backward without atomics.
 //
-// Program (reference spelling, SURVEY appendix E):
+// Program (reference spelling):
 //   s     = (src.x * a_src).sum(-1) + (dst.x * a_dst).sum(-1)        per head
 //   score = maximum(s, slope * s)                                     leaky-relu
 //   out   = online_softmax(score, src.x)                              per head
