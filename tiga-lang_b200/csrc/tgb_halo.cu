@@ -13,30 +13,52 @@ namespace {
 
 constexpr int kBlock = 256;
 
+constexpr int kLanes = 8;    // lanes per row on the vector path: four rows per warp
+constexpr int kInFlight = 4; // float4 per lane and pass: 8 x 4 x 16 = 512 bytes of a row per pass
+
 template <bool ADD>
 __global__ void __launch_bounds__(kBlock)
 k_move_rows(float *__restrict__ rows, const int64_t *__restrict__ ids, float *__restrict__ packed, int64_t n,
             int64_t F) {
-  // one warp per row, 128-bit accesses when the row allows it
-  const int lane = threadIdx.x & 31;
-  const int64_t i = ((int64_t)blockIdx.x * kBlock + threadIdx.x) >> 5;
-  if (i >= n) return;
-  float *row = rows + ids[i] * F;
-  float *pack = packed + i * F;
   const bool vec = (F & 3) == 0 && ((((uintptr_t)rows | (uintptr_t)packed) & 15u) == 0);
   if (vec) {
-    for (int64_t f = 4 * lane; f < F; f += 128) {
-      if (ADD) {
-        float4 a = *reinterpret_cast<float4 *>(row + f);
-        const float4 b = __ldcs(reinterpret_cast<const float4 *>(pack + f));
-        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
-        *reinterpret_cast<float4 *>(row + f) = a;
-      } else {
-        __stcs(reinterpret_cast<float4 *>(pack + f), *reinterpret_cast<const float4 *>(row + f));
+    // eight lanes per row, every lane keeps four 128-bit accesses in flight
+    const int lane = threadIdx.x & (kLanes - 1);
+    const int64_t i = ((int64_t)blockIdx.x * kBlock + threadIdx.x) / kLanes;
+    if (i >= n) return;
+    float *row = rows + ids[i] * F;
+    float *pack = packed + i * F;
+    for (int64_t f0 = 0; f0 < F; f0 += 4 * kLanes * kInFlight) {
+      float4 a[kInFlight], b[kInFlight];
+#pragma unroll
+      for (int q = 0; q < kInFlight; ++q) {
+        const int64_t f = f0 + 4 * (lane + kLanes * q);
+        if (f < F) {
+          a[q] = *reinterpret_cast<const float4 *>(row + f);
+          if (ADD) b[q] = __ldcs(reinterpret_cast<const float4 *>(pack + f));
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < kInFlight; ++q) {
+        const int64_t f = f0 + 4 * (lane + kLanes * q);
+        if (f < F) {
+          if (ADD) {
+            a[q].x += b[q].x; a[q].y += b[q].y; a[q].z += b[q].z; a[q].w += b[q].w;
+            *reinterpret_cast<float4 *>(row + f) = a[q];
+          } else {
+            __stcs(reinterpret_cast<float4 *>(pack + f), a[q]);
+          }
+        }
       }
     }
   } else {
-    for (int64_t f = lane; f < F; f += 32) {
+    // any width or alignment: the same eight lanes stride over the row's elements
+    const int lane = threadIdx.x & (kLanes - 1);
+    const int64_t i = ((int64_t)blockIdx.x * kBlock + threadIdx.x) / kLanes;
+    if (i >= n) return;
+    float *row = rows + ids[i] * F;
+    float *pack = packed + i * F;
+    for (int64_t f = lane; f < F; f += kLanes) {
       if (ADD) row[f] += pack[f];
       else pack[f] = row[f];
     }
@@ -48,7 +70,7 @@ int32_t move_rows(bool add, void *rows, const void *ids, void *packed, int64_t n
   if (n == 0) return TGB_STATUS_OK;
   if (!rows || !ids || !packed) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const unsigned blocks = (unsigned)ceil_div(n * 32, kBlock);
+  const unsigned blocks = (unsigned)ceil_div(n * kLanes, kBlock);
   if (add)
     k_move_rows<true><<<blocks, kBlock, 0, st>>>((float *)rows, (const int64_t *)ids, (float *)packed, n, F);
   else
