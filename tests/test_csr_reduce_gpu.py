@@ -343,3 +343,45 @@ def test_halo_row_movers(F):
     expect[ids] += update
     ops.rows_scatter_add(rows, ids, update)
     assert torch.equal(rows, expect)
+
+
+@pytest.mark.parametrize("F", (32, 64, 128))
+def test_owned_and_ghost_sub_relations_through_the_native_backend(oracle, F):
+    # One rank's local work of the halo runtime on a single GPU, no exchange: the relation is cut into an
+    # owned-source and a ghost-source sub-relation (edge maps into the caller's edge order), the second is
+    # accumulated onto the first, and the backward writes both parts of dw in place.
+    from tiga.distributed.runtime import NativeBackend
+
+    row_ptr, col = syn.rmat_csr(10, 12, seed=23)         # hubs above the split threshold
+    n, E = row_ptr.numel() - 1, col.numel()
+    gen = torch.Generator().manual_seed(100 + F)
+    x = torch.randn(n, F, generator=gen)
+    w = torch.rand(E, generator=gen)
+    dy = torch.randn(n, F, generator=gen)
+    cut = n // 3                                           # sources below `cut` play the owned rows
+    dst = torch.repeat_interleave(torch.arange(n), row_ptr[1:] - row_ptr[:-1])
+    own = col < cut
+
+    def sub(mask, columns, num_src):
+        ptr = torch.zeros(n + 1, dtype=torch.int64)
+        torch.cumsum(torch.bincount(dst[mask], minlength=n), 0, out=ptr[1:])
+        g = tg.Graph.from_csr(ptr.cuda(), columns.contiguous().cuda(), num_src=num_src)
+        g._edge_map = torch.nonzero(mask).reshape(-1).to(torch.int32).cuda()
+        return g
+
+    g_own = sub(own, col[own], cut)
+    g_ghost = sub(~own, col[~own] - cut, n - cut)
+    backend = NativeBackend()
+    xc, wc, dyc = x.cuda(), w.cuda(), dy.cuda()
+    out = backend.forward(g_own, xc[:cut].contiguous(), wc)
+    out = backend.forward(g_ghost, xc[cut:].contiguous(), wc, accumulate_into=out)
+    rp, cc = row_ptr.numpy(), col.numpy()
+    ref = oracle.wsum_fwd(rp, cc, x.numpy(), w.numpy())
+    assert_sum_close(out.cpu().numpy(), ref, oracle.wsum_fwd(rp, cc, x.abs().numpy(), w.numpy()))
+    dx = torch.cat((backend.backward_dx(g_own, dyc, wc), backend.backward_dx(g_ghost, dyc, wc)))
+    ref_dx = oracle.wsum_bwd_dx(rp, cc, n, dy.numpy(), w.numpy())
+    assert_sum_close(dx.cpu().numpy(), ref_dx, oracle.wsum_bwd_dx(rp, cc, n, dy.abs().numpy(), w.numpy()))
+    dw = torch.empty(E, device="cuda")
+    backend.backward_dw(g_own, dyc, xc[:cut].contiguous(), dw)
+    backend.backward_dw(g_ghost, dyc, xc[cut:].contiguous(), dw)
+    assert_dot_close(oracle, dw.cpu().numpy(), oracle.wsum_bwd_dw(rp, cc, dy.numpy(), x.numpy()), row_ptr, col, dy, x)
