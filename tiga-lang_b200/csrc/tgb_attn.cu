@@ -10,10 +10,11 @@
 // python/tiga/graph/core.py:314-351,650-709), and to a backward pass, which the
 // reference does not have.
 //
-// Forward, one CTA (128 threads) per (128-query tile, head):
-//   TMA loads Q once and K/V blocks of 128 keys into a two-stage ring
+// Forward, one CTA (four softmax warps + one issue warp) per (128-query tile, head):
+//   TMA loads Q once and K/V blocks of 64 keys into two-stage rings
 //   (128-byte rows, 128-byte swizzle; a 128-wide head is two 64-column boxes);
-//   one thread issues tcgen05.mma: S = Q K^T into tensor memory; the four warps
+//   one thread of the issue warp issues tcgen05.mma: S = Q K^T into one of two
+//   buffers in tensor memory, one block ahead of the softmax; the four warps
 //   read their 32 rows of S, keep the running max / denominator in registers,
 //   write P as bf16 into a swizzled shared-memory tile; a second MMA group
 //   accumulates P V in tensor memory over all key blocks (V is consumed
@@ -71,7 +72,7 @@ struct FwdSmem {
   alignas(1024) uint8_t k[2][HALVES][kKeyBoxBytes];
   alignas(1024) uint8_t v[2][HALVES][kKeyBoxBytes];
   alignas(1024) uint8_t p[kBoxBytes];              // [128 queries x 64 keys] bf16
-  uint64_t q_full, k_full[2], v_full[2], s_done, o_done;
+  uint64_t q_full, k_full[2], v_full[2], s_done[2], s_free[2], p_ready, o_done;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -82,8 +83,10 @@ struct FwdSmem {
 // 2^8 and the final O / l is the same quotient as with the exact maximum.
 constexpr float kRescaleGap = 8.0f;
 
+constexpr int kFwdThreads = 160;   // warps 0-3: softmax (one query row per thread); warp 4: TMA + MMA issue
+
 template <int HALVES>
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(kFwdThreads, 2)
 k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
            const __grid_constant__ CUtensorMap map_v, const Tile *__restrict__ tiles, int H,
            float scale_log2, int causal, __nv_bfloat16 *__restrict__ out, float *__restrict__ lse, int *error) {
@@ -97,19 +100,19 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const Tile tile = tiles[blockIdx.x];
   const int head = tile.head;
-  const int row = warp * 32 + lane;                 // query row of this thread inside the tile
-  const int q_index = tile.q_begin + row;
   const int key_limit = causal ? min(tile.q_begin + kTile, tile.seq_end) : tile.seq_end;
   const int n_blocks = (key_limit - tile.seq_begin + kKeyBlock - 1) / kKeyBlock;
 
   if (tid == 0) {
     sm.abort_flag = 0;
     mbar_init(&sm.q_full, 1);
-    mbar_init(&sm.k_full[0], 1);
-    mbar_init(&sm.k_full[1], 1);
-    mbar_init(&sm.v_full[0], 1);
-    mbar_init(&sm.v_full[1], 1);
-    mbar_init(&sm.s_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.k_full[i], 1);
+      mbar_init(&sm.v_full[i], 1);
+      mbar_init(&sm.s_done[i], 1);
+      mbar_init(&sm.s_free[i], 128);
+    }
+    mbar_init(&sm.p_ready, 128);
     mbar_init(&sm.o_done, 1);
     mbar_fence_init();
     tma_prefetch_descriptor(&map_q);
@@ -117,168 +120,190 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
     tma_prefetch_descriptor(&map_v);
   }
   __syncthreads();
-  if (warp == 0) tmem_alloc(&sm.tmem_base, 256);    // S: columns 0-63, P V: columns 128-255
+  if (warp == 0) tmem_alloc(&sm.tmem_base, 256);    // S: two buffers at columns 0-63 and 64-127, O: columns 128-255
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_s = sm.tmem_base, tmem_o = sm.tmem_base + 128;
-  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
   volatile int *abort_flag = &sm.abort_flag;
 
-  auto load_k = [&](int block, int stage) {
-    const int y = tile.seq_begin + block * kKeyBlock;
-    mbar_arrive_expect_tx(&sm.k_full[stage], HALVES * kKeyBoxBytes);
+  if (warp == 4) {
+    // ---- issue warp: one thread loads Q, K, V and issues the MMAs.  S of block kb+1 is issued before
+    // the softmax of block kb has run (two S buffers), P V of block kb while the softmax warps are
+    // already on block kb+1; issuing can stall on the tensor pipe, so this thread does nothing else.
+    if (lane == 0 && n_blocks > 0) {
+      auto load_k = [&](int block) {
+        const int stage = block & 1, y = tile.seq_begin + block * kKeyBlock;
+        mbar_arrive_expect_tx(&sm.k_full[stage], HALVES * kKeyBoxBytes);
 #pragma unroll
-    for (int j = 0; j < HALVES; ++j) tma_load_2d(sm.k[stage][j], &map_k, head * D + 64 * j, y, &sm.k_full[stage]);
-  };
-  auto load_v = [&](int block, int stage) {
-    const int y = tile.seq_begin + block * kKeyBlock;
-    mbar_arrive_expect_tx(&sm.v_full[stage], HALVES * kKeyBoxBytes);
+        for (int j = 0; j < HALVES; ++j) tma_load_2d(sm.k[stage][j], &map_k, head * D + 64 * j, y, &sm.k_full[stage]);
+      };
+      auto load_v = [&](int block) {
+        const int stage = block & 1, y = tile.seq_begin + block * kKeyBlock;
+        mbar_arrive_expect_tx(&sm.v_full[stage], HALVES * kKeyBoxBytes);
 #pragma unroll
-    for (int j = 0; j < HALVES; ++j) tma_load_2d(sm.v[stage][j], &map_v, head * D + 64 * j, y, &sm.v_full[stage]);
-  };
-  if (tid == 0) {
-    mbar_arrive_expect_tx(&sm.q_full, HALVES * kBoxBytes);
+        for (int j = 0; j < HALVES; ++j) tma_load_2d(sm.v[stage][j], &map_v, head * D + 64 * j, y, &sm.v_full[stage]);
+      };
+      constexpr uint32_t idesc_s = instr_desc(kFmtBF16, kFmtBF16, kTile, kKeyBlock, 0, 0);
+      constexpr uint32_t idesc_o = instr_desc(kFmtBF16, kFmtBF16, kTile, D, 0, 1);   // V is MN-major
+      auto issue_s = [&](int block) {
+        const int st = block & 1;
+        mbar_wait(&sm.k_full[st], (uint32_t)((block >> 1) & 1), abort_flag, error, 12);
+        if (block >= 2)       // the softmax of block-2 has read this S buffer
+          mbar_wait(&sm.s_free[st], (uint32_t)(((block >> 1) - 1) & 1), abort_flag, error, 17);
+        tc_fence_after_sync();
 #pragma unroll
-    for (int j = 0; j < HALVES; ++j) tma_load_2d(sm.q[j], &map_q, head * D + 64 * j, tile.q_begin, &sm.q_full);
-    load_k(0, 0);
-    load_v(0, 0);
-  }
-
-  constexpr uint32_t idesc_s = instr_desc(kFmtBF16, kFmtBF16, kTile, kKeyBlock, 0, 0);
-  constexpr uint32_t idesc_o = instr_desc(kFmtBF16, kFmtBF16, kTile, D, 0, 1);   // V is MN-major
-  float m = -INFINITY, l = 0.0f;                    // reference maximum (log2 domain) and denominator
-
-  mbar_wait(&sm.q_full, 0, abort_flag, error, 11);
-  for (int kb = 0; kb < n_blocks; ++kb) {
-    const int st = kb & 1;
-    const int key0 = tile.seq_begin + kb * kKeyBlock;
-    if (tid == 0 && kb + 1 < n_blocks) load_k(kb + 1, st ^ 1);    // S of block kb-1 was waited for last iteration
-    mbar_wait(&sm.k_full[st], (uint32_t)((kb >> 1) & 1), abort_flag, error, 12);
-    if (tid == 0) {
-      tc_fence_after_sync();
+        for (int k16 = 0; k16 < D / 16; ++k16) {       // 16 bf16 = 32 bytes of the 128-byte row per MMA
+          const int j = k16 >> 2;
+          const uint32_t off = (k16 & 3) * 32;
+          mma_f16(tmem_s + (uint32_t)st * kKeyBlock, smem_desc_k_major_sw128(smem_u32(sm.q[j]) + off),
+                  smem_desc_k_major_sw128(smem_u32(sm.k[st][j]) + off), idesc_s, k16 != 0);
+        }
+        mma_commit(&sm.s_done[st]);
+      };
+      mbar_arrive_expect_tx(&sm.q_full, HALVES * kBoxBytes);
 #pragma unroll
-      for (int k16 = 0; k16 < D / 16; ++k16) {       // 16 bf16 = 32 bytes of the 128-byte row per MMA
-        const int j = k16 >> 2;
-        const uint32_t off = (k16 & 3) * 32;
-        mma_f16(tmem_s, smem_desc_k_major_sw128(smem_u32(sm.q[j]) + off),
-                smem_desc_k_major_sw128(smem_u32(sm.k[st][j]) + off), idesc_s, k16 != 0);
+      for (int j = 0; j < HALVES; ++j) tma_load_2d(sm.q[j], &map_q, head * D + 64 * j, tile.q_begin, &sm.q_full);
+      load_k(0);
+      load_v(0);
+      if (n_blocks > 1) {
+        load_k(1);
+        load_v(1);
       }
-      mma_commit(&sm.s_done);
+      mbar_wait(&sm.q_full, 0, abort_flag, error, 11);
+      issue_s(0);
+      for (int kb = 0; kb < n_blocks; ++kb) {
+        const int st = kb & 1;
+        if (kb + 1 < n_blocks) issue_s(kb + 1);
+        if (kb + 2 < n_blocks) {                        // K stage of block kb is free once S(kb) is complete
+          mbar_wait(&sm.s_done[st], (uint32_t)((kb >> 1) & 1), abort_flag, error, 13);
+          load_k(kb + 2);
+        }
+        mbar_wait(&sm.p_ready, (uint32_t)(kb & 1), abort_flag, error, 18);
+        // the softmax threads waited for P V of block kb-1 before they wrote P: its V stage is free
+        if (kb >= 1 && kb + 1 < n_blocks) load_v(kb + 1);
+        mbar_wait(&sm.v_full[st], (uint32_t)((kb >> 1) & 1), abort_flag, error, 15);
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k16 = 0; k16 < kKeyBlock / 16; ++k16) {   // 16 keys per MMA, accumulated over all blocks
+          const uint64_t a_desc = smem_desc_k_major_sw128(smem_u32(sm.p) + k16 * 32);
+          const uint64_t b_desc = smem_desc_mn_major_sw128(smem_u32(sm.v[st][0]) + k16 * 16 * 128, kKeyBoxBytes);
+          mma_f16(tmem_o, a_desc, b_desc, idesc_o, (kb | k16) != 0);
+        }
+        mma_commit(&sm.o_done);
+      }
     }
-    mbar_wait(&sm.s_done, (uint32_t)(kb & 1), abort_flag, error, 13);
-    tc_fence_after_sync();
-
-    const bool masked = (key0 + kKeyBlock > tile.seq_end) || (causal && key0 + kKeyBlock - 1 > tile.q_begin);
-    // pass A: row maximum (overlaps P V of the previous block)
-    float block_max = -INFINITY;
-#pragma unroll 1
-    for (int c0 = 0; c0 < kKeyBlock; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld_32x32(tmem_s + lane_base + c0, r);
+  } else {
+    // ---- softmax warps -----------------------------------------------------------------------------
+    const int row = warp * 32 + lane;                 // query row of this thread inside the tile
+    const int q_index = tile.q_begin + row;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    float m = -INFINITY, l = 0.0f;                    // reference maximum (log2 domain) and denominator
+    for (int kb = 0; kb < n_blocks; ++kb) {
+      const int st = kb & 1;
+      const int key0 = tile.seq_begin + kb * kKeyBlock;
+      const uint32_t s_addr = tmem_s + (uint32_t)st * kKeyBlock + lane_base;
+      mbar_wait(&sm.s_done[st], (uint32_t)((kb >> 1) & 1), abort_flag, error, 13);
+      tc_fence_after_sync();
+      const bool masked = (key0 + kKeyBlock > tile.seq_end) || (causal && key0 + kKeyBlock - 1 > tile.q_begin);
+      // The 64 scores of the row stay in registers for both passes; the S buffer is released at once.
+      // Maximum and sum run as four independent chains: with two warps per scheduler every dependent
+      // instruction would otherwise wait out its full latency.
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32(s_addr, r0);
+      tmem_ld_32x32(s_addr + 32, r1);
       tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&sm.s_free[st]);                     // this S buffer may be overwritten
+      float sc[kKeyBlock];
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
-        const int key = key0 + c0 + c;
-        const bool valid = !masked || (key < tile.seq_end && (!causal || key <= q_index));
-        if (valid) block_max = fmaxf(block_max, __uint_as_float(r[c]));
+        sc[c] = __uint_as_float(r0[c]);
+        sc[32 + c] = __uint_as_float(r1[c]);
       }
+      if (masked) {
+#pragma unroll
+        for (int c = 0; c < kKeyBlock; ++c) {
+          const int key = key0 + c;
+          if (!(key < tile.seq_end && (!causal || key <= q_index))) sc[c] = -INFINITY;
+        }
+      }
+      float bm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < kKeyBlock; ++c) bm[c & 3] = fmaxf(bm[c & 3], sc[c]);
+      const float block_max = fmaxf(fmaxf(bm[0], bm[1]), fmaxf(bm[2], bm[3]));
+      const float m_blk = fmaxf(m, block_max * scale_log2);
+      float alpha = 1.0f;
+      if (m == -INFINITY) {
+        m = m_blk;                                     // nothing accumulated for this row yet
+      } else if (m_blk - m > kRescaleGap) {
+        alpha = fast_exp2(m - m_blk);
+        m = m_blk;
+      }
+      const float m_use = m == -INFINITY ? 0.0f : m;   // a fully masked row keeps p = 0
+      // p = 2^(s - m); masked scores are -inf and give exactly 0
+      float bs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int c = 0; c < kKeyBlock; ++c) {
+        sc[c] = fast_exp2(fmaf(sc[c], scale_log2, -m_use));
+        bs[c & 3] += sc[c];
+      }
+      l = l * alpha + ((bs[0] + bs[1]) + (bs[2] + bs[3]));
+      if (kb > 0) {
+        // P V of the previous block read the P tile and the accumulator
+        mbar_wait(&sm.o_done, (uint32_t)((kb - 1) & 1), abort_flag, error, 14);
+        tc_fence_after_sync();
+      }
+      if (__any_sync(0xffffffffu, alpha != 1.0f)) {    // rare: move the reference maximum of these 32 rows
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_o + lane_base + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+          tmem_st_32x32(tmem_o + lane_base + c0, r);
+        }
+        tmem_st_wait();
+      }
+#pragma unroll
+      for (int g = 0; g < kKeyBlock / 8; ++g)
+        store_swizzled_chunk(sm.p, row, g,
+                             make_uint4(pack_bf16(sc[8 * g], sc[8 * g + 1]), pack_bf16(sc[8 * g + 2], sc[8 * g + 3]),
+                                        pack_bf16(sc[8 * g + 4], sc[8 * g + 5]), pack_bf16(sc[8 * g + 6], sc[8 * g + 7])));
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      mbar_arrive(&sm.p_ready);                        // P written, accumulator rescaled
     }
-    const float m_blk = fmaxf(m, block_max * scale_log2);
-    float alpha = 1.0f;
-    if (m == -INFINITY) {
-      m = m_blk;                                     // nothing accumulated for this row yet
-    } else if (m_blk - m > kRescaleGap) {
-      alpha = fast_exp2(m - m_blk);
-      m = m_blk;
-    }
-    const float m_use = m == -INFINITY ? 0.0f : m;   // a fully masked row keeps p = 0
-    if (kb > 0) {
-      // P V of the previous block read the P tile, the other V stage and the accumulator
-      mbar_wait(&sm.o_done, (uint32_t)((kb - 1) & 1), abort_flag, error, 14);
+    if (n_blocks > 0) {
+      mbar_wait(&sm.o_done, (uint32_t)((n_blocks - 1) & 1), abort_flag, error, 16);
       tc_fence_after_sync();
     }
-    if (tid == 0 && kb + 1 < n_blocks) load_v(kb + 1, st ^ 1);
-    if (__any_sync(0xffffffffu, alpha != 1.0f)) {    // rare: move the reference maximum of these 32 rows
+    const bool writes = q_index < tile.seq_end && !*abort_flag;
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    __nv_bfloat16 *dst = out + ((int64_t)q_index * H + head) * D;
 #pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t r[32];
+    for (int c0 = 0; c0 < D; c0 += 32) {
+      uint32_t r[32];
+      if (n_blocks > 0) {
         tmem_ld_32x32(tmem_o + lane_base + c0, r);
         tmem_ld_wait();
+      } else {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
-        tmem_st_32x32(tmem_o + lane_base + c0, r);
+        for (int c = 0; c < 32; ++c) r[c] = 0u;
       }
-      tmem_st_wait();
-      l *= alpha;
-    }
-    // pass B: p = 2^(s - m), written as bf16 for the second MMA
-    float block_sum = 0.0f;
-#pragma unroll 1
-    for (int c0 = 0; c0 < kKeyBlock; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld_32x32(tmem_s + lane_base + c0, r);
-      tmem_ld_wait();
-      float p[32];
+      if (writes) {
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        const int key = key0 + c0 + c;
-        const bool valid = !masked || (key < tile.seq_end && (!causal || key <= q_index));
-        p[c] = valid ? fast_exp2(__uint_as_float(r[c]) * scale_log2 - m_use) : 0.0f;
-        block_sum += p[c];
+        for (int d = 0; d < 32; d += 8)
+          *reinterpret_cast<uint4 *>(dst + c0 + d) = make_uint4(
+              pack_bf16(__uint_as_float(r[d]) * inv, __uint_as_float(r[d + 1]) * inv),
+              pack_bf16(__uint_as_float(r[d + 2]) * inv, __uint_as_float(r[d + 3]) * inv),
+              pack_bf16(__uint_as_float(r[d + 4]) * inv, __uint_as_float(r[d + 5]) * inv),
+              pack_bf16(__uint_as_float(r[d + 6]) * inv, __uint_as_float(r[d + 7]) * inv));
       }
-      uint8_t *half = sm.p;
-#pragma unroll
-      for (int g = 0; g < 4; ++g)
-        store_swizzled_chunk(half, row, ((c0 & 63) >> 3) + g,
-                             make_uint4(pack_bf16(p[8 * g], p[8 * g + 1]), pack_bf16(p[8 * g + 2], p[8 * g + 3]),
-                                        pack_bf16(p[8 * g + 4], p[8 * g + 5]), pack_bf16(p[8 * g + 6], p[8 * g + 7])));
     }
-    l += block_sum;
-    fence_proxy_async_smem();
-    tc_fence_before_sync();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after_sync();
-      mbar_wait(&sm.v_full[st], (uint32_t)((kb >> 1) & 1), abort_flag, error, 15);
-#pragma unroll
-      for (int k16 = 0; k16 < kKeyBlock / 16; ++k16) {   // 16 keys per MMA, accumulated over all blocks
-        const uint64_t a_desc = smem_desc_k_major_sw128(smem_u32(sm.p) + k16 * 32);
-        const uint64_t b_desc = smem_desc_mn_major_sw128(smem_u32(sm.v[st][0]) + k16 * 16 * 128, kKeyBoxBytes);
-        mma_f16(tmem_o, a_desc, b_desc, idesc_o, (kb | k16) != 0);
-      }
-      mma_commit(&sm.o_done);
-    }
+    if (writes) lse[(int64_t)q_index * H + head] = l > 0.0f ? (m + log2f(l)) * kLn2 : -INFINITY;
   }
-  if (n_blocks > 0) {
-    mbar_wait(&sm.o_done, (uint32_t)((n_blocks - 1) & 1), abort_flag, error, 16);
-    tc_fence_after_sync();
-  }
-
-  const bool writes = q_index < tile.seq_end && !*abort_flag;
-  const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-  __nv_bfloat16 *dst = out + ((int64_t)q_index * H + head) * D;
-#pragma unroll 1
-  for (int c0 = 0; c0 < D; c0 += 32) {
-    uint32_t r[32];
-    if (n_blocks > 0) {
-      tmem_ld_32x32(tmem_o + lane_base + c0, r);
-      tmem_ld_wait();
-    } else {
-#pragma unroll
-      for (int c = 0; c < 32; ++c) r[c] = 0u;
-    }
-    if (writes) {
-#pragma unroll
-      for (int d = 0; d < 32; d += 8)
-        *reinterpret_cast<uint4 *>(dst + c0 + d) = make_uint4(
-            pack_bf16(__uint_as_float(r[d]) * inv, __uint_as_float(r[d + 1]) * inv),
-            pack_bf16(__uint_as_float(r[d + 2]) * inv, __uint_as_float(r[d + 3]) * inv),
-            pack_bf16(__uint_as_float(r[d + 4]) * inv, __uint_as_float(r[d + 5]) * inv),
-            pack_bf16(__uint_as_float(r[d + 6]) * inv, __uint_as_float(r[d + 7]) * inv));
-    }
-  }
-  if (writes) lse[(int64_t)q_index * H + head] = l > 0.0f ? (m + log2f(l)) * kLn2 : -INFINITY;
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(sm.tmem_base, 256);
@@ -678,7 +703,7 @@ extern "C" int32_t tgb_varlen_attn_fwd(const void *q, const void *k, const void 
       TGB_CUDA(cudaFuncSetAttribute(k_attn_fwd<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       configured = true;
     }
-    k_attn_fwd<2><<<grid, 128, smem, st>>>(map_q, map_k, map_v, (const Tile *)tiles, H, scale_log2, causal,
+    k_attn_fwd<2><<<grid, kFwdThreads, smem, st>>>(map_q, map_k, map_v, (const Tile *)tiles, H, scale_log2, causal,
                                            (__nv_bfloat16 *)out, (float *)lse, (int *)error_flag);
   } else {
     const size_t smem = sizeof(FwdSmem<1>);
@@ -687,7 +712,7 @@ extern "C" int32_t tgb_varlen_attn_fwd(const void *q, const void *k, const void 
       TGB_CUDA(cudaFuncSetAttribute(k_attn_fwd<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       configured = true;
     }
-    k_attn_fwd<1><<<grid, 128, smem, st>>>(map_q, map_k, map_v, (const Tile *)tiles, H, scale_log2, causal,
+    k_attn_fwd<1><<<grid, kFwdThreads, smem, st>>>(map_q, map_k, map_v, (const Tile *)tiles, H, scale_log2, causal,
                                            (__nv_bfloat16 *)out, (float *)lse, (int *)error_flag);
   }
   TGB_LAUNCHED();
