@@ -258,6 +258,12 @@ def run_attention(args, device):
 
     ms = time_steps(step, args.steps, args.warmup)
     ops.check_async_errors()
+    if args.kernel_table:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step()
+            torch.cuda.synchronize()
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=12, max_name_column_width=70), flush=True)
     pairs = float((lengths.double() * (lengths.double() + 1) / 2).sum())
     fwd_flops = 4.0 * H * D * pairs
     total_flops = 3.5 * fwd_flops

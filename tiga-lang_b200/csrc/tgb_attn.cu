@@ -110,9 +110,9 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       mbar_init(&sm.k_full[i], 1);
       mbar_init(&sm.v_full[i], 1);
       mbar_init(&sm.s_done[i], 1);
-      mbar_init(&sm.s_free[i], 128);
+      mbar_init(&sm.s_free[i], 4);        // one arrival per softmax warp
     }
-    mbar_init(&sm.p_ready, 128);
+    mbar_init(&sm.p_ready, 4);
     mbar_init(&sm.o_done, 1);
     mbar_fence_init();
     tma_prefetch_descriptor(&map_q);
@@ -214,7 +214,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
       tmem_ld_32x32(s_addr + 32, r1);
       tmem_ld_wait();
       tc_fence_before_sync();
-      mbar_arrive(&sm.s_free[st]);                     // this S buffer may be overwritten
+      mbar_arrive_warp(&sm.s_free[st]);                // this S buffer may be overwritten
       float sc[kKeyBlock];
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
@@ -273,7 +273,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
                                         pack_bf16(sc[8 * g + 4], sc[8 * g + 5]), pack_bf16(sc[8 * g + 6], sc[8 * g + 7])));
       tc_fence_before_sync();
       fence_proxy_async_smem();
-      mbar_arrive(&sm.p_ready);                        // P written, accumulator rescaled
+      mbar_arrive_warp(&sm.p_ready);                   // P written, accumulator rescaled
     }
     if (n_blocks > 0) {
       mbar_wait(&sm.o_done, (uint32_t)((n_blocks - 1) & 1), abort_flag, error, 16);
@@ -338,20 +338,6 @@ __global__ void k_attn_delta(const __nv_bfloat16 *__restrict__ o, const __nv_bfl
   if (lane == 0) delta[r] = acc;
 }
 
-template <int HALVES>
-struct BwdSmem {
-  alignas(1024) uint8_t fixed_a[HALVES][kBoxBytes];   // dkv: K tile      dq: Q tile
-  alignas(1024) uint8_t fixed_b[HALVES][kBoxBytes];   // dkv: V tile      dq: dO tile
-  alignas(1024) uint8_t stream_a[HALVES][kBoxBytes];  // dkv: Q block     dq: K block
-  alignas(1024) uint8_t stream_b[HALVES][kBoxBytes];  // dkv: dO block    dq: V block
-  alignas(1024) uint8_t p[2][kBoxBytes];              // dkv: P^T         dq: unused
-  alignas(1024) uint8_t ds[2][kBoxBytes];             // dkv: dS^T        dq: dS
-  float lse2[kTile];
-  float delta[kTile];
-  uint64_t fixed_full, stream_full, s_done, acc_done;
-  uint32_t tmem_base;
-  int abort_flag;
-};
 
 // [128 x 128] score-like product of two K-major tiles of width D into `tmem`
 template <int HALVES, int BOX_A, int BOX_B>
@@ -365,17 +351,34 @@ __device__ __forceinline__ void issue_scores(uint32_t tmem, uint8_t (*a)[BOX_A],
   }
 }
 
-// [128 x D] += A[128 x 128] (K-major halves of 64 columns) * B[128 rows x D] (MN-major as loaded)
-__device__ __forceinline__ void issue_gradient(uint32_t tmem, uint8_t (*a)[kBoxBytes], uint8_t *b, uint32_t idesc,
-                                               bool accumulate) {
-#pragma unroll
-  for (int k16 = 0; k16 < kTile / 16; ++k16)
-    mma_f16(tmem, smem_desc_k_major_sw128(smem_u32(a[k16 >> 2]) + (k16 & 3) * 32),
-            smem_desc_mn_major_sw128(smem_u32(b) + k16 * 16 * 128, kBoxBytes), idesc, accumulate || k16 != 0);
-}
+// dK/dV kernel: CTA = (128-key tile, head), eight compute warps (a thread owns a key row of the
+// transposed score tile and half of the block's queries) + one issue warp.  Queries stream in blocks of 64 through two stages; S^T and
+// dP^T have two buffers each in tensor memory (queries stream through three shared-memory stages), so the issue thread puts the score MMAs of block qb+1 in
+// flight while the compute warps turn block qb into P^T and dS^T, and issues the gradient MMAs of block
+// qb as soon as those tiles are written.  Tensor memory: S^T 0/64, dP^T 128/192, dV 256, dK 384.
+constexpr int kQBlock = 64;
+constexpr int kQBoxBytes = kQBlock * 128;
+constexpr int kDkvStages = 3;              // query-block stages: the TMA of block qb+2 starts when block qb-1 is done
+constexpr int kDkvComputeThreads = 256;   // eight compute warps: two per 32-lane quadrant, 32 queries of the block each
+constexpr int kDkvThreads = kDkvComputeThreads + 32;
 
 template <int HALVES>
-__global__ void __launch_bounds__(128, 1)
+struct DkvSmem {
+  alignas(1024) uint8_t k[HALVES][kBoxBytes];
+  alignas(1024) uint8_t v[HALVES][kBoxBytes];
+  alignas(1024) uint8_t q[kDkvStages][HALVES][kQBoxBytes];
+  alignas(1024) uint8_t d_o[kDkvStages][HALVES][kQBoxBytes];
+  alignas(1024) uint8_t p[2][kBoxBytes];     // P^T  [128 keys x 64 queries] bf16
+  alignas(1024) uint8_t ds[2][kBoxBytes];    // dS^T
+  float lse2[2][kQBlock];
+  float delta[2][kQBlock];
+  uint64_t fixed_full, stream_full[kDkvStages], s_done[2], s_free[2], pd_ready[2], g_done[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int HALVES>
+__global__ void __launch_bounds__(kDkvThreads, 1)
 k_attn_bwd_dkv(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                const Tile *__restrict__ tiles, int H, float scale, int causal, const float *__restrict__ lse,
@@ -383,23 +386,25 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                int *error) {
   constexpr int D = 64 * HALVES;
   extern __shared__ uint8_t smem_raw[];
-  BwdSmem<HALVES> &sm =
-      *reinterpret_cast<BwdSmem<HALVES> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  DkvSmem<HALVES> &sm =
+      *reinterpret_cast<DkvSmem<HALVES> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const Tile tile = tiles[blockIdx.x];               // q_begin holds the first key of this tile
   const int head = tile.head;
-  const int row = warp * 32 + lane;
-  const int key_index = tile.q_begin + row;
   const int q_first = causal ? tile.q_begin : tile.seq_begin;
-  const int n_blocks = (tile.seq_end - q_first + kTile - 1) / kTile;
+  const int n_blocks = (tile.seq_end - q_first + kQBlock - 1) / kQBlock;
   const float scale_log2 = scale * kLog2e;
 
   if (tid == 0) {
     sm.abort_flag = 0;
     mbar_init(&sm.fixed_full, 1);
-    mbar_init(&sm.stream_full, 1);
-    mbar_init(&sm.s_done, 1);
-    mbar_init(&sm.acc_done, 1);
+    for (int i = 0; i < kDkvStages; ++i) mbar_init(&sm.stream_full[i], 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.s_done[i], 1);
+      mbar_init(&sm.s_free[i], kDkvComputeThreads / 32);   // one arrival per compute warp
+      mbar_init(&sm.pd_ready[i], kDkvComputeThreads / 32);
+      mbar_init(&sm.g_done[i], 1);
+    }
     mbar_fence_init();
   }
   __syncthreads();
@@ -409,108 +414,137 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_st = sm.tmem_base, tmem_dpt = sm.tmem_base + 128, tmem_dv = sm.tmem_base + 256,
                  tmem_dk = sm.tmem_base + 384;
-  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
   volatile int *abort_flag = &sm.abort_flag;
 
-  if (tid == 0) {
-    mbar_arrive_expect_tx(&sm.fixed_full, 2 * HALVES * kBoxBytes);
+  if (warp == kDkvComputeThreads / 32) {
+    if (lane == 0 && n_blocks > 0) {
+      constexpr uint32_t idesc_s = instr_desc(kFmtBF16, kFmtBF16, kTile, kQBlock, 0, 0);
+      constexpr uint32_t idesc_g = instr_desc(kFmtBF16, kFmtBF16, kTile, D, 0, 1);
+      auto load_stream = [&](int block) {
+        const int st = block % kDkvStages, q0 = q_first + block * kQBlock;
+        mbar_arrive_expect_tx(&sm.stream_full[st], 2 * HALVES * kQBoxBytes);
 #pragma unroll
-    for (int j = 0; j < HALVES; ++j) {
-      tma_load_2d(sm.fixed_a[j], &map_k, head * D + 64 * j, tile.q_begin, &sm.fixed_full);
-      tma_load_2d(sm.fixed_b[j], &map_v, head * D + 64 * j, tile.q_begin, &sm.fixed_full);
-    }
-  }
-  constexpr uint32_t idesc_s = instr_desc(kFmtBF16, kFmtBF16, kTile, kTile, 0, 0);
-  constexpr uint32_t idesc_g = instr_desc(kFmtBF16, kFmtBF16, kTile, D, 0, 1);
-  mbar_wait(&sm.fixed_full, 0, abort_flag, error, 21);
-
-  for (int qb = 0; qb < n_blocks; ++qb) {
-    const int q0 = q_first + qb * kTile;
-    if (tid == 0) {                                   // the previous block's readers finished (acc_done)
-      mbar_arrive_expect_tx(&sm.stream_full, 2 * HALVES * kBoxBytes);
+        for (int j = 0; j < HALVES; ++j) {
+          tma_load_2d(sm.q[st][j], &map_q, head * D + 64 * j, q0, &sm.stream_full[st]);
+          tma_load_2d(sm.d_o[st][j], &map_do, head * D + 64 * j, q0, &sm.stream_full[st]);
+        }
+      };
+      auto issue_scores_of = [&](int block) {
+        const int st = block & 1, stage = block % kDkvStages;
+        mbar_wait(&sm.stream_full[stage], (uint32_t)((block / kDkvStages) & 1), abort_flag, error, 22);
+        if (block >= 2)       // the compute warps have read this pair of score buffers
+          mbar_wait(&sm.s_free[st], (uint32_t)(((block >> 1) - 1) & 1), abort_flag, error, 25);
+        tc_fence_after_sync();
+        issue_scores<HALVES, kBoxBytes, kQBoxBytes>(tmem_st + st * kQBlock, sm.k, sm.q[stage], idesc_s);     // S^T  = K Q^T
+        issue_scores<HALVES, kBoxBytes, kQBoxBytes>(tmem_dpt + st * kQBlock, sm.v, sm.d_o[stage], idesc_s);  // dP^T = V dO^T
+        mma_commit(&sm.s_done[st]);
+      };
+      mbar_arrive_expect_tx(&sm.fixed_full, 2 * HALVES * kBoxBytes);
 #pragma unroll
       for (int j = 0; j < HALVES; ++j) {
-        tma_load_2d(sm.stream_a[j], &map_q, head * D + 64 * j, q0, &sm.stream_full);
-        tma_load_2d(sm.stream_b[j], &map_do, head * D + 64 * j, q0, &sm.stream_full);
+        tma_load_2d(sm.k[j], &map_k, head * D + 64 * j, tile.q_begin, &sm.fixed_full);
+        tma_load_2d(sm.v[j], &map_v, head * D + 64 * j, tile.q_begin, &sm.fixed_full);
+      }
+      for (int blk = 0; blk < kDkvStages && blk < n_blocks; ++blk) load_stream(blk);
+      mbar_wait(&sm.fixed_full, 0, abort_flag, error, 21);
+      issue_scores_of(0);
+      for (int qb = 0; qb < n_blocks; ++qb) {
+        const int st = qb & 1, stage = qb % kDkvStages;
+        if (qb + 1 < n_blocks) issue_scores_of(qb + 1);
+        if (qb >= 1 && qb + 2 < n_blocks) {             // the stage of block qb-1 is free once its gradient MMAs are complete
+          mbar_wait(&sm.g_done[(qb - 1) & 1], (uint32_t)(((qb - 1) >> 1) & 1), abort_flag, error, 24);
+          load_stream(qb + 2);
+        }
+        mbar_wait(&sm.pd_ready[st], (uint32_t)((qb >> 1) & 1), abort_flag, error, 26);
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k16 = 0; k16 < kQBlock / 16; ++k16) {   // 16 queries per MMA; dO and Q consumed MN-major as loaded
+          const uint32_t boff = k16 * 16 * 128;
+          mma_f16(tmem_dv, smem_desc_k_major_sw128(smem_u32(sm.p[st]) + k16 * 32),                       // dV += P^T dO
+                  smem_desc_mn_major_sw128(smem_u32(sm.d_o[stage][0]) + boff, kQBoxBytes), idesc_g, (qb | k16) != 0);
+          mma_f16(tmem_dk, smem_desc_k_major_sw128(smem_u32(sm.ds[st]) + k16 * 32),                      // dK += dS^T Q
+                  smem_desc_mn_major_sw128(smem_u32(sm.q[stage][0]) + boff, kQBoxBytes), idesc_g, (qb | k16) != 0);
+        }
+        mma_commit(&sm.g_done[st]);
       }
     }
-    {                                                 // per-query softmax statistics of this block
-      const int qi = q0 + tid;
-      const bool ok = qi < tile.seq_end;
-      sm.lse2[tid] = ok ? lse[(int64_t)qi * H + head] * kLog2e : INFINITY;
-      sm.delta[tid] = ok ? delta[(int64_t)qi * H + head] : 0.0f;
-    }
-    mbar_wait(&sm.stream_full, (uint32_t)(qb & 1), abort_flag, error, 22);
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after_sync();
-      issue_scores<HALVES, kBoxBytes, kBoxBytes>(tmem_st, sm.fixed_a, sm.stream_a, idesc_s);    // S^T  = K Q^T
-      issue_scores<HALVES, kBoxBytes, kBoxBytes>(tmem_dpt, sm.fixed_b, sm.stream_b, idesc_s);   // dP^T = V dO^T
-      mma_commit(&sm.s_done);
-    }
-    mbar_wait(&sm.s_done, (uint32_t)(qb & 1), abort_flag, error, 23);
-    tc_fence_after_sync();
+  } else {
+    const int quad = warp & 3, h = warp >> 2;          // tensor-memory lane quadrant, half of the block's queries
+    const int row = quad * 32 + lane;
+    const int key_index = tile.q_begin + row;
     const bool key_ok = key_index < tile.seq_end;
-#pragma unroll 1
-    for (int c0 = 0; c0 < kTile; c0 += 32) {
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    // per-query softmax statistics: threads 0-63 fetch those of block qb+1 while block qb is computed
+    auto fetch_stats = [&](int block, float &l2, float &dl) {
+      const int qi = q_first + block * kQBlock + tid;
+      const bool ok = qi < tile.seq_end;
+      l2 = ok ? lse[(int64_t)qi * H + head] * kLog2e : INFINITY;
+      dl = ok ? delta[(int64_t)qi * H + head] : 0.0f;
+    };
+    if (tid < kQBlock && n_blocks > 0) fetch_stats(0, sm.lse2[0][tid], sm.delta[0][tid]);
+    for (int qb = 0; qb < n_blocks; ++qb) {
+      const int st = qb & 1;
+      const int q0 = q_first + qb * kQBlock;
+      float next_lse2 = INFINITY, next_delta = 0.0f;
+      const bool prefetch = tid < kQBlock && qb + 1 < n_blocks;
+      if (prefetch) fetch_stats(qb + 1, next_lse2, next_delta);
+      asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight compute warps only; their control flow never diverges
+      mbar_wait(&sm.s_done[st], (uint32_t)((qb >> 1) & 1), abort_flag, error, 23);
+      tc_fence_after_sync();
       uint32_t rs[32], rp[32];
-      tmem_ld_32x32(tmem_st + lane_base + c0, rs);
-      tmem_ld_32x32(tmem_dpt + lane_base + c0, rp);
+      tmem_ld_32x32(tmem_st + st * kQBlock + lane_base + 32 * h, rs);
+      tmem_ld_32x32(tmem_dpt + st * kQBlock + lane_base + 32 * h, rp);
       tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive_warp(&sm.s_free[st]);                 // the score buffers may be overwritten
+      if (qb >= 2)                                      // the gradient MMAs of block qb-2 have read these P^T / dS^T tiles
+        mbar_wait(&sm.g_done[st], (uint32_t)(((qb >> 1) - 1) & 1), abort_flag, error, 27);
       float p[32], ds[32];
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
-        const int qi = q0 + c0 + c;
+        const int qi = q0 + 32 * h + c;
         const bool valid = key_ok && (!causal || key_index <= qi);
-        p[c] = valid ? fast_exp2(__uint_as_float(rs[c]) * scale_log2 - sm.lse2[c0 + c]) : 0.0f;
-        ds[c] = p[c] * (__uint_as_float(rp[c]) - sm.delta[c0 + c]);
+        p[c] = valid ? fast_exp2(fmaf(__uint_as_float(rs[c]), scale_log2, -sm.lse2[st][32 * h + c])) : 0.0f;
+        ds[c] = p[c] * (__uint_as_float(rp[c]) - sm.delta[st][32 * h + c]);
       }
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
-        const int chunk = ((c0 & 63) >> 3) + g;
-        store_swizzled_chunk(sm.p[c0 >> 6], row, chunk,
+        store_swizzled_chunk(sm.p[st], row, 4 * h + g,
                              make_uint4(pack_bf16(p[8 * g], p[8 * g + 1]), pack_bf16(p[8 * g + 2], p[8 * g + 3]),
                                         pack_bf16(p[8 * g + 4], p[8 * g + 5]), pack_bf16(p[8 * g + 6], p[8 * g + 7])));
-        store_swizzled_chunk(sm.ds[c0 >> 6], row, chunk,
+        store_swizzled_chunk(sm.ds[st], row, 4 * h + g,
                              make_uint4(pack_bf16(ds[8 * g], ds[8 * g + 1]), pack_bf16(ds[8 * g + 2], ds[8 * g + 3]),
                                         pack_bf16(ds[8 * g + 4], ds[8 * g + 5]), pack_bf16(ds[8 * g + 6], ds[8 * g + 7])));
       }
+      fence_proxy_async_smem();
+      mbar_arrive_warp(&sm.pd_ready[st]);
+      if (prefetch) {       // every compute warp is past this iteration's barrier, so block qb-1's statistics are dead
+        sm.lse2[st ^ 1][tid] = next_lse2;
+        sm.delta[st ^ 1][tid] = next_delta;
+      }
     }
-    fence_proxy_async_smem();
-    tc_fence_before_sync();
-    __syncthreads();
-    if (tid == 0) {
+    if (n_blocks > 0) {                                 // the last commit covers every MMA issued before it
+      mbar_wait(&sm.g_done[(n_blocks - 1) & 1], (uint32_t)(((n_blocks - 1) >> 1) & 1), abort_flag, error, 28);
       tc_fence_after_sync();
-      issue_gradient(tmem_dv, sm.p, sm.stream_b[0], idesc_g, qb != 0);    // dV += P^T dO
-      issue_gradient(tmem_dk, sm.ds, sm.stream_a[0], idesc_g, qb != 0);   // dK += dS^T Q
-      mma_commit(&sm.acc_done);
     }
-    mbar_wait(&sm.acc_done, (uint32_t)(qb & 1), abort_flag, error, 24);
-    tc_fence_after_sync();
-  }
-
-  const bool store = key_index < tile.seq_end && !*abort_flag;
-  __nv_bfloat16 *dst_v = dv + ((int64_t)key_index * H + head) * D;
-  __nv_bfloat16 *dst_k = dk + ((int64_t)key_index * H + head) * D;
+    // warps 0-3 write dV, warps 4-7 write dK (scaled)
+    const bool store = key_ok && !*abort_flag && n_blocks > 0;
+    __nv_bfloat16 *dst = (h == 0 ? dv : dk) + ((int64_t)key_index * H + head) * D;
+    const float factor = h == 0 ? 1.0f : scale;
+    const uint32_t src = (h == 0 ? tmem_dv : tmem_dk) + lane_base;
 #pragma unroll 1
-  for (int c0 = 0; c0 < D; c0 += 32) {
-    uint32_t rv[32], rk[32];
-    tmem_ld_32x32(tmem_dv + lane_base + c0, rv);
-    tmem_ld_32x32(tmem_dk + lane_base + c0, rk);
-    tmem_ld_wait();
-    if (store) {
+    for (int c0 = 0; c0 < D; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld_32x32(src + c0, r);
+      tmem_ld_wait();
+      if (store) {
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        *reinterpret_cast<uint4 *>(dst_v + c0 + 8 * g) = make_uint4(
-            pack_bf16(__uint_as_float(rv[8 * g]), __uint_as_float(rv[8 * g + 1])),
-            pack_bf16(__uint_as_float(rv[8 * g + 2]), __uint_as_float(rv[8 * g + 3])),
-            pack_bf16(__uint_as_float(rv[8 * g + 4]), __uint_as_float(rv[8 * g + 5])),
-            pack_bf16(__uint_as_float(rv[8 * g + 6]), __uint_as_float(rv[8 * g + 7])));
-        *reinterpret_cast<uint4 *>(dst_k + c0 + 8 * g) = make_uint4(
-            pack_bf16(__uint_as_float(rk[8 * g]) * scale, __uint_as_float(rk[8 * g + 1]) * scale),
-            pack_bf16(__uint_as_float(rk[8 * g + 2]) * scale, __uint_as_float(rk[8 * g + 3]) * scale),
-            pack_bf16(__uint_as_float(rk[8 * g + 4]) * scale, __uint_as_float(rk[8 * g + 5]) * scale),
-            pack_bf16(__uint_as_float(rk[8 * g + 6]) * scale, __uint_as_float(rk[8 * g + 7]) * scale));
+        for (int g = 0; g < 4; ++g)
+          *reinterpret_cast<uint4 *>(dst + c0 + 8 * g) = make_uint4(
+              pack_bf16(__uint_as_float(r[8 * g]) * factor, __uint_as_float(r[8 * g + 1]) * factor),
+              pack_bf16(__uint_as_float(r[8 * g + 2]) * factor, __uint_as_float(r[8 * g + 3]) * factor),
+              pack_bf16(__uint_as_float(r[8 * g + 4]) * factor, __uint_as_float(r[8 * g + 5]) * factor),
+              pack_bf16(__uint_as_float(r[8 * g + 6]) * factor, __uint_as_float(r[8 * g + 7]) * factor));
       }
     }
   }
@@ -734,9 +768,11 @@ extern "C" int32_t tgb_varlen_attn_bwd(const void *q, const void *k, const void 
   if ((rc = head_map(&map_k, k, tokens, H, D))) return rc;
   if ((rc = head_map(&map_v, v, tokens, H, D))) return rc;
   if ((rc = head_map(&map_do, dout, tokens, H, D))) return rc;
-  CUtensorMap map_k64, map_v64;
+  CUtensorMap map_k64, map_v64, map_q64, map_do64;
   if ((rc = head_map(&map_k64, k, tokens, H, D, kKeyBlock))) return rc;
   if ((rc = head_map(&map_v64, v, tokens, H, D, kKeyBlock))) return rc;
+  if ((rc = head_map(&map_q64, q, tokens, H, D, kQBlock))) return rc;
+  if ((rc = head_map(&map_do64, dout, tokens, H, D, kQBlock))) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int64_t rows = tokens * H;
   k_attn_delta<<<(unsigned)ceil_div(rows * 32, 256), 256, 0, st>>>((const __nv_bfloat16 *)out,
@@ -746,7 +782,7 @@ extern "C" int32_t tgb_varlen_attn_bwd(const void *q, const void *k, const void 
   const unsigned grid = (unsigned)n_tiles;
 #define TGB_BWD(HV)                                                                                         \
   {                                                                                                         \
-    const size_t smem = sizeof(BwdSmem<HV>) + 1024;                                                         \
+    const size_t smem = sizeof(DkvSmem<HV>) + 1024;                                                         \
     const size_t smem_dq = sizeof(DqSmem<HV>);                                                              \
     static bool configured = false;                                                                         \
     if (!configured) {                                                                                      \
@@ -754,7 +790,7 @@ extern "C" int32_t tgb_varlen_attn_bwd(const void *q, const void *k, const void 
       TGB_CUDA(cudaFuncSetAttribute(k_attn_bwd_dq<HV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq)); \
       configured = true;                                                                                    \
     }                                                                                                       \
-    k_attn_bwd_dkv<HV><<<grid, 128, smem, st>>>(map_q, map_k, map_v, map_do, (const Tile *)key_tiles, H, scale, \
+    k_attn_bwd_dkv<HV><<<grid, kDkvThreads, smem, st>>>(map_q64, map_k, map_v, map_do64, (const Tile *)key_tiles, H, scale, \
                                                 causal, (const float *)lse, (const float *)delta,           \
                                                 (__nv_bfloat16 *)dk, (__nv_bfloat16 *)dv, (int *)error_flag); \
     TGB_LAUNCHED();                                                                                         \

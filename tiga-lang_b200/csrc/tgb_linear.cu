@@ -279,12 +279,12 @@ k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__res
     sm.abort_flag = 0;
     for (int i = 0; i < kWtRing; ++i) mbar_init(&sm.raw_full[i], 1);
     for (int i = 0; i < kWtOps; ++i) {
-      mbar_init(&sm.op_full[i], 128);
+      mbar_init(&sm.op_full[i], 4);      // one arrival per split warp
       mbar_init(&sm.mma_done[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sm.acc_full[i], 1);
-      mbar_init(&sm.acc_empty[i], 128);
+      mbar_init(&sm.acc_empty[i], 4);    // one arrival per epilogue warp
     }
     mbar_fence_init();
     tma_prefetch_descriptor(&map_a);
@@ -348,7 +348,7 @@ k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__res
       if (use_s >= 1) mbar_wait(&sm.mma_done[s], (use_s - 1) & 1, abort_flag, error, 2);   // operand slot free
       split_chunk_from(sm.raw[r], sm.a_hi[s], sm.a_lo[s], kChunkBytes, tid, 128);
       fence_proxy_async_smem();
-      mbar_arrive(&sm.op_full[s]);                    // 128 arrivals: operands written, raw[r] read
+      mbar_arrive_warp(&sm.op_full[s]);               // operands written, raw[r] read
     }
   } else if (warp == 8) {
     // ---- issue warp: one thread refills the TMA ring and issues the MMAs; issuing can stall on the
@@ -409,7 +409,7 @@ k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__res
           if (live && row0 + c0 + c < M) __stcs(dst + (int64_t)c * N, __uint_as_float(r[c]));
       }
       tc_fence_before_sync();
-      mbar_arrive(&sm.acc_empty[b]);                    // 128 arrivals complete the phase
+      mbar_arrive_warp(&sm.acc_empty[b]);
     }
   }
   tc_fence_before_sync();
@@ -460,7 +460,7 @@ k_linear_dw_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_const
     sm.abort_flag = 0;
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sm.full[i], 1);
-      mbar_init(&sm.op_full[i], kDwSplitWarps * 32);
+      mbar_init(&sm.op_full[i], kDwSplitWarps);   // one arrival per split warp
       mbar_init(&sm.mma_done[i], 1);
     }
     mbar_init(&sm.acc_done, 1);
@@ -496,7 +496,7 @@ k_linear_dw_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_const
       if (use >= 1) mbar_wait(&sm.mma_done[s], (use - 1) & 1, abort_flag, error, 51);   // operand slot free
       split_chunk_from(sm.raw[s][0], sm.hi[s][0], sm.lo[s][0], kBoxes * kDwBoxBytes, tid, kDwSplitWarps * 32);
       fence_proxy_async_smem();
-      mbar_arrive(&sm.op_full[s]);                    // operands written, raw[s] read
+      mbar_arrive_warp(&sm.op_full[s]);               // operands written, raw[s] read
     }
   } else if (lane == 0) {
     // ---- issue thread: refills the TMA slots and issues the MMAs, nothing else ----------------

@@ -40,6 +40,15 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// One arrival per warp: every lane has finished its part (and issued whatever
+// proxy / tensor-memory fence its writes need) before the warp synchronises,
+// then lane 0 arrives for all of them.  A barrier that 128 or 256 threads
+// arrive on one by one serialises that many shared-memory atomics per phase.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t *bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
