@@ -9,7 +9,9 @@ edges, symmetrised and de-duplicated, CSR by destination; edge weight
 1/sqrt(deg_i * deg_j); float32 features [N, 128]; sum reducer followed by a
 dense 128x128 float32 linear.  One step = forward plus the backward of
 out.sum() with respect to the features, the edge weights and the linear
-weights.  Metric: directed edges per second for forward + backward.
+weights; the cotangent of out.sum() is a resident matrix of ones handed to
+autograd, in this arm and in the CPU arm alike.  Metric: directed edges per
+second for forward + backward.
 
 The JSON line carries, besides the base fields:
   roofline     achieved algorithmic GB/s of the dominant gather kernel, timed
@@ -353,10 +355,12 @@ def run_native(args):
 
     instrument(ops, timings, recording)
 
+    ones = torch.ones((N, lin.shape[1]), dtype=torch.float32, device=device)   # d(out.sum()) / d(out)
+
     def step(xs, ws, ls):
         agg = layer(graph=graph, src={"x": xs}, dst={}, edge={"weight": ws})
         out = ops.dense_linear(agg, ls)
-        return torch.autograd.grad(out.sum(), (xs, ws, ls))
+        return torch.autograd.grad(out, (xs, ws, ls), ones)
 
     plan_start = time.perf_counter()
     graph.native_plan(transpose=True)
@@ -371,6 +375,12 @@ def run_native(args):
             v.clear()
         sampler = ClockSampler(local)
         sampler.start()
+        # nvidia-smi needs a moment to come up: keep the GPU under the same load, untimed, until its
+        # first sample is in (at most 1.5 s), so that the record covers clocks under load
+        waited = time.perf_counter()
+        while sampler.process is not None and not sampler.lines and time.perf_counter() - waited < 1.5:
+            step(x, weight, lin)
+            torch.cuda.synchronize()
         launches_before = _native.launch_count()
         recording["on"] = True
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -512,11 +522,13 @@ def run_native_multi(args, rank, world, device):
     recording = {"on": False}
     instrument(ops, timings, recording)
 
+    ones = torch.ones((e - b, lin.shape[1]), dtype=torch.float32, device=device)   # d(out.sum()) / d(out)
+
     def step(xs, ws, ls):
         with runtime:
             agg = layer(graph=graph, src={"x": xs}, dst={}, edge={"weight": ws})
         out = ops.dense_linear(agg, ls)
-        dx, dw, dl = torch.autograd.grad(out.sum(), (xs, ws, ls))
+        dx, dw, dl = torch.autograd.grad(out, (xs, ws, ls), ones)
         dist.all_reduce(dl)
         return dx, dw, dl
 
