@@ -133,7 +133,7 @@ class ClockSampler:
 
 # --------------------------------------------------------------------------- GPU arm
 def build_inputs(args, device):
-    from tiga import synthetic as syn
+    from baseline import synthetic as syn
 
     row_ptr, col = syn.rmat_csr(args.scale, args.edge_factor, seed=args.seed, symmetrize=True, device=device)
     n = row_ptr.numel() - 1
@@ -182,7 +182,7 @@ def run_gat(args, device):
     bf16 features [N, 8, 32], GAT logit, online-softmax reducer, forward + backward."""
     import tiga as tg
     from tiga import _native, ops
-    from tiga import synthetic as syn
+    from baseline import synthetic as syn
 
     scale = args.scale + 1 if args.scale == 20 else args.scale
     row_ptr, col = syn.rmat_csr(scale, args.edge_factor, seed=args.seed, symmetrize=False, device=device)
@@ -232,7 +232,7 @@ def run_attention(args, device):
     head width 128, bf16, causal inside each sequence, forward + backward."""
     import tiga as tg
     from tiga import _native, ops
-    from tiga import synthetic as syn
+    from baseline import synthetic as syn
 
     gen = torch.Generator().manual_seed(20260821)
     lengths = torch.randint(512, 8193, (32,), generator=gen)
@@ -484,7 +484,7 @@ def run_native_multi(args, rank, world, device):
 
     import tiga as tg
     from tiga import _native, ops
-    from tiga import synthetic as syn
+    from baseline import synthetic as syn
     from tiga.distributed.runtime import DistributedRuntime, NCCLTransport, shard_plan_for
 
     _native.lib()
@@ -739,7 +739,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from tiga import synthetic as syn
+    from baseline import synthetic as syn
 
     row_ptr, col = syn.rmat_csr(args.scale, args.edge_factor, seed=args.seed, symmetrize=True, device="cpu")
     n = row_ptr.numel() - 1

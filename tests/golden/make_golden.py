@@ -47,8 +47,14 @@ def _graphs(gen):
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", default=os.environ.get("TIGA_REFERENCE"),
+                        help="root of the unmodified reference checkout (or set TIGA_REFERENCE)")
     args = parser.parse_args()
+    if not args.reference:
+        sibling = os.path.join(os.path.dirname(ROOT), "reference")
+        if not os.path.isdir(sibling):
+            raise SystemExit("pass --reference /path/to/TIGA-lang (or set TIGA_REFERENCE)")
+        args.reference = sibling
     runtime = os.path.join(ROOT, "oracle", "_ref", "libtiga_runtime.so")
     if not os.path.exists(runtime):
         raise SystemExit("build oracle/_ref first: make -C oracle")

@@ -125,7 +125,43 @@ def test_capture_recognisers():
 
     assert cap.reducer_algebra(UserMax()) == "max"
     assert cap.reducer_algebra(tg.sum()) == "sum"
-    assert cap.reducer_algebra(tg.mean()) is None
+    assert cap.reducer_algebra(tg.prod()) is None
+    # tuple states whose components add independently, lifts that are monomials of the message
+    mean = cap.capture_reducer(tg.mean())
+    assert (mean.kind, mean.components, mean.scalar) == ("additive", ((1.0, 1), (1.0, 0)), False)
+
+    class Moments(tg.Reducer):
+        associative = commutative = True
+
+        def identity(self):
+            return 0.0, 0.0, 0.0
+
+        def lift(self, message):
+            return message, 0.5 * message * message, 1.0
+
+        def combine(self, left, right):
+            return left[0] + right[0], right[1] + left[1], left[2] + right[2]
+
+        def finalize(self, state):
+            return state[1] / state[2]
+
+    moments = cap.capture_reducer(Moments())
+    assert (moments.kind, moments.components) == ("additive", ((1.0, 1), (0.5, 2), (1.0, 0)))
+
+    class Crossed(Moments):          # component 0 mixes in component 1: not independent
+        def combine(self, left, right):
+            return left[0] + right[1], left[1] + right[1], left[2] + right[2]
+
+    assert cap.capture_reducer(Crossed()) is None
+
+    class FieldSoftmax(tg.MessagePassing):
+        reducer = tg.online_softmax()
+
+        def edge(self, src, dst, edge):
+            return self.reducer(edge.score, src.value)
+
+    assert cap.recognize_field_softmax(cap.capture_edge(FieldSoftmax().edge, {})) == \
+        cap.FieldSoftmaxPattern("score", "value")
 
 
 def test_graph_constructors_match_reference(golden):
@@ -185,7 +221,7 @@ def test_partition_model_matches_reference(golden):
 
 
 def test_synthetic_rmat_is_deterministic():
-    from tiga import synthetic as syn
+    from baseline import synthetic as syn
 
     a = syn.rmat_csr(10, 8, seed=7)
     b = syn.rmat_csr(10, 8, seed=7)

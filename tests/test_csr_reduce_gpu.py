@@ -9,7 +9,7 @@ import torch
 import tiga as tg
 from conftest import assert_sum_close
 from tiga import ops
-from tiga import synthetic as syn
+from baseline import synthetic as syn
 
 pytestmark = pytest.mark.gpu
 

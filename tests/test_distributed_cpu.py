@@ -79,7 +79,7 @@ def _worker(rank, world, port, balance, result_dir):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         import tiga as tg
-        from tiga import synthetic as syn
+        from baseline import synthetic as syn
         from tiga.distributed import model
         from tiga.distributed.runtime import DistributedRuntime, ProcessGroupTransport, shard_plan_for
 
@@ -137,7 +137,7 @@ def test_sharded_weighted_sum_matches_single_process(tmp_path, oracle, world, ba
     mp.start_processes(_worker, args=(world, port, balance, str(tmp_path)), nprocs=world, join=True,
                        start_method="spawn")
     sys.path.insert(0, os.path.join(ROOT, "tiga-lang_b200"))
-    from tiga import synthetic as syn
+    from baseline import synthetic as syn
 
     row_ptr, col = syn.rmat_csr(7, 6, seed=13)
     n, F = row_ptr.numel() - 1, 8
@@ -173,7 +173,7 @@ def _failing_worker(rank, world, port, result_dir):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
     import tiga as tg
-    from tiga import synthetic as syn
+    from baseline import synthetic as syn
     from tiga.distributed.runtime import DistributedRuntime, ProcessGroupTransport, halo_weighted_sum, shard_plan_for
 
     row_ptr, col = syn.rmat_csr(7, 6, seed=13)

@@ -31,7 +31,7 @@ def _worker(rank, world, port, result_dir):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
     try:
         import tiga as tg
-        from tiga import synthetic as syn
+        from baseline import synthetic as syn
         from tiga.distributed.runtime import DistributedRuntime, NCCLTransport, shard_plan_for
 
         class WeightedSum(tg.MessagePassing):
@@ -69,7 +69,7 @@ def test_two_gpu_halo_matches_oracle(tmp_path, oracle):
     world = 2
     mp.start_processes(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True,
                        start_method="spawn")
-    from tiga import synthetic as syn
+    from baseline import synthetic as syn
 
     row_ptr, col = syn.rmat_csr(11, 12, seed=13)
     n, F = row_ptr.numel() - 1, 64

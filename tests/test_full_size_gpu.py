@@ -8,7 +8,7 @@ import torch
 
 import tiga as tg
 from tiga import ops
-from tiga import synthetic as syn
+from baseline import synthetic as syn
 
 pytestmark = pytest.mark.gpu
 

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import tiga as tg
-from tiga import synthetic as syn
+from baseline import synthetic as syn
 
 pytestmark = pytest.mark.gpu
 

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 import tiga as tg
-from tiga import synthetic as syn
+from baseline import synthetic as syn
 from tiga.library import register_message_passing
 
 pytestmark = pytest.mark.gpu

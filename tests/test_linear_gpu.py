@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from tiga import ops
-from tiga import synthetic as syn
+from baseline import synthetic as syn
 
 pytestmark = pytest.mark.gpu
 

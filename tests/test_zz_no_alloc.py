@@ -17,7 +17,7 @@ import torch
 
 import tiga as tg
 from tiga import _native, ops
-from tiga import synthetic as syn
+from baseline import synthetic as syn
 
 pytestmark = pytest.mark.gpu
 

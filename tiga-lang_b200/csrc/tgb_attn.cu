@@ -732,20 +732,14 @@ extern "C" int32_t tgb_varlen_attn_fwd(const void *q, const void *k, const void 
   const float scale_log2 = scale * kLog2e;
   if (D == 128) {
     const size_t smem = sizeof(FwdSmem<2>);
-    static bool configured = false;
-    if (!configured) {
-      TGB_CUDA(cudaFuncSetAttribute(k_attn_fwd<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      configured = true;
-    }
+    // the attribute belongs to the current device's context, so it is set on every call (cheap)
+    TGB_CUDA(cudaFuncSetAttribute(k_attn_fwd<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k_attn_fwd<2><<<grid, kFwdThreads, smem, st>>>(map_q, map_k, map_v, (const Tile *)tiles, H, scale_log2, causal,
                                            (__nv_bfloat16 *)out, (float *)lse, (int *)error_flag);
   } else {
     const size_t smem = sizeof(FwdSmem<1>);
-    static bool configured = false;
-    if (!configured) {
-      TGB_CUDA(cudaFuncSetAttribute(k_attn_fwd<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      configured = true;
-    }
+    // the attribute belongs to the current device's context, so it is set on every call (cheap)
+    TGB_CUDA(cudaFuncSetAttribute(k_attn_fwd<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k_attn_fwd<1><<<grid, kFwdThreads, smem, st>>>(map_q, map_k, map_v, (const Tile *)tiles, H, scale_log2, causal,
                                            (__nv_bfloat16 *)out, (float *)lse, (int *)error_flag);
   }
@@ -784,12 +778,9 @@ extern "C" int32_t tgb_varlen_attn_bwd(const void *q, const void *k, const void 
   {                                                                                                         \
     const size_t smem = sizeof(DkvSmem<HV>) + 1024;                                                         \
     const size_t smem_dq = sizeof(DqSmem<HV>);                                                              \
-    static bool configured = false;                                                                         \
-    if (!configured) {                                                                                      \
-      TGB_CUDA(cudaFuncSetAttribute(k_attn_bwd_dkv<HV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-      TGB_CUDA(cudaFuncSetAttribute(k_attn_bwd_dq<HV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq)); \
-      configured = true;                                                                                    \
-    }                                                                                                       \
+    /* per-device attribute: set on every call */                                                          \
+    TGB_CUDA(cudaFuncSetAttribute(k_attn_bwd_dkv<HV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    TGB_CUDA(cudaFuncSetAttribute(k_attn_bwd_dq<HV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq)); \
     k_attn_bwd_dkv<HV><<<grid, kDkvThreads, smem, st>>>(map_q64, map_k, map_v, map_do64, (const Tile *)key_tiles, H, scale, \
                                                 causal, (const float *)lse, (const float *)delta,           \
                                                 (__nv_bfloat16 *)dk, (__nv_bfloat16 *)dv, (int *)error_flag); \

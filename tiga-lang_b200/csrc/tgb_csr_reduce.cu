@@ -569,6 +569,10 @@ int32_t check_common(const tgb_csr_plan *plan, int32_t reducer, int64_t F,
     TGB_FAIL(TGB_STATUS_UNSUPPORTED, "csr reduce kernels take float32 features");
   if (reducer == TGB_REDUCER_MAX && plan->num_edges >= ((int64_t)1 << 31))
     TGB_FAIL(TGB_STATUS_UNSUPPORTED, "max reducer needs fewer than 2^31 edges");
+  // winners are stored as CSR positions; an edge map renames the transposed side's edge ids, so the
+  // winner comparison of the backward would never match
+  if (reducer == TGB_REDUCER_MAX && plan->fwd.eid)
+    TGB_FAIL(TGB_STATUS_UNSUPPORTED, "the max reducer does not take a plan with an edge map");
   return TGB_STATUS_OK;
 }
 
@@ -632,8 +636,6 @@ int32_t tgb_csr_reduce_fwd(const tgb_csr_plan *plan, int32_t reducer,
     s = scalar_shape(F);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (side.eid && w) {   // weights are addressed through the plan's edge map
-    if (reducer == TGB_REDUCER_MAX)
-      TGB_FAIL(TGB_STATUS_UNSUPPORTED, "the max reducer does not take an edge map");
     return plan->index_bits == 32 ? launch_gather<int32_t, int32_t, kSum, true, true, false>(a, s, st)
                                   : launch_gather<int64_t, int64_t, kSum, true, true, false>(a, s, st);
   }
@@ -821,6 +823,9 @@ extern "C" int32_t tgb_csr_wsum_fwd_noalloc(const tgb_csr_plan *plan, const void
   a.identity = identity;
   Shape s = pick_shape(F, x, out);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (side.eid && w)   // the plan carries an edge map: weights are read as w[map[e]], as the regular entry does
+    return plan->index_bits == 32 ? launch_gather<int32_t, int32_t, kSum, true, true, false>(a, s, st)
+                                  : launch_gather<int64_t, int64_t, kSum, true, true, false>(a, s, st);
   if (plan->index_bits == 32)
     return w ? launch_gather<int32_t, int32_t, kSum, true, false, false>(a, s, st)
              : launch_gather<int32_t, int32_t, kSum, false, false, false>(a, s, st);

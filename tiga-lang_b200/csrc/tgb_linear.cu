@@ -598,26 +598,17 @@ extern "C" int32_t tgb_linear_f32(const void *a, const void *b_t, void *out, int
   if (N == 128 && ((uintptr_t)b_t & 15u) == 0) {
     // resident matrix in tensor memory, rows of `a` through a six-slot TMA ring
     const size_t smem_wt = sizeof(LinearWtSmem) + 1024;
-    static bool configured = false;
-    if (!configured) {
-      TGB_CUDA(cudaFuncSetAttribute(k_linear_wt_3xtf32, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_wt));
-      configured = true;
-    }
+    // the attribute belongs to the current device's context, so it is set on every call (cheap)
+    TGB_CUDA(cudaFuncSetAttribute(k_linear_wt_3xtf32, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_wt));
     k_linear_wt_3xtf32<<<grid, kWtThreads, smem_wt, st>>>(map_a, (const float *)b_t, (float *)out, M, K / 32,
                                                          (int *)error_flag);
   } else if (N == 128) {
-    static bool configured = false;
-    if (!configured) {
-      TGB_CUDA(cudaFuncSetAttribute(k_linear_3xtf32<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      configured = true;
-    }
+    // the attribute belongs to the current device's context, so it is set on every call (cheap)
+    TGB_CUDA(cudaFuncSetAttribute(k_linear_3xtf32<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k_linear_3xtf32<128><<<grid, 128, smem, st>>>(map_a, map_b, (float *)out, M, K / 32, (int *)error_flag);
   } else {
-    static bool configured = false;
-    if (!configured) {
-      TGB_CUDA(cudaFuncSetAttribute(k_linear_3xtf32<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      configured = true;
-    }
+    // the attribute belongs to the current device's context, so it is set on every call (cheap)
+    TGB_CUDA(cudaFuncSetAttribute(k_linear_3xtf32<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k_linear_3xtf32<64><<<grid, 128, smem, st>>>(map_a, map_b, (float *)out, M, K / 32, (int *)error_flag);
   }
   TGB_LAUNCHED();
@@ -655,18 +646,12 @@ extern "C" int32_t tgb_linear_dw_f32(const void *a, const void *dout, void *dw, 
   const size_t smem = sizeof(DwSmem) + 1024;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (N == 128) {
-    static bool configured = false;
-    if (!configured) {
-      TGB_CUDA(cudaFuncSetAttribute(k_linear_dw_3xtf32<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      configured = true;
-    }
+    // the attribute belongs to the current device's context, so it is set on every call (cheap)
+    TGB_CUDA(cudaFuncSetAttribute(k_linear_dw_3xtf32<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k_linear_dw_3xtf32<128><<<grid, kDwThreads, smem, st>>>(map_a, map_d, (float *)partial, M, (int *)error_flag);
   } else {
-    static bool configured = false;
-    if (!configured) {
-      TGB_CUDA(cudaFuncSetAttribute(k_linear_dw_3xtf32<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      configured = true;
-    }
+    // the attribute belongs to the current device's context, so it is set on every call (cheap)
+    TGB_CUDA(cudaFuncSetAttribute(k_linear_dw_3xtf32<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k_linear_dw_3xtf32<64><<<grid, kDwThreads, smem, st>>>(map_a, map_d, (float *)partial, M, (int *)error_flag);
   }
   TGB_LAUNCHED();

@@ -23,40 +23,25 @@ from __future__ import annotations
 
 import inspect
 from dataclasses import dataclass
-from typing import Any, Mapping
+from typing import Any, Callable, Mapping
 
 
-@dataclass(frozen=True, eq=False)
 class Expr:
-    op: str
-    args: tuple[Any, ...]
+    """A node of a staged expression: an operation name and its operands.
 
-    def _binary(self, op: str, other):
-        return Expr(op, (self, as_expr(other)))
+    Nodes compare and hash by identity (two structurally equal trees are different objects;
+    ``same`` compares structure).  The arithmetic operators and the three methods a staged body
+    may call (``sum``, ``maximum``, ``exp``) build new nodes; plain Python numbers met on the way
+    become ``constant`` leaves."""
 
-    def __add__(self, other):
-        return self._binary("add", other)
+    __slots__ = ("op", "args")
 
-    def __radd__(self, other):
-        return as_expr(other)._binary("add", self)
+    def __init__(self, op: str, args: tuple[Any, ...]):
+        self.op = op
+        self.args = tuple(args)
 
-    def __sub__(self, other):
-        return self._binary("sub", other)
-
-    def __rsub__(self, other):
-        return as_expr(other)._binary("sub", self)
-
-    def __mul__(self, other):
-        return self._binary("mul", other)
-
-    def __rmul__(self, other):
-        return as_expr(other)._binary("mul", self)
-
-    def __truediv__(self, other):
-        return self._binary("div", other)
-
-    def __rtruediv__(self, other):
-        return as_expr(other)._binary("div", self)
+    def __repr__(self) -> str:
+        return f"Expr({self.op!r}, {self.args!r})"
 
     def __neg__(self):
         return Expr("neg", (self,))
@@ -72,34 +57,63 @@ class Expr:
 
 
 def as_expr(value) -> Expr:
-    return value if isinstance(value, Expr) else Expr("constant", (value,))
+    """Operand of a staged operation: an Expr as it is, anything else as a constant leaf."""
+    if isinstance(value, Expr):
+        return value
+    return Expr("constant", (value,))
+
+
+def _install_arithmetic() -> None:
+    # `a <op> b` and the reflected `b <op> a` (b a plain number) for the four binary operations
+    for op, dunder in (("add", "add"), ("sub", "sub"), ("mul", "mul"), ("div", "truediv")):
+        def forward(self, other, _op=op):
+            return Expr(_op, (self, as_expr(other)))
+
+        def reflected(self, other, _op=op):
+            return Expr(_op, (as_expr(other), self))
+
+        setattr(Expr, f"__{dunder}__", forward)
+        setattr(Expr, f"__r{dunder}__", reflected)
+
+
+_install_arithmetic()
 
 
 def same(left: Any, right: Any) -> bool:
-    """Structural equality of two staged expressions."""
-    if isinstance(left, Expr) and isinstance(right, Expr):
-        return (left.op == right.op and len(left.args) == len(right.args)
-                and all(same(a, b) for a, b in zip(left.args, right.args)))
-    if isinstance(left, Expr) or isinstance(right, Expr):
+    """Structural equality of two staged expressions (leaves: identical objects, or equal
+    non-tensor values of one type)."""
+    left_is_expr, right_is_expr = isinstance(left, Expr), isinstance(right, Expr)
+    if left_is_expr != right_is_expr:
         return False
-    return left is right or (type(left) is type(right) and not hasattr(left, "shape") and left == right)
+    if left_is_expr:
+        if left.op != right.op or len(left.args) != len(right.args):
+            return False
+        return all(same(a, b) for a, b in zip(left.args, right.args))
+    if left is right:
+        return True
+    return type(left) is type(right) and not hasattr(left, "shape") and left == right
 
 
 class FieldNamespace:
+    """``src`` / ``dst`` / ``edge`` as ``edge()`` sees them while it is staged: every attribute
+    is a ``field`` leaf naming (role, attribute)."""
+
     def __init__(self, role: str) -> None:
-        self._role = role
+        object.__setattr__(self, "_role", role)
 
     def __getattr__(self, name: str) -> Expr:
-        if name.startswith("__"):
+        if name[:2] == "__":          # copy / pickle / inspect probes are not fields
             raise AttributeError(name)
         return Expr("field", (self._role, name))
 
 
 def selected_params(method, params: Mapping[str, Any]):
-    signature = inspect.signature(method)
-    accepts_rest = any(item.kind is inspect.Parameter.VAR_KEYWORD for item in signature.parameters.values())
-    return params if accepts_rest else {
-        name: value for name, value in params.items() if name in signature.parameters}
+    """The subset of ``params`` a user region takes: all of them if it declares ``**rest``,
+    otherwise those it names."""
+    declared = inspect.signature(method).parameters
+    if any(p.kind is inspect.Parameter.VAR_KEYWORD for p in declared.values()):
+        return params
+    return {name: params[name] for name in params if name in declared}
 
 
 def call_region(method, positional, params):
@@ -271,26 +285,125 @@ def recognize_dense_attention(item) -> DenseAttentionPattern | None:
                                  scale=scale)
 
 
+@dataclass(frozen=True)
+class FieldSoftmaxPattern:
+    """``self.reducer(edge.<score>, src.<value>)``: scores stored per edge, values per source."""
+
+    score_field: str
+    value_field: str
+
+
+def recognize_field_softmax(item) -> FieldSoftmaxPattern | None:
+    from .reducer import OnlineSoftmaxItem
+
+    if not isinstance(item, OnlineSoftmaxItem):
+        return None
+    score, value = _field(item.score, "edge"), _field(item.value, "src")
+    if score is None or value is None:
+        return None
+    return FieldSoftmaxPattern(score_field=score[1], value_field=value[1])
+
+
+# --------------------------------------------------------------------------- reducers
+@dataclass(frozen=True)
+class ReducerAlgebra:
+    """What staging a reducer's methods proved about it.
+
+    kind        "sum"       combine is ``left + right`` on a scalar state, lift and finalize are
+                            the identity map
+                "max"       combine is ``tg.math.maximum(left, right)``, lift / finalize identity
+                "additive"  tuple (or scalar) state whose components add independently and whose
+                            lift is, per component, ``coefficient * message ** power`` (power 0 is a
+                            count); ``finalize`` is arbitrary and runs on the finished states
+    components  (coefficient, power) per state component (additive only)
+    arity       number of state components
+    scalar      the state is a bare value, not a tuple
+    """
+
+    kind: str
+    components: tuple[tuple[float, int], ...] = ()
+    arity: int = 1
+    scalar: bool = True
+
+
+def _monomial(expr, message) -> tuple[float, int] | None:
+    """(c, p) with expr == c * message**p, or None.  Numbers are degree-0 monomials."""
+    if isinstance(expr, (int, float)) and not isinstance(expr, bool):
+        return float(expr), 0
+    if not isinstance(expr, Expr):
+        return None
+    if expr is message:
+        return 1.0, 1
+    if expr.op == "constant":
+        return _monomial(expr.args[0], message)
+    if expr.op == "neg":
+        inner = _monomial(expr.args[0], message)
+        return None if inner is None else (-inner[0], inner[1])
+    if expr.op in ("mul", "div"):
+        a, b = (_monomial(arg, message) for arg in expr.args)
+        if a is None or b is None:
+            return None
+        if expr.op == "mul":
+            return a[0] * b[0], a[1] + b[1]
+        if b[1] != 0 or b[0] == 0.0:      # only division by a non-zero number keeps a monomial
+            return None
+        return a[0] / b[0], a[1]
+    return None
+
+
+def _as_components(value) -> tuple[tuple[Any, ...], bool]:
+    if isinstance(value, (tuple, list)):
+        return tuple(value), False
+    return (value,), True
+
+
+def capture_reducer(reducer) -> ReducerAlgebra | None:
+    """Stage ``identity / lift / combine / finalize`` of a user reducer on symbols and classify
+    the algebra they form; None when nothing native matches.  The reference proves the same
+    properties on captured reducer regions before it picks a reduction tile
+    (python/tiga/compiler/reducer_capture.py:53-189, python/tiga/message_passing/core.py:84-132)."""
+    try:
+        start, scalar = _as_components(reducer.identity())
+    except Exception:
+        return None
+    arity = len(start)
+    message = Expr("reducer_message", ())
+    left = tuple(Expr("reducer_state", (0, k)) for k in range(arity))
+    right = tuple(Expr("reducer_state", (1, k)) for k in range(arity))
+    try:
+        lifted, lifted_scalar = _as_components(reducer.lift(message))
+        combined, combined_scalar = _as_components(
+            reducer.combine(left[0], right[0]) if scalar else reducer.combine(left, right))
+    except Exception:
+        return None
+    if len(lifted) != arity or len(combined) != arity or lifted_scalar != scalar or combined_scalar != scalar:
+        return None
+
+    def pairs_own_operands(expr, k, op):
+        if not (isinstance(expr, Expr) and expr.op == op and len(expr.args) == 2):
+            return False
+        return {id(expr.args[0]), id(expr.args[1])} == {id(left[k]), id(right[k])}
+
+    if scalar and lifted[0] is message:
+        try:
+            untouched = reducer.finalize(left[0]) is left[0]
+        except Exception:
+            untouched = False
+        if untouched and pairs_own_operands(combined[0], 0, "add"):
+            return ReducerAlgebra(kind="sum")
+        if untouched and pairs_own_operands(combined[0], 0, "maximum"):
+            return ReducerAlgebra(kind="max")
+    if not all(pairs_own_operands(combined[k], k, "add") for k in range(arity)):
+        return None
+    if any(not isinstance(v, (int, float)) or isinstance(v, bool) or float(v) != 0.0 for v in start):
+        return None        # an additive state has to start from zero
+    components = tuple(_monomial(lifted[k], message) for k in range(arity))
+    if any(c is None or c[1] < 0 or c[1] > 8 for c in components):
+        return None
+    return ReducerAlgebra(kind="additive", components=components, arity=arity, scalar=scalar)
+
+
 def reducer_algebra(reducer) -> str | None:
-    """Classify a user ``Reducer`` by capturing ``combine`` on two symbols:
-    'sum' (left+right) or 'max' (tg.math.maximum); None otherwise.  This is the
-    structural proof the reference does on captured reducer regions
-    (python/tiga/message_passing/core.py:84-132)."""
-    left, right = Expr("reducer_arg", (0,)), Expr("reducer_arg", (1,))
-    try:
-        combined = reducer.combine(left, right)
-    except Exception:
-        return None
-    if not isinstance(combined, Expr) or len(combined.args) != 2:
-        return None
-    operands = {id(combined.args[0]), id(combined.args[1])}
-    if operands != {id(left), id(right)}:
-        return None
-    try:
-        lifted = reducer.lift(left)
-        final = reducer.finalize(left)
-    except Exception:
-        return None
-    if lifted is not left or final is not left:
-        return None
-    return {"add": "sum", "maximum": "max"}.get(combined.op)
+    """'sum' / 'max' / 'additive' for a user reducer, or None."""
+    algebra = capture_reducer(reducer)
+    return None if algebra is None else algebra.kind

@@ -376,26 +376,42 @@ def halo_weighted_sum(graph: Graph, x: torch.Tensor, w: torch.Tensor | None, run
     return _HaloWeightedSum.apply(x, w, shard, runtime)
 
 
-def execute_sharded_message_passing(kernel, *, graph, src, dst, edge, params):
-    """Sharded call of a MessagePassing kernel on a ``Graph.halo()`` snapshot
-    (execute_sharded_message_passing, python/tiga/distributed/transport.py:898-1403
-    of the reference): every rank passes the fields of the rows it owns and gets
-    its rows of the result."""
-    runtime = current_distributed_runtime()
-    if runtime is None:
-        raise RuntimeError("a Graph.halo() snapshot needs an active DistributedRuntime")
+def specialise_sharded_message_passing(kernel, *, graph, src, dst, edge, params):
+    """Stage a MessagePassing kernel for a ``Graph.halo()`` snapshot: returns
+    (bindings, tensors, constants, runner) for the dispatcher's guarded warm path.  ``runner``
+    executes the sharded call under whichever DistributedRuntime is active when it is invoked:
+    every rank passes the fields of the rows it owns and gets its rows of the aggregate
+    (execute_sharded_message_passing, python/tiga/distributed/transport.py:898-1403 of the
+    reference)."""
     if not isinstance(kernel.reducer, SumReducer) or kernel.reducer.identity() != 0:
         raise NotImplementedError("sharded execution is implemented for the sum reducer")
     pattern = cap.recognize_weighted_sum(cap.capture_edge(kernel.edge, params))
     if pattern is None:
         raise NotImplementedError("sharded execution needs an `edge.w * src.x` or `src.x` message")
-    x = src[pattern.src_field]
-    w = edge[pattern.edge_field] if pattern.edge_field is not None else None
-    aggregate = halo_weighted_sum(graph, x, w, runtime)
+    bindings, tensors = [("src", pattern.src_field)], [src[pattern.src_field]]
+    if pattern.edge_field is not None:
+        bindings.append(("edge", pattern.edge_field))
+        tensors.append(edge[pattern.edge_field])
+    constants = {name: value for name, value in cap.selected_params(kernel.edge, params).items()
+                 if not isinstance(value, torch.Tensor)}
+
+    def runner(x, w=None):
+        return halo_weighted_sum(graph, x, w, current_distributed_runtime())
+
     kernel._record(graph, "b200-halo-csr-weighted-sum", ("partition-by-destination", "derive-halo",
                                                           "split-owned-ghost-edges", "overlap-exchange"),
                    ("halo rows land in their slice of the ghost buffer; owned-source edges reduce while the "
                     "exchange is in flight",))
+    return bindings, tensors, constants, runner
+
+
+def execute_sharded_message_passing(kernel, *, graph, src, dst, edge, params):
+    """One sharded call (aggregate plus the kernel's ``node`` epilogue)."""
+    if current_distributed_runtime() is None:
+        raise RuntimeError("a Graph.halo() snapshot needs an active DistributedRuntime")
+    _, tensors, _, runner = specialise_sharded_message_passing(kernel, graph=graph, src=src, dst=dst, edge=edge,
+                                                               params=params)
+    aggregate = runner(*tensors)
     from types import SimpleNamespace
 
     from ..message_passing import MessagePassing
@@ -407,4 +423,4 @@ def execute_sharded_message_passing(kernel, *, graph, src, dst, edge, params):
 
 __all__ = ["DistributedRuntime", "NCCLTransport", "NativeBackend", "ProcessGroupTransport", "ShardPlan",
            "build_shard_plan", "current_distributed_runtime", "execute_sharded_message_passing",
-           "halo_weighted_sum", "shard_plan_for"]
+           "halo_weighted_sum", "shard_plan_for", "specialise_sharded_message_passing"]

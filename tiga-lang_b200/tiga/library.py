@@ -1,33 +1,39 @@
-"""``torch.library`` operator facade over the native kernels.
+"""A specialised MessagePassing call as a ``torch.library`` dispatcher op.
 
-``register_message_passing(kernel, graph=, src=, dst=, edge=, **params)`` turns
-one specialised MessagePassing call into a functional dispatcher op
-``tiga::message_passing_<digest>(Tensor row_ptr, Tensor col_idx, Tensor
-input_0, ...) -> Tensor`` with a registered fake (meta) implementation and an
-autograd formula, the same boundary the reference offers
-(python/tiga/interop/torch/library.py:63-205 of walkerchi/TIGA-lang: same
-function name, same argument convention, same ``RegisteredMessagePassingOp``
-attributes).  The difference is underneath: both the implementation and the
-backward run the native CUDA kernels (the reference's backward replays its
-eager evaluator).  The backward re-enters the kernel under autograd, i.e. it
-recomputes the forward, because a dispatcher op cannot carry the inner
-Function's saved state.
+``register_message_passing(kernel, graph=, src=, dst=, edge=, **params)`` fixes
+one call shape -- kernel class, reducer, graph, field names, dtypes and shapes,
+static (non-tensor) parameters -- and publishes it as a functional op
+
+    tiga::message_passing_<digest>(Tensor row_ptr, Tensor col_idx,
+                                   Tensor input_0, ..., Tensor input_k) -> Tensor
+
+with a fake (meta) kernel and an autograd formula, so the call can sit inside
+``torch.compile`` / ``torch.export`` graphs.  Name, argument convention and the
+attributes of the returned handle (``qualified_name``, ``operation``,
+``topology``, ``bindings``, ``static_params``, ``opcheck``) are those of the
+reference's facade (python/tiga/interop/torch/library.py:63-205 of
+walkerchi/TIGA-lang).
+
+What differs is underneath.  Forward and backward both run the native CUDA
+kernels.  The backward is a second dispatcher op (``..._backward``) that calls
+the kernel again under autograd and differentiates it -- a dispatcher op cannot
+carry the saved state of the inner ``autograd.Function``, so the forward is
+recomputed -- whereas the reference replays its eager evaluator there.
 """
 from __future__ import annotations
 
 import hashlib
 from dataclasses import dataclass
-from typing import Any, Mapping
+from typing import Any, Mapping, Sequence
 
 import torch
 
-_LIBRARIES: list[Any] = []
-_REGISTERED: dict[str, "RegisteredMessagePassingOp"] = {}
+NAMESPACE = "tiga"
+ROLES = ("src", "dst", "edge")
 
-
-def _ordered_fields(src, dst, edge):
-    return tuple((role, name) for role, group in (("src", src), ("dst", dst), ("edge", edge))
-                 for name in sorted(group))
+# Fragments must stay alive for as long as their ops are callable.
+_fragments: list[Any] = []
+_ops_by_name: dict[str, "RegisteredMessagePassingOp"] = {}
 
 
 @dataclass(frozen=True)
@@ -38,124 +44,151 @@ class RegisteredMessagePassingOp:
     bindings: tuple[tuple[str, str], ...]
     static_params: Mapping[str, Any]
 
+    def _names(self, role: str) -> list[str]:
+        return sorted(field for r, field in self.bindings if r == role)
+
     def __call__(self, *, src, dst, edge=None):
-        groups = {"src": src, "dst": dst, "edge": {} if edge is None else edge}
-        for role, group in groups.items():
-            expected = sorted(name for r, name in self.bindings if r == role)
-            if sorted(group) != expected:
-                raise ValueError(f"{role} fields must be {expected}, got {sorted(group)}")
-        return self.operation(*self.topology, *(groups[role][name] for role, name in self.bindings))
+        given = dict(zip(ROLES, (src, dst, edge if edge is not None else {})))
+        for role in ROLES:
+            wanted = self._names(role)
+            if sorted(given[role]) != wanted:
+                raise ValueError(f"{role} fields must be {wanted}, got {sorted(given[role])}")
+        flat = [given[role][field] for role, field in self.bindings]
+        return self.operation(*self.topology, *flat)
 
     def opcheck(self, *values: Any) -> dict[str, str]:
         return torch.library.opcheck(self.operation, (*self.topology, *values))
 
 
+class _Specialisation:
+    """Everything fixed at registration time, plus the two op bodies."""
+
+    def __init__(self, kernel, graph, groups: Mapping[str, Mapping[str, torch.Tensor]], params):
+        self.kernel = kernel
+        self.graph = graph
+        self.params = dict(params)
+        self.row_ptr, self.col_idx = graph.resolve_csr()
+        self.bindings = tuple((role, field) for role in ROLES for field in sorted(groups[role]))
+        self.samples = tuple(groups[role][field] for role, field in self.bindings)
+        self.differentiable = tuple(i for i, t in enumerate(self.samples) if t.is_floating_point())
+
+    # ---- plumbing between the flat dispatcher signature and the keyword call
+    def fields(self, flat: Sequence[torch.Tensor]):
+        groups = {role: {} for role in ROLES}
+        for (role, field), tensor in zip(self.bindings, flat):
+            groups[role][field] = tensor
+        return groups
+
+    def graph_for(self, row_ptr, col_idx):
+        """The registered graph (with its cached launch plan) when the op is called on its own
+        topology tensors, otherwise a fresh graph over the tensors that were passed."""
+        if row_ptr.data_ptr() == self.row_ptr.data_ptr() and col_idx.data_ptr() == self.col_idx.data_ptr():
+            return self.graph
+        from .graph import Graph
+
+        return Graph.from_csr(row_ptr, col_idx, num_src=self.graph.schema.num_src, validate="basic")
+
+    def run(self, row_ptr, col_idx, flat):
+        groups = self.fields(flat)
+        return self.kernel(graph=self.graph_for(row_ptr, col_idx), src=groups["src"], dst=groups["dst"],
+                           edge=groups["edge"], **self.params)
+
+    # ---- op bodies
+    def forward(self, row_ptr, col_idx, *flat):
+        return self.run(row_ptr, col_idx, flat)
+
+    def backward(self, grad_output, row_ptr, col_idx, *flat):
+        leaves = [t.detach() for t in flat]
+        targets = [leaves[i].requires_grad_(True) for i in self.differentiable]
+        with torch.enable_grad():
+            result = self.run(row_ptr, col_idx, leaves)
+            grads = torch.autograd.grad(result, targets, grad_output.contiguous(), allow_unused=True)
+        return [torch.zeros_like(t) if g is None else g for g, t in zip(grads, targets)]
+
+    # ---- identity of the specialisation
+    def digest(self, output: torch.Tensor) -> str:
+        parts = (
+            type(self.kernel).__module__, type(self.kernel).__qualname__,
+            self.kernel.reducer.specialization_key(), self.graph.planning_key(), self.bindings,
+            tuple((tuple(t.shape), str(t.dtype)) for t in self.samples),
+            tuple(sorted((name, repr(value)) for name, value in self.params.items())),
+            tuple(output.shape), str(output.dtype),
+        )
+        return hashlib.sha256(repr(parts).encode()).hexdigest()[:20]
+
+
+def _check_name(name: str) -> None:
+    if not (name[:1].isalpha() and name.replace("_", "").isalnum()):
+        raise ValueError("Torch op name must begin with a letter and be alphanumeric/_")
+
+
 def register_message_passing(kernel, *, graph, src: Mapping[str, Any], dst: Mapping[str, Any],
                              edge: Mapping[str, Any] | None = None, name: str | None = None,
                              **params: Any) -> RegisteredMessagePassingOp:
-    from .graph import Graph
-
-    edge = {} if edge is None else edge
-    if graph.schema.realization != "materialized_csr" or graph.schema.lifecycle != "static":
+    schema = graph.schema
+    if schema.realization != "materialized_csr" or schema.lifecycle != "static":
         raise NotImplementedError("torch.library registration requires a static CSR graph")
-    row_ptr, col_idx = graph.resolve_csr()
-    bindings = _ordered_fields(src, dst, edge)
-    groups = {"src": src, "dst": dst, "edge": edge}
-    values = tuple(groups[role][field] for role, field in bindings)
-    if not values or any(not isinstance(value, torch.Tensor) for value in values):
+    groups = {"src": src, "dst": dst, "edge": edge if edge is not None else {}}
+    spec = _Specialisation(kernel, graph, groups, params)
+    if len(spec.samples) == 0 or not all(isinstance(t, torch.Tensor) for t in spec.samples):
         raise TypeError("registered MessagePassing fields must be torch.Tensor values")
     if any(isinstance(value, torch.Tensor) for value in params.values()):
         raise TypeError("Tensor parameters must be expressed as src/dst/edge fields")
-    with torch.no_grad():   # one native call fixes the result shape and dtype
-        sample = kernel(graph=graph, src=src, dst=dst, edge=edge, **params)
-    if not isinstance(sample, torch.Tensor):
+
+    # One real call pins down the result's shape and dtype for the fake kernel and the digest.
+    with torch.no_grad():
+        probe = spec.forward(spec.row_ptr, spec.col_idx, *spec.samples)
+    if not isinstance(probe, torch.Tensor):
         raise NotImplementedError("the torch.library facade requires one Tensor result")
-    output_shape, output_dtype = tuple(sample.shape), sample.dtype
-    signature = repr((type(kernel).__module__, type(kernel).__qualname__, kernel.reducer.specialization_key(),
-                      graph.planning_key(), bindings,
-                      tuple((tuple(v.shape), str(v.dtype)) for v in values),
-                      tuple(sorted((k, repr(v)) for k, v in params.items())), output_shape, str(output_dtype)))
-    op_name = name or f"message_passing_{hashlib.sha256(signature.encode()).hexdigest()[:20]}"
-    if not op_name.replace("_", "").isalnum() or not op_name[0].isalpha():
-        raise ValueError("Torch op name must begin with a letter and be alphanumeric/_")
-    qualified = f"tiga::{op_name}"
-    if qualified in _REGISTERED:
-        return _REGISTERED[qualified]
+    out_shape, out_dtype = tuple(probe.shape), probe.dtype
 
-    library = torch.library.Library("tiga", "FRAGMENT")
-    arguments = ", ".join(["Tensor row_ptr", "Tensor col_idx",
-                           *(f"Tensor input_{i}" for i in range(len(bindings)))])
-    library.define(f"{op_name}({arguments}) -> Tensor")
+    op_name = name if name else f"message_passing_{spec.digest(probe)}"
+    _check_name(op_name)
+    qualified = f"{NAMESPACE}::{op_name}"
+    known = _ops_by_name.get(qualified)
+    if known is not None:
+        return known
 
-    def unpack(flat):
-        fields = {"src": {}, "dst": {}, "edge": {}}
-        for (role, field), value in zip(bindings, flat):
-            fields[role][field] = value
-        return fields
+    fragment = torch.library.Library(NAMESPACE, "FRAGMENT")
+    tensor_args = ", ".join(["Tensor row_ptr", "Tensor col_idx"]
+                            + [f"Tensor input_{i}" for i in range(len(spec.bindings))])
+    grad_name = f"{op_name}_backward"
+    fragment.define(f"{op_name}({tensor_args}) -> Tensor")
+    fragment.define(f"{grad_name}(Tensor grad_output, {tensor_args}) -> Tensor[]")
+    fragment.impl(op_name, spec.forward, "CompositeExplicitAutograd")
+    fragment.impl(grad_name, spec.backward, "CompositeExplicitAutograd")
 
-    def runtime_graph(flat):
-        # the registered graph (and its cached launch plan) is reused when the op is called with its own topology
-        if flat[0].data_ptr() == row_ptr.data_ptr() and flat[1].data_ptr() == col_idx.data_ptr():
-            return graph
-        return Graph.from_csr(flat[0], flat[1], num_src=graph.schema.num_src, validate="basic")
+    def fake_forward(row_ptr, col_idx, *flat):
+        return flat[0].new_empty(out_shape, dtype=out_dtype)
 
-    def implementation(*flat):
-        fields = unpack(flat[2:])
-        return kernel(graph=runtime_graph(flat), src=fields["src"], dst=fields["dst"], edge=fields["edge"],
-                      **params)
+    def fake_backward(grad_output, row_ptr, col_idx, *flat):
+        return [torch.empty_like(flat[i]) for i in spec.differentiable]
 
-    library.impl(op_name, implementation, "CompositeExplicitAutograd")
-    torch.library.register_fake(qualified, lambda *flat: flat[2].new_empty(output_shape, dtype=output_dtype),
-                                lib=library)
+    torch.library.register_fake(qualified, fake_forward, lib=fragment)
+    torch.library.register_fake(f"{NAMESPACE}::{grad_name}", fake_backward, lib=fragment)
+    grad_op = getattr(getattr(torch.ops, NAMESPACE), grad_name).default
+    offset = 2  # row_ptr, col_idx precede the fields
 
-    # The backward is a dispatcher op of its own (opaque to tracing, with a fake implementation), so
-    # compiled / exported graphs can differentiate through the forward op.
-    float_positions = tuple(i for i, v in enumerate(values) if v.is_floating_point())
-    backward_name = f"{op_name}_backward"
-    library.define(f"{backward_name}(Tensor grad_output, {arguments}) -> Tensor[]")
-
-    def backward_implementation(grad_output, *flat):
-        replay = [value.detach() for value in flat]
-        wanted = []
-        for position in float_positions:
-            replay[2 + position].requires_grad_(True)
-            wanted.append(replay[2 + position])
-        fields = unpack(replay[2:])
-        with torch.enable_grad():
-            output = kernel(graph=runtime_graph(replay), src=fields["src"], dst=fields["dst"],
-                            edge=fields["edge"], **params)
-            computed = torch.autograd.grad(output, wanted, grad_output.contiguous(), allow_unused=True)
-        return [g if g is not None else torch.zeros_like(w) for g, w in zip(computed, wanted)]
-
-    library.impl(backward_name, backward_implementation, "CompositeExplicitAutograd")
-    torch.library.register_fake(
-        f"tiga::{backward_name}",
-        lambda grad_output, *flat: [torch.empty_like(flat[2 + position]) for position in float_positions],
-        lib=library)
-    backward_operation = getattr(getattr(torch.ops.tiga, backward_name), "default")
-
-    def setup_context(ctx, inputs, output):
+    def save_inputs(ctx, inputs, output):
         ctx.save_for_backward(*inputs)
 
-    def backward(ctx, grad_output):
-        saved = ctx.saved_tensors
-        if not any(ctx.needs_input_grad[2 + position] for position in float_positions):
-            return (None,) * len(saved)
-        computed = backward_operation(grad_output, *saved)
-        gradients = [None] * len(saved)
-        for position, gradient in zip(float_positions, computed):
-            if ctx.needs_input_grad[2 + position]:
-                gradients[2 + position] = gradient
-        return tuple(gradients)
+    def autograd_formula(ctx, grad_output):
+        inputs = ctx.saved_tensors
+        wanted = [i for i in spec.differentiable if ctx.needs_input_grad[offset + i]]
+        result: list[Any] = [None] * len(inputs)
+        if wanted:
+            computed = dict(zip(spec.differentiable, grad_op(grad_output, *inputs)))
+            for i in wanted:
+                result[offset + i] = computed[i]
+        return tuple(result)
 
-    torch.library.register_autograd(qualified, backward, setup_context=setup_context, lib=library)
-    operation = getattr(getattr(torch.ops.tiga, op_name), "default")
-    registered = RegisteredMessagePassingOp(qualified_name=qualified, operation=operation,
-                                            topology=(row_ptr, col_idx), bindings=bindings,
-                                            static_params=dict(params))
-    _LIBRARIES.append(library)
-    _REGISTERED[qualified] = registered
-    return registered
+    torch.library.register_autograd(qualified, autograd_formula, setup_context=save_inputs, lib=fragment)
+    handle = RegisteredMessagePassingOp(
+        qualified_name=qualified, operation=getattr(getattr(torch.ops, NAMESPACE), op_name).default,
+        topology=(spec.row_ptr, spec.col_idx), bindings=spec.bindings, static_params=dict(params))
+    _fragments.append(fragment)
+    _ops_by_name[qualified] = handle
+    return handle
 
 
 __all__ = ["RegisteredMessagePassingOp", "register_message_passing"]

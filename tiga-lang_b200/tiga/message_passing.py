@@ -60,6 +60,7 @@ def _validate_fields(role, fields, entities, device) -> None:
 
 
 def _reducer_kind(reducer) -> str | None:
+    """'sum' / 'mean' / 'max' / 'additive' for reducers the CSR kernels can fold, else None."""
     if isinstance(reducer, SumReducer):
         return "sum"
     if isinstance(reducer, MeanReducer):
@@ -68,8 +69,60 @@ def _reducer_kind(reducer) -> str | None:
         return "max"
     if isinstance(reducer, (OnlineSoftmaxReducer, ProductReducer)):
         return None
-    algebra = cap.reducer_algebra(reducer)
-    return algebra
+    return cap.reducer_algebra(reducer)
+
+
+_MISS = object()
+
+
+def _tensor_spec(t: torch.Tensor):
+    return (t.dtype, tuple(t.shape), tuple(t.stride()), t.device, t.requires_grad)
+
+
+class _GuardedLaunch:
+    """A specialised call kept for the warm path.
+
+    The first call of a (kernel, reducer, graph, field layout, parameter) combination stages
+    ``edge()``, recognises the program, builds launch plans and records a variant.  What it
+    learned is stored here as `runner` plus the guards under which the runner stays valid:
+    the same Graph object (graphs are immutable snapshots, so identity proves topology and plan),
+    the same reducer object, and for every tensor the runner reads the same dtype, shape, strides,
+    device and requires_grad; non-tensor parameters (they are folded into the staged program as
+    constants) must compare equal.  A warm call therefore does no staging, no recognition and no
+    key building: it checks the guards and launches.  The reference keeps the same kind of record
+    (``_GuardedExecutable`` and the installed fast path,
+    python/tiga/interop/torch/message_passing.py:974-1007, 3680-3797)."""
+
+    __slots__ = ("graph", "reducer", "bindings", "specs", "constants", "runner", "variant")
+
+    def __init__(self, graph, reducer, bindings, tensors, constants, runner, variant):
+        self.graph = graph
+        self.reducer = reducer
+        self.bindings = tuple(bindings)            # (role, name) per tensor the runner takes
+        self.specs = tuple(_tensor_spec(t) for t in tensors)
+        self.constants = dict(constants)           # non-tensor params the staged program absorbed
+        self.runner = runner
+        self.variant = variant
+
+    def try_run(self, kernel, graph, src, dst, edge, params):
+        if graph is not self.graph or kernel.reducer is not self.reducer:
+            return _MISS
+        spaces = {"src": src, "dst": dst, "edge": edge, "param": params}
+        tensors = []
+        try:
+            for (role, name), spec in zip(self.bindings, self.specs):
+                t = spaces[role][name]
+                if (t.dtype, tuple(t.shape), tuple(t.stride()), t.device, t.requires_grad) != spec:
+                    return _MISS
+                tensors.append(t)
+            for name, value in self.constants.items():
+                if params[name] != value:
+                    return _MISS
+        except (KeyError, TypeError, AttributeError):
+            return _MISS
+        if len(params) != len(self.constants) + sum(1 for role, _ in self.bindings if role == "param"):
+            return _MISS
+        return self.runner(*tensors)
 
 
 class _Prepared:
@@ -91,7 +144,20 @@ class MessagePassing(Kernel):
 
     def __init__(self) -> None:
         super().__init__()
-        self._torch_fast_path = None
+        self._launches: list[_GuardedLaunch] = []   # most recently used first
+
+    @property
+    def _torch_fast_path(self):
+        """``(graph, src, dst, edge, params) -> (hit, result)`` once a call has specialised the
+        kernel, else None: the hook name of the reference (python/tiga/message_passing/core.py:550-556)."""
+        if not self._launches:
+            return None
+
+        def fast_path(graph, src, dst, edge, params):
+            result = self._warm(graph, src, dst, edge, params)
+            return (False, None) if result is _MISS else (True, result)
+
+        return fast_path
 
     def edge(self, src, dst, edge, **params):
         raise NotImplementedError
@@ -105,22 +171,46 @@ class MessagePassing(Kernel):
             raise TypeError("graph must be a tiga.Graph")
         src, dst = _resolve_node_fields(graph, src, dst, ndata)
         edge = {} if edge is None else edge
-        if graph.is_distributed:
-            from .distributed.runtime import current_distributed_runtime, execute_sharded_message_passing
-
-            if current_distributed_runtime() is None:
-                raise RuntimeError("a Graph.halo() snapshot needs an active DistributedRuntime")
-            return execute_sharded_message_passing(self, graph=graph, src=src, dst=dst, edge=edge, params=params)
-        _validate_fields("src", src, graph.schema.num_src, graph.device)
-        _validate_fields("dst", dst, graph.schema.num_dst, graph.device)
-        if graph.device.type != "cuda":
-            raise NotImplementedError(
-                "this build executes MessagePassing on CUDA tensors only; there is no CPU path "
-                "(kernel.reference(...) evaluates the eager semantic definition on any device)")
-        aggregate = self._execute_native(graph, src, dst, edge, params)
+        aggregate = self._warm(graph, src, dst, edge, params) if self._launches else _MISS
+        if aggregate is _MISS:
+            aggregate = self._cold(graph, src, dst, edge, params)
         if type(self).node is MessagePassing.node:
             return aggregate
         return cap.call_region(self.node, (SimpleNamespace(**dst), aggregate), params)
+
+    def _warm(self, graph, src, dst, edge, params):
+        launches = self._launches
+        for position, launch in enumerate(launches):
+            result = launch.try_run(self, graph, src, dst, edge, params)
+            if result is not _MISS:
+                if position:
+                    launches.insert(0, launches.pop(position))
+                self._cache.hits += 1
+                self._cache.last = launch.variant
+                return result
+        return _MISS
+
+    def _cold(self, graph, src, dst, edge, params):
+        if graph.is_distributed:
+            from .distributed.runtime import current_distributed_runtime, specialise_sharded_message_passing
+
+            if current_distributed_runtime() is None:
+                raise RuntimeError("a Graph.halo() snapshot needs an active DistributedRuntime")
+            bindings, tensors, constants, runner = specialise_sharded_message_passing(
+                self, graph=graph, src=src, dst=dst, edge=edge, params=params)
+        else:
+            _validate_fields("src", src, graph.schema.num_src, graph.device)
+            _validate_fields("dst", dst, graph.schema.num_dst, graph.device)
+            if graph.device.type != "cuda":
+                raise NotImplementedError(
+                    "this build executes MessagePassing on CUDA tensors only; there is no CPU path "
+                    "(kernel.reference(...) evaluates the eager semantic definition on any device)")
+            bindings, tensors, constants, runner = self._specialise(graph, src, dst, edge, params)
+        result = runner(*tensors)
+        launch = _GuardedLaunch(graph, self.reducer, bindings, tensors, constants, runner, self.last_variant)
+        self._launches.insert(0, launch)
+        del self._launches[8:]
+        return result
 
     def _record(self, graph, lowering, passes, remarks, extra_key=()):
         key = (type(self).__qualname__, self.reducer.specialization_key(), graph.specialization_key(),
@@ -134,75 +224,114 @@ class MessagePassing(Kernel):
         else:
             self._cache_hits += 1
 
-    def _execute_native(self, graph, src, dst, edge, params):
-        from . import ops
-
+    # ------------------------------------------------------ specialisation
+    def _specialise(self, graph, src, dst, edge, params):
+        """Stage ``edge()``, recognise the program and return
+        (bindings, tensors, constants, runner): `runner(*tensors)` launches the native kernels."""
         staged = cap.capture_edge(self.edge, params)
         if staged is None:
             raise NotImplementedError(
                 f"edge() of {type(self).__name__} leaves the staging vocabulary "
                 "(field, +, -, *, /, sum(-1), maximum, exp); no native kernel and no fallback exists")
+        constants = {name: value for name, value in cap.selected_params(self.edge, params).items()
+                     if not isinstance(value, torch.Tensor)}
         if isinstance(self.reducer, OnlineSoftmaxReducer):
-            return self._execute_online_softmax(graph, src, dst, edge, params, staged)
+            return self._specialise_online_softmax(graph, src, dst, edge, params, staged, constants)
         kind = _reducer_kind(self.reducer)
         pattern = cap.recognize_weighted_sum(staged)
         if kind is None or pattern is None:
             raise NotImplementedError(
                 f"no native kernel for reducer {type(self.reducer).__name__} with this edge expression")
-        if graph.schema.realization not in {"materialized_csr"} and graph._row_ptr is None:
-            graph.resolve_csr()
+        from . import ops
+
         row_ptr, col_idx = graph.resolve_csr()
         _validate_fields("edge", edge, col_idx.numel(), graph.device)
         if pattern.src_field not in src:
             raise KeyError(f"edge() reads src.{pattern.src_field}, which was not bound")
-        x = src[pattern.src_field]
-        w = None
+        bindings, tensors = [("src", pattern.src_field)], [src[pattern.src_field]]
         if pattern.edge_field is not None:
             if pattern.edge_field not in edge:
                 raise KeyError(f"edge() reads edge.{pattern.edge_field}, which was not bound")
-            w = edge[pattern.edge_field]
-            if w.numel() != col_idx.numel():
+            if edge[pattern.edge_field].numel() != col_idx.numel():
                 raise NotImplementedError("edge weights must be one scalar per edge ([E] or [E, 1])")
-        identity = float(self.reducer.identity()) if kind in ("sum", "max") else 0.0
-        out = ops.csr_reduce(graph, kind, x, w, identity)
+            bindings.append(("edge", pattern.edge_field))
+            tensors.append(edge[pattern.edge_field])
+        weighted = pattern.edge_field is not None
         info = graph.native_plan(transpose=False).info
+        planner_remark = (f"rows by degree bucket, {info['long_rows']} split rows in {info['segments']} "
+                          f"segments of {info['segment_edges']} edges")
+        if kind == "additive":
+            algebra = cap.capture_reducer(self.reducer)
+            runner = _additive_runner(graph, self.reducer, algebra, weighted)
+            self._record(
+                graph, "b200-csr-additive-tuple-state",
+                ("capture-edge-udf", "capture-reducer", "prove-additive-state", "plan-degree-buckets"),
+                (planner_remark, f"{algebra.arity} state components, one fused CSR sum per non-constant "
+                                 "component; finalize runs on the finished states"),
+                extra_key=(tuple(tensors[0].shape[1:]), weighted, algebra.components))
+            return bindings, tensors, constants, runner
+        identity = float(self.reducer.identity()) if kind in ("sum", "max") else 0.0
+
+        def runner(x, w=None):
+            return ops.csr_reduce(graph, kind, x, w, identity)
+
         self._record(
             graph, f"b200-csr-{'weighted-sum' if kind == 'sum' else kind}-degree-bucket",
             ("capture-edge-udf", "recognize-weighted-sum", "plan-degree-buckets", "plan-split-rows",
              "cache-transposed-relation"),
-            (f"rows by degree bucket, {info['long_rows']} split rows in {info['segments']} segments of "
-             f"{info['segment_edges']} edges",
+            (planner_remark,
              "backward: dx gathers over the cached stable transposed relation (no atomics), "
              "dw is a per-edge dot product"),
-            extra_key=(tuple(x.shape[1:]), w is not None))
-        return out
+            extra_key=(tuple(tensors[0].shape[1:]), weighted))
+        return bindings, tensors, constants, runner
 
-    def _execute_online_softmax(self, graph, src, dst, edge, params, staged):
+    def _specialise_online_softmax(self, graph, src, dst, edge, params, staged, constants):
+        from . import attention
+
         gat = cap.recognize_gat(staged)
         if gat is not None:
-            from . import attention
+            slope = gat.slope
+            bindings = [("src", gat.src_field), ("dst", gat.dst_field), ("param", gat.src_param),
+                        ("param", gat.dst_param)]
+            tensors = [src[gat.src_field], dst[gat.dst_field], params[gat.src_param], params[gat.dst_param]]
 
-            out = attention.gat_attention(graph, src[gat.src_field], dst[gat.dst_field],
-                                          params[gat.src_param], params[gat.dst_param], gat.slope)
+            def runner(x_src, x_dst, a_src, a_dst):
+                return attention.gat_attention(graph, x_src, x_dst, a_src, a_dst, slope)
+
             self._record(graph, "b200-csr-edge-attention-online-softmax",
                          ("capture-edge-udf", "recognize-gat-logit", "plan-degree-buckets"),
                          ("row-centric online softmax, float32 state, (m, l) saved for backward",))
-            return out
-        dense = cap.recognize_dense_attention(self._with_scalar_params(params))
-        if dense is not None and graph.sequence_boundaries() is not None:
-            from . import attention
+            return bindings, tensors, constants, runner
+        field = cap.recognize_field_softmax(staged)
+        if field is not None and graph.sequence_boundaries() is None:
+            row_ptr, col_idx = graph.resolve_csr()
+            _validate_fields("edge", edge, col_idx.numel(), graph.device)
+            bindings = [("edge", field.score_field), ("src", field.value_field)]
+            tensors = [edge[field.score_field], src[field.value_field]]
 
-            out = attention.varlen_attention(graph, dst[dense.query_field], src[dense.key_field],
-                                             src[dense.value_field], dense.scale)
+            def runner(score, value):
+                return attention.field_softmax(graph, score, value)
+
+            self._record(graph, "b200-csr-stable-weighted-online-softmax",
+                         ("capture-edge-udf", "recognize-field-score-softmax", "plan-degree-buckets",
+                          "cache-transposed-relation"),
+                         ("per-edge scores, per-source values; float32 (m, l) state saved for backward; "
+                          "d_value gathers over the transposed relation (no atomics)",))
+            return bindings, tensors, constants, runner
+        dense = cap.recognize_dense_attention(staged)
+        if dense is not None and graph.sequence_boundaries() is not None:
+            scale = dense.scale
+            bindings = [("dst", dense.query_field), ("src", dense.key_field), ("src", dense.value_field)]
+            tensors = [dst[dense.query_field], src[dense.key_field], src[dense.value_field]]
+
+            def runner(query, key, value):
+                return attention.varlen_attention(graph, query, key, value, scale)
+
             self._record(graph, "b200-dense-streaming-reduction-tcgen05",
                          ("capture-edge-udf", "recognize-dense-attention", "schedule-varlen-tiles"),
                          ("implicit block-lower-triangular relation; no edge is materialised",))
-            return out
+            return bindings, tensors, constants, runner
         raise NotImplementedError("no native kernel for this online_softmax edge expression")
-
-    def _with_scalar_params(self, params):
-        # float params (e.g. scale) must appear as constants in the staged tree
-        return cap.capture_edge(self.edge, params)
 
     # ------------------------------------------------------------- prepare
     def prepare(self, *, graph: Graph, src=None, dst=None, edge=None, ndata=None, **params: Any):
@@ -282,7 +411,41 @@ def _eager_reduce(reducer, message, destination, num_dst):
     if isinstance(reducer, ProductReducer):
         start = torch.full(shape, reducer.identity(), dtype=message.dtype, device=message.device)
         return start.index_reduce(0, destination, message, "prod")
+    if kind == "additive":
+        algebra = cap.capture_reducer(reducer)
+        states = []
+        for coefficient, power in algebra.components:
+            term = torch.ones_like(message) if power == 0 else message ** power
+            states.append(torch.zeros(shape, dtype=message.dtype, device=message.device)
+                          .index_add_(0, destination, term * coefficient))
+        return reducer.finalize(states[0] if algebra.scalar else tuple(states))
     raise NotImplementedError(f"no eager evaluator for reducer {type(reducer).__name__}")
+
+
+def _additive_runner(graph, reducer, algebra, weighted: bool):
+    """Additive tuple-state reducer: state component k is sum_e c_k * m_e**p_k with m_e = w_e * x[src_e]
+    (or x[src_e]).  Because (w x)**p = w**p * x**p, every component with p >= 1 is one fused CSR sum
+    over element-wise powers of the node and edge arrays (never an [E, F] temporary); p = 0 counts
+    the row's edges.  ``finalize`` then runs on the finished [num_dst, ...] states with Torch ops,
+    and autograd differentiates through both."""
+    from . import ops
+
+    def runner(x, w=None):
+        row_ptr = graph.resolve_csr()[0]
+        shape = (graph.num_dst,) + (1,) * (x.ndim - 1)
+        states = []
+        for coefficient, power in algebra.components:
+            if power == 0:
+                degree = (row_ptr[1:] - row_ptr[:-1]).to(x.dtype).reshape(shape)
+                state = degree.expand((graph.num_dst,) + tuple(x.shape[1:]))
+            else:
+                xs = x if power == 1 else x ** power
+                ws = w if (w is None or power == 1) else w ** power
+                state = ops.csr_reduce(graph, "sum", xs, ws, 0.0)
+            states.append(state if coefficient == 1.0 else state * coefficient)
+        return reducer.finalize(states[0] if algebra.scalar else tuple(states))
+
+    return runner
 
 
 __all__ = ["MessagePassing"]

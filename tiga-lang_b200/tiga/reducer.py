@@ -1,36 +1,65 @@
-"""Reducer kernels: sum, mean, prod, online_softmax and user algebras.
+"""Reducers: how the messages of one destination row are folded.
 
-Same public surface as python/tiga/reducer/core.py:24-229 of the reference
-(``Reducer`` with identity/lift/combine/finalize and the
-associative/commutative/deterministic declarations, ``tg.sum(identity=)``,
-``tg.mean()``, ``tg.online_softmax(accumulation_dtype=, deterministic=,
-block_prune_threshold=)``, staged bindings ``ReducerCall`` /
-``OnlineSoftmaxItem``).  ``tg.max()`` is an addition of this package: the
-reference has no built-in maximum (docs/reducers.md:270-277) but runs a user
-``Reducer`` whose ``combine`` is ``tg.math.maximum``; ``MaxReducer`` is exactly
-such a reducer.
+A reducer is a small algebra -- ``identity()``, ``lift(message)``,
+``combine(left, right)``, ``finalize(state)`` -- plus three declarations
+(``associative``, ``commutative``, ``deterministic``) that the planner trusts.
+The fold it describes is ``finalize(combine(...combine(identity, lift(m1))...))``.
+
+The vocabulary is the reference's (python/tiga/reducer/core.py:24-229 of
+walkerchi/TIGA-lang): ``tg.sum(identity=)``, ``tg.mean()`` (tuple state
+``(sum, count)``; an empty row is 0/0 = NaN), ``tg.prod()``,
+``tg.online_softmax(accumulation_dtype=, deterministic=,
+block_prune_threshold=)``, user subclasses of ``Reducer``, and the two staged
+bindings an ``edge()`` may return: ``self.reducer(message, ...)`` ->
+``ReducerCall`` and, for the softmax reducer, ``self.reducer(score, value)`` ->
+``OnlineSoftmaxItem``.
+
+``tg.max()`` is an addition.  The reference documents that it has no built-in
+maximum (docs/reducers.md:270-277) but accepts a user reducer whose
+``combine`` is ``tg.math.maximum``; ``MaxReducer`` is such a reducer with the
+start value as a constructor argument.
+
+How a reducer reaches a CUDA kernel is decided in ``tiga.capture`` by staging
+these methods on symbols, never by looking at the class.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+import dataclasses
 from typing import Any
 
 from .kernel import Kernel
 
 
-@dataclass(frozen=True)
+@dataclasses.dataclass(frozen=True)
 class ReducerCall:
+    """``self.reducer(m0, m1, ...)`` inside ``edge()``: the messages bound to a reducer."""
+
     reducer: "Reducer"
     messages: tuple[Any, ...]
 
 
-@dataclass(frozen=True)
+@dataclasses.dataclass(frozen=True)
 class OnlineSoftmaxItem:
+    """``self.reducer(score, value)`` of the online-softmax reducer."""
+
     score: Any
     value: Any
 
 
+def _public_configuration(obj) -> tuple[tuple[str, str], ...]:
+    """Constructor-set attributes that distinguish two instances of one reducer class."""
+    pairs = []
+    for name in sorted(vars(obj)):
+        if name.startswith("_") or name == "deterministic":
+            continue
+        pairs.append((name, repr(getattr(obj, name))))
+    return tuple(pairs)
+
+
 class Reducer(Kernel):
+    """Base class of user reducers.  Override ``identity`` and ``combine``; ``lift`` and
+    ``finalize`` default to the identity map."""
+
     name = "custom"
     associative = False
     commutative = False
@@ -41,34 +70,33 @@ class Reducer(Kernel):
         self.deterministic = bool(deterministic)
 
     def identity(self):
-        raise NotImplementedError
+        raise NotImplementedError(f"{type(self).__name__} must define identity()")
 
     def lift(self, *messages):
-        return messages[0] if len(messages) == 1 else tuple(messages)
+        if len(messages) == 1:
+            return messages[0]
+        return tuple(messages)
 
     def combine(self, left, right):
-        raise NotImplementedError
+        raise NotImplementedError(f"{type(self).__name__} must define combine(left, right)")
 
     def finalize(self, state):
         return state
 
     def __call__(self, *messages: Any) -> ReducerCall:
-        if not messages:
+        if len(messages) == 0:
             raise TypeError("a reducer binding requires at least one message")
-        return ReducerCall(self, tuple(messages))
+        return ReducerCall(reducer=self, messages=tuple(messages))
 
     def specialization_key(self) -> tuple[object, ...]:
-        configuration = tuple(sorted(
-            (name, repr(value)) for name, value in vars(self).items()
-            if not name.startswith("_") and name != "deterministic"))
-        return (type(self).__module__, type(self).__qualname__, self.name, self.associative,
-                self.commutative, self.deterministic, configuration)
+        cls = type(self)
+        return (cls.__module__, cls.__qualname__, self.name, self.associative, self.commutative,
+                self.deterministic, _public_configuration(self))
 
 
 class SumReducer(Reducer):
     name = "sum"
-    associative = True
-    commutative = True
+    associative = commutative = True
 
     def __init__(self, *, identity: float | int = 0, deterministic: bool = False) -> None:
         super().__init__(deterministic=deterministic)
@@ -81,33 +109,35 @@ class SumReducer(Reducer):
         return left + right
 
     def specialization_key(self) -> tuple[object, ...]:
-        return self.name, self.identity_value, self.deterministic
+        return (self.name, self.identity_value, self.deterministic)
 
 
 class MeanReducer(Reducer):
-    """Neighbour mean as tuple state (sum, count); an empty row is 0/0 = NaN."""
+    """State ``(sum of messages, number of messages)``; the result is their quotient, so a
+    row without edges yields 0/0 = NaN."""
 
     name = "mean"
-    associative = True
-    commutative = True
+    associative = commutative = True
 
     def identity(self):
-        return 0.0, 0.0
+        return (0.0, 0.0)
 
     def lift(self, message):
-        return message, 1.0
+        return (message, 1.0)
 
     def combine(self, left, right):
-        return left[0] + right[0], left[1] + right[1]
+        total = left[0] + right[0]
+        count = left[1] + right[1]
+        return (total, count)
 
     def finalize(self, state):
-        return state[0] / state[1]
+        total, count = state
+        return total / count
 
 
 class ProductReducer(Reducer):
     name = "prod"
-    associative = True
-    commutative = True
+    associative = commutative = True
 
     def identity(self):
         return 1.0
@@ -117,11 +147,11 @@ class ProductReducer(Reducer):
 
 
 class MaxReducer(Reducer):
-    """Element-wise NaN-propagating maximum with a configurable start value."""
+    """Element-wise maximum in which a NaN message poisons the element (``arith.maximumf``
+    semantics); an empty row yields the start value."""
 
     name = "max"
-    associative = True
-    commutative = True
+    associative = commutative = True
 
     def __init__(self, *, identity: float = float("-inf"), deterministic: bool = False) -> None:
         super().__init__(deterministic=deterministic)
@@ -137,26 +167,35 @@ class MaxReducer(Reducer):
 
 
 class OnlineSoftmaxReducer(Reducer):
+    """Softmax-weighted sum of values, folded in one pass with a running maximum.
+
+    ``accumulation_dtype``     state dtype (float32 for half-precision inputs when None)
+    ``block_prune_threshold``  in (0, 1]: the approximate block-pruned variant of the reference;
+                               accepted and keyed on, no native kernel implements it
+    """
+
     name = "online_softmax"
-    associative = True
-    commutative = True
+    associative = commutative = True
 
     def __init__(self, *, accumulation_dtype: object | None = None, deterministic: bool = False,
                  block_prune_threshold: float | None = None) -> None:
         super().__init__(deterministic=deterministic)
-        if block_prune_threshold is not None and not (0.0 < float(block_prune_threshold) <= 1.0):
-            raise ValueError("block_prune_threshold must be in (0, 1]")
+        if block_prune_threshold is not None:
+            block_prune_threshold = float(block_prune_threshold)
+            if not 0.0 < block_prune_threshold <= 1.0:
+                raise ValueError("block_prune_threshold must be in (0, 1]")
         self.accumulation_dtype = accumulation_dtype
-        self.block_prune_threshold = None if block_prune_threshold is None else float(block_prune_threshold)
+        self.block_prune_threshold = block_prune_threshold
 
     def __call__(self, score: Any, value: Any) -> OnlineSoftmaxItem:
         return OnlineSoftmaxItem(score=score, value=value)
 
     def specialization_key(self) -> tuple[object, ...]:
-        return self.name, str(self.accumulation_dtype), self.deterministic, self.block_prune_threshold
+        return (self.name, str(self.accumulation_dtype), self.deterministic, self.block_prune_threshold)
 
 
-def sum(*, identity: float | int = 0, deterministic: bool = False) -> SumReducer:
+# ---- the lower-case factories programs call (tg.sum(), tg.mean(), ...) -------------------------
+def sum(*, identity: float | int = 0, deterministic: bool = False) -> SumReducer:  # noqa: A001
     return SumReducer(identity=identity, deterministic=deterministic)
 
 
@@ -168,7 +207,7 @@ def prod(*, deterministic: bool = False) -> ProductReducer:
     return ProductReducer(deterministic=deterministic)
 
 
-def max(*, identity: float = float("-inf"), deterministic: bool = False) -> MaxReducer:
+def max(*, identity: float = float("-inf"), deterministic: bool = False) -> MaxReducer:  # noqa: A001
     return MaxReducer(identity=identity, deterministic=deterministic)
 
 
