@@ -1,0 +1,326 @@
+"""The other benchmark configurations, measured on one GPU and reported inside
+bench.py's JSON line under "extra" (each with at least 10 timed steps, CUDA
+events on the launching stream and its own clock record):
+
+  c1_weighted_sum   N = 16 384, exactly 16 in-edges per row, F = 64 fp32: forward + grads of x and
+                    weight, plus the warm-call host overhead of the public API
+  c2_gcn_layer      R-MAT 2^20 nodes / 32 * 2^20 generated edges, symmetrised + de-duplicated,
+                    F = 128 fp32, sum reducer + 128x128 linear
+  c2_gcn_layer_max  the same graph with the maximum reducer
+  c3_gat            directed R-MAT 2^21 nodes / 64 M generated edges, bf16 [N, 8, 32], GAT logit,
+                    online softmax
+  c4_attention      32 packed sequences, L ~ U[512, 8192], 16 heads x 128, bf16, causal; flash-attn's
+                    varlen kernel is timed beside it as the on-box comparator
+  l2_hostile_sum    uniform random sources, N = 2^22, 16 edges per row, F = 128: a 2 GB source table,
+                    so the no-reuse algorithmic bytes are close to the real DRAM bytes
+
+`bench` is the bench.py module (timing helpers, peaks, roofline arithmetic).
+"""
+from __future__ import annotations
+
+import time
+
+import torch
+
+
+def _free():
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+
+
+def _steps(args):
+    return max(args.steps, 10)
+
+
+def weighted_sum_c1(args, device, bench):
+    import tiga as tg
+    from baseline import synthetic as syn
+    from tiga import _native
+
+    N, degree, F = 16384, 16, 64
+    row_ptr, col = syn.fixed_degree_graph(N, degree, seed=1234, device=device)
+    E = col.numel()
+    gen = torch.Generator().manual_seed(1234)
+    x = torch.randn(N, F, generator=gen).to(device).requires_grad_()
+    w = torch.rand(E, generator=gen).to(device).requires_grad_()
+    graph = tg.Graph.from_csr(row_ptr, col, num_src=N)
+    layer = bench.build_gcn_layer_class()()
+    ones = torch.ones((N, F), device=device)
+
+    def step():
+        out = layer(graph=graph, src={"x": x}, dst={}, edge={"weight": w})
+        return torch.autograd.grad(out, (x, w), ones)
+
+    xd, wd = x.detach(), w.detach()
+
+    def forward_only():
+        return layer(graph=graph, src={"x": xd}, dst={}, edge={"weight": wd})
+
+    steps = max(_steps(args), 200)
+    ms, clocks = bench.timed(step, steps, args.warmup, device.index or 0)
+    fwd_ms, _ = bench.timed(forward_only, steps, args.warmup, device.index or 0)
+    # host cost of a warm call: enqueue `steps` forwards without waiting for the device
+    forward_only()
+    torch.cuda.synchronize()
+    before = _native.launch_count()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        forward_only()
+    host_us = (time.perf_counter() - t0) / steps * 1e6
+    torch.cuda.synchronize()
+    launches = (_native.launch_count() - before) / steps
+    misses = layer.cache_info["misses"]
+    alg = 812 * E + 792 * N
+    peak, kind = bench.hbm_peak()
+    return {"workload": "weighted sum N=16384 degree=16 F=64 fp32 i64 fwd+bwd (x, weight)", "steps": steps,
+            "ms_per_step": round(ms, 5), "value": round(E / (ms * 1e-3) / 1e9, 3), "unit": bench.UNIT,
+            "forward_us_device": round(fwd_ms * 1e3, 2), "forward_us_host_per_warm_call": round(host_us, 2),
+            "launches_per_forward": launches, "staging_runs": misses,
+            "algorithmic_frac": round(alg / (ms * 1e-3) / 1e9 / peak, 4), "peak_kind": f"of {kind}",
+            "note": "67 MB of gathered rows: the working set sits in L2, so the step is bound by launch and "
+                    "host overhead, not by HBM", "clocks": clocks}
+
+
+def _gcn_layer(args, device, bench, reducer_name):
+    import tiga as tg
+    from baseline import synthetic as syn
+    from tiga import ops
+
+    scale, edge_factor, F = 20, 32, 128
+    row_ptr, col = syn.rmat_csr(scale, edge_factor, seed=args.seed, symmetrize=True, device=device)
+    N, E = row_ptr.numel() - 1, col.numel()
+    weight = syn.gcn_norm_weights(row_ptr, col).requires_grad_()
+    x = syn.normal((N, F), seed=args.seed + 1, device=device).requires_grad_()
+    lin = syn.normal((F, F), seed=args.seed + 2, device=device, std=F ** -0.5).requires_grad_()
+    graph = tg.Graph.from_csr(row_ptr, col, num_src=N)
+    graph.native_plan(transpose=True)
+    ones = torch.ones((N, F), device=device)
+
+    if reducer_name == "sum":
+        layer = bench.build_gcn_layer_class()()
+
+        def step():
+            agg = layer(graph=graph, src={"x": x}, dst={}, edge={"weight": weight})
+            return torch.autograd.grad(ops.dense_linear(agg, lin), (x, weight, lin), ones)
+    else:
+        class MaxLayer(tg.MessagePassing):
+            reducer = tg.max()
+
+            def edge(self, src, dst, edge):
+                return self.reducer(edge.weight * src.x)
+
+        layer = MaxLayer()
+
+        def step():
+            out = layer(graph=graph, src={"x": x}, dst={}, edge={"weight": weight})
+            return torch.autograd.grad(out, (x, weight), ones)
+
+    timings = {"fwd": [], "dx": [], "dw": []}
+    recording = {"on": False}
+    bench.instrument(ops, timings, recording)
+    steps = _steps(args)
+    for _ in range(3):
+        step()
+    recording["on"] = True
+    ms, clocks = bench.timed(step, steps, 0, device.index or 0)
+    recording["on"] = False
+    kernel_ms = {k: sum(a.elapsed_time(b) for a, b in v[-steps:]) / steps for k, v in timings.items()}
+    result = {"workload": f"gcn layer rmat scale={scale} edge_factor={edge_factor} symmetrized dedup F={F} fp32 "
+                          f"{'sum + 128x128 linear' if reducer_name == 'sum' else 'max reducer'} fwd+bwd",
+              "num_nodes": N, "num_edges": E, "steps": steps, "ms_per_step": round(ms, 4),
+              "value": round(E / (ms * 1e-3) / 1e9, 4), "unit": bench.UNIT, "clocks": clocks}
+    if reducer_name == "sum":
+        key = f"gcn layer rmat scale={scale} edge_factor={edge_factor} F={F}"
+        result["roofline"] = bench.gather_roofline(kernel_ms, bench.algorithmic_bytes(E, N, F),
+                                                   bench.ideal_cache_bytes(E, N, F), key,
+                                                   {k: 1 for k in kernel_ms})
+    else:
+        peak, kind = bench.hbm_peak()
+        row = 4 * F
+        fwd_bytes = E * (8 + 4 + row) + N * (8 + 2 * row)
+        result["kernel_ms_per_step"] = {k: round(v, 4) for k, v in kernel_ms.items()}
+        result["forward_algorithmic_frac"] = round(fwd_bytes / (kernel_ms["fwd"] * 1e-3) / 1e9 / peak, 4)
+        result["peak_kind"] = f"of {kind}"
+    return result
+
+
+def gcn_layer_sum(args, device, bench):
+    return _gcn_layer(args, device, bench, "sum")
+
+
+def gcn_layer_max(args, device, bench):
+    return _gcn_layer(args, device, bench, "max")
+
+
+def gat(args, device, bench):
+    import tiga as tg
+    from baseline import synthetic as syn
+
+    scale, edge_factor, H, D = 21, 32, 8, 32
+    row_ptr, col = syn.rmat_csr(scale, edge_factor, seed=args.seed, symmetrize=False, device=device)
+    N, E = row_ptr.numel() - 1, col.numel()
+    x = syn.normal((N, H, D), seed=args.seed + 1, device=device, dtype=torch.bfloat16).requires_grad_()
+    a_src = syn.normal((H, D), seed=args.seed + 2, device=device, dtype=torch.bfloat16, std=0.1).requires_grad_()
+    a_dst = syn.normal((H, D), seed=args.seed + 3, device=device, dtype=torch.bfloat16, std=0.1).requires_grad_()
+    dy = syn.normal((N, H, D), seed=args.seed + 4, device=device, dtype=torch.bfloat16)
+    graph = tg.Graph.from_csr(row_ptr, col, num_src=N)
+
+    class GAT(tg.MessagePassing):
+        reducer = tg.online_softmax()
+
+        def edge(self, src, dst, edge, a_src, a_dst):
+            s = (src.x * a_src).sum(dim=-1) + (dst.x * a_dst).sum(dim=-1)
+            return self.reducer(tg.math.maximum(s, 0.2 * s), src.x)
+
+    layer = GAT()
+    xd, sd, dd = x.detach(), a_src.detach(), a_dst.detach()
+
+    def step():
+        out = layer(graph=graph, ndata={"x": x}, a_src=a_src, a_dst=a_dst)
+        return torch.autograd.grad(out, (x, a_src, a_dst), dy)
+
+    steps = _steps(args)
+    fwd_ms, _ = bench.timed(lambda: layer(graph=graph, ndata={"x": xd}, a_src=sd, a_dst=dd), steps, args.warmup,
+                            device.index or 0)
+    ms, clocks = bench.timed(step, steps, args.warmup, device.index or 0)
+    peak, kind = bench.hbm_peak()
+    alg, alg_fwd = 1696 * E + 3152 * N, 520 * E + 1032 * N
+    return {"workload": f"gat edge attention rmat scale={scale} directed dedup bf16 [N,8,32] fwd+bwd",
+            "num_nodes": N, "num_edges": E, "steps": steps, "ms_per_step": round(ms, 4),
+            "forward_ms": round(fwd_ms, 4), "value": round(E / (ms * 1e-3) / 1e9, 4), "unit": bench.UNIT,
+            "algorithmic_frac": round(alg / (ms * 1e-3) / 1e9 / peak, 4),
+            "forward_algorithmic_frac": round(alg_fwd / (fwd_ms * 1e-3) / 1e9 / peak, 4),
+            "peak_kind": f"of {kind}", "clocks": clocks}
+
+
+def attention(args, device, bench):
+    import tiga as tg
+    from baseline import synthetic as syn
+    from tiga import ops
+
+    gen = torch.Generator().manual_seed(20260821)
+    lengths = torch.randint(512, 8193, (32,), generator=gen)
+    cu = torch.cat((torch.zeros(1, dtype=torch.int64), lengths.cumsum(0)))
+    T, H, D = int(cu[-1]), 16, 128
+    q, k, v = (syn.normal((T, H, D), seed=args.seed + i, device=device, dtype=torch.bfloat16).requires_grad_()
+               for i in range(3))
+    dy = syn.normal((T, H, D), seed=args.seed + 9, device=device, dtype=torch.bfloat16)
+    graph = tg.Graph.cu_seqlens(cu.to(device), causal=True)
+
+    class Attention(tg.MessagePassing):
+        reducer = tg.online_softmax()
+
+        def edge(self, src, dst, edge, scale):
+            return self.reducer((src.key * dst.query).sum(dim=-1) * scale, src.value)
+
+    layer = Attention()
+    scale = D ** -0.5
+    qd, kd, vd = q.detach(), k.detach(), v.detach()
+
+    def step():
+        out = layer(graph=graph, src={"key": k, "value": v}, dst={"query": q}, scale=scale)
+        return torch.autograd.grad(out, (q, k, v), dy)
+
+    steps = _steps(args)
+    fwd_ms, _ = bench.timed(lambda: layer(graph=graph, src={"key": kd, "value": vd}, dst={"query": qd}, scale=scale),
+                            steps, args.warmup, device.index or 0)
+    ms, clocks = bench.timed(step, steps, args.warmup, device.index or 0)
+    ops.check_async_errors()
+    pairs = float((lengths.double() * (lengths.double() + 1) / 2).sum())
+    fwd_flops = 4.0 * H * D * pairs
+    total_flops = 3.5 * fwd_flops
+    peak, kind = bench.bf16_peak()
+    result = {"workload": "varlen causal attention 32 sequences L~U[512,8192] H=16 D=128 bf16 fwd+bwd",
+              "tokens": T, "steps": steps, "ms_per_step": round(ms, 4), "forward_ms": round(fwd_ms, 4),
+              "value": round(total_flops / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+              "forward_tflops": round(fwd_flops / (fwd_ms * 1e-3) / 1e12, 2),
+              "tensor_frac": round(total_flops / (ms * 1e-3) / 1e12 / peak, 4),
+              "forward_tensor_frac": round(fwd_flops / (fwd_ms * 1e-3) / 1e12 / peak, 4),
+              "peak_kind": f"of {kind}", "clocks": clocks}
+    # comparator on the same box: flash-attn's varlen kernels (library code, not part of this build)
+    try:
+        from flash_attn import flash_attn_varlen_func
+
+        cu32 = cu.to(device=device, dtype=torch.int32)
+        longest = int(lengths.max())
+
+        def flash_forward():
+            return flash_attn_varlen_func(qd, kd, vd, cu32, cu32, longest, longest, softmax_scale=scale, causal=True)
+
+        def flash_step():
+            out = flash_attn_varlen_func(q, k, v, cu32, cu32, longest, longest, softmax_scale=scale, causal=True)
+            return torch.autograd.grad(out, (q, k, v), dy)
+
+        ref_fwd, _ = bench.timed(flash_forward, steps, args.warmup, device.index or 0)
+        ref_ms, _ = bench.timed(flash_step, steps, args.warmup, device.index or 0)
+        result["comparator"] = {"name": "flash_attn.flash_attn_varlen_func (installed flash-attn 2.x kernels)",
+                                "forward_ms": round(ref_fwd, 4), "ms_per_step": round(ref_ms, 4),
+                                "forward_tflops": round(fwd_flops / (ref_fwd * 1e-3) / 1e12, 2),
+                                "value": round(total_flops / (ref_ms * 1e-3) / 1e12, 2)}
+    except Exception as error:       # the comparator is optional
+        result["comparator"] = {"unavailable": f"{type(error).__name__}: {error}"[:160]}
+    return result
+
+
+def l2_hostile(args, device, bench):
+    import tiga as tg
+    from baseline import synthetic as syn
+    from tiga import ops
+
+    N, degree, F = 1 << 22, 16, 128
+    gen = torch.Generator(device=device).manual_seed(args.seed)
+    row_ptr = torch.arange(0, N * degree + 1, degree, dtype=torch.int64, device=device)
+    col = torch.randint(0, N, (N * degree,), generator=gen, dtype=torch.int64, device=device)
+    E = col.numel()
+    weight = torch.rand(E, generator=gen, device=device).requires_grad_()
+    x = syn.normal((N, F), seed=args.seed + 1, device=device).requires_grad_()
+    graph = tg.Graph.from_csr(row_ptr, col, num_src=N)
+    graph.native_plan(transpose=True)
+    layer = bench.build_gcn_layer_class()()
+    ones = torch.ones((N, F), device=device)
+
+    def step():
+        out = layer(graph=graph, src={"x": x}, dst={}, edge={"weight": weight})
+        return torch.autograd.grad(out, (x, weight), ones)
+
+    timings = {"fwd": [], "dx": [], "dw": []}
+    recording = {"on": False}
+    bench.instrument(ops, timings, recording)
+    steps = _steps(args)
+    for _ in range(3):
+        step()
+    recording["on"] = True
+    ms, clocks = bench.timed(step, steps, 0, device.index or 0)
+    recording["on"] = False
+    kernel_ms = {k: sum(a.elapsed_time(b) for a, b in v[-steps:]) / steps for k, v in timings.items()}
+    key = f"l2-hostile uniform N={N} degree={degree} F={F}"
+    return {"workload": f"weighted sum, uniform random sources, N=2^22 degree={degree} F={F} fp32 i64 fwd+bwd "
+                        "(2 GB source table: almost no gathered row is reused from L2)",
+            "num_nodes": N, "num_edges": E, "steps": steps, "ms_per_step": round(ms, 4),
+            "value": round(E / (ms * 1e-3) / 1e9, 4), "unit": bench.UNIT,
+            "roofline": bench.gather_roofline(kernel_ms, bench.algorithmic_bytes(E, N, F),
+                                              bench.ideal_cache_bytes(E, N, F), key, {k: 1 for k in kernel_ms}),
+            "clocks": clocks}
+
+
+WORKLOADS = {"weighted-sum": ("c1_weighted_sum", weighted_sum_c1), "gcn-layer": ("c2_gcn_layer", gcn_layer_sum),
+             "gcn-layer-max": ("c2_gcn_layer_max", gcn_layer_max), "gat": ("c3_gat", gat),
+             "attention": ("c4_attention", attention), "l2-hostile": ("l2_hostile_sum", l2_hostile)}
+
+
+def run_one(name, args, device, bench):
+    key, function = WORKLOADS[name]
+    result = function(args, device, bench)
+    _free()
+    return {key: result}
+
+
+def run_all(args, device, bench):
+    results = {}
+    for name in WORKLOADS:
+        try:
+            results.update(run_one(name, args, device, bench))
+        except Exception as error:          # one configuration failing must not lose the headline line
+            results[WORKLOADS[name][0]] = {"error": f"{type(error).__name__}: {error}"[:300]}
+            _free()
+    return results

@@ -1,30 +1,40 @@
 """Benchmark of the fused CSR message-passing path (forward + backward).
 
-    python bench.py --gpus 1 --steps K --warmup W           # this build, on B200
-    python bench.py --impl reference --steps K --warmup W   # the CPU arm
+    python bench.py --gpus N --steps K --warmup W            # this build, on B200s
+    python bench.py --impl reference --steps K --warmup W    # the CPU arm
 
-Workload at one GPU: the "GCN layer" configuration -- an R-MAT graph
-(a, b, c, d = 0.57, 0.19, 0.19, 0.05) with 2^20 nodes and 32 * 2^20 generated
-edges, symmetrised and de-duplicated, CSR by destination; edge weight
-1/sqrt(deg_i * deg_j); float32 features [N, 128]; sum reducer followed by a
-dense 128x128 float32 linear.  One step = forward plus the backward of
-out.sum() with respect to the features, the edge weights and the linear
-weights; the cotangent of out.sum() is a resident matrix of ones handed to
-autograd, in this arm and in the CPU arm alike.  Metric: directed edges per
-second for forward + backward.
+Headline workload, the same at every N (strong scaling): the distributed-halo GCN
+configuration -- an R-MAT graph (a, b, c, d = 0.57, 0.19, 0.19, 0.05), 2^scale
+nodes and 16 * 2^scale generated edges, symmetrised and de-duplicated, vertex ids
+relabelled at random, CSR by destination; edge weight 1/sqrt(deg_i * deg_j);
+float32 features [N, 64]; two layers of (sum reducer, dense 64x64 float32
+linear); one step = forward plus the backward of out.sum() with respect to the
+features, the edge weights and both linear weights.  With N > 1 the graph is cut
+into N contiguous destination ranges (the reference's owned_range rule), every
+rank generates only its own rows, ghost features are exchanged with NCCL every
+layer and their cotangents sent back.  Default scale 25 (the largest that fits
+one GPU, so that N = 1 runs the same graph); --scale 26 is the full-size
+configuration for N >= 2.  Metric: directed edges traversed per second for
+forward + backward, every edge counted once per layer.
 
-The JSON line carries, besides the base fields:
-  roofline     achieved algorithmic GB/s of the dominant gather kernel, timed
-               with CUDA events inside the timed region, against the measured
-               HBM copy bandwidth of MEASURED_PEAKS.json
-  e2e          the same step through the public API with host (pinned) inputs
-               copied to the device and gradients copied back every step
-  cpu_baseline the CPU oracle port (test infrastructure, OpenMP over rows)
-               timed on a bounded sample of the same workload
+Before timing, one step is checked against the CPU oracle on sampled rows
+("check" in the JSON line; a miss exits non-zero).  The JSON line carries,
+besides the base fields:
+  roofline     the dominant kernel's algorithmic GB/s (CUDA events on the
+               launching stream inside the timed region) against the measured
+               HBM copy bandwidth, the compulsory-traffic figure, and measured
+               DRAM traffic when a capture of the current kernel source exists
+  e2e          the same step with HOST inputs copied in and gradients copied out
+  cpu_baseline the CPU oracle port on a bounded sample of the same workload
+  extra        (N = 1) the other configurations: config-1 weighted sum with its
+               warm-call host overhead, the GCN layer (sum and max), GAT edge
+               attention, varlen causal attention next to flash-attn, and an
+               L2-hostile uniform-random gather
 """
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import subprocess
@@ -41,6 +51,7 @@ import torch  # noqa: E402
 METRIC = "GEdges/s fwd+bwd for fused CSR message passing"
 UNIT = "GEdges/s"
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
 
 
 def parse_args():
@@ -49,37 +60,42 @@ def parse_args():
     p.add_argument("--steps", type=int, default=10)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", default="native", choices=("native", "reference"))
-    p.add_argument("--scale", type=int, default=20, help="log2 of the node count")
-    p.add_argument("--edge-factor", type=int, default=32)
-    p.add_argument("--features", type=int, default=128)
+    p.add_argument("--scale", type=int, default=25, help="log2 of the node count of the headline graph")
+    p.add_argument("--edge-factor", type=int, default=16)
+    p.add_argument("--features", type=int, default=64)
+    p.add_argument("--layers", type=int, default=2)
     p.add_argument("--seed", type=int, default=20261125)
     p.add_argument("--labels", default="random", choices=("natural", "random"),
-                   help="multi-GPU workload: relabel the vertices at random as Graph500-style generators "
-                        "prescribe (default), or keep the generator's ids with the hubs at low ids; the "
-                        "single-GPU workload always keeps the generator's ids")
+                   help="vertex ids relabelled at random (what Graph500-style generators prescribe; contiguous "
+                        "ranges then hold the same mix of degrees) or the generator's ids with hubs at low ids")
+    p.add_argument("--waves", type=int, default=None, help="forward halo exchange waves (multi-GPU)")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
-    p.add_argument("--cpu-sample-seconds", type=float, default=15.0)
-    p.add_argument("--workload", default="gcn", choices=("gcn", "gat", "attention"),
-                   help="gcn = the headline GCN-layer configuration; gat / attention measure the edge-attention "
-                        "and dense-attention configurations (one GPU)")
+    p.add_argument("--no-check", action="store_true")
+    p.add_argument("--no-extra", action="store_true")
+    p.add_argument("--cpu-sample-seconds", type=float, default=12.0)
+    p.add_argument("--workload", default="halo-gcn",
+                   choices=("halo-gcn", "gcn-layer", "gcn-layer-max", "weighted-sum", "gat", "attention", "l2-hostile"),
+                   help="halo-gcn = the headline; the others print one of the `extra` sub-results alone (one GPU)")
     p.add_argument("--kernel-table", action="store_true",
                    help="after the timed run, print a per-kernel device-time table of two more steps to stderr")
     return p.parse_args()
 
 
-def hbm_peak():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+def measured_peak(key, fallback):
     try:
-        with open(path) as handle:
-            return float(json.load(handle)["hbm_gbs"]), "measured"
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as handle:
+            return float(json.load(handle)[key]), "measured"
     except Exception:
-        return FALLBACK_HBM_GBS, "fallback"
+        return fallback, "fallback"
 
 
-def workload_name(args):
-    return (f"gcn-layer rmat scale={args.scale} edge_factor={args.edge_factor} symmetrized dedup "
-            f"F={args.features} fp32 sum+linear fwd+bwd")
+def hbm_peak():
+    return measured_peak("hbm_gbs", FALLBACK_HBM_GBS)
+
+
+def bf16_peak():
+    return measured_peak("bf16_tflops", FALLBACK_BF16_TFLOPS)
 
 
 class ClockSampler:
@@ -102,10 +118,19 @@ class ClockSampler:
             threading.Thread(target=self._pump, daemon=True).start()
         except Exception:
             self.process = None
+        return self
 
     def _pump(self):
         for line in self.process.stdout:
             self.lines.append(line.strip())
+
+    def wait_for_first_sample(self, keep_busy, limit=1.5):
+        """nvidia-smi needs a moment to come up: keep the GPU under the same load, untimed, until
+        its first sample is in, so that the record covers clocks under load."""
+        waited = time.perf_counter()
+        while self.process is not None and not self.lines and time.perf_counter() - waited < limit:
+            keep_busy()
+            torch.cuda.synchronize()
 
     def stop(self):
         if self.process is None:
@@ -131,162 +156,9 @@ class ClockSampler:
                 "samples": len(clocks), "reasons": sorted(reasons)}
 
 
-# --------------------------------------------------------------------------- GPU arm
-def build_inputs(args, device):
-    from baseline import synthetic as syn
-
-    row_ptr, col = syn.rmat_csr(args.scale, args.edge_factor, seed=args.seed, symmetrize=True, device=device)
-    n = row_ptr.numel() - 1
-    weight = syn.gcn_norm_weights(row_ptr, col)
-    x = syn.normal((n, args.features), seed=args.seed + 1, device=device)
-    lin = syn.normal((args.features, args.features), seed=args.seed + 2, device=device, std=args.features ** -0.5)
-    return row_ptr, col, weight, x, lin
-
-
-def algorithmic_bytes(E, N, F):
-    """No-reuse algorithmic traffic per launch: 8-byte indices as given by the
-    API, 4-byte weights, one F*4-byte row per edge, pointer + one row per node."""
-    row = 4 * F
-    return {
-        "fwd": E * (8 + 4 + row) + N * (8 + row),
-        "dx": E * (8 + 8 + 4 + row) + N * (8 + row),
-        "dw": E * (8 + row + 4) + N * (8 + row),
-    }
-
-
-def bf16_peak():
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as handle:
-            return float(json.load(handle)["bf16_tflops"]), "measured"
-    except Exception:
-        return 1590.0, "fallback"
-
-
-def time_steps(step, steps, warmup):
-    for _ in range(max(warmup, 3)):
-        step()
-    torch.cuda.synchronize()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.profiler.start()
-    begin.record()
-    for _ in range(steps):
-        step()
-    end.record()
-    torch.cuda.synchronize()
-    torch.cuda.profiler.stop()
-    return begin.elapsed_time(end) / steps
-
-
-def run_gat(args, device):
-    """Edge-attention configuration: directed R-MAT (2^21 nodes, 64M generated edges, de-duplicated),
-    bf16 features [N, 8, 32], GAT logit, online-softmax reducer, forward + backward."""
-    import tiga as tg
-    from tiga import _native, ops
-    from baseline import synthetic as syn
-
-    scale = args.scale + 1 if args.scale == 20 else args.scale
-    row_ptr, col = syn.rmat_csr(scale, args.edge_factor, seed=args.seed, symmetrize=False, device=device)
-    N, E, H, D = row_ptr.numel() - 1, col.numel(), 8, 32
-    x = syn.normal((N, H, D), seed=args.seed + 1, device=device, dtype=torch.bfloat16).requires_grad_()
-    a_src = syn.normal((H, D), seed=args.seed + 2, device=device, dtype=torch.bfloat16, std=0.1).requires_grad_()
-    a_dst = syn.normal((H, D), seed=args.seed + 3, device=device, dtype=torch.bfloat16, std=0.1).requires_grad_()
-    graph = tg.Graph.from_csr(row_ptr, col, num_src=N)
-
-    class GAT(tg.MessagePassing):
-        reducer = tg.online_softmax()
-
-        def edge(self, src, dst, edge, a_src, a_dst):
-            s = (src.x * a_src).sum(dim=-1) + (dst.x * a_dst).sum(dim=-1)
-            return self.reducer(tg.math.maximum(s, 0.2 * s), src.x)
-
-    layer = GAT()
-    dy = syn.normal((N, H, D), seed=args.seed + 4, device=device, dtype=torch.bfloat16)
-    fwd_ms = time_steps(lambda: layer(graph=graph, ndata={"x": x.detach()}, a_src=a_src.detach(),
-                                      a_dst=a_dst.detach()), args.steps, args.warmup)
-
-    def step():
-        out = layer(graph=graph, ndata={"x": x}, a_src=a_src, a_dst=a_dst)
-        return torch.autograd.grad(out, (x, a_src, a_dst), dy)
-
-    before = _native.launch_count()
-    ms = time_steps(step, args.steps, args.warmup)
-    launches = (_native.launch_count() - before) // (args.steps + max(args.warmup, 3))
-    peak, kind = hbm_peak()
-    alg = 1696 * E + 3152 * N
-    alg_fwd = 520 * E + 1032 * N
-    print(json.dumps({
-        "metric": METRIC, "value": round(E / (ms * 1e-3) / 1e9, 4), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"gat edge attention rmat scale={scale} directed dedup bf16 [N,8,32] fwd+bwd",
-                   "num_nodes": N, "num_edges": E, "forward_ms": round(fwd_ms, 4), "l2": "inputs exceed L2"},
-        "roofline": {"bound": "hbm", "kernel": "k_gat_fwd + k_gat_bwd_dst + k_gat_bwd_src (whole step)",
-                     "achieved": round(alg / (ms * 1e-3) / 1e9, 1), "peak": peak, "peak_kind": f"of {kind}",
-                     "unit": "GB/s", "frac": round(alg / (ms * 1e-3) / 1e9 / peak, 4), "traffic": None,
-                     "forward_frac": round(alg_fwd / (fwd_ms * 1e-3) / 1e9 / peak, 4)},
-        "gpu_launches": int(launches)}), flush=True)
-
-
-def run_attention(args, device):
-    """Dense-relation configuration: 32 sequences with lengths uniform in [512, 8192], 16 heads,
-    head width 128, bf16, causal inside each sequence, forward + backward."""
-    import tiga as tg
-    from tiga import _native, ops
-    from baseline import synthetic as syn
-
-    gen = torch.Generator().manual_seed(20260821)
-    lengths = torch.randint(512, 8193, (32,), generator=gen)
-    cu = torch.cat((torch.zeros(1, dtype=torch.int64), lengths.cumsum(0)))
-    T, H, D = int(cu[-1]), 16, 128
-    q, k, v = (syn.normal((T, H, D), seed=args.seed + i, device=device, dtype=torch.bfloat16).requires_grad_()
-               for i in range(3))
-    dy = syn.normal((T, H, D), seed=args.seed + 9, device=device, dtype=torch.bfloat16)
-    graph = tg.Graph.cu_seqlens(cu.to(device), causal=True)
-
-    class Attention(tg.MessagePassing):
-        reducer = tg.online_softmax()
-
-        def edge(self, src, dst, edge, scale):
-            return self.reducer((src.key * dst.query).sum(dim=-1) * scale, src.value)
-
-    layer = Attention()
-    scale = D ** -0.5
-    fwd_ms = time_steps(lambda: layer(graph=graph, src={"key": k.detach(), "value": v.detach()},
-                                      dst={"query": q.detach()}, scale=scale), args.steps, args.warmup)
-
-    def step():
-        out = layer(graph=graph, src={"key": k, "value": v}, dst={"query": q}, scale=scale)
-        return torch.autograd.grad(out, (q, k, v), dy)
-
-    ms = time_steps(step, args.steps, args.warmup)
-    ops.check_async_errors()
-    if args.kernel_table:
-        from torch.profiler import ProfilerActivity, profile
-        with profile(activities=[ProfilerActivity.CUDA]) as prof:
-            step()
-            torch.cuda.synchronize()
-        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=12, max_name_column_width=70), flush=True)
-    pairs = float((lengths.double() * (lengths.double() + 1) / 2).sum())
-    fwd_flops = 4.0 * H * D * pairs
-    total_flops = 3.5 * fwd_flops
-    peak, kind = bf16_peak()
-    print(json.dumps({
-        "metric": "TFLOP/s fwd+bwd for varlen causal dense-relation attention", "value": round(total_flops / (ms * 1e-3) / 1e12, 2),
-        "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "varlen causal attention 32 sequences L~U[512,8192] H=16 D=128 bf16 fwd+bwd",
-                   "tokens": T, "forward_ms": round(fwd_ms, 4),
-                   "forward_tflops": round(fwd_flops / (fwd_ms * 1e-3) / 1e12, 2)},
-        "roofline": {"bound": "tensor", "kernel": "k_attn_fwd + k_attn_bwd_dkv + k_attn_bwd_dq",
-                     "achieved": round(total_flops / (ms * 1e-3) / 1e12, 2), "peak": peak, "peak_kind": f"of {kind}",
-                     "unit": "TFLOP/s", "frac": round(total_flops / (ms * 1e-3) / 1e12 / peak, 4), "traffic": None,
-                     "forward_frac": round(fwd_flops / (fwd_ms * 1e-3) / 1e12 / peak, 4)}}), flush=True)
-
-
 def clock_record_rejects(clocks):
-    """Why a timed region has to be measured again, or None: a slowdown reason
-    that invalidates the number, or a clock record without a single sample (the
-    sampler could not run beside the steps, so the host was not keeping up)."""
+    """Why a timed region has to be measured again, or None: a slowdown reason that invalidates
+    the number, or a clock record without a single sample."""
     bad = [r for r in clocks.get("reasons", []) if r in ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown")]
     if bad:
         return ",".join(bad)
@@ -295,48 +167,144 @@ def clock_record_rejects(clocks):
     return None
 
 
-def measured_dram_traffic(args, kernel):
-    """DRAM bytes (read + write) of one launch of `kernel` ("fwd", "dx" or
-    "dw"), taken from a one-pass ncu capture of dram__bytes_read.sum and
-    dram__bytes_write.sum on this exact workload (the table is in
-    profiles/csr_reduce_gcn_layer_ncu.md).  The
-    figure is a recorded measurement, not something this run can observe, so it
-    is reported only for the workload it was captured on."""
-    if getattr(args, "workload", "gcn") == "gcn" and args.scale == 20 and args.features == 128 \
-            and args.edge_factor == 32:
-        return {"fwd": 7.69e9, "dx": 12.36e9, "dw": 7.02e9}[kernel]
-    return None
+def timed(step, steps, warmup, device_index=0):
+    """(ms per step, clock record): W >= 3 warm-up steps, then `steps` steps between CUDA events on
+    the current stream with a synchronize on both sides; measured again once if the clock record
+    shows a slowdown."""
+    for _ in range(max(warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+
+    def region():
+        sampler = ClockSampler(device_index).start()
+        sampler.wait_for_first_sample(step)
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()       # a profiler started with --profile-from-start off sees the timed steps only
+        begin.record()
+        for _ in range(steps):
+            step()
+        end.record()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        return begin.elapsed_time(end) / steps, sampler.stop()
+
+    ms, clocks = region()
+    rejected = clock_record_rejects(clocks)
+    if rejected:
+        ms, clocks = region()
+        clocks["remeasured_after"] = rejected
+    return ms, clocks
 
 
-def run_native(args):
-    import torch.distributed as dist
+# --------------------------------------------------------------------------- roofline figures
+def algorithmic_bytes(E, N, F, index_bytes=8):
+    """No-reuse algorithmic traffic per launch: indices as given by the API, 4-byte weights, one
+    F*4-byte row per edge, a pointer and one row per node."""
+    row = 4 * F
+    i = index_bytes
+    return {"fwd": E * (i + 4 + row) + N * (i + row),
+            "dx": E * (2 * i + 4 + row) + N * (i + row),
+            "dw": E * (i + row + 4) + N * (i + row)}
 
+
+def ideal_cache_bytes(E, N, F, index_bytes=8):
+    """Compulsory traffic: every array moved exactly once (a perfect cache for the gathered rows)."""
+    row = 4 * F
+    i = index_bytes
+    return {"fwd": E * (i + 4) + N * (i + 2 * row),
+            "dx": E * (2 * i + 4) + N * (i + 2 * row),
+            "dw": E * (i + 4) + N * (i + 2 * row)}
+
+
+def kernel_source_id():
+    """Identifies the gather kernels' source: recorded DRAM captures apply to one version of it."""
+    digest = hashlib.sha1()
+    for name in ("tgb_csr_reduce.cu", "tgb_common.cuh"):
+        with open(os.path.join(ROOT, "tiga-lang_b200", "csrc", name), "rb") as handle:
+            digest.update(handle.read())
+    return digest.hexdigest()[:12]
+
+
+def recorded_dram_traffic(workload_key):
+    """DRAM bytes per launch from a committed one-pass ncu capture (dram__bytes_read.sum +
+    dram__bytes_write.sum) of this workload, or None.  A capture is used only while the kernel
+    source it was taken from is the one that runs now."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as handle:
+            table = json.load(handle)
+    except Exception:
+        return None
+    entry = table.get(workload_key)
+    if not entry or entry.get("kernel_source") != kernel_source_id():
+        return None
+    return entry
+
+
+def instrument(ops, timings, recording):
+    """Wraps the three kernel entry points with CUDA events on the launching stream."""
+    def wrap(name, function):
+        def wrapper(*a, **k):
+            if not recording["on"]:
+                return function(*a, **k)
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            result = function(*a, **k)
+            stop.record()
+            timings[name].append((start, stop))
+            return result
+        wrapper.__wrapped__ = function
+        return wrapper
+
+    for name, attribute in (("fwd", "csr_reduce_forward"), ("dx", "csr_reduce_backward_dx"),
+                            ("dw", "csr_reduce_backward_dw")):
+        current = getattr(ops, attribute)
+        setattr(ops, attribute, wrap(name, getattr(current, "__wrapped__", current)))
+
+
+def gather_roofline(kernel_ms, bytes_per, ideal_per, workload_key, launches_per_step):
+    """Roofline object for the dominant CSR kernel of a step.  `kernel_ms` is device time per step
+    per kernel kind, `bytes_per` / `ideal_per` the algorithmic and compulsory bytes per step."""
+    peak, peak_kind = hbm_peak()
+    dominant = max(kernel_ms, key=kernel_ms.get)
+    achieved = bytes_per[dominant] / (kernel_ms[dominant] * 1e-3) / 1e9
+    names = {"fwd": "k_gather_vec (forward)", "dx": "k_gather_vec (transposed relation, dx)",
+             "dw": "k_edge_dot_vec (dw)"}
+    capture = recorded_dram_traffic(workload_key)
+    traffic = capture["bytes_per_launch"].get(dominant) if capture else None
+    per_launch = max(launches_per_step.get(dominant, 1), 1)
+    roofline = {
+        "bound": "hbm", "kernel": names[dominant], "achieved": round(achieved, 1), "peak": peak,
+        "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": round(achieved / peak, 4),
+        "traffic": traffic,
+        "launches_per_step": per_launch,
+        "algorithmic_bytes_per_launch": int(bytes_per[dominant] // per_launch),
+        "ideal_cache_bytes_per_launch": int(ideal_per[dominant] // per_launch),
+        "ideal_cache_frac": round(ideal_per[dominant] / (kernel_ms[dominant] * 1e-3) / 1e9 / peak, 4),
+        "kernel_ms_per_step": {k: round(v, 4) for k, v in kernel_ms.items()},
+        "kernel_algorithmic_gbs": {k: round(bytes_per[k] / (kernel_ms[k] * 1e-3) / 1e9, 1) for k in kernel_ms
+                                   if kernel_ms[k] > 0},
+        "step_algorithmic_frac": round(sum(bytes_per.values()) / (sum(kernel_ms.values()) * 1e-3) / 1e9 / peak, 4),
+        "note": "algorithmic bytes count every gathered row once per edge (no reuse); rows that hit in the "
+                "126 MB L2 make frac exceed 1, ideal_cache_frac is the same time against compulsory bytes",
+    }
+    if capture:
+        launch_ms = kernel_ms[dominant] / per_launch
+        roofline["dram_frac"] = round(traffic / (launch_ms * 1e-3) / 1e9 / peak, 4) if traffic else None
+        roofline["traffic_capture"] = {k: capture[k] for k in ("commit", "kernel_source", "how") if k in capture}
+    else:
+        roofline["dram_frac"] = None
+    return roofline
+
+
+# --------------------------------------------------------------------------- headline: halo GCN
+def headline_name(args):
+    return (f"halo gcn {args.layers} layers rmat scale={args.scale} edge_factor={args.edge_factor} symmetrized "
+            f"dedup labels={args.labels} F={args.features} fp32 sum+linear fwd+bwd")
+
+
+def build_gcn_layer_class():
     import tiga as tg
-    from tiga import _native, ops
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-        try:
-            return run_native_multi(args, rank, world, device)
-        finally:
-            dist.destroy_process_group()
-
-    _native.lib()
-    torch.backends.cuda.matmul.allow_tf32 = False
-    if args.workload == "gat":
-        return run_gat(args, device)
-    if args.workload == "attention":
-        return run_attention(args, device)
-    row_ptr, col, weight, x, lin = build_inputs(args, device)
-    N, E, F = row_ptr.numel() - 1, col.numel(), args.features
-    graph = tg.Graph.from_csr(row_ptr, col, num_src=N)
 
     class GCNLayer(tg.MessagePassing):
         reducer = tg.sum()
@@ -344,101 +312,260 @@ def run_native(args):
         def edge(self, src, dst, edge):
             return edge.weight * src.x
 
-    layer = GCNLayer()
-    x.requires_grad_()
-    weight.requires_grad_()
-    lin.requires_grad_()
+    return GCNLayer
 
-    # per-kernel CUDA-event timing inside the step (events on the launching stream)
+
+class _NullContext:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+def run_halo_gcn(args):
+    import torch.distributed as dist
+
+    import tiga as tg
+    from baseline import synthetic as syn
+    from baseline import verify
+    from tiga import _native, ops
+    from tiga.distributed.model import owned_range
+    from tiga.distributed.runtime import DistributedRuntime, NCCLTransport, shard_plan_for
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    _native.lib()
+    torch.backends.cuda.matmul.allow_tf32 = False
+    F, layers, N = args.features, args.layers, 1 << args.scale
+    first, last = owned_range(N, world, rank)
+
+    # ---- this rank's rows only: the whole graph is never held anywhere
+    setup = time.perf_counter()
+    row_ptr, col = syn.rmat_csr_rows(args.scale, args.edge_factor, first, last, seed=args.seed, symmetrize=True,
+                                     relabel=args.labels == "random", device=device)
+    local_degree = row_ptr[1:] - row_ptr[:-1]
+    if world > 1:
+        sizes = [owned_range(N, world, r) for r in range(world)]
+        widest = max(e - b for b, e in sizes)
+        padded = torch.zeros(widest, dtype=torch.int64, device=device)
+        padded[:local_degree.numel()] = local_degree
+        pieces = [torch.empty_like(padded) for _ in range(world)]
+        dist.all_gather(pieces, padded)
+        degree = torch.cat([piece[:e - b] for piece, (b, e) in zip(pieces, sizes)])
+        del pieces, padded
+    else:
+        degree = local_degree
+    E_local = int(col.numel())
+    totals = torch.tensor([E_local], dtype=torch.int64, device=device)
+    if world > 1:
+        dist.all_reduce(totals)
+    E = int(totals.item())
+    weight = syn.gcn_norm_weights_rows(row_ptr, col, degree, first).requires_grad_()
+    max_degree = int(degree.max().item())
+    del degree, local_degree
+    x = syn.normal_rows(first, last, F, seed=args.seed + 1, device=device).requires_grad_()
+    linears = [syn.normal((F, F), seed=args.seed + 2 + k, device=device, std=F ** -0.5).requires_grad_()
+               for k in range(layers)]
+    runtime = None
+    if world > 1:
+        graph = tg.Graph.from_csr_shard(row_ptr, col, num_nodes=N, first_row=first).halo(tg.DeviceMesh("cuda", world))
+        runtime = DistributedRuntime(NCCLTransport(device=device), trace=True, waves=args.waves)
+        with runtime:
+            shard = shard_plan_for(graph, runtime)
+        for relation in (shard.graph_own, shard.graph_ghost):
+            relation.native_plan(transpose=True)
+        for _, relation in shard.waves:
+            relation.native_plan(transpose=False)
+    else:
+        graph = tg.Graph.from_csr(row_ptr, col, num_src=N)
+        graph.native_plan(transpose=True)
+        shard = None
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    setup_s = time.perf_counter() - setup
+    rows = last - first
+    layer = build_gcn_layer_class()()
+    ones = torch.ones((rows, F), dtype=torch.float32, device=device)     # d(out.sum()) / d(out)
+
+    def forward(xs, ws, ls, keep=None):
+        h = xs
+        for k, matrix in enumerate(ls):
+            agg = layer(graph=graph, src={"x": h}, dst={}, edge={"weight": ws})
+            h = ops.dense_linear(agg, matrix)
+            if keep is not None:
+                keep[f"agg{k + 1}"], keep[f"h{k + 1}"] = agg, h
+        return h
+
+    def step(xs=x, ws=weight, ls=linears):
+        if runtime is not None:
+            with runtime:
+                out = forward(xs, ws, ls)
+                grads = torch.autograd.grad(out, (xs, ws, *ls), ones)
+            flat = torch.cat([g.reshape(-1) for g in grads[2:]])
+            dist.all_reduce(flat)                # replicated linear weights: one all-reduce of their gradients
+            return grads[0], grads[1], flat
+        out = forward(xs, ws, ls)
+        grads = torch.autograd.grad(out, (xs, ws, *ls), ones)
+        return grads[0], grads[1], torch.cat([g.reshape(-1) for g in grads[2:]])
+
+    # ---- verification step: sampled rows against the CPU oracle, on every rank
+    check = None
+    if not args.no_check and layers == 2:
+        from oracle import oracle
+
+        oracle.build()
+        keep = {}
+        with (runtime if runtime is not None else _NullContext()):
+            out = forward(x, weight, linears, keep)
+            wanted = (x, weight, linears[0], linears[1], keep["agg1"], keep["h1"], keep["agg2"])
+            dx, dw, dW1, dW2, d_agg1, d_h1, d_agg2 = torch.autograd.grad(out, wanted, ones)
+        if world > 1:
+            dist.all_reduce(dW1)
+            dist.all_reduce(dW2)
+        tensors = {"agg1": keep["agg1"], "h1": keep["h1"], "agg2": keep["agg2"], "out": out, "d_agg1": d_agg1,
+                   "d_h1": d_h1, "d_agg2": d_agg2, "dx": dx, "dw": dw, "dW1": dW1, "dW2": dW2}
+        mine = verify.check_two_layer_gcn(
+            oracle, row_ptr=row_ptr, col_idx=col, first_row=first, num_nodes=N, weight=weight,
+            feature_of=lambda ids: syn.normal_rows(0, 0, F, seed=args.seed + 1, ids=ids), tensors=tensors,
+            linears=linears, world=world)
+        del tensors, keep, out, dx, dw, d_agg1, d_h1, d_agg2, wanted, dW1, dW2
+        ops.check_async_errors()
+        gathered = [mine]
+        if world > 1:
+            gathered = [None] * world
+            dist.all_gather_object(gathered, mine)
+        worst = max(gathered, key=lambda c: c["max_excess"])
+        check = {"rows": sum(c["rows"] for c in gathered), "edges": sum(c["edges"] for c in gathered),
+                 "max_excess": worst["max_excess"], "worst": worst["worst"],
+                 "ok": all(c["ok"] for c in gathered), "ranks": len(gathered),
+                 "checked": "agg1 agg2 h1 out dx d_h1 d_agg1 dw dW1 dW2 on sampled owned rows of every rank vs the "
+                            "CPU oracle (rel 1e-5 / abs 1e-6 + 8 ulp of sum |terms|); remote rows fetched by all-reduce",
+                 "excess_rank0": gathered[0]["excess"]}
+        torch.cuda.empty_cache()
+
+    # ---- timed region
     timings = {"fwd": [], "dx": [], "dw": []}
     recording = {"on": False}
-
     instrument(ops, timings, recording)
-
-    ones = torch.ones((N, lin.shape[1]), dtype=torch.float32, device=device)   # d(out.sum()) / d(out)
-
-    def step(xs, ws, ls):
-        agg = layer(graph=graph, src={"x": xs}, dst={}, edge={"weight": ws})
-        out = ops.dense_linear(agg, ls)
-        return torch.autograd.grad(out, (xs, ws, ls), ones)
-
-    plan_start = time.perf_counter()
-    graph.native_plan(transpose=True)
-    torch.cuda.synchronize()
-    plan_ms = (time.perf_counter() - plan_start) * 1e3
-
     for _ in range(max(args.warmup, 3)):
-        step(x, weight, lin)
+        step()
     torch.cuda.synchronize()
-    def timed_region():
+    sync = dist.barrier if world > 1 else None
+
+    def region():
         for v in timings.values():
             v.clear()
-        sampler = ClockSampler(local)
-        sampler.start()
-        # nvidia-smi needs a moment to come up: keep the GPU under the same load, untimed, until its
-        # first sample is in (at most 1.5 s), so that the record covers clocks under load
-        waited = time.perf_counter()
-        while sampler.process is not None and not sampler.lines and time.perf_counter() - waited < 1.5:
-            step(x, weight, lin)
-            torch.cuda.synchronize()
-        launches_before = _native.launch_count()
+        if runtime is not None:
+            runtime.reset_trace()
+        sampler = ClockSampler(local).start()
+        if world == 1:
+            sampler.wait_for_first_sample(step)
+        if sync:
+            sync()
+        before = _native.launch_count()
         recording["on"] = True
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
-        torch.cuda.profiler.start()   # lets a profiler started with --profile-from-start off see only the timed steps
+        torch.cuda.profiler.start()
         begin.record()
         for _ in range(args.steps):
-            step(x, weight, lin)
+            step()
         end.record()
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
+        if sync:
+            sync()
         recording["on"] = False
-        return (begin.elapsed_time(end) / args.steps, _native.launch_count() - launches_before, sampler.stop())
+        return begin.elapsed_time(end) / args.steps, _native.launch_count() - before, sampler.stop()
 
-    ms_per_step, launches, clocks = timed_region()
+    ms_mine, launches, clocks = region()
     rejected = clock_record_rejects(clocks)
-    if rejected:        # thermal / hardware slowdown, or no clock sample at all: measure once more
-        ms_per_step, launches, clocks = timed_region()
-        clocks["remeasured_after"] = rejected
+    again = bool(rejected)
+    if world > 1:       # every rank must agree on a second measurement
+        flag = torch.tensor([1 if rejected else 0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        again = bool(flag.item())
+    if again:
+        ms_mine, launches, clocks = region()
+        clocks["remeasured_after"] = rejected or "a peer's clock record"
     ops.check_async_errors()
-    value = E / (ms_per_step * 1e-3) / 1e9
+    slowest = torch.tensor([ms_mine], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+    ms_per_step = float(slowest.item())
+    traversed = layers * E
+    value = traversed / (ms_per_step * 1e-3) / 1e9
 
-    bytes_per = algorithmic_bytes(E, N, F)
-    kernel_ms = {k: sum(a.elapsed_time(b) for a, b in v) / max(len(v), 1) for k, v in timings.items()}
-    dominant = max(kernel_ms, key=kernel_ms.get)
-    peak, peak_kind = hbm_peak()
-    achieved = bytes_per[dominant] / (kernel_ms[dominant] * 1e-3) / 1e9
-    total_alg = sum(bytes_per.values())
-    total_kernel_ms = sum(kernel_ms.values())
-    roofline = {
-        "bound": "hbm", "kernel": {"fwd": "k_gather_vec (forward)", "dx": "k_gather_vec (transposed, dx)",
-                                   "dw": "k_edge_dot_vec (dw)"}[dominant],
-        "achieved": round(achieved, 1), "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
-        "frac": round(achieved / peak, 4), "traffic": measured_dram_traffic(args, dominant),
-        "algorithmic_bytes_per_launch": bytes_per[dominant],
-        "kernel_ms": {k: round(v, 4) for k, v in kernel_ms.items()},
-        "kernel_gbs": {k: round(bytes_per[k] / (kernel_ms[k] * 1e-3) / 1e9, 1) for k in kernel_ms},
-        "fwd_bwd_frac": round(total_alg / (total_kernel_ms * 1e-3) / 1e9 / peak, 4),
-    }
+    kernel_ms = {k: sum(a.elapsed_time(b) for a, b in v) / args.steps for k, v in timings.items()}
+    launches_per_step = {k: len(v) // args.steps for k, v in timings.items()}
+    table_rows = rows + (int(shard.ghosts.numel()) if shard is not None else 0)
+    bytes_per = {k: v * layers for k, v in algorithmic_bytes(E_local, rows, F).items()}
+    ideal_per = {k: v * layers for k, v in ideal_cache_bytes(E_local, table_rows, F).items()}
+    workload = headline_name(args)
+    roofline = gather_roofline(kernel_ms, bytes_per, ideal_per, f"{workload} n_gpus={world}", launches_per_step)
+    if world > 1:
+        roofline["kernel"] = f"rank 0: {roofline['kernel']} (owned-source + ghost-source passes)"
 
-    result = {
-        "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args), "num_nodes": N, "num_edges": E, "features": F,
-                   "index_dtype": "int64", "max_degree": int(graph.native_plan(transpose=True).info["max_degree"]),
-                   "l2": "inputs exceed L2 (features and indices are each > 126 MB)", "plan_ms": round(plan_ms, 2)},
-        "roofline": roofline, "gpu_launches": int(launches), "clocks": clocks,
-    }
+    config = {"workload": workload, "num_nodes": N, "num_edges": E, "layers": layers, "features": F,
+              "edges_traversed_per_step": traversed, "index_dtype": "int64", "max_degree": max_degree,
+              "partition": "contiguous destination ranges, balanced node counts (the reference's owned_range rule)",
+              "l2": "inputs exceed L2 (feature table and index arrays are each far above 126 MB)",
+              "setup_s": round(setup_s, 2)}
+    if shard is not None:
+        stats = torch.tensor([E_local, rows, int(shard.ghosts.numel()), int(shard.edges_ghost.numel())],
+                             device=device, dtype=torch.int64)
+        gathered = [torch.empty_like(stats) for _ in range(world)]
+        dist.all_gather(gathered, stats)
+        phases = runtime.phase_times()
+        runtime.trace = False
+        names = sorted(phases)
+        mine = torch.tensor([phases[k] / args.steps for k in names] + [ms_mine], device=device, dtype=torch.float64)
+        everyone = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        config.update({
+            "waves": len(shard.waves),
+            "per_rank_edges_rows_ghosts_ghostedges": torch.stack(gathered).tolist(),
+            "halo_bytes_per_layer_rank0": int(shard.ghosts.numel()) * F * 4,
+            "phase_ms_per_rank": {name: [round(float(r[i]), 3) for r in everyone]
+                                  for i, name in enumerate(names + ["step (own clock)"])}})
 
     if args.kernel_table:
-        kernel_table(lambda: step(x, weight, lin), 0)
-    if not args.no_e2e:
-        result["e2e"] = run_e2e(args, step, x, weight, lin, E)
-    if not args.no_cpu_baseline:
-        result["cpu_baseline"] = cpu_baseline(args, row_ptr.cpu(), col.cpu(), weight.detach().cpu(),
-                                              x.detach().cpu(), lin.detach().cpu(), steps=1, warmup=0)
-    print(json.dumps(result), flush=True)
+        kernel_table(step, rank)
+    e2e = None if args.no_e2e else run_e2e(args, step, x, weight, linears, traversed, world)
+    result = {
+        "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+        "roofline": roofline, "gpu_launches": int(launches), "clocks": clocks,
+    }
+    if check is not None:
+        result["check"] = check
+    if e2e is not None:
+        result["e2e"] = e2e
+    failed = check is not None and not check["ok"]
+    if rank == 0 and world == 1 and not failed and not args.no_cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline_halo(args, row_ptr, col, weight, x, linears, steps=1, warmup=0,
+                                                   seconds=args.cpu_sample_seconds)
+    # free the headline workload before the other configurations run
+    del x, weight, linears, ones, row_ptr, col, graph, layer, step, forward, shard
+    torch.cuda.empty_cache()
+    if rank == 0 and world == 1 and not failed and not args.no_extra:
+        from baseline import bench_extra
+
+        result["extra"] = bench_extra.run_all(args, device, sys.modules[__name__])
+    if rank == 0:
+        print(json.dumps(result), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if failed:
+        raise SystemExit(f"verification failed: {check['worst']} exceeds its bound by {check['max_excess']:.3e}")
 
 
 def kernel_table(run, rank, steps=2):
@@ -453,181 +580,31 @@ def kernel_table(run, rank, steps=2):
     print(f"---- rank {rank}: device time over {steps} steps\n{table}", file=sys.stderr, flush=True)
 
 
-def instrument(ops, timings, recording):
-    """Wraps the three kernel entry points with CUDA events on the launching stream."""
-    def timed(name, function):
-        def wrapper(*a, **k):
-            if not recording["on"]:
-                return function(*a, **k)
-            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            result = function(*a, **k)
-            stop.record()
-            timings[name].append((start, stop))
-            return result
-        return wrapper
-
-    ops.csr_reduce_forward = timed("fwd", ops.csr_reduce_forward)
-    ops.csr_reduce_backward_dx = timed("dx", ops.csr_reduce_backward_dx)
-    ops.csr_reduce_backward_dw = timed("dw", ops.csr_reduce_backward_dw)
-
-
-def run_native_multi(args, rank, world, device):
-    """N > 1: the same GCN layer on a graph that grows with N (weak scaling:
-    2^scale * N nodes), partitioned into N contiguous destination ranges with
-    balanced cost (edges + 32 per row); features of ghost rows are exchanged with NCCL
-    send/recv every step (forward) and their cotangents sent back (backward);
-    the linear weights are replicated and their gradient all-reduced."""
-    import math
-
-    import torch.distributed as dist
-
-    import tiga as tg
-    from tiga import _native, ops
-    from baseline import synthetic as syn
-    from tiga.distributed.runtime import DistributedRuntime, NCCLTransport, shard_plan_for
-
-    _native.lib()
-    torch.backends.cuda.matmul.allow_tf32 = False
-    scale = args.scale + int(round(math.log2(world)))
-    F = args.features
-    row_ptr, col = syn.rmat_csr(scale, args.edge_factor, seed=args.seed, symmetrize=True, device=device,
-                                relabel=args.labels == "random")
-    N, E = row_ptr.numel() - 1, col.numel()
-    graph = tg.Graph.from_csr(row_ptr, col, num_src=N).halo(
-        tg.DeviceMesh("cuda", world), partition=tg.ByDestination(balance="cost"))
-    runtime = DistributedRuntime(NCCLTransport(device=device), trace=True)
-
-    class GCNLayer(tg.MessagePassing):
-        reducer = tg.sum()
-
-        def edge(self, src, dst, edge):
-            return edge.weight * src.x
-
-    layer = GCNLayer()
-    with runtime:
-        shard = shard_plan_for(graph, runtime)
-    b, e = shard.begin, shard.end
-    lo, hi = int(row_ptr[b].item()), int(row_ptr[e].item())
-    weight = syn.gcn_norm_weights(row_ptr, col)[lo:hi].clone().requires_grad_()
-    x = syn.normal((N, F), seed=args.seed + 1, device=device)[b:e].clone().requires_grad_()
-    lin = syn.normal((F, F), seed=args.seed + 2, device=device, std=F ** -0.5).requires_grad_()
-    del row_ptr, col
-    graph._row_ptr = graph._col_idx = None      # the shard plan holds the local relations
-    torch.cuda.empty_cache()
-    for g in (shard.graph_own, shard.graph_ghost):
-        g.native_plan(transpose=True)
-
-    timings = {"fwd": [], "dx": [], "dw": []}
-    recording = {"on": False}
-    instrument(ops, timings, recording)
-
-    ones = torch.ones((e - b, lin.shape[1]), dtype=torch.float32, device=device)   # d(out.sum()) / d(out)
-
-    def step(xs, ws, ls):
-        with runtime:
-            agg = layer(graph=graph, src={"x": xs}, dst={}, edge={"weight": ws})
-        out = ops.dense_linear(agg, ls)
-        dx, dw, dl = torch.autograd.grad(out, (xs, ws, ls), ones)
-        dist.all_reduce(dl)
-        return dx, dw, dl
-
-    for _ in range(max(args.warmup, 3)):
-        step(x, weight, lin)
-    torch.cuda.synchronize()
-    runtime.reset_trace()
-    dist.barrier()
-    sampler = ClockSampler(device.index)
-    sampler.start()
-    launches_before = _native.launch_count()
-    recording["on"] = True
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    begin.record()
-    for _ in range(args.steps):
-        step(x, weight, lin)
-    end.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    recording["on"] = False
-    launches = _native.launch_count() - launches_before
-    clocks = sampler.stop()
-    phases = runtime.phase_times()
-    runtime.trace = False
-    phase_names = sorted(phases)
-    mine = torch.tensor([phases[k] / args.steps for k in phase_names] + [begin.elapsed_time(end) / args.steps],
-                        device=device, dtype=torch.float64)
-    all_phases = [torch.empty_like(mine) for _ in range(world)]
-    dist.all_gather(all_phases, mine)
-    elapsed = torch.tensor([begin.elapsed_time(end)], device=device, dtype=torch.float64)
-    dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
-    ms_per_step = float(elapsed.item()) / args.steps
-    value = E / (ms_per_step * 1e-3) / 1e9
-
-    if args.kernel_table:
-        kernel_table(lambda: step(x, weight, lin), rank)
-    stats = torch.tensor([hi - lo, e - b, int(shard.ghosts.numel()), int(shard.edges_ghost.numel())],
-                         device=device, dtype=torch.int64)
-    gathered = [torch.empty_like(stats) for _ in range(world)]
-    dist.all_gather(gathered, stats)
-    e2e = None if args.no_e2e else run_e2e(args, step, x, weight, lin, E, reduce_max=True)
-
-    if rank == 0:
-        kernel_ms = {k: sum(a.elapsed_time(b_) for a, b_ in v) / max(args.steps, 1) for k, v in timings.items()}
-        peak, peak_kind = hbm_peak()
-        local_edges = hi - lo
-        bytes_per = algorithmic_bytes(local_edges, e - b, F)
-        dominant = max(kernel_ms, key=kernel_ms.get)
-        achieved = bytes_per[dominant] / (kernel_ms[dominant] * 1e-3) / 1e9
-        per_rank = torch.stack(gathered).tolist()
-        result = {
-            "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"halo gcn-layer rmat scale={scale} (2^{args.scale} nodes per GPU) "
-                                   f"edge_factor={args.edge_factor} symmetrized dedup F={F} fp32 sum+linear fwd+bwd",
-                       "num_nodes": N, "num_edges": E, "features": F, "vertex_labels": args.labels,
-                       "partition": "contiguous ranges balancing edges + 32 per row",
-                       "per_rank_edges_rows_ghosts_ghostedges": per_rank,
-                       "halo_bytes_per_step_rank0": int(shard.ghosts.numel()) * F * 4 * 2,
-                       "phase_ms_per_rank": {name: [round(float(r[i]), 3) for r in all_phases]
-                                             for i, name in enumerate(phase_names + ["step (own clock)"])},
-                       "l2": "inputs exceed L2"},
-            "roofline": {"bound": "hbm", "kernel": f"rank 0 {dominant} (owned + ghost parts)",
-                         "achieved": round(achieved, 1), "peak": peak, "peak_kind": f"of {peak_kind}",
-                         "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
-                         "kernel_ms": {k: round(v, 4) for k, v in kernel_ms.items()}},
-            "gpu_launches": int(launches), "clocks": clocks,
-        }
-        if e2e is not None:
-            result["e2e"] = e2e
-        print(json.dumps(result), flush=True)
-
-
-def run_e2e(args, step, x, weight, lin, E, reduce_max=False):
+def run_e2e(args, step, x, weight, linears, traversed, world):
     """The step through the public API with HOST inputs and HOST results: every step copies its
     inputs (features, edge weights, linear weights) from pinned host memory to the device and
-    copies the three gradients back to pinned host memory.  Copies run on their own streams so
-    that step i+1's upload and step i-1's download overlap step i's kernels (a three-stage
-    pipeline over double-buffered device and host buffers); the timed region covers every copy."""
+    copies the gradients back to pinned host memory.  Upload, compute and download run on their
+    own streams, so step i+1's upload and step i-1's download overlap step i's kernels; the timed
+    region covers every copy.  Device input buffers are double buffered while they fit."""
     device = x.device
-    host_in = [t.detach().cpu().pin_memory() for t in (x, weight, lin)]
-    host_out = [[torch.empty_like(t).pin_memory() for t in host_in] for _ in range(2)]
-    dev_in = [[torch.empty_like(t, device=device) for t in host_in] for _ in range(2)]
+    host_in = [t.detach().cpu().pin_memory() for t in (x, weight, *linears)]
+    slots = 2 if sum(t.numel() * 4 for t in host_in) < 8e9 else 1
+    packed = sum(m.numel() for m in linears)
+    host_out = [[torch.empty_like(host_in[0]).pin_memory(), torch.empty_like(host_in[1]).pin_memory(),
+                 torch.empty(packed, dtype=torch.float32).pin_memory()] for _ in range(slots)]
+    dev_in = [[torch.empty_like(t, device=device) for t in host_in] for _ in range(slots)]
     h2d = sum(t.numel() * t.element_size() for t in host_in)
     d2h = sum(t.numel() * t.element_size() for t in host_out[0])
     compute = torch.cuda.current_stream(device)
     upload, download = torch.cuda.Stream(device), torch.cuda.Stream(device)
 
     def run(steps):
-        uploaded = [None, None]
-        computed = [None, None]
-        downloaded = [None, None]
+        uploaded, computed, downloaded = [None] * slots, [None] * slots, [None] * slots
 
         def start_upload(i):
-            slot = i & 1
+            slot = i % slots
             with torch.cuda.stream(upload):
-                if computed[slot] is not None:           # step i-2 has read this input slot
+                if computed[slot] is not None:           # the step that read this input slot is done
                     upload.wait_event(computed[slot])
                 for d, h in zip(dev_in[slot], host_in):
                     d.copy_(h, non_blocking=True)
@@ -635,25 +612,28 @@ def run_e2e(args, step, x, weight, lin, E, reduce_max=False):
 
         start_upload(0)
         for i in range(steps):
-            slot = i & 1
-            if i + 1 < steps:
+            slot = i % slots
+            if slots > 1 and i + 1 < steps:
                 start_upload(i + 1)
             compute.wait_event(uploaded[slot])
             leaves = [d.detach().requires_grad_() for d in dev_in[slot]]
-            grads = step(*leaves)
+            grads = step(leaves[0], leaves[1], leaves[2:])
             computed[slot] = compute.record_event()
+            if slots == 1 and i + 1 < steps:
+                start_upload(i + 1)
             with torch.cuda.stream(download):
                 download.wait_event(computed[slot])
                 if downloaded[slot] is not None:
-                    downloaded[slot].synchronize()        # host buffer of step i-2 is free again
+                    downloaded[slot].synchronize()        # the host buffer is free again
                 for h, g in zip(host_out[slot], grads):
                     g.record_stream(download)
                     h.copy_(g, non_blocking=True)
                 downloaded[slot] = download.record_event()
+            del grads, leaves
         torch.cuda.synchronize(device)
 
     run(2)
-    steps = max(4, min(args.steps, 10))
+    steps = max(3, min(args.steps, 5 if h2d > 4e9 else 10))
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize(device)
     begin.record()
@@ -661,100 +641,135 @@ def run_e2e(args, step, x, weight, lin, E, reduce_max=False):
     end.record()
     torch.cuda.synchronize(device)
     ms = begin.elapsed_time(end) / steps
-    if reduce_max:
+    if world > 1:
         import torch.distributed as dist
 
-        slowest = torch.tensor([ms], device=x.device, dtype=torch.float64)
+        slowest = torch.tensor([ms], device=device, dtype=torch.float64)
         dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
         ms = float(slowest.item())
-    return {"value": round(E / (ms * 1e-3) / 1e9, 4), "unit": UNIT, "ms_per_step": round(ms, 3),
+    return {"value": round(traversed / (ms * 1e-3) / 1e9, 4), "unit": UNIT, "ms_per_step": round(ms, 3),
             "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": steps,
-            "pipeline": "upload / compute / download on three streams, double buffered"}
+            "pipeline": f"upload / compute / download on three streams, {slots} input slot(s); bytes are per rank"}
 
 
 # --------------------------------------------------------------------------- CPU arm
-def cpu_step_factory(row_ptr, col, weight, x, lin, rows):
-    """One forward+backward of the GCN layer on the first `rows` destination
-    rows, evaluated by the CPU oracle port (aggregation, dx, dw) and torch.mm
-    (the linear, which is ordinary Torch user code in the reference)."""
-    import numpy as np
-
+def cpu_gcn_step_factory(rp, ci, w, table, linears, layers):
+    """One forward+backward of the GCN layers on a block of destination rows, evaluated by the
+    CPU oracle port (aggregation, dx, dw) and torch.mm (the linear, which is ordinary Torch user
+    code in the reference).  Every layer gathers from the same feature table (a sample of rows
+    cannot produce the hidden features of all its neighbours; the work per layer is the same)."""
     from oracle import oracle
 
-    rp = row_ptr[: rows + 1].numpy().copy()
-    edges = int(rp[-1])
-    ci = col[:edges].numpy().copy()
-    w = weight[:edges].numpy().copy()
-    xn = x.numpy()
-    n_src = x.shape[0]
+    rows = rp.shape[0] - 1
+    n_src = table.shape[0]
     t_ptr, t_col, order = oracle.csr_transpose(rp, ci, n_src)
-    ones = torch.ones(rows, lin.shape[1])
+    mats = [m.detach().cpu() for m in linears]
+    ones = torch.ones(rows, mats[0].shape[1])
 
     def step():
-        agg = oracle.wsum_fwd(rp, ci, xn, w)
-        agg_t = torch.from_numpy(agg)
-        out = agg_t @ lin
-        d_agg = ones @ lin.t()
-        d_lin = agg_t.t() @ ones
-        d_agg_n = d_agg.numpy()
-        dx = oracle.wsum_bwd_dx_pre(rp, t_ptr, t_col, order, n_src, d_agg_n, w)
-        dw = oracle.wsum_bwd_dw(rp, ci, d_agg_n, xn)
-        return out, dx, dw, d_lin
+        results = []
+        for k in range(layers):
+            agg = oracle.wsum_fwd(rp, ci, table, w)
+            agg_t = torch.from_numpy(agg)
+            out = agg_t @ mats[k]
+            d_agg = ones @ mats[k].t()
+            d_lin = agg_t.t() @ ones
+            d_agg_n = d_agg.numpy()
+            dx = oracle.wsum_bwd_dx_pre(rp, t_ptr, t_col, order, n_src, d_agg_n, w)
+            dw = oracle.wsum_bwd_dw(rp, ci, d_agg_n, table)
+            results.append((out, dx, dw, d_lin))
+        return results
 
-    return step, edges
+    return step
 
 
-def cpu_baseline(args, row_ptr, col, weight, x, lin, steps, warmup):
+def cpu_sample(row_ptr, col, weight, feature_rows, rows):
+    """The first `rows` destination rows with their edges, sources renumbered onto the compact
+    table of the feature rows they read (numpy arrays on the host).  `feature_rows(ids)` returns
+    the feature rows of global ids as a tensor."""
+    edges = int(row_ptr[rows].item())
+    rp = row_ptr[:rows + 1].cpu().numpy().copy()
+    sources, compact = torch.unique(col[:edges], return_inverse=True)
+    table = feature_rows(sources).cpu().numpy()
+    return rp, compact.cpu().numpy(), weight.detach()[:edges].cpu().numpy().copy(), table, edges
+
+
+def cpu_baseline_rows(row_ptr, col, weight, feature_rows, linears, steps, warmup, seconds):
+    """Oracle port on the first rows of a graph, sized from a probe so that the whole leg takes
+    about `seconds`.  Uses every host core."""
     from oracle import oracle
 
     oracle.build()
+    cores = os.cpu_count() or 1
+    oracle.set_num_threads(cores)        # a launcher may have exported OMP_NUM_THREADS=1
+    torch.set_num_threads(cores)
     cores = oracle.num_threads()
-    torch.set_num_threads(max(cores, 1))
     N = row_ptr.numel() - 1
-    # size the sample from a small probe so the whole leg stays bounded
-    probe_rows = max(N // 64, 1)
-    probe, probe_edges = cpu_step_factory(row_ptr, col, weight, x, lin, probe_rows)
+    layers = len(linears)
+
+    def make(rows):
+        rp, ci, w, table, edges = cpu_sample(row_ptr, col, weight, feature_rows, rows)
+        return cpu_gcn_step_factory(rp, ci, w, table, linears, layers), edges, table.shape[0]
+
+    probe_rows = max(min(N // 64, 1 << 14), 1)
+    probe, probe_edges, _ = make(probe_rows)
     t0 = time.perf_counter()
     probe()
     probe_s = time.perf_counter() - t0
-    budget = args.cpu_sample_seconds / max(steps + warmup, 1)
-    E = col.numel()
-    target_edges = min(E, int(probe_edges * budget / max(probe_s, 1e-6)))
-    rows = int(torch.searchsorted(row_ptr, torch.tensor(target_edges), right=True).item()) - 1
+    budget = seconds / max(steps + warmup, 1)
+    target = min(int(col.numel()), int(probe_edges * budget / max(probe_s, 1e-6)))
+    rows = int(torch.searchsorted(row_ptr, torch.tensor(target, device=row_ptr.device), right=True).item()) - 1
     rows = max(min(rows, N), probe_rows)
-    step, edges = cpu_step_factory(row_ptr, col, weight, x, lin, rows)
+    step, edges, table_rows = make(rows)
     for _ in range(warmup):
         step()
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
-    seconds = (time.perf_counter() - t0) / steps
-    return {"value": round(edges / seconds / 1e9, 5), "unit": UNIT, "cores": cores, "kind": "port",
-            "seconds_per_step": round(seconds, 3),
-            "sample": f"first {rows} of {N} destination rows ({edges} of {E} edges), full feature matrix"}
+    per_step = (time.perf_counter() - t0) / steps
+    return {"value": round(layers * edges / per_step / 1e9, 5), "unit": UNIT, "cores": cores, "kind": "port",
+            "seconds_per_step": round(per_step, 3),
+            "sample": f"first {rows} of {N} held destination rows ({edges} of {col.numel()} held edges) x {layers} "
+                      f"layer(s), gathering from the {table_rows} feature rows those edges read"}
+
+
+def cpu_baseline_halo(args, row_ptr, col, weight, x, linears, steps, warmup, seconds):
+    return cpu_baseline_rows(row_ptr, col, weight, lambda ids: x.detach().index_select(0, ids), linears,
+                             steps, warmup, seconds)
 
 
 def run_reference(args):
-    """CPU arm: the oracle port on the host cores, same workload and metric."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """CPU arm: the oracle port (the reference's MLIR/LLVM CPU path cannot be built here and its
+    Python evaluator cannot travel to the GPU box) on all host cores, same workload and metric.
+    The sample's inputs are generated on the GPU when one is present (generation is not timed) and
+    copied to the host; under a multi-rank launch rank 0 alone works."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
     from baseline import synthetic as syn
 
-    row_ptr, col = syn.rmat_csr(args.scale, args.edge_factor, seed=args.seed, symmetrize=True, device="cpu")
-    n = row_ptr.numel() - 1
-    weight = syn.gcn_norm_weights(row_ptr, col)
-    x = syn.normal((n, args.features), seed=args.seed + 1)
-    lin = syn.normal((args.features, args.features), seed=args.seed + 2, std=args.features ** -0.5)
-    args.cpu_sample_seconds = 60.0
-    base = cpu_baseline(args, row_ptr, col, weight, x, lin, steps=args.steps, warmup=args.warmup)
+    device = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    if device.type != "cuda":
+        args.scale = min(args.scale, 20)          # generating 2^25 * 16 edges on host cores takes many minutes
+    N, F = 1 << args.scale, args.features
+    held = max(N // 64, 1)                         # a block of rows larger than any sample the time budget allows
+    row_ptr, col = syn.rmat_csr_rows(args.scale, args.edge_factor, 0, held, seed=args.seed, symmetrize=True,
+                                     relabel=args.labels == "random", device=device)
+    # source degrees outside the held block are unknown here; the graph-wide mean stands in for them
+    # (a weight's value does not change the work that is timed)
+    degree = torch.full((N,), float(col.numel()) / held, device=device)
+    degree[:held] = (row_ptr[1:] - row_ptr[:-1]).clamp(min=1).float()
+    weight = syn.gcn_norm_weights_rows(row_ptr, col, degree, 0)
+    linears = [syn.normal((F, F), seed=args.seed + 2 + k, std=F ** -0.5) for k in range(args.layers)]
+    steps = max(args.steps, 1)
+    base = cpu_baseline_rows(
+        row_ptr, col, weight, lambda ids: syn.normal_rows(0, 0, F, seed=args.seed + 1, device=device, ids=ids),
+        linears, steps=steps, warmup=args.warmup, seconds=min(150.0, max(45.0, 8.0 * (steps + args.warmup))))
     value = base["value"]
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(base["seconds_per_step"] * 1e3, 3),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args), "num_nodes": n, "num_edges": col.numel(),
-                   "features": args.features},
+        "steps": steps, "warmup": args.warmup, "ms_per_step": round(base["seconds_per_step"] * 1e3, 3),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": headline_name(args), "num_nodes": N, "layers": args.layers, "features": F},
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
@@ -763,9 +778,16 @@ def run_reference(args):
 def main():
     args = parse_args()
     if args.impl == "reference":
-        run_reference(args)
-    else:
-        run_native(args)
+        return run_reference(args)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    if args.workload == "halo-gcn":
+        return run_halo_gcn(args)
+    from baseline import bench_extra
+
+    torch.cuda.set_device(0)
+    print(json.dumps(bench_extra.run_one(args.workload, args, torch.device("cuda", 0), sys.modules[__name__])),
+          flush=True)
 
 
 if __name__ == "__main__":

@@ -176,7 +176,10 @@ TGB_API int32_t tgb_csr_reduce_fwd(const tgb_csr_plan *plan, int32_t reducer,
  * (python/tiga/interop/torch/message_passing.py:386-409) and
  * compile_source_vjp (python/tiga/interop/torch/relation_vjp.py:45-105).
  * MEAN: dy rows are divided by the destination's row length first (done into
- * scratch).  MAX: only the winning edge of each (row, element) contributes. */
+ * scratch).  MAX: only the winning edge of each (row, element) contributes.
+ * SUM / MEAN with weights: a first pass writes the weights in transposed order
+ * into scratch (4 bytes per edge, included in tgb_csr_plan_scratch_bytes for
+ * direction 1) so that the gather reads them in order. */
 TGB_API int32_t tgb_csr_reduce_bwd_dx(const tgb_csr_plan *plan, int32_t reducer,
                                       const void *dy, const void *w,
                                       const void *aux, void *dx, int64_t F,
@@ -333,8 +336,12 @@ TGB_API int32_t tgb_linear_f32(const void *a, const void *b_t, void *out,
 /* Weight gradient of the linear: dw[K, N] = a[M, K]^T @ dout[M, N], tensor
  * cores (tcgen05, 3xTF32), deterministic split over the M rows: every
  * persistent CTA accumulates its row tiles in tensor memory and writes one
- * partial [K, N] matrix into `partial` (tgb_linear_dw_partials(M) matrices of
- * K*N floats), a second kernel adds them in CTA order.  K = 128, N in {64,128}. */
+ * partial [128, N] matrix into `partial`, a second kernel adds the first K rows
+ * of them in CTA order; more than 8192 rows per CTA are processed in several
+ * such rounds whose results are added in order (bounds the rounding of the
+ * round-toward-zero accumulators).  `partial` must hold
+ * tgb_linear_dw_partials(M) matrices of 128*N floats.
+ * K in {32, 64, 96, 128}, N in {64, 128}. */
 TGB_API int32_t tgb_linear_dw_f32(const void *a, const void *dout, void *dw,
                                   void *partial, uint64_t partial_bytes,
                                   int64_t M, int32_t K, int32_t N,

@@ -71,7 +71,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, balance, result_dir):
+def _worker(rank, world, port, balance, result_dir, shard_only=False, waves=1):
     for path in (ROOT, os.path.join(ROOT, "tiga-lang_b200")):
         sys.path.insert(0, path)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -95,11 +95,23 @@ def _worker(rank, world, port, balance, result_dir):
         x = torch.randn(n, F, generator=gen)
         w = torch.rand(col.numel(), generator=gen)
         dy = torch.randn(n, F, generator=gen)
-        graph = tg.Graph.from_csr(row_ptr, col, num_src=n).halo(
-            tg.DeviceMesh("cpu", world), partition=tg.ByDestination(balance=balance))
-        runtime = DistributedRuntime(ProcessGroupTransport(), backend=OracleBackend())
+        if shard_only:
+            # every rank holds nothing but its own block of rows, generated without the whole graph
+            first, last = model.owned_range(n, world, rank)
+            block_ptr, block_col = syn.rmat_csr_rows(7, 6, first, last, seed=13, chunk=256)
+            assert torch.equal(block_col, col[int(row_ptr[first]):int(row_ptr[last])])
+            graph = tg.Graph.from_csr_shard(block_ptr, block_col, num_nodes=n, first_row=first).halo(
+                tg.DeviceMesh("cpu", world))
+            with pytest.raises(RuntimeError):
+                tg.Graph.from_csr_shard(block_ptr, block_col, num_nodes=n, first_row=first).resolve_csr()
+        else:
+            graph = tg.Graph.from_csr(row_ptr, col, num_src=n).halo(
+                tg.DeviceMesh("cpu", world), partition=tg.ByDestination(balance=balance))
+        runtime = DistributedRuntime(ProcessGroupTransport(), backend=OracleBackend(), waves=waves)
         with runtime:
             shard = shard_plan_for(graph, runtime)
+            assert len(shard.waves) == min(waves, world - 1)
+            assert sorted(p for pairs, _ in shard.waves for p, _ in pairs) == [p for p in range(world) if p != rank]
             b, e = shard.begin, shard.end
             lo, hi = int(row_ptr[b]), int(row_ptr[e])
             xs = x[b:e].clone().requires_grad_()
@@ -131,11 +143,13 @@ def _worker(rank, world, port, balance, result_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,balance", ((2, "auto"), (3, "auto"), (2, "edges"), (3, "cost")))
-def test_sharded_weighted_sum_matches_single_process(tmp_path, oracle, world, balance):
+@pytest.mark.parametrize("world,balance,shard_only,waves", (
+    (2, "auto", False, 1), (3, "auto", False, 2), (2, "edges", False, 1), (3, "cost", False, 1),
+    (4, "auto", True, 2), (4, "auto", False, 3)))
+def test_sharded_weighted_sum_matches_single_process(tmp_path, oracle, world, balance, shard_only, waves):
     port = _free_port()
-    mp.start_processes(_worker, args=(world, port, balance, str(tmp_path)), nprocs=world, join=True,
-                       start_method="spawn")
+    mp.start_processes(_worker, args=(world, port, balance, str(tmp_path), shard_only, waves), nprocs=world,
+                       join=True, start_method="spawn")
     sys.path.insert(0, os.path.join(ROOT, "tiga-lang_b200"))
     from baseline import synthetic as syn
 
@@ -204,3 +218,84 @@ def test_peer_leaving_between_steps_surfaces_as_an_error(tmp_path):
         process.join(90)
         assert not process.is_alive(), "a rank is still waiting: the failure did not surface"
     assert (tmp_path / "rank0.txt").read_text().startswith("raised")
+
+
+def _verify_worker(rank, world, port, result_dir, corrupt):
+    """Two-layer GCN over shard-only graphs with the oracle backend, then the bench's in-run
+    verification; with `corrupt` the hidden rows one rank sends to its peers arrive damaged."""
+    for path in (ROOT, os.path.join(ROOT, "tiga-lang_b200")):
+        sys.path.insert(0, path)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import tiga as tg
+        from baseline import synthetic as syn
+        from baseline import verify
+        from oracle import oracle
+        from tiga.distributed import model
+        from tiga.distributed.runtime import DistributedRuntime, ProcessGroupTransport
+
+        class WeightedSum(tg.MessagePassing):
+            reducer = tg.sum()
+
+            def edge(self, src, dst, edge):
+                return edge.weight * src.x
+
+        scale, factor, F, seed = 9, 8, 8, 21
+        n = 1 << scale
+        first, last = model.owned_range(n, world, rank)
+        row_ptr, col = syn.rmat_csr_rows(scale, factor, first, last, seed=seed, relabel=True)
+        pieces = [torch.zeros(n // world, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(pieces, row_ptr.diff())
+        degree = torch.cat(pieces)
+        weight = syn.gcn_norm_weights_rows(row_ptr, col, degree, first).requires_grad_()
+        x = syn.normal_rows(first, last, F, seed=seed + 1).requires_grad_()
+        W1 = syn.normal((F, F), seed=3, std=F ** -0.5).requires_grad_()
+        W2 = syn.normal((F, F), seed=4, std=F ** -0.5).requires_grad_()
+        graph = tg.Graph.from_csr_shard(row_ptr, col, num_nodes=n, first_row=first).halo(tg.DeviceMesh("cpu", world))
+        layer = WeightedSum()
+        ones = torch.ones(last - first, F)
+        class LossyBackend(OracleBackend):
+            """Damages the rows rank 1 sends in the second exchange: a stand-in for a transport fault."""
+            calls = 0
+
+            def pack_rows(self, rows, ids):
+                packed = rows.index_select(0, ids)
+                type(self).calls += 1
+                if corrupt and rank == 1 and type(self).calls > world - 1:
+                    packed = packed + 1e-3
+                return packed
+
+        with DistributedRuntime(ProcessGroupTransport(), backend=LossyBackend(), waves=2):
+            agg1 = layer(graph=graph, src={"x": x}, dst={}, edge={"weight": weight})
+            h1 = agg1 @ W1
+            agg2 = layer(graph=graph, src={"x": h1}, dst={}, edge={"weight": weight})
+            out = agg2 @ W2
+            dx, dw, dW1, dW2, d_agg1, d_h1, d_agg2 = torch.autograd.grad(
+                out, (x, weight, W1, W2, agg1, h1, agg2), ones)
+        dist.all_reduce(dW1)
+        dist.all_reduce(dW2)
+        tensors = {"agg1": agg1, "h1": h1, "agg2": agg2, "out": out, "d_agg1": d_agg1, "d_h1": d_h1,
+                   "d_agg2": d_agg2, "dx": dx, "dw": dw, "dW1": dW1, "dW2": dW2}
+        report = verify.check_two_layer_gcn(
+            oracle, row_ptr=row_ptr, col_idx=col, first_row=first, num_nodes=n, weight=weight,
+            feature_of=lambda ids: syn.normal_rows(0, 0, F, seed=seed + 1, ids=ids), tensors=tensors,
+            linears=(W1, W2), world=world)
+        with open(os.path.join(result_dir, f"rank{rank}.txt"), "w") as handle:
+            handle.write(f"{int(report['ok'])} {report['worst']} {report['rows']} {report['edges']}")
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("corrupt", (False, True))
+def test_in_run_verification_passes_and_detects_a_wrong_ghost_row(tmp_path, oracle, corrupt):
+    world = 2
+    mp.start_processes(_verify_worker, args=(world, _free_port(), str(tmp_path), corrupt), nprocs=world, join=True,
+                       start_method="spawn")
+    reports = [(tmp_path / f"rank{r}.txt").read_text().split(" ", 1) for r in range(world)]
+    if corrupt:
+        assert reports[0][0] == "0" and reports[0][1].startswith("agg2"), reports   # rank 0 read the damaged rows
+    else:
+        assert all(ok == "1" for ok, _ in reports), reports

@@ -46,8 +46,9 @@ def test_values_that_stress_the_split(oracle):
     ops.check_async_errors()
 
 
-def test_backward_matches_oracle(oracle):
-    M, K, N = 5000, 128, 128
+@pytest.mark.parametrize("K,N", ((128, 128), (64, 64), (64, 128), (128, 64)))
+def test_backward_matches_oracle(oracle, K, N):
+    M = 5000
     a = syn.normal((M, K), seed=1)
     w = syn.normal((K, N), seed=2, std=K ** -0.5)
     dy = syn.normal((M, N), seed=3)
@@ -62,9 +63,9 @@ def test_backward_matches_oracle(oracle):
 
 
 @pytest.mark.parametrize("M", (1, 31, 32, 33, 4777, 200000))
-@pytest.mark.parametrize("N", (64, 128))
-def test_weight_gradient_kernel(oracle, M, N):
-    a = syn.normal((M, 128), seed=M)
+@pytest.mark.parametrize("K,N", ((128, 64), (128, 128), (64, 64), (32, 128), (96, 64)))
+def test_weight_gradient_kernel(oracle, M, K, N):
+    a = syn.normal((M, K), seed=M)
     dy = syn.normal((M, N), seed=M + 1)
     dw = ops._linear_dw_raw(a.cuda(), dy.cuda())
     again = ops._linear_dw_raw(a.cuda(), dy.cuda())
@@ -77,3 +78,5 @@ def test_weight_gradient_kernel(oracle, M, N):
 def test_unsupported_shapes_raise():
     with pytest.raises(NotImplementedError):
         ops.dense_linear(torch.zeros(4, 100, device="cuda"), torch.zeros(100, 128, device="cuda"))
+    with pytest.raises(NotImplementedError):     # K = 32 has no d(a) kernel: refused up front, never a library fallback
+        ops.dense_linear(torch.zeros(4, 32, device="cuda", requires_grad=True), torch.zeros(32, 128, device="cuda"))

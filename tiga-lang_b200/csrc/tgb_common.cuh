@@ -47,6 +47,15 @@ extern std::atomic<int64_t> g_launches;
 constexpr int kSplitThreshold = 512;
 constexpr int kSegmentEdges = 256;
 
+// One unit of work of the CSR kernels: a whole row, or one segment of a split
+// row.  16 bytes, so a thread group fetches its assignment with one 128-bit
+// load instead of chasing order[] -> row_ptr[row], row_ptr[row + 1].
+struct WorkItem {
+  long long beg;   // first edge
+  int32_t row;     // row the edges belong to
+  int32_t count;   // number of edges
+};
+
 // One traversal direction: rows are destinations (forward, dw) or sources
 // (dx over the transposed relation).
 struct Side {
@@ -56,6 +65,7 @@ struct Side {
   const int32_t *order = nullptr;     // [n_rows] long rows first, then buckets
   const int32_t *seg_row = nullptr;   // [n_seg] ordinal of the long row
   const int32_t *seg_ptr = nullptr;   // [n_long+1] first segment of long row
+  const WorkItem *items = nullptr;    // [n_seg + n_rows - n_long] segments first, then rows in bucket order
   int64_t n_rows = 0;
   int64_t n_long = 0;
   int64_t n_seg = 0;
@@ -108,32 +118,29 @@ struct WorkList {
   const int32_t *order;
   const int32_t *seg_row;
   const int32_t *seg_ptr;
+  const WorkItem *items;
   int64_t n_rows, n_long, n_seg;
 };
 
 inline WorkList work_list(const Side &side) {
-  return WorkList{side.ptr, side.idx, side.eid, side.order, side.seg_row, side.seg_ptr,
+  return WorkList{side.ptr, side.idx, side.eid, side.order, side.seg_row, side.seg_ptr, side.items,
                   side.n_rows, side.n_long, side.n_seg};
+}
+
+// The (row, edge range) of group `gid`: one 128-bit load of its work item.
+__device__ __forceinline__ void load_work_item(const WorkItem *items, int64_t n_seg, int64_t gid,
+                                               int64_t &row, int64_t &beg, int64_t &end, int64_t &seg) {
+  const int4 raw = __ldg(reinterpret_cast<const int4 *>(items) + gid);
+  beg = (int64_t)(((unsigned long long)(unsigned)raw.y << 32) | (unsigned long long)(unsigned)raw.x);
+  row = raw.z;
+  end = beg + raw.w;
+  seg = gid < n_seg ? gid : -1;
 }
 
 template <typename PtrT>
 __device__ __forceinline__ void decode_group(const WorkList &w, int64_t gid, int64_t &row,
                                              int64_t &beg, int64_t &end, int64_t &seg) {
-  const PtrT *ptr = static_cast<const PtrT *>(w.ptr);
-  if (gid < w.n_seg) {
-    const int32_t lr = w.seg_row[gid];
-    row = w.order[lr];
-    const int64_t k = gid - w.seg_ptr[lr];
-    const int64_t rb = (int64_t)ptr[row], re = (int64_t)ptr[row + 1];
-    beg = rb + k * kSegmentEdges;
-    end = beg + kSegmentEdges < re ? beg + kSegmentEdges : re;
-    seg = gid;
-  } else {
-    row = w.order[w.n_long + (gid - w.n_seg)];
-    beg = (int64_t)ptr[row];
-    end = (int64_t)ptr[row + 1];
-    seg = -1;
-  }
+  load_work_item(w.items, w.n_seg, gid, row, beg, end, seg);
 }
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }

@@ -35,6 +35,17 @@ namespace {
 #ifndef TGB_U32
 #define TGB_U32 4
 #endif
+// Index pipeline of the gather kernel (ids of batch b+2 load while batch b is gathered): measured
+// on B200 at 128 / 64 floats per row, forward 2.36 -> 2.31 / 1.35 -> 1.27 ms and the transposed pass
+// 2.93 -> 2.70 / 1.93 -> 1.70 ms on the 60 M-edge R-MAT; the per-edge dot kernel measured 2 % slower
+// with the same pipeline (2.42 -> 2.47 ms), so it keeps the plain loop.
+#ifndef TGB_PREFETCH
+#define TGB_PREFETCH 1
+#endif
+#ifndef TGB_PREFETCH_DOT
+#define TGB_PREFETCH_DOT 0
+#endif
+
 constexpr int kBlock = TGB_BLOCK;
 
 enum Mode { kSum = 0, kMax = 2 };
@@ -46,6 +57,7 @@ struct GatherArgs {
   const int32_t *order;   // plan row order
   const int32_t *seg_row; // segment -> long-row ordinal
   const int32_t *seg_ptr; // long-row ordinal -> first segment
+  const WorkItem *items;  // one per thread group: (first edge, row, edge count)
   int64_t n_rows, n_long, n_seg;
   const float *x;         // gathered rows [*, F]
   const float *w;         // per-edge weight or null
@@ -66,27 +78,14 @@ __device__ __forceinline__ T shfl_group(unsigned mask, T v, int src, int width) 
   return __shfl_sync(mask, v, src, width);
 }
 
-// Decodes which (row, edge range) group `gid` owns.  Groups [0, n_seg) own
-// segments of long rows; the rest own whole rows in bucket order.
+// Which (row, edge range) group `gid` owns: groups [0, n_seg) own segments of
+// long rows, the rest whole rows in bucket order.  The plan stores the answer
+// as one 16-byte work item per group.
 template <typename PtrT>
 __device__ __forceinline__ void decode_work(const GatherArgs &a, int64_t gid,
                                             int64_t &row, int64_t &beg,
                                             int64_t &end, int64_t &seg) {
-  const PtrT *ptr = static_cast<const PtrT *>(a.ptr);
-  if (gid < a.n_seg) {
-    int32_t lr = a.seg_row[gid];
-    row = a.order[lr];
-    int64_t k = gid - a.seg_ptr[lr];
-    int64_t rb = (int64_t)ptr[row], re = (int64_t)ptr[row + 1];
-    beg = rb + k * kSegmentEdges;
-    end = beg + kSegmentEdges < re ? beg + kSegmentEdges : re;
-    seg = gid;
-  } else {
-    row = a.order[a.n_long + (gid - a.n_seg)];
-    beg = (int64_t)ptr[row];
-    end = (int64_t)ptr[row + 1];
-    seg = -1;
-  }
+  load_work_item(a.items, a.n_seg, gid, row, beg, end, seg);
 }
 
 __device__ __forceinline__ void max_update(float m, int32_t e, float &acc,
@@ -134,16 +133,32 @@ k_gather_vec(const GatherArgs a) {
     if constexpr (MODE == kMax) arg[v] = make_int4(-1, -1, -1, -1);
   }
 
-  for (int64_t base = beg; base < end; base += G) {
-    const int64_t e = base + lane;
-    int32_t c = 0;
-    float wv = 1.0f;
-    uint32_t my_eid = 0;
-    if (e < end) {
-      c = (int32_t)ld_stream(idx + e);
-      if (W_BY_EID || ARG_FILTER) my_eid = ld_stream(a.eid + e);
-      if (HAS_W) wv = W_BY_EID ? __ldg(a.w + my_eid) : ld_stream(a.w + e);
+  // Index pipeline: while the rows of batch b are gathered, the neighbour ids (and edge ids /
+  // direct weights) of batch b+2 are already loading and the edge-mapped weights of batch b+1,
+  // whose edge ids arrived one batch ago, are issued; no gather waits on an index load after the
+  // first batch of a row.
+  auto load_ids = [&](int64_t at, int32_t &c_, uint32_t &eid_, float &w_) {
+    c_ = 0; eid_ = 0; w_ = 1.0f;
+    const int64_t e_ = at + lane;
+    if (e_ < end) {
+      c_ = (int32_t)ld_stream(idx + e_);
+      if (W_BY_EID || ARG_FILTER) eid_ = ld_stream(a.eid + e_);
+      if (HAS_W && !W_BY_EID) w_ = ld_stream(a.w + e_);
     }
+  };
+  int32_t c, c1, c2;
+  uint32_t my_eid, eid1, eid2;
+  float wv, w1, w2;
+  load_ids(beg, c, my_eid, wv);
+#if TGB_PREFETCH
+  load_ids(beg + G, c1, eid1, w1);
+#endif
+  if (HAS_W && W_BY_EID && beg + lane < end) wv = __ldg(a.w + my_eid);
+  for (int64_t base = beg; base < end; base += G) {
+#if TGB_PREFETCH
+    load_ids(base + 2 * G, c2, eid2, w2);
+    if (HAS_W && W_BY_EID && base + G + lane < end) w1 = __ldg(a.w + eid1);
+#endif
     const int n = (int)(end - base < G ? end - base : G);
     for (int k0 = 0; k0 < n; k0 += U) {
       float4 val[U][VPL];
@@ -198,6 +213,13 @@ k_gather_vec(const GatherArgs a) {
         }
       }
     }
+#if TGB_PREFETCH
+    c = c1; my_eid = eid1; wv = w1;
+    c1 = c2; eid1 = eid2; w1 = w2;
+#else
+    load_ids(base + G, c, my_eid, wv);
+    if (HAS_W && W_BY_EID && base + G + lane < end) wv = __ldg(a.w + my_eid);
+#endif
   }
   if (!active) return;
   if (seg < 0 && a.mean) {
@@ -338,9 +360,24 @@ k_edge_dot_vec(const GatherArgs a, const float *dy, float *dw) {
       win[v] = active ? __ldg(reinterpret_cast<const int4 *>(a.arg_in + row * F + 4 * (lane + v * G)))
                       : make_int4(-1, -1, -1, -1);
   }
+  // the neighbour ids (and mapped edge ids) of the next batch load while this batch is gathered
+  auto load_ids = [&](int64_t at, int32_t &c_, int64_t &slot_) {
+    const int64_t e_ = at + lane;
+    c_ = 0;
+    slot_ = e_;
+    if (e_ < end) {
+      c_ = (int32_t)ld_stream(idx + e_);
+      if (a.eid) slot_ = (int64_t)ld_stream(a.eid + e_);
+    }
+  };
+  int32_t c, c_next = 0;
+  int64_t slot, slot_next = 0;
+  load_ids(beg, c, slot);
   for (int64_t base = beg; base < end; base += G) {
     const int64_t e = base + lane;
-    const int32_t c = e < end ? (int32_t)ld_stream(idx + e) : 0;
+#if TGB_PREFETCH_DOT
+    load_ids(base + G, c_next, slot_next);
+#endif
     const int n = (int)(end - base < G ? end - base : G);
     float mine = 0.0f;
     for (int k0 = 0; k0 < n; k0 += U) {
@@ -375,7 +412,12 @@ k_edge_dot_vec(const GatherArgs a, const float *dy, float *dw) {
         if (lane == k0 + u) mine = p;
       }
     }
-    if (e < end) dw[a.eid ? (int64_t)a.eid[e] : e] = mine;
+    if (e < end) dw[slot] = mine;
+#if TGB_PREFETCH_DOT
+    c = c_next; slot = slot_next;
+#else
+    load_ids(base + G, c, slot);
+#endif
   }
 }
 
@@ -548,6 +590,7 @@ void fill_side(GatherArgs &a, const Side &side) {
   a.order = side.order;
   a.seg_row = side.seg_row;
   a.seg_ptr = side.seg_ptr;
+  a.items = side.items;
   a.n_rows = side.n_rows;
   a.n_long = side.n_long;
   a.n_seg = side.n_seg;
@@ -556,6 +599,21 @@ void fill_side(GatherArgs &a, const Side &side) {
 uint64_t partial_bytes(const Side &side, int32_t reducer, int64_t F) {
   uint64_t b = align_up((uint64_t)side.n_seg * (uint64_t)F * 4, 256);
   return reducer == TGB_REDUCER_MAX ? 2 * b : b;
+}
+
+// dx over the transposed relation needs w[eid[k]] for entry k.  Reading it inside the gather
+// kernel puts a dependent random 4-byte load in front of every row gather; a streaming pass that
+// writes the weights in transposed order first (what the reference's generated VJP keeps as its
+// `jacobian = w[order]`, python/tiga/interop/torch/relation_vjp.py:61-87) lets the gather kernel
+// read them in order.  Measured on the 2^24-node R-MAT with 64 floats per row: 33.0 -> 23.7 ms per
+// transposed pass including the permutation.  The max reducer filters by edge id and keeps the
+// in-kernel lookup.
+bool permute_weights_first(int32_t reducer) { return reducer != TGB_REDUCER_MAX; }
+
+__global__ void k_permute_weights(const float *__restrict__ w, const uint32_t *__restrict__ eid, int64_t E,
+                                  float *__restrict__ out) {
+  const int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (k < E) out[k] = __ldg(w + ld_stream(eid + k));
 }
 
 int32_t check_common(const tgb_csr_plan *plan, int32_t reducer, int64_t F,
@@ -593,6 +651,8 @@ int32_t tgb_csr_plan_scratch_bytes(const tgb_csr_plan *plan, int32_t direction,
     TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "plan has no transposed relation");
   const Side &side = direction == 1 ? plan->bwd : plan->fwd;
   uint64_t b = partial_bytes(side, reducer, feature_elems);
+  if (direction == 1 && permute_weights_first(reducer))
+    b += align_up((uint64_t)plan->num_edges * 4, 256);   // weights in transposed order
   // the mean reducer's backward also stores dy / degree
   if (reducer == TGB_REDUCER_MEAN)
     b += align_up((uint64_t)plan->num_dst * (uint64_t)feature_elems * 4, 256);
@@ -666,7 +726,10 @@ int32_t tgb_csr_reduce_bwd_dx(const tgb_csr_plan *plan, int32_t reducer,
   uint64_t need = part;
   if (reducer == TGB_REDUCER_MEAN)
     need += align_up((uint64_t)plan->num_dst * (uint64_t)F * 4, 256);
-  if (need > 0 && (side.n_seg > 0 || reducer == TGB_REDUCER_MEAN) &&
+  const bool permute = w && permute_weights_first(reducer) && plan->num_edges > 0;
+  const uint64_t permuted_at = need;
+  if (permute) need += align_up((uint64_t)plan->num_edges * 4, 256);
+  if (need > 0 && (side.n_seg > 0 || reducer == TGB_REDUCER_MEAN || permute) &&
       (!scratch || scratch_bytes < need))
     TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "scratch too small: %llu < %llu bytes",
              (unsigned long long)scratch_bytes, (unsigned long long)need);
@@ -699,6 +762,14 @@ int32_t tgb_csr_reduce_bwd_dx(const tgb_csr_plan *plan, int32_t reducer,
   if (reducer == TGB_REDUCER_MAX)
     return w ? launch_gather<int64_t, int32_t, kSum, true, true, true>(a, s, st)
              : launch_gather<int64_t, int32_t, kSum, false, false, true>(a, s, st);
+  if (permute) {
+    float *w_t = (float *)((char *)scratch + permuted_at);
+    k_permute_weights<<<(unsigned)ceil_div(plan->num_edges, 256), 256, 0, st>>>(
+        (const float *)w, side.eid, plan->num_edges, w_t);
+    TGB_LAUNCHED();
+    a.w = w_t;
+    return launch_gather<int64_t, int32_t, kSum, true, false, false>(a, s, st);
+  }
   return w ? launch_gather<int64_t, int32_t, kSum, true, true, false>(a, s, st)
            : launch_gather<int64_t, int32_t, kSum, false, false, false>(a, s, st);
 }

@@ -431,6 +431,7 @@ k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__res
 constexpr int kDwRows = 32;                        // rows (reduction) per tile
 constexpr int kDwBoxBytes = kDwRows * 128;         // one [32 rows x 32 floats] box
 constexpr int kDwMaxBoxes = 8;                     // (K + N) / 32 <= 8
+constexpr int kDwChunkRowsPerCta = 8192;           // rows one accumulator sees before it is written out
 
 struct DwSmem {
   alignas(1024) uint8_t hi[2][kDwMaxBoxes][kDwBoxBytes];   // a blocks first, then dout blocks
@@ -559,11 +560,14 @@ k_linear_dw_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_const
   if (warp == 0) tmem_dealloc(tmem, N);
 }
 
-__global__ void k_sum_dw_partials(const float *__restrict__ partial, int blocks, int elems, float *__restrict__ out) {
+// Adds the CTAs' partial matrices in CTA order (deterministic).  A partial matrix always has 128
+// rows; only the first `elems / N` of them belong to the result.
+__global__ void k_sum_dw_partials(const float *__restrict__ partial, int blocks, int elems, int64_t stride,
+                                  float *__restrict__ out) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= elems) return;
   float acc = 0.0f;
-  for (int b = 0; b < blocks; ++b) acc += partial[(int64_t)b * elems + i];
+  for (int b = 0; b < blocks; ++b) acc += partial[(int64_t)b * stride + i];
   out[i] = acc;
 }
 
@@ -619,8 +623,11 @@ extern "C" int32_t tgb_linear_dw_f32(const void *a, const void *dout, void *dw, 
                                      uint64_t partial_bytes, int64_t M, int32_t K, int32_t N, void *error_flag,
                                      uint64_t stream) {
   if (M < 0) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "negative row count");
-  if (K != 128 || (N != 64 && N != 128))
-    TGB_FAIL(TGB_STATUS_UNSUPPORTED, "tensor-core weight gradient supports K = 128 and N in {64, 128} (got K=%d, N=%d)", K, N);
+  // The MMA always produces a 128-row accumulator.  A narrower `a` (K = 32, 64, 96) is read through a
+  // tensor map of its true width: the boxes beyond column K come back zero-filled by the TMA unit
+  // (no memory traffic), and only the first K rows of the accumulator are summed into dw.
+  if (K <= 0 || K > 128 || K % 32 != 0 || (N != 64 && N != 128))
+    TGB_FAIL(TGB_STATUS_UNSUPPORTED, "tensor-core weight gradient supports K in {32, 64, 96, 128} and N in {64, 128} (got K=%d, N=%d)", K, N);
   if (!a || !dout || !dw || !partial || !error_flag) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
   if (M > (int64_t)INT32_MAX - 256) TGB_FAIL(TGB_STATUS_UNSUPPORTED, "more than 2^31 rows");
   if (M == 0) {
@@ -630,44 +637,68 @@ extern "C" int32_t tgb_linear_dw_f32(const void *a, const void *dout, void *dw, 
   int device = 0, sms = 0;
   TGB_CUDA(cudaGetDevice(&device));
   TGB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-  const int64_t tiles = ceil_div(M > 0 ? M : 1, kDwRows);
-  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  const uint64_t need = (uint64_t)grid * K * N * 4;
+  // The rows are processed in chunks of at most kDwChunkRowsPerCta rows per CTA, one launch per chunk.
+  // A tensor-memory accumulator adds with round-toward-zero, so its error grows with the number of
+  // additions times the size of the running sum; bounding the rows one accumulator sees keeps the
+  // result within a few tens of float32 ulps of sum |a * dout| however large M is.  Chunk results are
+  // added in chunk order (deterministic).
+  const int64_t chunk_rows = (int64_t)sms * kDwChunkRowsPerCta;
+  const int64_t chunks = ceil_div(M, chunk_rows);
+  const int64_t first_tiles = ceil_div(M < chunk_rows ? M : chunk_rows, kDwRows);
+  const unsigned max_grid = (unsigned)(first_tiles < sms ? first_tiles : sms);
+  const uint64_t need = ((uint64_t)max_grid + (chunks > 1 ? (uint64_t)chunks : 0)) * 128 * N * 4;
   if (partial_bytes < need)
     TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "partial buffer too small: %llu < %llu bytes",
              (unsigned long long)partial_bytes, (unsigned long long)need);
-  CUtensorMap map_a, map_d;
-  int32_t rc = make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a, (uint64_t)(M > 0 ? M : 1), (uint64_t)K,
-                                  (uint64_t)K * 4, 32, kDwRows, true);
-  if (rc) return rc;
-  rc = make_tensor_map_2d(&map_d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dout, (uint64_t)(M > 0 ? M : 1), (uint64_t)N,
-                          (uint64_t)N * 4, 32, kDwRows, true);
-  if (rc) return rc;
+  float *cta_partials = (float *)partial;
+  float *chunk_sums = cta_partials + (size_t)max_grid * 128 * N;
   const size_t smem = sizeof(DwSmem) + 1024;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (N == 128) {
-    // the attribute belongs to the current device's context, so it is set on every call (cheap)
+  // the attribute belongs to the current device's context, so it is set on every call (cheap)
+  if (N == 128)
     TGB_CUDA(cudaFuncSetAttribute(k_linear_dw_3xtf32<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k_linear_dw_3xtf32<128><<<grid, kDwThreads, smem, st>>>(map_a, map_d, (float *)partial, M, (int *)error_flag);
-  } else {
-    // the attribute belongs to the current device's context, so it is set on every call (cheap)
+  else
     TGB_CUDA(cudaFuncSetAttribute(k_linear_dw_3xtf32<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k_linear_dw_3xtf32<64><<<grid, kDwThreads, smem, st>>>(map_a, map_d, (float *)partial, M, (int *)error_flag);
+  for (int64_t c = 0; c < chunks; ++c) {
+    const int64_t row0 = c * chunk_rows;
+    const int64_t rows = M - row0 < chunk_rows ? M - row0 : chunk_rows;
+    const int64_t tiles = ceil_div(rows, kDwRows);
+    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+    CUtensorMap map_a, map_d;
+    int32_t rc = make_tensor_map_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (const float *)a + row0 * K,
+                                    (uint64_t)rows, (uint64_t)K, (uint64_t)K * 4, 32, kDwRows, true);
+    if (rc) return rc;
+    rc = make_tensor_map_2d(&map_d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (const float *)dout + row0 * N,
+                            (uint64_t)rows, (uint64_t)N, (uint64_t)N * 4, 32, kDwRows, true);
+    if (rc) return rc;
+    if (N == 128)
+      k_linear_dw_3xtf32<128><<<grid, kDwThreads, smem, st>>>(map_a, map_d, cta_partials, rows, (int *)error_flag);
+    else
+      k_linear_dw_3xtf32<64><<<grid, kDwThreads, smem, st>>>(map_a, map_d, cta_partials, rows, (int *)error_flag);
+    TGB_LAUNCHED();
+    float *target = chunks > 1 ? chunk_sums + (size_t)c * K * N : (float *)dw;
+    k_sum_dw_partials<<<(unsigned)ceil_div((int64_t)K * N, 256), 256, 0, st>>>(cta_partials, (int)grid, K * N,
+                                                                              (int64_t)128 * N, target);
+    TGB_LAUNCHED();
   }
-  TGB_LAUNCHED();
-  k_sum_dw_partials<<<(unsigned)ceil_div((int64_t)K * N, 256), 256, 0, st>>>((const float *)partial, (int)grid, K * N,
-                                                                            (float *)dw);
-  TGB_LAUNCHED();
+  if (chunks > 1) {
+    k_sum_dw_partials<<<(unsigned)ceil_div((int64_t)K * N, 256), 256, 0, st>>>(chunk_sums, (int)chunks, K * N,
+                                                                              (int64_t)K * N, (float *)dw);
+    TGB_LAUNCHED();
+  }
   return TGB_STATUS_OK;
 }
 
-/* number of persistent CTAs (= partial matrices) tgb_linear_dw_f32 uses for M rows */
+/* number of [128, N] float matrices the `partial` scratch of tgb_linear_dw_f32 must hold for M rows */
 extern "C" int32_t tgb_linear_dw_partials(int64_t M, int32_t *count) {
   if (!count) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null output");
   int device = 0, sms = 0;
   TGB_CUDA(cudaGetDevice(&device));
   TGB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-  const int64_t tiles = ceil_div(M > 0 ? M : 1, kDwRows);
-  *count = (int32_t)(tiles < sms ? tiles : sms);
+  if (M < 1) M = 1;
+  const int64_t chunk_rows = (int64_t)sms * kDwChunkRowsPerCta;
+  const int64_t chunks = ceil_div(M, chunk_rows);
+  const int64_t tiles = ceil_div(M < chunk_rows ? M : chunk_rows, kDwRows);
+  *count = (int32_t)((tiles < sms ? tiles : sms) + (chunks > 1 ? chunks : 0));
   return TGB_STATUS_OK;
 }

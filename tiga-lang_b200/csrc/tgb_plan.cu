@@ -147,6 +147,32 @@ __global__ void k_transposed_dst(const PtrT *row_ptr, int64_t num_dst,
   t_dst[k] = (int32_t)lo;
 }
 
+// Work item of group g: segments of split rows first (g < n_seg), then whole
+// rows in bucket order.
+template <typename PtrT>
+__global__ void k_fill_items(const PtrT *ptr, const int32_t *order, const int32_t *seg_row,
+                             const int32_t *seg_ptr, int64_t n_rows, int64_t n_long,
+                             int64_t n_seg, WorkItem *items) {
+  const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= n_seg + (n_rows - n_long)) return;
+  WorkItem it;
+  if (g < n_seg) {
+    const int32_t lr = seg_row[g];
+    const int32_t row = order[lr];
+    const long long rb = (long long)ptr[row], re = (long long)ptr[row + 1];
+    const long long beg = rb + (long long)(g - seg_ptr[lr]) * kSegmentEdges;
+    it.beg = beg;
+    it.row = row;
+    it.count = (int32_t)((beg + kSegmentEdges < re ? beg + kSegmentEdges : re) - beg);
+  } else {
+    const int32_t row = order[n_long + (g - n_seg)];
+    it.beg = (long long)ptr[row];
+    it.row = row;
+    it.count = (int32_t)((long long)ptr[row + 1] - it.beg);
+  }
+  items[g] = it;
+}
+
 __global__ void k_copy_u32(const uint32_t *src, int64_t n, int32_t *dst) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) dst[i] = (int32_t)src[i];
@@ -172,8 +198,8 @@ int bits_for(int64_t n) {
 
 struct Layout {
   // persistent
-  uint64_t order_f, seg_ptr_f, seg_row_f;
-  uint64_t t_ptr, t_dst, eid, order_b, seg_ptr_b, seg_row_b;
+  uint64_t order_f, seg_ptr_f, seg_row_f, items_f;
+  uint64_t t_ptr, t_dst, eid, order_b, seg_ptr_b, seg_row_b, items_b;
   uint64_t persistent_bytes;
   // temp
   uint64_t counters, k0, k1, v0, v1, seg_count, cub, cub_bytes;
@@ -191,6 +217,7 @@ int32_t compute_layout(int64_t num_dst, int64_t num_src, int64_t E, int flags,
   L->order_f = take((uint64_t)(num_dst > 0 ? num_dst : 1) * 4);
   L->seg_ptr_f = take((uint64_t)(long_row_bound(E, num_dst) + 1) * 4);
   L->seg_row_f = take((uint64_t)segment_bound(E, num_dst) * 4);
+  L->items_f = take((uint64_t)(segment_bound(E, num_dst) + num_dst) * sizeof(WorkItem));
   if (flags & TGB_PLAN_TRANSPOSE) {
     L->t_ptr = take((uint64_t)(num_src + 1) * 8);
     L->t_dst = take((uint64_t)(E > 0 ? E : 1) * 4);
@@ -198,6 +225,7 @@ int32_t compute_layout(int64_t num_dst, int64_t num_src, int64_t E, int flags,
     L->order_b = take((uint64_t)(num_src > 0 ? num_src : 1) * 4);
     L->seg_ptr_b = take((uint64_t)(long_row_bound(E, num_src) + 1) * 4);
     L->seg_row_b = take((uint64_t)segment_bound(E, num_src) * 4);
+    L->items_b = take((uint64_t)(segment_bound(E, num_src) + num_src) * sizeof(WorkItem));
   }
   L->persistent_bytes = p;
 
@@ -240,7 +268,7 @@ int32_t compute_layout(int64_t num_dst, int64_t num_src, int64_t E, int flags,
 template <typename PtrT>
 int32_t build_side(const PtrT *ptr, int64_t n_rows, int64_t E, char *temp,
                    const Layout &L, int32_t *order_out, int32_t *seg_ptr_out,
-                   int32_t *seg_row_out, cudaStream_t stream, Side *side) {
+                   int32_t *seg_row_out, WorkItem *items_out, cudaStream_t stream, Side *side) {
   Counters *counters = reinterpret_cast<Counters *>(temp + L.counters);
   uint32_t *k0 = reinterpret_cast<uint32_t *>(temp + L.k0);
   uint32_t *k1 = reinterpret_cast<uint32_t *>(temp + L.k1);
@@ -289,6 +317,13 @@ int32_t build_side(const PtrT *ptr, int64_t n_rows, int64_t E, char *temp,
   side->n_seg = (int64_t)host.n_seg;
   side->min_degree = n_rows > 0 && host.min_degree != LLONG_MAX ? host.min_degree : 0;
   side->max_degree = host.max_degree;
+  side->items = items_out;
+  const int64_t groups = side->n_seg + (n_rows - side->n_long);
+  if (groups > 0) {
+    k_fill_items<PtrT><<<grid_for(groups), kThreads, 0, stream>>>(
+        ptr, order_out, seg_row_out, seg_ptr_out, n_rows, side->n_long, side->n_seg, items_out);
+    TGB_LAUNCHED();
+  }
   return TGB_STATUS_OK;
 }
 
@@ -304,8 +339,8 @@ int32_t create_typed(const IdxT *row_ptr, const IdxT *col_idx, int64_t num_dst,
       row_ptr, num_dst, E, temp, L,
       reinterpret_cast<int32_t *>(persistent + L.order_f),
       reinterpret_cast<int32_t *>(persistent + L.seg_ptr_f),
-      reinterpret_cast<int32_t *>(persistent + L.seg_row_f), stream,
-      &plan->fwd);
+      reinterpret_cast<int32_t *>(persistent + L.seg_row_f),
+      reinterpret_cast<WorkItem *>(persistent + L.items_f), stream, &plan->fwd);
   if (rc) return rc;
   if (!(flags & TGB_PLAN_TRANSPOSE)) return TGB_STATUS_OK;
 
@@ -347,8 +382,8 @@ int32_t create_typed(const IdxT *row_ptr, const IdxT *col_idx, int64_t num_dst,
       t_ptr, num_src, E, temp, L,
       reinterpret_cast<int32_t *>(persistent + L.order_b),
       reinterpret_cast<int32_t *>(persistent + L.seg_ptr_b),
-      reinterpret_cast<int32_t *>(persistent + L.seg_row_b), stream,
-      &plan->bwd);
+      reinterpret_cast<int32_t *>(persistent + L.seg_row_b),
+      reinterpret_cast<WorkItem *>(persistent + L.items_b), stream, &plan->bwd);
 }
 
 int32_t check_sizes(int64_t num_dst, int64_t num_src, int64_t E, int32_t bits) {

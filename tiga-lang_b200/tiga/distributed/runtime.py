@@ -36,6 +36,7 @@ from ..reducer import SumReducer
 from .model import HaloMap, partition_bounds
 
 _ACTIVE = contextvars.ContextVar("tiga_distributed_runtime", default=None)
+DEFAULT_WAVES = 3
 
 
 def current_distributed_runtime():
@@ -142,12 +143,16 @@ class DistributedRuntime:
     (the reference's ``last_execution_trace`` keeps host nanoseconds and declines to claim overlap,
     python/tiga/distributed/transport.py:1311-1370)."""
 
-    def __init__(self, transport: ProcessGroupTransport, *, backend=None, trace: bool = False):
+    def __init__(self, transport: ProcessGroupTransport, *, backend=None, trace: bool = False,
+                 waves: int | None = None):
         self.transport = transport
         self.backend = backend or NativeBackend()
         self._token = None
         self.trace = bool(trace)
         self.last_execution_trace = []
+        # the forward halo arrives in `waves` grouped exchanges; the ghost-source edges of a wave
+        # are reduced as soon as that wave has landed, while the later waves are still in flight
+        self.waves = DEFAULT_WAVES if waves is None else max(int(waves), 1)
 
     def reset_trace(self) -> None:
         self.last_execution_trace = []
@@ -194,10 +199,11 @@ class ShardPlan:
     recv_offsets: list      # per peer: (offset, count) into the ghost buffer
     send_ids: list          # per peer: local row indices (tensor) that peer needs
     graph_own: Graph        # local rows x owned sources
-    graph_ghost: Graph      # local rows x ghost sources
+    graph_ghost: Graph      # local rows x ghost sources (all of them: the backward uses this one)
     edges_own: torch.Tensor    # positions of the owned-source edges in the local edge list
     edges_ghost: torch.Tensor  # positions of the ghost-source edges
     num_local_edges: int
+    waves: list             # per wave: (peers received from, Graph of the ghost-source edges they own)
 
     @property
     def owned(self) -> int:
@@ -217,50 +223,104 @@ class ShardPlan:
                        ghost_ids=tuple(ghosts), receive_from=tuple(receives), send_to=tuple(sends))
 
 
-def build_shard_plan(graph: Graph, transport: ProcessGroupTransport) -> ShardPlan:
-    """Partition, ghost lists, request exchange and the two local relations."""
+def exchange_waves(rank: int, world: int, waves: int) -> list:
+    """Peers in the order their rows are received, cut into at most `waves` consecutive groups.
+    Ring order: at step s (1 .. world-1) a rank receives from rank - s and sends to rank + s, so
+    every step pairs all ranks up at once and the groups of all ranks line up."""
+    steps = list(range(1, world))
+    if not steps:
+        return []
+    waves = min(max(waves, 1), len(steps))
+    cuts = [(len(steps) * k) // waves for k in range(waves + 1)]
+    return [[((rank - s) % world, (rank + s) % world) for s in steps[cuts[k]:cuts[k + 1]]] for k in range(waves)]
+
+
+def _local_rows(graph: Graph, transport: ProcessGroupTransport):
+    """(bounds, local row_ptr starting at 0 as int64, local col_idx with global ids)."""
+    world, rank = transport.world_size, transport.rank
+    n = graph.num_dst
+    if graph._shard is not None:
+        first_row, _ = graph._shard
+        row_ptr, col_idx = graph._row_ptr, graph._col_idx
+        mine = torch.tensor([first_row, row_ptr.numel() - 1], dtype=torch.int64, device=row_ptr.device)
+        blocks = transport.all_gather_counts(mine).tolist()
+        bounds = [int(b[0]) for b in blocks] + [n]
+        for r, (first, rows) in enumerate(blocks):
+            if first + rows != bounds[r + 1] or (r == 0 and first != 0):
+                raise ValueError("the ranks' blocks of rows do not tile [0, num_nodes) in rank order: "
+                                 f"rank {r} holds rows [{first}, {first + rows}), the next block starts at "
+                                 f"{bounds[r + 1]}")
+        return bounds, row_ptr.to(torch.int64), col_idx
     row_ptr, col_idx = graph.resolve_csr()
-    if graph.num_src != graph.num_dst:
-        raise NotImplementedError("halo partitions need a homogeneous relation (num_src == num_dst)")
-    n, world, rank = graph.num_dst, transport.world_size, transport.rank
     placement = graph.placement
-    if placement is not None and placement.mesh.size != world:
-        raise ValueError(f"graph was placed on a mesh of {placement.mesh.size} ranks, the runtime has {world}")
     balance = placement.partition.balance if placement is not None else "auto"
     bounds = partition_bounds(n, world, row_ptr=row_ptr, balance=balance)
     begin, end = bounds[rank], bounds[rank + 1]
-    owned = end - begin
-    device, index_dtype = row_ptr.device, row_ptr.dtype
-
     first, last = int(row_ptr[begin].item()), int(row_ptr[end].item())
-    local_ptr = (row_ptr[begin:end + 1] - first).to(torch.int64)
-    local_col = col_idx[first:last].to(torch.int64)
+    return bounds, (row_ptr[begin:end + 1] - first).to(torch.int64), col_idx[first:last]
+
+
+def build_shard_plan(graph: Graph, transport: ProcessGroupTransport, waves: int = 1) -> ShardPlan:
+    """Partition, ghost lists, request exchange and the local relations."""
+    if graph.num_src != graph.num_dst:
+        raise NotImplementedError("halo partitions need a homogeneous relation (num_src == num_dst)")
+    world, rank = transport.world_size, transport.rank
+    placement = graph.placement
+    if placement is not None and placement.mesh.size != world:
+        raise ValueError(f"graph was placed on a mesh of {placement.mesh.size} ranks, the runtime has {world}")
+    bounds, local_ptr, local_col = _local_rows(graph, transport)
+    begin, end = bounds[rank], bounds[rank + 1]
+    owned = end - begin
+    device, index_dtype = local_ptr.device, graph.schema.index_dtype
+    if local_col.numel() >= 1 << 31:
+        raise NotImplementedError("more than 2^31 local edges per rank")
+    local_col = local_col.to(torch.int64)
     degree = local_ptr[1:] - local_ptr[:-1]
     local_dst = torch.repeat_interleave(torch.arange(owned, device=device), degree)
     is_own = (local_col >= begin) & (local_col < end)
 
-    def sub_relation(mask, columns, num_src):
-        counts = torch.bincount(local_dst[mask], minlength=owned)
+    def sub_relation(positions, columns, num_src):
+        """CSR over the owned rows of the edges at `positions` (ascending) of the local edge list;
+        it reads the caller's per-edge arrays through those positions."""
+        counts = torch.bincount(local_dst[positions], minlength=owned)
         ptr = torch.zeros(owned + 1, dtype=torch.int64, device=device)
         torch.cumsum(counts, 0, out=ptr[1:])
-        return Graph.from_csr(ptr.to(index_dtype), columns.to(index_dtype).contiguous(), num_src=num_src)
+        relation = Graph.from_csr(ptr.to(index_dtype), columns.to(index_dtype).contiguous(), num_src=num_src)
+        relation._edge_map = positions.to(torch.int32)
+        return relation
 
-    if local_col.numel() >= 1 << 31:
-        raise NotImplementedError("more than 2^31 local edges per rank")
     edges_own = torch.nonzero(is_own).reshape(-1)
     edges_ghost = torch.nonzero(~is_own).reshape(-1)
+    del is_own
     ghost_cols = local_col[edges_ghost]
     ghosts = torch.unique(ghost_cols, sorted=True)
-    graph_own = sub_relation(is_own, local_col[edges_own] - begin, owned)
-    graph_ghost = sub_relation(~is_own, torch.searchsorted(ghosts, ghost_cols), max(int(ghosts.numel()), 0))
-    # the two sub-relations address the caller's per-edge arrays through their positions
-    graph_own._edge_map = edges_own.to(torch.int32)
-    graph_ghost._edge_map = edges_ghost.to(torch.int32)
+    num_ghosts = int(ghosts.numel())
+    graph_own = sub_relation(edges_own, local_col[edges_own] - begin, owned)
+    ghost_slot = torch.searchsorted(ghosts, ghost_cols)           # position in the ghost buffer
+    graph_ghost = sub_relation(edges_ghost, ghost_slot, num_ghosts)
 
     # ghosts are sorted, owners are contiguous ranges => each owner's ids are one slice
     bound_t = torch.tensor(bounds, dtype=torch.int64, device=device)
     cuts = torch.searchsorted(ghosts, bound_t).tolist()
     recv_offsets = [(cuts[p], cuts[p + 1] - cuts[p]) for p in range(world)]
+
+    # the forward reduces the ghost-source edges wave by wave: one sub-relation per wave of peers
+    wave_plans = []
+    schedule = exchange_waves(rank, world, waves)
+    if len(schedule) <= 1:
+        wave_plans = [([pair for pair in schedule[0]] if schedule else [], graph_ghost)]
+    else:
+        wave_of_peer = torch.full((world,), -1, dtype=torch.int64, device=device)
+        for k, pairs in enumerate(schedule):
+            for source, _ in pairs:
+                wave_of_peer[source] = k
+        owner = torch.searchsorted(bound_t, ghost_cols, right=True) - 1
+        wave_of_edge = wave_of_peer[owner]
+        for k, pairs in enumerate(schedule):
+            chosen = torch.nonzero(wave_of_edge == k).reshape(-1)
+            wave_plans.append((pairs, sub_relation(edges_ghost[chosen], ghost_slot[chosen], num_ghosts)))
+        del owner, wave_of_edge
+    del ghost_cols, ghost_slot, local_dst
 
     # tell every owner which of its rows this rank needs
     counts = torch.tensor([c for _, c in recv_offsets], dtype=torch.int64, device=device)
@@ -277,14 +337,15 @@ def build_shard_plan(graph: Graph, transport: ProcessGroupTransport) -> ShardPla
             raise RuntimeError("a peer requested a row this rank does not own")
     return ShardPlan(rank=rank, world_size=world, bounds=bounds, begin=begin, end=end, ghosts=ghosts,
                      recv_offsets=recv_offsets, send_ids=send_ids, graph_own=graph_own, graph_ghost=graph_ghost,
-                     edges_own=edges_own, edges_ghost=edges_ghost, num_local_edges=int(local_col.numel()))
+                     edges_own=edges_own, edges_ghost=edges_ghost, num_local_edges=int(local_col.numel()),
+                     waves=wave_plans)
 
 
 def shard_plan_for(graph: Graph, runtime: DistributedRuntime) -> ShardPlan:
     cache = graph.__dict__.setdefault("_shard_plans", {})
-    key = (id(runtime.transport), runtime.transport.rank, runtime.transport.world_size)
+    key = (id(runtime.transport), runtime.transport.rank, runtime.transport.world_size, runtime.waves)
     if key not in cache:
-        cache[key] = build_shard_plan(graph, runtime.transport)
+        cache[key] = build_shard_plan(graph, runtime.transport, runtime.waves)
     return cache[key]
 
 
@@ -301,17 +362,22 @@ class _HaloWeightedSum(torch.autograd.Function):
         device = rows.device
         runtime.mark("forward:begin", device)
         ghost_x = torch.empty((int(shard.ghosts.numel()), F), dtype=rows.dtype, device=rows.device)
-        packed = [(p, backend.pack_rows(rows, ids)) for p, ids in enumerate(shard.send_ids) if ids.numel()]
-        receives = [(p, ghost_x[o:o + c]) for p, (o, c) in enumerate(shard.recv_offsets) if c and p != shard.rank]
-        works = transport.exchange(sends=packed, receives=receives)      # halo in flight ...
+        packed = {p: backend.pack_rows(rows, ids) for p, ids in enumerate(shard.send_ids) if ids.numel()}
+        in_flight = []
+        for pairs, relation in shard.waves:             # every wave is one grouped exchange
+            receives = [(source, ghost_x[o:o + c]) for source, _ in pairs
+                        for o, c in (shard.recv_offsets[source],) if c]
+            sends = [(target, packed[target]) for _, target in pairs if target in packed]
+            in_flight.append((transport.exchange(sends=sends, receives=receives), relation))
         runtime.mark("forward pack + start exchange", device)
         out = backend.forward(shard.graph_own, rows, w_own)              # ... while owned-source edges reduce
         runtime.mark("forward owned-source part", device)
-        transport.wait(works)
-        runtime.mark("forward exposed halo wait", device)
-        if shard.edges_ghost.numel():
-            out = backend.forward(shard.graph_ghost, ghost_x, w_ghost, accumulate_into=out)
-        runtime.mark("forward ghost-source part", device)
+        for works, relation in in_flight:               # a wave's edges reduce while later waves are in flight
+            transport.wait(works)
+            runtime.mark("forward exposed halo wait", device)
+            if relation.resolve_csr()[1].numel():
+                out = backend.forward(relation, ghost_x, w_ghost, accumulate_into=out)
+            runtime.mark("forward ghost-source part", device)
         ctx.shard, ctx.runtime = shard, runtime
         ctx.x_shape, ctx.w_shape = x.shape, None if w is None else w.shape
         ctx.save_for_backward(rows, w_flat, ghost_x)

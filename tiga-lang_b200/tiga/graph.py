@@ -62,6 +62,7 @@ class Graph:
         self._plans = {}
         self._transpose_cache = None
         self._edge_map = None   # set for sub-relations whose weights live in a larger edge list
+        self._shard = None      # (first_row, num_nodes) when the tensors hold one rank's block of rows only
 
     # ------------------------------------------------------------ properties
     @property
@@ -139,6 +140,30 @@ class Graph:
                              realization="materialized_csr", index_dtype=col_idx.dtype,
                              sorted_by_dst=sorted_by_dst)
         return cls(schema, row_ptr=row_ptr, col_idx=col_idx)
+
+    @classmethod
+    def from_csr_shard(cls, row_ptr, col_idx, *, num_nodes: int, first_row: int) -> "Graph":
+        """One rank's block of destination rows of a homogeneous relation over ``num_nodes`` nodes:
+        ``row_ptr`` (starting at 0) and ``col_idx`` (GLOBAL source ids) describe rows
+        ``[first_row, first_row + len(row_ptr) - 1)``.  Only ``.halo(mesh)`` snapshots of such a
+        graph can be executed; every rank of the mesh passes its own block and the blocks must tile
+        ``[0, num_nodes)`` in rank order.  An addition to the reference's constructors for graphs
+        that are too large to hold whole on every rank (its ``halo()`` starts from the full CSR,
+        python/tiga/distributed/transport.py:969-983)."""
+        cls._validate_index_tensor("row_ptr", row_ptr)
+        cls._validate_index_tensor("col_idx", col_idx)
+        if row_ptr.device != col_idx.device:
+            raise ValueError("row_ptr and col_idx must be on the same device")
+        if row_ptr.numel() == 0:
+            raise ValueError("row_ptr must contain at least the initial zero")
+        rows = row_ptr.numel() - 1
+        if not (0 <= first_row and first_row + rows <= num_nodes):
+            raise ValueError("the block of rows must lie inside [0, num_nodes)")
+        schema = GraphSchema(num_src=int(num_nodes), num_dst=int(num_nodes), origin="explicit", lifecycle="static",
+                             realization="materialized_csr", index_dtype=col_idx.dtype, sorted_by_dst=True)
+        graph = cls(schema, row_ptr=row_ptr, col_idx=col_idx)
+        graph._shard = (int(first_row), int(num_nodes))
+        return graph
 
     @classmethod
     def from_coo(cls, src, dst, *, num_src: int | None = None, num_dst: int | None = None) -> "Graph":
@@ -273,6 +298,9 @@ class Graph:
         return None
 
     def resolve_csr(self):
+        if self._shard is not None and self._placement is None:
+            raise RuntimeError("a Graph.from_csr_shard block is executable only as a .halo(mesh) snapshot "
+                               "under a DistributedRuntime")
         if self._row_ptr is not None:
             return self._row_ptr, self._col_idx
         dtype = self._schema.index_dtype

@@ -155,8 +155,14 @@ def check_async_errors(device=None) -> None:
 
 
 def linear_supported(a: torch.Tensor, weight: torch.Tensor) -> bool:
-    return (a.is_cuda and a.dtype == torch.float32 and weight.dtype == torch.float32 and a.ndim == 2
-            and weight.ndim == 2 and weight.shape[0] in (32, 64, 96, 128) and weight.shape[1] in (64, 128))
+    """Shapes every pass (forward, d(a), d(W)) runs on the tensor cores: K and N in {64, 128}.
+    K = 32 or 96 works forward-only (the d(a) pass would need an output width of 32 / 96)."""
+    if not (a.is_cuda and a.dtype == torch.float32 and weight.dtype == torch.float32 and a.ndim == 2
+            and weight.ndim == 2 and weight.shape[1] in (64, 128)):
+        return False
+    if weight.shape[0] in (64, 128):
+        return True
+    return weight.shape[0] in (32, 96) and not (a.requires_grad and torch.is_grad_enabled())
 
 
 def _linear_raw(a: torch.Tensor, b_t: torch.Tensor) -> torch.Tensor:
@@ -183,7 +189,7 @@ def _linear_dw_raw(a: torch.Tensor, d_out: torch.Tensor) -> torch.Tensor:
     count = ctypes.c_int32()
     with torch.cuda.device(a.device):
         _native.check(lib.tgb_linear_dw_partials(M, ctypes.byref(count)), "tgb_linear_dw_partials")
-        partial = torch.empty((count.value, K, N), dtype=torch.float32, device=a.device)
+        partial = torch.empty((count.value, 128, N), dtype=torch.float32, device=a.device)   # 128-row accumulators
         dw = torch.empty((K, N), dtype=torch.float32, device=a.device)
         _native.check(lib.tgb_linear_dw_f32(a.data_ptr(), d_out.data_ptr(), dw.data_ptr(), partial.data_ptr(),
                                             partial.numel() * 4, M, K, N, error_flag(a.device).data_ptr(),
@@ -192,7 +198,7 @@ def _linear_dw_raw(a: torch.Tensor, d_out: torch.Tensor) -> torch.Tensor:
 
 
 class DenseLinearFunction(torch.autograd.Function):
-    """out = a @ W with W [K, N]; forward, d(a) and (for K = 128) d(W) = a^T @ dout run on tcgen05."""
+    """out = a @ W with W [K, N]; forward, d(a) = dout @ W^T and d(W) = a^T @ dout all run on tcgen05."""
 
     @staticmethod
     def forward(ctx, a, weight):
@@ -205,22 +211,19 @@ class DenseLinearFunction(torch.autograd.Function):
         grad_output = grad_output.contiguous()
         da = dw = None
         if ctx.needs_input_grad[0]:
-            if weight.shape[0] in (64, 128) and weight.shape[1] % 32 == 0:
-                da = _linear_raw(grad_output, weight)
-            else:
-                da = grad_output @ weight.t()
+            # d(a) = dout @ W^T is the same kernel with the roles of K and N swapped: it needs an output
+            # width (K) of 64 or 128; narrower inputs are refused by dense_linear up front
+            da = _linear_raw(grad_output, weight)
         if ctx.needs_input_grad[1]:
-            if weight.shape[0] == 128 and weight.shape[1] in (64, 128):
-                dw = _linear_dw_raw(a, grad_output)
-            else:
-                dw = a.t() @ grad_output
+            dw = _linear_dw_raw(a, grad_output)
         return da, dw
 
 
 def dense_linear(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """``a @ weight`` for float32 [M, K] x [K, N] with K, N <= 128 on the tensor cores."""
     if not linear_supported(a, weight):
-        raise NotImplementedError("dense_linear takes float32 CUDA matrices with K in {32,64,96,128}, N in {64,128}")
+        raise NotImplementedError("dense_linear takes float32 CUDA matrices with K, N in {64, 128} "
+                                  "(K in {32, 96} too when the input needs no gradient)")
     return DenseLinearFunction.apply(a, weight)
 
 
