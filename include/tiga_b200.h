@@ -145,7 +145,8 @@ TGB_API int32_t tgb_csr_plan_array(const tgb_csr_plan *plan, int32_t which,
 
 /* Scratch bytes one reduce call needs for split rows (partial sums), for a
  * feature row of `feature_elems` elements; direction 0 = forward/dw over the
- * CSR rows, 1 = dx over the transposed rows. */
+ * CSR rows, 1 = dx over the transposed rows (includes 4 bytes per edge for the
+ * weights in transposed order), 2 = dx when the caller passes those weights. */
 TGB_API int32_t tgb_csr_plan_scratch_bytes(const tgb_csr_plan *plan,
                                            int32_t direction, int32_t reducer,
                                            int64_t feature_elems, int32_t dtype,
@@ -179,12 +180,20 @@ TGB_API int32_t tgb_csr_reduce_fwd(const tgb_csr_plan *plan, int32_t reducer,
  * scratch).  MAX: only the winning edge of each (row, element) contributes.
  * SUM / MEAN with weights: a first pass writes the weights in transposed order
  * into scratch (4 bytes per edge, included in tgb_csr_plan_scratch_bytes for
- * direction 1) so that the gather reads them in order. */
+ * direction 1) so that the gather reads them in order; a caller that has them
+ * already (tgb_csr_transposed_weights, e.g. kept across the layers that share
+ * one weight array) passes them as `aux` and that pass is skipped. */
 TGB_API int32_t tgb_csr_reduce_bwd_dx(const tgb_csr_plan *plan, int32_t reducer,
                                       const void *dy, const void *w,
                                       const void *aux, void *dx, int64_t F,
                                       int32_t dtype, void *scratch,
                                       uint64_t scratch_bytes, uint64_t stream);
+
+/* w_t[k] = w[eid[k]]: the weights in the order of the plan's stable transposed
+ * relation (`jacobian = w[order]` of python/tiga/interop/torch/relation_vjp.py:
+ * 61-87).  float32 [E]; honours an edge map.  The plan needs TGB_PLAN_TRANSPOSE. */
+TGB_API int32_t tgb_csr_transposed_weights(const tgb_csr_plan *plan, const void *w,
+                                           void *w_t, uint64_t stream);
 
 /* dw[e] = <dy[dst(e),:], x[col[e],:]>  (per-edge dot product; the contract of
  * benchmarks/autograd/message_passing_backward.py:346-353). */
@@ -285,7 +294,10 @@ TGB_API int32_t tgb_rows_scatter_add(void *rows, const void *ids,
  * message_passing.py:1910-2020); the packed relation is Graph.cu_seqlens /
  * Graph.cat of triangular blocks (python/tiga/graph/core.py:314-351,650-709),
  * which the reference materialises edge by edge and evaluates eagerly.
- *   q, k, v, out  [tokens, H, D] bf16 contiguous, D in {64, 128}
+ *   q, out        [tokens, H, D] bf16 contiguous, D in {64, 128}
+ *   k, v          [tokens, H_kv, D]; H a multiple of H_kv: query head h reads
+ *                 key/value head h / (H / H_kv) (grouped queries, the query-lane
+ *                 to source-lane map of Translate.cpp:1654-1680)
  *   lse           [tokens, H] float32: log-sum-exp of the scaled scores
  *   tiles         int32 [n_tiles, 4] = {first query, sequence begin, sequence
  *                 end, head}: one entry per (128-query tile, head); one CTA
@@ -297,25 +309,60 @@ TGB_API int32_t tgb_rows_scatter_add(void *rows, const void *ids,
 TGB_API int32_t tgb_varlen_attn_fwd(const void *q, const void *k, const void *v,
                                     void *out, void *lse, const void *tiles,
                                     int64_t n_tiles, int64_t tokens, int32_t H,
-                                    int32_t D, float scale, int32_t causal,
-                                    void *error_flag, uint64_t stream);
+                                    int32_t H_kv, int32_t D, float scale,
+                                    int32_t causal, void *error_flag,
+                                    uint64_t stream);
 
 /* Gradients of tgb_varlen_attn_fwd (no counterpart in the reference, whose
  * dense path is forward only: python/tiga/interop/torch/message_passing.py:
- * 1910-2020 returns without an autograd Function).  dq, dk, dv [tokens, H, D]
- * bf16; delta is scratch, float32 [tokens, H]; query_tiles as in the forward,
- * key_tiles the same tiles ordered for the key-major kernel (field 0 = first
- * key of the tile).  No atomics: dK/dV are accumulated per key tile over the
- * query blocks that see it, dQ per query tile over its key blocks. */
+ * 1910-2020 returns without an autograd Function).  dq [tokens, H, D], dk, dv
+ * [tokens, H_kv, D] bf16; delta is scratch, float32 [tokens, H]; query_tiles
+ * (n_tiles entries, one per 128-query tile and query head) as in the forward,
+ * key_tiles (n_key_tiles entries, one per 128-key tile and key/value head; field
+ * 0 = first key of the tile) for the key-major kernel.  No atomics: dK/dV are
+ * accumulated per key tile over the query blocks of every query head of its
+ * group, dQ per query tile over its key blocks. */
 TGB_API int32_t tgb_varlen_attn_bwd(const void *q, const void *k, const void *v,
                                     const void *out, const void *dout,
                                     const void *lse, void *dq, void *dk,
                                     void *dv, void *delta,
                                     const void *query_tiles,
                                     const void *key_tiles, int64_t n_tiles,
-                                    int64_t tokens, int32_t H, int32_t D,
+                                    int64_t n_key_tiles, int64_t tokens,
+                                    int32_t H, int32_t H_kv, int32_t D,
                                     float scale, int32_t causal,
                                     void *error_flag, uint64_t stream);
+
+/* ------------------------------------------------------------------------
+ * Online-softmax reducer with per-edge scores and per-source values:
+ *   edge(): return self.reducer(edge.score, src.value)
+ *   out[i,h,:] = sum_e p[e,h] * value[col[e],h,:],  p = softmax of score over row i
+ * Replaces the reference's stable-weighted reduction tile
+ * (lib/Target/Triton/Translate.cpp:3296-3352) and the eager evaluator
+ * (python/tiga/interop/torch/reducer_oracle.py:60-137) for this program:
+ * float32 state, an empty row yields exactly 0.
+ *   score [E, H] float32; value [num_src, H, D] float32 or bf16 (value_dtype);
+ *   out [num_dst, H, D] float32; m, l [num_dst, H] float32 (kept for the backward).
+ * Backward (no atomics): d_score [E, H] float32, d_value [num_src, H, D] float32;
+ * dout, out float32; p_scratch = E*H floats; the plan needs TGB_PLAN_TRANSPOSE.
+ * ------------------------------------------------------------------------ */
+TGB_API int32_t tgb_softmax_field_fwd(const tgb_csr_plan *plan, const void *score,
+                                      const void *value, int32_t value_dtype,
+                                      void *out, void *m, void *l, int32_t H,
+                                      int32_t D, uint64_t stream);
+TGB_API int32_t tgb_softmax_field_bwd(const tgb_csr_plan *plan, const void *score,
+                                      const void *value, int32_t value_dtype,
+                                      const void *out, const void *dout,
+                                      const void *m, const void *l, int32_t H,
+                                      int32_t D, void *d_score, void *d_value,
+                                      void *p_scratch, uint64_t stream);
+
+/* Self-test of the bounded waits of the tensor-core kernels (no reference
+ * counterpart): one warp waits at most `polls` (<= 2^20) polls on a barrier that
+ * nothing signals, gives up, stores code 99 in `error_flag` (int32, zero before
+ * the call) and 1 in `fell_through` (int32), and the kernel returns. */
+TGB_API int32_t tgb_selftest_bounded_wait(void *error_flag, uint32_t polls,
+                                          void *fell_through, uint64_t stream);
 
 /* ------------------------------------------------------------------------
  * Dense float32 linear on the tensor cores (tcgen05, 3xTF32 split):

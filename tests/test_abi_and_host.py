@@ -232,3 +232,52 @@ def test_synthetic_rmat_is_deterministic():
     assert torch.equal(key, torch.unique(key))            # sorted by (dst, src), no duplicates
     rev = col * 1024 + dst
     assert torch.equal(torch.sort(rev).values, key)        # symmetric
+
+
+def test_degree_histogram_and_locality_signal():
+    # ragged CSR with empty rows: degrees 2, 0, 3, 1, 0
+    row_ptr = torch.tensor([0, 2, 2, 5, 6, 6])
+    col = torch.tensor([0, 4, 1, 2, 3, 3])
+    g = tg.Graph.from_csr(row_ptr, col, num_src=5)
+    assert g.degree_histogram() == (2, 1, 1, 1)
+    assert sum(d * c for d, c in enumerate(g.degree_histogram())) == col.numel()
+    # every sampled slot: |col - row| = 0, 4, 1, 0, 1, 0 -> mean 1.0, over 5 endpoints
+    assert abs(g.source_index_span_ratio() - 1.0 / 5) < 1e-12
+    assert tg.Graph.triangular(4).degree_histogram() == (0, 1, 1, 1, 1)
+    assert tg.Graph.dense(3, 2).degree_histogram() == (0, 0, 0, 2)
+    rows = torch.arange(1000).repeat_interleave(3)
+    banded = (rows + torch.arange(3).repeat(1000)).clamp(max=999)      # row i reads i, i+1, i+2: index-local
+    local = tg.Graph.from_csr(torch.arange(0, 3001, 3), banded, num_src=1000)
+    assert local.source_index_span_ratio() < 0.01
+    gen = torch.Generator().manual_seed(0)
+    random_col = torch.randint(0, 4096, (4096 * 8,), generator=gen)
+    scattered = tg.Graph.from_csr(torch.arange(0, 4096 * 8 + 1, 8), random_col, num_src=4096)
+    assert 0.28 < scattered.source_index_span_ratio() < 0.39    # random numbering approaches one third
+    hub = tg.Graph.from_csr(torch.tensor([0, 5000]), torch.zeros(5000, dtype=torch.int64), num_src=1)
+    with pytest.raises(ValueError):
+        hub.degree_histogram()
+
+
+def test_b200_native_codegen_provider_is_registered():
+    from tiga import _native, codegen
+
+    assert "b200-native" in codegen.discover_providers()
+    provider = codegen.get_provider("b200-native")
+    report = codegen.provider_conformance(provider)
+    assert report == {"abi_version": 1, "name": "b200-native", "target_family": "cuda-sm100a", "devices": ("cuda",),
+                      "input_ir": "vendor-ir", "artifacts": ("shared-library",), "supports_async": True,
+                      "supports_distributed": True}
+    # every lowering name resolves to entry points the header declares
+    for lowering, entries in codegen.LOWERINGS.items():
+        compiled = provider.compile(lowering, target="sm_100a", options={})
+        assert compiled.entry_points == entries and all(name in _native.exported_symbols() for name in entries)
+    with pytest.raises(NotImplementedError):
+        provider.compile("gf-kernel-to-ttir-fixed-csr-weighted-sum", target=None, options={})
+    with pytest.raises(NotImplementedError):
+        provider.compile("b200-csr-weighted-sum-degree-bucket", target="sm_90a", options={})
+    with pytest.raises(ValueError):
+        codegen.ProviderCapabilities("x", "y", ("cuda",), "ptx", (), False, False)
+    with pytest.raises(LookupError):
+        codegen.get_provider("triton")
+    with pytest.raises(ValueError):
+        codegen.register_provider("b200-native", codegen.provider_factory)

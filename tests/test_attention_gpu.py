@@ -78,3 +78,43 @@ def test_backward_matches_oracle(oracle, lengths, H, D, causal):
     rq, rk, rv = oracle.varlen_attn_bwd(cu.numpy(), qf, kf, vf, ref_out, dy.float().numpy(), scale, causal=causal)
     for got, ref in ((dq, rq), (dk, rk), (dv, rv)):
         np.testing.assert_allclose(got.float().cpu().numpy(), ref, rtol=2e-2, atol=2e-2 * np.abs(ref).max())
+
+
+@pytest.mark.parametrize("lengths,H,H_kv,D,causal", (
+    ([128], 8, 2, 64, True),                 # the reference's grouped-query case: 8 query lanes on 2 source lanes
+    ([300, 129, 513], 4, 1, 128, True),
+    ([200, 77], 6, 3, 64, False),
+))
+def test_grouped_queries_match_oracle(oracle, lengths, H, H_kv, D, causal):
+    """Fewer key/value heads than query heads: query head h reads head h // (H / H_kv), the map of
+    the reference's dense kernel (tests/python/test_mlir_bridge.py:441-467 checks it against SDPA
+    with enable_gqa).  The oracle has one head count, so K and V are repeated per group for it and
+    its dK, dV are summed over each group."""
+    gen = torch.Generator().manual_seed(H * 10 + D)
+    T, group = sum(lengths), H // H_kv
+    q = torch.randn(T, H, D, generator=gen).to(torch.bfloat16)
+    k, v = (torch.randn(T, H_kv, D, generator=gen).to(torch.bfloat16) for _ in range(2))
+    dy = torch.randn(T, H, D, generator=gen).to(torch.bfloat16)
+    cu = torch.tensor([0] + list(np.cumsum(lengths)), dtype=torch.int64)
+    scale = D ** -0.5
+    graph = tg.Graph.cu_seqlens(cu.cuda(), causal=causal)
+    qg, kg, vg = (t.cuda().requires_grad_() for t in (q, k, v))
+    out = Attention()(graph=graph, src={"key": kg, "value": vg}, dst={"query": qg}, scale=scale)
+    dq, dk, dv = torch.autograd.grad(out, (qg, kg, vg), dy.cuda())
+    ops.check_async_errors()
+    assert dk.shape == k.shape and dv.shape == v.shape
+    qf = q.float().numpy()
+    kf, vf = (t.float().repeat_interleave(group, dim=1).numpy() for t in (k, v))
+    ref, _ = oracle.varlen_attn_fwd(cu.numpy(), qf, kf, vf, scale, causal=causal)
+    np.testing.assert_allclose(out.detach().float().cpu().numpy(), ref, rtol=2e-2, atol=2e-2)
+    rq, rk, rv = oracle.varlen_attn_bwd(cu.numpy(), qf, kf, vf, ref, dy.float().numpy(), scale, causal=causal)
+    rk, rv = (r.reshape(T, H_kv, group, D).sum(2) for r in (rk, rv))
+    for got, want in ((dq, rq), (dk, rk), (dv, rv)):
+        np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=2e-2, atol=2e-2 * np.abs(want).max())
+    # against Torch's grouped-query SDPA on the first sequence, as the reference's own test does
+    if causal:
+        n = lengths[0]
+        expected = torch.nn.functional.scaled_dot_product_attention(
+            qg[:n].detach().permute(1, 0, 2), kg[:n].detach().permute(1, 0, 2), vg[:n].detach().permute(1, 0, 2),
+            is_causal=True, enable_gqa=True).permute(1, 0, 2)
+        torch.testing.assert_close(out[:n].detach().float(), expected.float(), rtol=2e-2, atol=2e-2)

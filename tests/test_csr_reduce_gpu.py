@@ -385,3 +385,120 @@ def test_owned_and_ghost_sub_relations_through_the_native_backend(oracle, F):
     backend.backward_dw(g_own, dyc, xc[:cut].contiguous(), dw)
     backend.backward_dw(g_ghost, dyc, xc[cut:].contiguous(), dw)
     assert_dot_close(oracle, dw.cpu().numpy(), oracle.wsum_bwd_dw(rp, cc, dy.numpy(), x.numpy()), row_ptr, col, dy, x)
+
+
+def test_warm_call_does_not_stage_edge_again():
+    """The second call with the same graph and tensor layouts takes the guarded launch: edge() is
+    not run again, no new variant is recorded, and the result has the same bits."""
+    calls = {"edge": 0}
+
+    class Counted(tg.MessagePassing):
+        reducer = tg.sum()
+
+        def edge(self, src, dst, edge):
+            calls["edge"] += 1
+            return edge.weight * src.x
+
+    row_ptr, col = syn.fixed_degree_graph(256, 8, seed=2)
+    g = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=256)
+    x = torch.randn(256, 32, device="cuda", requires_grad=True)
+    w = torch.rand(2048, device="cuda", requires_grad=True)
+    kernel = Counted()
+    assert kernel._torch_fast_path is None
+    first = kernel(graph=g, src={"x": x}, dst={}, edge={"weight": w})
+    staged = calls["edge"]
+    assert staged >= 1 and kernel._torch_fast_path is not None
+    for _ in range(3):
+        again = kernel(graph=g, src={"x": x}, dst={}, edge={"weight": w})
+    assert calls["edge"] == staged and torch.equal(first, again)
+    assert kernel.cache_info == {"hits": 3, "misses": 1, "variants": 1}
+    dx, dw = torch.autograd.grad(again.sum(), (x, w))             # the warm result is differentiable
+    assert dx.shape == x.shape and dw.shape == w.shape
+    hit, value = kernel._torch_fast_path(g, {"x": x}, {}, {"weight": w}, {})
+    assert hit and torch.equal(value, first)
+    # anything the guards watch sends the call back through staging: another dtype layout, graph or reducer
+    other = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=256)
+    kernel(graph=other, src={"x": x}, dst={}, edge={"weight": w})
+    assert calls["edge"] > staged
+    staged = calls["edge"]
+    kernel(graph=g, src={"x": x.detach()}, dst={}, edge={"weight": w})     # requires_grad pattern changed
+    assert calls["edge"] > staged
+    hit, _ = kernel._torch_fast_path(g, {"y": x}, {}, {"weight": w}, {})
+    assert not hit
+
+
+def test_additive_tuple_state_reducer_matches_eager_evaluator():
+    """A user reducer with tuple state (sum, sum of squares, count) and a finalize: every component
+    runs as a fused CSR sum and autograd reaches the inputs through finalize."""
+    class Variance(tg.Reducer):
+        associative = commutative = True
+
+        def identity(self):
+            return 0.0, 0.0, 0.0
+
+        def lift(self, message):
+            return message, message * message, 1.0
+
+        def combine(self, left, right):
+            return left[0] + right[0], left[1] + right[1], left[2] + right[2]
+
+        def finalize(self, state):
+            mean = state[0] / state[2]
+            return state[1] / state[2] - mean * mean
+
+    class Spread(tg.MessagePassing):
+        reducer = Variance()
+
+        def edge(self, src, dst, edge):
+            return self.reducer(edge.weight * src.x)
+
+    row_ptr, col = syn.rmat_csr(9, 8, seed=4)
+    n, E = row_ptr.numel() - 1, col.numel()
+    g = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=n)
+    x = torch.randn(n, 16, device="cuda", dtype=torch.float32, requires_grad=True)
+    w = (torch.rand(E, device="cuda") + 0.5).requires_grad_()
+    kernel = Spread()
+    out = kernel(graph=g, src={"x": x}, dst={}, edge={"weight": w})
+    ref = kernel.reference(graph=g, src={"x": x}, dst={}, edge={"weight": w[:, None]})
+    assert "additive" in kernel.last_variant.lowering
+    has_edges = (row_ptr.diff() > 0).cuda()
+    torch.testing.assert_close(out[has_edges], ref[has_edges], rtol=1e-4, atol=1e-5)
+    assert torch.isnan(out[~has_edges]).all()                 # 0 / 0 for rows without edges, like mean
+    dy = torch.randn_like(out) * has_edges[:, None]
+    got = torch.autograd.grad((out[has_edges] * dy[has_edges]).sum(), (x, w))
+    want = torch.autograd.grad((ref[has_edges] * dy[has_edges]).sum(), (x, w))
+    for a, b in zip(got, want):
+        torch.testing.assert_close(a, b, rtol=1e-3, atol=1e-4)
+
+
+def test_from_coo_on_the_device_matches_reference_fixture(golden):
+    src = torch.from_numpy(golden["coo_src"]).cuda()
+    dst = torch.from_numpy(golden["coo_dst"]).cuda()
+    g = tg.Graph.from_coo(src, dst, num_src=23, num_dst=17)
+    row_ptr, col = g.resolve_csr()
+    assert row_ptr.is_cuda and col.is_cuda
+    np.testing.assert_array_equal(row_ptr.cpu().numpy(), golden["coo_row_ptr"])
+    np.testing.assert_array_equal(col.cpu().numpy(), golden["coo_col"])
+    np.testing.assert_array_equal(g.destination_index().cpu().numpy(), golden["coo_destination"])
+    # the device-built graph feeds the kernels directly
+    x = torch.randn(23, 8, device="cuda")
+    out = PlainSum()(graph=g, src={"x": x}, dst={})
+    expect = torch.full((17, 8), 0.5, device="cuda").index_add_(0, dst[torch.argsort(dst, stable=True)],
+                                                               x[col])
+    torch.testing.assert_close(out, expect, rtol=1e-5, atol=1e-6)
+    assert g.degree_histogram() == tuple(np.bincount(np.diff(golden["coo_row_ptr"])).tolist())
+
+
+def test_max_reducer_refuses_an_edge_mapped_plan():
+    from tiga import _native
+    from tiga.plan import CSRPlan
+
+    row_ptr, col = syn.fixed_degree_graph(64, 4, seed=3)
+    mapped = CSRPlan(row_ptr.cuda(), col.cuda(), 64, transpose=True,
+                     edge_map=torch.arange(256, dtype=torch.int32).flip(0))
+    x = torch.randn(64, 8, device="cuda")
+    with pytest.raises(NotImplementedError, match="edge map"):
+        ops.csr_reduce_forward(mapped, "max", x, None)
+    with pytest.raises(NotImplementedError, match="edge map"):
+        ops.csr_reduce_backward_dx(mapped, "max", x, None, torch.zeros(64, 8, dtype=torch.int32, device="cuda"))
+    assert _native.lib().tgb_last_error().decode()

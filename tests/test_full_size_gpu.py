@@ -85,6 +85,61 @@ def test_gcn_layer_configuration_full_size(oracle):
     np.testing.assert_allclose(dw.cpu()[edges].numpy(), ref_dw, rtol=1e-4, atol=1e-4)
 
 
+def test_gcn_layer_configuration_max_reducer_full_size(oracle):
+    # config 2, maximum reducer: values and winning edges bit for bit, at 2^20 nodes and 128 floats per row
+    device = torch.device("cuda")
+    row_ptr, col = syn.rmat_csr(20, 32, seed=20261125, symmetrize=True, device=device)
+    n, E, F = row_ptr.numel() - 1, col.numel(), 128
+    w = syn.gcn_norm_weights(row_ptr, col)
+    x = syn.normal((n, F), seed=1, device=device)
+    graph = tg.Graph.from_csr(row_ptr, col, num_src=n)
+
+    class WeightedMax(tg.MessagePassing):
+        reducer = tg.max()
+
+        def edge(self, src, dst, edge):
+            return self.reducer(edge.weight * src.x)
+
+    kernel = WeightedMax()
+    xg, wg = x.clone().requires_grad_(), w.clone().requires_grad_()
+    out = kernel(graph=graph, src={"x": xg}, dst={}, edge={"weight": wg})
+    plan = graph.native_plan(transpose=True)
+    values, winners = ops.csr_reduce_forward(plan, "max", x, w, float("-inf"))
+    assert torch.equal(values, out.detach())
+    deg = row_ptr.diff()
+    assert torch.all(out.detach()[deg == 0] == float("-inf"))         # an empty row keeps the start value
+    # (1) the product's second, independent statement of the semantics -- reference()'s scatter amax --
+    # on blocks of destination rows (the eager evaluator materialises [edges, F]), bit for bit
+    for first in (0, 1 << 18, (1 << 20) - (1 << 16)):
+        last = first + (1 << 16)
+        lo, hi = int(row_ptr[first]), int(row_ptr[last])
+        block = tg.Graph.from_csr(row_ptr[first:last + 1] - lo, col[lo:hi], num_src=n)
+        eager = kernel.reference(graph=block, src={"x": x}, dst={}, edge={"weight": w[lo:hi, None]})
+        assert torch.equal(eager, out.detach()[first:last])
+    # (2) the CPU oracle on sampled rows, hubs included: values and winners
+    picks = torch.unique(torch.cat((torch.topk(deg, 3).indices, torch.nonzero(deg == 0)[:3, 0], torch.randint(
+        0, n, (300,), device=device, generator=torch.Generator(device).manual_seed(9))))).cpu()
+    rp, ci = row_ptr.cpu(), col.cpu()
+    sub_ptr = torch.cat((torch.zeros(1, dtype=torch.int64), deg.cpu()[picks].cumsum(0)))
+    edges = torch.cat([torch.arange(rp[r], rp[r + 1]) for r in picks.tolist()])
+    ref_values, ref_winners = oracle.max_fwd(sub_ptr.numpy(), ci[edges].numpy(), x.cpu().numpy(),
+                                             w.cpu()[edges].numpy())
+    np.testing.assert_array_equal(values.cpu()[picks].numpy(), ref_values)
+    # winners are positions in the full edge list; the oracle's are positions in the sampled list
+    got_winners = winners.cpu()[picks].numpy()
+    want = np.where(ref_winners >= 0, edges.numpy()[np.clip(ref_winners, 0, None)], -1)
+    np.testing.assert_array_equal(got_winners, want)
+    # (3) backward: every (row, element) cotangent reaches exactly one edge and one source element
+    dy = syn.normal((n, F), seed=2, device=device)
+    dx, dw = torch.autograd.grad(out, (xg, wg), dy)
+    routed = torch.where(winners >= 0, dy, torch.zeros_like(dy))
+    lhs = (routed.double() * out.detach().double().nan_to_num(neginf=0.0)).sum().item()
+    mid = (dx.double() * x.double()).sum().item()
+    rhs = (dw.double() * w.double()).sum().item()
+    scale = (routed.double().abs() * out.detach().double().nan_to_num(neginf=0.0).abs()).sum().item()
+    assert abs(lhs - mid) < 1e-6 * scale and abs(lhs - rhs) < 1e-6 * scale
+
+
 def test_gat_configuration_full_size():
     # config 3: directed R-MAT 2^21 nodes, 64M generated edges, bf16 [N, 8, 32]
     device = torch.device("cuda")

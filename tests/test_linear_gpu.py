@@ -80,3 +80,34 @@ def test_unsupported_shapes_raise():
         ops.dense_linear(torch.zeros(4, 100, device="cuda"), torch.zeros(100, 128, device="cuda"))
     with pytest.raises(NotImplementedError):     # K = 32 has no d(a) kernel: refused up front, never a library fallback
         ops.dense_linear(torch.zeros(4, 32, device="cuda", requires_grad=True), torch.zeros(32, 128, device="cuda"))
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable(oracle):
+    """A bounded wait that gives up must end the kernel with an error code, not hang: the self-test
+    kernel waits 4096 polls on a barrier nothing signals.  The code then surfaces through the error
+    word (here by the explicit check, in product use at the next tensor-core call), and the next
+    real kernel on the same context is correct."""
+    import ctypes
+
+    from tiga import _native
+
+    device = torch.device("cuda", torch.cuda.current_device())
+    ops.check_async_errors()
+    word = ops.error_flag(device)
+    fell_through = torch.zeros(1, dtype=torch.int32, device=device)
+    status = _native.lib().tgb_selftest_bounded_wait(word.data_ptr(), ctypes.c_uint32(4096), fell_through.data_ptr(),
+                                                     torch.cuda.current_stream().cuda_stream)
+    assert status == _native.OK
+    ops.launched(device)
+    torch.cuda.synchronize()
+    assert int(fell_through.item()) == 1                   # the second wait returned at once
+    with pytest.raises(RuntimeError, match="code 99"):
+        ops.error_flag(device)                             # what the next launch would do first
+    ops.check_async_errors()                               # the word was cleared when it was reported
+    a = syn.normal((1000, 64), seed=1)
+    w = syn.normal((64, 64), seed=2, std=0.125)
+    out = ops.dense_linear(a.cuda(), w.cuda())
+    ops.check_async_errors()
+    assert_gemm_close(out.cpu().numpy(), a.numpy(), w.numpy(), oracle.linear(a.numpy(), w.numpy()))
+    assert _native.lib().tgb_selftest_bounded_wait(word.data_ptr(), ctypes.c_uint32(0), fell_through.data_ptr(),
+                                                   0) == _native.INVALID_ARGUMENT

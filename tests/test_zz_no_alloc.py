@@ -71,3 +71,26 @@ def test_noalloc_refuses_graphs_beyond_its_capacity():
     status, got = _call_noalloc(plan, x, None)
     assert status == _native.OK
     np.testing.assert_array_equal(got.cpu().numpy(), expect.cpu().numpy())
+
+
+def test_noalloc_honours_a_plan_edge_map():
+    """A plan whose edges address the caller's weight array through an edge map (the halo runtime's
+    sub-relations do) must read w[map[e]] in the allocation-free entry point too."""
+    from tiga.plan import CSRPlan
+
+    row_ptr, col = syn.rmat_csr(11, 16, seed=7)
+    n, E = row_ptr.numel() - 1, col.numel()
+    perm = torch.randperm(E, generator=torch.Generator().manual_seed(1)).to(torch.int32)
+    plan = CSRPlan(row_ptr.cuda(), col.cuda(), n, transpose=False, edge_map=perm)
+    assert plan.info["segments"] > 0
+    x = syn.normal((n, 64), seed=2).cuda()
+    w = torch.rand(E, generator=torch.Generator().manual_seed(3)).cuda()
+    expect, _ = ops.csr_reduce_forward(plan, "sum", x, w, 0.0)
+    status, got = _call_noalloc(plan, x, w)
+    assert status == _native.OK, _native.lib().tgb_last_error()
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(got.cpu().numpy(), expect.cpu().numpy())
+    # and that really is the mapped weight: the same sums from a plan without a map and w gathered by hand
+    plain = CSRPlan(row_ptr.cuda(), col.cuda(), n, transpose=False)
+    by_hand, _ = ops.csr_reduce_forward(plain, "sum", x, w[perm.long().cuda()], 0.0)
+    np.testing.assert_array_equal(got.cpu().numpy(), by_hand.cpu().numpy())

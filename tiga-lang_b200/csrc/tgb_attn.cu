@@ -88,7 +88,7 @@ constexpr int kFwdThreads = 160;   // warps 0-3: softmax (one query row per thre
 template <int HALVES>
 __global__ void __launch_bounds__(kFwdThreads, 2)
 k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-           const __grid_constant__ CUtensorMap map_v, const Tile *__restrict__ tiles, int H,
+           const __grid_constant__ CUtensorMap map_v, const Tile *__restrict__ tiles, int H, int group,
            float scale_log2, int causal, __nv_bfloat16 *__restrict__ out, float *__restrict__ lse, int *error) {
   constexpr int D = 64 * HALVES;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -100,6 +100,7 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const Tile tile = tiles[blockIdx.x];
   const int head = tile.head;
+  const int kv_head = head / group;                  // grouped queries: `group` query heads read one K/V head
   const int key_limit = causal ? min(tile.q_begin + kTile, tile.seq_end) : tile.seq_end;
   const int n_blocks = (key_limit - tile.seq_begin + kKeyBlock - 1) / kKeyBlock;
 
@@ -136,13 +137,13 @@ k_attn_fwd(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CU
         const int stage = block & 1, y = tile.seq_begin + block * kKeyBlock;
         mbar_arrive_expect_tx(&sm.k_full[stage], HALVES * kKeyBoxBytes);
 #pragma unroll
-        for (int j = 0; j < HALVES; ++j) tma_load_2d(sm.k[stage][j], &map_k, head * D + 64 * j, y, &sm.k_full[stage]);
+        for (int j = 0; j < HALVES; ++j) tma_load_2d(sm.k[stage][j], &map_k, kv_head * D + 64 * j, y, &sm.k_full[stage]);
       };
       auto load_v = [&](int block) {
         const int stage = block & 1, y = tile.seq_begin + block * kKeyBlock;
         mbar_arrive_expect_tx(&sm.v_full[stage], HALVES * kKeyBoxBytes);
 #pragma unroll
-        for (int j = 0; j < HALVES; ++j) tma_load_2d(sm.v[stage][j], &map_v, head * D + 64 * j, y, &sm.v_full[stage]);
+        for (int j = 0; j < HALVES; ++j) tma_load_2d(sm.v[stage][j], &map_v, kv_head * D + 64 * j, y, &sm.v_full[stage]);
       };
       constexpr uint32_t idesc_s = instr_desc(kFmtBF16, kFmtBF16, kTile, kKeyBlock, 0, 0);
       constexpr uint32_t idesc_o = instr_desc(kFmtBF16, kFmtBF16, kTile, D, 0, 1);   // V is MN-major
@@ -381,19 +382,26 @@ template <int HALVES>
 __global__ void __launch_bounds__(kDkvThreads, 1)
 k_attn_bwd_dkv(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-               const Tile *__restrict__ tiles, int H, float scale, int causal, const float *__restrict__ lse,
-               const float *__restrict__ delta, __nv_bfloat16 *__restrict__ dk, __nv_bfloat16 *__restrict__ dv,
-               int *error) {
+               const Tile *__restrict__ tiles, int H, int H_kv, float scale, int causal,
+               const float *__restrict__ lse, const float *__restrict__ delta, __nv_bfloat16 *__restrict__ dk,
+               __nv_bfloat16 *__restrict__ dv, int *error) {
   constexpr int D = 64 * HALVES;
   extern __shared__ uint8_t smem_raw[];
   DkvSmem<HALVES> &sm =
       *reinterpret_cast<DkvSmem<HALVES> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const Tile tile = tiles[blockIdx.x];               // q_begin holds the first key of this tile
-  const int head = tile.head;
+  const int head = tile.head;                        // a K/V head
+  const int group = H / H_kv;                        // query heads that read this K/V head
   const int q_first = causal ? tile.q_begin : tile.seq_begin;
-  const int n_blocks = (tile.seq_end - q_first + kQBlock - 1) / kQBlock;
+  const int blocks_per_head = (tile.seq_end - q_first + kQBlock - 1) / kQBlock;
+  // The streamed blocks run over every query head of the group in turn: block b is query block
+  // b % blocks_per_head of query head head * group + b / blocks_per_head.  dK and dV accumulate in
+  // tensor memory over all of them.
+  const int n_blocks = blocks_per_head * group;
   const float scale_log2 = scale * kLog2e;
+  auto q_head_of = [&](int block) { return head * group + block / blocks_per_head; };
+  auto q_begin_of = [&](int block) { return q_first + (block % blocks_per_head) * kQBlock; };
 
   if (tid == 0) {
     sm.abort_flag = 0;
@@ -421,12 +429,12 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       constexpr uint32_t idesc_s = instr_desc(kFmtBF16, kFmtBF16, kTile, kQBlock, 0, 0);
       constexpr uint32_t idesc_g = instr_desc(kFmtBF16, kFmtBF16, kTile, D, 0, 1);
       auto load_stream = [&](int block) {
-        const int st = block % kDkvStages, q0 = q_first + block * kQBlock;
+        const int st = block % kDkvStages, q0 = q_begin_of(block), qh = q_head_of(block);
         mbar_arrive_expect_tx(&sm.stream_full[st], 2 * HALVES * kQBoxBytes);
 #pragma unroll
         for (int j = 0; j < HALVES; ++j) {
-          tma_load_2d(sm.q[st][j], &map_q, head * D + 64 * j, q0, &sm.stream_full[st]);
-          tma_load_2d(sm.d_o[st][j], &map_do, head * D + 64 * j, q0, &sm.stream_full[st]);
+          tma_load_2d(sm.q[st][j], &map_q, qh * D + 64 * j, q0, &sm.stream_full[st]);
+          tma_load_2d(sm.d_o[st][j], &map_do, qh * D + 64 * j, q0, &sm.stream_full[st]);
         }
       };
       auto issue_scores_of = [&](int block) {
@@ -476,15 +484,16 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     // per-query softmax statistics: threads 0-63 fetch those of block qb+1 while block qb is computed
     auto fetch_stats = [&](int block, float &l2, float &dl) {
-      const int qi = q_first + block * kQBlock + tid;
+      const int qi = q_begin_of(block) + tid;
       const bool ok = qi < tile.seq_end;
-      l2 = ok ? lse[(int64_t)qi * H + head] * kLog2e : INFINITY;
-      dl = ok ? delta[(int64_t)qi * H + head] : 0.0f;
+      const int qh = q_head_of(block);
+      l2 = ok ? lse[(int64_t)qi * H + qh] * kLog2e : INFINITY;
+      dl = ok ? delta[(int64_t)qi * H + qh] : 0.0f;
     };
     if (tid < kQBlock && n_blocks > 0) fetch_stats(0, sm.lse2[0][tid], sm.delta[0][tid]);
     for (int qb = 0; qb < n_blocks; ++qb) {
       const int st = qb & 1;
-      const int q0 = q_first + qb * kQBlock;
+      const int q0 = q_begin_of(qb);
       float next_lse2 = INFINITY, next_delta = 0.0f;
       const bool prefetch = tid < kQBlock && qb + 1 < n_blocks;
       if (prefetch) fetch_stats(qb + 1, next_lse2, next_delta);
@@ -529,7 +538,7 @@ k_attn_bwd_dkv(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
     // warps 0-3 write dV, warps 4-7 write dK (scaled)
     const bool store = key_ok && !*abort_flag && n_blocks > 0;
-    __nv_bfloat16 *dst = (h == 0 ? dv : dk) + ((int64_t)key_index * H + head) * D;
+    __nv_bfloat16 *dst = (h == 0 ? dv : dk) + ((int64_t)key_index * H_kv + head) * D;
     const float factor = h == 0 ? 1.0f : scale;
     const uint32_t src = (h == 0 ? tmem_dv : tmem_dk) + lane_base;
 #pragma unroll 1
@@ -571,8 +580,9 @@ template <int HALVES>
 __global__ void __launch_bounds__(128, 2)
 k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
               const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-              const Tile *__restrict__ tiles, int H, float scale, int causal, const float *__restrict__ lse,
-              const float *__restrict__ delta, __nv_bfloat16 *__restrict__ dq, int *error) {
+              const Tile *__restrict__ tiles, int H, int group, float scale, int causal,
+              const float *__restrict__ lse, const float *__restrict__ delta, __nv_bfloat16 *__restrict__ dq,
+              int *error) {
   constexpr int D = 64 * HALVES;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   DqSmem<HALVES> &sm = *reinterpret_cast<DqSmem<HALVES> *>(smem_raw);
@@ -583,6 +593,7 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const Tile tile = tiles[blockIdx.x];
   const int head = tile.head;
+  const int kv_head = head / group;
   const int row = warp * 32 + lane;
   const int q_index = tile.q_begin + row;
   const int key_limit = causal ? min(tile.q_begin + kTile, tile.seq_end) : tile.seq_end;
@@ -627,8 +638,8 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       mbar_arrive_expect_tx(&sm.stream_full, 2 * HALVES * kKeyBoxBytes);
 #pragma unroll
       for (int j = 0; j < HALVES; ++j) {
-        tma_load_2d(sm.k[j], &map_k, head * D + 64 * j, key0, &sm.stream_full);
-        tma_load_2d(sm.v[j], &map_v, head * D + 64 * j, key0, &sm.stream_full);
+        tma_load_2d(sm.k[j], &map_k, kv_head * D + 64 * j, key0, &sm.stream_full);
+        tma_load_2d(sm.v[j], &map_v, kv_head * D + 64 * j, key0, &sm.stream_full);
       }
     }
     mbar_wait(&sm.stream_full, (uint32_t)(kb & 1), abort_flag, error, 32);
@@ -698,9 +709,11 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   if (warp == 0) tmem_dealloc(sm.tmem_base, 256);
 }
 
-int32_t check_attn(const void *q, const void *k, const void *v, int64_t tokens, int32_t H, int32_t D) {
+int32_t check_attn(const void *q, const void *k, const void *v, int64_t tokens, int32_t H, int32_t H_kv, int32_t D) {
   if (!q || !k || !v) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
   if (H <= 0 || tokens < 0) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "invalid shape");
+  if (H_kv <= 0 || H % H_kv != 0)
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "the %d query heads must be a multiple of the %d key/value heads", H, H_kv);
   if (D != 64 && D != 128) TGB_FAIL(TGB_STATUS_UNSUPPORTED, "dense attention supports head widths 64 and 128 (got %d)", D);
   if (tokens > (int64_t)INT32_MAX - 256) TGB_FAIL(TGB_STATUS_UNSUPPORTED, "too many tokens");
   return TGB_STATUS_OK;
@@ -717,30 +730,31 @@ int32_t head_map(CUtensorMap *map, const void *base, int64_t tokens, int32_t H, 
 using namespace tgb;
 
 extern "C" int32_t tgb_varlen_attn_fwd(const void *q, const void *k, const void *v, void *out, void *lse,
-                                       const void *tiles, int64_t n_tiles, int64_t tokens, int32_t H, int32_t D,
-                                       float scale, int32_t causal, void *error_flag, uint64_t stream) {
-  int32_t rc = check_attn(q, k, v, tokens, H, D);
+                                       const void *tiles, int64_t n_tiles, int64_t tokens, int32_t H, int32_t H_kv,
+                                       int32_t D, float scale, int32_t causal, void *error_flag, uint64_t stream) {
+  int32_t rc = check_attn(q, k, v, tokens, H, H_kv, D);
   if (rc) return rc;
   if (n_tiles == 0) return TGB_STATUS_OK;
   if (!out || !lse || !tiles || !error_flag) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
   CUtensorMap map_q, map_k, map_v;
   if ((rc = head_map(&map_q, q, tokens, H, D))) return rc;
-  if ((rc = head_map(&map_k, k, tokens, H, D, kKeyBlock))) return rc;
-  if ((rc = head_map(&map_v, v, tokens, H, D, kKeyBlock))) return rc;
+  if ((rc = head_map(&map_k, k, tokens, H_kv, D, kKeyBlock))) return rc;
+  if ((rc = head_map(&map_v, v, tokens, H_kv, D, kKeyBlock))) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const unsigned grid = (unsigned)n_tiles;
   const float scale_log2 = scale * kLog2e;
+  const int group = H / H_kv;
   if (D == 128) {
     const size_t smem = sizeof(FwdSmem<2>);
     // the attribute belongs to the current device's context, so it is set on every call (cheap)
     TGB_CUDA(cudaFuncSetAttribute(k_attn_fwd<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k_attn_fwd<2><<<grid, kFwdThreads, smem, st>>>(map_q, map_k, map_v, (const Tile *)tiles, H, scale_log2, causal,
+    k_attn_fwd<2><<<grid, kFwdThreads, smem, st>>>(map_q, map_k, map_v, (const Tile *)tiles, H, group, scale_log2, causal,
                                            (__nv_bfloat16 *)out, (float *)lse, (int *)error_flag);
   } else {
     const size_t smem = sizeof(FwdSmem<1>);
     // the attribute belongs to the current device's context, so it is set on every call (cheap)
     TGB_CUDA(cudaFuncSetAttribute(k_attn_fwd<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k_attn_fwd<1><<<grid, kFwdThreads, smem, st>>>(map_q, map_k, map_v, (const Tile *)tiles, H, scale_log2, causal,
+    k_attn_fwd<1><<<grid, kFwdThreads, smem, st>>>(map_q, map_k, map_v, (const Tile *)tiles, H, group, scale_log2, causal,
                                            (__nv_bfloat16 *)out, (float *)lse, (int *)error_flag);
   }
   TGB_LAUNCHED();
@@ -750,21 +764,22 @@ extern "C" int32_t tgb_varlen_attn_fwd(const void *q, const void *k, const void 
 extern "C" int32_t tgb_varlen_attn_bwd(const void *q, const void *k, const void *v, const void *out,
                                        const void *dout, const void *lse, void *dq, void *dk, void *dv,
                                        void *delta, const void *query_tiles, const void *key_tiles,
-                                       int64_t n_tiles, int64_t tokens, int32_t H, int32_t D, float scale,
-                                       int32_t causal, void *error_flag, uint64_t stream) {
-  int32_t rc = check_attn(q, k, v, tokens, H, D);
+                                       int64_t n_tiles, int64_t n_key_tiles, int64_t tokens, int32_t H,
+                                       int32_t H_kv, int32_t D, float scale, int32_t causal, void *error_flag,
+                                       uint64_t stream) {
+  int32_t rc = check_attn(q, k, v, tokens, H, H_kv, D);
   if (rc) return rc;
   if (n_tiles == 0) return TGB_STATUS_OK;
   if (!out || !dout || !lse || !dq || !dk || !dv || !delta || !query_tiles || !key_tiles || !error_flag)
     TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
   CUtensorMap map_q, map_k, map_v, map_do;
   if ((rc = head_map(&map_q, q, tokens, H, D))) return rc;
-  if ((rc = head_map(&map_k, k, tokens, H, D))) return rc;
-  if ((rc = head_map(&map_v, v, tokens, H, D))) return rc;
+  if ((rc = head_map(&map_k, k, tokens, H_kv, D))) return rc;
+  if ((rc = head_map(&map_v, v, tokens, H_kv, D))) return rc;
   if ((rc = head_map(&map_do, dout, tokens, H, D))) return rc;
   CUtensorMap map_k64, map_v64, map_q64, map_do64;
-  if ((rc = head_map(&map_k64, k, tokens, H, D, kKeyBlock))) return rc;
-  if ((rc = head_map(&map_v64, v, tokens, H, D, kKeyBlock))) return rc;
+  if ((rc = head_map(&map_k64, k, tokens, H_kv, D, kKeyBlock))) return rc;
+  if ((rc = head_map(&map_v64, v, tokens, H_kv, D, kKeyBlock))) return rc;
   if ((rc = head_map(&map_q64, q, tokens, H, D, kQBlock))) return rc;
   if ((rc = head_map(&map_do64, dout, tokens, H, D, kQBlock))) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -773,7 +788,8 @@ extern "C" int32_t tgb_varlen_attn_bwd(const void *q, const void *k, const void 
                                                                   (const __nv_bfloat16 *)dout, rows, D,
                                                                   (float *)delta);
   TGB_LAUNCHED();
-  const unsigned grid = (unsigned)n_tiles;
+  const unsigned grid = (unsigned)n_tiles, key_grid = (unsigned)n_key_tiles;
+  const int group = H / H_kv;
 #define TGB_BWD(HV)                                                                                         \
   {                                                                                                         \
     const size_t smem = sizeof(DkvSmem<HV>) + 1024;                                                         \
@@ -781,11 +797,11 @@ extern "C" int32_t tgb_varlen_attn_bwd(const void *q, const void *k, const void 
     /* per-device attribute: set on every call */                                                          \
     TGB_CUDA(cudaFuncSetAttribute(k_attn_bwd_dkv<HV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
     TGB_CUDA(cudaFuncSetAttribute(k_attn_bwd_dq<HV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq)); \
-    k_attn_bwd_dkv<HV><<<grid, kDkvThreads, smem, st>>>(map_q64, map_k, map_v, map_do64, (const Tile *)key_tiles, H, scale, \
+    k_attn_bwd_dkv<HV><<<key_grid, kDkvThreads, smem, st>>>(map_q64, map_k, map_v, map_do64, (const Tile *)key_tiles, H, H_kv, scale, \
                                                 causal, (const float *)lse, (const float *)delta,           \
                                                 (__nv_bfloat16 *)dk, (__nv_bfloat16 *)dv, (int *)error_flag); \
     TGB_LAUNCHED();                                                                                         \
-    k_attn_bwd_dq<HV><<<grid, 128, smem_dq, st>>>(map_q, map_k64, map_v64, map_do, (const Tile *)query_tiles, H, scale, \
+    k_attn_bwd_dq<HV><<<grid, 128, smem_dq, st>>>(map_q, map_k64, map_v64, map_do, (const Tile *)query_tiles, H, group, scale, \
                                                causal, (const float *)lse, (const float *)delta,            \
                                                (__nv_bfloat16 *)dq, (int *)error_flag);                     \
     TGB_LAUNCHED();                                                                                         \

@@ -647,9 +647,10 @@ int32_t tgb_csr_plan_scratch_bytes(const tgb_csr_plan *plan, int32_t direction,
   if (!bytes) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null output");
   int32_t rc = check_common(plan, reducer, feature_elems, dtype);
   if (rc) return rc;
-  if (direction == 1 && !(plan->flags & TGB_PLAN_TRANSPOSE))
+  if (direction < 0 || direction > 2) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "direction must be 0, 1 or 2");
+  if (direction >= 1 && !(plan->flags & TGB_PLAN_TRANSPOSE))
     TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "plan has no transposed relation");
-  const Side &side = direction == 1 ? plan->bwd : plan->fwd;
+  const Side &side = direction >= 1 ? plan->bwd : plan->fwd;
   uint64_t b = partial_bytes(side, reducer, feature_elems);
   if (direction == 1 && permute_weights_first(reducer))
     b += align_up((uint64_t)plan->num_edges * 4, 256);   // weights in transposed order
@@ -726,7 +727,9 @@ int32_t tgb_csr_reduce_bwd_dx(const tgb_csr_plan *plan, int32_t reducer,
   uint64_t need = part;
   if (reducer == TGB_REDUCER_MEAN)
     need += align_up((uint64_t)plan->num_dst * (uint64_t)F * 4, 256);
-  const bool permute = w && permute_weights_first(reducer) && plan->num_edges > 0;
+  // SUM / MEAN: `aux`, when given, holds the weights already in transposed order
+  const float *ready = reducer != TGB_REDUCER_MAX ? (const float *)aux : nullptr;
+  const bool permute = w && !ready && permute_weights_first(reducer) && plan->num_edges > 0;
   const uint64_t permuted_at = need;
   if (permute) need += align_up((uint64_t)plan->num_edges * 4, 256);
   if (need > 0 && (side.n_seg > 0 || reducer == TGB_REDUCER_MEAN || permute) &&
@@ -762,6 +765,10 @@ int32_t tgb_csr_reduce_bwd_dx(const tgb_csr_plan *plan, int32_t reducer,
   if (reducer == TGB_REDUCER_MAX)
     return w ? launch_gather<int64_t, int32_t, kSum, true, true, true>(a, s, st)
              : launch_gather<int64_t, int32_t, kSum, false, false, true>(a, s, st);
+  if (ready) {
+    a.w = ready;
+    return launch_gather<int64_t, int32_t, kSum, true, false, false>(a, s, st);
+  }
   if (permute) {
     float *w_t = (float *)((char *)scratch + permuted_at);
     k_permute_weights<<<(unsigned)ceil_div(plan->num_edges, 256), 256, 0, st>>>(
@@ -772,6 +779,18 @@ int32_t tgb_csr_reduce_bwd_dx(const tgb_csr_plan *plan, int32_t reducer,
   }
   return w ? launch_gather<int64_t, int32_t, kSum, true, true, false>(a, s, st)
            : launch_gather<int64_t, int32_t, kSum, false, false, false>(a, s, st);
+}
+
+int32_t tgb_csr_transposed_weights(const tgb_csr_plan *plan, const void *w, void *w_t, uint64_t stream) {
+  if (!plan) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null plan");
+  if (!(plan->flags & TGB_PLAN_TRANSPOSE))
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "plan was created without TGB_PLAN_TRANSPOSE");
+  if (plan->num_edges == 0) return TGB_STATUS_OK;
+  if (!w || !w_t) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
+  k_permute_weights<<<(unsigned)ceil_div(plan->num_edges, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const float *)w, plan->bwd.eid, plan->num_edges, (float *)w_t);
+  TGB_LAUNCHED();
+  return TGB_STATUS_OK;
 }
 
 int32_t tgb_csr_reduce_bwd_dw(const tgb_csr_plan *plan, int32_t reducer,

@@ -63,15 +63,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 
 // Bounded wait.  `abort_flag` lives in shared memory (one per CTA), `error`
 // in global memory (one per launch); `code` says which wait gave up.
-__device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                          int *error, int code) {
+__device__ __forceinline__ void mbar_wait_limited(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                                  int *error, int code, uint32_t limit) {
   if (*abort_flag) return;
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     if (mbar_try_wait(bar, parity)) return;
     if ((spin & 1023u) == 1023u && *abort_flag) return;
   }
   *abort_flag = 1;
   atomicCAS(error, 0, code);
+}
+
+__device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                          int *error, int code) {
+  mbar_wait_limited(bar, parity, abort_flag, error, code, kSpinLimit);
 }
 
 // ---- proxies / fences ---------------------------------------------------------

@@ -6,7 +6,7 @@ Public names follow python/tiga/__init__.py:45-105 of the reference for the
 part of the API that lies on this path: ``MessagePassing``, ``Graph``, the
 reducers, ``tg.math``, and the distributed placement objects.
 """
-from . import math
+from . import codegen, math
 from .distributed import ByDestination, DeviceMesh, GraphPlacement, HaloMap, derive_halo_map
 from .graph import Graph, GraphSchema
 from .kernel import AnalysisFinding, CompiledVariant, Kernel
@@ -20,5 +20,5 @@ __all__ = [
     "AnalysisFinding", "ByDestination", "CompiledVariant", "DeviceMesh", "Graph", "GraphPlacement",
     "GraphSchema", "HaloMap", "Kernel", "MaxReducer", "MeanReducer", "MessagePassing", "OnlineSoftmaxItem",
     "OnlineSoftmaxReducer", "ProductReducer", "Reducer", "ReducerCall", "SumReducer", "derive_halo_map",
-    "math", "max", "mean", "online_softmax", "prod", "sum",
+    "codegen", "math", "max", "mean", "online_softmax", "prod", "sum",
 ]

@@ -47,11 +47,12 @@ _SIGNATURES = {
     "tgb_csr_reduce_fwd": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _i32, _vp, _u64, _u64]),
     "tgb_csr_reduce_bwd_dx": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i32, _vp, _u64, _u64]),
     "tgb_csr_reduce_bwd_dw": (_i32, [_vp, _i32, _vp, _vp, _vp, _vp, _i64, _i32, _vp, _u64, _u64]),
+    "tgb_csr_transposed_weights": (_i32, [_vp, _vp, _vp, _u64]),
     "tgb_csr_wsum_fwd_noalloc": (_i32, [_vp, _vp, _vp, _vp, _i64, _f32, _u64]),
     "tgb_rows_gather": (_i32, [_vp, _vp, _vp, _i64, _i64, _u64]),
     "tgb_rows_scatter_add": (_i32, [_vp, _vp, _vp, _i64, _i64, _u64]),
-    "tgb_varlen_attn_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _f32, _i32, _vp, _u64]),
-    "tgb_varlen_attn_bwd": (_i32, [_vp] * 12 + [_i64, _i64, _i32, _i32, _f32, _i32, _vp, _u64]),
+    "tgb_varlen_attn_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _f32, _i32, _vp, _u64]),
+    "tgb_varlen_attn_bwd": (_i32, [_vp] * 12 + [_i64, _i64, _i64, _i32, _i32, _i32, _f32, _i32, _vp, _u64]),
     "tgb_linear_f32": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _vp, _u64]),
     "tgb_linear_dw_f32": (_i32, [_vp, _vp, _vp, _vp, _u64, _i64, _i32, _i32, _vp, _u64]),
     "tgb_linear_dw_partials": (_i32, [_i64, ctypes.POINTER(_i32)]),
@@ -59,6 +60,9 @@ _SIGNATURES = {
     "tgb_gat_scratch_bytes": (_i32, [_vp, _i32, _i32, _i32, ctypes.POINTER(_u64)]),
     "tgb_gat_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _f32, _vp, _u64, _u64]),
     "tgb_gat_bwd": (_i32, [_vp] * 11 + [_i32, _i32, _f32, _vp, _vp, _vp, _vp, _vp, _u64, _u64]),
+    "tgb_selftest_bounded_wait": (_i32, [_vp, ctypes.c_uint32, _vp, _u64]),
+    "tgb_softmax_field_fwd": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _u64]),
+    "tgb_softmax_field_bwd": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _u64]),
 }
 
 
@@ -89,7 +93,7 @@ def lib() -> ctypes.CDLL:
 
 
 def check(status: int, operation: str) -> None:
-    if status != OK:
+    if status:
         handle = lib()
         message = handle.tgb_last_error().decode() or handle.tgb_status_string(status).decode()
         if status == UNSUPPORTED:

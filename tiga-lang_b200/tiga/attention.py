@@ -97,31 +97,103 @@ def gat_attention(graph, x_src, x_dst, a_src, a_dst, slope: float):
     return GATFunction.apply(x_src, x_dst, a_src, a_dst, graph, slope)
 
 
-def _attention_tiles(graph, device, heads):
+class FieldSoftmaxFunction(torch.autograd.Function):
+    """``online_softmax(edge.score, src.value)``: scores per edge, values per source.
+
+    score [E, *lanes] (trailing singleton dims are dropped, as the reference's evaluator does,
+    python/tiga/interop/torch/reducer_oracle.py:69-72), value [num_src, *lanes, *payload];
+    float32 state; the result has the value's dtype and is exactly 0 for a row without edges."""
+
+    @staticmethod
+    def forward(ctx, score, value, graph):
+        squeezed = score
+        while squeezed.ndim > 1 and squeezed.shape[-1] == 1:
+            squeezed = squeezed.squeeze(-1)
+        lanes = tuple(squeezed.shape[1:])
+        if tuple(value.shape[1:1 + len(lanes)]) != lanes:
+            raise ValueError(f"value {tuple(value.shape)} does not carry the score's lanes {lanes}")
+        if value.dtype not in (torch.float32, torch.bfloat16):
+            raise NotImplementedError(f"online-softmax values must be float32 or bfloat16, got {value.dtype}")
+        if not score.dtype.is_floating_point:
+            raise NotImplementedError("online-softmax scores must be floating point")
+        H = 1
+        for extent in lanes:
+            H *= int(extent)
+        E, num_src = squeezed.shape[0], value.shape[0]
+        D = max(int(value.numel() // max(num_src * H, 1)), 1) if num_src else 1
+        s32 = squeezed.reshape(E, H).to(torch.float32).contiguous()
+        v = value.contiguous()
+        needs_grad = score.requires_grad or value.requires_grad
+        plan = graph.native_plan(transpose=needs_grad)
+        if plan.num_edges != E or plan.num_src != num_src:
+            raise ValueError("score must have one row per edge and value one row per source")
+        device = v.device
+        out = torch.empty((plan.num_dst, H * D), dtype=torch.float32, device=device)
+        m = torch.empty((plan.num_dst, H), dtype=torch.float32, device=device)
+        l = torch.empty_like(m)
+        dtype_id = _native.DTYPE_BF16 if v.dtype == torch.bfloat16 else _native.DTYPE_F32
+        with torch.cuda.device(device):
+            _native.check(_native.lib().tgb_softmax_field_fwd(
+                plan.handle, s32.data_ptr(), v.data_ptr(), dtype_id, out.data_ptr(), m.data_ptr(), l.data_ptr(),
+                H, D, _stream(device)), "tgb_softmax_field_fwd")
+        ctx.graph, ctx.H, ctx.D, ctx.dtype_id = graph, H, D, dtype_id
+        ctx.score_meta, ctx.value_meta = (score.shape, score.dtype), (value.shape, value.dtype)
+        ctx.save_for_backward(s32, v, out, m, l)
+        return out.reshape((plan.num_dst,) + tuple(value.shape[1:])).to(value.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        s32, v, out, m, l = ctx.saved_tensors
+        plan = ctx.graph.native_plan(transpose=True)
+        H, D = ctx.H, ctx.D
+        device = v.device
+        dout = grad_output.reshape(plan.num_dst, H * D).to(torch.float32).contiguous()
+        d_score = torch.empty_like(s32)
+        d_value = torch.empty((plan.num_src, H * D), dtype=torch.float32, device=device)
+        weights = torch.empty_like(s32)
+        with torch.cuda.device(device):
+            _native.check(_native.lib().tgb_softmax_field_bwd(
+                plan.handle, s32.data_ptr(), v.data_ptr(), ctx.dtype_id, out.data_ptr(), dout.data_ptr(),
+                m.data_ptr(), l.data_ptr(), H, D, d_score.data_ptr(), d_value.data_ptr(), weights.data_ptr(),
+                _stream(device)), "tgb_softmax_field_bwd")
+        (score_shape, score_dtype), (value_shape, value_dtype) = ctx.score_meta, ctx.value_meta
+        needs = ctx.needs_input_grad
+        return (d_score.reshape(score_shape).to(score_dtype) if needs[0] else None,
+                d_value.reshape(value_shape).to(value_dtype) if needs[1] else None, None)
+
+
+def field_softmax(graph, score, value):
+    if not value.is_cuda:
+        raise RuntimeError("the online-softmax reducer runs on CUDA tensors only (no CPU fallback)")
+    return FieldSoftmaxFunction.apply(score, value, graph)
+
+
+def _attention_tiles(graph, device, heads, kv_heads):
     """int32 [n, 4] = (first token of the tile, sequence begin, sequence end, head) for every
     (128-token tile, head).  Order: longest sequence first, then head, then the heaviest tile of
     that (sequence, head) first -- CTAs that are resident together then read the same K/V (or
     Q/dO) stream, which keeps it in L2, while the long tiles still start early.  Returns the
-    table for the query-major kernels, the causal flag and the table for the key-major kernel."""
+    table for the query-major kernels (query heads), the causal flag and the table for the
+    key-major kernel (key/value heads)."""
     cached = graph.__dict__.get("_attention_tiles")
-    if cached is not None and cached[0].device == device and cached[3] == heads:
+    if cached is not None and cached[0].device == device and cached[3] == (heads, kv_heads):
         return cached
     bounds = graph.sequence_boundaries().tolist()
     causal = graph._dense_boundary == "lower_inclusive"
     sequences = sorted(zip(bounds[:-1], bounds[1:]), key=lambda be: be[0] - be[1])
 
-    def table(key_major):
+    def table(key_major, count):
         rows = []
         for begin, end in sequences:
             starts = list(range(begin, end, 128))
             # query-major + causal: later tiles see more keys; key-major + causal: earlier tiles see more queries
             if causal and not key_major:
                 starts.reverse()
-            for head in range(heads):
+            for head in range(count):
                 rows.extend((t0, begin, end, head) for t0 in starts)
         return torch.tensor(rows, dtype=torch.int32).reshape(-1, 4).to(device)
 
-    graph.__dict__["_attention_tiles"] = (table(False), causal, table(True), heads)
+    graph.__dict__["_attention_tiles"] = (table(False, heads), causal, table(True, kv_heads), (heads, kv_heads))
     return graph.__dict__["_attention_tiles"]
 
 
@@ -133,20 +205,27 @@ class VarlenAttentionFunction(torch.autograd.Function):
         for name, t in (("query", query), ("key", key), ("value", value)):
             if t.dtype != torch.bfloat16:
                 raise NotImplementedError(f"dense attention kernels take bfloat16 inputs; {name} is {t.dtype}")
-            if t.ndim != 3 or t.shape != query.shape:
-                raise NotImplementedError("dense attention expects query, key, value of one shape [tokens, H, D]")
+            if t.ndim != 3:
+                raise NotImplementedError("dense attention expects fields of shape [tokens, heads, D]")
         tokens, H, D = query.shape
+        H_kv = key.shape[1]
+        if key.shape != value.shape or key.shape[0] != tokens or key.shape[2] != D or H % max(H_kv, 1):
+            raise NotImplementedError(
+                "dense attention expects key and value of one shape [tokens, H_kv, D] with the query's tokens "
+                f"and D, and H a multiple of H_kv (grouped queries); got query {tuple(query.shape)}, "
+                f"key {tuple(key.shape)}, value {tuple(value.shape)}")
         if tokens != graph.num_dst:
             raise ValueError(f"fields must have {graph.num_dst} rows, got {tokens}")
         q, k, v = query.contiguous(), key.contiguous(), value.contiguous()
-        tiles, causal, _, _ = _attention_tiles(graph, q.device, H)
+        tiles, causal, _, _ = _attention_tiles(graph, q.device, H, H_kv)
         out = torch.empty_like(q)
         lse = torch.empty((tokens, H), dtype=torch.float32, device=q.device)
         with torch.cuda.device(q.device):
             _native.check(_native.lib().tgb_varlen_attn_fwd(
                 q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), tiles.data_ptr(),
-                tiles.shape[0], tokens, H, D, float(scale), int(causal), ops.error_flag(q.device).data_ptr(),
+                tiles.shape[0], tokens, H, H_kv, D, float(scale), int(causal), ops.error_flag(q.device).data_ptr(),
                 _stream(q.device)), "tgb_varlen_attn_fwd")
+            ops.launched(q.device)
         ctx.graph, ctx.scale = graph, float(scale)
         ctx.save_for_backward(q, k, v, out, lse)
         return out
@@ -157,21 +236,24 @@ class VarlenAttentionFunction(torch.autograd.Function):
 
         q, k, v, out, lse = ctx.saved_tensors
         tokens, H, D = q.shape
+        H_kv = k.shape[1]
         d_out = grad_output.contiguous().to(torch.bfloat16)
-        query_tiles, causal, key_tiles, _ = _attention_tiles(ctx.graph, q.device, H)
+        query_tiles, causal, key_tiles, _ = _attention_tiles(ctx.graph, q.device, H, H_kv)
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         delta = torch.empty((tokens, H), dtype=torch.float32, device=q.device)
         with torch.cuda.device(q.device):
             _native.check(_native.lib().tgb_varlen_attn_bwd(
                 q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), d_out.data_ptr(), lse.data_ptr(),
                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr(), query_tiles.data_ptr(),
-                key_tiles.data_ptr(), query_tiles.shape[0], tokens, H, D, ctx.scale, int(causal),
-                ops.error_flag(q.device).data_ptr(), _stream(q.device)), "tgb_varlen_attn_bwd")
+                key_tiles.data_ptr(), query_tiles.shape[0], key_tiles.shape[0], tokens, H, H_kv, D, ctx.scale,
+                int(causal), ops.error_flag(q.device).data_ptr(), _stream(q.device)), "tgb_varlen_attn_bwd")
+            ops.launched(q.device)
         return dq, dk, dv, None, None
 
 
 def varlen_attention(graph, query, key, value, scale):
-    """softmax(q k^T * scale [+ causal]) v inside every sequence of a packed batch."""
+    """softmax(q k^T * scale [+ causal]) v inside every sequence of a packed batch; with fewer
+    key/value heads than query heads, consecutive query heads share one (grouped queries)."""
     if not query.is_cuda:
         raise RuntimeError("dense attention runs on CUDA tensors only (no CPU fallback)")
     return VarlenAttentionFunction.apply(query, key, value, graph, scale)

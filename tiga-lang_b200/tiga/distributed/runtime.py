@@ -109,6 +109,15 @@ class NativeBackend:
         return out
 
     @staticmethod
+    def begin_forward(shard):
+        """A new forward over the shard: weights kept in transposed order by the last backward go."""
+        from .. import ops
+
+        for relation in (shard.graph_own, shard.graph_ghost):
+            for plan in relation._plans.values():
+                ops.forget_transposed_weights(plan)
+
+    @staticmethod
     def backward_dx(graph, dy, w):
         from .. import ops
 
@@ -361,6 +370,8 @@ class _HaloWeightedSum(torch.autograd.Function):
         w_own = w_ghost = w_flat        # the sub-relations read it through their edge maps
         device = rows.device
         runtime.mark("forward:begin", device)
+        if hasattr(backend, "begin_forward"):
+            backend.begin_forward(shard)
         ghost_x = torch.empty((int(shard.ghosts.numel()), F), dtype=rows.dtype, device=rows.device)
         packed = {p: backend.pack_rows(rows, ids) for p, ids in enumerate(shard.send_ids) if ids.numel()}
         in_flight = []

@@ -368,6 +368,47 @@ class Graph:
         lo, hi = self.degree_bounds()
         return lo if lo == hi else None
 
+    _HISTOGRAM_DEGREE_LIMIT = 4096
+
+    def degree_histogram(self) -> tuple[int, ...]:
+        """``counts[d]`` = number of destination rows with exactly ``d`` edges, for ``d`` up to the
+        largest degree; exact, integer work on the graph's device.  Like the reference's
+        (python/tiga/interop/torch/graph.py:1258-1277) it refuses graphs whose largest degree
+        exceeds 4096: the table is a planning aid for bounded-degree graphs."""
+        _, largest, _ = self.degree_statistics()
+        if largest > self._HISTOGRAM_DEGREE_LIMIT:
+            raise ValueError("exact degree histogram is limited to degree_max <= 4096")
+        if self._row_ptr is None and self._schema.realization == "implicit_dense":
+            if self._dense_boundary == "lower_inclusive":     # row i sees i + 1 sources
+                return (0,) + (1,) * largest
+            return (0,) * largest + (self.num_dst,)
+        row_ptr = self.resolve_csr()[0]
+        lengths = (row_ptr[1:] - row_ptr[:-1]).to(torch.int64)
+        return tuple(torch.bincount(lengths, minlength=largest + 1).cpu().tolist())
+
+    def source_index_span_ratio(self, samples: int = 4096) -> float:
+        """Locality signal for planning: mean ``|source id - destination id|`` over up to
+        ``samples`` evenly spaced edge slots, divided by the larger endpoint count.  Near 0 for
+        index-local gathers, about 1/3 for random numbering (the reference's definition,
+        python/tiga/interop/torch/graph.py:1279-1311); cached on the immutable snapshot."""
+        cached = self.__dict__.get("_span_ratio_cache")
+        if cached is not None:
+            return cached
+        if self._row_ptr is None and self._schema.realization in ("implicit_dense", "implicit_block_dense"):
+            return 1.0 / 3.0
+        row_ptr, col_idx = self.resolve_csr()
+        edges = int(col_idx.numel())
+        ratio = 0.0
+        if edges:
+            picked = torch.linspace(0, edges - 1, min(int(samples), edges), dtype=torch.float64,
+                                    device=col_idx.device).to(row_ptr.dtype)
+            owner = torch.searchsorted(row_ptr[1:].contiguous(), picked, right=True)
+            distance = (col_idx[picked.long()].to(torch.int64) - owner).abs().double().mean()
+            ratio = float(distance.item()) / max(1, self.num_src, self.num_dst)
+        ratio = min(max(ratio, 0.0), 1.0)
+        self.__dict__["_span_ratio_cache"] = ratio
+        return ratio
+
     def specialization_key(self) -> tuple[object, ...]:
         placement = self._placement.specialization_key() if self._placement is not None else ()
         return (*self._schema.specialization_key(), self._dense_boundary, placement)

@@ -28,7 +28,28 @@ def _as_rows(tensor: torch.Tensor, rows: int) -> torch.Tensor:
     if tensor.dtype != torch.float32:
         raise NotImplementedError(
             f"the CSR reduce kernels take float32 fields, got {tensor.dtype}")
+    if tensor.ndim == 2 and tensor.is_contiguous():
+        return tensor
     return tensor.contiguous().reshape(rows, -1)
+
+
+class _OnDevice:
+    """`with _OnDevice(device):` makes `device` current for a launch; costs nothing when it already is
+    (the usual case: one process per GPU)."""
+
+    __slots__ = ("guard",)
+
+    def __init__(self, device):
+        self.guard = None if torch.cuda.current_device() == device.index else torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
+        return False
 
 
 def csr_reduce_forward(plan: CSRPlan, reducer: str, x: torch.Tensor, w: torch.Tensor | None,
@@ -41,13 +62,40 @@ def csr_reduce_forward(plan: CSRPlan, reducer: str, x: torch.Tensor, w: torch.Te
     out = accumulate_into if accumulate_into is not None else torch.empty(
         (plan.num_dst, F), dtype=torch.float32, device=x.device)
     flags = _native.REDUCE_ACCUMULATE if accumulate_into is not None else 0
+    forget_transposed_weights(plan)
     aux = torch.empty((plan.num_dst, F), dtype=torch.int32, device=x.device) if reducer == "max" else None
     keep, scratch, scratch_bytes = plan.scratch(0, rid, F)
-    with torch.cuda.device(x.device):
+    with _OnDevice(x.device):
         _native.check(lib.tgb_csr_reduce_fwd(plan.handle, rid, _ptr(x), _ptr(w), _ptr(out), _ptr(aux), F,
                                              _native.DTYPE_F32, float(identity), flags, scratch, scratch_bytes,
                                              _stream(x.device)), "tgb_csr_reduce_fwd")
     return out, aux
+
+
+def forget_transposed_weights(plan: CSRPlan) -> None:
+    """Every forward over a plan drops the transposed weights kept from the last backward."""
+    plan.__dict__.pop("_transposed_weights", None)
+
+
+def transposed_weights(plan: CSRPlan, w: torch.Tensor) -> torch.Tensor:
+    """The weights in the order of the plan's transposed relation.  They are kept on the plan from
+    one backward call to the next while the same weight tensor (same memory, same version counter)
+    comes back, and dropped by the next forward over the plan: the layers of a network that share
+    one edge-weight array permute it once per backward pass, not once per layer, and nothing
+    survives into the next step.  The cache holds a reference to the weight tensor so that its
+    memory cannot be handed to another tensor meanwhile."""
+    cached = plan.__dict__.get("_transposed_weights")
+    if cached is not None:
+        held, version, w_t = cached
+        if held.data_ptr() == w.data_ptr() and held.numel() == w.numel() and w._version == version \
+                and held._version == version:
+            return w_t
+    w_t = torch.empty(plan.num_edges, dtype=torch.float32, device=w.device)
+    with _OnDevice(w.device):
+        _native.check(_native.lib().tgb_csr_transposed_weights(plan.handle, w.data_ptr(), w_t.data_ptr(),
+                                                               _stream(w.device)), "tgb_csr_transposed_weights")
+    plan.__dict__["_transposed_weights"] = (w, w._version, w_t)
+    return w_t
 
 
 def csr_reduce_backward_dx(plan: CSRPlan, reducer: str, dy: torch.Tensor, w: torch.Tensor | None, aux=None):
@@ -55,8 +103,11 @@ def csr_reduce_backward_dx(plan: CSRPlan, reducer: str, dy: torch.Tensor, w: tor
     rid = _REDUCER_IDS[reducer]
     F = dy.shape[1]
     dx = torch.empty((plan.num_src, F), dtype=torch.float32, device=dy.device)
-    keep, scratch, scratch_bytes = plan.scratch(1, rid, F)
-    with torch.cuda.device(dy.device):
+    ready = w is not None and reducer != "max" and plan.num_edges > 0
+    if ready:
+        aux = transposed_weights(plan, w)
+    keep, scratch, scratch_bytes = plan.scratch(2 if ready else 1, rid, F)
+    with _OnDevice(dy.device):
         _native.check(lib.tgb_csr_reduce_bwd_dx(plan.handle, rid, _ptr(dy), _ptr(w), _ptr(aux), _ptr(dx), F,
                                                 _native.DTYPE_F32, scratch, scratch_bytes,
                                                 _stream(dy.device)), "tgb_csr_reduce_bwd_dx")
@@ -72,7 +123,7 @@ def csr_reduce_backward_dw(plan: CSRPlan, reducer: str, dy: torch.Tensor, x: tor
         raise ValueError("a plan with an edge map writes dw into the caller's full-length array: pass out=")
     dw = out if out is not None else torch.empty((plan.num_edges,), dtype=torch.float32, device=dy.device)
     keep, scratch, scratch_bytes = plan.scratch(0, rid, F)
-    with torch.cuda.device(dy.device):
+    with _OnDevice(dy.device):
         _native.check(lib.tgb_csr_reduce_bwd_dw(plan.handle, rid, _ptr(dy), _ptr(x), _ptr(aux), _ptr(dw), F,
                                                 _native.DTYPE_F32, scratch, scratch_bytes,
                                                 _stream(dy.device)), "tgb_csr_reduce_bwd_dw")
@@ -128,30 +179,82 @@ def csr_reduce(graph, reducer: str, x: torch.Tensor, w: torch.Tensor | None, ide
     """Differentiable ``reduce_{e in row i} w[e] * x[col[e]]`` on the GPU."""
     if not x.is_cuda:
         raise RuntimeError("csr_reduce runs on CUDA tensors only (no CPU fallback)")
+    if not (torch.is_grad_enabled() and (x.requires_grad or (w is not None and w.requires_grad))):
+        # nothing to differentiate: launch the forward kernel without building an autograd node
+        if w is not None:
+            if w.dtype != torch.float32:
+                raise NotImplementedError(f"edge weights must be float32, got {w.dtype}")
+            w = w if w.ndim == 1 and w.is_contiguous() else w.contiguous().reshape(-1)
+        out, _ = csr_reduce_forward(graph.native_plan(transpose=False), reducer, _as_rows(x, graph.num_src), w,
+                                    float(identity))
+        return out if x.ndim == 2 else out.reshape((graph.num_dst,) + tuple(x.shape[1:]))
     return CSRReduceFunction.apply(x, w, graph, reducer, float(identity))
 
 
 # --------------------------------------------------------------------------- dense linear
-_error_flags = {}
+class _ErrorWord:
+    """One int32 per device that the tensor-core kernels set when a bounded wait gives up, with a
+    pinned host mirror.  After every launch that may set it, the word is copied to the mirror on the
+    launching stream (asynchronously); the next tensor-core call on the device looks at the mirror of
+    the copies that have completed by then and raises, so a give-up surfaces without the caller
+    asking and without a synchronisation on the good path."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.word = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.mirror = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.copied = None
+
+    def after_launch(self):
+        self.mirror.copy_(self.word, non_blocking=True)
+        self.copied = torch.cuda.Event()
+        self.copied.record(torch.cuda.current_stream(self.device))
+
+    def raise_if_set(self, wait: bool):
+        if wait:
+            code = int(self.word.item())
+        elif self.copied is not None and self.copied.query():
+            code = int(self.mirror[0])
+        else:
+            return
+        if code:
+            self.word.zero_()
+            self.mirror.zero_()
+            raise RuntimeError(f"a tensor-core kernel gave up on a bounded wait (code {code}); "
+                               "the results of that call are invalid")
+
+
+_error_words = {}
+
+
+def _error_word(device) -> _ErrorWord:
+    key = torch.device(device).index
+    if key is None:
+        key = torch.cuda.current_device()
+    if key not in _error_words:
+        _error_words[key] = _ErrorWord(torch.device("cuda", key))
+    return _error_words[key]
 
 
 def error_flag(device) -> torch.Tensor:
-    """One int32 per device that tensor-core kernels set when a bounded wait gives up."""
-    key = torch.device(device).index
-    if key not in _error_flags:
-        _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _error_flags[key]
+    """The device's error word, for a launch that is about to start: raises first if an earlier
+    kernel on this device is known to have given up on a wait."""
+    state = _error_word(device)
+    state.raise_if_set(wait=False)
+    return state.word
+
+
+def launched(device) -> None:
+    """To be called after a launch that was given `error_flag(device)`."""
+    _error_word(device).after_launch()
 
 
 def check_async_errors(device=None) -> None:
     """Synchronises and raises if a tensor-core kernel reported a timed-out wait."""
-    for key, flag in list(_error_flags.items()):
-        if device is not None and torch.device(device).index != key:
+    for key, state in list(_error_words.items()):
+        if device is not None and torch.device(device).index not in (None, key):
             continue
-        code = int(flag.item())
-        if code:
-            flag.zero_()
-            raise RuntimeError(f"a tensor-core kernel gave up on a bounded wait (code {code})")
+        state.raise_if_set(wait=True)
 
 
 def linear_supported(a: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -175,6 +278,7 @@ def _linear_raw(a: torch.Tensor, b_t: torch.Tensor) -> torch.Tensor:
         _native.check(_native.lib().tgb_linear_f32(a.data_ptr(), b_t.data_ptr(), out.data_ptr(), M, K, N,
                                                    error_flag(a.device).data_ptr(), _stream(a.device)),
                       "tgb_linear_f32")
+        launched(a.device)
     return out
 
 
@@ -194,6 +298,7 @@ def _linear_dw_raw(a: torch.Tensor, d_out: torch.Tensor) -> torch.Tensor:
         _native.check(lib.tgb_linear_dw_f32(a.data_ptr(), d_out.data_ptr(), dw.data_ptr(), partial.data_ptr(),
                                             partial.numel() * 4, M, K, N, error_flag(a.device).data_ptr(),
                                             _stream(a.device)), "tgb_linear_dw_f32")
+        launched(a.device)
     return dw
 
 
