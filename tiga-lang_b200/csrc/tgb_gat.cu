@@ -39,6 +39,12 @@ namespace {
 
 constexpr int kBlock = 128;
 constexpr int kU = 4;           // gathered rows in flight per lane
+#ifndef TGB_GAT_HEAD_LANES
+#define TGB_GAT_HEAD_LANES 1
+#endif
+#ifndef TGB_GAT_BWD_U
+#define TGB_GAT_BWD_U 1
+#endif
 constexpr int kReduceBlocks = 592;  // 4 CTAs per SM for the parameter-gradient reduction
 
 __device__ __forceinline__ float bf16_round(float v) {
@@ -521,6 +527,169 @@ k_gat_fwd_q(const GatArgs a) {
 }
 
 // ---------------------------------------------------------------------------
+// Backward passes for rows of 8 heads x 32 elements with one lane per HEAD: a row is owned by
+// 8 lanes, lane h keeps the 4 vectors (64 contiguous bytes) of head h.  Everything a head needs
+// then lives in one lane: its logit, softmax weight and exp are evaluated once per (edge, head)
+// instead of once per lane of the head, the dot products <dO, x> and <dO, O> need no shuffles, the
+// per-edge (P, Q) pair is written and read by one lane, and a warp keeps four rows (and four
+// gathered rows per step) in flight.  Partial rows of split rows keep the vector-major layout of
+// the one-vector-per-lane kernels, so the finalize kernels are shared.
+// ---------------------------------------------------------------------------
+constexpr int kHL = 8, kHV = 4;     // lanes per row, vectors per lane
+
+template <typename PtrT, typename IdxT, int U>
+__global__ void __launch_bounds__(kBlock)
+k_gat_bwd_dst_h(const GatArgs a) {
+  const int lane = threadIdx.x & (kHL - 1);          // = head
+  const int64_t gid = ((int64_t)blockIdx.x * kBlock + threadIdx.x) / kHL;
+  if (gid >= a.work.n_seg + (a.work.n_rows - a.work.n_long)) return;
+  const unsigned gmask = 0xffu << ((threadIdx.x & 31) & ~(kHL - 1));
+  int64_t row, beg, end, seg;
+  decode_group<PtrT>(a.work, gid, row, beg, end, seg);
+  const IdxT *idx = static_cast<const IdxT *>(a.work.idx);
+  const uint4 *xs = reinterpret_cast<const uint4 *>(a.x_src);
+  constexpr int H = kHL;
+  const float sd = __ldg(a.s_dst + row * H + lane);
+  const float m = __ldg(a.m + row * H + lane);
+  const float l = __ldg(a.l + row * H + lane);
+  const float inv_l = l > 0.0f ? 1.0f / l : 0.0f;
+  uint4 graw[kHV];
+  float delta = 0.0f;
+#pragma unroll
+  for (int v = 0; v < kHV; ++v) {
+    graw[v] = ldg_u4(a.dout + ((row * kHL + lane) * kHV + v) * 8);
+    float g[8], ov[8];
+    unpack8(graw[v], g);
+    unpack8(ldg_u4(a.o + ((row * kHL + lane) * kHV + v) * 8), ov);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) delta = fmaf(g[i], ov[i], delta);
+  }
+  float dsd = 0.0f;
+  for (int64_t base = beg; base < end; base += kHL) {
+    const int64_t e = base + lane;
+    const int32_t c = e < end ? (int32_t)ld_stream(idx + e) : 0;
+    const int n = (int)(end - base < kHL ? end - base : kHL);
+    for (int k0 = 0; k0 < n; k0 += U) {
+      uint4 raw[U][kHV];
+      float ss[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int k = k0 + u;
+        const int32_t cc = __shfl_sync(gmask, c, k < n ? k : n - 1, kHL);
+        if (k < n) {
+#pragma unroll
+          for (int v = 0; v < kHV; ++v) raw[u][v] = __ldg(xs + ((int64_t)cc * kHL + lane) * kHV + v);
+          ss[u] = __ldg(a.s_src + (int64_t)cc * H + lane);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (k0 + u < n) {
+          float pre;
+          const float logit = logit_of(ss[u], sd, a.slope_bf, pre);
+          const float w = __expf(logit - m) * inv_l;
+          float gv = 0.0f;
+#pragma unroll
+          for (int v = 0; v < kHV; ++v) {
+            float g[8], x[8];
+            unpack8(graw[v], g);
+            unpack8(raw[u][v], x);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) gv = fmaf(g[i], x[i], gv);
+          }
+          const float dpre = w * (gv - delta) * leaky_grad(pre, a.slope_bf);
+          dsd += dpre;
+          const int64_t at = (base + k0 + u) * H + lane;      // 8 lanes: one 32-byte line per edge
+          __stcs(a.P + at, w);
+          __stcs(a.Q + at, dpre);
+        }
+      }
+    }
+  }
+  if (seg >= 0) a.part_h[seg * H + lane] = dsd;
+  else a.d_sdst[row * H + lane] = dsd;
+}
+
+template <int U>
+__global__ void __launch_bounds__(kBlock)
+k_gat_bwd_src_h(const GatArgs a) {
+  const int lane = threadIdx.x & (kHL - 1);          // = head
+  const int64_t gid = ((int64_t)blockIdx.x * kBlock + threadIdx.x) / kHL;
+  if (gid >= a.work.n_seg + (a.work.n_rows - a.work.n_long)) return;
+  const unsigned gmask = 0xffu << ((threadIdx.x & 31) & ~(kHL - 1));
+  int64_t row, beg, end, seg;
+  decode_group<int64_t>(a.work, gid, row, beg, end, seg);
+  const int32_t *idx = static_cast<const int32_t *>(a.work.idx);
+  const uint4 *go = reinterpret_cast<const uint4 *>(a.dout);
+  constexpr int H = kHL;
+  float acc[kHV][8];
+#pragma unroll
+  for (int v = 0; v < kHV; ++v)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[v][i] = 0.0f;
+  float dss = 0.0f;
+  for (int64_t base = beg; base < end; base += kHL) {
+    const int64_t e = base + lane;
+    int32_t c = 0;
+    uint32_t my_eid = 0;
+    if (e < end) {
+      c = ld_stream(idx + e);
+      my_eid = ld_stream(a.work.eid + e);
+    }
+    const int n = (int)(end - base < kHL ? end - base : kHL);
+    for (int k0 = 0; k0 < n; k0 += U) {
+      uint4 raw[U][kHV];
+      float p[U], q[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int k = k0 + u;
+        const int src = k < n ? k : n - 1;
+        const int32_t cc = __shfl_sync(gmask, c, src, kHL);
+        const uint32_t ee = __shfl_sync(gmask, my_eid, src, kHL);
+        if (k < n) {
+#pragma unroll
+          for (int v = 0; v < kHV; ++v) raw[u][v] = __ldg(go + ((int64_t)cc * kHL + lane) * kHV + v);
+          p[u] = __ldg(a.P + (int64_t)ee * H + lane);
+          q[u] = __ldg(a.Q + (int64_t)ee * H + lane);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (k0 + u < n) {
+#pragma unroll
+          for (int v = 0; v < kHV; ++v) {
+            float gv[8];
+            unpack8(raw[u][v], gv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[v][i] = fmaf(p[u], gv[i], acc[v][i]);
+          }
+          dss += q[u];
+        }
+      }
+    }
+  }
+  if (seg >= 0) {
+#pragma unroll
+    for (int v = 0; v < kHV; ++v) {
+      float *pa = a.part_acc + ((seg * kHL + lane) * kHV + v) * 8;
+      *reinterpret_cast<float4 *>(pa) = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+      *reinterpret_cast<float4 *>(pa + 4) = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
+    }
+    a.part_h[seg * H + lane] = dss;
+    return;
+  }
+#pragma unroll
+  for (int v = 0; v < kHV; ++v) {
+    float av[8], o[8];
+    unpack8(ldg_u4(a.a_src + (lane * kHV + v) * 8), av);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = fmaf(dss, av[i], acc[v][i]);
+    *reinterpret_cast<uint4 *>(a.dx_src + ((row * kHL + lane) * kHV + v) * 8) = pack8(o);
+  }
+  a.d_ssrc[row * H + lane] = dss;
+}
+
+// ---------------------------------------------------------------------------
 // backward pass 3: dx_dst rows and the two parameter gradients
 //   dx_dst[r] = d_sdst[r,h] * a_dst ;  partial[b] = sum_{rows of CTA b} d_s[r,h] * x[r]
 // One thread per 8-element vector of the row; CTAs stride over rows.
@@ -761,8 +930,14 @@ int32_t tgb_gat_bwd(const tgb_csr_plan *plan, const void *x_src, const void *x_d
   // pass 1: destination-major
   a.work = work_list(plan->fwd);
   int64_t groups = a.work.n_seg + (a.work.n_rows - a.work.n_long);
+  const bool head_lanes = H == kHL && D == 8 * kHV && TGB_GAT_HEAD_LANES;   // one lane per head (8 x 32 rows)
   if (groups > 0) {
-    if (plan->index_bits == 32) {
+    if (head_lanes) {
+      if (plan->index_bits == 32)
+        k_gat_bwd_dst_h<int32_t, int32_t, TGB_GAT_BWD_U><<<blocks_for(groups, kHL), kBlock, 0, st>>>(a);
+      else
+        k_gat_bwd_dst_h<int64_t, int64_t, TGB_GAT_BWD_U><<<blocks_for(groups, kHL), kBlock, 0, st>>>(a);
+    } else if (plan->index_bits == 32) {
       TGB_DISPATCH_G(shape.G, k_gat_bwd_dst<int32_t, int32_t, GG><<<blocks_for(groups, GG), kBlock, 0, st>>>(a));
     } else {
       TGB_DISPATCH_G(shape.G, k_gat_bwd_dst<int64_t, int64_t, GG><<<blocks_for(groups, GG), kBlock, 0, st>>>(a));
@@ -777,7 +952,11 @@ int32_t tgb_gat_bwd(const tgb_csr_plan *plan, const void *x_src, const void *x_d
   a.work = work_list(plan->bwd);
   groups = a.work.n_seg + (a.work.n_rows - a.work.n_long);
   if (groups > 0) {
-    TGB_DISPATCH_G(shape.G, k_gat_bwd_src<GG><<<blocks_for(groups, GG), kBlock, 0, st>>>(a));
+    if (head_lanes) {
+      k_gat_bwd_src_h<TGB_GAT_BWD_U><<<blocks_for(groups, kHL), kBlock, 0, st>>>(a);
+    } else {
+      TGB_DISPATCH_G(shape.G, k_gat_bwd_src<GG><<<blocks_for(groups, GG), kBlock, 0, st>>>(a));
+    }
     TGB_LAUNCHED();
     if (a.work.n_long > 0) {
       TGB_DISPATCH_G(shape.G, k_gat_bwd_src_finalize<GG><<<(unsigned)a.work.n_long, 32, 0, st>>>(a));
