@@ -231,7 +231,7 @@ def recorded_dram_traffic(workload_key):
     dram__bytes_write.sum) of this workload, or None.  A capture is used only while the kernel
     source it was taken from is the one that runs now."""
     try:
-        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as handle:
+        with open(os.path.join(ROOT, "baseline", "dram_traffic.json")) as handle:
             table = json.load(handle)
     except Exception:
         return None
