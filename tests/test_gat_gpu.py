@@ -120,5 +120,36 @@ def test_unsupported_shapes_raise():
     a = torch.randn(3, 8, device="cuda").to(torch.bfloat16)
     with pytest.raises(NotImplementedError):
         GAT()(graph=g, ndata={"x": x}, a_src=a, a_dst=a)
-    with pytest.raises(NotImplementedError):
-        GAT()(graph=g, ndata={"x": x.float()}, a_src=a.float(), a_dst=a.float())
+    with pytest.raises(NotImplementedError):     # mixed precisions are refused, not converted silently
+        GAT()(graph=g, ndata={"x": x.float()}, a_src=a, a_dst=a)
+    out = GAT()(graph=g, ndata={"x": x.float()}, a_src=a.float(), a_dst=a.float())   # float32: any head count
+    assert out.dtype == torch.float32 and out.shape == x.shape
+
+
+def test_float32_inputs_run_on_the_stable_weighted_kernels(oracle):
+    """float32 features (the reference's nn-attention precision): same program, lowered onto the
+    field-score softmax kernels; checked against the float64-free CPU oracle of that reducer."""
+    row_ptr, col = syn.rmat_csr(9, 8, seed=12, symmetrize=False)
+    n, E, H, D = row_ptr.numel() - 1, col.numel(), 4, 16
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn(n, H, D, generator=gen)
+    a_src, a_dst = torch.randn(H, D, generator=gen) * 0.3, torch.randn(H, D, generator=gen) * 0.3
+    dy = torch.randn(n, H, D, generator=gen)
+    g = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=n)
+    xg, sg, dg = x.cuda().requires_grad_(), a_src.cuda().requires_grad_(), a_dst.cuda().requires_grad_()
+    kernel = GAT()
+    out = kernel(graph=g, ndata={"x": xg}, a_src=sg, a_dst=dg)
+    assert out.dtype == torch.float32
+    destination = torch.repeat_interleave(torch.arange(n), row_ptr.diff())
+    pre = (x * a_src).sum(-1)[col] + (x * a_dst).sum(-1)[destination]
+    score = torch.maximum(pre, 0.2 * pre)
+    ref, _, _ = oracle.online_softmax_fwd(row_ptr.numpy(), score.numpy(), x.numpy()[col.numpy()])
+    np.testing.assert_allclose(out.detach().cpu().numpy(), ref, rtol=1e-4, atol=1e-5)
+    # gradients against Torch autograd of the eager evaluator (float32 on the CPU)
+    xc, sc, dc = x.clone().requires_grad_(), a_src.clone().requires_grad_(), a_dst.clone().requires_grad_()
+    cpu_graph = tg.Graph.from_csr(row_ptr, col, num_src=n)
+    eager = GAT().reference(graph=cpu_graph, src={"x": xc}, dst={"x": xc}, a_src=sc, a_dst=dc)
+    want = torch.autograd.grad(eager, (xc, sc, dc), dy)
+    got = torch.autograd.grad(out, (xg, sg, dg), dy.cuda())
+    for a, b in zip(got, want):
+        torch.testing.assert_close(a.cpu(), b, rtol=2e-3, atol=2e-4)

@@ -94,7 +94,33 @@ class GATFunction(torch.autograd.Function):
 def gat_attention(graph, x_src, x_dst, a_src, a_dst, slope: float):
     if not x_src.is_cuda:
         raise RuntimeError("edge attention runs on CUDA tensors only (no CPU fallback)")
+    if x_src.dtype == torch.float32:
+        return _gat_attention_float32(graph, x_src, x_dst, a_src, a_dst, slope)
     return GATFunction.apply(x_src, x_dst, a_src, a_dst, graph, slope)
+
+
+def _gat_attention_float32(graph, x_src, x_dst, a_src, a_dst, slope: float):
+    """float32 edge attention (the precision of the reference's nn-attention kernel,
+    python/tiga/compiler/edge_nn_attention.py:127-338).  The fused bf16 kernels do not apply; the
+    program is lowered onto the stable-weighted softmax kernels instead: the per-node halves of the
+    logit and the per-edge score [E, H] are assembled with Torch element-wise / gather ops (a
+    per-edge scalar per head, never an [E, H, D] temporary), and the gather-heavy part -- softmax
+    over each destination row and the weighted sum of source rows, forward and backward -- runs in
+    tgb_softmax_field_fwd / _bwd.  Autograd carries the score's cotangent back to x and a; the
+    per-source accumulation there is Torch's index_add (atomic adds)."""
+    for name, t in (("dst feature", x_dst), ("a_src", a_src), ("a_dst", a_dst)):
+        if t.dtype != torch.float32:
+            raise NotImplementedError(f"edge attention inputs must share one dtype; {name} is {t.dtype}")
+    if x_src.ndim != 3 or x_dst.shape[1:] != x_src.shape[1:] or a_src.shape != x_src.shape[1:] \
+            or a_dst.shape != x_src.shape[1:]:
+        raise NotImplementedError("edge attention expects x [N, H, D] and a_src, a_dst [H, D]")
+    row_ptr, col_idx = graph.resolve_csr()
+    destination = graph.destination_index(row_ptr).long()
+    s_src = (x_src * a_src).sum(dim=-1)                     # [num_src, H]
+    s_dst = (x_dst * a_dst).sum(dim=-1)                     # [num_dst, H]
+    pre = s_src.index_select(0, col_idx.long()) + s_dst.index_select(0, destination)
+    score = torch.maximum(pre, pre * slope)
+    return FieldSoftmaxFunction.apply(score, x_src, graph)
 
 
 class FieldSoftmaxFunction(torch.autograd.Function):
