@@ -281,3 +281,51 @@ def test_b200_native_codegen_provider_is_registered():
         codegen.get_provider("triton")
     with pytest.raises(ValueError):
         codegen.register_provider("b200-native", codegen.provider_factory)
+
+
+def test_gfg_reader_and_writer_match_the_reference_files(tmp_path):
+    """tests/golden/gfg_case/ was written by the unmodified reference's tg.save: this package must
+    read it, report what the reference's tg.load reports, and write the same bytes."""
+    import filecmp
+    import json
+
+    case = os.path.join(ROOT, "tests", "golden", "gfg_case")
+    expected = json.load(open(os.path.join(case, "expected.json")))
+    row_ptr = [0, 2, 2, 5, 6, 6, 9]
+    col_idx = [0, 4, 1, 2, 3, 3, 0, 2, 4]
+    for name, dtype in (("plain_i32.gfg", torch.int32), ("fields_i64.gfg", torch.int64)):
+        graph = tg.load(os.path.join(case, name))
+        want = expected[name]
+        assert (graph.schema.realization, graph.schema.origin) == (want["realization"], want["origin"])
+        assert (graph.num_src, graph.num_dst, graph.num_edges) == (want["num_src"], want["num_dst"], want["num_edges"])
+        assert [list(part) for part in graph.paged_rows(2, 5)] == want["paged_rows_2_5"]
+        rows, cols, first = graph.paged_page(3, 6)
+        assert [list(rows), list(cols), first] == want["paged_page_3_6"]
+        assert "backing=nvme:" in graph.explain() and graph.schema.index_dtype == dtype
+        loaded_rows, loaded_cols = graph.resolve_csr()
+        assert loaded_rows.tolist() == row_ptr and loaded_cols.tolist() == col_idx and loaded_rows.dtype == dtype
+    stored = tg.load(os.path.join(case, "fields_i64.gfg"))
+    fields = {role: stored.fields(role) for role in ("src", "dst", "edge")}
+    assert fields["src"]["x"].shape == (5, 3) and fields["src"]["x"][2].tolist() == [1.0, 2.0, 3.0]
+    assert fields["edge"]["weight"].tolist() == [1.0 + 0.125 * e for e in range(9)]
+    # writer: same files, byte for byte (manifest text included)
+    plain = tg.Graph.from_csr(torch.tensor(row_ptr, dtype=torch.int32), torch.tensor(col_idx, dtype=torch.int32),
+                              num_src=5, validate="full")
+    tg.save(plain, tmp_path / "plain_i32.gfg")
+    wide = tg.Graph.from_csr(torch.tensor(row_ptr), torch.tensor(col_idx), num_src=5)
+    tg.save(wide, tmp_path / "fields_i64.gfg", fields=fields)
+    for name in ("plain_i32.gfg", "fields_i64.gfg"):
+        listing = filecmp.dircmp(os.path.join(case, name), tmp_path / name)
+        assert not listing.left_only and not listing.right_only and not listing.diff_files, listing.report()
+        sub = filecmp.dircmp(os.path.join(case, name, "fields"), tmp_path / name / "fields") if name.startswith("fields") else None
+        assert sub is None or (not sub.diff_files and not sub.left_only and not sub.right_only)
+    # a paged graph is copied without materialising it; overwriting and corrupt files are refused
+    tg.save(tg.load(tmp_path / "plain_i32.gfg"), tmp_path / "copy.gfg")
+    assert tg.load(tmp_path / "copy.gfg").paged_rows(2, 5) == tg.load(tmp_path / "plain_i32.gfg").paged_rows(2, 5)
+    with pytest.raises(FileExistsError):
+        tg.save(plain, tmp_path / "copy.gfg")
+    (tmp_path / "copy.gfg" / "col_idx.bin").write_bytes(b"")
+    with pytest.raises(ValueError, match="col_idx size"):
+        tg.load(tmp_path / "copy.gfg")
+    with pytest.raises(ValueError):
+        tg.save(plain, tmp_path / "again.gfg", overwrite=True)

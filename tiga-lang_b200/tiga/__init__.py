@@ -11,6 +11,7 @@ from .distributed import ByDestination, DeviceMesh, GraphPlacement, HaloMap, der
 from .graph import Graph, GraphSchema
 from .kernel import AnalysisFinding, CompiledVariant, Kernel
 from .message_passing import MessagePassing
+from .storage import load, save
 from .reducer import (MaxReducer, MeanReducer, OnlineSoftmaxItem, OnlineSoftmaxReducer, ProductReducer, Reducer,
                       ReducerCall, SumReducer, max, mean, online_softmax, prod, sum)
 
@@ -20,5 +21,5 @@ __all__ = [
     "AnalysisFinding", "ByDestination", "CompiledVariant", "DeviceMesh", "Graph", "GraphPlacement",
     "GraphSchema", "HaloMap", "Kernel", "MaxReducer", "MeanReducer", "MessagePassing", "OnlineSoftmaxItem",
     "OnlineSoftmaxReducer", "ProductReducer", "Reducer", "ReducerCall", "SumReducer", "derive_halo_map",
-    "codegen", "math", "max", "mean", "online_softmax", "prod", "sum",
+    "codegen", "load", "math", "max", "mean", "online_softmax", "prod", "save", "sum",
 ]

@@ -14,6 +14,7 @@ relation) is built lazily and cached on the graph.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Literal
 
@@ -63,6 +64,8 @@ class Graph:
         self._transpose_cache = None
         self._edge_map = None   # set for sub-relations whose weights live in a larger edge list
         self._shard = None      # (first_row, num_nodes) when the tensors hold one rank's block of rows only
+        self._paged_store = None   # PagedCSRStore of a graph opened from a .gfg directory
+        self.page_rows = int(os.environ.get("TIGA_PAGE_ROWS", 1 << 20))   # destination rows per page
 
     # ------------------------------------------------------------ properties
     @property
@@ -164,6 +167,51 @@ class Graph:
         graph = cls(schema, row_ptr=row_ptr, col_idx=col_idx)
         graph._shard = (int(first_row), int(num_nodes))
         return graph
+
+    @classmethod
+    def open(cls, path, *, device="cpu") -> "Graph":
+        """Open a persistent ``.gfg`` graph without loading its CSR arrays
+        (python/tiga/graph/core.py:413-426 of the reference).  The topology stays on disk
+        (``schema.realization == "paged_csr"``); MessagePassing calls run page by page over blocks
+        of ``page_rows`` destination rows, ``resolve_csr()`` materialises it on the graph's device."""
+        from .storage import PagedCSRStore
+
+        store = PagedCSRStore(path)
+        schema = GraphSchema(num_src=store.num_src, num_dst=store.num_dst, origin="persistent", lifecycle="static",
+                             realization="paged_csr", index_dtype=store.index_dtype,
+                             sorted_by_dst=store.sorted_by_dst)
+        graph = cls(schema, device=device)
+        graph._paged_store = store
+        return graph
+
+    @property
+    def num_edges(self) -> int | None:
+        if self._paged_store is not None:
+            return self._paged_store.num_edges
+        return None if self._col_idx is None else int(self._col_idx.numel())
+
+    def paged_rows(self, begin: int, end: int):
+        """(row_ptr from 0, col_idx) of destination rows [begin, end) of a persistent graph."""
+        if self._paged_store is None:
+            raise TypeError("paged_rows requires a graph opened from a .gfg directory")
+        return self._paged_store.read_rows(begin, end)
+
+    def paged_page(self, begin: int, end: int):
+        """paged_rows plus the global position of the page's first edge."""
+        if self._paged_store is None:
+            raise TypeError("paged_page requires a graph opened from a .gfg directory")
+        return self._paged_store.read_page(begin, end)
+
+    def fields(self, role: str):
+        """Node / edge fields stored inside the .gfg, loaded onto the graph's device."""
+        if self._paged_store is None:
+            raise TypeError("fields() requires a graph opened from a .gfg directory")
+        return self._paged_store.fields(role, self._device)
+
+    def explain(self) -> str:
+        backing = f" backing=nvme:{self._paged_store.path}" if self._paged_store is not None else ""
+        return (f"Graph num_src={self.num_src} num_dst={self.num_dst} origin={self._schema.origin} "
+                f"realization={self._schema.realization} device={self._device}{backing}")
 
     @classmethod
     def from_coo(cls, src, dst, *, num_src: int | None = None, num_dst: int | None = None) -> "Graph":
@@ -302,6 +350,9 @@ class Graph:
             raise RuntimeError("a Graph.from_csr_shard block is executable only as a .halo(mesh) snapshot "
                                "under a DistributedRuntime")
         if self._row_ptr is not None:
+            return self._row_ptr, self._col_idx
+        if self._paged_store is not None:      # a persistent graph: load the whole topology onto the device
+            self._row_ptr, self._col_idx = self._paged_store.materialize(device=self._device)
             return self._row_ptr, self._col_idx
         dtype = self._schema.index_dtype
         device = self._device

@@ -171,12 +171,46 @@ class MessagePassing(Kernel):
             raise TypeError("graph must be a tiga.Graph")
         src, dst = _resolve_node_fields(graph, src, dst, ndata)
         edge = {} if edge is None else edge
+        if graph.schema.realization == "paged_csr" and graph._row_ptr is None:
+            return self._execute_paged(graph, src, dst, edge, params)
         aggregate = self._warm(graph, src, dst, edge, params) if self._launches else _MISS
         if aggregate is _MISS:
             aggregate = self._cold(graph, src, dst, edge, params)
         if type(self).node is MessagePassing.node:
             return aggregate
         return cap.call_region(self.node, (SimpleNamespace(**dst), aggregate), params)
+
+    def _execute_paged(self, graph, src, dst, edge, params):
+        """A graph whose topology lives in a .gfg directory: blocks of `graph.page_rows` destination
+        rows are read from the memory-mapped files, moved to the device and reduced one after the
+        other by the same kernels as a resident graph (execute_paged_message_passing,
+        python/tiga/message_passing/paged.py:434-583 of the reference, which runs its host evaluator
+        per page).  Source fields are whole tensors on the device, destination and edge fields are
+        sliced per page; every page's plan is dropped before the next is built, so device memory
+        holds one page of topology at a time.  Autograd works through the pages."""
+        store = graph._paged_store
+        _validate_fields("src", src, graph.schema.num_src, graph.device)
+        _validate_fields("dst", dst, graph.schema.num_dst, graph.device)
+        _validate_fields("edge", edge, store.num_edges, graph.device)
+        if graph.device.type != "cuda":
+            raise NotImplementedError("this build executes MessagePassing on CUDA tensors only; open the graph "
+                                      "with tg.load(path, device='cuda')")
+        pieces = []
+        rows_per_page = max(int(graph.page_rows), 1)
+        for begin in range(0, graph.schema.num_dst, rows_per_page):
+            end = min(graph.schema.num_dst, begin + rows_per_page)
+            row_ptr, col_idx, first = store.page_tensors(begin, end, graph.device)
+            page = Graph.from_csr(row_ptr, col_idx, num_src=graph.schema.num_src)
+            page_dst = {name: value[begin:end] for name, value in dst.items()}
+            page_edge = {name: value[first:first + col_idx.numel()] for name, value in edge.items()}
+            _, tensors, _, runner = self._specialise(page, src, page_dst, page_edge, params)
+            aggregate = runner(*tensors)
+            if type(self).node is not MessagePassing.node:
+                aggregate = cap.call_region(self.node, (SimpleNamespace(**page_dst), aggregate), params)
+            pieces.append(aggregate)
+        if not pieces:
+            raise NotImplementedError("a persistent graph without destination rows has nothing to execute")
+        return torch.cat(pieces, dim=0)
 
     def _warm(self, graph, src, dst, edge, params):
         launches = self._launches
