@@ -6,7 +6,9 @@ Public names follow python/tiga/__init__.py:45-105 of the reference for the
 part of the API that lies on this path: ``MessagePassing``, ``Graph``, the
 reducers, ``tg.math``, and the distributed placement objects.
 """
-from . import codegen, math
+from . import codegen, control, math
+from .control import repeat
+from .program import GraphProgram, ProgramValue, program
 from .distributed import ByDestination, DeviceMesh, GraphPlacement, HaloMap, derive_halo_map
 from .graph import Graph, GraphSchema
 from .kernel import AnalysisFinding, CompiledVariant, Kernel
@@ -21,5 +23,5 @@ __all__ = [
     "AnalysisFinding", "ByDestination", "CompiledVariant", "DeviceMesh", "Graph", "GraphPlacement",
     "GraphSchema", "HaloMap", "Kernel", "MaxReducer", "MeanReducer", "MessagePassing", "OnlineSoftmaxItem",
     "OnlineSoftmaxReducer", "ProductReducer", "Reducer", "ReducerCall", "SumReducer", "derive_halo_map",
-    "codegen", "load", "math", "max", "mean", "online_softmax", "prod", "save", "sum",
+    "GraphProgram", "ProgramValue", "codegen", "control", "load", "program", "repeat", "math", "max", "mean", "online_softmax", "prod", "save", "sum",
 ]

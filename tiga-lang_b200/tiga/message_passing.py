@@ -34,6 +34,12 @@ from .reducer import (MaxReducer, MeanReducer, OnlineSoftmaxItem, OnlineSoftmaxR
 PROVIDER = "b200-native"
 
 
+def _active_program():
+    from .program import active_program
+
+    return active_program()
+
+
 def _resolve_node_fields(graph, src, dst, ndata):
     if ndata is not None:
         if src is not None or dst is not None:
@@ -171,6 +177,9 @@ class MessagePassing(Kernel):
             raise TypeError("graph must be a tiga.Graph")
         src, dst = _resolve_node_fields(graph, src, dst, ndata)
         edge = {} if edge is None else edge
+        recording = _active_program()
+        if recording is not None:          # inside @tg.program: the call becomes a lazy application
+            return recording.apply(self, graph=graph, src=src, dst=dst, edge=edge, **params)
         if graph.schema.realization == "paged_csr" and graph._row_ptr is None:
             return self._execute_paged(graph, src, dst, edge, params)
         aggregate = self._warm(graph, src, dst, edge, params) if self._launches else _MISS
