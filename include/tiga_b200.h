@@ -395,6 +395,116 @@ TGB_API int32_t tgb_linear_dw_f32(const void *a, const void *dout, void *dw,
                                   void *error_flag, uint64_t stream);
 TGB_API int32_t tgb_linear_dw_partials(int64_t M, int32_t *count);
 
+/* ------------------------------------------------------------------------
+ * Dynamic relations: radius and k-nearest-neighbour builders, and the fused
+ * radius consumer that never materialises the relation.
+ *
+ * Replace, for contiguous float32 positions on the device, the Torch tensor
+ * programs of Graph.radius / Graph.knn (python/tiga/interop/torch/graph.py:
+ * 391-534 constructors, :851-1003 resolve_csr, :1023-1125 cell-list
+ * candidates, :1127-1176 pair selection, :1203-1210 minimum image,
+ * :1403-1444 implicit edge fields), the hash-grid directory of
+ * python/tiga/interop/torch/radius_grid.py and the generated
+ * radius-distance-sum kernel (`gf-kernel-to-ttir-generated-radius-distance-sum`,
+ * tests/python/test_reference.py:533-560).
+ *
+ * Results are bit-identical to the reference's CPU evaluation: same edge order
+ * (destination ascending; inside a row the 3^D neighbour cells in meshgrid
+ * order, first axis slowest, and the points of a cell in ascending index),
+ * same float32 operation order (displacement = source - destination,
+ * distance = sqrt(fma(z, z, fma(y, y, x * x))), lattice products as fused
+ * multiply-add chains in increasing k).
+ * ------------------------------------------------------------------------ */
+
+/* Geometry of the broad phase.  Open boundary: cell = floor(p / cell_size).
+ * Periodic: fractional = p @ inverse, wrapped to [0, 1), cell = min(floor(
+ * fractional * extents), extents - 1); `lattice`, `inverse` row-major
+ * [dims, dims]; `extents` = cells per axis, computed by the caller as
+ * floor(1 / (cell_size * column norms of inverse)), at least 1
+ * (graph.py:1044-1054). */
+typedef struct tgb_cell_space {
+  int32_t dims;      /* 1, 2 or 3 */
+  int32_t periodic;  /* 0 open boundary, 1 lattice */
+  float cell_size;   /* edge of a cell = the scalar cutoff */
+  float lattice[9];
+  float inverse[9];
+  int32_t extents[3];
+} tgb_cell_space;
+
+/* Bytes of the cell directory of `n` points (`persistent_bytes`, alive while
+ * the directory is used) and of the scratch of its construction. */
+TGB_API int32_t tgb_cell_directory_sizes(int64_t n, int32_t dims,
+                                         uint64_t *persistent_bytes,
+                                         uint64_t *temp_bytes);
+
+/* Sorts the points into modular hash buckets of their cells (stable: ascending
+ * index inside a bucket) and writes the directory into `persistent`.
+ * positions: float32 [n, dims], row-major.  n < 2^31.  No synchronisation. */
+TGB_API int32_t tgb_cell_directory_build(const void *positions, int64_t n,
+                                         const tgb_cell_space *space,
+                                         void *persistent, uint64_t persistent_bytes,
+                                         void *temp, uint64_t temp_bytes,
+                                         uint64_t stream);
+
+/* row_ptr[0..n] (int64) of the radius relation and, in `candidate_pairs`
+ * (one uint64 in device memory, may be null), the number of broad-phase
+ * candidates (build_info["candidate_pairs"] of the reference).  An edge is a
+ * pair with distance <= cutoff, minus i == j when exclude_self.
+ * `temp` needs tgb_cell_directory_sizes' temp_bytes. */
+TGB_API int32_t tgb_radius_row_ptr(const void *positions, int64_t n,
+                                   const tgb_cell_space *space, const void *directory,
+                                   float cutoff, int32_t exclude_self, void *row_ptr,
+                                   void *candidate_pairs, void *temp, uint64_t temp_bytes,
+                                   uint64_t stream);
+
+/* col[E] (int64) in the reference's order and, when not null, distance[E] and
+ * displacement[E, dims] (float32): the implicit edge fields. */
+TGB_API int32_t tgb_radius_fill(const void *positions, int64_t n,
+                                const tgb_cell_space *space, const void *directory,
+                                float cutoff, int32_t exclude_self, const void *row_ptr,
+                                void *col, void *distance, void *displacement,
+                                uint64_t stream);
+
+/* Weight of a pair in the fused consumer. */
+enum { TGB_PAIR_WEIGHT_ONE = 0, TGB_PAIR_WEIGHT_DISTANCE = 1 };
+
+/* out[i, :] = sum over the radius neighbours j of i, in the relation's edge
+ * order, of weight(i, j) * x[j, :]; x, out float32 [n, F], F <= 128.  The sum
+ * is the sequential float32 fold of the CSR kernels, so it equals
+ * tgb_csr_reduce_fwd over the materialised relation bit for bit. */
+TGB_API int32_t tgb_radius_wsum_fwd(const void *positions, int64_t n,
+                                    const tgb_cell_space *space, const void *directory,
+                                    float cutoff, int32_t exclude_self, int32_t weight,
+                                    const void *x, int64_t F, void *out, uint64_t stream);
+
+/* Position cotangent of the distance-weighted sum:
+ * dpos[i, :] = - sum_j (dy[i,:].x[j,:] + dy[j,:].x[i,:]) * displacement(i, j) / distance(i, j),
+ * pairs at distance zero contributing nothing (the subgradient Torch's
+ * vector_norm uses).  Requires the symmetric relation of a scalar cutoff. */
+TGB_API int32_t tgb_radius_wsum_bwd_pos(const void *positions, int64_t n,
+                                        const tgb_cell_space *space, const void *directory,
+                                        float cutoff, int32_t exclude_self, const void *x,
+                                        const void *dy, int64_t F, void *dpos,
+                                        uint64_t stream);
+
+/* Exact k nearest candidates of every query, ascending by (squared distance,
+ * candidate index): col[nq, k] int64 and, when not null, dist_sq[nq, k].
+ * exclude_self drops candidate i of query i (self search).  dims <= 64,
+ * 1 <= k <= 128, k <= nc - exclude_self. */
+TGB_API int32_t tgb_knn(const void *queries, int64_t nq, const void *candidates,
+                        int64_t nc, int32_t dims, int32_t k, int32_t exclude_self,
+                        void *col, void *dist_sq, uint64_t stream);
+
+/* Implicit edge fields of a stored relation: displacement[e, :] =
+ * src_positions[col[e], :] - dst_positions[row of e, :] (minimum image when
+ * `space` is periodic; only dims, periodic, lattice and inverse are read, dims
+ * <= 8 for an open boundary) and distance[e]; either output may be null.
+ * row_ptr, col int64. */
+TGB_API int32_t tgb_edge_geometry(const void *dst_positions, const void *src_positions,
+                                  const tgb_cell_space *space, const void *row_ptr,
+                                  const void *col, int64_t num_dst, int64_t num_edges,
+                                  void *displacement, void *distance, uint64_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -29,7 +29,8 @@ def build(force: bool = False) -> str:
     """Compile the C oracle (and the reference runtime when it is present)."""
     if force or not os.path.exists(_LIB_PATH) or (
             os.path.getmtime(_LIB_PATH)
-            < os.path.getmtime(os.path.join(_HERE, "tiga_oracle.c"))):
+            < max(os.path.getmtime(os.path.join(_HERE, name))
+                  for name in ("tiga_oracle.c", "tiga_geometry_oracle.c"))):
         subprocess.run(["make", "-C", _HERE], check=True,
                        stdout=subprocess.DEVNULL)
     return _LIB_PATH
@@ -43,6 +44,8 @@ def lib():
         _lib.orc_destination_owner.restype = ctypes.c_int64
         _lib.orc_derive_ghosts.restype = ctypes.c_int64
         _lib.orc_num_threads.restype = ctypes.c_int
+        _lib.orc_radius_build.restype = ctypes.c_int64
+        _lib.orc_knn_build.restype = ctypes.c_int32
     return _lib
 
 
@@ -415,3 +418,64 @@ def local_csr(row_ptr, col_idx, num_entities, world, rank, ghost_ids):
                         local_ptr.ctypes.data_as(_i64p),
                         local_col.ctypes.data_as(_i64p))
     return local_ptr, local_col
+
+
+# ------------------------------------------------------- dynamic relations
+def _lattice_arguments(lattice, inverse, dims):
+    if lattice is None:
+        return None, None, None, None
+    lattice, pl = _f32(np.asarray(lattice, np.float32).reshape(dims, dims))
+    inverse, pi = _f32(np.asarray(inverse, np.float32).reshape(dims, dims))
+    return lattice, pl, inverse, pi
+
+
+def radius_build(positions, cutoff, *, exclude_self=True, lattice=None, inverse=None, extents=None,
+                 use_cells=True):
+    """Graph.radius -> (row_ptr, col, distance, displacement, candidate_pairs).  `lattice`/`inverse`
+    are the [D, D] periodic lattice and its inverse, `extents` the periodic cells per axis."""
+    positions, pp = _f32(np.asarray(positions, np.float32))
+    n, dims = positions.shape
+    cutoff, pc = _f32(np.atleast_1d(np.asarray(cutoff, np.float32)))
+    lattice, pl, inverse, pi = _lattice_arguments(lattice, inverse, dims)
+    ext, pe = _i64(np.zeros(dims, np.int64) if extents is None else extents)
+    row_ptr = np.zeros(n + 1, np.int64)
+    pairs = ctypes.c_int64()
+    args = (pp, _c64(n), ctypes.c_int32(dims), pc, _c64(cutoff.size), ctypes.c_int32(bool(exclude_self)),
+            pl, pi, pe, ctypes.c_int32(bool(use_cells)), row_ptr.ctypes.data_as(_i64p))
+    edges = lib().orc_radius_build(*args, None, None, None, ctypes.byref(pairs))
+    if edges < 0:
+        raise ValueError("orc_radius_build rejected its arguments")
+    col = np.zeros(edges, np.int64)
+    distance = np.zeros(edges, np.float32)
+    displacement = np.zeros((edges, dims), np.float32)
+    lib().orc_radius_build(*args, col.ctypes.data_as(_i64p), distance.ctypes.data_as(_f32p),
+                           displacement.ctypes.data_as(_f32p), ctypes.byref(pairs))
+    return row_ptr, col, distance, displacement, int(pairs.value)
+
+
+def knn_build(queries, candidates, k, *, exclude_self):
+    """Graph.knn -> col [nq, k], ascending by (squared distance, candidate index)."""
+    queries, pq = _f32(np.asarray(queries, np.float32))
+    candidates, pc = _f32(np.asarray(candidates, np.float32))
+    col = np.zeros((queries.shape[0], int(k)), np.int64)
+    status = lib().orc_knn_build(pq, _c64(queries.shape[0]), pc, _c64(candidates.shape[0]),
+                                 ctypes.c_int32(queries.shape[1]), ctypes.c_int32(int(k)),
+                                 ctypes.c_int32(bool(exclude_self)), col.ctypes.data_as(_i64p))
+    if status != 0:
+        raise ValueError("k out of range for the candidate set")
+    return col
+
+
+def edge_geometry(dst_positions, src_positions, destination, col, *, lattice=None, inverse=None):
+    """Graph.implicit_edge_fields -> (displacement [E, D], distance [E])."""
+    dst_positions, pd = _f32(np.asarray(dst_positions, np.float32))
+    src_positions, ps = _f32(np.asarray(src_positions, np.float32))
+    dims = dst_positions.shape[1]
+    destination, pdst = _i64(destination)
+    col, pcol = _i64(col)
+    lattice, pl, inverse, pi = _lattice_arguments(lattice, inverse, dims)
+    displacement = np.zeros((col.size, dims), np.float32)
+    distance = np.zeros(col.size, np.float32)
+    lib().orc_edge_geometry(pd, ps, ctypes.c_int32(dims), pdst, pcol, _c64(col.size), pl, pi,
+                            displacement.ctypes.data_as(_f32p), distance.ctypes.data_as(_f32p))
+    return displacement, distance

@@ -55,6 +55,9 @@ class Graph:
         self._dense_boundary = dense_boundary
         self._device = torch.device(device) if device is not None else (
             row_ptr.device if row_ptr is not None else torch.device("cpu"))
+        if self._device.type == "cuda" and self._device.index is None and torch.cuda.is_available():
+            # tensors report "cuda:<index>"
+            self._device = torch.device("cuda", torch.cuda.current_device())
         self._placement = placement
         self._cu_seqlens = cu_seqlens  # packed block-diagonal relation kept implicit
         self._causal = causal
@@ -65,6 +68,7 @@ class Graph:
         self._edge_map = None   # set for sub-relations whose weights live in a larger edge list
         self._shard = None      # (first_row, num_nodes) when the tensors hold one rank's block of rows only
         self._paged_store = None   # PagedCSRStore of a graph opened from a .gfg directory
+        self._geometry = None      # GeometricRelation of a Graph.radius / Graph.knn relation
         self.page_rows = int(os.environ.get("TIGA_PAGE_ROWS", 1 << 20))   # destination rows per page
 
     # ------------------------------------------------------------ properties
@@ -184,10 +188,62 @@ class Graph:
         graph._paged_store = store
         return graph
 
+    # ------------------------------------------------------ dynamic relations
+    @classmethod
+    def radius(cls, positions, cutoff, *, exclude_self: bool = True, fields=None, metric=None, select=None,
+               periodic=None) -> "Graph":
+        """Rebuildable radius relation over ``positions`` [N, D]: j is a neighbour of i when the
+        (minimum-image) distance is at most ``cutoff`` (a scalar, one value per destination or an
+        [N, N] matrix).  ``metric(src, dst, edge)`` replaces the Euclidean distance,
+        ``select(src, dst, edge)`` is an additional boolean filter; the endpoint namespaces hold
+        ``position`` plus ``fields``, the edge namespace ``displacement``, ``distance``, ``cutoff``
+        (Graph.radius of the reference, python/tiga/interop/torch/graph.py:391-478)."""
+        from .dynamic_graph import GeometricRelation, check_radius_arguments
+
+        periodic, fields = check_radius_arguments(positions, cutoff, fields, metric, select, periodic)
+        count = positions.shape[0]
+        schema = GraphSchema(num_src=count, num_dst=count, origin="geometric_radius", lifecycle="dynamic",
+                             realization="procedural_radius", index_dtype=torch.int64, sorted_by_dst=True)
+        graph = cls(schema, device=positions.device)
+        graph._geometry = GeometricRelation("radius", positions, cutoff=cutoff, periodic=periodic,
+                                            exclude_self=exclude_self, fields=fields, metric=metric, select=select)
+        return graph
+
+    @classmethod
+    def knn(cls, positions, k: int, *, candidates=None, exclude_self: bool | None = None) -> "Graph":
+        """Exact k-nearest-neighbour relation: row i holds the k candidates nearest to query i,
+        ascending by (distance, candidate index); ``candidates=None`` searches the queries themselves
+        and then skips i (Graph.knn of the reference, graph.py:481-534)."""
+        from .dynamic_graph import GeometricRelation, check_knn_arguments
+
+        sources, exclude_self = check_knn_arguments(positions, k, candidates, exclude_self)
+        schema = GraphSchema(num_src=(positions if sources is None else sources).shape[0],
+                             num_dst=positions.shape[0], origin="geometric_knn", lifecycle="dynamic",
+                             realization="procedural_knn", index_dtype=torch.int64, sorted_by_dst=True)
+        graph = cls(schema, device=positions.device)
+        graph._geometry = GeometricRelation("knn", positions, k=k, source_positions=sources,
+                                            exclude_self=exclude_self)
+        return graph
+
+    @property
+    def build_info(self) -> dict:
+        """How the last resolve of a dynamic relation ran: builder, candidate_pairs, accepted_edges,
+        materialized, cache_hit."""
+        if self._geometry is None or self._geometry.build_info is None:
+            raise RuntimeError("dynamic graph has not been resolved yet")
+        return dict(self._geometry.build_info)
+
+    def dynamic_signature(self):
+        """Hashable description of a dynamic relation's search (None for stored relations): two graphs
+        with equal signatures differ only in the tensors they were handed."""
+        return None if self._geometry is None else (self._schema.specialization_key(), self._geometry.signature())
+
     @property
     def num_edges(self) -> int | None:
         if self._paged_store is not None:
             return self._paged_store.num_edges
+        if self._geometry is not None:          # a dynamic relation has no edge count of its own
+            return None
         return None if self._col_idx is None else int(self._col_idx.numel())
 
     def paged_rows(self, begin: int, end: int):
@@ -210,8 +266,10 @@ class Graph:
 
     def explain(self) -> str:
         backing = f" backing=nvme:{self._paged_store.path}" if self._paged_store is not None else ""
+        dynamic = "" if self._geometry is None else self._geometry.describe()
         return (f"Graph num_src={self.num_src} num_dst={self.num_dst} origin={self._schema.origin} "
-                f"realization={self._schema.realization} device={self._device}{backing}")
+                f"lifecycle={self._schema.lifecycle} realization={self._schema.realization} "
+                f"device={self._device}{backing}{dynamic}")
 
     @classmethod
     def from_coo(cls, src, dst, *, num_src: int | None = None, num_dst: int | None = None) -> "Graph":
@@ -349,6 +407,15 @@ class Graph:
         if self._shard is not None and self._placement is None:
             raise RuntimeError("a Graph.from_csr_shard block is executable only as a .halo(mesh) snapshot "
                                "under a DistributedRuntime")
+        if self._geometry is not None:
+            row_ptr, col_idx, rebuilt = self._geometry.resolve(self._schema.num_dst)
+            if rebuilt or self._row_ptr is not row_ptr:
+                # a new physical snapshot: everything derived from the previous CSR is stale
+                self._plans, self._transpose_cache = {}, None
+                self._destination_cache = self._degree_bounds_cache = None
+                self.__dict__.pop("_span_ratio_cache", None)
+            self._row_ptr, self._col_idx = row_ptr, col_idx
+            return row_ptr, col_idx
         if self._row_ptr is not None:
             return self._row_ptr, self._col_idx
         if self._paged_store is not None:      # a persistent graph: load the whole topology onto the device
@@ -398,7 +465,11 @@ class Graph:
         return self._destination_cache[1]
 
     def implicit_edge_fields(self, row_ptr, col_idx):
-        return {}
+        """Edge fields the relation provides by itself: ``displacement`` (source - destination,
+        minimum image) and ``distance`` of geometric relations, nothing for stored ones."""
+        if self._geometry is None:
+            return {}
+        return self._geometry.edge_fields(row_ptr, col_idx, self.destination_index(row_ptr))
 
     def degree_bounds(self) -> tuple[int, int]:
         if self._degree_bounds_cache is None:
@@ -491,6 +562,8 @@ class Graph:
         """Launch plan of the CUDA library for this CSR, cached per graph."""
         from .plan import CSRPlan
 
+        if self._geometry is not None:
+            self.resolve_csr()           # drops the cached plans when the positions have changed
         plan = self._plans.get(True) or (None if transpose else self._plans.get(False))
         if plan is None:
             row_ptr, col_idx = self.resolve_csr()

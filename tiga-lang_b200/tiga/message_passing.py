@@ -65,6 +65,17 @@ def _validate_fields(role, fields, entities, device) -> None:
             raise ValueError(f"{role}.{name} must be on {device}")
 
 
+def _implicit_edge_names(graph) -> tuple[str, ...]:
+    """Names of the edge fields a relation provides by itself (geometric relations only)."""
+    return ("displacement", "distance") if getattr(graph, "_geometry", None) is not None else ()
+
+
+def _refuse_shadowing(implicit, edge) -> None:
+    overlap = set(implicit) & set(edge)
+    if overlap:
+        raise ValueError(f"edge fields shadow graph-provided fields: {', '.join(sorted(overlap))}")
+
+
 def _reducer_kind(reducer) -> str | None:
     """'sum' / 'mean' / 'max' / 'additive' for reducers the CSR kernels can fold, else None."""
     if isinstance(reducer, SumReducer):
@@ -99,10 +110,15 @@ class _GuardedLaunch:
     (``_GuardedExecutable`` and the installed fast path,
     python/tiga/interop/torch/message_passing.py:974-1007, 3680-3797)."""
 
-    __slots__ = ("graph", "reducer", "bindings", "specs", "constants", "runner", "variant")
+    __slots__ = ("graph", "reducer", "bindings", "specs", "constants", "runner", "variant", "signature")
 
     def __init__(self, graph, reducer, bindings, tensors, constants, runner, variant):
         self.graph = graph
+        # dynamic relations (Graph.radius / Graph.knn) are rebuilt per call, usually as new Graph
+        # objects: their launches are guarded by the search signature instead of object identity and
+        # the runner is re-pointed at the graph of the call (the reference's ranked executable reuse,
+        # python/tiga/interop/torch/message_passing.py `_RankedExecutable`)
+        self.signature = graph.dynamic_signature() if hasattr(runner, "cell") else None
         self.reducer = reducer
         self.bindings = tuple(bindings)            # (role, name) per tensor the runner takes
         self.specs = tuple(_tensor_spec(t) for t in tensors)
@@ -111,8 +127,11 @@ class _GuardedLaunch:
         self.variant = variant
 
     def try_run(self, kernel, graph, src, dst, edge, params):
-        if graph is not self.graph or kernel.reducer is not self.reducer:
+        if kernel.reducer is not self.reducer:
             return _MISS
+        if graph is not self.graph:
+            if self.signature is None or graph.dynamic_signature() != self.signature:
+                return _MISS
         spaces = {"src": src, "dst": dst, "edge": edge, "param": params}
         tensors = []
         try:
@@ -128,6 +147,8 @@ class _GuardedLaunch:
             return _MISS
         if len(params) != len(self.constants) + sum(1 for role, _ in self.bindings if role == "param"):
             return _MISS
+        if graph is not self.graph:
+            self.runner.cell.graph = self.graph = graph
         return self.runner(*tensors)
 
 
@@ -287,12 +308,45 @@ class MessagePassing(Kernel):
                 f"no native kernel for reducer {type(self.reducer).__name__} with this edge expression")
         from . import ops
 
-        row_ptr, col_idx = graph.resolve_csr()
-        _validate_fields("edge", edge, col_idx.numel(), graph.device)
+        implicit = _implicit_edge_names(graph)
+        _refuse_shadowing(implicit, edge)
         if pattern.src_field not in src:
             raise KeyError(f"edge() reads src.{pattern.src_field}, which was not bound")
-        bindings, tensors = [("src", pattern.src_field)], [src[pattern.src_field]]
-        if pattern.edge_field is not None:
+        cell = SimpleNamespace(graph=graph)     # the graph the runner works on; re-pointed on warm rebinds
+        implicit_weight = pattern.edge_field is not None and pattern.edge_field in implicit
+        if implicit_weight and pattern.edge_field != "distance":
+            raise NotImplementedError("only the scalar edge.distance can weight a source field; "
+                                      "edge.displacement is a vector per edge")
+        identity = float(self.reducer.identity()) if kind in ("sum", "max") else 0.0
+        x_probe = src[pattern.src_field]
+        if (kind == "sum" and identity == 0.0 and graph._geometry is not None and graph._geometry.fusable()
+                and (pattern.edge_field is None or implicit_weight) and x_probe.dtype == torch.float32
+                and x_probe.is_cuda and x_probe.numel() <= 128 * max(int(x_probe.shape[0]), 1)):
+            # the relation is never written: the walk over the cell directory folds the messages
+            from . import geometry
+
+            weight = geometry.PAIR_WEIGHT_DISTANCE if implicit_weight else geometry.PAIR_WEIGHT_ONE
+
+            def fused_runner(x):
+                relation = cell.graph._geometry
+                return geometry.RadiusWeightedSumFunction.apply(
+                    relation.positions, x, relation.directory(), relation.scalar_cutoff(),
+                    relation.exclude_self, weight)
+
+            fused_runner.cell = cell
+            self._record(
+                graph, "b200-generated-radius-distance-sum" if implicit_weight else "b200-generated-radius-sum",
+                ("capture-edge-udf", "recognize-weighted-sum", "elide-implicit-edge-geometry",
+                 "build-hash-cell-directory"),
+                ("radius relation consumed from the cell directory: no edge, distance or displacement "
+                 "is materialised; backward folds dy over the same (symmetric) relation and has a "
+                 "position-cotangent kernel",),
+                extra_key=(tuple(x_probe.shape[1:]), implicit_weight))
+            return [("src", pattern.src_field)], [x_probe], constants, fused_runner
+        row_ptr, col_idx = graph.resolve_csr()
+        _validate_fields("edge", edge, col_idx.numel(), graph.device)
+        bindings, tensors = [("src", pattern.src_field)], [x_probe]
+        if pattern.edge_field is not None and not implicit_weight:
             if pattern.edge_field not in edge:
                 raise KeyError(f"edge() reads edge.{pattern.edge_field}, which was not bound")
             if edge[pattern.edge_field].numel() != col_idx.numel():
@@ -300,24 +354,38 @@ class MessagePassing(Kernel):
             bindings.append(("edge", pattern.edge_field))
             tensors.append(edge[pattern.edge_field])
         weighted = pattern.edge_field is not None
+        implicit_name = pattern.edge_field if implicit_weight else None
+
+        def graph_weight(w):
+            """The weight array of this call: the bound edge field, or the relation's own field."""
+            if implicit_name is None:
+                return w
+            current = cell.graph
+            return current.implicit_edge_fields(*current.resolve_csr())[implicit_name]
+
         info = graph.native_plan(transpose=False).info
         planner_remark = (f"rows by degree bucket, {info['long_rows']} split rows in {info['segments']} "
                           f"segments of {info['segment_edges']} edges")
         if kind == "additive":
             algebra = cap.capture_reducer(self.reducer)
-            runner = _additive_runner(graph, self.reducer, algebra, weighted)
+            additive = _additive_runner(cell, self.reducer, algebra, weighted)
+
+            def additive_runner(x, w=None):
+                return additive(x, graph_weight(w))
+
+            additive_runner.cell = cell
             self._record(
                 graph, "b200-csr-additive-tuple-state",
                 ("capture-edge-udf", "capture-reducer", "prove-additive-state", "plan-degree-buckets"),
                 (planner_remark, f"{algebra.arity} state components, one fused CSR sum per non-constant "
                                  "component; finalize runs on the finished states"),
                 extra_key=(tuple(tensors[0].shape[1:]), weighted, algebra.components))
-            return bindings, tensors, constants, runner
-        identity = float(self.reducer.identity()) if kind in ("sum", "max") else 0.0
+            return bindings, tensors, constants, additive_runner
 
         def runner(x, w=None):
-            return ops.csr_reduce(graph, kind, x, w, identity)
+            return ops.csr_reduce(cell.graph, kind, x, graph_weight(w), identity)
 
+        runner.cell = cell
         self._record(
             graph, f"b200-csr-{'weighted-sum' if kind == 'sum' else kind}-degree-bucket",
             ("capture-edge-udf", "recognize-weighted-sum", "plan-degree-buckets", "plan-split-rows",
@@ -397,6 +465,9 @@ class MessagePassing(Kernel):
         row_ptr, col_idx = graph.resolve_csr()
         _validate_fields("edge", edge, col_idx.numel(), graph.device)
         destination = graph.destination_index(row_ptr)
+        implicit = graph.implicit_edge_fields(row_ptr, col_idx)
+        _refuse_shadowing(implicit, edge)
+        edge = {**implicit, **edge}
         src_at_edge = SimpleNamespace(**{name: value[col_idx] for name, value in src.items()})
         dst_at_edge = SimpleNamespace(**{name: value[destination] for name, value in dst.items()})
         message = cap.call_region(self.edge, (src_at_edge, dst_at_edge, SimpleNamespace(**edge)), params)
@@ -465,7 +536,7 @@ def _eager_reduce(reducer, message, destination, num_dst):
     raise NotImplementedError(f"no eager evaluator for reducer {type(reducer).__name__}")
 
 
-def _additive_runner(graph, reducer, algebra, weighted: bool):
+def _additive_runner(cell, reducer, algebra, weighted: bool):
     """Additive tuple-state reducer: state component k is sum_e c_k * m_e**p_k with m_e = w_e * x[src_e]
     (or x[src_e]).  Because (w x)**p = w**p * x**p, every component with p >= 1 is one fused CSR sum
     over element-wise powers of the node and edge arrays (never an [E, F] temporary); p = 0 counts
@@ -474,6 +545,7 @@ def _additive_runner(graph, reducer, algebra, weighted: bool):
     from . import ops
 
     def runner(x, w=None):
+        graph = cell.graph
         row_ptr = graph.resolve_csr()[0]
         shape = (graph.num_dst,) + (1,) * (x.ndim - 1)
         states = []
