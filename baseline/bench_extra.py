@@ -14,6 +14,12 @@ events on the launching stream and its own clock record):
   l2_hostile_sum    uniform random sources, N = 2^22, 16 edges per row, F = 128: a 2 GB source table,
                     so the no-reuse algorithmic bytes are close to the real DRAM bytes
 
+  dynamic_radius    131 072 points in the unit cube on a binary coordinate grid, scalar features,
+                    cutoff between two squared-distance levels (about 16 neighbours): every step copies
+                    one of two coordinate snapshots into the live position tensor, searches the
+                    neighbours and folds edge.distance * src.x (the reference's dynamic-radius protocol)
+  dynamic_knn       131 072 points, exact 13 nearest neighbours, scalar features, same protocol
+
 `bench` is the bench.py module (timing helpers, peaks, roofline arithmetic).
 """
 from __future__ import annotations
@@ -303,9 +309,115 @@ def l2_hostile(args, device, bench):
             "clocks": clocks}
 
 
+def _binary_grid_snapshots(n, device, seed):
+    """Two coordinate snapshots on a 1/1024 grid of the unit cube: float32 squared distances between
+    grid points are exact, so no pair sits within rounding distance of the cutoff."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    return [(torch.rand(n, 3, generator=gen, device=device) * 1024).floor() / 1024 for _ in range(2)]
+
+
+def _dynamic_relation(args, device, bench, kind):
+    import time as _time
+
+    import numpy as np
+
+    import tiga as tg
+    from oracle import oracle
+
+    n = 131072
+    snapshots = _binary_grid_snapshots(n, device, args.seed)
+    cutoff = float(np.sqrt(np.float32(994.5))) / 1024.0        # between the levels 994 and 995 of |d|^2 * 1024^2
+    k = 13
+    x = torch.rand(n, generator=torch.Generator(device=device).manual_seed(args.seed + 7), device=device)
+    positions = snapshots[0].clone()
+
+    class DistanceSum(tg.MessagePassing):
+        reducer = tg.sum()
+
+        def edge(self, src, dst, edge):
+            return edge.distance * src.x
+
+    class NeighborSum(tg.MessagePassing):
+        reducer = tg.sum()
+
+        def edge(self, src, dst, edge):
+            return src.x
+
+    kernel = DistanceSum() if kind == "radius" else NeighborSum()
+    state = {"calls": 0}
+
+    def relation():
+        return tg.Graph.radius(positions, cutoff) if kind == "radius" else tg.Graph.knn(positions, k)
+
+    def step():
+        positions.copy_(snapshots[state["calls"] & 1])          # coordinate copy is part of the call
+        state["calls"] += 1
+        return kernel(graph=relation(), src={"x": x}, dst={})
+
+    # every snapshot's output is checked against the CPU oracle before anything is timed
+    checks = []
+    cpu_seconds = 0.0
+    for snapshot in snapshots:
+        positions.copy_(snapshot)
+        got = kernel(graph=relation(), src={"x": x}, dst={}).cpu().numpy()
+        t0 = _time.perf_counter()
+        if kind == "radius":
+            row_ptr, col, distance, _, _ = oracle.radius_build(snapshot.cpu().numpy(), np.float32(cutoff),
+                                                               exclude_self=True, use_cells=True)
+            want = oracle.wsum_fwd(row_ptr, col, x.cpu().numpy()[:, None], distance)[:, 0]
+            edges = int(col.size)
+        else:
+            sample = 2048                                        # brute force on the CPU: a bounded sample of queries
+            col = oracle.knn_build(snapshot.cpu().numpy()[:sample], snapshot.cpu().numpy(), k, exclude_self=True)
+            want = x.cpu().numpy()[col].astype(np.float32)
+            want = np.add.reduce(want, axis=1, dtype=np.float32)
+            got = got[:sample]
+            edges = n * k
+        cpu_seconds += _time.perf_counter() - t0
+        checks.append(bool(np.allclose(got, want, rtol=1e-5, atol=1e-5)) if kind == "knn"
+                      else bool(np.array_equal(got, want)))
+    steps = _steps(args)
+    ms, clocks = bench.timed(step, steps, max(args.warmup, 4), device.index or 0)
+    result = {"workload": (f"dynamic radius, {n} points, binary grid, cutoff {cutoff:.6f} (~{edges / n:.1f} "
+                           "neighbours), scalar features, fused distance-weighted sum"
+                           if kind == "radius" else
+                           f"dynamic exact kNN, {n} points, k={k}, scalar features, neighbour sum"),
+              "points": n, "edges": edges, "steps": steps, "ms_per_call": round(ms, 4),
+              "lowering": kernel.last_variant.lowering, "staging_runs": kernel.cache_info["misses"],
+              "outputs_checked_against_oracle": checks, "clocks": clocks,
+              "includes": "coordinate copy + neighbour search + aggregation, a new Graph per call"}
+    if kind == "radius":
+        # the same relation written out as a CSR (count, scan, fill with distance and displacement)
+        def build_only():
+            positions.copy_(snapshots[state["calls"] & 1])
+            state["calls"] += 1
+            return tg.Graph.radius(positions, cutoff).resolve_csr()
+
+        build_ms, _ = bench.timed(build_only, steps, 3, device.index or 0)
+        result["csr_build_ms"] = round(build_ms, 4)
+        result["cpu_oracle_s_per_snapshot"] = round(cpu_seconds / 2, 3)
+        result["reference_published_ms"] = {"tiga": 1.84, "pyg": 80.24, "hardware": "the reference's own GPU"}
+    else:
+        pairs = float(n) * n
+        result["pair_distances_per_s"] = round(pairs / (ms * 1e-3) / 1e12, 3)
+        result["pair_unit"] = "T pairs/s"
+        result["cpu_oracle_s_for_2048_queries"] = round(cpu_seconds / 2, 3)
+        result["reference_published_ms"] = {"tiga": 172.37, "pyg": 393.21, "hardware": "the reference's own GPU"}
+    return result
+
+
+def dynamic_radius(args, device, bench):
+    return _dynamic_relation(args, device, bench, "radius")
+
+
+def dynamic_knn(args, device, bench):
+    return _dynamic_relation(args, device, bench, "knn")
+
+
 WORKLOADS = {"weighted-sum": ("c1_weighted_sum", weighted_sum_c1), "gcn-layer": ("c2_gcn_layer", gcn_layer_sum),
              "gcn-layer-max": ("c2_gcn_layer_max", gcn_layer_max), "gat": ("c3_gat", gat),
-             "attention": ("c4_attention", attention), "l2-hostile": ("l2_hostile_sum", l2_hostile)}
+             "attention": ("c4_attention", attention), "l2-hostile": ("l2_hostile_sum", l2_hostile),
+             "dynamic-radius": ("dynamic_radius", dynamic_radius), "dynamic-knn": ("dynamic_knn", dynamic_knn)}
 
 
 def run_one(name, args, device, bench):

@@ -505,6 +505,79 @@ TGB_API int32_t tgb_edge_geometry(const void *dst_positions, const void *src_pos
                                   const void *col, int64_t num_dst, int64_t num_edges,
                                   void *displacement, void *distance, uint64_t stream);
 
+/* ------------------------------------------------------------------------
+ * Generic edge programs: an arbitrary element-wise edge expression folded over
+ * CSR rows.  Replace the reference's generic CSR kernels gf_csr_additive_tile
+ * (one row per program, lib/Target/Triton/Translate.cpp:2630-2783, expression
+ * emitter :381-460) and gf_csr_scalar_reduce (:3452-3634) reached through
+ * _execute_generic_csr (python/tiga/interop/torch/message_passing.py:2579-2815),
+ * and the Torch autograd replay of the eager evaluator for their gradients.
+ *
+ * The expression is a register program: instruction i computes
+ *   value[i] = op[i](value[a[i]], value[b[i]])
+ * in float32, the last instruction is the message.  LOAD reads operand a[i]
+ * (every operand is loaded by exactly one instruction), CONST reads
+ * constants[a[i]].  An operand is a float32 array of per-entity rows: entity =
+ * source of the edge (role 0), destination row (1), edge id (2) or none (3, a
+ * tensor parameter); operand_modulus 0 = `width` elements per entity (element
+ * f), 1 = one element per entity, m > 1 = m elements per entity (element f % m).
+ * ------------------------------------------------------------------------ */
+enum {
+  TGB_EP_LOAD = 0, TGB_EP_CONST = 1, TGB_EP_ADD = 2, TGB_EP_SUB = 3, TGB_EP_MUL = 4,
+  TGB_EP_DIV = 5, TGB_EP_MAX = 6, TGB_EP_EXP = 7, TGB_EP_NEG = 8
+};
+enum { TGB_EP_ROLE_SRC = 0, TGB_EP_ROLE_DST = 1, TGB_EP_ROLE_EDGE = 2, TGB_EP_ROLE_PARAM = 3 };
+#define TGB_EP_MAX_INSTRUCTIONS 48
+#define TGB_EP_MAX_OPERANDS 8
+#define TGB_EP_MAX_CONSTANTS 16
+
+typedef struct tgb_edge_program {
+  int32_t num_instructions;
+  int32_t num_operands;
+  int32_t width; /* elements of one message */
+  int32_t reserved;
+  uint8_t op[TGB_EP_MAX_INSTRUCTIONS];
+  uint8_t a[TGB_EP_MAX_INSTRUCTIONS];
+  uint8_t b[TGB_EP_MAX_INSTRUCTIONS];
+  float constants[TGB_EP_MAX_CONSTANTS];
+  int32_t operand_role[TGB_EP_MAX_OPERANDS];
+  int32_t operand_modulus[TGB_EP_MAX_OPERANDS];
+} tgb_edge_program;
+
+/* out[i, f] = reduce over the edges of row i, in edge order, of the message
+ * element f.  reducer: TGB_REDUCER_SUM (rows without edges give `identity`),
+ * _MEAN (NaN for rows without edges), _MAX (identity).  operands[k]: device
+ * pointer of operand k.  out: float32 [num_dst, width]. */
+TGB_API int32_t tgb_edge_program_fwd(const tgb_csr_plan *plan,
+                                     const tgb_edge_program *program,
+                                     const void *const *operands, int32_t reducer,
+                                     float identity, void *out, uint64_t stream);
+
+/* Reverse mode, destination-major pass (SUM / MEAN): for every operand k with
+ * grads[k] != null and role DST, EDGE or PARAM, writes its cotangent given
+ * dy [num_dst, width]: DST -> [num_dst, elements], EDGE -> [E, elements],
+ * PARAM -> one partial row per destination, [num_dst, elements], to be summed
+ * with tgb_column_sum.  Cotangents are supported for modulus 0 and 1. */
+TGB_API int32_t tgb_edge_program_bwd_rows(const tgb_csr_plan *plan,
+                                          const tgb_edge_program *program,
+                                          const void *const *operands, int32_t reducer,
+                                          const void *dy, void *const *grads,
+                                          uint64_t stream);
+
+/* Reverse mode, source-major pass over the plan's transposed relation (the
+ * plan needs TGB_PLAN_TRANSPOSE): cotangents of the SRC operands with
+ * grads[k] != null, [num_src, elements]; no atomics. */
+TGB_API int32_t tgb_edge_program_bwd_sources(const tgb_csr_plan *plan,
+                                             const tgb_edge_program *program,
+                                             const void *const *operands, int32_t reducer,
+                                             const void *dy, void *const *grads,
+                                             uint64_t stream);
+
+/* out[c] = sum over r of partial[r, c] (float32, rows added in a fixed order:
+ * strips of rows by one thread each, then the strips in order). */
+TGB_API int32_t tgb_column_sum(const void *partial, int64_t rows, int64_t cols,
+                               void *out, uint64_t stream);
+
 #ifdef __cplusplus
 }
 #endif

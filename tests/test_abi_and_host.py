@@ -329,3 +329,34 @@ def test_gfg_reader_and_writer_match_the_reference_files(tmp_path):
         tg.load(tmp_path / "copy.gfg")
     with pytest.raises(ValueError):
         tg.save(plain, tmp_path / "again.gfg", overwrite=True)
+
+
+def test_edge_expression_compiles_to_a_register_program():
+    from tiga import capture as cap, edge_program as ep
+
+    class Flux(tg.MessagePassing):
+        reducer = tg.sum()
+
+        def edge(self, src, dst, edge, k, gain):
+            s = edge.weight * (src.u - dst.u) * gain
+            return tg.math.maximum(s, k * s) / 2.0 + (-src.u).exp()
+
+    staged = cap.capture_edge(Flux().edge, {"k": 0.2, "gain": torch.ones(4)})
+    program = ep.compile_expression(staged)
+    assert [o.role for o in program.operands] == ["edge", "src", "dst", "param"]
+    assert program.ops.count(ep.OP_LOAD) == 4            # `s` and src.u are used twice, loaded once
+    assert program.constants == (0.2, 2.0)
+    for i, op in enumerate(program.ops):                 # operands are earlier instructions
+        if op not in (ep.OP_LOAD, ep.OP_CONST):
+            assert program.lhs[i] < i and program.rhs[i] <= i
+    # shapes: fields share a rank, tensor parameters broadcast from the right
+    shape, moduli = ep.bind(program, [torch.zeros(7, 1), torch.zeros(5, 4), torch.zeros(5, 4), torch.ones(4)])
+    assert shape == (4,) and moduli == (1, 0, 0, 0)
+    shape, moduli = ep.bind(program, [torch.zeros(7, 1, 1), torch.zeros(5, 3, 4), torch.zeros(5, 3, 4), torch.ones(4)])
+    assert shape == (3, 4) and moduli == (1, 0, 0, 4)
+    with pytest.raises(NotImplementedError, match="same number of dimensions"):
+        ep.bind(program, [torch.zeros(7), torch.zeros(5, 4), torch.zeros(5, 4), torch.ones(4)])
+    struct = ep.make_struct(program, 4, (1, 0, 0, 0))
+    assert struct.num_instructions == len(program.ops) and struct.width == 4
+    # a reduction over features is not element-wise: no program
+    assert ep.compile_expression(cap.capture_edge(lambda src, dst, edge: (src.x * dst.x).sum(-1), {})) is None

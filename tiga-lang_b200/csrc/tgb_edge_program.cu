@@ -1,0 +1,395 @@
+// Generic edge programs: an element-wise edge expression, given as a small register program,
+// evaluated per edge and feature element and folded over CSR rows; plus its reverse mode.
+//
+// Replaces the reference's generic CSR kernels (gf_csr_additive_tile with one row per program,
+// lib/Target/Triton/Translate.cpp:2630-2783 with the expression emitter at :381-460, and
+// gf_csr_scalar_reduce, :3452-3634, of walkerchi/TIGA-lang) and the Torch autograd replay behind them.
+//
+// One thread group of LANES lanes owns a row; lane l evaluates the feature elements l, l + LANES, ...
+// one chunk after the other, walking the row's edges sequentially for each chunk, so a row is
+// folded in edge order (the reference's left fold) and nothing is reduced with atomics.
+//   forward           rows = destinations
+//   backward (rows)   rows = destinations: cotangents of dst / edge / parameter operands
+//   backward (sources) rows = sources over the plan's transposed relation: cotangents of src operands
+// The interpreter costs ~10 instructions per program instruction; programs the library has a
+// dedicated kernel for (weighted sums, attention) never come here.
+#include "tgb_common.cuh"
+
+namespace tgb {
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kMaxI = TGB_EP_MAX_INSTRUCTIONS;
+constexpr int kMaxO = TGB_EP_MAX_OPERANDS;
+
+struct Operands {
+  const float *ptr[kMaxO];
+};
+struct Sinks {
+  float *ptr[kMaxO];
+};
+
+// One traversal: rows with their entries; entry -> (neighbour, edge id).
+struct Walk {
+  const void *ptr;        // row pointers
+  const void *idx;        // neighbour per entry
+  const uint32_t *eid;    // original edge id per entry, or null: entry index = edge id
+  int ptr_bits, idx_bits;
+  int64_t n_rows;
+};
+
+__device__ __forceinline__ int64_t load_index(const void *base, int bits, int64_t i) {
+  return bits == 64 ? __ldg(static_cast<const int64_t *>(base) + i)
+                    : (int64_t)__ldg(static_cast<const int32_t *>(base) + i);
+}
+
+// value[] of every instruction for one (source, destination, edge, element)
+__device__ __forceinline__ void evaluate(const tgb_edge_program &p, const Operands &in, int64_t src, int64_t dst,
+                                         int64_t edge, int f, float *value) {
+  const int n = p.num_instructions;
+  for (int i = 0; i < n; ++i) {
+    const int a = p.a[i], b = p.b[i];
+    float v;
+    switch (p.op[i]) {
+      case TGB_EP_LOAD: {
+        const int role = p.operand_role[a], m = p.operand_modulus[a];
+        const int64_t entity = role == TGB_EP_ROLE_SRC ? src : role == TGB_EP_ROLE_DST ? dst
+                               : role == TGB_EP_ROLE_EDGE ? edge : 0;
+        const int count = m == 0 ? p.width : m;
+        const int offset = m == 0 ? f : (m == 1 ? 0 : f % m);
+        v = __ldg(in.ptr[a] + entity * count + offset);
+        break;
+      }
+      case TGB_EP_CONST: v = p.constants[a]; break;
+      case TGB_EP_ADD: v = __fadd_rn(value[a], value[b]); break;
+      case TGB_EP_SUB: v = __fsub_rn(value[a], value[b]); break;
+      case TGB_EP_MUL: v = __fmul_rn(value[a], value[b]); break;
+      case TGB_EP_DIV: v = __fdiv_rn(value[a], value[b]); break;
+      case TGB_EP_MAX: {     // torch.maximum: NaN wins
+        const float x = value[a], y = value[b];
+        v = (x != x || y != y) ? __int_as_float(0x7fc00000) : fmaxf(x, y);
+        break;
+      }
+      case TGB_EP_EXP: v = expf(value[a]); break;
+      default: v = -value[a]; break;   // TGB_EP_NEG
+    }
+    value[i] = v;
+  }
+}
+
+// adjoint[] of every instruction given the cotangent g of the message
+__device__ __forceinline__ void reverse_sweep(const tgb_edge_program &p, const float *value, float g, float *adjoint) {
+  const int n = p.num_instructions;
+  for (int i = 0; i < n; ++i) adjoint[i] = 0.0f;
+  adjoint[n - 1] = g;
+  for (int i = n - 1; i >= 0; --i) {
+    const float gi = adjoint[i];
+    const int a = p.a[i], b = p.b[i];
+    switch (p.op[i]) {
+      case TGB_EP_ADD: adjoint[a] += gi; adjoint[b] += gi; break;
+      case TGB_EP_SUB: adjoint[a] += gi; adjoint[b] -= gi; break;
+      case TGB_EP_MUL: adjoint[a] += gi * value[b]; adjoint[b] += gi * value[a]; break;
+      case TGB_EP_DIV: {
+        const float q = gi / value[b];
+        adjoint[a] += q;
+        adjoint[b] -= q * value[i];
+        break;
+      }
+      case TGB_EP_MAX: {     // the larger operand takes the cotangent, equal operands share it
+        const float x = value[a], y = value[b];
+        adjoint[a] += x > y ? gi : (x == y ? 0.5f * gi : 0.0f);
+        adjoint[b] += y > x ? gi : (x == y ? 0.5f * gi : 0.0f);
+        break;
+      }
+      case TGB_EP_EXP: adjoint[a] += gi * value[i]; break;
+      case TGB_EP_NEG: adjoint[a] -= gi; break;
+      default: break;        // LOAD: a sink; CONST: nothing
+    }
+  }
+}
+
+template <int LANES>
+__device__ __forceinline__ unsigned group_mask() {
+  return LANES == 32 ? 0xffffffffu : ((1u << LANES) - 1u) << ((threadIdx.x & 31) / LANES * LANES);
+}
+
+template <int LANES>
+__device__ __forceinline__ float group_sum(float v, unsigned mask) {
+#pragma unroll
+  for (int offset = LANES / 2; offset > 0; offset >>= 1) v += __shfl_xor_sync(mask, v, offset, LANES);
+  return v;
+}
+
+template <int LANES>
+__global__ void __launch_bounds__(kThreads)
+k_edge_program_fwd(const __grid_constant__ tgb_edge_program p, Operands in, Walk w, int reducer, float identity,
+                   float *__restrict__ out) {
+  const int64_t row = ((int64_t)blockIdx.x * kThreads + threadIdx.x) / LANES;
+  const int lane = threadIdx.x % LANES;
+  if (row >= w.n_rows) return;
+  const int64_t begin = load_index(w.ptr, w.ptr_bits, row), end = load_index(w.ptr, w.ptr_bits, row + 1);
+  float value[kMaxI];
+  for (int f = lane; f < p.width; f += LANES) {
+    float acc = reducer == TGB_REDUCER_MEAN ? 0.0f : identity;      // the fold starts from the identity
+    for (int64_t e = begin; e < end; ++e) {
+      evaluate(p, in, load_index(w.idx, w.idx_bits, e), row, e, f, value);
+      const float m = value[p.num_instructions - 1];
+      if (reducer == TGB_REDUCER_MAX) acc = (acc != acc || m != m) ? __int_as_float(0x7fc00000) : fmaxf(acc, m);
+      else acc = __fadd_rn(acc, m);
+    }
+    if (reducer == TGB_REDUCER_MEAN) acc = __fdiv_rn(acc, (float)(end - begin));
+    out[row * p.width + f] = acc;
+  }
+}
+
+// Reverse mode over one traversal.  The pass owns, per ROW, the operands of its own side (dst and
+// tensor parameters in the destination-major pass, src in the source-major pass); EDGE operands are
+// written per entry by the destination-major pass.
+template <int LANES, bool SOURCE_MAJOR>
+__global__ void __launch_bounds__(kThreads)
+k_edge_program_bwd(const __grid_constant__ tgb_edge_program p, Operands in, Sinks sinks, Walk w, int reducer,
+                   const void *__restrict__ degree_ptr, int degree_bits, const float *__restrict__ dy) {
+  const int64_t row = ((int64_t)blockIdx.x * kThreads + threadIdx.x) / LANES;
+  const int lane = threadIdx.x % LANES;
+  if (row >= w.n_rows) return;
+  const unsigned mask = group_mask<LANES>();
+  const int64_t begin = load_index(w.ptr, w.ptr_bits, row), end = load_index(w.ptr, w.ptr_bits, row + 1);
+  float value[kMaxI], adjoint[kMaxI];
+  float scalar_total[kMaxO];          // per-lane partial sums of the row-owned operands with one element per entity
+#pragma unroll
+  for (int k = 0; k < kMaxO; ++k) scalar_total[k] = 0.0f;
+  // the group runs ceil(width / LANES) chunks together, so that its shuffles see all lanes
+  const int chunks = (p.width + LANES - 1) / LANES;
+  for (int chunk = 0; chunk < chunks; ++chunk) {
+    const int f = chunk * LANES + lane;
+    const bool live = f < p.width;
+    float full_total[kMaxO];
+#pragma unroll
+    for (int k = 0; k < kMaxO; ++k) full_total[k] = 0.0f;
+    for (int64_t t = begin; t < end; ++t) {
+      const int64_t other = load_index(w.idx, w.idx_bits, t);
+      const int64_t edge = w.eid ? (int64_t)__ldg(w.eid + t) : t;
+      const int64_t src = SOURCE_MAJOR ? row : other, dst = SOURCE_MAJOR ? other : row;
+      if (live) {
+        float g = __ldg(dy + dst * p.width + f);
+        if (reducer == TGB_REDUCER_MEAN) {
+          const int64_t degree = load_index(degree_ptr, degree_bits, dst + 1) - load_index(degree_ptr, degree_bits, dst);
+          g = g / (float)degree;
+        }
+        evaluate(p, in, src, dst, edge, f, value);
+        reverse_sweep(p, value, g, adjoint);
+      }
+      // every operand is loaded by exactly one instruction: its adjoint is the operand's cotangent
+      for (int i = 0; i < p.num_instructions; ++i) {
+        if (p.op[i] != TGB_EP_LOAD) continue;
+        const int k = p.a[i];
+        float *sink = sinks.ptr[k];
+        if (sink == nullptr) continue;
+        const int role = p.operand_role[k];
+        const bool full = p.operand_modulus[k] == 0 || p.width == 1;
+        const float gk = live ? adjoint[i] : 0.0f;
+        if (role == TGB_EP_ROLE_EDGE) {
+          if (SOURCE_MAJOR) continue;
+          if (full) {
+            if (live) sink[edge * p.width + f] = gk;
+          } else {             // one value per edge: lanes and chunks add up, chunk after chunk by lane 0
+            const float total = group_sum<LANES>(gk, mask);
+            if (lane == 0) sink[edge] = chunk == 0 ? total : sink[edge] + total;
+          }
+        } else if ((role == TGB_EP_ROLE_SRC) == SOURCE_MAJOR) {
+#pragma unroll
+          for (int q = 0; q < kMaxO; ++q)
+            if (q == k) {
+              if (full) full_total[q] += gk; else scalar_total[q] += gk;
+            }
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxO; ++k) {
+      if (k >= p.num_operands || sinks.ptr[k] == nullptr) continue;
+      const int role = p.operand_role[k];
+      if (role == TGB_EP_ROLE_EDGE || (role == TGB_EP_ROLE_SRC) != SOURCE_MAJOR) continue;
+      const bool full = p.operand_modulus[k] == 0 || p.width == 1;
+      if (full && live) sinks.ptr[k][row * p.width + f] = full_total[k];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kMaxO; ++k) {
+    if (k >= p.num_operands || sinks.ptr[k] == nullptr) continue;
+    const int role = p.operand_role[k];
+    if (role == TGB_EP_ROLE_EDGE || (role == TGB_EP_ROLE_SRC) != SOURCE_MAJOR) continue;
+    const bool full = p.operand_modulus[k] == 0 || p.width == 1;
+    if (full) continue;
+    const float total = group_sum<LANES>(scalar_total[k], mask);
+    if (lane == 0) sinks.ptr[k][row] = total;
+  }
+}
+
+// out[c] = sum_r partial[r, c]: 32 columns x 8 row strips per block, strips added in order
+__global__ void __launch_bounds__(256)
+k_column_sum(const float *__restrict__ partial, int64_t rows, int64_t cols, float *__restrict__ out) {
+  __shared__ float strip[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t c = (int64_t)blockIdx.x * 32 + tx;
+  float acc = 0.0f;
+  if (c < cols)
+    for (int64_t r = ty; r < rows; r += 8) acc += __ldg(partial + r * cols + c);
+  strip[ty][tx] = acc;
+  __syncthreads();
+  if (ty == 0 && c < cols) {
+    float total = strip[0][tx];
+#pragma unroll
+    for (int s = 1; s < 8; ++s) total += strip[s][tx];
+    out[c] = total;
+  }
+}
+
+int lanes_for_width(int width) {
+  int lanes = 1;
+  while (lanes < 32 && lanes < width) lanes <<= 1;
+  return lanes;
+}
+
+int32_t check_program(const tgb_csr_plan *plan, const tgb_edge_program *p, const void *const *operands) {
+  if (!plan || !p || !operands) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null argument");
+  if (p->num_instructions < 1 || p->num_instructions > kMaxI || p->num_operands < 1 || p->num_operands > kMaxO)
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "program size out of range");
+  if (p->width < 1) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "message width must be positive");
+  int loads[kMaxO] = {0};
+  for (int i = 0; i < p->num_instructions; ++i) {
+    const int op = p->op[i];
+    if (op > TGB_EP_NEG) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "unknown opcode %d", op);
+    if (op == TGB_EP_LOAD) {
+      if (p->a[i] >= p->num_operands) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "operand index out of range");
+      if (++loads[p->a[i]] > 1) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "an operand must be loaded by one instruction");
+    } else if (op == TGB_EP_CONST) {
+      if (p->a[i] >= TGB_EP_MAX_CONSTANTS) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "constant index out of range");
+    } else {
+      const bool binary = op >= TGB_EP_ADD && op <= TGB_EP_MAX;
+      if (p->a[i] >= i || (binary && p->b[i] >= i))
+        TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "instruction %d reads a later value", i);
+    }
+  }
+  for (int k = 0; k < p->num_operands; ++k) {
+    if (!operands[k]) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null operand %d", k);
+    const int m = p->operand_modulus[k];
+    if (m < 0 || (m > 1 && p->width % m != 0)) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "operand %d: bad modulus", k);
+    if (p->operand_role[k] < 0 || p->operand_role[k] > TGB_EP_ROLE_PARAM)
+      TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "operand %d: bad role", k);
+  }
+  return TGB_STATUS_OK;
+}
+
+Walk forward_walk(const tgb_csr_plan *plan) {
+  return Walk{plan->fwd.ptr, plan->fwd.idx, nullptr, plan->fwd.ptr_bits, plan->fwd.idx_bits, plan->num_dst};
+}
+
+}  // namespace
+}  // namespace tgb
+
+using namespace tgb;
+
+#define TGB_EP_LANES(lanes, CALL)       \
+  switch (lanes) {                      \
+    case 1: CALL(1); break;             \
+    case 2: CALL(2); break;             \
+    case 4: CALL(4); break;             \
+    case 8: CALL(8); break;             \
+    case 16: CALL(16); break;           \
+    default: CALL(32); break;           \
+  }
+
+extern "C" int32_t tgb_edge_program_fwd(const tgb_csr_plan *plan, const tgb_edge_program *program,
+                                        const void *const *operands, int32_t reducer, float identity, void *out,
+                                        uint64_t stream) {
+  const int32_t status = check_program(plan, program, operands);
+  if (status != TGB_STATUS_OK) return status;
+  if (reducer != TGB_REDUCER_SUM && reducer != TGB_REDUCER_MEAN && reducer != TGB_REDUCER_MAX)
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "unknown reducer");
+  if (plan->num_dst == 0) return TGB_STATUS_OK;
+  if (!out) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null output");
+  Operands in;
+  for (int k = 0; k < kMaxO; ++k) in.ptr[k] = k < program->num_operands ? static_cast<const float *>(operands[k]) : nullptr;
+  const Walk w = forward_walk(plan);
+  const int lanes = lanes_for_width(program->width);
+  const unsigned blocks = (unsigned)ceil_div(plan->num_dst * lanes, kThreads);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define TGB_FWD(L) \
+  k_edge_program_fwd<L><<<blocks, kThreads, 0, st>>>(*program, in, w, reducer, identity, static_cast<float *>(out))
+  TGB_EP_LANES(lanes, TGB_FWD)
+#undef TGB_FWD
+  TGB_LAUNCHED();
+  return TGB_STATUS_OK;
+}
+
+namespace {
+
+int32_t backward(bool source_major, const tgb_csr_plan *plan, const tgb_edge_program *program,
+                 const void *const *operands, int32_t reducer, const void *dy, void *const *grads,
+                 uint64_t stream) {
+  const int32_t status = check_program(plan, program, operands);
+  if (status != TGB_STATUS_OK) return status;
+  if (reducer != TGB_REDUCER_SUM && reducer != TGB_REDUCER_MEAN)
+    TGB_FAIL(TGB_STATUS_UNSUPPORTED, "reverse mode covers the sum and mean reducers");
+  if (!dy || !grads) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null cotangent");
+  if (source_major && !(plan->flags & TGB_PLAN_TRANSPOSE))
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "the source-major pass needs a plan with the transposed relation");
+  Operands in;
+  Sinks sinks;
+  bool any = false;
+  for (int k = 0; k < kMaxO; ++k) {
+    in.ptr[k] = k < program->num_operands ? static_cast<const float *>(operands[k]) : nullptr;
+    sinks.ptr[k] = nullptr;
+    if (k >= program->num_operands || !grads[k]) continue;
+    const int role = program->operand_role[k];
+    const bool mine = source_major ? role == TGB_EP_ROLE_SRC : role != TGB_EP_ROLE_SRC;
+    if (!mine) continue;
+    if (program->operand_modulus[k] > 1)
+      TGB_FAIL(TGB_STATUS_UNSUPPORTED, "operand %d broadcasts along trailing dimensions: no cotangent kernel", k);
+    sinks.ptr[k] = static_cast<float *>(grads[k]);
+    any = true;
+  }
+  if (!any) return TGB_STATUS_OK;
+  Walk w = forward_walk(plan);
+  if (source_major) w = Walk{plan->bwd.ptr, plan->bwd.idx, plan->bwd.eid, plan->bwd.ptr_bits, plan->bwd.idx_bits,
+                             plan->num_src};
+  if (w.n_rows == 0) return TGB_STATUS_OK;
+  const int lanes = lanes_for_width(program->width);
+  const unsigned blocks = (unsigned)ceil_div(w.n_rows * lanes, kThreads);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define TGB_BWD(L)                                                                                               \
+  if (source_major)                                                                                              \
+    k_edge_program_bwd<L, true><<<blocks, kThreads, 0, st>>>(*program, in, sinks, w, reducer, plan->fwd.ptr,    \
+                                                             plan->fwd.ptr_bits, static_cast<const float *>(dy)); \
+  else                                                                                                           \
+    k_edge_program_bwd<L, false><<<blocks, kThreads, 0, st>>>(*program, in, sinks, w, reducer, plan->fwd.ptr,   \
+                                                              plan->fwd.ptr_bits, static_cast<const float *>(dy))
+  TGB_EP_LANES(lanes, TGB_BWD)
+#undef TGB_BWD
+  TGB_LAUNCHED();
+  return TGB_STATUS_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t tgb_edge_program_bwd_rows(const tgb_csr_plan *plan, const tgb_edge_program *program,
+                                             const void *const *operands, int32_t reducer, const void *dy,
+                                             void *const *grads, uint64_t stream) {
+  return backward(false, plan, program, operands, reducer, dy, grads, stream);
+}
+
+extern "C" int32_t tgb_edge_program_bwd_sources(const tgb_csr_plan *plan, const tgb_edge_program *program,
+                                                const void *const *operands, int32_t reducer, const void *dy,
+                                                void *const *grads, uint64_t stream) {
+  return backward(true, plan, program, operands, reducer, dy, grads, stream);
+}
+
+extern "C" int32_t tgb_column_sum(const void *partial, int64_t rows, int64_t cols, void *out, uint64_t stream) {
+  if (rows < 0 || cols < 1) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "invalid shape");
+  if (!out || (rows > 0 && !partial)) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
+  k_column_sum<<<(unsigned)ceil_div(cols, 32), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float *>(partial), rows, cols, static_cast<float *>(out));
+  TGB_LAUNCHED();
+  return TGB_STATUS_OK;
+}

@@ -303,6 +303,14 @@ class MessagePassing(Kernel):
             return self._specialise_online_softmax(graph, src, dst, edge, params, staged, constants)
         kind = _reducer_kind(self.reducer)
         pattern = cap.recognize_weighted_sum(staged)
+        if kind in ("sum", "mean", "max") and isinstance(staged, cap.Expr):
+            vector_weight = (pattern is not None and pattern.edge_field is not None and pattern.edge_field in edge
+                             and pattern.src_field in src
+                             and edge[pattern.edge_field].numel() != edge[pattern.edge_field].shape[0])
+            if pattern is None or vector_weight:
+                generic = self._specialise_edge_program(graph, src, dst, edge, params, staged, constants, kind)
+                if generic is not None:
+                    return generic
         if kind is None or pattern is None:
             raise NotImplementedError(
                 f"no native kernel for reducer {type(self.reducer).__name__} with this edge expression")
@@ -394,6 +402,58 @@ class MessagePassing(Kernel):
              "backward: dx gathers over the cached stable transposed relation (no atomics), "
              "dw is a per-edge dot product"),
             extra_key=(tuple(tensors[0].shape[1:]), weighted))
+        return bindings, tensors, constants, runner
+
+    def _specialise_edge_program(self, graph, src, dst, edge, params, staged, constants, kind):
+        """Any element-wise edge expression: compiled to a register program for the interpreting
+        kernels (forward, destination-major and source-major reverse mode)."""
+        from . import edge_program as ep
+
+        program = ep.compile_expression(staged)
+        if program is None:
+            return None
+        implicit = _implicit_edge_names(graph)
+        _refuse_shadowing(implicit, edge)
+        row_ptr, col_idx = graph.resolve_csr()
+        _validate_fields("edge", edge, col_idx.numel(), graph.device)
+        spaces = {"src": src, "dst": dst, "edge": edge, "param": params}
+        bindings, tensors, slots = [], [], []        # slots: index into the bound tensors, or an implicit name
+        for operand in program.operands:
+            if operand.role == "edge" and operand.name in implicit:
+                slots.append(operand.name)
+                continue
+            if operand.name not in spaces[operand.role]:
+                raise KeyError(f"edge() reads {operand.role}.{operand.name}, which was not bound")
+            slots.append(len(tensors))
+            bindings.append((operand.role, operand.name))
+            tensors.append(spaces[operand.role][operand.name])
+        cell = SimpleNamespace(graph=graph)
+        reducer_id = {"sum": ep.REDUCE_SUM, "mean": ep.REDUCE_MEAN, "max": ep.REDUCE_MAX}[kind]
+        identity = float(self.reducer.identity()) if kind in ("sum", "max") else 0.0
+
+        def runner(*bound):
+            current = cell.graph
+            provided = None
+            operands = []
+            for slot in slots:
+                if isinstance(slot, str):
+                    if provided is None:
+                        provided = current.implicit_edge_fields(*current.resolve_csr())
+                    operands.append(provided[slot])
+                else:
+                    operands.append(bound[slot])
+            return ep.EdgeProgramFunction.apply(current, program, reducer_id, identity, *operands)
+
+        runner.cell = cell
+        probe_shapes = tuple(tuple(t.shape[1:]) if role != "param" else tuple(t.shape)
+                             for (role, _), t in zip(bindings, tensors))
+        self._record(
+            graph, "b200-generic-csr-scalar-reducer",
+            ("capture-edge-udf", "compile-edge-register-program", "reverse-mode-edge-program"),
+            (f"{len(program.ops)} instructions over {len(program.operands)} operands, evaluated per edge and "
+             "feature element; rows folded in edge order; cotangents by a destination-major and a "
+             "source-major pass without atomics",),
+            extra_key=(program.key(), probe_shapes, kind))
         return bindings, tensors, constants, runner
 
     def _specialise_online_softmax(self, graph, src, dst, edge, params, staged, constants):
