@@ -162,7 +162,7 @@ def gat(args, device, bench):
     import tiga as tg
     from baseline import synthetic as syn
 
-    scale, edge_factor, H, D = 21, 32, 8, 32
+    scale, edge_factor, H, D = getattr(args, "gat_scale", 21), 32, 8, 32
     row_ptr, col = syn.rmat_csr(scale, edge_factor, seed=args.seed, symmetrize=False, device=device)
     N, E = row_ptr.numel() - 1, col.numel()
     x = syn.normal((N, H, D), seed=args.seed + 1, device=device, dtype=torch.bfloat16).requires_grad_()

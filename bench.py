@@ -61,6 +61,7 @@ def parse_args():
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", default="native", choices=("native", "reference"))
     p.add_argument("--scale", type=int, default=25, help="log2 of the node count of the headline graph")
+    p.add_argument("--gat-scale", type=int, default=21, help="log2 of the node count of the gat workload's graph")
     p.add_argument("--edge-factor", type=int, default=16)
     p.add_argument("--features", type=int, default=64)
     p.add_argument("--layers", type=int, default=2)

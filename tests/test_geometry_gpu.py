@@ -176,6 +176,10 @@ def test_fused_consumer_equals_the_materialised_relation(features, periodic):
         want = Weighted()(graph=stored, src={"x": x2}, dst={}, edge={"w": distance})
         want_dp, want_dx = torch.autograd.grad(want, (p2, x2), dy)
         torch.testing.assert_close(dp, want_dp, rtol=2e-4, atol=2e-5)
+        # the bit-for-bit statement needs the distances in the kernels' own rounding (Torch's norm on
+        # the device may differ by an ulp): the relation's implicit field
+        own = graph.implicit_edge_fields(row_ptr, col)["distance"]
+        want = Weighted()(graph=stored, src={"x": x}, dst={}, edge={"w": own})
     else:
         want = NeighborSum()(graph=stored, src={"x": x2}, dst={})
         (want_dx,) = torch.autograd.grad(want, (x2,), dy)

@@ -111,3 +111,51 @@ def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable(oracle):
     assert_gemm_close(out.cpu().numpy(), a.numpy(), w.numpy(), oracle.linear(a.numpy(), w.numpy()))
     assert _native.lib().tgb_selftest_bounded_wait(word.data_ptr(), ctypes.c_uint32(0), fell_through.data_ptr(),
                                                    0) == _native.INVALID_ARGUMENT
+
+
+def test_matmul_written_in_node_runs_on_the_tensor_core_kernels(oracle):
+    """`aggregate @ W` inside node() (the reference's GCN example) launches this library's linear
+    kernels, forward and backward, not a library GEMM; other shapes fall through to Torch."""
+    import tiga as tg
+    from baseline import synthetic as syn
+    from tiga import _native
+
+    class Layer(tg.MessagePassing):
+        reducer = tg.sum()
+
+        def edge(self, src, dst, edge):
+            return edge.weight * src.x
+
+        def node(self, dst, aggregate, W):
+            return aggregate @ W
+
+    row_ptr, col = syn.rmat_csr(10, 8, seed=3)
+    n = row_ptr.numel() - 1
+    gen = torch.Generator().manual_seed(0)
+    x = torch.randn(n, 64, generator=gen).cuda().requires_grad_()
+    w = torch.rand(col.numel(), generator=gen).cuda()
+    W = (torch.randn(64, 128, generator=gen) / 8).cuda().requires_grad_()
+    graph = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=n)
+    layer = Layer()
+    layer(graph=graph, src={"x": x}, dst={}, edge={"weight": w}, W=W)          # specialise
+    before = _native.launch_count()
+    out = layer(graph=graph, src={"x": x}, dst={}, edge={"weight": w}, W=W)
+    forward_launches = _native.launch_count() - before
+    assert type(out) is torch.Tensor and out.shape == (n, 128)
+    assert forward_launches >= 2                      # the gather and the linear are both this library's
+    agg = oracle.wsum_fwd(row_ptr.numpy(), col.numpy(), x.detach().cpu().numpy(), w.cpu().numpy())
+    want = oracle.linear(agg, W.detach().cpu().numpy())
+    np.testing.assert_allclose(out.detach().cpu().numpy(), want, rtol=2e-5, atol=2e-5 * np.abs(want).max())
+    before = _native.launch_count()
+    dx, dW = torch.autograd.grad(out, (x, W), torch.ones_like(out))
+    assert _native.launch_count() - before >= 4       # d(aggregate), dW (+ its partial sum), dx gather
+    ref_x, ref_W = x.detach().clone().requires_grad_(), W.detach().clone().requires_grad_()
+    ref = Layer().reference(graph=graph, src={"x": ref_x}, dst={}, edge={"weight": w}, W=ref_W)
+    want_dx, want_dW = torch.autograd.grad(ref, (ref_x, ref_W), torch.ones_like(ref))
+    torch.testing.assert_close(dx, want_dx, rtol=1e-4, atol=1e-4 * float(want_dx.abs().max()))
+    torch.testing.assert_close(dW, want_dW, rtol=1e-4, atol=1e-4 * float(want_dW.abs().max()))
+    # a width the kernels do not take: plain Torch, same answer as Torch
+    W3 = torch.randn(64, 3, device="cuda")
+    out3 = layer(graph=graph, src={"x": x}, dst={}, edge={"weight": w}, W=W3)
+    torch.testing.assert_close(out3, layer.reference(graph=graph, src={"x": x}, dst={}, edge={"weight": w}, W=W3),
+                               rtol=1e-4, atol=1e-4)

@@ -13,6 +13,7 @@ from .distributed import ByDestination, DeviceMesh, GraphPlacement, HaloMap, der
 from .graph import Graph, GraphSchema
 from .kernel import AnalysisFinding, CompiledVariant, Kernel
 from .message_passing import MessagePassing
+from .ops import linear
 from .storage import load, save
 from .reducer import (MaxReducer, MeanReducer, OnlineSoftmaxItem, OnlineSoftmaxReducer, ProductReducer, Reducer,
                       ReducerCall, SumReducer, max, mean, online_softmax, prod, sum)
@@ -23,5 +24,5 @@ __all__ = [
     "AnalysisFinding", "ByDestination", "CompiledVariant", "DeviceMesh", "Graph", "GraphPlacement",
     "GraphSchema", "HaloMap", "Kernel", "MaxReducer", "MeanReducer", "MessagePassing", "OnlineSoftmaxItem",
     "OnlineSoftmaxReducer", "ProductReducer", "Reducer", "ReducerCall", "SumReducer", "derive_halo_map",
-    "GraphProgram", "ProgramValue", "codegen", "control", "load", "program", "repeat", "math", "max", "mean", "online_softmax", "prod", "save", "sum",
+    "GraphProgram", "ProgramValue", "codegen", "control", "linear", "load", "program", "repeat", "math", "max", "mean", "online_softmax", "prod", "save", "sum",
 ]

@@ -128,11 +128,12 @@ class CellDirectory:
             col = torch.empty(edges, dtype=torch.int64, device=device)
             distance = torch.empty(edges, dtype=torch.float32, device=device) if with_fields else None
             displacement = torch.empty((edges, dims), dtype=torch.float32, device=device) if with_fields else None
-            _native.check(lib.tgb_radius_fill(
-                self.positions.data_ptr(), n, ctypes.byref(self.space.struct), self.buffer.data_ptr(),
-                float(cutoff), int(bool(exclude_self)), row_ptr.data_ptr(), col.data_ptr(),
-                0 if distance is None else distance.data_ptr(),
-                0 if displacement is None else displacement.data_ptr(), _stream(device)), "tgb_radius_fill")
+            if edges > 0:
+                _native.check(lib.tgb_radius_fill(
+                    self.positions.data_ptr(), n, ctypes.byref(self.space.struct), self.buffer.data_ptr(),
+                    float(cutoff), int(bool(exclude_self)), row_ptr.data_ptr(), col.data_ptr(),
+                    0 if distance is None else distance.data_ptr(),
+                    0 if displacement is None else displacement.data_ptr(), _stream(device)), "tgb_radius_fill")
         return row_ptr, col, distance, displacement, candidate_pairs
 
     # -- fused consumer ----------------------------------------------------------------------------

@@ -208,7 +208,9 @@ class MessagePassing(Kernel):
             aggregate = self._cold(graph, src, dst, edge, params)
         if type(self).node is MessagePassing.node:
             return aggregate
-        return cap.call_region(self.node, (SimpleNamespace(**dst), aggregate), params)
+        from .ops import as_aggregate      # `aggregate @ W` inside node() reaches the tensor-core linear
+
+        return cap.call_region(self.node, (SimpleNamespace(**dst), as_aggregate(aggregate)), params)
 
     def _execute_paged(self, graph, src, dst, edge, params):
         """A graph whose topology lives in a .gfg directory: blocks of `graph.page_rows` destination

@@ -332,6 +332,43 @@ def dense_linear(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return DenseLinearFunction.apply(a, weight)
 
 
+def linear(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``a @ weight``: the tensor-core kernels when the shapes are theirs (float32 CUDA, K and N in
+    {64, 128}), Torch's matmul otherwise."""
+    if isinstance(a, torch.Tensor) and isinstance(weight, torch.Tensor) and linear_supported(a, weight):
+        return DenseLinearFunction.apply(a, weight)
+    return torch.matmul(a, weight)
+
+
+_MATMULS = (torch.matmul, torch.mm, torch.Tensor.matmul, torch.Tensor.mm, torch.Tensor.__matmul__)
+
+
+class AggregateTensor(torch.Tensor):
+    """What ``node(dst, aggregate)`` receives: an ordinary tensor whose ``aggregate @ W`` (the GCN
+    layer's linear, written by the user the way the reference's examples write it) runs on the
+    tcgen05 linear kernels when the shapes are theirs.  Every other operation behaves as on a plain
+    tensor and returns plain tensors."""
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        with torch._C.DisableTorchFunctionSubclass():
+            if func in _MATMULS and len(args) == 2 and not kwargs and isinstance(args[0], AggregateTensor) \
+                    and isinstance(args[1], torch.Tensor):
+                left = args[0].as_subclass(torch.Tensor)
+                right = args[1].as_subclass(torch.Tensor)
+                if linear_supported(left, right):
+                    return DenseLinearFunction.apply(left, right)
+            result = func(*args, **kwargs)
+        if isinstance(result, AggregateTensor):
+            return result.as_subclass(torch.Tensor)
+        return result
+
+
+def as_aggregate(tensor: torch.Tensor) -> torch.Tensor:
+    return tensor.as_subclass(AggregateTensor) if tensor.is_cuda and tensor.dtype == torch.float32 else tensor
+
+
 # --------------------------------------------------------------------------- halo row movers
 def rows_gather(rows: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     """packed[i] = rows[ids[i]] for float32 rows and int64 ids."""
