@@ -398,6 +398,13 @@ def _dynamic_relation(args, device, bench, kind):
         result["cpu_oracle_s_per_snapshot"] = round(cpu_seconds / 2, 3)
         result["reference_published_ms"] = {"tiga": 1.84, "pyg": 80.24, "hardware": "the reference's own GPU"}
     else:
+        def search_only():
+            positions.copy_(snapshots[state["calls"] & 1])
+            state["calls"] += 1
+            return tg.Graph.knn(positions, k).resolve_csr()
+
+        search_ms, _ = bench.timed(search_only, steps, 3, device.index or 0)
+        result["search_only_ms"] = round(search_ms, 4)
         pairs = float(n) * n
         result["pair_distances_per_s"] = round(pairs / (ms * 1e-3) / 1e12, 3)
         result["pair_unit"] = "T pairs/s"

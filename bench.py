@@ -590,7 +590,12 @@ def run_e2e(args, step, x, weight, linears, traversed, world):
     region covers every copy.  Device input buffers are double buffered while they fit."""
     device = x.device
     host_in = [t.detach().cpu().pin_memory() for t in (x, weight, *linears)]
-    slots = 2 if sum(t.numel() * 4 for t in host_in) < 8e9 else 1
+    # a second set of device input buffers lets step i + 1 upload while step i computes; it is used
+    # whenever it fits beside the step's own working set with 16 GB to spare
+    torch.cuda.empty_cache()
+    input_bytes = sum(t.numel() * t.element_size() for t in host_in)
+    free_bytes, _ = torch.cuda.mem_get_info(device)
+    slots = 2 if free_bytes - 2 * input_bytes > 16e9 else 1
     packed = sum(m.numel() for m in linears)
     host_out = [[torch.empty_like(host_in[0]).pin_memory(), torch.empty_like(host_in[1]).pin_memory(),
                  torch.empty(packed, dtype=torch.float32).pin_memory()] for _ in range(slots)]

@@ -495,6 +495,21 @@ TGB_API int32_t tgb_knn(const void *queries, int64_t nq, const void *candidates,
                         int64_t nc, int32_t dims, int32_t k, int32_t exclude_self,
                         void *col, void *dist_sq, uint64_t stream);
 
+/* The same selection as tgb_knn through a cell directory built over the
+ * CANDIDATES (tgb_cell_directory_build, open boundary, dims <= 3): every query
+ * walks the shells of cells around its own cell and stops once its k-th
+ * distance is strictly below the distance to the boundary of the cells it has
+ * covered, less `margin` (an absolute bound on the rounding of a coordinate:
+ * a few ulps of the largest |coordinate|); queries not settled within six
+ * shells are finished by a scan over all candidates, so the result is exact
+ * and identical to tgb_knn for every input.  `unsettled`: int32[nq] scratch.
+ * self_search != 0: the queries are the candidates themselves (nq == nc). */
+TGB_API int32_t tgb_knn_grid(const void *queries, int64_t nq, const void *candidates,
+                             int64_t nc, const tgb_cell_space *space,
+                             const void *directory, int32_t k, int32_t exclude_self,
+                             int32_t self_search, float margin, void *col,
+                             void *dist_sq, void *unsettled, uint64_t stream);
+
 /* Implicit edge fields of a stored relation: displacement[e, :] =
  * src_positions[col[e], :] - dst_positions[row of e, :] (minimum image when
  * `space` is periodic; only dims, periodic, lattice and inverse are read, dims

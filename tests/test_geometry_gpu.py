@@ -206,9 +206,13 @@ def test_positions_changed_in_place_rebuild_without_respecialising():
     distances = torch.cdist(q, q, compute_mode="donot_use_mm_for_euclid_dist")
     torch.testing.assert_close(third, (distances * (distances <= 0.25)).sum(-1), atol=2e-5, rtol=2e-5)
     assert kernel.cache_info["misses"] == 1 and kernel.cache_info["hits"] >= 2
-    # another cutoff is another signature
-    kernel(graph=tg.Graph.radius(q, 0.3), src={"x": x}, dst={})
-    assert kernel.cache_info["misses"] == 2
+    # the cutoff is a runtime scalar: another value reuses the launch and is honoured
+    wider = kernel(graph=tg.Graph.radius(q, 0.3), src={"x": x}, dst={})
+    torch.testing.assert_close(wider, (distances * (distances <= 0.3)).sum(-1), atol=2e-5, rtol=2e-5)
+    assert kernel.cache_info["misses"] == 1
+    # a different search (self pairs kept) is another signature
+    kernel(graph=tg.Graph.radius(q, 0.3, exclude_self=False), src={"x": x}, dst={})
+    assert kernel.cache_info["misses"] == 1 and len(kernel._launches) == 2
 
 
 def test_other_reducers_and_select_run_over_the_built_csr(geo):
@@ -247,7 +251,7 @@ def test_knn_matches_reference_fixtures(geo, oracle):
         k = int(geo[key + "_k"])
         graph = tg.Graph.knn(pos, k, **kwargs)
         row_ptr, col = graph.resolve_csr()
-        assert graph.build_info["builder"] == "b200-exact-knn-tiled-scan"
+        assert graph.build_info["builder"].startswith("b200-exact-knn-")
         np.testing.assert_array_equal(row_ptr.cpu().numpy(), geo[key + "_row_ptr"])
         candidates = geo[key + "_pos"] if self_search else geo[key + "_candidates"]
         want = oracle.knn_build(geo[key + "_pos"], candidates, k, exclude_self=self_search and "keep" not in key)
@@ -258,6 +262,36 @@ def test_knn_matches_reference_fixtures(geo, oracle):
         x = torch.from_numpy(geo[key + "_x"]).cuda()
         out = NeighborSum()(graph=graph, src={"x": x}, dst={})
         np.testing.assert_allclose(out.cpu().numpy(), geo[key + "_out"], rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("search", ("scan", "shells"))
+def test_knn_searches_agree_on_hard_inputs(oracle, monkeypatch, search):
+    """The shell search over the cell directory and the scan over all candidates are both exact:
+    fixtures with few points, duplicated points, a dense cluster beside far outliers (unsettled
+    queries finish by the scan), collinear points, bipartite queries outside the candidates' box."""
+    from tiga import geometry
+
+    monkeypatch.setattr(geometry, "KNN_GRID_MIN_CANDIDATES", 1 if search == "shells" else 1 << 60)
+    gen = torch.Generator().manual_seed(77)
+    cluster = torch.rand(3000, 3, generator=gen) * 0.05
+    outliers = torch.rand(40, 3, generator=gen) * 500.0 - 250.0
+    duplicated = torch.rand(500, 3, generator=gen).repeat(2, 1)
+    line = torch.cat((torch.rand(2000, 1, generator=gen), torch.zeros(2000, 2)), dim=1)
+    cases = {"cluster+outliers": torch.cat((cluster, outliers))[torch.randperm(3040, generator=gen)],
+             "duplicates": duplicated, "line": line, "grid": (torch.rand(4000, 2, generator=gen) * 16).floor() / 16}
+    for name, points in cases.items():
+        for k in (1, 7, 32):
+            graph = tg.Graph.knn(points.cuda(), k)
+            col = graph.resolve_csr()[1].cpu().numpy().reshape(-1, k)
+            want = oracle.knn_build(points.numpy(), points.numpy(), k, exclude_self=True)
+            np.testing.assert_array_equal(col, want, err_msg=f"{name} k={k} {search}")
+            expected = "b200-exact-knn-cell-shells" if search == "shells" else "b200-exact-knn-tiled-scan"
+            assert graph.build_info["builder"] == expected
+    queries = torch.rand(300, 3, generator=gen) * 3.0 - 1.0          # partly outside the unit cube
+    candidates = torch.rand(5000, 3, generator=gen)
+    graph = tg.Graph.knn(queries.cuda(), 9, candidates=candidates.cuda())
+    want = oracle.knn_build(queries.numpy(), candidates.numpy(), 9, exclude_self=False)
+    np.testing.assert_array_equal(graph.resolve_csr()[1].cpu().numpy().reshape(-1, 9), want)
 
 
 @pytest.mark.parametrize("k", (1, 13, 16, 63, 128))

@@ -17,8 +17,6 @@
 // Summation order inside a row is the edge order and the product is rounded
 // before the add, i.e. the sequential CPU definition of the reference
 // (lib/Transforms/LowerTensorToCPU.cpp:672-702) for every unsplit row.
-#include <cstdlib>
-
 #include "tgb_common.cuh"
 
 namespace tgb {
@@ -46,11 +44,6 @@ namespace {
 #endif
 #ifndef TGB_PREFETCH_DOT
 #define TGB_PREFETCH_DOT 0
-#endif
-
-// Ring depth of the shared-memory gather path (0: register path).
-#ifndef TGB_RING_DEPTH
-#define TGB_RING_DEPTH 0
 #endif
 
 constexpr int kBlock = TGB_BLOCK;
@@ -248,121 +241,6 @@ k_gather_vec(const GatherArgs a) {
   }
 }
 
-// ---------------------------------------------------------------------------
-// Ring path of the vector gather (sum / mean): the gathered rows do not pass through registers on
-// their way in.  Every lane owns a private ring of S slots in shared memory and keeps S edges of
-// its row in flight with cp.async: the bytes in flight per SM are bounded by shared memory (about
-// 150 KB) instead of by registers x resident warps (64 KB with the register path), which is what
-// an L2-resident gather needs to keep the L2 busy.  The neighbour ids, the weights and (edge-mapped
-// plans) the edge ids travel through rings of their own, two and three ring lengths ahead, so that
-// no copy ever waits on an index load after the row's start-up.  Timeline of iteration t (edge
-// positions relative to the row's first edge; one commit group per iteration, groups up to t - S
-// are complete after the wait):
-//     read   rows(t), w(t)            -> registers
-//     read   idx(t + S), eid(t + 2S)
-//     issue  eid(t + 3S), idx(t + 2S), w(t + 2S), rows(t + S)
-//     fold   rows(t) * w(t) into the accumulators (edge order: same bits as the register path)
-// Rings are lane-private: no barrier, no cross-lane visibility question.
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ void cp_async_16(void *smem, const void *gmem) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)),
-               "l"(gmem));
-}
-__device__ __forceinline__ void cp_async_4(void *smem, const void *gmem) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)),
-               "l"(gmem));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
-}
-
-template <int VPL, int S, bool W_BY_EID>
-constexpr int ring_bytes_per_thread() {
-  return S * VPL * 16 + S * 4 + 2 * S * 4 + (W_BY_EID ? S * 4 : 0);
-}
-
-template <typename IdxT, int G, int VPL, int S, bool HAS_W, bool W_BY_EID>
-__global__ void __launch_bounds__(kBlock)
-k_gather_ring(const GatherArgs a) {
-  extern __shared__ __align__(16) unsigned char ring_smem[];
-  float4 *rows = reinterpret_cast<float4 *>(ring_smem);                  // [S][VPL][kBlock]
-  uint32_t *idx_ring = reinterpret_cast<uint32_t *>(rows + S * VPL * kBlock);   // [S][kBlock]
-  float *w_ring = reinterpret_cast<float *>(idx_ring + S * kBlock);      // [2S][kBlock]
-  uint32_t *eid_ring = reinterpret_cast<uint32_t *>(w_ring + 2 * S * kBlock);   // [S][kBlock], edge-mapped plans
-  const int tid = threadIdx.x;
-  const int lane = tid & (G - 1);
-  const int64_t gid = ((int64_t)blockIdx.x * kBlock + tid) / G;
-  if (gid >= a.n_seg + (a.n_rows - a.n_long)) return;
-  int64_t row, beg, end, seg;
-  load_work_item(a.items, a.n_seg, gid, row, beg, end, seg);
-  const int64_t F = a.F;
-  const float start = (seg >= 0 || a.mean) ? 0.0f : a.identity;
-  if (a.accumulate && beg == end) return;
-  float4 acc[VPL];
-#pragma unroll
-  for (int v = 0; v < VPL; ++v) {
-    acc[v] = make_float4(start, start, start, start);
-    if (a.accumulate && seg < 0) acc[v] = *reinterpret_cast<const float4 *>(a.out + row * F + 4 * (lane + v * G));
-  }
-  // the low word of an index is the index (fewer than 2^31 rows; little endian)
-  const char *idx_bytes = static_cast<const char *>(a.idx);
-  const int n = (int)(end - beg);
-  constexpr int kLead = (W_BY_EID ? 3 : 2) * S;
-  for (int t = -kLead; t < n; ++t) {
-    cp_async_wait<S - 1>();
-    float4 val[VPL];
-    float wt = 1.0f;
-    if (t >= 0) {
-#pragma unroll
-      for (int v = 0; v < VPL; ++v) val[v] = rows[((t % S) * VPL + v) * kBlock + tid];
-      if (HAS_W) wt = w_ring[(t % (2 * S)) * kBlock + tid];
-    }
-    const int p_rows = t + S, p_w = t + 2 * S, p_eid = t + 3 * S;
-    if (p_rows >= 0 && p_rows < n) {
-      const int64_t cc = (int64_t)idx_ring[(p_rows % S) * kBlock + tid];
-      const float *xr = a.x + cc * F;
-#pragma unroll
-      for (int v = 0; v < VPL; ++v)
-        cp_async_16(&rows[((p_rows % S) * VPL + v) * kBlock + tid], xr + 4 * (lane + v * G));
-    }
-    if (p_w >= 0 && p_w < n) {
-      cp_async_4(&idx_ring[(p_w % S) * kBlock + tid], idx_bytes + (beg + p_w) * (int64_t)sizeof(IdxT));
-      if (HAS_W) {
-        const float *ws = W_BY_EID ? a.w + eid_ring[(p_w % S) * kBlock + tid] : a.w + beg + p_w;
-        cp_async_4(&w_ring[(p_w % (2 * S)) * kBlock + tid], ws);
-      }
-    }
-    if (W_BY_EID && p_eid >= 0 && p_eid < n)
-      cp_async_4(&eid_ring[(p_eid % S) * kBlock + tid], a.eid + beg + p_eid);
-    cp_async_commit();
-    if (t >= 0) {
-#pragma unroll
-      for (int v = 0; v < VPL; ++v) {
-        float4 m = val[v];
-        if (HAS_W) {
-          m.x = __fmul_rn(wt, m.x); m.y = __fmul_rn(wt, m.y);
-          m.z = __fmul_rn(wt, m.z); m.w = __fmul_rn(wt, m.w);
-        }
-        acc[v].x = __fadd_rn(acc[v].x, m.x); acc[v].y = __fadd_rn(acc[v].y, m.y);
-        acc[v].z = __fadd_rn(acc[v].z, m.z); acc[v].w = __fadd_rn(acc[v].w, m.w);
-      }
-    }
-  }
-  if (seg < 0 && a.mean) {
-    const float count = (float)n;
-#pragma unroll
-    for (int v = 0; v < VPL; ++v) {
-      acc[v].x = __fdiv_rn(acc[v].x, count); acc[v].y = __fdiv_rn(acc[v].y, count);
-      acc[v].z = __fdiv_rn(acc[v].z, count); acc[v].w = __fdiv_rn(acc[v].w, count);
-    }
-  }
-  float *dst = seg >= 0 ? a.partial + seg * F : a.out + row * F;
-#pragma unroll
-  for (int v = 0; v < VPL; ++v) st_stream_f4(dst + 4 * (lane + v * G), acc[v]);
-}
-
 // Scalar path: any F, no alignment requirement.  A group of G lanes strides
 // over the F elements of the row.
 template <typename PtrT, typename IdxT, int G, int MODE, bool HAS_W,
@@ -543,72 +421,6 @@ k_edge_dot_vec(const GatherArgs a, const float *dy, float *dw) {
   }
 }
 
-// Ring path of the per-edge dot product: same lane-private cp.async rings as k_gather_ring (rows S
-// ahead, neighbour ids 2S ahead, mapped edge ids with the ids); the row's cotangent stays in
-// registers, a group reduces each edge's partial products by shuffles and stores G results at once.
-template <typename IdxT, int G, int VPL, int S>
-__global__ void __launch_bounds__(kBlock)
-k_edge_dot_ring(const GatherArgs a, const float *__restrict__ dy, float *__restrict__ dw) {
-  extern __shared__ __align__(16) unsigned char ring_smem[];
-  float4 *rows = reinterpret_cast<float4 *>(ring_smem);                          // [S][VPL][kBlock]
-  uint32_t *idx_ring = reinterpret_cast<uint32_t *>(rows + S * VPL * kBlock);     // [S][kBlock]
-  uint32_t *eid_ring = idx_ring + S * kBlock;                                     // [2S][kBlock]
-  const int tid = threadIdx.x;
-  const int lane = tid & (G - 1);
-  const int64_t gid = ((int64_t)blockIdx.x * kBlock + tid) / G;
-  if (gid >= a.n_seg + (a.n_rows - a.n_long)) return;
-  const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << ((tid & 31) & ~(G - 1)));
-  int64_t row, beg, end, seg;
-  load_work_item(a.items, a.n_seg, gid, row, beg, end, seg);
-  const int64_t F = a.F;
-  float4 g[VPL];
-#pragma unroll
-  for (int v = 0; v < VPL; ++v) g[v] = ldg_f4(dy + row * F + 4 * (lane + v * G));
-  const char *idx_bytes = static_cast<const char *>(a.idx);
-  const bool mapped = a.eid != nullptr;
-  const int n = (int)(end - beg);
-  float mine = 0.0f;
-  uint32_t my_slot = 0;
-  for (int t = -2 * S; t < n; ++t) {
-    cp_async_wait<S - 1>();
-    float4 val[VPL];
-    if (t >= 0) {
-#pragma unroll
-      for (int v = 0; v < VPL; ++v) val[v] = rows[((t % S) * VPL + v) * kBlock + tid];
-    }
-    const int p_rows = t + S, p_idx = t + 2 * S;
-    if (p_rows >= 0 && p_rows < n) {
-      const float *xr = a.x + (int64_t)idx_ring[(p_rows % S) * kBlock + tid] * F;
-#pragma unroll
-      for (int v = 0; v < VPL; ++v)
-        cp_async_16(&rows[((p_rows % S) * VPL + v) * kBlock + tid], xr + 4 * (lane + v * G));
-    }
-    if (p_idx >= 0 && p_idx < n) {
-      cp_async_4(&idx_ring[(p_idx % S) * kBlock + tid], idx_bytes + (beg + p_idx) * (int64_t)sizeof(IdxT));
-      if (mapped) cp_async_4(&eid_ring[(p_idx % (2 * S)) * kBlock + tid], a.eid + beg + p_idx);
-    }
-    cp_async_commit();
-    if (t >= 0) {
-      float p = 0.0f;
-#pragma unroll
-      for (int v = 0; v < VPL; ++v) {
-        p = fmaf(g[v].x, val[v].x, p); p = fmaf(g[v].y, val[v].y, p);
-        p = fmaf(g[v].z, val[v].z, p); p = fmaf(g[v].w, val[v].w, p);
-      }
-#pragma unroll
-      for (int o = G >> 1; o; o >>= 1) p += __shfl_xor_sync(gmask, p, o, G);
-      const int k = t % G;
-      if (lane == k) {
-        mine = p;
-        my_slot = mapped ? eid_ring[(t % (2 * S)) * kBlock + tid] : 0u;
-      }
-      if (k == G - 1 || t == n - 1) {
-        if (lane <= k) dw[mapped ? (int64_t)my_slot : beg + (t - k) + lane] = mine;
-      }
-    }
-  }
-}
-
 template <typename PtrT, typename IdxT, bool ARG_FILTER>
 __global__ void __launch_bounds__(kBlock)
 k_edge_dot_scalar(const GatherArgs a, const float *dy, float *dw) {
@@ -690,71 +502,12 @@ Shape pick_shape(int64_t F, const void *x, const void *out, bool dot = false) {
   return s;
 }
 
-// Ring depth of the gather (edges in flight per lane); 0 selects the register path.
-// TGB_GATHER_RING in the environment overrides the default, for sweeps.
-int ring_depth() {
-  static const int depth = [] {
-    const char *text = getenv("TGB_GATHER_RING");
-    return text ? atoi(text) : TGB_RING_DEPTH;
-  }();
-  return depth;
-}
-
-template <typename IdxT, int G, int VPL, int S, bool HAS_W, bool W_BY_EID>
-int32_t launch_ring(const GatherArgs &a, unsigned blocks, cudaStream_t stream) {
-  constexpr int bytes = ring_bytes_per_thread<VPL, S, W_BY_EID>() * kBlock;
-  auto kernel = k_gather_ring<IdxT, G, VPL, S, HAS_W, W_BY_EID>;
-  if (bytes > 48 * 1024)
-    TGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  kernel<<<blocks, kBlock, bytes, stream>>>(a);
-  TGB_LAUNCHED();
-  return TGB_STATUS_OK;
-}
-
-template <typename IdxT, int G, int VPL, int S>
-int32_t launch_dot_ring(const GatherArgs &a, const float *dy, float *dw, unsigned blocks, cudaStream_t stream) {
-  constexpr int bytes = (S * VPL * 16 + S * 4 + 2 * S * 4) * kBlock;
-  auto kernel = k_edge_dot_ring<IdxT, G, VPL, S>;
-  if (bytes > 48 * 1024)
-    TGB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  kernel<<<blocks, kBlock, bytes, stream>>>(a, dy, dw);
-  TGB_LAUNCHED();
-  return TGB_STATUS_OK;
-}
-
 template <typename PtrT, typename IdxT, int MODE, bool HAS_W, bool W_BY_EID,
           bool ARG_FILTER>
 int32_t launch_gather(const GatherArgs &a, const Shape &s, cudaStream_t stream) {
   const int64_t groups = a.n_seg + (a.n_rows - a.n_long);
   if (groups <= 0) return TGB_STATUS_OK;
   const unsigned blocks = blocks_for_groups(groups, s.G);
-  if constexpr (MODE == kSum && !ARG_FILTER) {
-    const int depth = ring_depth();
-    if (depth > 0 && s.vec && (int64_t)s.G * s.VPL * 4 == a.F && (s.VPL == 4 || s.VPL == 2)) {
-      int32_t rc = TGB_STATUS_UNSUPPORTED;
-#define TGB_RING(GG, VV)                                                                       \
-  rc = depth >= 8   ? launch_ring<IdxT, GG, VV, 8, HAS_W, W_BY_EID>(a, blocks, stream)          \
-       : depth >= 6 ? launch_ring<IdxT, GG, VV, 6, HAS_W, W_BY_EID>(a, blocks, stream)          \
-                    : launch_ring<IdxT, GG, VV, 4, HAS_W, W_BY_EID>(a, blocks, stream)
-      switch (s.G * 10 + s.VPL) {
-        case 42: TGB_RING(4, 2); break;
-        case 44: TGB_RING(4, 4); break;
-        case 84: TGB_RING(8, 4); break;
-        case 164: TGB_RING(16, 4); break;
-        case 324: TGB_RING(32, 4); break;
-        default: break;
-      }
-#undef TGB_RING
-      if (rc != TGB_STATUS_UNSUPPORTED) {
-        if (rc != TGB_STATUS_OK) return rc;
-        if (a.n_long > 0) {
-          k_finalize_split<PtrT, MODE><<<(unsigned)a.n_long, kBlock, 0, stream>>>(a);
-          TGB_LAUNCHED();
-        }
-        return TGB_STATUS_OK;
-      }
-    }
-  }
 #define TGB_VEC(GG, VV, UU)                                                    \
   k_gather_vec<PtrT, IdxT, GG, VV, UU, MODE, HAS_W, W_BY_EID, ARG_FILTER>     \
       <<<blocks, kBlock, 0, stream>>>(a)
@@ -802,27 +555,6 @@ int32_t launch_edge_dot(const GatherArgs &a, const Shape &s, const float *dy,
                         float *dw, cudaStream_t stream) {
   const int64_t groups = a.n_seg + (a.n_rows - a.n_long);
   if (groups <= 0) return TGB_STATUS_OK;
-  if constexpr (!ARG_FILTER) {
-    const int depth = ring_depth();
-    if (depth > 0 && s.vec && (int64_t)s.G * s.VPL * 4 == a.F) {
-      int32_t rc = TGB_STATUS_UNSUPPORTED;
-#define TGB_DOT_RING(GG, VV)                                                                        \
-  rc = depth >= 8   ? launch_dot_ring<IdxT, GG, VV, 8>(a, dy, dw, blocks_for_groups(groups, GG), stream) \
-       : depth >= 6 ? launch_dot_ring<IdxT, GG, VV, 6>(a, dy, dw, blocks_for_groups(groups, GG), stream) \
-                    : launch_dot_ring<IdxT, GG, VV, 4>(a, dy, dw, blocks_for_groups(groups, GG), stream)
-      switch (s.G * 10 + s.VPL) {
-        case 42: TGB_DOT_RING(4, 2); break;
-        case 82: TGB_DOT_RING(8, 2); break;
-        case 84: TGB_DOT_RING(8, 4); break;
-        case 164: TGB_DOT_RING(16, 4); break;
-        case 322: TGB_DOT_RING(32, 2); break;
-        case 324: TGB_DOT_RING(32, 4); break;
-        default: break;
-      }
-#undef TGB_DOT_RING
-      if (rc != TGB_STATUS_UNSUPPORTED) return rc;
-    }
-  }
 #define TGB_DOT(GG, VV, UU)                                                    \
   k_edge_dot_vec<PtrT, IdxT, GG, VV, UU, ARG_FILTER>                          \
       <<<blocks_for_groups(groups, GG), kBlock, 0, stream>>>(a, dy, dw)

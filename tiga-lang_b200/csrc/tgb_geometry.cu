@@ -556,6 +556,154 @@ k_knn_wide(const float *__restrict__ queries, int64_t nq, const float *__restric
   }
 }
 
+// ---- exact k nearest neighbours over the cell directory ---------------------------------------
+// One thread per query walks the shells of cells around the query's cell (Chebyshev radius 0, 1,
+// 2, ...), inserting candidates by the (squared distance, index) key, and stops as soon as its k-th
+// best distance is strictly smaller than the distance to the boundary of the block of cells it has
+// covered (minus a rounding margin): no closer candidate can lie outside.  With the cell edge chosen
+// for about k points per ball of that radius, two shells (27 cells) settle almost every query, so the
+// search costs O(k) distance evaluations per query instead of the number of candidates.  A query that
+// is not settled within kKnnMaxShells shells is flagged and finished by the brute-force scan below
+// (k_knn_flagged), so the result is exact for every input.
+constexpr int kKnnMaxShells = 6;
+
+__device__ __forceinline__ void knn_insert_keyed(float *best_d, int32_t *best_j, int k, float d, int32_t j) {
+  // ascending by (d, j); candidates arrive in any order
+  int at = k - 1;
+  while (at > 0) {
+    const float pd = best_d[(at - 1) * kKnnThreads];
+    const int32_t pj = best_j[(at - 1) * kKnnThreads];
+    if (pd < d || (pd == d && pj < j && pj >= 0)) break;
+    best_d[at * kKnnThreads] = pd;
+    best_j[at * kKnnThreads] = pj;
+    --at;
+  }
+  best_d[at * kKnnThreads] = d;
+  best_j[at * kKnnThreads] = j;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kKnnThreads)
+k_knn_grid(const float *__restrict__ queries, int64_t nq, Space sp, Directory dir, int k, int exclude_self,
+           int self_order, float margin, int64_t *__restrict__ col, float *__restrict__ dist_sq,
+           int32_t *__restrict__ unsettled) {
+  extern __shared__ __align__(16) unsigned char knn_smem[];
+  float *best_d = reinterpret_cast<float *>(knn_smem) + threadIdx.x;
+  int32_t *best_j = reinterpret_cast<int32_t *>(knn_smem + (size_t)k * kKnnThreads * 4) + threadIdx.x;
+  const int64_t s = (int64_t)blockIdx.x * kKnnThreads + threadIdx.x;
+  if (s >= nq) return;
+  // a self search takes its queries in directory order: the threads of a warp share cells
+  const int64_t i = self_order ? destination_of(dir, s) : s;
+  float q[3];
+  int cell[3];
+  load_point<D>(queries, i, q);
+  cell_of<D>(q, sp, cell);
+  for (int r = 0; r < k; ++r) {
+    best_d[r * kKnnThreads] = __int_as_float(0x7f800000);
+    best_j[r * kKnnThreads] = -1;
+  }
+  float worst = __int_as_float(0x7f800000);
+  int32_t worst_j = -1;
+  const int64_t self = exclude_self ? i : -1;
+  bool settled = false;
+  for (int shell = 0; shell <= kKnnMaxShells && !settled; ++shell) {
+    const int lo1 = D > 1 ? -shell : 0, hi1 = D > 1 ? shell : 0;
+    const int lo2 = D > 2 ? -shell : 0, hi2 = D > 2 ? shell : 0;
+    for (int o0 = -shell; o0 <= shell; ++o0)
+      for (int o1 = lo1; o1 <= hi1; ++o1)
+        for (int o2 = lo2; o2 <= hi2; ++o2) {
+          const int reach = max(abs(o0), max(abs(o1), abs(o2)));
+          if (reach != shell) continue;             // interior cells were covered by earlier shells
+          const int target[3] = {cell[0] + o0, cell[1] + o1, cell[2] + o2};
+          const uint32_t bucket = bucket_of<D>(target, sp.bits);
+          const int begin = __ldg(dir.bucket_ptr + bucket), end = __ldg(dir.bucket_ptr + bucket + 1);
+          for (int e = begin; e < end; ++e) {
+            const int4 c = __ldg(dir.cells + e);
+            if (c.x != target[0] || (D > 1 && c.y != target[1]) || (D > 2 && c.z != target[2])) continue;
+            const float4 p = __ldg(dir.points + e);
+            const int32_t j = (int32_t)__float_as_uint(p.w);
+            const float d0 = __fsub_rn(p.x, q[0]);
+            float acc = __fmul_rn(d0, d0);
+            if (D > 1) {
+              const float d1 = __fsub_rn(p.y, q[1]);
+              acc = __fmaf_rn(d1, d1, acc);
+            }
+            if (D > 2) {
+              const float d2 = __fsub_rn(p.z, q[2]);
+              acc = __fmaf_rn(d2, d2, acc);
+            }
+            if ((acc < worst || (acc == worst && j < worst_j)) && (int64_t)j != self) {
+              knn_insert_keyed(best_d, best_j, k, acc, j);
+              worst = best_d[(k - 1) * kKnnThreads];
+              worst_j = best_j[(k - 1) * kKnnThreads];
+            }
+          }
+        }
+    // everything outside the covered block [cell - shell, cell + shell + 1) * cell_size is at least
+    // `cover` away from the query
+    float cover = __int_as_float(0x7f800000);
+#pragma unroll
+    for (int a = 0; a < D; ++a) {
+      const float low = q[a] - (float)(cell[a] - shell) * sp.cell_size;
+      const float high = (float)(cell[a] + shell + 1) * sp.cell_size - q[a];
+      cover = fminf(cover, fminf(low, high));
+    }
+    cover -= margin;
+    settled = worst_j >= 0 && cover > 0.0f && worst < cover * cover * 0.99999f;
+  }
+  unsettled[i] = settled ? 0 : 1;
+  if (!settled) return;
+  for (int r = 0; r < k; ++r) {
+    col[i * k + r] = (int64_t)best_j[r * kKnnThreads];
+    if (dist_sq) dist_sq[i * k + r] = best_d[r * kKnnThreads];
+  }
+}
+
+// Brute-force scan for the queries the shell search left unsettled (a handful in sparse regions,
+// every query when the points sit in a few cells): same selection as k_knn_small, straight from
+// global memory, candidates in ascending index.
+template <int D>
+__global__ void __launch_bounds__(kKnnThreads)
+k_knn_flagged(const float *__restrict__ queries, int64_t nq, const float *__restrict__ candidates, int64_t nc,
+              int k, int exclude_self, const int32_t *__restrict__ unsettled, int64_t *__restrict__ col,
+              float *__restrict__ dist_sq) {
+  extern __shared__ __align__(16) unsigned char knn_smem[];
+  float *best_d = reinterpret_cast<float *>(knn_smem) + threadIdx.x;
+  int32_t *best_j = reinterpret_cast<int32_t *>(knn_smem + (size_t)k * kKnnThreads * 4) + threadIdx.x;
+  const int64_t i = (int64_t)blockIdx.x * kKnnThreads + threadIdx.x;
+  if (i >= nq || !unsettled[i]) return;
+  float q[3];
+  load_point<D>(queries, i, q);
+  for (int r = 0; r < k; ++r) {
+    best_d[r * kKnnThreads] = __int_as_float(0x7f800000);
+    best_j[r * kKnnThreads] = -1;
+  }
+  float worst = __int_as_float(0x7f800000);
+  const int64_t self = exclude_self ? i : -1;
+  for (int64_t j = 0; j < nc; ++j) {
+    float p[3];
+    load_point<D>(candidates, j, p);
+    const float d0 = __fsub_rn(p[0], q[0]);
+    float acc = __fmul_rn(d0, d0);
+    if (D > 1) {
+      const float d1 = __fsub_rn(p[1], q[1]);
+      acc = __fmaf_rn(d1, d1, acc);
+    }
+    if (D > 2) {
+      const float d2 = __fsub_rn(p[2], q[2]);
+      acc = __fmaf_rn(d2, d2, acc);
+    }
+    if (acc < worst && j != self) {
+      knn_insert(best_d, best_j, k, acc, (int32_t)j);
+      worst = best_d[(k - 1) * kKnnThreads];
+    }
+  }
+  for (int r = 0; r < k; ++r) {
+    col[i * k + r] = (int64_t)best_j[r * kKnnThreads];
+    if (dist_sq) dist_sq[i * k + r] = best_d[r * kKnnThreads];
+  }
+}
+
 // ---- implicit edge fields of a stored relation ---------------------------------------------------
 constexpr int kMaxGeometryDims = 8;
 
@@ -875,6 +1023,45 @@ extern "C" int32_t tgb_knn(const void *queries, int64_t nq, const void *candidat
     k_knn_wide<<<blocks, kKnnThreads, smem, st>>>(q, nq, c, nc, dims, k, exclude_self, out, dist);
   }
   TGB_LAUNCHED();
+  return TGB_STATUS_OK;
+}
+
+extern "C" int32_t tgb_knn_grid(const void *queries, int64_t nq, const void *candidates, int64_t nc,
+                                const tgb_cell_space *space, const void *directory, int32_t k,
+                                int32_t exclude_self, int32_t self_search, float margin, void *col,
+                                void *dist_sq, void *unsettled, uint64_t stream) {
+  RadiusCall c;
+  const int32_t status = radius_call(space, nc, directory, candidates, &c);
+  if (status != TGB_STATUS_OK) return status;
+  if (c.sp.periodic) TGB_FAIL(TGB_STATUS_UNSUPPORTED, "the nearest-neighbour search has no periodic form");
+  if (nq < 0 || (self_search && nq != nc)) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "query count out of range");
+  if (k < 1 || k > 128) TGB_FAIL(TGB_STATUS_UNSUPPORTED, "k must be in [1, 128]");
+  if ((int64_t)k > nc - (exclude_self ? 1 : 0))
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "k exceeds the number of admissible candidates");
+  if (!(margin >= 0.0f)) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "margin must be non-negative");
+  if (nq == 0) return TGB_STATUS_OK;
+  if (!queries || !col || !unsettled) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const float *q = static_cast<const float *>(queries), *cand = static_cast<const float *>(candidates);
+  const unsigned blocks = grid_for(nq, kKnnThreads);
+  const size_t smem = (size_t)k * kKnnThreads * 8;
+#define TGB_KNN_GRID(DIMS)                                                                                       \
+  do {                                                                                                           \
+    TGB_CUDA(cudaFuncSetAttribute(k_knn_grid<DIMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));    \
+    TGB_CUDA(cudaFuncSetAttribute(k_knn_flagged<DIMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    k_knn_grid<DIMS><<<blocks, kKnnThreads, smem, st>>>(q, nq, c.sp, c.dir, k, exclude_self, self_search, margin, \
+                                                         static_cast<int64_t *>(col),                            \
+                                                         static_cast<float *>(dist_sq),                          \
+                                                         static_cast<int32_t *>(unsettled));                     \
+    k_knn_flagged<DIMS><<<blocks, kKnnThreads, smem, st>>>(q, nq, cand, nc, k, exclude_self,                     \
+                                                            static_cast<const int32_t *>(unsettled),             \
+                                                            static_cast<int64_t *>(col),                         \
+                                                            static_cast<float *>(dist_sq));                      \
+  } while (0)
+  if (c.sp.dims == 1) TGB_KNN_GRID(1); else if (c.sp.dims == 2) TGB_KNN_GRID(2); else TGB_KNN_GRID(3);
+#undef TGB_KNN_GRID
+  TGB_CUDA(cudaGetLastError());
+  g_launches.fetch_add(2);
   return TGB_STATUS_OK;
 }
 

@@ -70,6 +70,7 @@ _SIGNATURES = {
     "tgb_radius_wsum_fwd": (_i32, [_vp, _i64, _vp, _vp, _f32, _i32, _i32, _vp, _i64, _vp, _u64]),
     "tgb_radius_wsum_bwd_pos": (_i32, [_vp, _i64, _vp, _vp, _f32, _i32, _vp, _vp, _i64, _vp, _u64]),
     "tgb_knn": (_i32, [_vp, _i64, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _u64]),
+    "tgb_knn_grid": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _u64]),
     "tgb_edge_geometry": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _u64]),
     "tgb_edge_program_fwd": (_i32, [_vp, _vp, _vp, _i32, _f32, _vp, _u64]),
     "tgb_edge_program_bwd_rows": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _u64]),

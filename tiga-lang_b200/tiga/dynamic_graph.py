@@ -89,9 +89,11 @@ class GeometricRelation:
         """What a specialised launch depends on besides the tensors it is handed: a new Graph over a
         new snapshot with the same signature reuses the launch."""
         cutoff = self.cutoff
+        # the cutoff VALUE is a runtime scalar (the runner reads it from the graph of the call); only
+        # what selects the code path is part of the signature
         return (self.kind, tuple(self.positions.shape[1:]), self.positions.dtype, self.positions.device,
-                None if cutoff is None or isinstance(cutoff, torch.Tensor) else float(cutoff),
-                isinstance(cutoff, torch.Tensor), self.k, self.exclude_self, self.source_positions is None,
+                None if cutoff is None else (isinstance(cutoff, torch.Tensor), self.scalar_cutoff() is not None),
+                self.k, self.exclude_self, self.source_positions is None,
                 None if self.periodic is None else tuple(self.periodic.shape),
                 self.metric is None, self.select is None, tuple(sorted(self.fields)))
 
@@ -163,8 +165,8 @@ class GeometricRelation:
         candidates = queries if self.source_positions is None else self.source_positions
         k = int(self.k)
         if queries.is_cuda and queries.dtype == torch.float32 and queries.shape[1] <= 64 and k <= 128:
-            col = geometry.knn_indices(queries, candidates, k, self.exclude_self)
-            builder = "b200-exact-knn-tiled-scan"
+            col, builder = geometry.knn_indices(queries, candidates, k, self.exclude_self,
+                                                self_search=self.source_positions is None)
         else:
             distances = torch.cdist(queries.detach(), candidates.detach(),
                                     compute_mode="donot_use_mm_for_euclid_dist")

@@ -187,16 +187,57 @@ class RadiusWeightedSumFunction(torch.autograd.Function):
         return dpos, dx, None, None, None, None
 
 
-def knn_indices(queries: torch.Tensor, candidates: torch.Tensor, k: int, exclude_self: bool) -> torch.Tensor:
-    """col [nq * k] int64: the k nearest candidates of every query, ascending by (squared distance,
-    candidate index)."""
+_UNIT_BALL = {1: 2.0, 2: 3.141592653589793, 3: 4.1887902047863905}
+KNN_GRID_MIN_CANDIDATES = 4096      # below this the tiled scan over all candidates is as fast
+
+
+def _knn_cell_size(lower, upper, count: int, k: int, dims: int) -> float:
+    """Cell edge for the shell search: the radius of a ball that holds about k points at the mean
+    density of the candidates' bounding box, plus a fifth."""
+    extents = [float(h) - float(l) for l, h in zip(lower, upper)]
+    widest = max(extents)
+    if widest <= 0.0:
+        return 1.0
+    volume = 1.0
+    for extent in extents:
+        volume *= max(extent, 1.0e-6 * widest)
+    radius = (k * volume / (count * _UNIT_BALL[dims])) ** (1.0 / dims)
+    return 1.2 * radius
+
+
+def knn_indices(queries: torch.Tensor, candidates: torch.Tensor, k: int, exclude_self: bool, *,
+                self_search: bool | None = None) -> tuple[torch.Tensor, str]:
+    """(col [nq * k] int64, builder name): the k nearest candidates of every query, ascending by
+    (squared distance, candidate index).  Up to three dimensions and enough candidates: the shell
+    search over a cell directory of the candidates; otherwise the tiled scan over all candidates.
+    Both are exact and give identical results."""
     lib = _native.lib()
     q, c = _check_positions(queries), _check_positions(candidates)
+    if self_search is None:
+        self_search = queries is candidates
     col = torch.empty(q.shape[0] * int(k), dtype=torch.int64, device=q.device)
+    dims = int(q.shape[1])
+    if dims <= 3 and c.shape[0] >= KNN_GRID_MIN_CANDIDATES and q.shape[0] > 0:
+        # one small read-back: the bounding boxes size the cells and bound the rounding of a coordinate
+        box = torch.stack((*c.aminmax(dim=0), *q.aminmax(dim=0))).tolist()
+        lower, upper = box[0], box[1]
+        largest = max(max(abs(v) for v in row) for row in box)
+        cell = _knn_cell_size(lower, upper, int(c.shape[0]), int(k), dims)
+        if all(v == v and abs(v) != float("inf") for row in box for v in row) and largest / cell < 2.0 ** 30:
+            space = make_cell_space(dims, cell, None)
+            directory = CellDirectory(c, space)
+            unsettled = torch.empty(q.shape[0], dtype=torch.int32, device=q.device)
+            margin = 4.0e-7 * largest
+            with torch.cuda.device(q.device):
+                _native.check(lib.tgb_knn_grid(
+                    q.data_ptr(), q.shape[0], c.data_ptr(), c.shape[0], ctypes.byref(space.struct),
+                    directory.buffer.data_ptr(), int(k), int(bool(exclude_self)), int(bool(self_search)),
+                    float(margin), col.data_ptr(), 0, unsettled.data_ptr(), _stream(q.device)), "tgb_knn_grid")
+            return col, "b200-exact-knn-cell-shells"
     with torch.cuda.device(q.device):
         _native.check(lib.tgb_knn(q.data_ptr(), q.shape[0], c.data_ptr(), c.shape[0], q.shape[1], int(k),
                                   int(bool(exclude_self)), col.data_ptr(), 0, _stream(q.device)), "tgb_knn")
-    return col
+    return col, "b200-exact-knn-tiled-scan"
 
 
 def edge_geometry(dst_positions: torch.Tensor, src_positions: torch.Tensor, space: CellSpace,

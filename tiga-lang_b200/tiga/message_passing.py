@@ -145,7 +145,9 @@ class _GuardedLaunch:
                     return _MISS
         except (KeyError, TypeError, AttributeError):
             return _MISS
-        if len(params) != len(self.constants) + sum(1 for role, _ in self.bindings if role == "param"):
+        # only the parameters edge() takes are part of the staged program; node() may take others
+        if kernel._edge_parameter_count(params) != len(self.constants) + sum(
+                1 for role, _ in self.bindings if role == "param"):
             return _MISS
         if graph is not self.graph:
             self.runner.cell.graph = self.graph = graph
@@ -188,6 +190,17 @@ class MessagePassing(Kernel):
 
     def edge(self, src, dst, edge, **params):
         raise NotImplementedError
+
+    def _edge_parameter_count(self, params) -> int:
+        """How many of the call's keyword parameters ``edge()`` receives (the signature is read once)."""
+        spec = self.__dict__.get("_edge_parameter_spec")
+        if spec is None:
+            import inspect
+
+            declared = inspect.signature(self.edge).parameters
+            spec = (any(p.kind is inspect.Parameter.VAR_KEYWORD for p in declared.values()), frozenset(declared))
+            self.__dict__["_edge_parameter_spec"] = spec
+        return len(params) if spec[0] else sum(1 for name in params if name in spec[1])
 
     def node(self, dst, aggregate, **params):
         return aggregate
