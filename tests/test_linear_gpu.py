@@ -150,12 +150,12 @@ def test_matmul_written_in_node_runs_on_the_tensor_core_kernels(oracle):
     dx, dW = torch.autograd.grad(out, (x, W), torch.ones_like(out))
     assert _native.launch_count() - before >= 4       # d(aggregate), dW (+ its partial sum), dx gather
     ref_x, ref_W = x.detach().clone().requires_grad_(), W.detach().clone().requires_grad_()
-    ref = Layer().reference(graph=graph, src={"x": ref_x}, dst={}, edge={"weight": w}, W=ref_W)
+    ref = Layer().reference(graph=graph, src={"x": ref_x}, dst={}, edge={"weight": w[:, None]}, W=ref_W)
     want_dx, want_dW = torch.autograd.grad(ref, (ref_x, ref_W), torch.ones_like(ref))
     torch.testing.assert_close(dx, want_dx, rtol=1e-4, atol=1e-4 * float(want_dx.abs().max()))
     torch.testing.assert_close(dW, want_dW, rtol=1e-4, atol=1e-4 * float(want_dW.abs().max()))
     # a width the kernels do not take: plain Torch, same answer as Torch
     W3 = torch.randn(64, 3, device="cuda")
     out3 = layer(graph=graph, src={"x": x}, dst={}, edge={"weight": w}, W=W3)
-    torch.testing.assert_close(out3, layer.reference(graph=graph, src={"x": x}, dst={}, edge={"weight": w}, W=W3),
+    torch.testing.assert_close(out3, layer.reference(graph=graph, src={"x": x}, dst={}, edge={"weight": w[:, None]}, W=W3),
                                rtol=1e-4, atol=1e-4)
