@@ -14,6 +14,8 @@
 // issues 12 MMAs (M=128, N, K=8) per chunk, and after the last chunk the four
 // warps read the accumulator from tensor memory and store their rows.
 // Tensor-core bound in flops but HBM bound in practice: 2*M*K*4 bytes per call.
+#include <cstdlib>
+
 #include "tgb_common.cuh"
 #include "tgb_tcgen05.cuh"
 
@@ -269,11 +271,18 @@ __device__ __forceinline__ void mbar_wait_teardown(uint64_t *bar, uint32_t parit
 
 __global__ void __launch_bounds__(kWtThreads, 1)
 k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__restrict__ b_t,
-                   float *__restrict__ out, int64_t M, int k_chunks, int n_out, int *error) {
+                   float *__restrict__ out, int64_t M, int k_chunks, int n_out, int pair, int *error) {
   // The accumulator always has 128 feature rows (the M of the MMA).  With n_out = 64 output
   // features the upper 64 rows of the resident matrix are zero and are never stored: the kernel is
   // bound by the rows of `a` it streams, not by MMA work.
+  // pair (n_out = 64, K = 64): one accumulator serves TWO row tiles.  The resident matrix is the
+  // block-diagonal [b_t 0; 0 b_t] (128 x 2K) and the streamed operand stacks the chunks of rows
+  // [r, r + 128) on those of rows [r + 128, r + 256) along K, so accumulator rows 0..63 hold the
+  // features of the first tile and rows 64..127 those of the second: 256 rows per accumulator at the
+  // chunk and MMA count of a 128 x 128 tile, all epilogue lanes storing.
   constexpr int N = 128;
+  const int tile_chunks = pair ? 2 * k_chunks : k_chunks;      // chunks feeding one accumulator
+  const int tile_rows = pair ? 2 * kTileM : kTileM;            // rows of `a` behind one accumulator
   extern __shared__ uint8_t smem_raw[];
   LinearWtSmem &sm =
       *reinterpret_cast<LinearWtSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -301,15 +310,16 @@ k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__res
   const uint32_t w_hi = tmem, w_lo = tmem + 128, acc0 = tmem + 256;
   volatile int *abort_flag = &sm.abort_flag;
 
-  const int64_t n_tiles = (M + kTileM - 1) / kTileM;
+  const int64_t n_tiles = (M + tile_rows - 1) / tile_rows;
   const int64_t my_tiles = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  const int64_t total_chunks = my_tiles * k_chunks;
+  const int64_t total_chunks = my_tiles * tile_chunks;
   auto load_chunk = [&](int64_t chunk) {             // thread 0 only
     const int r = (int)(chunk % kWtRing);
-    const int kc = (int)(chunk % k_chunks);
-    const int64_t row = (blockIdx.x + (chunk / k_chunks) * gridDim.x) * kTileM;
+    const int kc = (int)(chunk % tile_chunks);
+    // second half of a pair: the same columns, 128 rows further down (rows past M read as zero)
+    const int64_t row = (blockIdx.x + (chunk / tile_chunks) * gridDim.x) * tile_rows + (kc / k_chunks) * kTileM;
     mbar_arrive_expect_tx(&sm.raw_full[r], kChunkBytes);
-    tma_load_2d(sm.raw[r], &map_a, kc * kChunkK, (int32_t)row, &sm.raw_full[r]);
+    tma_load_2d(sm.raw[r], &map_a, (kc % k_chunks) * kChunkK, (int32_t)row, &sm.raw_full[r]);
   };
   if (tid == 0)
     for (int64_t c = 0; c < kWtRing && c < total_chunks; ++c) load_chunk(c);
@@ -318,13 +328,17 @@ k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__res
     // b_t row `tid` (an output feature) -> hi/lo -> this thread's lane of tensor memory
     const int K = k_chunks * kChunkK;
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    // pair: accumulator row `tid` is feature tid % 64 of tile half tid / 64, fed by that half's chunks only
+    const int feature = pair ? (tid & 63) : tid;
 #pragma unroll 1
-    for (int kc = 0; kc < k_chunks; ++kc) {
+    for (int kc = 0; kc < tile_chunks; ++kc) {
       uint32_t hi[32], lo[32];
-      const float4 *src = reinterpret_cast<const float4 *>(b_t + (int64_t)(tid < n_out ? tid : 0) * K + kc * kChunkK);
+      const bool fed = feature < n_out && (!pair || kc / k_chunks == tid / 64);
+      const float4 *src = reinterpret_cast<const float4 *>(b_t + (int64_t)(fed ? feature : 0) * K +
+                                                           (kc % k_chunks) * kChunkK);
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
-        const float4 v = tid < n_out ? __ldg(src + q) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const float4 v = fed ? __ldg(src + q) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         float h, l;
         split_tf32(v.x, h, l); hi[4 * q] = __float_as_uint(h); lo[4 * q] = __float_as_uint(l);
         split_tf32(v.y, h, l); hi[4 * q + 1] = __float_as_uint(h); lo[4 * q + 1] = __float_as_uint(l);
@@ -361,7 +375,7 @@ k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__res
       int64_t it = 0;
       for (int64_t t = 0; t < my_tiles; ++t) {
         const uint32_t acc = acc0 + (uint32_t)(t & 1) * kTileM;
-        for (int kc = 0; kc < k_chunks; ++kc, ++it) {
+        for (int kc = 0; kc < tile_chunks; ++kc, ++it) {
           const int s = (int)(it % kWtOps);
           mbar_wait(&sm.op_full[s], (uint32_t)((it / kWtOps) & 1), abort_flag, error, 8);
           if (it + kWtRing < total_chunks) load_chunk(it + kWtRing);   // its slot raw[it % ring] has been read
@@ -378,7 +392,7 @@ k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__res
             mma_tf32_a_tmem(acc, w_hi + col, ah, idesc, 1);
           }
           mma_commit(&sm.mma_done[s]);
-          if (kc == k_chunks - 1) mma_commit(&sm.acc_full[t & 1]);
+          if (kc == tile_chunks - 1) mma_commit(&sm.acc_full[t & 1]);
         }
       }
       // no TMA or MMA may be in flight when shared and tensor memory go away
@@ -399,17 +413,19 @@ k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__res
       const int b = (int)(t & 1);
       mbar_wait(&sm.acc_full[b], (uint32_t)((t >> 1) & 1), abort_flag, error, 4);
       tc_fence_after_sync();
-      const int64_t row0 = (blockIdx.x + t * gridDim.x) * kTileM;
+      // pair: lanes 64..127 hold the second row tile of the pair
+      const int feature = pair ? (n & 63) : n;
+      const int64_t row0 = (blockIdx.x + t * gridDim.x) * tile_rows + (pair ? (n >> 6) * kTileM : 0);
       const bool live = !*abort_flag;
 #pragma unroll 1
       for (int c0 = 0; c0 < kTileM; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(acc0 + (uint32_t)(b * kTileM) + lane_base + c0, r);
         tmem_ld_wait();
-        float *dst = out + (row0 + c0) * n_out + n;
+        float *dst = out + (row0 + c0) * n_out + feature;
 #pragma unroll
         for (int c = 0; c < 32; ++c)
-          if (live && n < n_out && row0 + c0 + c < M) __stcs(dst + (int64_t)c * n_out, __uint_as_float(r[c]));
+          if (live && feature < n_out && row0 + c0 + c < M) __stcs(dst + (int64_t)c * n_out, __uint_as_float(r[c]));
       }
       tc_fence_before_sync();
       mbar_arrive_warp(&sm.acc_empty[b]);
@@ -615,6 +631,16 @@ extern "C" int32_t tgb_selftest_bounded_wait(void *error_flag, uint32_t polls, v
   return TGB_STATUS_OK;
 }
 
+// K = N = 64 runs two row tiles per accumulator; TGB_LINEAR_PAIR=0 in the environment selects the
+// older kernel (both operands in shared memory), for comparisons.
+static bool linear_pair_enabled() {
+  static const bool enabled = [] {
+    const char *text = getenv("TGB_LINEAR_PAIR");
+    return text ? atoi(text) != 0 : true;
+  }();
+  return enabled;
+}
+
 extern "C" int32_t tgb_linear_f32(const void *a, const void *b_t, void *out, int64_t M, int32_t K, int32_t N,
                                   void *error_flag, uint64_t stream) {
   if (M < 0) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "negative row count");
@@ -638,16 +664,20 @@ extern "C" int32_t tgb_linear_f32(const void *a, const void *b_t, void *out, int
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
   const size_t smem = sizeof(LinearSmem) + 1024;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (N == 128 && ((uintptr_t)b_t & 15u) == 0) {
-    // resident matrix in tensor memory, rows of `a` through a six-slot TMA ring.  The kernel also
-    // takes 64 output features (upper half of the resident matrix zero), but measured slower there
-    // than the kernel with both operands in shared memory (4.43 vs 3.65 ms for 2^24 rows, K = 64):
-    // a tile costs about 5 us whatever its MMA count, so N = 64 keeps the older kernel.
+  const bool pair = N == 64 && K == 64 && linear_pair_enabled();
+  if ((N == 128 || pair) && ((uintptr_t)b_t & 15u) == 0) {
+    // resident matrix in tensor memory, rows of `a` through a six-slot TMA ring.  A tile costs about
+    // 5 us whatever its MMA count, so 64 output features with the upper half of the resident matrix
+    // zero measured slower than the kernel with both operands in shared memory (4.43 vs 3.65 ms for
+    // 2^24 rows, K = 64); K = N = 64 therefore runs PAIRED: two row tiles per accumulator behind a
+    // block-diagonal resident matrix, 256 rows at the cost of one tile.
     const size_t smem_wt = sizeof(LinearWtSmem) + 1024;
+    const int64_t wt_tiles = ceil_div(M, pair ? 2 * kTileM : kTileM);
+    const unsigned wt_grid = (unsigned)(wt_tiles < sms ? wt_tiles : sms);
     // the attribute belongs to the current device's context, so it is set on every call (cheap)
     TGB_CUDA(cudaFuncSetAttribute(k_linear_wt_3xtf32, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_wt));
-    k_linear_wt_3xtf32<<<grid, kWtThreads, smem_wt, st>>>(map_a, (const float *)b_t, (float *)out, M, K / 32, N,
-                                                         (int *)error_flag);
+    k_linear_wt_3xtf32<<<wt_grid, kWtThreads, smem_wt, st>>>(map_a, (const float *)b_t, (float *)out, M, K / 32, N,
+                                                            pair ? 1 : 0, (int *)error_flag);
   } else if (N == 128) {
     // the attribute belongs to the current device's context, so it is set on every call (cheap)
     TGB_CUDA(cudaFuncSetAttribute(k_linear_3xtf32<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
