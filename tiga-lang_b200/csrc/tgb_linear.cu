@@ -449,37 +449,62 @@ k_linear_wt_3xtf32(const __grid_constant__ CUtensorMap map_a, const float *__res
 // ---------------------------------------------------------------------------
 constexpr int kDwRows = 32;                        // rows (reduction) per tile
 constexpr int kDwBoxBytes = kDwRows * 128;         // one [32 rows x 32 floats] box
-constexpr int kDwMaxBoxes = 8;                     // (K + N) / 32 <= 8
 constexpr int kDwChunkRowsPerCta = 8192;           // rows one accumulator sees before it is written out
 
-struct DwSmem {
-  alignas(1024) uint8_t hi[2][kDwMaxBoxes][kDwBoxBytes];   // a blocks first, then dout blocks
-  alignas(1024) uint8_t lo[2][kDwMaxBoxes][kDwBoxBytes];
-  alignas(1024) uint8_t raw[2][kDwMaxBoxes][kDwBoxBytes];  // TMA destination ring
-  uint64_t op_full[2];
-  uint64_t full[2];
-  uint64_t mma_done[2];
+constexpr int kDwSplitWarps = 8;
+constexpr int kDwThreads = (kDwSplitWarps + 1) * 32;   // warps 0-7 split, warp 8 issues TMA and MMAs
+constexpr int kDwMaxOpSlots = 3;                       // hi/lo operand slots at most
+constexpr int kDwMaxRing = 6;                          // TMA slots in flight at most
+
+// Shared-memory plan of the kernel for KR real columns of `a` (64 or 128) and N columns of dout.
+// The TMA ring holds only boxes that exist in memory; an operand slot always has four `a` positions
+// (the MMA's M is 128), of which the ones beyond KR stay zero for the whole kernel.
+template <int KR, int N>
+struct DwPlan {
+  static constexpr int kARealBoxes = KR / 32, kDBoxes = N / 32;
+  static constexpr int kRawBoxes = kARealBoxes + kDBoxes;          // boxes one tile brings in
+  static constexpr int kOpBoxes = 4 + kDBoxes;                     // boxes of one hi (or lo) operand slot
+  // two operand slots: a third one (the split warps two tiles ahead of the MMAs) measured no faster
+  static constexpr int kOpSlots = 2;
+  static constexpr int kOperandBytes = 2 * kOpSlots * kOpBoxes * kDwBoxBytes;
+  static constexpr int kBudget = 216 * 1024 - kOperandBytes;
+  static constexpr int kRingFit = kBudget / (kRawBoxes * kDwBoxBytes);
+  static constexpr int kRing = kRingFit > kDwMaxRing ? kDwMaxRing : (kRingFit < 2 ? 2 : kRingFit);
+  static constexpr int kRawOffset = 0;
+  static constexpr int kHiOffset = kRing * kRawBoxes * kDwBoxBytes;
+  static constexpr int kLoOffset = kHiOffset + kOpSlots * kOpBoxes * kDwBoxBytes;
+  static constexpr int kBarOffset = kLoOffset + kOpSlots * kOpBoxes * kDwBoxBytes;
+  static constexpr int kBytes = kBarOffset + 256;
+};
+
+struct DwBarriers {
+  uint64_t raw_full[kDwMaxRing];    // tile landed in TMA slot r
+  uint64_t op_full[kDwMaxOpSlots];  // operand slot s holds the split tile (and its TMA slot has been read)
+  uint64_t mma_done[kDwMaxOpSlots]; // the MMAs that read operand slot s have finished
   uint64_t acc_done;
   uint32_t tmem_base;
   int abort_flag;
 };
 
-constexpr int kDwSplitWarps = 8;
-constexpr int kDwThreads = (kDwSplitWarps + 1) * 32;   // warps 0-7 split, warp 8 issues TMA and MMAs
-
-template <int N>
+template <int KR, int N>
 __global__ void __launch_bounds__(kDwThreads, 1)
 k_linear_dw_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_d,
                    float *__restrict__ partial, int64_t M, int *error) {
-  constexpr int K = 128;                             // rows of dw = M dimension of the MMA
-  constexpr int kABoxes = K / 32, kDBoxes = N / 32, kBoxes = kABoxes + kDBoxes;
+  using P = DwPlan<KR, N>;
+  constexpr int K = 128;                             // rows of the accumulator = M dimension of the MMA
+  constexpr int kRing = P::kRing;
+  constexpr int kDwOpSlots = P::kOpSlots;
   extern __shared__ uint8_t smem_raw[];
-  DwSmem &sm = *reinterpret_cast<DwSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t *raw = base + P::kRawOffset;               // [kRing][kRawBoxes][box]
+  uint8_t *hi = base + P::kHiOffset;                 // [slots][kOpBoxes][box]: four `a` positions, then dout
+  uint8_t *lo = base + P::kLoOffset;
+  DwBarriers &sm = *reinterpret_cast<DwBarriers *>(base + P::kBarOffset);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     sm.abort_flag = 0;
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&sm.full[i], 1);
+    for (int i = 0; i < kRing; ++i) mbar_init(&sm.raw_full[i], 1);
+    for (int i = 0; i < kDwOpSlots; ++i) {
       mbar_init(&sm.op_full[i], kDwSplitWarps);   // one arrival per split warp
       mbar_init(&sm.mma_done[i], 1);
     }
@@ -487,6 +512,19 @@ k_linear_dw_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_const
     mbar_fence_init();
     tma_prefetch_descriptor(&map_a);
     tma_prefetch_descriptor(&map_d);
+  }
+  if (P::kARealBoxes < 4) {
+    // the `a` positions no tile ever fills: zero once, in both parts of both operand slots
+    constexpr int kZeroBytes = (4 - P::kARealBoxes) * kDwBoxBytes;
+    for (int slot = 0; slot < kDwOpSlots; ++slot) {
+      float4 *zh = reinterpret_cast<float4 *>(hi + (slot * P::kOpBoxes + P::kARealBoxes) * kDwBoxBytes);
+      float4 *zl = reinterpret_cast<float4 *>(lo + (slot * P::kOpBoxes + P::kARealBoxes) * kDwBoxBytes);
+      for (int i = tid; i < kZeroBytes / 16; i += kDwThreads) {
+        zh[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        zl[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+    }
+    fence_proxy_async_smem();
   }
   __syncthreads();
   if (warp == 0) tmem_alloc(&sm.tmem_base, N);
@@ -498,38 +536,46 @@ k_linear_dw_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
   const int64_t n_tiles = (M + kDwRows - 1) / kDwRows;
   const int64_t my_tiles = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  auto load_tile = [&](int64_t t, int slot) {
+  auto load_tile = [&](int64_t t) {                   // issue thread only; tile t goes to TMA slot t % kRing
+    const int r = (int)(t % kRing);
     const int32_t row0 = (int32_t)((blockIdx.x + t * gridDim.x) * kDwRows);
-    mbar_arrive_expect_tx(&sm.full[slot], kBoxes * kDwBoxBytes);
+    uint8_t *slot = raw + (size_t)r * P::kRawBoxes * kDwBoxBytes;
+    mbar_arrive_expect_tx(&sm.raw_full[r], P::kRawBoxes * kDwBoxBytes);
 #pragma unroll
-    for (int j = 0; j < kABoxes; ++j) tma_load_2d(sm.raw[slot][j], &map_a, 32 * j, row0, &sm.full[slot]);
+    for (int j = 0; j < P::kARealBoxes; ++j) tma_load_2d(slot + j * kDwBoxBytes, &map_a, 32 * j, row0, &sm.raw_full[r]);
 #pragma unroll
-    for (int j = 0; j < kDBoxes; ++j) tma_load_2d(sm.raw[slot][kABoxes + j], &map_d, 32 * j, row0, &sm.full[slot]);
+    for (int j = 0; j < P::kDBoxes; ++j)
+      tma_load_2d(slot + (P::kARealBoxes + j) * kDwBoxBytes, &map_d, 32 * j, row0, &sm.raw_full[r]);
   };
 
   if (warp < kDwSplitWarps) {
     // ---- split warps: raw tile -> hi/lo operand slot ------------------------------------------
     for (int64_t t = 0; t < my_tiles; ++t) {
-      const int s = (int)(t & 1);
-      const uint32_t use = (uint32_t)(t >> 1);
-      mbar_wait(&sm.full[s], use & 1, abort_flag, error, 52);
-      if (use >= 1) mbar_wait(&sm.mma_done[s], (use - 1) & 1, abort_flag, error, 51);   // operand slot free
-      split_chunk_from(sm.raw[s][0], sm.hi[s][0], sm.lo[s][0], kBoxes * kDwBoxBytes, tid, kDwSplitWarps * 32);
+      const int r = (int)(t % kRing);
+      const int s = (int)(t % kDwOpSlots);
+      const uint32_t use_s = (uint32_t)(t / kDwOpSlots);
+      mbar_wait(&sm.raw_full[r], (uint32_t)((t / kRing) & 1), abort_flag, error, 52);
+      if (use_s >= 1) mbar_wait(&sm.mma_done[s], (use_s - 1) & 1, abort_flag, error, 51);   // operand slot free
+      const uint8_t *src = raw + (size_t)r * P::kRawBoxes * kDwBoxBytes;
+      uint8_t *h = hi + (size_t)s * P::kOpBoxes * kDwBoxBytes, *l = lo + (size_t)s * P::kOpBoxes * kDwBoxBytes;
+      split_chunk_from(src, h, l, P::kARealBoxes * kDwBoxBytes, tid, kDwSplitWarps * 32);
+      split_chunk_from(src + P::kARealBoxes * kDwBoxBytes, h + 4 * kDwBoxBytes, l + 4 * kDwBoxBytes,
+                       P::kDBoxes * kDwBoxBytes, tid, kDwSplitWarps * 32);
       fence_proxy_async_smem();
-      mbar_arrive_warp(&sm.op_full[s]);               // operands written, raw[s] read
+      mbar_arrive_warp(&sm.op_full[s]);               // operands written, the TMA slot read
     }
   } else if (lane == 0) {
-    // ---- issue thread: refills the TMA slots and issues the MMAs, nothing else ----------------
+    // ---- issue thread: refills the TMA ring and issues the MMAs, nothing else ------------------
     constexpr uint32_t idesc = instr_desc(kFmtTF32, kFmtTF32, K, N, 1, 1);    // both operands MN-major
-    if (my_tiles > 0) load_tile(0, 0);
-    if (my_tiles > 1) load_tile(1, 1);
+    for (int64_t t = 0; t < kRing && t < my_tiles; ++t) load_tile(t);
     for (int64_t t = 0; t < my_tiles; ++t) {
-      const int s = (int)(t & 1);
-      mbar_wait(&sm.op_full[s], (uint32_t)((t >> 1) & 1), abort_flag, error, 55);
-      if (t + 2 < my_tiles) load_tile(t + 2, s);      // every split thread has read raw[s]
+      const int s = (int)(t % kDwOpSlots);
+      mbar_wait(&sm.op_full[s], (uint32_t)((t / kDwOpSlots) & 1), abort_flag, error, 55);
+      if (t + kRing < my_tiles) load_tile(t + kRing);  // every split thread has read TMA slot t % kRing
       tc_fence_after_sync();
-      const uint32_t a_hi = smem_u32(sm.hi[s][0]), a_lo = smem_u32(sm.lo[s][0]);
-      const uint32_t d_hi = smem_u32(sm.hi[s][kABoxes]), d_lo = smem_u32(sm.lo[s][kABoxes]);
+      const uint32_t a_hi = smem_u32(hi + (size_t)s * P::kOpBoxes * kDwBoxBytes);
+      const uint32_t a_lo = smem_u32(lo + (size_t)s * P::kOpBoxes * kDwBoxBytes);
+      const uint32_t d_hi = a_hi + 4 * kDwBoxBytes, d_lo = a_lo + 4 * kDwBoxBytes;
 #pragma unroll
       for (int k = 0; k < kDwRows / 8; ++k) {          // 8 reduction rows = one 1024-byte swizzle atom per MMA
         const uint32_t off = k * 1024;
@@ -546,7 +592,7 @@ k_linear_dw_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
     if (my_tiles > 1) {                                // the tile before the last: its MMAs must be complete too
       const int64_t prev = my_tiles - 2;
-      mbar_wait_teardown(&sm.mma_done[prev & 1], (uint32_t)((prev >> 1) & 1));
+      mbar_wait_teardown(&sm.mma_done[prev % kDwOpSlots], (uint32_t)((prev / kDwOpSlots) & 1));
     }
   }
   // epilogue: warps 0-3 write this CTA's partial matrix (row of dw = column of a = tensor-memory lane)
@@ -724,13 +770,16 @@ extern "C" int32_t tgb_linear_dw_f32(const void *a, const void *dout, void *dw, 
              (unsigned long long)partial_bytes, (unsigned long long)need);
   float *cta_partials = (float *)partial;
   float *chunk_sums = cta_partials + (size_t)max_grid * 128 * N;
-  const size_t smem = sizeof(DwSmem) + 1024;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // columns of `a` that exist in memory, in whole 64-column halves of the accumulator's 128 rows
+  const int kr = K <= 64 ? 64 : 128;
   // the attribute belongs to the current device's context, so it is set on every call (cheap)
-  if (N == 128)
-    TGB_CUDA(cudaFuncSetAttribute(k_linear_dw_3xtf32<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  else
-    TGB_CUDA(cudaFuncSetAttribute(k_linear_dw_3xtf32<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+#define TGB_DW_CASE(KR_, N_)                                                                                   \
+  if (kr == KR_ && N == N_)                                                                                    \
+    TGB_CUDA(cudaFuncSetAttribute(k_linear_dw_3xtf32<KR_, N_>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                                  DwPlan<KR_, N_>::kBytes + 1024));
+  TGB_DW_CASE(64, 64) TGB_DW_CASE(64, 128) TGB_DW_CASE(128, 64) TGB_DW_CASE(128, 128)
+#undef TGB_DW_CASE
   for (int64_t c = 0; c < chunks; ++c) {
     const int64_t row0 = c * chunk_rows;
     const int64_t rows = M - row0 < chunk_rows ? M - row0 : chunk_rows;
@@ -743,10 +792,12 @@ extern "C" int32_t tgb_linear_dw_f32(const void *a, const void *dout, void *dw, 
     rc = make_tensor_map_2d(&map_d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (const float *)dout + row0 * N,
                             (uint64_t)rows, (uint64_t)N, (uint64_t)N * 4, 32, kDwRows, true);
     if (rc) return rc;
-    if (N == 128)
-      k_linear_dw_3xtf32<128><<<grid, kDwThreads, smem, st>>>(map_a, map_d, cta_partials, rows, (int *)error_flag);
-    else
-      k_linear_dw_3xtf32<64><<<grid, kDwThreads, smem, st>>>(map_a, map_d, cta_partials, rows, (int *)error_flag);
+#define TGB_DW_CASE(KR_, N_)                                                                       \
+  if (kr == KR_ && N == N_)                                                                        \
+    k_linear_dw_3xtf32<KR_, N_><<<grid, kDwThreads, DwPlan<KR_, N_>::kBytes + 1024, st>>>(         \
+        map_a, map_d, cta_partials, rows, (int *)error_flag);
+    TGB_DW_CASE(64, 64) TGB_DW_CASE(64, 128) TGB_DW_CASE(128, 64) TGB_DW_CASE(128, 128)
+#undef TGB_DW_CASE
     TGB_LAUNCHED();
     float *target = chunks > 1 ? chunk_sums + (size_t)c * K * N : (float *)dw;
     k_sum_dw_partials<<<(unsigned)ceil_div((int64_t)K * N, 256), 256, 0, st>>>(cta_partials, (int)grid, K * N,

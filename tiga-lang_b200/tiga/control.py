@@ -65,6 +65,15 @@ def repeat(initial, body: Callable, *, iterations: int, cuda_graph: bool | None 
     return results[0] if single else results
 
 
+def _write_back(static, produced) -> None:
+    """static[i] <- produced[i].  A body may hand back its own inputs (a swap, a view): such values
+    are staged first, so that no buffer is overwritten before it has been read."""
+    storages = {item.untyped_storage().data_ptr() for item in static}
+    staged = [value.clone() if value.untyped_storage().data_ptr() in storages else value for value in produced]
+    for target, value in zip(static, staged):
+        target.copy_(value)
+
+
 def _replay(body, states, iterations: int):
     """One iteration captured into a CUDA graph, then replayed.  The first iteration runs eagerly
     (it builds launch plans and caches, which may synchronise and must not be captured)."""
@@ -76,15 +85,11 @@ def _replay(body, states, iterations: int):
         side = torch.cuda.Stream(device=static[0].device)
         side.wait_stream(torch.cuda.current_stream(static[0].device))
         with torch.cuda.stream(side):                                  # iteration 2, eager on the capture stream
-            warm = _call_body(body, static, "repeat")
-            for target, value in zip(static, warm):
-                target.copy_(value)
+            _write_back(static, _call_body(body, static, "repeat"))
         torch.cuda.current_stream(static[0].device).wait_stream(side)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            produced = _call_body(body, static, "repeat")
-            for target, value in zip(static, produced):
-                target.copy_(value)
+            _write_back(static, _call_body(body, static, "repeat"))
         for _ in range(iterations - 2):
             graph.replay()
         return tuple(item.clone() for item in static)
