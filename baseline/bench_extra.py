@@ -14,6 +14,9 @@ events on the launching stream and its own clock record):
   l2_hostile_sum    uniform random sources, N = 2^22, 16 edges per row, F = 128: a 2 GB source table,
                     so the no-reuse algorithmic bytes are close to the real DRAM bytes
 
+  generic_program   R-MAT 2^20 nodes (config 2's graph), F = 16: `edge.weight * (src.u - dst.u)`, an edge
+                    expression no dedicated kernel covers, through the interpreting kernels, fwd + grads
+                    of both node fields and the edge weights
   dynamic_radius    131 072 points in the unit cube on a binary coordinate grid, scalar features,
                     cutoff between two squared-distance levels (about 16 neighbours): every step copies
                     one of two coordinate snapshots into the live position tensor, searches the
@@ -309,6 +312,52 @@ def l2_hostile(args, device, bench):
             "clocks": clocks}
 
 
+def generic_program(args, device, bench):
+    import tiga as tg
+    from baseline import synthetic as syn
+
+    scale, edge_factor, F = 20, 32, 16
+    row_ptr, col = syn.rmat_csr(scale, edge_factor, seed=args.seed, symmetrize=True, device=device)
+    N, E = row_ptr.numel() - 1, col.numel()
+    gen = torch.Generator(device=device).manual_seed(args.seed + 3)
+    u = torch.randn(N, F, generator=gen, device=device).requires_grad_()
+    v = torch.randn(N, F, generator=gen, device=device).requires_grad_()
+    w = torch.rand(E, 1, generator=gen, device=device).requires_grad_()
+    graph = tg.Graph.from_csr(row_ptr, col, num_src=N)
+    graph.native_plan(transpose=True)
+
+    class Flux(tg.MessagePassing):
+        reducer = tg.sum()
+
+        def edge(self, src, dst, edge):
+            return edge.weight * (src.u - dst.u)
+
+    kernel = Flux()
+    ones = torch.ones((N, F), device=device)
+
+    def step():
+        out = kernel(graph=graph, src={"u": u}, dst={"u": v}, edge={"weight": w})
+        return torch.autograd.grad(out, (u, v, w), ones)
+
+    def forward_only():
+        with torch.no_grad():
+            return kernel(graph=graph, src={"u": u}, dst={"u": v}, edge={"weight": w})
+
+    steps = _steps(args)
+    ms, clocks = bench.timed(step, steps, args.warmup, device.index or 0)
+    fwd_ms, _ = bench.timed(forward_only, steps, args.warmup, device.index or 0)
+    # the same sum written as two kernels the library has (weighted gather minus dst.u * row sums of w)
+    alg_fwd = E * (8 + 4 + 4 * F) + N * (8 + 8 * F)
+    peak, kind = bench.hbm_peak()
+    return {"workload": f"generic edge program w * (src.u - dst.u), rmat scale={scale} edge_factor={edge_factor} "
+                        f"F={F} fp32, fwd + grads of src.u, dst.u, weight",
+            "num_nodes": N, "num_edges": E, "steps": steps, "ms_per_step": round(ms, 4),
+            "forward_ms": round(fwd_ms, 4), "value": round(E / (ms * 1e-3) / 1e9, 4), "unit": bench.UNIT,
+            "lowering": kernel.last_variant.lowering,
+            "forward_algorithmic_frac": round(alg_fwd / (fwd_ms * 1e-3) / 1e9 / peak, 4), "peak_kind": f"of {kind}",
+            "note": "interpreted register program (no dedicated kernel): the correctness path", "clocks": clocks}
+
+
 def _binary_grid_snapshots(n, device, seed):
     """Two coordinate snapshots on a 1/1024 grid of the unit cube: float32 squared distances between
     grid points are exact, so no pair sits within rounding distance of the cutoff."""
@@ -424,6 +473,7 @@ def dynamic_knn(args, device, bench):
 WORKLOADS = {"weighted-sum": ("c1_weighted_sum", weighted_sum_c1), "gcn-layer": ("c2_gcn_layer", gcn_layer_sum),
              "gcn-layer-max": ("c2_gcn_layer_max", gcn_layer_max), "gat": ("c3_gat", gat),
              "attention": ("c4_attention", attention), "l2-hostile": ("l2_hostile_sum", l2_hostile),
+             "generic-program": ("generic_program", generic_program),
              "dynamic-radius": ("dynamic_radius", dynamic_radius), "dynamic-knn": ("dynamic_knn", dynamic_knn)}
 
 

@@ -193,15 +193,17 @@ KNN_GRID_MIN_CANDIDATES = 4096      # below this the tiled scan over all candida
 
 def _knn_cell_size(lower, upper, count: int, k: int, dims: int) -> float:
     """Cell edge for the shell search: the radius of a ball that holds about k points at the mean
-    density of the candidates' bounding box, plus a fifth."""
+    density of the candidates' bounding box, plus a fifth.  Axes along which the points do not
+    spread (a plane or a line embedded in space) do not count as dimensions of that density."""
     extents = [float(h) - float(l) for l, h in zip(lower, upper)]
     widest = max(extents)
     if widest <= 0.0:
         return 1.0
+    spread = [extent for extent in extents if extent >= 1.0e-3 * widest]
     volume = 1.0
-    for extent in extents:
-        volume *= max(extent, 1.0e-6 * widest)
-    radius = (k * volume / (count * _UNIT_BALL[dims])) ** (1.0 / dims)
+    for extent in spread:
+        volume *= extent
+    radius = (k * volume / (count * _UNIT_BALL[len(spread)])) ** (1.0 / len(spread))
     return 1.2 * radius
 
 
