@@ -360,3 +360,17 @@ def test_edge_expression_compiles_to_a_register_program():
     assert struct.num_instructions == len(program.ops) and struct.width == 4
     # a reduction over features is not element-wise: no program
     assert ep.compile_expression(cap.capture_edge(lambda src, dst, edge: (src.x * dst.x).sum(-1), {})) is None
+
+
+def test_repeat_write_back_stages_values_that_alias_the_carried_buffers():
+    from tiga import control
+
+    a, b = torch.arange(4.0), torch.arange(4.0) * 10
+    static = (a.clone(), b.clone())
+    control._write_back(static, (static[1], static[0]))                 # a swap hands back the inputs themselves
+    assert torch.equal(static[0], b) and torch.equal(static[1], a)
+    control._write_back(static, (static[0][:], static[0] + 1))           # a view of a carried buffer
+    assert torch.equal(static[0], b) and torch.equal(static[1], b + 1)
+    # the host loop (no CUDA graph) gives the same swap semantics
+    x, y = tg.repeat((a, b), lambda p, q: (q, p), iterations=5)
+    assert torch.equal(x, b) and torch.equal(y, a)
