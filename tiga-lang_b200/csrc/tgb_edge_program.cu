@@ -36,6 +36,9 @@ struct Walk {
   const uint32_t *eid;    // original edge id per entry, or null: entry index = edge id
   int ptr_bits, idx_bits;
   int64_t n_rows;
+  const int32_t *order;   // plan row order: the n_long rows above the split threshold first
+  int64_t n_long;
+  int64_t split_threshold;
 };
 
 __device__ __forceinline__ int64_t load_index(const void *base, int bits, int64_t i) {
@@ -120,40 +123,101 @@ __device__ __forceinline__ float group_sum(float v, unsigned mask) {
   return v;
 }
 
-template <int LANES>
-__global__ void __launch_bounds__(kThreads)
+// LONG = false: one lane group per row, rows longer than the plan's split threshold are left to the
+// LONG launch.  LONG = true: one CTA per long row (blockIdx.x-th entry of the plan's row order, which
+// lists the long rows first); its lane groups fold contiguous slices of the row's edges and the slices'
+// partial results are combined in slice order through shared memory (deterministic).
+constexpr int kLongThreads = 256;
+
+template <int LANES, bool LONG>
+__global__ void __launch_bounds__(LONG ? kLongThreads : kThreads)
 k_edge_program_fwd(const __grid_constant__ tgb_edge_program p, Operands in, Walk w, int reducer, float identity,
                    float *__restrict__ out) {
-  const int64_t row = ((int64_t)blockIdx.x * kThreads + threadIdx.x) / LANES;
-  const int lane = threadIdx.x % LANES;
-  if (row >= w.n_rows) return;
-  const int64_t begin = load_index(w.ptr, w.ptr_bits, row), end = load_index(w.ptr, w.ptr_bits, row + 1);
+  constexpr int kGroups = (LONG ? kLongThreads : kThreads) / LANES;
+  __shared__ float part[LONG ? kLongThreads : 1];
+  const int lane = threadIdx.x % LANES, group = threadIdx.x / LANES;
+  int64_t row;
+  if (LONG) {
+    row = __ldg(w.order + blockIdx.x);
+  } else {
+    row = (int64_t)blockIdx.x * kGroups + group;
+    if (row >= w.n_rows) return;
+  }
+  int64_t begin = load_index(w.ptr, w.ptr_bits, row), end = load_index(w.ptr, w.ptr_bits, row + 1);
+  const int64_t degree = end - begin;
+  if (!LONG && degree > w.split_threshold) return;
+  if (LONG) {
+    const int64_t slice = (degree + kGroups - 1) / kGroups;
+    begin = begin + group * slice;
+    end = begin + slice < end ? begin + slice : end;
+  }
   float value[kMaxI];
-  for (int f = lane; f < p.width; f += LANES) {
-    float acc = reducer == TGB_REDUCER_MEAN ? 0.0f : identity;      // the fold starts from the identity
-    for (int64_t e = begin; e < end; ++e) {
-      evaluate(p, in, load_index(w.idx, w.idx_bits, e), row, e, f, value);
-      const float m = value[p.num_instructions - 1];
-      if (reducer == TGB_REDUCER_MAX) acc = (acc != acc || m != m) ? __int_as_float(0x7fc00000) : fmaxf(acc, m);
-      else acc = __fadd_rn(acc, m);
+  for (int f0 = 0; f0 < p.width; f0 += LANES) {
+    const int f = f0 + lane;
+    // the fold starts from the identity; the slices of a long row start from the neutral element
+    float acc = reducer == TGB_REDUCER_MAX ? identity : ((LONG || reducer == TGB_REDUCER_MEAN) ? 0.0f : identity);
+    if (f < p.width) {
+      for (int64_t e = begin; e < end; ++e) {
+        evaluate(p, in, load_index(w.idx, w.idx_bits, e), row, e, f, value);
+        const float m = value[p.num_instructions - 1];
+        if (reducer == TGB_REDUCER_MAX) acc = (acc != acc || m != m) ? __int_as_float(0x7fc00000) : fmaxf(acc, m);
+        else acc = __fadd_rn(acc, m);
+      }
     }
-    if (reducer == TGB_REDUCER_MEAN) acc = __fdiv_rn(acc, (float)(end - begin));
-    out[row * p.width + f] = acc;
+    if (LONG) {
+      part[group * LANES + lane] = acc;
+      __syncthreads();
+      if (group == 0 && f < p.width) {
+        float total = reducer == TGB_REDUCER_SUM ? identity : acc;      // SUM: identity, then the slices in order
+        for (int g = reducer == TGB_REDUCER_SUM ? 0 : 1; g < kGroups; ++g) {
+          const float q = part[g * LANES + lane];
+          if (reducer == TGB_REDUCER_MAX) total = (total != total || q != q) ? __int_as_float(0x7fc00000) : fmaxf(total, q);
+          else total = __fadd_rn(total, q);
+        }
+        acc = total;
+      }
+      __syncthreads();
+      if (group != 0) continue;
+    }
+    if (f < p.width) {
+      if (reducer == TGB_REDUCER_MEAN) acc = __fdiv_rn(acc, (float)degree);
+      out[row * p.width + f] = acc;
+    }
   }
 }
 
 // Reverse mode over one traversal.  The pass owns, per ROW, the operands of its own side (dst and
 // tensor parameters in the destination-major pass, src in the source-major pass); EDGE operands are
 // written per entry by the destination-major pass.
-template <int LANES, bool SOURCE_MAJOR>
-__global__ void __launch_bounds__(kThreads)
+template <int LANES, bool SOURCE_MAJOR, bool LONG>
+__global__ void __launch_bounds__(LONG ? kLongThreads : kThreads)
 k_edge_program_bwd(const __grid_constant__ tgb_edge_program p, Operands in, Sinks sinks, Walk w, int reducer,
                    const void *__restrict__ degree_ptr, int degree_bits, const float *__restrict__ dy) {
-  const int64_t row = ((int64_t)blockIdx.x * kThreads + threadIdx.x) / LANES;
-  const int lane = threadIdx.x % LANES;
-  if (row >= w.n_rows) return;
+  constexpr int kGroups = (LONG ? kLongThreads : kThreads) / LANES;
+  __shared__ float part_full[LONG ? kMaxO * kLongThreads : 1];     // [operand][group][lane]
+  __shared__ float part_scalar[LONG ? kMaxO * kLongThreads : 1];   // [operand][group]
+  const int lane = threadIdx.x % LANES, group = threadIdx.x / LANES;
+  int64_t row;
+  if (LONG) {
+    row = __ldg(w.order + blockIdx.x);
+  } else {
+    row = (int64_t)blockIdx.x * kGroups + group;
+    if (row >= w.n_rows) return;
+  }
   const unsigned mask = group_mask<LANES>();
-  const int64_t begin = load_index(w.ptr, w.ptr_bits, row), end = load_index(w.ptr, w.ptr_bits, row + 1);
+  int64_t begin = load_index(w.ptr, w.ptr_bits, row), end = load_index(w.ptr, w.ptr_bits, row + 1);
+  if (!LONG && end - begin > w.split_threshold) return;
+  if (LONG) {            // contiguous slices of the row's entries, one per lane group
+    const int64_t slice = (end - begin + kGroups - 1) / kGroups;
+    begin = begin + group * slice;
+    end = begin + slice < end ? begin + slice : end;
+  }
+  // does this pass own operand k per row?
+  auto row_owned = [&](int k) {
+    if (k >= p.num_operands || sinks.ptr[k] == nullptr) return false;
+    const int role = p.operand_role[k];
+    return role != TGB_EP_ROLE_EDGE && (role == TGB_EP_ROLE_SRC) == SOURCE_MAJOR;
+  };
   float value[kMaxI], adjoint[kMaxI];
   float scalar_total[kMaxO];          // per-lane partial sums of the row-owned operands with one element per entity
 #pragma unroll
@@ -205,24 +269,54 @@ k_edge_program_bwd(const __grid_constant__ tgb_edge_program p, Operands in, Sink
         }
       }
     }
+    if (LONG) {          // the slices' sums of this chunk, added in slice order by the first group
 #pragma unroll
-    for (int k = 0; k < kMaxO; ++k) {
-      if (k >= p.num_operands || sinks.ptr[k] == nullptr) continue;
-      const int role = p.operand_role[k];
-      if (role == TGB_EP_ROLE_EDGE || (role == TGB_EP_ROLE_SRC) != SOURCE_MAJOR) continue;
-      const bool full = p.operand_modulus[k] == 0 || p.width == 1;
-      if (full && live) sinks.ptr[k][row * p.width + f] = full_total[k];
+      for (int k = 0; k < kMaxO; ++k) part_full[k * kLongThreads + threadIdx.x] = full_total[k];
+      __syncthreads();
+      if (group == 0) {
+#pragma unroll
+        for (int k = 0; k < kMaxO; ++k) {
+          float total = 0.0f;
+          for (int g = 0; g < kGroups; ++g) total += part_full[k * kLongThreads + g * LANES + lane];
+          full_total[k] = total;
+        }
+      }
+      __syncthreads();
+    }
+    if (!LONG || group == 0) {
+#pragma unroll
+      for (int k = 0; k < kMaxO; ++k) {
+        if (!row_owned(k)) continue;
+        const bool full = p.operand_modulus[k] == 0 || p.width == 1;
+        if (full && live) sinks.ptr[k][row * p.width + f] = full_total[k];
+      }
     }
   }
+  if constexpr (LONG) {
 #pragma unroll
-  for (int k = 0; k < kMaxO; ++k) {
-    if (k >= p.num_operands || sinks.ptr[k] == nullptr) continue;
-    const int role = p.operand_role[k];
-    if (role == TGB_EP_ROLE_EDGE || (role == TGB_EP_ROLE_SRC) != SOURCE_MAJOR) continue;
-    const bool full = p.operand_modulus[k] == 0 || p.width == 1;
-    if (full) continue;
-    const float total = group_sum<LANES>(scalar_total[k], mask);
-    if (lane == 0) sinks.ptr[k][row] = total;
+    for (int k = 0; k < kMaxO; ++k) {
+      const float total = group_sum<LANES>(scalar_total[k], mask);
+      if (lane == 0) part_scalar[k * kLongThreads + group] = total;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+      for (int k = 0; k < kMaxO; ++k) {
+        if (!row_owned(k) || p.operand_modulus[k] == 0 || p.width == 1) continue;
+        float total = 0.0f;
+        for (int g = 0; g < kGroups; ++g) total += part_scalar[k * kLongThreads + g];
+        sinks.ptr[k][row] = total;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < kMaxO; ++k) {
+      if (!row_owned(k)) continue;
+      const bool full = p.operand_modulus[k] == 0 || p.width == 1;
+      if (full) continue;
+      const float total = group_sum<LANES>(scalar_total[k], mask);
+      if (lane == 0) sinks.ptr[k][row] = total;
+    }
   }
 }
 
@@ -253,6 +347,7 @@ int lanes_for_width(int width) {
 
 int32_t check_program(const tgb_csr_plan *plan, const tgb_edge_program *p, const void *const *operands) {
   if (!plan || !p || !operands) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null argument");
+  if (plan->fwd.eid) TGB_FAIL(TGB_STATUS_UNSUPPORTED, "edge programs do not take a plan with an edge map");
   if (p->num_instructions < 1 || p->num_instructions > kMaxI || p->num_operands < 1 || p->num_operands > kMaxO)
     TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "program size out of range");
   if (p->width < 1) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "message width must be positive");
@@ -282,7 +377,8 @@ int32_t check_program(const tgb_csr_plan *plan, const tgb_edge_program *p, const
 }
 
 Walk forward_walk(const tgb_csr_plan *plan) {
-  return Walk{plan->fwd.ptr, plan->fwd.idx, nullptr, plan->fwd.ptr_bits, plan->fwd.idx_bits, plan->num_dst};
+  return Walk{plan->fwd.ptr, plan->fwd.idx, nullptr, plan->fwd.ptr_bits, plan->fwd.idx_bits, plan->num_dst,
+              plan->fwd.order, plan->fwd.n_long, kSplitThreshold};
 }
 
 }  // namespace
@@ -315,11 +411,16 @@ extern "C" int32_t tgb_edge_program_fwd(const tgb_csr_plan *plan, const tgb_edge
   const int lanes = lanes_for_width(program->width);
   const unsigned blocks = (unsigned)ceil_div(plan->num_dst * lanes, kThreads);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-#define TGB_FWD(L) \
-  k_edge_program_fwd<L><<<blocks, kThreads, 0, st>>>(*program, in, w, reducer, identity, static_cast<float *>(out))
+#define TGB_FWD(L)                                                                                          \
+  k_edge_program_fwd<L, false><<<blocks, kThreads, 0, st>>>(*program, in, w, reducer, identity,             \
+                                                            static_cast<float *>(out));                     \
+  if (w.n_long > 0)                                                                                         \
+    k_edge_program_fwd<L, true><<<(unsigned)w.n_long, kLongThreads, 0, st>>>(*program, in, w, reducer, identity, \
+                                                                             static_cast<float *>(out))
   TGB_EP_LANES(lanes, TGB_FWD)
 #undef TGB_FWD
   TGB_LAUNCHED();
+  if (w.n_long > 0) TGB_LAUNCHED();
   return TGB_STATUS_OK;
 }
 
@@ -353,21 +454,29 @@ int32_t backward(bool source_major, const tgb_csr_plan *plan, const tgb_edge_pro
   if (!any) return TGB_STATUS_OK;
   Walk w = forward_walk(plan);
   if (source_major) w = Walk{plan->bwd.ptr, plan->bwd.idx, plan->bwd.eid, plan->bwd.ptr_bits, plan->bwd.idx_bits,
-                             plan->num_src};
+                             plan->num_src, plan->bwd.order, plan->bwd.n_long, kSplitThreshold};
   if (w.n_rows == 0) return TGB_STATUS_OK;
   const int lanes = lanes_for_width(program->width);
   const unsigned blocks = (unsigned)ceil_div(w.n_rows * lanes, kThreads);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-#define TGB_BWD(L)                                                                                               \
-  if (source_major)                                                                                              \
-    k_edge_program_bwd<L, true><<<blocks, kThreads, 0, st>>>(*program, in, sinks, w, reducer, plan->fwd.ptr,    \
-                                                             plan->fwd.ptr_bits, static_cast<const float *>(dy)); \
-  else                                                                                                           \
-    k_edge_program_bwd<L, false><<<blocks, kThreads, 0, st>>>(*program, in, sinks, w, reducer, plan->fwd.ptr,   \
-                                                              plan->fwd.ptr_bits, static_cast<const float *>(dy))
+#define TGB_BWD(L)                                                                                            \
+  if (source_major) {                                                                                         \
+    k_edge_program_bwd<L, true, false><<<blocks, kThreads, 0, st>>>(*program, in, sinks, w, reducer,          \
+        plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy));                                   \
+    if (w.n_long > 0)                                                                                         \
+      k_edge_program_bwd<L, true, true><<<(unsigned)w.n_long, kLongThreads, 0, st>>>(*program, in, sinks, w,  \
+          reducer, plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy));                        \
+  } else {                                                                                                    \
+    k_edge_program_bwd<L, false, false><<<blocks, kThreads, 0, st>>>(*program, in, sinks, w, reducer,         \
+        plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy));                                   \
+    if (w.n_long > 0)                                                                                         \
+      k_edge_program_bwd<L, false, true><<<(unsigned)w.n_long, kLongThreads, 0, st>>>(*program, in, sinks, w, \
+          reducer, plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy));                        \
+  }
   TGB_EP_LANES(lanes, TGB_BWD)
 #undef TGB_BWD
   TGB_LAUNCHED();
+  if (w.n_long > 0) TGB_LAUNCHED();
   return TGB_STATUS_OK;
 }
 
