@@ -70,6 +70,9 @@ def parse_args():
                    help="vertex ids relabelled at random (what Graph500-style generators prescribe; contiguous "
                         "ranges then hold the same mix of degrees) or the generator's ids with hubs at low ids")
     p.add_argument("--waves", type=int, default=None, help="forward halo exchange waves (multi-GPU)")
+    p.add_argument("--halo", default="nccl", choices=("nccl", "push"),
+                   help="multi-GPU halo transport: grouped NCCL send/recv, or stores into the peers' "
+                        "ghost buffers through CUDA IPC windows")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-check", action="store_true")
@@ -377,7 +380,8 @@ def run_halo_gcn(args):
     runtime = None
     if world > 1:
         graph = tg.Graph.from_csr_shard(row_ptr, col, num_nodes=N, first_row=first).halo(tg.DeviceMesh("cuda", world))
-        runtime = DistributedRuntime(NCCLTransport(device=device), trace=True, waves=args.waves)
+        runtime = DistributedRuntime(NCCLTransport(device=device), trace=True, waves=args.waves,
+                                     push=args.halo == "push")
         with runtime:
             shard = shard_plan_for(graph, runtime)
         for relation in (shard.graph_own, shard.graph_ghost):
@@ -532,6 +536,8 @@ def run_halo_gcn(args):
         dist.all_gather(everyone, mine)
         config.update({
             "waves": len(shard.waves),
+            "halo_transport": ("stores into the peers' ghost buffers through CUDA IPC windows + one-element "
+                               "all-reduce signals" if args.halo == "push" else "grouped NCCL send/recv"),
             "per_rank_edges_rows_ghosts_ghostedges": torch.stack(gathered).tolist(),
             "halo_bytes_per_layer_rank0": int(shard.ghosts.numel()) * F * 4,
             "phase_ms_per_rank": {name: [round(float(r[i]), 3) for r in everyone]

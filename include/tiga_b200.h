@@ -396,6 +396,24 @@ TGB_API int32_t tgb_linear_dw_f32(const void *a, const void *dout, void *dw,
 TGB_API int32_t tgb_linear_dw_partials(int64_t M, int32_t *count);
 
 /* ------------------------------------------------------------------------
+ * Peer windows (one node): device memory of another process mapped into this
+ * one, so that tgb_rows_gather / tgb_peer_copy store straight into a peer's halo
+ * buffer over NVLink instead of packing, sending and receiving
+ * (python/tiga/distributed/nccl.py:256-284 of the reference moves the same rows
+ * through ncclSend / ncclRecv).  Legacy CUDA IPC; no multicast object is made.
+ * Completion is signalled by the caller's own stream-ordered collective.
+ * ------------------------------------------------------------------------ */
+
+/* 64-byte handle of the allocation that holds `ptr`, and ptr's byte offset in it. */
+TGB_API int32_t tgb_peer_export(const void *ptr, void *handle64, uint64_t *offset);
+/* Maps a peer's allocation (a handle from tgb_peer_export in another process)
+ * into this process; open a handle once per process and close it at the end. */
+TGB_API int32_t tgb_peer_open(const void *handle64, uint64_t *mapped_base);
+TGB_API int32_t tgb_peer_close(uint64_t mapped_base);
+/* Asynchronous device-to-device copy to any mapped address (peer or local). */
+TGB_API int32_t tgb_peer_copy(uint64_t dst, const void *src, uint64_t bytes, uint64_t stream);
+
+/* ------------------------------------------------------------------------
  * Dynamic relations: radius and k-nearest-neighbour builders, and the fused
  * radius consumer that never materialises the relation.
  *

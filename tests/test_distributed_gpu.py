@@ -20,7 +20,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, result_dir, shard_only=False, waves=1, index_dtype=torch.int64, F=64):
+def _worker(rank, world, port, result_dir, shard_only=False, waves=1, index_dtype=torch.int64, F=64, push=False):
     for path in (ROOT, os.path.join(ROOT, "tiga-lang_b200")):
         sys.path.insert(0, path)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -55,14 +55,14 @@ def _worker(rank, world, port, result_dir, shard_only=False, waves=1, index_dtyp
         else:
             graph = tg.Graph.from_csr(row_ptr.to(index_dtype), col.to(index_dtype), num_src=n).halo(
                 tg.DeviceMesh("cuda", world))
-        runtime = DistributedRuntime(NCCLTransport(device=device), waves=waves)
+        runtime = DistributedRuntime(NCCLTransport(device=device), waves=waves, push=push)
         with runtime:
             shard = shard_plan_for(graph, runtime)
             b, e = shard.begin, shard.end
             lo, hi = int(row_ptr[b]), int(row_ptr[e])
             xs = x[b:e].clone().requires_grad_()
             ws = w[lo:hi].clone().requires_grad_()
-            for _ in range(2):     # second call reuses the cached shard plan
+            for _ in range(3 if push else 2):     # later calls reuse the cached shard plan (and window slots)
                 out = WeightedSum()(graph=graph, src={"x": xs}, dst={}, edge={"weight": ws})
                 dx, dw = torch.autograd.grad(out, (xs, ws), dy[b:e])
         torch.cuda.synchronize()
@@ -73,10 +73,10 @@ def _worker(rank, world, port, result_dir, shard_only=False, waves=1, index_dtyp
         dist.destroy_process_group()
 
 
-def _run_and_compare(tmp_path, oracle, world, shard_only, waves, index_dtype, F):
+def _run_and_compare(tmp_path, oracle, world, shard_only, waves, index_dtype, F, push=False):
     from conftest import assert_sum_close
 
-    mp.start_processes(_worker, args=(world, _free_port(), str(tmp_path), shard_only, waves, index_dtype, F),
+    mp.start_processes(_worker, args=(world, _free_port(), str(tmp_path), shard_only, waves, index_dtype, F, push),
                        nprocs=world, join=True, start_method="spawn")
     from baseline import synthetic as syn
 
@@ -114,3 +114,16 @@ def test_two_gpu_halo_matches_oracle(tmp_path, oracle, shard_only, index_dtype, 
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
 def test_four_gpu_halo_in_waves_matches_oracle(tmp_path, oracle):
     _run_and_compare(tmp_path, oracle, 4, True, 3, torch.int64, 64)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("F", (64, 6))
+def test_two_gpu_halo_through_peer_windows_matches_oracle(tmp_path, oracle, F):
+    """push=True: halo rows are stored straight into the peer's ghost buffer (CUDA IPC window), the
+    cotangents straight into the owner's landing window; signals are one-element all-reduces."""
+    _run_and_compare(tmp_path, oracle, 2, True, 1, torch.int64, F, push=True)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
+def test_four_gpu_halo_through_peer_windows_in_waves_matches_oracle(tmp_path, oracle):
+    _run_and_compare(tmp_path, oracle, 4, True, 3, torch.int64, 64, push=True)

@@ -6,6 +6,8 @@
 // reverse_halo_device).  The ids of one call are unique (a peer asks for / returns each row
 // once), so the add is a plain read-modify-write: no atomics, deterministic.
 // HBM bound: F*4 bytes read + written (gather), read + read + written (scatter-add) per row.
+#include <cstring>
+
 #include "tgb_common.cuh"
 
 namespace tgb {
@@ -90,4 +92,74 @@ extern "C" int32_t tgb_rows_gather(const void *rows, const void *ids, void *pack
 extern "C" int32_t tgb_rows_scatter_add(void *rows, const void *ids, const void *packed, int64_t n, int64_t F,
                                         uint64_t stream) {
   return tgb::move_rows(true, rows, ids, const_cast<void *>(packed), n, F, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Peer windows: device memory of another process on the same node, mapped into this process so that
+// the row movers above (and plain copies) can store straight into a peer's halo buffer over NVLink.
+// Legacy CUDA IPC only (no multicast object is ever created).  The reference moves halo rows through
+// its transport's send / recv (python/tiga/distributed/nccl.py:256-284); a window replaces the pack
+// buffer + send + receive of one direction by stores into the receiver's own buffer.
+// ---------------------------------------------------------------------------
+#include <cuda.h>
+
+namespace {
+
+typedef CUresult (*AddressRangeFn)(CUdeviceptr *, size_t *, CUdeviceptr);
+
+int32_t allocation_base(const void *ptr, uint64_t *base) {
+  static AddressRangeFn fn = nullptr;
+  if (!fn) {
+    void *entry = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    cudaError_t err = cudaGetDriverEntryPoint("cuMemGetAddressRange", &entry, cudaEnableDefault, &query);
+    if (err != cudaSuccess || query != cudaDriverEntryPointSuccess || !entry)
+      TGB_FAIL(TGB_STATUS_INTERNAL, "cuMemGetAddressRange is not available from the driver");
+    fn = reinterpret_cast<AddressRangeFn>(entry);
+  }
+  CUdeviceptr start = 0;
+  size_t size = 0;
+  const CUresult rc = fn(&start, &size, reinterpret_cast<CUdeviceptr>(ptr));
+  if (rc != CUDA_SUCCESS) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "not a device allocation (driver code %d)", (int)rc);
+  *base = static_cast<uint64_t>(start);
+  return TGB_STATUS_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t tgb_peer_export(const void *ptr, void *handle64, uint64_t *offset) {
+  if (!ptr || !handle64 || !offset) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handles are 64 bytes");
+  uint64_t base = 0;
+  const int32_t rc = allocation_base(ptr, &base);
+  if (rc) return rc;
+  cudaIpcMemHandle_t handle;
+  TGB_CUDA(cudaIpcGetMemHandle(&handle, reinterpret_cast<void *>(base)));
+  memcpy(handle64, &handle, 64);
+  *offset = reinterpret_cast<uint64_t>(ptr) - base;
+  return TGB_STATUS_OK;
+}
+
+extern "C" int32_t tgb_peer_open(const void *handle64, uint64_t *mapped_base) {
+  if (!handle64 || !mapped_base) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
+  cudaIpcMemHandle_t handle;
+  memcpy(&handle, handle64, 64);
+  void *mapped = nullptr;
+  TGB_CUDA(cudaIpcOpenMemHandle(&mapped, handle, cudaIpcMemLazyEnablePeerAccess));
+  *mapped_base = reinterpret_cast<uint64_t>(mapped);
+  return TGB_STATUS_OK;
+}
+
+extern "C" int32_t tgb_peer_close(uint64_t mapped_base) {
+  if (!mapped_base) return TGB_STATUS_OK;
+  TGB_CUDA(cudaIpcCloseMemHandle(reinterpret_cast<void *>(mapped_base)));
+  return TGB_STATUS_OK;
+}
+
+extern "C" int32_t tgb_peer_copy(uint64_t dst, const void *src, uint64_t bytes, uint64_t stream) {
+  if (bytes == 0) return TGB_STATUS_OK;
+  if (!dst || !src) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
+  TGB_CUDA(cudaMemcpyAsync(reinterpret_cast<void *>(dst), src, bytes, cudaMemcpyDeviceToDevice,
+                           reinterpret_cast<cudaStream_t>(stream)));
+  return TGB_STATUS_OK;
 }

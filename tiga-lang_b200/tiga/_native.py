@@ -63,6 +63,10 @@ _SIGNATURES = {
     "tgb_selftest_bounded_wait": (_i32, [_vp, ctypes.c_uint32, _vp, _u64]),
     "tgb_softmax_field_fwd": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _u64]),
     "tgb_softmax_field_bwd": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp, _u64]),
+    "tgb_peer_export": (_i32, [_vp, _vp, ctypes.POINTER(_u64)]),
+    "tgb_peer_open": (_i32, [_vp, ctypes.POINTER(_u64)]),
+    "tgb_peer_close": (_i32, [_u64]),
+    "tgb_peer_copy": (_i32, [_u64, _vp, _u64, _u64]),
     "tgb_cell_directory_sizes": (_i32, [_i64, _i32, ctypes.POINTER(_u64), ctypes.POINTER(_u64)]),
     "tgb_cell_directory_build": (_i32, [_vp, _i64, _vp, _vp, _u64, _vp, _u64, _u64]),
     "tgb_radius_row_ptr": (_i32, [_vp, _i64, _vp, _vp, _f32, _i32, _vp, _vp, _vp, _u64, _u64]),

@@ -153,18 +153,58 @@ class DistributedRuntime:
     python/tiga/distributed/transport.py:1311-1370)."""
 
     def __init__(self, transport: ProcessGroupTransport, *, backend=None, trace: bool = False,
-                 waves: int | None = None):
+                 waves: int | None = None, push: bool = False, window_slots: int = 4):
         self.transport = transport
         self.backend = backend or NativeBackend()
         self._token = None
         self.trace = bool(trace)
         self.last_execution_trace = []
+        # push=True (one node, CUDA): halo rows are stored straight into the receivers' ghost buffers
+        # through peer windows (see peer.py) instead of pack + send / recv; off by default
+        self.push = bool(push)
+        self.window_slots = max(int(window_slots), 2)
+        self._windows = {}
+        self._signals = None
+        self._comm_stream = None
         # the forward halo arrives in `waves` grouped exchanges; the ghost-source edges of a wave
         # are reduced as soon as that wave has landed, while the later waves are still in flight
         self.waves = DEFAULT_WAVES if waves is None else max(int(waves), 1)
 
     def reset_trace(self) -> None:
         self.last_execution_trace = []
+
+    # ---------------------------------------------------------------- peer windows (push=True)
+    def comm_stream(self, device):
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=device)
+        return self._comm_stream
+
+    def signals(self, device):
+        from .peer import PushSignals
+
+        if self._signals is None:
+            self._signals = PushSignals(self.transport, device)
+        return self._signals
+
+    def halo_windows(self, shard: "ShardPlan", F: int, device):
+        """(ghost window, cotangent window) of a shard for rows of F floats; created collectively on
+        first use.  A slot of the ghost window is this rank's ghost buffer [G, F]; a slot of the
+        cotangent window holds, peer after peer, the cotangent rows the peers return."""
+        from .peer import PeerWindow
+
+        key = (id(shard), int(F))
+        if key not in self._windows:
+            row_bytes = 4 * int(F)
+            ghost_layout = {"recv_offsets": [o for o, _ in shard.recv_offsets]}
+            ghost = PeerWindow(self.transport, device, int(shard.ghosts.numel()) * row_bytes, self.window_slots,
+                               ghost_layout)
+            starts, total = [], 0
+            for ids in shard.send_ids:
+                starts.append(total)
+                total += int(ids.numel())
+            landing = PeerWindow(self.transport, device, total * row_bytes, 2, {"starts": starts})
+            self._windows[key] = (ghost, landing, starts)
+        return self._windows[key]
 
     def mark(self, name: str, device) -> None:
         if self.trace and torch.device(device).type == "cuda":
@@ -358,6 +398,79 @@ def shard_plan_for(graph: Graph, runtime: DistributedRuntime) -> ShardPlan:
     return cache[key]
 
 
+def _push_forward(runtime, shard: ShardPlan, window, slot: int, rows, w_own, w_ghost, F: int):
+    """Forward halo through peer windows: every wave's rows are gathered straight into the
+    receivers' ghost buffers by the row mover, on the communication stream, and a one-element
+    all-reduce after the wave tells every rank that the wave has landed everywhere."""
+    from .peer import push_rows
+
+    backend = runtime.backend
+    device = rows.device
+    compute = torch.cuda.current_stream(device)
+    comm = runtime.comm_stream(device)
+    signals = runtime.signals(device)
+    ghost_x = window.view(slot, (int(shard.ghosts.numel()), F))
+    row_bytes = 4 * F
+    comm.wait_stream(compute)                              # the rows to send are final
+    if window.released[slot] is not None:
+        comm.wait_event(window.released[slot])             # this rank's last read of the slot
+    landed = []
+    with torch.cuda.stream(comm):
+        signals.barrier()                                  # ... and every other rank's: the slot is free everywhere
+        for pairs, _ in shard.waves:
+            for _, target in pairs:
+                ids = shard.send_ids[target]
+                if ids.numel():
+                    where = window.peer_layout[target]["recv_offsets"][shard.rank] * row_bytes
+                    push_rows(rows, ids, window.address(target, slot, where))
+            signals.barrier()
+            landed.append(comm.record_event())
+    rows.record_stream(comm)
+    runtime.mark("forward pack + start exchange", device)
+    out = backend.forward(shard.graph_own, rows, w_own)
+    runtime.mark("forward owned-source part", device)
+    for (_, relation), event in zip(shard.waves, landed):
+        compute.wait_event(event)
+        runtime.mark("forward exposed halo wait", device)
+        if relation.resolve_csr()[1].numel():
+            out = backend.forward(relation, ghost_x, w_ghost, accumulate_into=out)
+        runtime.mark("forward ghost-source part", device)
+    return out, ghost_x
+
+
+def _push_cotangents(runtime, shard: ShardPlan, d_ghost, F: int):
+    """Reverse halo through peer windows: each owner's slice of the ghost cotangents is copied into
+    that owner's landing window; returns (landed, (event, window, slot))."""
+    from .peer import push_block
+
+    device = d_ghost.device
+    _, landing, starts = runtime.halo_windows(shard, F, device)
+    slot = landing.acquire()
+    if slot is None:
+        raise RuntimeError("the cotangent window is still in use: backward calls must not overlap")
+    compute = torch.cuda.current_stream(device)
+    comm = runtime.comm_stream(device)
+    signals = runtime.signals(device)
+    row_bytes = 4 * F
+    comm.wait_stream(compute)                              # d_ghost is final
+    if landing.released[slot] is not None:
+        comm.wait_event(landing.released[slot])
+    with torch.cuda.stream(comm):
+        signals.barrier()                                  # the landing slot is free on every rank
+        for owner, (offset, count) in enumerate(shard.recv_offsets):
+            if count and owner != shard.rank:
+                where = landing.peer_layout[owner]["starts"][shard.rank] * row_bytes
+                push_block(d_ghost[offset:offset + count], landing.address(owner, slot, where))
+        signals.barrier()
+        done = comm.record_event()
+    d_ghost.record_stream(comm)
+    total_rows = starts[-1] + int(shard.send_ids[-1].numel()) if starts else 0
+    buffer = landing.view(slot, (max(total_rows, 1), F))
+    landed = [(p, ids, buffer[starts[p]:starts[p] + ids.numel()]) for p, ids in enumerate(shard.send_ids)
+              if ids.numel()]
+    return landed, (done, landing, slot)
+
+
 class _HaloWeightedSum(torch.autograd.Function):
     """out[owned rows] = sum over local edges of w * x[source], sources owned or ghost."""
 
@@ -372,23 +485,34 @@ class _HaloWeightedSum(torch.autograd.Function):
         runtime.mark("forward:begin", device)
         if hasattr(backend, "begin_forward"):
             backend.begin_forward(shard)
-        ghost_x = torch.empty((int(shard.ghosts.numel()), F), dtype=rows.dtype, device=rows.device)
-        packed = {p: backend.pack_rows(rows, ids) for p, ids in enumerate(shard.send_ids) if ids.numel()}
-        in_flight = []
-        for pairs, relation in shard.waves:             # every wave is one grouped exchange
-            receives = [(source, ghost_x[o:o + c]) for source, _ in pairs
-                        for o, c in (shard.recv_offsets[source],) if c]
-            sends = [(target, packed[target]) for _, target in pairs if target in packed]
-            in_flight.append((transport.exchange(sends=sends, receives=receives), relation))
-        runtime.mark("forward pack + start exchange", device)
-        out = backend.forward(shard.graph_own, rows, w_own)              # ... while owned-source edges reduce
-        runtime.mark("forward owned-source part", device)
-        for works, relation in in_flight:               # a wave's edges reduce while later waves are in flight
-            transport.wait(works)
-            runtime.mark("forward exposed halo wait", device)
-            if relation.resolve_csr()[1].numel():
-                out = backend.forward(relation, ghost_x, w_ghost, accumulate_into=out)
-            runtime.mark("forward ghost-source part", device)
+        slot = window = None
+        if runtime.push and rows.is_cuda and rows.dtype == torch.float32:
+            window, _, _ = runtime.halo_windows(shard, F, device)
+            slot = window.acquire()                     # None: every slot is still held by a forward
+        if slot is not None:
+            out, ghost_x = _push_forward(runtime, shard, window, slot, rows, w_own, w_ghost, F)
+        else:
+            ghost_x = torch.empty((int(shard.ghosts.numel()), F), dtype=rows.dtype, device=rows.device)
+            packed = {p: backend.pack_rows(rows, ids) for p, ids in enumerate(shard.send_ids) if ids.numel()}
+            in_flight = []
+            for pairs, relation in shard.waves:             # every wave is one grouped exchange
+                receives = [(source, ghost_x[o:o + c]) for source, _ in pairs
+                            for o, c in (shard.recv_offsets[source],) if c]
+                sends = [(target, packed[target]) for _, target in pairs if target in packed]
+                in_flight.append((transport.exchange(sends=sends, receives=receives), relation))
+            runtime.mark("forward pack + start exchange", device)
+            out = backend.forward(shard.graph_own, rows, w_own)              # ... while owned-source edges reduce
+            runtime.mark("forward owned-source part", device)
+            for works, relation in in_flight:               # a wave's edges reduce while later waves are in flight
+                transport.wait(works)
+                runtime.mark("forward exposed halo wait", device)
+                if relation.resolve_csr()[1].numel():
+                    out = backend.forward(relation, ghost_x, w_ghost, accumulate_into=out)
+                runtime.mark("forward ghost-source part", device)
+        ctx.window, ctx.slot = window, slot
+        if slot is not None and not (torch.is_grad_enabled() and (x.requires_grad or (w is not None and w.requires_grad))):
+            window.release(slot, torch.cuda.current_stream(device))      # no backward will read the slot
+            ctx.slot = None
         ctx.shard, ctx.runtime = shard, runtime
         ctx.x_shape, ctx.w_shape = x.shape, None if w is None else w.shape
         ctx.save_for_backward(rows, w_flat, ghost_x)
@@ -405,20 +529,26 @@ class _HaloWeightedSum(torch.autograd.Function):
         dy = grad_output.contiguous().reshape(shard.owned, -1)
         F = dy.shape[1]
         dx = dw = None
-        works, landed = [], []
+        works, landed, pushed = [], [], None
         device = dy.device
         runtime.mark("backward:begin", device)
         if need_x:
             # ghost cotangents go back to their owners while everything else of the backward runs
-            if shard.edges_ghost.numel() or any(ids.numel() for ids in shard.send_ids):
+            use_push = runtime.push and dy.is_cuda and dy.dtype == torch.float32
+            # the pushed exchange is collective (its signals are all-reduces): every rank takes part,
+            # also one without ghosts or requests
+            if use_push or shard.edges_ghost.numel() or any(ids.numel() for ids in shard.send_ids):
                 d_ghost = (backend.backward_dx(shard.graph_ghost, dy, w_ghost) if shard.ghosts.numel()
                            else dy.new_zeros((0, F)))
-                landed = [(p, ids, torch.empty((ids.numel(), F), dtype=dy.dtype, device=dy.device))
-                          for p, ids in enumerate(shard.send_ids) if ids.numel()]
-                works = transport.exchange(
-                    sends=[(p, d_ghost[o:o + c]) for p, (o, c) in enumerate(shard.recv_offsets)
-                           if c and p != shard.rank],
-                    receives=[(p, buffer) for p, _, buffer in landed])
+                if use_push:
+                    landed, pushed = _push_cotangents(runtime, shard, d_ghost, F)
+                else:
+                    landed = [(p, ids, torch.empty((ids.numel(), F), dtype=dy.dtype, device=dy.device))
+                              for p, ids in enumerate(shard.send_ids) if ids.numel()]
+                    works = transport.exchange(
+                        sends=[(p, d_ghost[o:o + c]) for p, (o, c) in enumerate(shard.recv_offsets)
+                               if c and p != shard.rank],
+                        receives=[(p, buffer) for p, _, buffer in landed])
             runtime.mark("backward ghost cotangents + start exchange", device)
             dx = backend.backward_dx(shard.graph_own, dy, w_own)
             runtime.mark("backward dx owned part", device)
@@ -431,12 +561,20 @@ class _HaloWeightedSum(torch.autograd.Function):
             dw = dw.reshape(ctx.w_shape)
             runtime.mark("backward dw", device)
         if need_x:
-            transport.wait(works)
+            if pushed is not None:
+                torch.cuda.current_stream(device).wait_event(pushed[0])   # every peer's rows have landed
+            else:
+                transport.wait(works)
             runtime.mark("backward exposed cotangent wait", device)
             for _, ids, buffer in landed:            # fixed peer order: deterministic
                 backend.add_rows(dx, ids, buffer)
+            if pushed is not None:
+                pushed[1].release(pushed[2], torch.cuda.current_stream(device))
             dx = dx.reshape(ctx.x_shape)
             runtime.mark("backward add received cotangents", device)
+        if ctx.slot is not None:                     # the ghost rows of this call have been read for the last time
+            ctx.window.release(ctx.slot, torch.cuda.current_stream(device))
+            ctx.slot = None
         return dx, dw, None, None
 
 
