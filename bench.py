@@ -601,27 +601,43 @@ def run_e2e(args, step, x, weight, linears, traversed, world):
     torch.cuda.empty_cache()
     input_bytes = sum(t.numel() * t.element_size() for t in host_in)
     free_bytes, _ = torch.cuda.mem_get_info(device)
-    slots = 2 if free_bytes - 2 * input_bytes > 16e9 else 1
+    slots = 2 if free_bytes - 3 * input_bytes > 16e9 else 1       # two input sets and the staging set
     packed = sum(m.numel() for m in linears)
     host_out = [[torch.empty_like(host_in[0]).pin_memory(), torch.empty_like(host_in[1]).pin_memory(),
                  torch.empty(packed, dtype=torch.float32).pin_memory()] for _ in range(slots)]
     dev_in = [[torch.empty_like(t, device=device) for t in host_in] for _ in range(slots)]
+    # the gradients leave through one persistent staging set: the step's own tensors are released as soon
+    # as they are copied into it (a device-to-device copy on the compute stream), so the caching allocator
+    # never holds blocks back for the download stream and never has to synchronise to find memory
+    dev_out = [torch.empty_like(t, device=device) for t in host_out[0]]
     h2d = sum(t.numel() * t.element_size() for t in host_in)
     d2h = sum(t.numel() * t.element_size() for t in host_out[0])
     compute = torch.cuda.current_stream(device)
     upload, download = torch.cuda.Stream(device), torch.cuda.Stream(device)
 
+    timeline = []     # per step: events at the start / end of its upload, compute and download
+
+    def stamp(stream):
+        event = torch.cuda.Event(enable_timing=True)
+        event.record(stream)
+        return event
+
     def run(steps):
         uploaded, computed, downloaded = [None] * slots, [None] * slots, [None] * slots
+        staged = {"free": None}
+        del timeline[:]
+        timeline.extend({} for _ in range(steps))
 
         def start_upload(i):
             slot = i % slots
             with torch.cuda.stream(upload):
                 if computed[slot] is not None:           # the step that read this input slot is done
                     upload.wait_event(computed[slot])
+                timeline[i]["upload"] = [stamp(upload)]
                 for d, h in zip(dev_in[slot], host_in):
                     d.copy_(h, non_blocking=True)
                 uploaded[slot] = upload.record_event()
+                timeline[i]["upload"].append(stamp(upload))
 
         start_upload(0)
         for i in range(steps):
@@ -629,24 +645,32 @@ def run_e2e(args, step, x, weight, linears, traversed, world):
             if slots > 1 and i + 1 < steps:
                 start_upload(i + 1)
             compute.wait_event(uploaded[slot])
+            timeline[i]["compute"] = [stamp(compute)]
             leaves = [d.detach().requires_grad_() for d in dev_in[slot]]
             grads = step(leaves[0], leaves[1], leaves[2:])
+            if staged["free"] is not None:
+                compute.wait_event(staged["free"])        # the previous step's download has read the staging set
+            for staging, g in zip(dev_out, grads):
+                staging.copy_(g.reshape(staging.shape))
             computed[slot] = compute.record_event()
+            timeline[i]["compute"].append(stamp(compute))
             if slots == 1 and i + 1 < steps:
                 start_upload(i + 1)
             with torch.cuda.stream(download):
                 download.wait_event(computed[slot])
                 if downloaded[slot] is not None:
                     downloaded[slot].synchronize()        # the host buffer is free again
-                for h, g in zip(host_out[slot], grads):
-                    g.record_stream(download)
-                    h.copy_(g, non_blocking=True)
+                timeline[i]["download"] = [stamp(download)]
+                for h, staging in zip(host_out[slot], dev_out):
+                    h.copy_(staging, non_blocking=True)
                 downloaded[slot] = download.record_event()
+                staged["free"] = downloaded[slot]
+                timeline[i]["download"].append(stamp(download))
             del grads, leaves
         torch.cuda.synchronize(device)
 
     run(2)
-    steps = max(3, min(args.steps, 5 if h2d > 4e9 else 10))
+    steps = max(3, min(args.steps, 10))
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize(device)
     begin.record()
@@ -654,6 +678,9 @@ def run_e2e(args, step, x, weight, linears, traversed, world):
     end.record()
     torch.cuda.synchronize(device)
     ms = begin.elapsed_time(end) / steps
+    # when each phase of each timed step ran on the device, in ms from the start of the timed region
+    phases = [{name: [round(begin.elapsed_time(a), 1), round(begin.elapsed_time(b), 1)]
+               for name, (a, b) in entry.items()} for entry in timeline]
     if world > 1:
         import torch.distributed as dist
 
@@ -662,7 +689,8 @@ def run_e2e(args, step, x, weight, linears, traversed, world):
         ms = float(slowest.item())
     return {"value": round(traversed / (ms * 1e-3) / 1e9, 4), "unit": UNIT, "ms_per_step": round(ms, 3),
             "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": steps,
-            "pipeline": f"upload / compute / download on three streams, {slots} input slot(s); bytes are per rank"}
+            "pipeline": f"upload / compute / download on three streams, {slots} input slot(s); bytes are per rank",
+            "timeline_ms": phases}
 
 
 # --------------------------------------------------------------------------- CPU arm

@@ -77,6 +77,13 @@ TGB_API const char *tgb_last_error(void);
 TGB_API const char *tgb_version(void);
 /* number of kernels this library has launched from the calling process */
 TGB_API int64_t tgb_launch_count(void);
+/* Copies one int32 (an error word of the tensor-core entry points) from device
+ * memory to pinned host memory with a one-thread kernel on `stream`: no copy
+ * engine is involved, so the mirror never waits behind a bulk transfer that
+ * another stream has in flight.  The host word must be page-locked memory that
+ * the device can address (cudaHostAlloc / a pinned Torch tensor). */
+TGB_API int32_t tgb_mirror_word(const void *device_word, void *pinned_host_word,
+                                uint64_t stream);
 
 /* ------------------------------------------------------------------------
  * Plans: the per-graph schedule.  Replaces the reference's schedule passes

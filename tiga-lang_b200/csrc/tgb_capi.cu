@@ -17,7 +17,27 @@ void set_error(const char *format, ...) {
 
 }  // namespace tgb
 
+namespace tgb {
+namespace {
+// one int32 from device memory to pinned (device-mapped) host memory, by a store from an SM: unlike a
+// copy-engine transfer it does not queue behind a bulk device-to-host copy that another stream has in
+// flight, so mirroring a status word never stalls the stream that launches it
+__global__ void k_mirror_word(const int32_t *__restrict__ word, int32_t *__restrict__ host_word) {
+  *reinterpret_cast<volatile int32_t *>(host_word) = *word;
+  __threadfence_system();
+}
+}  // namespace
+}  // namespace tgb
+
 extern "C" {
+
+int32_t tgb_mirror_word(const void *device_word, void *pinned_host_word, uint64_t stream) {
+  if (!device_word || !pinned_host_word) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
+  tgb::k_mirror_word<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const int32_t *>(device_word), static_cast<int32_t *>(pinned_host_word));
+  TGB_LAUNCHED();
+  return TGB_STATUS_OK;
+}
 
 const char *tgb_status_string(int32_t status) {
   switch (status) {

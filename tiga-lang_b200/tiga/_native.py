@@ -36,6 +36,7 @@ _SIGNATURES = {
     "tgb_last_error": (ctypes.c_char_p, []),
     "tgb_version": (ctypes.c_char_p, []),
     "tgb_launch_count": (_i64, []),
+    "tgb_mirror_word": (_i32, [_vp, _vp, _u64]),
     "tgb_csr_plan_sizes": (_i32, [_i64, _i64, _i64, _i32, _i32, ctypes.POINTER(_u64), ctypes.POINTER(_u64)]),
     "tgb_csr_plan_create": (_i32, [_vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp, _u64, _vp, _u64, _u64,
                                    ctypes.POINTER(_vp)]),

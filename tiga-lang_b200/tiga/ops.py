@@ -194,8 +194,8 @@ def csr_reduce(graph, reducer: str, x: torch.Tensor, w: torch.Tensor | None, ide
 # --------------------------------------------------------------------------- dense linear
 class _ErrorWord:
     """One int32 per device that the tensor-core kernels set when a bounded wait gives up, with a
-    pinned host mirror.  After every launch that may set it, the word is copied to the mirror on the
-    launching stream (asynchronously); the next tensor-core call on the device looks at the mirror of
+    pinned host mirror.  After every launch that may set it, the word is mirrored on the
+    launching stream (asynchronously, by a one-thread kernel); the next tensor-core call on the device looks at the mirror of
     the copies that have completed by then and raises, so a give-up surfaces without the caller
     asking and without a synchronisation on the good path."""
 
@@ -206,9 +206,14 @@ class _ErrorWord:
         self.copied = None
 
     def after_launch(self):
-        self.mirror.copy_(self.word, non_blocking=True)
+        # a one-thread kernel stores the word into the pinned mirror: a copy-engine transfer would
+        # queue behind any bulk device-to-host copy another stream has in flight and stall this stream
+        stream = torch.cuda.current_stream(self.device)
+        with torch.cuda.device(self.device):
+            _native.check(_native.lib().tgb_mirror_word(self.word.data_ptr(), self.mirror.data_ptr(),
+                                                        stream.cuda_stream), "tgb_mirror_word")
         self.copied = torch.cuda.Event()
-        self.copied.record(torch.cuda.current_stream(self.device))
+        self.copied.record(stream)
 
     def raise_if_set(self, wait: bool):
         if wait:
