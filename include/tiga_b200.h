@@ -52,7 +52,8 @@ enum { TGB_DTYPE_F32 = 0, TGB_DTYPE_BF16 = 1 };
 /* Reducers.  SUM/MEAN: python/tiga/reducer/core.py:85-143.  MAX: a user
  * Reducer whose combine is tg.math.maximum (the variadic-reduce algebra
  * branch, lib/Target/Triton/Translate.cpp:3353-3402). */
-enum { TGB_REDUCER_SUM = 0, TGB_REDUCER_MEAN = 1, TGB_REDUCER_MAX = 2 };
+enum { TGB_REDUCER_SUM = 0, TGB_REDUCER_MEAN = 1, TGB_REDUCER_MAX = 2,
+       TGB_REDUCER_PROD = 3 /* edge programs only */ };
 
 /* Flags of tgb_csr_reduce_fwd. */
 enum {
@@ -586,23 +587,40 @@ typedef struct tgb_edge_program {
 
 /* out[i, f] = reduce over the edges of row i, in edge order, of the message
  * element f.  reducer: TGB_REDUCER_SUM (rows without edges give `identity`),
- * _MEAN (NaN for rows without edges), _MAX (identity).  operands[k]: device
- * pointer of operand k.  out: float32 [num_dst, width]. */
+ * _MEAN (NaN for rows without edges), _MAX (identity), _PROD (identity; the
+ * reference's product monoid, python/tiga/reducer/core.py:146-158 of
+ * walkerchi/TIGA-lang).  operands[k]: device pointer of operand k.
+ * out: float32 [num_dst, width].
+ * What the reverse mode of MAX and PROD needs is written when the pointers
+ * are given (both may be null for a call without gradients):
+ *   saved_index int32 [num_dst, width]  MAX: entry of the first message that
+ *                                       reached the maximum (-1: none did);
+ *                                       PROD: number of zero messages
+ *   saved_value float32 [num_dst, width] PROD: the product with every zero
+ *                                       message replaced by one */
 TGB_API int32_t tgb_edge_program_fwd(const tgb_csr_plan *plan,
                                      const tgb_edge_program *program,
                                      const void *const *operands, int32_t reducer,
-                                     float identity, void *out, uint64_t stream);
+                                     float identity, void *out, void *saved_value,
+                                     void *saved_index, uint64_t stream);
 
-/* Reverse mode, destination-major pass (SUM / MEAN): for every operand k with
+/* Reverse mode, destination-major pass: for every operand k with
  * grads[k] != null and role DST, EDGE or PARAM, writes its cotangent given
  * dy [num_dst, width]: DST -> [num_dst, elements], EDGE -> [E, elements],
  * PARAM -> one partial row per destination, [num_dst, elements], to be summed
- * with tgb_column_sum.  Cotangents are supported for modulus 0 and 1. */
+ * with tgb_column_sum.  Cotangents are supported for modulus 0 and 1.
+ * The cotangent of a message is dy (SUM), dy / degree (MEAN), dy for the
+ * saved winner and 0 for the others (MAX), dy times the product of the row's
+ * other messages (PROD: dy * saved_value / message in a row without zeros,
+ * dy * saved_value for the only zero of a row, else 0 -- the zero-safe rule
+ * of the reference's csr_segment_product_vjp, python/tiga/tensor/core.py:
+ * 1586-1598).  saved_value / saved_index: as the forward wrote them. */
 TGB_API int32_t tgb_edge_program_bwd_rows(const tgb_csr_plan *plan,
                                           const tgb_edge_program *program,
                                           const void *const *operands, int32_t reducer,
                                           const void *dy, void *const *grads,
-                                          uint64_t stream);
+                                          const void *saved_value,
+                                          const void *saved_index, uint64_t stream);
 
 /* Reverse mode, source-major pass over the plan's transposed relation (the
  * plan needs TGB_PLAN_TRANSPOSE): cotangents of the SRC operands with
@@ -611,7 +629,8 @@ TGB_API int32_t tgb_edge_program_bwd_sources(const tgb_csr_plan *plan,
                                              const tgb_edge_program *program,
                                              const void *const *operands, int32_t reducer,
                                              const void *dy, void *const *grads,
-                                             uint64_t stream);
+                                             const void *saved_value,
+                                             const void *saved_index, uint64_t stream);
 
 /* out[c] = sum over r of partial[r, c] (float32, rows added in a fixed order:
  * strips of rows by one thread each, then the strips in order). */

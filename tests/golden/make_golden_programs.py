@@ -5,8 +5,9 @@
 
 Edge expressions outside the weighted-sum / attention patterns (the reference's generic CSR path):
 the reference's eager evaluator ``kernel.reference(...)`` plus ``torch.autograd.grad`` give outputs and
-cotangents for every operand role (src, dst, edge, tensor parameter), sum and mean reducers, scalar
-and vector features, rows without edges and a hub row.
+cotangents for every operand role (src, dst, edge, tensor parameter), sum, mean and product reducers
+(rows with no, one and several zero messages), scalar and vector features, rows without edges and a
+hub row.
 """
 from __future__ import annotations
 
@@ -99,6 +100,43 @@ def main() -> None:
     gain = torch.randn(6, generator=gen).requires_grad_()
     record("gated", Gated(), {"src": {"x": x}, "dst": {"y": y}, "edge": {"w": w}},
            {"gain": gain, "slope": 0.1}, ("x", "y", "w", "gain"))
+
+    # the product monoid (tg.prod): plain source field with rows holding no, one and several zeros,
+    # a per-edge field, and an expression; cotangents are Torch's zero-safe index_reduce("prod") rule
+    class SourceProduct(tg.MessagePassing):
+        reducer = tg.prod()
+
+        def edge(self, src, dst, edge):
+            return self.reducer(src.x)
+
+    class EdgeProduct(tg.MessagePassing):
+        reducer = tg.prod()
+
+        def edge(self, src, dst, edge):
+            return self.reducer(edge.x)
+
+    class ShiftedProduct(tg.MessagePassing):
+        reducer = tg.prod()
+
+        def edge(self, src, dst, edge, bias):
+            return 1.0 + edge.w * (src.x - dst.y) * bias
+
+    px = (1.0 + 0.2 * torch.randn(n_src, 3, generator=gen))
+    px[2, 0] = 0.0
+    px[5, :] = 0.0
+    px[9, 1] = 0.0
+    px = px.requires_grad_()
+    record("prod_src", SourceProduct(), {"src": {"x": px}, "dst": {}, "edge": {}}, {}, ("x",))
+    pe = (1.0 + 0.2 * torch.randn(edges, generator=gen))
+    pe[[0, 1, 4, 80, 90]] = 0.0                      # row 0: two zeros; row 3 (the hub): one zero; row 6: one
+    pe = pe.requires_grad_()
+    record("prod_edge", EdgeProduct(), {"src": {}, "dst": {}, "edge": {"x": pe}}, {}, ("x",))
+    sx = (0.3 * torch.randn(n_src, 4, generator=gen)).requires_grad_()
+    sy = (0.3 * torch.randn(n_dst, 4, generator=gen)).requires_grad_()
+    sw = torch.rand(edges, 1, generator=gen).requires_grad_()
+    bias = torch.randn(4, generator=gen).requires_grad_()
+    record("prod_shifted", ShiftedProduct(), {"src": {"x": sx}, "dst": {"y": sy}, "edge": {"w": sw}},
+           {"bias": bias}, ("x", "y", "w", "bias"))
 
     out_path = os.path.join(HERE, "program_cases.npz")
     np.savez_compressed(out_path, **saved)

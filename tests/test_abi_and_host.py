@@ -125,7 +125,19 @@ def test_capture_recognisers():
 
     assert cap.reducer_algebra(UserMax()) == "max"
     assert cap.reducer_algebra(tg.sum()) == "sum"
-    assert cap.reducer_algebra(tg.prod()) is None
+    assert cap.reducer_algebra(tg.prod()) == "prod"
+
+    class UserProduct(tg.Reducer):
+        name = "user_product"
+        associative = commutative = True
+
+        def identity(self):
+            return 1.0
+
+        def combine(self, left, right):
+            return right * left
+
+    assert cap.reducer_algebra(UserProduct()) == "prod"
     # tuple states whose components add independently, lifts that are monomials of the message
     mean = cap.capture_reducer(tg.mean())
     assert (mean.kind, mean.components, mean.scalar) == ("additive", ((1.0, 1), (1.0, 0)), False)

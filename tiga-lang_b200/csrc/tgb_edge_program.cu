@@ -129,12 +129,30 @@ __device__ __forceinline__ float group_sum(float v, unsigned mask) {
 // partial results are combined in slice order through shared memory (deterministic).
 constexpr int kLongThreads = 256;
 
+// What the forward keeps per (row, element) for the reverse mode of the reducers whose message
+// cotangent depends on the other messages of the row:
+//   MAX   index = entry (CSR position) of the first message that reached the row's maximum, -1 if none did
+//   PROD  value = product of the row's messages with every zero replaced by one, index = number of zeros
+struct Saved {
+  float *value;
+  int32_t *index;
+};
+
+__device__ __forceinline__ float max_step(float state, float m) {      // NaN poisons the state
+  return (state != state || m != m) ? __int_as_float(0x7fc00000) : fmaxf(state, m);
+}
+__device__ __forceinline__ bool max_takes(float state, float m) {      // does m replace the state's winner?
+  return state == state && (m != m || m > state);
+}
+
 template <int LANES, bool LONG>
 __global__ void __launch_bounds__(LONG ? kLongThreads : kThreads)
 k_edge_program_fwd(const __grid_constant__ tgb_edge_program p, Operands in, Walk w, int reducer, float identity,
-                   float *__restrict__ out) {
+                   float *__restrict__ out, Saved saved) {
   constexpr int kGroups = (LONG ? kLongThreads : kThreads) / LANES;
   __shared__ float part[LONG ? kLongThreads : 1];
+  __shared__ float part_masked[LONG ? kLongThreads : 1];
+  __shared__ int32_t part_mark[LONG ? kLongThreads : 1];
   const int lane = threadIdx.x % LANES, group = threadIdx.x / LANES;
   int64_t row;
   if (LONG) {
@@ -151,30 +169,58 @@ k_edge_program_fwd(const __grid_constant__ tgb_edge_program p, Operands in, Walk
     begin = begin + group * slice;
     end = begin + slice < end ? begin + slice : end;
   }
+  const bool is_max = reducer == TGB_REDUCER_MAX, is_prod = reducer == TGB_REDUCER_PROD;
   float value[kMaxI];
   for (int f0 = 0; f0 < p.width; f0 += LANES) {
     const int f = f0 + lane;
     // the fold starts from the identity; the slices of a long row start from the neutral element
-    float acc = reducer == TGB_REDUCER_MAX ? identity : ((LONG || reducer == TGB_REDUCER_MEAN) ? 0.0f : identity);
+    float acc = is_max ? identity : is_prod ? (LONG ? 1.0f : identity)
+                                            : ((LONG || reducer == TGB_REDUCER_MEAN) ? 0.0f : identity);
+    float masked = acc;                 // PROD only
+    int32_t mark = is_max ? -1 : 0;     // MAX: winning entry; PROD: zeros seen
     if (f < p.width) {
       for (int64_t e = begin; e < end; ++e) {
         evaluate(p, in, load_index(w.idx, w.idx_bits, e), row, e, f, value);
         const float m = value[p.num_instructions - 1];
-        if (reducer == TGB_REDUCER_MAX) acc = (acc != acc || m != m) ? __int_as_float(0x7fc00000) : fmaxf(acc, m);
-        else acc = __fadd_rn(acc, m);
+        if (is_max) {
+          if (max_takes(acc, m)) mark = (int32_t)e;
+          acc = max_step(acc, m);
+        } else if (is_prod) {
+          acc = __fmul_rn(acc, m);
+          masked = __fmul_rn(masked, m == 0.0f ? 1.0f : m);
+          mark += m == 0.0f;
+        } else {
+          acc = __fadd_rn(acc, m);
+        }
       }
     }
     if (LONG) {
       part[group * LANES + lane] = acc;
+      part_masked[group * LANES + lane] = masked;
+      part_mark[group * LANES + lane] = mark;
       __syncthreads();
       if (group == 0 && f < p.width) {
-        float total = reducer == TGB_REDUCER_SUM ? identity : acc;      // SUM: identity, then the slices in order
-        for (int g = reducer == TGB_REDUCER_SUM ? 0 : 1; g < kGroups; ++g) {
+        // SUM / PROD: identity, then the slices in order; MAX / MEAN: the first slice, then the others
+        const bool from_identity = reducer == TGB_REDUCER_SUM || is_prod;
+        float total = from_identity ? identity : acc;
+        float masked_total = identity;
+        int32_t mark_total = is_prod ? 0 : mark;
+        for (int g = from_identity ? 0 : 1; g < kGroups; ++g) {
           const float q = part[g * LANES + lane];
-          if (reducer == TGB_REDUCER_MAX) total = (total != total || q != q) ? __int_as_float(0x7fc00000) : fmaxf(total, q);
-          else total = __fadd_rn(total, q);
+          if (is_max) {
+            if (max_takes(total, q)) mark_total = part_mark[g * LANES + lane];
+            total = max_step(total, q);
+          } else if (is_prod) {
+            total = __fmul_rn(total, q);
+            masked_total = __fmul_rn(masked_total, part_masked[g * LANES + lane]);
+            mark_total += part_mark[g * LANES + lane];
+          } else {
+            total = __fadd_rn(total, q);
+          }
         }
         acc = total;
+        masked = masked_total;
+        mark = mark_total;
       }
       __syncthreads();
       if (group != 0) continue;
@@ -182,6 +228,8 @@ k_edge_program_fwd(const __grid_constant__ tgb_edge_program p, Operands in, Walk
     if (f < p.width) {
       if (reducer == TGB_REDUCER_MEAN) acc = __fdiv_rn(acc, (float)degree);
       out[row * p.width + f] = acc;
+      if (saved.value) saved.value[row * p.width + f] = masked;
+      if (saved.index) saved.index[row * p.width + f] = mark;
     }
   }
 }
@@ -192,7 +240,8 @@ k_edge_program_fwd(const __grid_constant__ tgb_edge_program p, Operands in, Walk
 template <int LANES, bool SOURCE_MAJOR, bool LONG>
 __global__ void __launch_bounds__(LONG ? kLongThreads : kThreads)
 k_edge_program_bwd(const __grid_constant__ tgb_edge_program p, Operands in, Sinks sinks, Walk w, int reducer,
-                   const void *__restrict__ degree_ptr, int degree_bits, const float *__restrict__ dy) {
+                   const void *__restrict__ degree_ptr, int degree_bits, const float *__restrict__ dy,
+                   const float *__restrict__ saved_value, const int32_t *__restrict__ saved_index) {
   constexpr int kGroups = (LONG ? kLongThreads : kThreads) / LANES;
   __shared__ float part_full[LONG ? kMaxO * kLongThreads : 1];     // [operand][group][lane]
   __shared__ float part_scalar[LONG ? kMaxO * kLongThreads : 1];   // [operand][group]
@@ -235,12 +284,21 @@ k_edge_program_bwd(const __grid_constant__ tgb_edge_program p, Operands in, Sink
       const int64_t edge = w.eid ? (int64_t)__ldg(w.eid + t) : t;
       const int64_t src = SOURCE_MAJOR ? row : other, dst = SOURCE_MAJOR ? other : row;
       if (live) {
+        evaluate(p, in, src, dst, edge, f, value);
+        // the message's cotangent: what the reducer passes down from the row's cotangent
         float g = __ldg(dy + dst * p.width + f);
         if (reducer == TGB_REDUCER_MEAN) {
           const int64_t degree = load_index(degree_ptr, degree_bits, dst + 1) - load_index(degree_ptr, degree_bits, dst);
           g = g / (float)degree;
+        } else if (reducer == TGB_REDUCER_MAX) {      // the first message that reached the maximum takes it all
+          if (__ldg(saved_index + dst * p.width + f) != (int32_t)edge) g = 0.0f;
+        } else if (reducer == TGB_REDUCER_PROD) {     // g times the product of the row's other messages, zero-safe
+          const float m = value[p.num_instructions - 1];
+          const float others = __ldg(saved_value + dst * p.width + f);
+          const int32_t zeros = __ldg(saved_index + dst * p.width + f);
+          g = zeros == 0 ? __fdiv_rn(__fmul_rn(g, others), m)
+                         : (zeros == 1 && m == 0.0f) ? __fmul_rn(g, others) : 0.0f;
         }
-        evaluate(p, in, src, dst, edge, f, value);
         reverse_sweep(p, value, g, adjoint);
       }
       // every operand is loaded by exactly one instruction: its adjoint is the operand's cotangent
@@ -398,13 +456,17 @@ using namespace tgb;
 
 extern "C" int32_t tgb_edge_program_fwd(const tgb_csr_plan *plan, const tgb_edge_program *program,
                                         const void *const *operands, int32_t reducer, float identity, void *out,
-                                        uint64_t stream) {
+                                        void *saved_value, void *saved_index, uint64_t stream) {
   const int32_t status = check_program(plan, program, operands);
   if (status != TGB_STATUS_OK) return status;
-  if (reducer != TGB_REDUCER_SUM && reducer != TGB_REDUCER_MEAN && reducer != TGB_REDUCER_MAX)
-    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "unknown reducer");
+  if (reducer < TGB_REDUCER_SUM || reducer > TGB_REDUCER_PROD) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "unknown reducer");
   if (plan->num_dst == 0) return TGB_STATUS_OK;
   if (!out) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null output");
+  if (saved_index && plan->num_edges >= ((int64_t)1 << 31))
+    TGB_FAIL(TGB_STATUS_UNSUPPORTED, "the saved entry index is 32 bits wide");
+  const Saved saved{reducer == TGB_REDUCER_PROD ? static_cast<float *>(saved_value) : nullptr,
+                    reducer == TGB_REDUCER_PROD || reducer == TGB_REDUCER_MAX ? static_cast<int32_t *>(saved_index)
+                                                                                : nullptr};
   Operands in;
   for (int k = 0; k < kMaxO; ++k) in.ptr[k] = k < program->num_operands ? static_cast<const float *>(operands[k]) : nullptr;
   const Walk w = forward_walk(plan);
@@ -413,10 +475,10 @@ extern "C" int32_t tgb_edge_program_fwd(const tgb_csr_plan *plan, const tgb_edge
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 #define TGB_FWD(L)                                                                                          \
   k_edge_program_fwd<L, false><<<blocks, kThreads, 0, st>>>(*program, in, w, reducer, identity,             \
-                                                            static_cast<float *>(out));                     \
+                                                            static_cast<float *>(out), saved);              \
   if (w.n_long > 0)                                                                                         \
     k_edge_program_fwd<L, true><<<(unsigned)w.n_long, kLongThreads, 0, st>>>(*program, in, w, reducer, identity, \
-                                                                             static_cast<float *>(out))
+                                                                             static_cast<float *>(out), saved)
   TGB_EP_LANES(lanes, TGB_FWD)
 #undef TGB_FWD
   TGB_LAUNCHED();
@@ -428,11 +490,14 @@ namespace {
 
 int32_t backward(bool source_major, const tgb_csr_plan *plan, const tgb_edge_program *program,
                  const void *const *operands, int32_t reducer, const void *dy, void *const *grads,
-                 uint64_t stream) {
+                 const void *saved_value, const void *saved_index, uint64_t stream) {
   const int32_t status = check_program(plan, program, operands);
   if (status != TGB_STATUS_OK) return status;
-  if (reducer != TGB_REDUCER_SUM && reducer != TGB_REDUCER_MEAN)
-    TGB_FAIL(TGB_STATUS_UNSUPPORTED, "reverse mode covers the sum and mean reducers");
+  if (reducer < TGB_REDUCER_SUM || reducer > TGB_REDUCER_PROD) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "unknown reducer");
+  if ((reducer == TGB_REDUCER_MAX || reducer == TGB_REDUCER_PROD) && !saved_index)
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "this reducer's reverse mode needs what the forward saved (saved_index)");
+  if (reducer == TGB_REDUCER_PROD && !saved_value)
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "the product reducer's reverse mode needs saved_value");
   if (!dy || !grads) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null cotangent");
   if (source_major && !(plan->flags & TGB_PLAN_TRANSPOSE))
     TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "the source-major pass needs a plan with the transposed relation");
@@ -459,19 +524,21 @@ int32_t backward(bool source_major, const tgb_csr_plan *plan, const tgb_edge_pro
   const int lanes = lanes_for_width(program->width);
   const unsigned blocks = (unsigned)ceil_div(w.n_rows * lanes, kThreads);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const float *sv = static_cast<const float *>(saved_value);
+  const int32_t *si = static_cast<const int32_t *>(saved_index);
 #define TGB_BWD(L)                                                                                            \
   if (source_major) {                                                                                         \
     k_edge_program_bwd<L, true, false><<<blocks, kThreads, 0, st>>>(*program, in, sinks, w, reducer,          \
-        plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy));                                   \
+        plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy), sv, si);                           \
     if (w.n_long > 0)                                                                                         \
       k_edge_program_bwd<L, true, true><<<(unsigned)w.n_long, kLongThreads, 0, st>>>(*program, in, sinks, w,  \
-          reducer, plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy));                        \
+          reducer, plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy), sv, si);                \
   } else {                                                                                                    \
     k_edge_program_bwd<L, false, false><<<blocks, kThreads, 0, st>>>(*program, in, sinks, w, reducer,         \
-        plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy));                                   \
+        plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy), sv, si);                           \
     if (w.n_long > 0)                                                                                         \
       k_edge_program_bwd<L, false, true><<<(unsigned)w.n_long, kLongThreads, 0, st>>>(*program, in, sinks, w, \
-          reducer, plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy));                        \
+          reducer, plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy), sv, si);                \
   }
   TGB_EP_LANES(lanes, TGB_BWD)
 #undef TGB_BWD
@@ -484,14 +551,16 @@ int32_t backward(bool source_major, const tgb_csr_plan *plan, const tgb_edge_pro
 
 extern "C" int32_t tgb_edge_program_bwd_rows(const tgb_csr_plan *plan, const tgb_edge_program *program,
                                              const void *const *operands, int32_t reducer, const void *dy,
-                                             void *const *grads, uint64_t stream) {
-  return backward(false, plan, program, operands, reducer, dy, grads, stream);
+                                             void *const *grads, const void *saved_value, const void *saved_index,
+                                             uint64_t stream) {
+  return backward(false, plan, program, operands, reducer, dy, grads, saved_value, saved_index, stream);
 }
 
 extern "C" int32_t tgb_edge_program_bwd_sources(const tgb_csr_plan *plan, const tgb_edge_program *program,
                                                 const void *const *operands, int32_t reducer, const void *dy,
-                                                void *const *grads, uint64_t stream) {
-  return backward(true, plan, program, operands, reducer, dy, grads, stream);
+                                                void *const *grads, const void *saved_value,
+                                                const void *saved_index, uint64_t stream) {
+  return backward(true, plan, program, operands, reducer, dy, grads, saved_value, saved_index, stream);
 }
 
 extern "C" int32_t tgb_column_sum(const void *partial, int64_t rows, int64_t cols, void *out, uint64_t stream) {

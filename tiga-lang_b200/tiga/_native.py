@@ -77,9 +77,9 @@ _SIGNATURES = {
     "tgb_knn": (_i32, [_vp, _i64, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _u64]),
     "tgb_knn_grid": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _u64]),
     "tgb_edge_geometry": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _u64]),
-    "tgb_edge_program_fwd": (_i32, [_vp, _vp, _vp, _i32, _f32, _vp, _u64]),
-    "tgb_edge_program_bwd_rows": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _u64]),
-    "tgb_edge_program_bwd_sources": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _u64]),
+    "tgb_edge_program_fwd": (_i32, [_vp, _vp, _vp, _i32, _f32, _vp, _vp, _vp, _u64]),
+    "tgb_edge_program_bwd_rows": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _u64]),
+    "tgb_edge_program_bwd_sources": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _u64]),
     "tgb_column_sum": (_i32, [_vp, _i64, _i64, _vp, _u64]),
 }
 

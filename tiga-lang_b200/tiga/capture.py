@@ -312,6 +312,7 @@ class ReducerAlgebra:
     kind        "sum"       combine is ``left + right`` on a scalar state, lift and finalize are
                             the identity map
                 "max"       combine is ``tg.math.maximum(left, right)``, lift / finalize identity
+                "prod"      combine is ``left * right`` (the product monoid), lift / finalize identity
                 "additive"  tuple (or scalar) state whose components add independently and whose
                             lift is, per component, ``coefficient * message ** power`` (power 0 is a
                             count); ``finalize`` is arbitrary and runs on the finished states
@@ -393,6 +394,8 @@ def capture_reducer(reducer) -> ReducerAlgebra | None:
             return ReducerAlgebra(kind="sum")
         if untouched and pairs_own_operands(combined[0], 0, "maximum"):
             return ReducerAlgebra(kind="max")
+        if untouched and pairs_own_operands(combined[0], 0, "mul"):
+            return ReducerAlgebra(kind="prod")
     if not all(pairs_own_operands(combined[k], k, "add") for k in range(arity)):
         return None
     if any(not isinstance(v, (int, float)) or isinstance(v, bool) or float(v) != 0.0 for v in start):
@@ -404,6 +407,6 @@ def capture_reducer(reducer) -> ReducerAlgebra | None:
 
 
 def reducer_algebra(reducer) -> str | None:
-    """'sum' / 'max' / 'additive' for a user reducer, or None."""
+    """'sum' / 'max' / 'prod' / 'additive' for a user reducer, or None."""
     algebra = capture_reducer(reducer)
     return None if algebra is None else algebra.kind

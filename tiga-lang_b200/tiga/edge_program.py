@@ -38,7 +38,7 @@ _BINARY = {"add": OP_ADD, "sub": OP_SUB, "mul": OP_MUL, "div": OP_DIV, "maximum"
 _UNARY = {"exp": OP_EXP, "neg": OP_NEG}
 ROLE_SRC, ROLE_DST, ROLE_EDGE, ROLE_PARAM = range(4)
 _ROLES = {"src": ROLE_SRC, "dst": ROLE_DST, "edge": ROLE_EDGE}
-REDUCE_SUM, REDUCE_MEAN, REDUCE_MAX = range(3)
+REDUCE_SUM, REDUCE_MEAN, REDUCE_MAX, REDUCE_PROD = range(4)
 
 
 class ProgramStruct(ctypes.Structure):
@@ -223,22 +223,34 @@ class EdgeProgramFunction(torch.autograd.Function):
         plan = graph.native_plan(transpose=False)
         device = rows[0].device
         out = torch.empty((graph.num_dst, width), dtype=torch.float32, device=device)
+        # what the reverse mode of max / prod needs of the row (winning entry; zero count and the
+        # product of the non-zero messages), written by the forward kernel when gradients are wanted
+        wants_grad = any(ctx.needs_input_grad[4:])
+        saved_index = saved_value = None
+        if wants_grad and reducer in (REDUCE_MAX, REDUCE_PROD):
+            saved_index = torch.empty((graph.num_dst, width), dtype=torch.int32, device=device)
+        if wants_grad and reducer == REDUCE_PROD:
+            saved_value = torch.empty((graph.num_dst, width), dtype=torch.float32, device=device)
         with torch.cuda.device(device):
             _native.check(lib.tgb_edge_program_fwd(plan.handle, ctypes.byref(struct), _pointers(rows), int(reducer),
-                                                   float(identity), out.data_ptr(), _stream(device)),
+                                                   float(identity), out.data_ptr(),
+                                                   None if saved_value is None else saved_value.data_ptr(),
+                                                   None if saved_index is None else saved_index.data_ptr(),
+                                                   _stream(device)),
                           "tgb_edge_program_fwd")
         ctx.graph, ctx.program, ctx.reducer, ctx.struct = graph, program, reducer, struct
         ctx.moduli, ctx.width = moduli, width
-        ctx.save_for_backward(*rows)
+        ctx.count = len(rows)
+        ctx.save_for_backward(*rows, *[t for t in (saved_value, saved_index) if t is not None])
         ctx.shapes = [tuple(t.shape) for t in tensors]
         return out.reshape((graph.num_dst,) + feature_shape)
 
     @staticmethod
     def backward(ctx, dy):
-        if ctx.reducer == REDUCE_MAX:
-            raise NotImplementedError("the maximum reducer over a generic edge program is forward-only")
         lib = _native.lib()
-        rows = ctx.saved_tensors
+        rows, kept = ctx.saved_tensors[:ctx.count], ctx.saved_tensors[ctx.count:]
+        saved_value = kept[0].data_ptr() if ctx.reducer == REDUCE_PROD else None
+        saved_index = kept[-1].data_ptr() if ctx.reducer in (REDUCE_MAX, REDUCE_PROD) else None
         program, graph, struct = ctx.program, ctx.graph, ctx.struct
         needs = ctx.needs_input_grad[4:]
         device = dy.device
@@ -266,12 +278,14 @@ class EdgeProgramFunction(torch.autograd.Function):
             if any_dst_major:
                 plan = graph.native_plan(transpose=False)
                 _native.check(lib.tgb_edge_program_bwd_rows(plan.handle, ctypes.byref(struct), _pointers(rows),
-                                                            ctx.reducer, dy.data_ptr(), wanted, _stream(device)),
+                                                            ctx.reducer, dy.data_ptr(), wanted, saved_value,
+                                                            saved_index, _stream(device)),
                               "tgb_edge_program_bwd_rows")
             if any_src_major:
                 plan = graph.native_plan(transpose=True)
                 _native.check(lib.tgb_edge_program_bwd_sources(plan.handle, ctypes.byref(struct), _pointers(rows),
-                                                               ctx.reducer, dy.data_ptr(), wanted, _stream(device)),
+                                                               ctx.reducer, dy.data_ptr(), wanted, saved_value,
+                                                               saved_index, _stream(device)),
                               "tgb_edge_program_bwd_sources")
             for i, partial in param_partials.items():
                 total = torch.empty(partial.shape[1], dtype=torch.float32, device=device)
@@ -283,4 +297,4 @@ class EdgeProgramFunction(torch.autograd.Function):
 
 
 __all__ = ["EdgeProgram", "EdgeProgramFunction", "Operand", "compile_expression", "bind", "make_struct",
-           "REDUCE_SUM", "REDUCE_MEAN", "REDUCE_MAX"]
+           "REDUCE_SUM", "REDUCE_MEAN", "REDUCE_MAX", "REDUCE_PROD"]

@@ -77,14 +77,17 @@ def _refuse_shadowing(implicit, edge) -> None:
 
 
 def _reducer_kind(reducer) -> str | None:
-    """'sum' / 'mean' / 'max' / 'additive' for reducers the CSR kernels can fold, else None."""
+    """'sum' / 'mean' / 'max' / 'prod' / 'additive' for reducers the CSR kernels can fold, else None.
+    'prod' is folded by the edge-program kernels only."""
     if isinstance(reducer, SumReducer):
         return "sum"
     if isinstance(reducer, MeanReducer):
         return "mean"
     if isinstance(reducer, MaxReducer):
         return "max"
-    if isinstance(reducer, (OnlineSoftmaxReducer, ProductReducer)):
+    if isinstance(reducer, ProductReducer):
+        return "prod"
+    if isinstance(reducer, OnlineSoftmaxReducer):
         return None
     return cap.reducer_algebra(reducer)
 
@@ -318,15 +321,15 @@ class MessagePassing(Kernel):
             return self._specialise_online_softmax(graph, src, dst, edge, params, staged, constants)
         kind = _reducer_kind(self.reducer)
         pattern = cap.recognize_weighted_sum(staged)
-        if kind in ("sum", "mean", "max") and isinstance(staged, cap.Expr):
+        if kind in ("sum", "mean", "max", "prod") and isinstance(staged, cap.Expr):
             vector_weight = (pattern is not None and pattern.edge_field is not None and pattern.edge_field in edge
                              and pattern.src_field in src
                              and edge[pattern.edge_field].numel() != edge[pattern.edge_field].shape[0])
-            if pattern is None or vector_weight:
+            if pattern is None or vector_weight or kind == "prod":
                 generic = self._specialise_edge_program(graph, src, dst, edge, params, staged, constants, kind)
                 if generic is not None:
                     return generic
-        if kind is None or pattern is None:
+        if kind is None or kind == "prod" or pattern is None:
             raise NotImplementedError(
                 f"no native kernel for reducer {type(self.reducer).__name__} with this edge expression")
         from . import ops
@@ -443,8 +446,8 @@ class MessagePassing(Kernel):
             bindings.append((operand.role, operand.name))
             tensors.append(spaces[operand.role][operand.name])
         cell = SimpleNamespace(graph=graph)
-        reducer_id = {"sum": ep.REDUCE_SUM, "mean": ep.REDUCE_MEAN, "max": ep.REDUCE_MAX}[kind]
-        identity = float(self.reducer.identity()) if kind in ("sum", "max") else 0.0
+        reducer_id = {"sum": ep.REDUCE_SUM, "mean": ep.REDUCE_MEAN, "max": ep.REDUCE_MAX, "prod": ep.REDUCE_PROD}[kind]
+        identity = float(self.reducer.identity()) if kind in ("sum", "max", "prod") else 0.0
 
         def runner(*bound):
             current = cell.graph
@@ -597,9 +600,13 @@ def _eager_reduce(reducer, message, destination, num_dst):
         start = torch.full(shape, float(reducer.identity()), dtype=message.dtype, device=message.device)
         index = destination.reshape(-1, *((1,) * (message.ndim - 1))).expand_as(message)
         return start.scatter_reduce(0, index, message, reduce="amax", include_self=True)
-    if isinstance(reducer, ProductReducer):
+    if kind == "prod":
+        import warnings
+
         start = torch.full(shape, reducer.identity(), dtype=message.dtype, device=message.device)
-        return start.index_reduce(0, destination, message, "prod")
+        with warnings.catch_warnings():         # Torch still tags the differentiable segment product "beta"
+            warnings.simplefilter("ignore", UserWarning)
+            return start.index_reduce(0, destination, message, "prod")
     if kind == "additive":
         algebra = cap.capture_reducer(reducer)
         states = []
