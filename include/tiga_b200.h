@@ -632,6 +632,86 @@ TGB_API int32_t tgb_edge_program_bwd_sources(const tgb_csr_plan *plan,
                                              const void *saved_value,
                                              const void *saved_index, uint64_t stream);
 
+/* ---------------------------------------------------------------------------
+ * Edge programs folded by a USER ALGEBRA: any associative reducer with a tuple
+ * state (the reference's captured reducer regions,
+ * python/tiga/compiler/reducer_capture.py:53-130 of walkerchi/TIGA-lang, run by
+ * its generic tile gf_csr_algebra_tile, lib/Target/Triton/Translate.cpp:
+ * 3065-3092).  Per (row, element):
+ *     state = identity
+ *     for the row's edges in order:  state = step(state, messages of the edge)
+ *     out   = finalize(state)
+ * with step(state, m) = combine(state, lift(m)).  A region is a register
+ * program like tgb_edge_program whose TGB_EP_LOAD reads ARGUMENT a[i]:
+ *     step      arguments: state[0..arity), then messages[0..num_messages)
+ *     combine   arguments: left[0..arity), then right[0..arity)
+ *     finalize  arguments: state[0..arity);  one output
+ * out[k] names the instruction whose value is output k.  The messages of an
+ * edge are the values of the instructions message_slot[j] of the edge program.
+ * Rows above the plan's split threshold are folded in contiguous slices that
+ * `combine` joins in order: the algebra must be associative with `identity`
+ * neutral, as the reference requires of a parallel reducer; it need not be
+ * commutative.
+ * ------------------------------------------------------------------------ */
+#define TGB_ALG_MAX_INSTRUCTIONS 40
+#define TGB_ALG_MAX_STATE 4
+#define TGB_ALG_MAX_MESSAGES 4
+#define TGB_ALG_MAX_CONSTANTS 8
+
+typedef struct tgb_region {
+  int32_t num_instructions;
+  uint8_t op[TGB_ALG_MAX_INSTRUCTIONS];
+  uint8_t a[TGB_ALG_MAX_INSTRUCTIONS];
+  uint8_t b[TGB_ALG_MAX_INSTRUCTIONS];
+  uint8_t out[TGB_ALG_MAX_STATE];
+  float constants[TGB_ALG_MAX_CONSTANTS];
+} tgb_region;
+
+typedef struct tgb_edge_algebra {
+  int32_t arity;        /* state components, 1..TGB_ALG_MAX_STATE */
+  int32_t num_messages; /* 1..TGB_ALG_MAX_MESSAGES */
+  float identity[TGB_ALG_MAX_STATE];
+  uint8_t message_slot[TGB_ALG_MAX_MESSAGES];
+  tgb_region step;
+  tgb_region combine;
+  tgb_region finalize;
+} tgb_edge_algebra;
+
+/* out: float32 [num_dst, width]. */
+TGB_API int32_t tgb_edge_algebra_fwd(const tgb_csr_plan *plan,
+                                     const tgb_edge_program *program,
+                                     const tgb_edge_algebra *algebra,
+                                     const void *const *operands, void *out,
+                                     uint64_t stream);
+
+/* Reverse mode through the fold: the cotangent of every message of every
+ * edge, message_grads float32 [num_messages, E, width], given
+ * dy [num_dst, width].  prefix: scratch float32 [E, arity, width] (the state
+ * before each edge, kept by the first sweep over a row for the backward sweep
+ * over it). */
+TGB_API int32_t tgb_edge_algebra_bwd_messages(const tgb_csr_plan *plan,
+                                              const tgb_edge_program *program,
+                                              const tgb_edge_algebra *algebra,
+                                              const void *const *operands,
+                                              const void *dy, void *prefix,
+                                              void *message_grads, uint64_t stream);
+
+/* From message cotangents to operand cotangents: the two passes of
+ * tgb_edge_program_bwd_rows / _sources, seeded per edge and message slot from
+ * message_grads [num_messages, E, width] instead of a reducer rule. */
+TGB_API int32_t tgb_edge_algebra_bwd_rows(const tgb_csr_plan *plan,
+                                          const tgb_edge_program *program,
+                                          const tgb_edge_algebra *algebra,
+                                          const void *const *operands,
+                                          const void *message_grads,
+                                          void *const *grads, uint64_t stream);
+TGB_API int32_t tgb_edge_algebra_bwd_sources(const tgb_csr_plan *plan,
+                                             const tgb_edge_program *program,
+                                             const tgb_edge_algebra *algebra,
+                                             const void *const *operands,
+                                             const void *message_grads,
+                                             void *const *grads, uint64_t stream);
+
 /* out[c] = sum over r of partial[r, c] (float32, rows added in a fixed order:
  * strips of rows by one thread each, then the strips in order). */
 TGB_API int32_t tgb_column_sum(const void *partial, int64_t rows, int64_t cols,

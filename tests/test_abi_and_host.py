@@ -138,6 +138,33 @@ def test_capture_recognisers():
             return right * left
 
     assert cap.reducer_algebra(UserProduct()) == "prod"
+
+    # anything else is staged into step / combine / finalize register programs
+    from tiga import algebra as alg
+
+    class AffineComposition(tg.Reducer):
+        associative = True
+
+        def identity(self):
+            return 1.0, 0.0
+
+        def lift(self, scale, bias):
+            return scale, bias
+
+        def combine(self, left, right):
+            return right[0] * left[0], right[0] * left[1] + right[1]
+
+        def finalize(self, state):
+            return state[1]
+
+    assert cap.reducer_algebra(AffineComposition()) is None
+    rules = alg.capture_algebra(AffineComposition(), 2)
+    assert rules.arity == 2 and rules.identity == (1.0, 0.0) and len(rules.finalize.ops) == 1
+    assert rules.step.ops.count(0) == 4 and rules.combine.ops.count(0) == 4       # four argument loads each
+    struct = alg.make_struct(rules, (0, 1))
+    assert struct.step.num_instructions == len(rules.step.ops) and struct.finalize.out[0] == rules.finalize.outs[0]
+    AffineComposition.associative = False
+    assert alg.capture_algebra(AffineComposition(), 2) is None
     # tuple states whose components add independently, lifts that are monomials of the message
     mean = cap.capture_reducer(tg.mean())
     assert (mean.kind, mean.components, mean.scalar) == ("additive", ((1.0, 1), (1.0, 0)), False)

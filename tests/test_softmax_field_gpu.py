@@ -93,16 +93,26 @@ def test_bf16_values_and_trailing_singleton_scores(oracle):
     assert torch.all(per_row.abs() <= 2e-2 * scale + 1e-3)
 
 
-def test_other_online_softmax_programs_still_raise():
-    class Odd(tg.MessagePassing):
+def test_other_online_softmax_programs_take_the_algebra_kernels_or_raise():
+    """A score EXPRESSION (not a stored field) with one score per edge runs through the interpreting
+    algebra kernels; several score lanes per edge against a payload have no kernel and raise."""
+    class Scaled(tg.MessagePassing):
         reducer = tg.online_softmax()
 
         def edge(self, src, dst, edge):
             return self.reducer(edge.score * 2.0, src.value)
 
-    row_ptr = torch.tensor([0, 1, 2]).cuda()
-    col = torch.tensor([1, 0]).cuda()
+    row_ptr = torch.tensor([0, 2, 3]).cuda()
+    col = torch.tensor([1, 0, 0]).cuda()
     graph = tg.Graph.from_csr(row_ptr, col, num_src=2)
+    value = torch.randn(2, 4, device="cuda", generator=torch.Generator("cuda").manual_seed(3))
+    score = torch.tensor([0.3, -0.2, 0.9], device="cuda")
+    kernel = Scaled()
+    got = kernel(graph=graph, src={"value": value}, dst={}, edge={"score": score})
+    assert kernel.last_variant.lowering == "b200-generic-csr-algebra-reducer"
+    want = Scaled().reference(graph=tg.Graph.from_csr(row_ptr.cpu(), col.cpu(), num_src=2), src={"value": value.cpu()},
+                              dst={}, edge={"score": score.cpu()})
+    torch.testing.assert_close(got.cpu(), want, rtol=1e-5, atol=1e-6)
     with pytest.raises(NotImplementedError):
-        Odd()(graph=graph, src={"value": torch.zeros(2, 4, device="cuda")}, dst={},
-              edge={"score": torch.zeros(2, device="cuda")})
+        Scaled()(graph=graph, src={"value": torch.zeros(2, 2, 4, device="cuda")}, dst={},
+                 edge={"score": torch.zeros(3, 2, device="cuda")})

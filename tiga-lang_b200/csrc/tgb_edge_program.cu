@@ -46,6 +46,19 @@ __device__ __forceinline__ int64_t load_index(const void *base, int bits, int64_
                     : (int64_t)__ldg(static_cast<const int32_t *>(base) + i);
 }
 
+// one arithmetic instruction (everything but LOAD and CONST)
+__device__ __forceinline__ float apply_op(int op, float x, float y) {
+  switch (op) {
+    case TGB_EP_ADD: return __fadd_rn(x, y);
+    case TGB_EP_SUB: return __fsub_rn(x, y);
+    case TGB_EP_MUL: return __fmul_rn(x, y);
+    case TGB_EP_DIV: return __fdiv_rn(x, y);
+    case TGB_EP_MAX: return (x != x || y != y) ? __int_as_float(0x7fc00000) : fmaxf(x, y);   // torch.maximum: NaN wins
+    case TGB_EP_EXP: return expf(x);
+    default: return -x;   // TGB_EP_NEG
+  }
+}
+
 // value[] of every instruction for one (source, destination, edge, element)
 __device__ __forceinline__ void evaluate(const tgb_edge_program &p, const Operands &in, int64_t src, int64_t dst,
                                          int64_t edge, int f, float *value) {
@@ -53,39 +66,27 @@ __device__ __forceinline__ void evaluate(const tgb_edge_program &p, const Operan
   for (int i = 0; i < n; ++i) {
     const int a = p.a[i], b = p.b[i];
     float v;
-    switch (p.op[i]) {
-      case TGB_EP_LOAD: {
-        const int role = p.operand_role[a], m = p.operand_modulus[a];
-        const int64_t entity = role == TGB_EP_ROLE_SRC ? src : role == TGB_EP_ROLE_DST ? dst
-                               : role == TGB_EP_ROLE_EDGE ? edge : 0;
-        const int count = m == 0 ? p.width : m;
-        const int offset = m == 0 ? f : (m == 1 ? 0 : f % m);
-        v = __ldg(in.ptr[a] + entity * count + offset);
-        break;
-      }
-      case TGB_EP_CONST: v = p.constants[a]; break;
-      case TGB_EP_ADD: v = __fadd_rn(value[a], value[b]); break;
-      case TGB_EP_SUB: v = __fsub_rn(value[a], value[b]); break;
-      case TGB_EP_MUL: v = __fmul_rn(value[a], value[b]); break;
-      case TGB_EP_DIV: v = __fdiv_rn(value[a], value[b]); break;
-      case TGB_EP_MAX: {     // torch.maximum: NaN wins
-        const float x = value[a], y = value[b];
-        v = (x != x || y != y) ? __int_as_float(0x7fc00000) : fmaxf(x, y);
-        break;
-      }
-      case TGB_EP_EXP: v = expf(value[a]); break;
-      default: v = -value[a]; break;   // TGB_EP_NEG
+    if (p.op[i] == TGB_EP_LOAD) {
+      const int role = p.operand_role[a], m = p.operand_modulus[a];
+      const int64_t entity = role == TGB_EP_ROLE_SRC ? src : role == TGB_EP_ROLE_DST ? dst
+                             : role == TGB_EP_ROLE_EDGE ? edge : 0;
+      const int count = m == 0 ? p.width : m;
+      const int offset = m == 0 ? f : (m == 1 ? 0 : f % m);
+      v = __ldg(in.ptr[a] + entity * count + offset);
+    } else if (p.op[i] == TGB_EP_CONST) {
+      v = p.constants[a];
+    } else {
+      v = apply_op(p.op[i], value[a], value[b]);
     }
     value[i] = v;
   }
 }
 
-// adjoint[] of every instruction given the cotangent g of the message
-__device__ __forceinline__ void reverse_sweep(const tgb_edge_program &p, const float *value, float g, float *adjoint) {
-  const int n = p.num_instructions;
-  for (int i = 0; i < n; ++i) adjoint[i] = 0.0f;
-  adjoint[n - 1] = g;
-  for (int i = n - 1; i >= 0; --i) {
+// Pushes the adjoints of a program's instructions (tgb_edge_program or tgb_region) down to its
+// leaves; the caller has put the seeds into adjoint[].
+template <typename Program>
+__device__ __forceinline__ void sweep_back(const Program &p, const float *value, float *adjoint) {
+  for (int i = p.num_instructions - 1; i >= 0; --i) {
     const float gi = adjoint[i];
     const int a = p.a[i], b = p.b[i];
     switch (p.op[i]) {
@@ -110,6 +111,24 @@ __device__ __forceinline__ void reverse_sweep(const tgb_edge_program &p, const f
     }
   }
 }
+
+// adjoint[] of every instruction given the cotangent g of the message (the last instruction)
+__device__ __forceinline__ void reverse_sweep(const tgb_edge_program &p, const float *value, float g, float *adjoint) {
+  const int n = p.num_instructions;
+  for (int i = 0; i < n; ++i) adjoint[i] = 0.0f;
+  adjoint[n - 1] = g;
+  sweep_back(p, value, adjoint);
+}
+
+// Message cotangents given per edge and message slot (the reverse mode of a user algebra hands them
+// over this way): [count][edges][width].
+struct Seeds {
+  const float *base;
+  int64_t edges;
+  int count;
+  uint8_t slot[TGB_ALG_MAX_MESSAGES];
+};
+constexpr int kReducerSeeded = -1;     // k_edge_program_bwd: take the message cotangents from Seeds
 
 template <int LANES>
 __device__ __forceinline__ unsigned group_mask() {
@@ -241,7 +260,7 @@ template <int LANES, bool SOURCE_MAJOR, bool LONG>
 __global__ void __launch_bounds__(LONG ? kLongThreads : kThreads)
 k_edge_program_bwd(const __grid_constant__ tgb_edge_program p, Operands in, Sinks sinks, Walk w, int reducer,
                    const void *__restrict__ degree_ptr, int degree_bits, const float *__restrict__ dy,
-                   const float *__restrict__ saved_value, const int32_t *__restrict__ saved_index) {
+                   const float *__restrict__ saved_value, const int32_t *__restrict__ saved_index, Seeds seeds) {
   constexpr int kGroups = (LONG ? kLongThreads : kThreads) / LANES;
   __shared__ float part_full[LONG ? kMaxO * kLongThreads : 1];     // [operand][group][lane]
   __shared__ float part_scalar[LONG ? kMaxO * kLongThreads : 1];   // [operand][group]
@@ -286,7 +305,7 @@ k_edge_program_bwd(const __grid_constant__ tgb_edge_program p, Operands in, Sink
       if (live) {
         evaluate(p, in, src, dst, edge, f, value);
         // the message's cotangent: what the reducer passes down from the row's cotangent
-        float g = __ldg(dy + dst * p.width + f);
+        float g = reducer == kReducerSeeded ? 0.0f : __ldg(dy + dst * p.width + f);
         if (reducer == TGB_REDUCER_MEAN) {
           const int64_t degree = load_index(degree_ptr, degree_bits, dst + 1) - load_index(degree_ptr, degree_bits, dst);
           g = g / (float)degree;
@@ -299,7 +318,14 @@ k_edge_program_bwd(const __grid_constant__ tgb_edge_program p, Operands in, Sink
           g = zeros == 0 ? __fdiv_rn(__fmul_rn(g, others), m)
                          : (zeros == 1 && m == 0.0f) ? __fmul_rn(g, others) : 0.0f;
         }
-        reverse_sweep(p, value, g, adjoint);
+        if (reducer == kReducerSeeded) {
+          for (int i = 0; i < p.num_instructions; ++i) adjoint[i] = 0.0f;
+          for (int j = 0; j < seeds.count; ++j)
+            adjoint[seeds.slot[j]] += __ldg(seeds.base + ((int64_t)j * seeds.edges + edge) * p.width + f);
+          sweep_back(p, value, adjoint);
+        } else {
+          reverse_sweep(p, value, g, adjoint);
+        }
       }
       // every operand is loaded by exactly one instruction: its adjoint is the operand's cotangent
       for (int i = 0; i < p.num_instructions; ++i) {
@@ -490,10 +516,12 @@ namespace {
 
 int32_t backward(bool source_major, const tgb_csr_plan *plan, const tgb_edge_program *program,
                  const void *const *operands, int32_t reducer, const void *dy, void *const *grads,
-                 const void *saved_value, const void *saved_index, uint64_t stream) {
+                 const void *saved_value, const void *saved_index, uint64_t stream,
+                 Seeds seeds = Seeds{nullptr, 0, 0, {0, 0, 0, 0}}) {
   const int32_t status = check_program(plan, program, operands);
   if (status != TGB_STATUS_OK) return status;
-  if (reducer < TGB_REDUCER_SUM || reducer > TGB_REDUCER_PROD) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "unknown reducer");
+  if (reducer == kReducerSeeded ? seeds.base == nullptr : (reducer < TGB_REDUCER_SUM || reducer > TGB_REDUCER_PROD))
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "unknown reducer");
   if ((reducer == TGB_REDUCER_MAX || reducer == TGB_REDUCER_PROD) && !saved_index)
     TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "this reducer's reverse mode needs what the forward saved (saved_index)");
   if (reducer == TGB_REDUCER_PROD && !saved_value)
@@ -529,16 +557,16 @@ int32_t backward(bool source_major, const tgb_csr_plan *plan, const tgb_edge_pro
 #define TGB_BWD(L)                                                                                            \
   if (source_major) {                                                                                         \
     k_edge_program_bwd<L, true, false><<<blocks, kThreads, 0, st>>>(*program, in, sinks, w, reducer,          \
-        plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy), sv, si);                           \
+        plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy), sv, si, seeds);                         \
     if (w.n_long > 0)                                                                                         \
       k_edge_program_bwd<L, true, true><<<(unsigned)w.n_long, kLongThreads, 0, st>>>(*program, in, sinks, w,  \
-          reducer, plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy), sv, si);                \
+          reducer, plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy), sv, si, seeds);              \
   } else {                                                                                                    \
     k_edge_program_bwd<L, false, false><<<blocks, kThreads, 0, st>>>(*program, in, sinks, w, reducer,         \
-        plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy), sv, si);                           \
+        plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy), sv, si, seeds);                         \
     if (w.n_long > 0)                                                                                         \
       k_edge_program_bwd<L, false, true><<<(unsigned)w.n_long, kLongThreads, 0, st>>>(*program, in, sinks, w, \
-          reducer, plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy), sv, si);                \
+          reducer, plan->fwd.ptr, plan->fwd.ptr_bits, static_cast<const float *>(dy), sv, si, seeds);              \
   }
   TGB_EP_LANES(lanes, TGB_BWD)
 #undef TGB_BWD
@@ -570,4 +598,330 @@ extern "C" int32_t tgb_column_sum(const void *partial, int64_t rows, int64_t col
       static_cast<const float *>(partial), rows, cols, static_cast<float *>(out));
   TGB_LAUNCHED();
   return TGB_STATUS_OK;
+}
+
+// ===================================================================================================
+// User algebras: the fold of a row is state = step(state, messages of the edge) from the identity,
+// out = finalize(state), with step / combine / finalize given as register programs over arguments
+// (the reference's captured reducer regions, python/tiga/compiler/reducer_capture.py:53-130, run by its
+// generic tile gf_csr_algebra_tile, lib/Target/Triton/Translate.cpp:3065-3092).  Same row ownership as
+// the kernels above: a lane group per row and element chunk, edges in order; a long row is folded in
+// contiguous slices by one CTA and the slices are joined in order with `combine` (associativity is
+// what the reducer declares; commutativity is not needed).
+namespace tgb {
+namespace {
+
+constexpr int kMaxA = TGB_ALG_MAX_STATE;
+constexpr int kMaxM = TGB_ALG_MAX_MESSAGES;
+constexpr int kMaxR = TGB_ALG_MAX_INSTRUCTIONS;
+constexpr int kMaxArgs = kMaxA + (kMaxA > kMaxM ? kMaxA : kMaxM);
+
+__device__ __forceinline__ void region_eval(const tgb_region &r, const float *args, float *value) {
+  for (int i = 0; i < r.num_instructions; ++i) {
+    const int op = r.op[i], a = r.a[i], b = r.b[i];
+    value[i] = op == TGB_EP_LOAD ? args[a] : op == TGB_EP_CONST ? r.constants[a] : apply_op(op, value[a], value[b]);
+  }
+}
+
+// cotangents of the region's arguments given the cotangents of its outputs
+__device__ __forceinline__ void region_reverse(const tgb_region &r, const float *value, const float *out_adjoint,
+                                               int n_out, float *adjoint, float *arg_adjoint, int n_args) {
+  for (int i = 0; i < r.num_instructions; ++i) adjoint[i] = 0.0f;
+  for (int k = 0; k < n_out; ++k) adjoint[r.out[k]] += out_adjoint[k];
+  sweep_back(r, value, adjoint);
+  for (int k = 0; k < n_args; ++k) arg_adjoint[k] = 0.0f;
+  for (int i = 0; i < r.num_instructions; ++i)
+    if (r.op[i] == TGB_EP_LOAD) arg_adjoint[r.a[i]] += adjoint[i];
+}
+
+// state <- step(state, messages of one edge), given the edge program's values
+__device__ __forceinline__ void fold_edge(const tgb_edge_algebra &alg, const float *edge_value, float *state,
+                                          float *args, float *rv) {
+  for (int k = 0; k < alg.arity; ++k) args[k] = state[k];
+  for (int j = 0; j < alg.num_messages; ++j) args[alg.arity + j] = edge_value[alg.message_slot[j]];
+  region_eval(alg.step, args, rv);
+  for (int k = 0; k < alg.arity; ++k) state[k] = rv[alg.step.out[k]];
+}
+
+struct RowSpan {
+  int64_t row, begin, end, degree, slice;
+};
+
+// The (slice of the) row this lane group works on; ok = false: nothing to do.
+template <int LANES, bool LONG>
+__device__ __forceinline__ bool row_span(const Walk &w, RowSpan *span) {
+  constexpr int kGroups = (LONG ? kLongThreads : kThreads) / LANES;
+  const int group = threadIdx.x / LANES;
+  if (LONG) {
+    span->row = __ldg(w.order + blockIdx.x);
+  } else {
+    span->row = (int64_t)blockIdx.x * kGroups + group;
+    if (span->row >= w.n_rows) return false;
+  }
+  span->begin = load_index(w.ptr, w.ptr_bits, span->row);
+  span->end = load_index(w.ptr, w.ptr_bits, span->row + 1);
+  span->degree = span->end - span->begin;
+  span->slice = 0;
+  if (!LONG && span->degree > w.split_threshold) return false;
+  if (LONG) {
+    span->slice = (span->degree + kGroups - 1) / kGroups;
+    span->begin = span->begin + group * span->slice;
+    span->end = span->begin + span->slice < span->end ? span->begin + span->slice : span->end;
+  }
+  return true;
+}
+
+template <int LANES, bool LONG>
+__global__ void __launch_bounds__(LONG ? kLongThreads : kThreads)
+k_edge_algebra_fwd(const __grid_constant__ tgb_edge_program p, const __grid_constant__ tgb_edge_algebra alg,
+                   Operands in, Walk w, float *__restrict__ out) {
+  constexpr int kGroups = (LONG ? kLongThreads : kThreads) / LANES;
+  __shared__ float part[LONG ? kMaxA * kLongThreads : 1];        // [component][group][lane]: slice totals
+  const int lane = threadIdx.x % LANES, group = threadIdx.x / LANES;
+  RowSpan span;
+  if (!row_span<LANES, LONG>(w, &span)) return;
+  float value[kMaxI], rv[kMaxR], args[kMaxArgs], state[kMaxA];
+  for (int f0 = 0; f0 < p.width; f0 += LANES) {
+    const int f = f0 + lane;
+    const bool live = f < p.width;
+    for (int k = 0; k < alg.arity; ++k) state[k] = alg.identity[k];
+    if (live) {
+      for (int64_t e = span.begin; e < span.end; ++e) {
+        evaluate(p, in, load_index(w.idx, w.idx_bits, e), span.row, e, f, value);
+        fold_edge(alg, value, state, args, rv);
+      }
+    }
+    if (LONG) {
+      for (int k = 0; k < alg.arity; ++k) part[k * kLongThreads + threadIdx.x] = state[k];
+      __syncthreads();
+      if (group == 0 && live) {
+        for (int k = 0; k < alg.arity; ++k) state[k] = alg.identity[k];
+        for (int g = 0; g < kGroups && (int64_t)g * span.slice < span.degree; ++g) {     // the non-empty slices, in order
+          for (int k = 0; k < alg.arity; ++k) {
+            args[k] = state[k];
+            args[alg.arity + k] = part[k * kLongThreads + g * LANES + lane];
+          }
+          region_eval(alg.combine, args, rv);
+          for (int k = 0; k < alg.arity; ++k) state[k] = rv[alg.combine.out[k]];
+        }
+      }
+      __syncthreads();
+      if (group != 0) continue;
+    }
+    if (live) {
+      region_eval(alg.finalize, state, rv);
+      out[span.row * p.width + f] = rv[alg.finalize.out[0]];
+    }
+  }
+}
+
+// Cotangent of every message of every edge.  Sweep 1 folds the row and keeps the state BEFORE each
+// edge in `prefix`; the cotangent of the final state comes from finalize; sweep 2 walks the row
+// backwards through step, handing each edge its message cotangents and passing the state's on.
+// Long rows: slice totals T_g, running joins R_{g+1} = combine(R_g, T_g) by the first group, the
+// reverse of that chain gives every slice the cotangent of its total, and the slices then run their
+// own sweep 2 (prefix states inside a slice are counted from the identity, as T_g is).
+template <int LANES, bool LONG>
+__global__ void __launch_bounds__(LONG ? kLongThreads : kThreads)
+k_edge_algebra_bwd_messages(const __grid_constant__ tgb_edge_program p, const __grid_constant__ tgb_edge_algebra alg,
+                            Operands in, Walk w, const float *__restrict__ dy, float *__restrict__ prefix,
+                            float *__restrict__ message_grads, int64_t num_edges) {
+  constexpr int kGroups = (LONG ? kLongThreads : kThreads) / LANES;
+  __shared__ float part[LONG ? kMaxA * kLongThreads : 1];        // slice totals, then their cotangents
+  __shared__ float joined[LONG ? kMaxA * kLongThreads : 1];      // R_g: the join of the slices before g
+  const int lane = threadIdx.x % LANES, group = threadIdx.x / LANES;
+  RowSpan span;
+  if (!row_span<LANES, LONG>(w, &span)) return;
+  const int arity = alg.arity;
+  float value[kMaxI], rv[kMaxR], radj[kMaxR], args[kMaxArgs], arg_adjoint[kMaxArgs], state[kMaxA], carried[kMaxA];
+  for (int f0 = 0; f0 < p.width; f0 += LANES) {
+    const int f = f0 + lane;
+    const bool live = f < p.width;
+    for (int k = 0; k < arity; ++k) state[k] = alg.identity[k];
+    if (live) {
+      for (int64_t e = span.begin; e < span.end; ++e) {
+        for (int k = 0; k < arity; ++k) prefix[(e * arity + k) * p.width + f] = state[k];
+        evaluate(p, in, load_index(w.idx, w.idx_bits, e), span.row, e, f, value);
+        fold_edge(alg, value, state, args, rv);
+      }
+    }
+    for (int k = 0; k < arity; ++k) carried[k] = 0.0f;
+    if (!LONG) {
+      if (live) {
+        const float g = __ldg(dy + span.row * p.width + f);
+        region_eval(alg.finalize, state, rv);
+        region_reverse(alg.finalize, rv, &g, 1, radj, carried, arity);
+      }
+    } else {
+      for (int k = 0; k < arity; ++k) part[k * kLongThreads + threadIdx.x] = state[k];
+      __syncthreads();
+      if (group == 0 && live) {
+        int used = 0;
+        for (int k = 0; k < arity; ++k) state[k] = alg.identity[k];
+        for (int g = 0; g < kGroups && (int64_t)g * span.slice < span.degree; ++g, ++used) {
+          for (int k = 0; k < arity; ++k) {
+            joined[k * kLongThreads + g * LANES + lane] = state[k];
+            args[k] = state[k];
+            args[arity + k] = part[k * kLongThreads + g * LANES + lane];
+          }
+          region_eval(alg.combine, args, rv);
+          for (int k = 0; k < arity; ++k) state[k] = rv[alg.combine.out[k]];
+        }
+        const float g_row = __ldg(dy + span.row * p.width + f);
+        region_eval(alg.finalize, state, rv);
+        region_reverse(alg.finalize, rv, &g_row, 1, radj, carried, arity);
+        for (int g = used - 1; g >= 0; --g) {
+          for (int k = 0; k < arity; ++k) {
+            args[k] = joined[k * kLongThreads + g * LANES + lane];
+            args[arity + k] = part[k * kLongThreads + g * LANES + lane];
+          }
+          region_eval(alg.combine, args, rv);
+          region_reverse(alg.combine, rv, carried, arity, radj, arg_adjoint, 2 * arity);
+          for (int k = 0; k < arity; ++k) {
+            carried[k] = arg_adjoint[k];
+            part[k * kLongThreads + g * LANES + lane] = arg_adjoint[arity + k];
+          }
+        }
+      }
+      __syncthreads();
+      for (int k = 0; k < arity; ++k) carried[k] = part[k * kLongThreads + threadIdx.x];
+    }
+    if (live) {
+      for (int64_t e = span.end - 1; e >= span.begin; --e) {
+        evaluate(p, in, load_index(w.idx, w.idx_bits, e), span.row, e, f, value);
+        for (int k = 0; k < arity; ++k) args[k] = prefix[(e * arity + k) * p.width + f];
+        for (int j = 0; j < alg.num_messages; ++j) args[arity + j] = value[alg.message_slot[j]];
+        region_eval(alg.step, args, rv);
+        region_reverse(alg.step, rv, carried, arity, radj, arg_adjoint, arity + alg.num_messages);
+        for (int k = 0; k < arity; ++k) carried[k] = arg_adjoint[k];
+        for (int j = 0; j < alg.num_messages; ++j)
+          message_grads[((int64_t)j * num_edges + e) * p.width + f] = arg_adjoint[arity + j];
+      }
+    }
+    if (LONG) __syncthreads();       // `part` is written again by the next chunk
+  }
+}
+
+int32_t check_region(const tgb_region &r, int n_args, int n_out, const char *name) {
+  if (r.num_instructions < 1 || r.num_instructions > kMaxR)
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "%s: region size out of range", name);
+  for (int i = 0; i < r.num_instructions; ++i) {
+    const int op = r.op[i];
+    if (op > TGB_EP_NEG) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "%s: unknown opcode %d", name, op);
+    if (op == TGB_EP_LOAD) {
+      if (r.a[i] >= n_args) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "%s: argument index out of range", name);
+    } else if (op == TGB_EP_CONST) {
+      if (r.a[i] >= TGB_ALG_MAX_CONSTANTS) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "%s: constant index out of range", name);
+    } else {
+      const bool binary = op >= TGB_EP_ADD && op <= TGB_EP_MAX;
+      if (r.a[i] >= i || (binary && r.b[i] >= i))
+        TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "%s: instruction %d reads a later value", name, i);
+    }
+  }
+  for (int k = 0; k < n_out; ++k)
+    if (r.out[k] >= r.num_instructions) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "%s: output %d out of range", name, k);
+  return TGB_STATUS_OK;
+}
+
+int32_t check_algebra(const tgb_edge_program *p, const tgb_edge_algebra *alg) {
+  if (!alg) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null algebra");
+  if (alg->arity < 1 || alg->arity > kMaxA || alg->num_messages < 1 || alg->num_messages > kMaxM)
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "algebra: state or message count out of range");
+  for (int j = 0; j < alg->num_messages; ++j)
+    if (alg->message_slot[j] >= p->num_instructions) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "algebra: message slot out of range");
+  int32_t status = check_region(alg->step, alg->arity + alg->num_messages, alg->arity, "step");
+  if (status == TGB_STATUS_OK) status = check_region(alg->combine, 2 * alg->arity, alg->arity, "combine");
+  if (status == TGB_STATUS_OK) status = check_region(alg->finalize, alg->arity, 1, "finalize");
+  return status;
+}
+
+Operands operand_table(const tgb_edge_program *program, const void *const *operands) {
+  Operands in;
+  for (int k = 0; k < kMaxO; ++k) in.ptr[k] = k < program->num_operands ? static_cast<const float *>(operands[k]) : nullptr;
+  return in;
+}
+
+Seeds message_seeds(const tgb_csr_plan *plan, const tgb_edge_algebra *alg, const void *message_grads) {
+  Seeds seeds{static_cast<const float *>(message_grads), plan->num_edges, alg->num_messages, {0, 0, 0, 0}};
+  for (int j = 0; j < alg->num_messages; ++j) seeds.slot[j] = alg->message_slot[j];
+  return seeds;
+}
+
+}  // namespace
+}  // namespace tgb
+
+extern "C" int32_t tgb_edge_algebra_fwd(const tgb_csr_plan *plan, const tgb_edge_program *program,
+                                        const tgb_edge_algebra *algebra, const void *const *operands, void *out,
+                                        uint64_t stream) {
+  int32_t status = check_program(plan, program, operands);
+  if (status == TGB_STATUS_OK) status = check_algebra(program, algebra);
+  if (status != TGB_STATUS_OK) return status;
+  if (plan->num_dst == 0) return TGB_STATUS_OK;
+  if (!out) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null output");
+  const Operands in = operand_table(program, operands);
+  const Walk w = forward_walk(plan);
+  const int lanes = lanes_for_width(program->width);
+  const unsigned blocks = (unsigned)ceil_div(plan->num_dst * lanes, kThreads);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define TGB_FWD(L)                                                                                                  \
+  k_edge_algebra_fwd<L, false><<<blocks, kThreads, 0, st>>>(*program, *algebra, in, w, static_cast<float *>(out)); \
+  if (w.n_long > 0)                                                                                                 \
+    k_edge_algebra_fwd<L, true><<<(unsigned)w.n_long, kLongThreads, 0, st>>>(*program, *algebra, in, w,            \
+                                                                             static_cast<float *>(out))
+  TGB_EP_LANES(lanes, TGB_FWD)
+#undef TGB_FWD
+  TGB_LAUNCHED();
+  if (w.n_long > 0) TGB_LAUNCHED();
+  return TGB_STATUS_OK;
+}
+
+extern "C" int32_t tgb_edge_algebra_bwd_messages(const tgb_csr_plan *plan, const tgb_edge_program *program,
+                                                 const tgb_edge_algebra *algebra, const void *const *operands,
+                                                 const void *dy, void *prefix, void *message_grads,
+                                                 uint64_t stream) {
+  int32_t status = check_program(plan, program, operands);
+  if (status == TGB_STATUS_OK) status = check_algebra(program, algebra);
+  if (status != TGB_STATUS_OK) return status;
+  if (plan->num_dst == 0 || plan->num_edges == 0) return TGB_STATUS_OK;
+  if (!dy || !prefix || !message_grads) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
+  const Operands in = operand_table(program, operands);
+  const Walk w = forward_walk(plan);
+  const int lanes = lanes_for_width(program->width);
+  const unsigned blocks = (unsigned)ceil_div(plan->num_dst * lanes, kThreads);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define TGB_BWD(L)                                                                                                   \
+  k_edge_algebra_bwd_messages<L, false><<<blocks, kThreads, 0, st>>>(                                                \
+      *program, *algebra, in, w, static_cast<const float *>(dy), static_cast<float *>(prefix),                      \
+      static_cast<float *>(message_grads), plan->num_edges);                                                        \
+  if (w.n_long > 0)                                                                                                  \
+    k_edge_algebra_bwd_messages<L, true><<<(unsigned)w.n_long, kLongThreads, 0, st>>>(                              \
+        *program, *algebra, in, w, static_cast<const float *>(dy), static_cast<float *>(prefix),                    \
+        static_cast<float *>(message_grads), plan->num_edges)
+  TGB_EP_LANES(lanes, TGB_BWD)
+#undef TGB_BWD
+  TGB_LAUNCHED();
+  if (w.n_long > 0) TGB_LAUNCHED();
+  return TGB_STATUS_OK;
+}
+
+extern "C" int32_t tgb_edge_algebra_bwd_rows(const tgb_csr_plan *plan, const tgb_edge_program *program,
+                                             const tgb_edge_algebra *algebra, const void *const *operands,
+                                             const void *message_grads, void *const *grads, uint64_t stream) {
+  if (!plan || !program) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null argument");
+  const int32_t status = check_algebra(program, algebra);
+  if (status != TGB_STATUS_OK) return status;
+  if (!message_grads) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null message cotangents");
+  return backward(false, plan, program, operands, kReducerSeeded, message_grads, grads, nullptr, nullptr, stream,
+                  message_seeds(plan, algebra, message_grads));
+}
+
+extern "C" int32_t tgb_edge_algebra_bwd_sources(const tgb_csr_plan *plan, const tgb_edge_program *program,
+                                                const tgb_edge_algebra *algebra, const void *const *operands,
+                                                const void *message_grads, void *const *grads, uint64_t stream) {
+  if (!plan || !program) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null argument");
+  const int32_t status = check_algebra(program, algebra);
+  if (status != TGB_STATUS_OK) return status;
+  if (!message_grads) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null message cotangents");
+  return backward(true, plan, program, operands, kReducerSeeded, message_grads, grads, nullptr, nullptr, stream,
+                  message_seeds(plan, algebra, message_grads));
 }

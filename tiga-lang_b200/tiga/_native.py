@@ -80,6 +80,10 @@ _SIGNATURES = {
     "tgb_edge_program_fwd": (_i32, [_vp, _vp, _vp, _i32, _f32, _vp, _vp, _vp, _u64]),
     "tgb_edge_program_bwd_rows": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _u64]),
     "tgb_edge_program_bwd_sources": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _u64]),
+    "tgb_edge_algebra_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64]),
+    "tgb_edge_algebra_bwd_messages": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64]),
+    "tgb_edge_algebra_bwd_rows": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u64]),
+    "tgb_edge_algebra_bwd_sources": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u64]),
     "tgb_column_sum": (_i32, [_vp, _i64, _i64, _vp, _u64]),
 }
 

@@ -130,8 +130,9 @@ def _stage_params(params: Mapping[str, Any]):
 
 
 def capture_edge(method, params: Mapping[str, Any]):
-    """Run ``edge`` on symbolic fields; returns an Expr, an OnlineSoftmaxItem or
-    a ReducerCall of Exprs, or None when the body leaves the vocabulary."""
+    """Run ``edge`` on symbolic fields; returns an Expr (one message), an OnlineSoftmaxItem, a
+    ReducerCall of several Exprs (``self.reducer(m0, m1, ...)``), or None when the body leaves the
+    vocabulary."""
     from .reducer import OnlineSoftmaxItem, ReducerCall
 
     try:
@@ -143,6 +144,9 @@ def capture_edge(method, params: Mapping[str, Any]):
         return result
     if isinstance(result, ReducerCall) and len(result.messages) == 1 and isinstance(result.messages[0], Expr):
         return result.messages[0]
+    if isinstance(result, ReducerCall) and all(
+            isinstance(m, Expr) or (isinstance(m, (int, float)) and not isinstance(m, bool)) for m in result.messages):
+        return ReducerCall(reducer=result.reducer, messages=tuple(as_expr(m) for m in result.messages))
     return None
 
 

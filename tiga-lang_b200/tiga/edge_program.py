@@ -75,7 +75,15 @@ class EdgeProgram:
 def compile_expression(expr) -> EdgeProgram | None:
     """Register program of a staged expression, or None when it leaves the element-wise vocabulary
     (a ``sum`` over features, a non-numeric constant) or exceeds the kernel's table sizes.
-    Structurally equal sub-expressions (``s`` used twice in ``maximum(s, 0.2 * s)``) are evaluated once."""
+    Structurally equal sub-expressions (``s`` used twice in ``maximum(s, 0.2 * s)``) are evaluated once.
+    The message is the value of the last instruction."""
+    compiled = compile_expressions((expr,))
+    return None if compiled is None else compiled[0]
+
+
+def compile_expressions(roots) -> tuple[EdgeProgram, tuple[int, ...]] | None:
+    """One register program for several staged expressions (the messages ``self.reducer(m0, m1, ...)``
+    binds) and, per expression, the instruction that holds its value."""
     ops, lhs, rhs, constants, operands = [], [], [], [], []
     memo: dict[int, int] = {}
 
@@ -120,13 +128,17 @@ def compile_expression(expr) -> EdgeProgram | None:
         memo[id(node)] = result
         return result
 
-    if visit(expr) is None:
-        return None
+    slots = []
+    for root in roots:
+        slot = visit(root)
+        if slot is None:
+            return None
+        slots.append(slot)
     if len(ops) > MAX_INSTRUCTIONS or len(operands) > MAX_OPERANDS or len(constants) > MAX_CONSTANTS:
         return None
     if not operands:
         return None
-    return EdgeProgram(tuple(ops), tuple(lhs), tuple(rhs), tuple(constants), tuple(operands))
+    return EdgeProgram(tuple(ops), tuple(lhs), tuple(rhs), tuple(constants), tuple(operands)), tuple(slots)
 
 
 def _entity_shape(operand: Operand, tensor: torch.Tensor) -> tuple[int, ...]:
@@ -296,5 +308,6 @@ class EdgeProgramFunction(torch.autograd.Function):
                                            for g, shape in zip(grads, ctx.shapes)])
 
 
-__all__ = ["EdgeProgram", "EdgeProgramFunction", "Operand", "compile_expression", "bind", "make_struct",
+__all__ = ["EdgeProgram", "EdgeProgramFunction", "Operand", "compile_expression", "compile_expressions", "bind",
+           "make_struct",
            "REDUCE_SUM", "REDUCE_MEAN", "REDUCE_MAX", "REDUCE_PROD"]

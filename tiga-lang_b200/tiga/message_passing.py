@@ -92,6 +92,34 @@ def _reducer_kind(reducer) -> str | None:
     return cap.reducer_algebra(reducer)
 
 
+class _StableSoftmaxAlgebra(Reducer):
+    """``tg.online_softmax()`` as a plain tuple algebra -- state (running maximum, denominator,
+    numerator), the regions of the reference's ``capture_online_softmax``
+    (python/tiga/compiler/reducer_capture.py:133-189) -- for score / value expressions no dedicated
+    kernel takes.  A row without edges finalizes to 0 / tiny = 0, the reference's empty-row value."""
+
+    name = "online_softmax"
+    associative = commutative = True
+
+    def identity(self):
+        return -1.0e30, 0.0, 0.0
+
+    def lift(self, score, value):
+        return score, 1.0, value
+
+    def combine(self, left, right):
+        from . import math as tg_math
+
+        top = tg_math.maximum(left[0], right[0])
+        keep_left, keep_right = tg_math.exp(left[0] - top), tg_math.exp(right[0] - top)
+        return top, keep_left * left[1] + keep_right * right[1], keep_left * left[2] + keep_right * right[2]
+
+    def finalize(self, state):
+        from . import math as tg_math
+
+        return state[2] / tg_math.maximum(state[1], 1.0e-30)
+
+
 _MISS = object()
 
 
@@ -320,6 +348,14 @@ class MessagePassing(Kernel):
         if isinstance(self.reducer, OnlineSoftmaxReducer):
             return self._specialise_online_softmax(graph, src, dst, edge, params, staged, constants)
         kind = _reducer_kind(self.reducer)
+        if isinstance(staged, ReducerCall) or kind is None:
+            generic = self._specialise_algebra(graph, src, dst, edge, params, staged, constants)
+            if generic is None:
+                raise NotImplementedError(
+                    f"no native kernel for reducer {type(self.reducer).__name__} with this edge expression: "
+                    "a user algebra needs associative = True, a state of at most four numbers, one finalized "
+                    "value and element-wise edge expressions")
+            return generic
         pattern = cap.recognize_weighted_sum(staged)
         if kind in ("sum", "mean", "max", "prod") and isinstance(staged, cap.Expr):
             vector_weight = (pattern is not None and pattern.edge_field is not None and pattern.edge_field in edge
@@ -474,6 +510,72 @@ class MessagePassing(Kernel):
             extra_key=(program.key(), probe_shapes, kind))
         return bindings, tensors, constants, runner
 
+    def _specialise_algebra(self, graph, src, dst, edge, params, staged, constants, reducer=None,
+                            scalars_broadcast=False):
+        """A reducer none of the dedicated kernels folds: its staged ``lift / combine / finalize`` run
+        as register programs inside the interpreting kernels, forward and reverse mode.
+        ``scalars_broadcast``: fields with one number per entity are taken as ``[n, 1, ...]`` against
+        fields with more dimensions (a score per edge against a payload vector)."""
+        from . import algebra as alg
+        from . import edge_program as ep
+
+        reducer = self.reducer if reducer is None else reducer
+        messages = staged.messages if isinstance(staged, ReducerCall) else (staged,)
+        if not all(isinstance(m, cap.Expr) for m in messages):
+            return None
+        rules = alg.capture_algebra(reducer, len(messages))
+        compiled = ep.compile_expressions(messages)
+        if rules is None or compiled is None:
+            return None
+        program, message_slots = compiled
+        implicit = _implicit_edge_names(graph)
+        _refuse_shadowing(implicit, edge)
+        row_ptr, col_idx = graph.resolve_csr()
+        _validate_fields("edge", edge, col_idx.numel(), graph.device)
+        spaces = {"src": src, "dst": dst, "edge": edge, "param": params}
+        bindings, tensors, slots = [], [], []
+        for operand in program.operands:
+            if operand.role == "edge" and operand.name in implicit:
+                slots.append(operand.name)
+                continue
+            if operand.name not in spaces[operand.role]:
+                raise KeyError(f"edge() reads {operand.role}.{operand.name}, which was not bound")
+            slots.append(len(tensors))
+            bindings.append((operand.role, operand.name))
+            tensors.append(spaces[operand.role][operand.name])
+        cell = SimpleNamespace(graph=graph)
+
+        def runner(*bound):
+            current = cell.graph
+            provided = None
+            operands = []
+            for slot in slots:
+                if isinstance(slot, str):
+                    if provided is None:
+                        provided = current.implicit_edge_fields(*current.resolve_csr())
+                    operands.append(provided[slot])
+                else:
+                    operands.append(bound[slot])
+            if scalars_broadcast:
+                rank = max(t.ndim - 1 for o, t in zip(program.operands, operands) if o.role != "param")
+                operands = [t.reshape(t.shape[0], *((1,) * rank)) if o.role != "param" and t.ndim == 1 and rank else t
+                            for o, t in zip(program.operands, operands)]
+            return alg.EdgeAlgebraFunction.apply(current, program, message_slots, rules, *operands)
+
+        runner.cell = cell
+        probe_shapes = tuple(tuple(t.shape[1:]) if role != "param" else tuple(t.shape)
+                             for (role, _), t in zip(bindings, tensors))
+        self._record(
+            graph, "b200-generic-csr-algebra-reducer",
+            ("capture-edge-udf", "capture-reducer-regions", "compile-edge-register-program",
+             "reverse-mode-fold", "reverse-mode-edge-program"),
+            (f"{len(messages)} message(s), state of {rules.arity}: step / combine / finalize of "
+             f"{len(rules.step.ops)} / {len(rules.combine.ops)} / {len(rules.finalize.ops)} instructions; rows "
+             "folded from the identity in edge order (combine(earlier, later)); the fold is differentiated "
+             "by a forward sweep that keeps the state before each edge and a backward sweep through step",),
+            extra_key=(program.key(), message_slots, rules.key(), probe_shapes))
+        return bindings, tensors, constants, runner
+
     def _specialise_online_softmax(self, graph, src, dst, edge, params, staged, constants):
         from . import attention
 
@@ -520,6 +622,15 @@ class MessagePassing(Kernel):
                          ("capture-edge-udf", "recognize-dense-attention", "schedule-varlen-tiles"),
                          ("implicit block-lower-triangular relation; no edge is materialised",))
             return bindings, tensors, constants, runner
+        # any other score / value expressions with one score per edge: the reducer written as a plain
+        # tuple algebra and folded by the interpreting kernels
+        if graph.sequence_boundaries() is None and isinstance(staged, OnlineSoftmaxItem):
+            messages = (cap.as_expr(staged.score), cap.as_expr(staged.value))
+            generic = self._specialise_algebra(graph, src, dst, edge, params,
+                                               ReducerCall(reducer=self.reducer, messages=messages), constants,
+                                               reducer=_StableSoftmaxAlgebra(), scalars_broadcast=True)
+            if generic is not None:
+                return generic
         raise NotImplementedError("no native kernel for this online_softmax edge expression")
 
     # ------------------------------------------------------------- prepare
@@ -549,11 +660,20 @@ class MessagePassing(Kernel):
         src_at_edge = SimpleNamespace(**{name: value[col_idx] for name, value in src.items()})
         dst_at_edge = SimpleNamespace(**{name: value[destination] for name, value in dst.items()})
         message = cap.call_region(self.edge, (src_at_edge, dst_at_edge, SimpleNamespace(**edge)), params)
-        if isinstance(message, ReducerCall):
-            if len(message.messages) != 1:
-                raise NotImplementedError("the eager evaluator takes single-message reducer bindings")
+        if isinstance(message, ReducerCall) and len(message.messages) == 1:
             message = message.messages[0]
-        aggregate = _eager_reduce(self.reducer, message, destination, graph.schema.num_dst)
+        if isinstance(message, ReducerCall) or (
+                not isinstance(self.reducer, OnlineSoftmaxReducer) and _reducer_kind(self.reducer) is None):
+            # a user algebra: the definition itself, row by row (small graphs only)
+            from .algebra import fold_eagerly
+
+            messages = message.messages if isinstance(message, ReducerCall) else (message,)
+            edges = col_idx.numel()
+            messages = tuple(m if isinstance(m, torch.Tensor) else torch.full((edges,), float(m), device=graph.device)
+                             for m in messages)
+            aggregate = fold_eagerly(self.reducer, messages, row_ptr, graph.schema.num_dst)
+        else:
+            aggregate = _eager_reduce(self.reducer, message, destination, graph.schema.num_dst)
         if type(self).node is MessagePassing.node:
             return aggregate
         return cap.call_region(self.node, (SimpleNamespace(**dst), aggregate), params)
