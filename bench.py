@@ -670,7 +670,9 @@ def run_e2e(args, step, x, weight, linears, traversed, world):
         torch.cuda.synchronize(device)
 
     run(2)
-    steps = max(3, min(args.steps, 10))
+    # the same number of steps as the device-resident measurement (bounded: a step moves 25 GB over the
+    # host link); the pipeline starts empty and is drained inside the timed region
+    steps = max(3, min(args.steps, 40))
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize(device)
     begin.record()
