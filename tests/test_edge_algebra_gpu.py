@@ -93,7 +93,7 @@ def test_noncommutative_composition_known_answers():
     bias = torch.tensor([1.0, 4.0, 2.0], device="cuda", requires_grad=True)
     kernel = Composition()
     out = kernel(graph=small_graph(), src={"scale": scale, "bias": bias}, dst={})
-    assert kernel.last_variant.lowering == "b200-generic-csr-algebra-reducer"
+    assert kernel.last_variant.lowering == "b200-csr-algebra-tile"
     assert out.tolist() == [7.0, 0.0, 37.0]
     dscale, dbias = torch.autograd.grad(out.sum(), (scale, bias))
     assert dscale.tolist() == [0.0, 6.0, 7.0]
@@ -135,7 +135,7 @@ def test_builtin_online_softmax_with_source_scores_known_answers():
     value = torch.tensor([[1.0, 0.0], [0.0, 2.0], [3.0, 1.0]], device="cuda", requires_grad=True)
     kernel = SourceScoreAttention()
     out = kernel(graph=graph, src={"score": score, "value": value}, dst={})
-    assert kernel.last_variant.lowering == "b200-generic-csr-algebra-reducer"
+    assert kernel.last_variant.lowering == "b200-csr-algebra-tile"
     want = torch.tensor([[1.2384058, 0.1192029], [0.0, 2.0], [0.7310586, 0.5378829]])
     torch.testing.assert_close(out.detach().cpu(), want, rtol=1e-5, atol=1e-5)
     dscore, dvalue = torch.autograd.grad(out.sum(), (score, value))

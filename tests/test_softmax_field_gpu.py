@@ -109,7 +109,7 @@ def test_other_online_softmax_programs_take_the_algebra_kernels_or_raise():
     score = torch.tensor([0.3, -0.2, 0.9], device="cuda")
     kernel = Scaled()
     got = kernel(graph=graph, src={"value": value}, dst={}, edge={"score": score})
-    assert kernel.last_variant.lowering == "b200-generic-csr-algebra-reducer"
+    assert kernel.last_variant.lowering == "b200-csr-algebra-tile"
     want = Scaled().reference(graph=tg.Graph.from_csr(row_ptr.cpu(), col.cpu(), num_src=2), src={"value": value.cpu()},
                               dst={}, edge={"score": score.cpu()})
     torch.testing.assert_close(got.cpu(), want, rtol=1e-5, atol=1e-6)

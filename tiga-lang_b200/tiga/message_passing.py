@@ -566,7 +566,7 @@ class MessagePassing(Kernel):
         probe_shapes = tuple(tuple(t.shape[1:]) if role != "param" else tuple(t.shape)
                              for (role, _), t in zip(bindings, tensors))
         self._record(
-            graph, "b200-generic-csr-algebra-reducer",
+            graph, "b200-csr-algebra-tile",
             ("capture-edge-udf", "capture-reducer-regions", "compile-edge-register-program",
              "reverse-mode-fold", "reverse-mode-edge-program"),
             (f"{len(messages)} message(s), state of {rules.arity}: step / combine / finalize of "
