@@ -194,6 +194,29 @@ def wsum_bwd_dw(row_ptr, col_idx, dy, x, mean=False):
     return dw
 
 
+# ------------------------------------------------------------------ product
+def product_fwd(row_ptr, message):
+    """out[i] = product of the rows ``message[row_ptr[i]:row_ptr[i+1]]`` (1 for a row without edges)."""
+    row_ptr, prow = _i64(row_ptr)
+    m2, shape = _as_2d(message)
+    N, F = row_ptr.size - 1, m2.shape[1]
+    out = np.zeros((N, F), np.float32)
+    lib().orc_csr_product_fwd_f32(prow, _c64(N), m2.ctypes.data_as(_f32p), _c64(F), out.ctypes.data_as(_f32p))
+    return out.reshape((N,) + tuple(shape[1:]))
+
+
+def product_vjp(row_ptr, message, dy):
+    """Cotangent of every message: dy[row] times the product of the row's other messages."""
+    row_ptr, prow = _i64(row_ptr)
+    m2, shape = _as_2d(message)
+    dy2, _ = _as_2d(dy)
+    N, F = row_ptr.size - 1, m2.shape[1]
+    grad = np.zeros_like(m2)
+    lib().orc_csr_product_vjp_f32(prow, _c64(N), m2.ctypes.data_as(_f32p), _c64(F), dy2.ctypes.data_as(_f32p),
+                                  grad.ctypes.data_as(_f32p))
+    return grad.reshape(shape)
+
+
 # ---------------------------------------------------------------------- max
 def max_fwd(row_ptr, col_idx, x, w=None, identity=-np.inf):
     row_ptr, prow = _i64(row_ptr)

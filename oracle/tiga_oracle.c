@@ -242,6 +242,43 @@ ORC_API void orc_csr_wsum_bwd_dw_f32(const int64_t *row_ptr,
 }
 
 /* ------------------------------------------------------------------------ */
+/* Product reducer (tg.prod)                                                  */
+/* ------------------------------------------------------------------------ */
+
+/* out[i,f] = product of the messages of row i, left to right from 1
+ * (csr_segment_product, python/tiga/tensor/core.py:1575-1585; the Torch
+ * interop folds the same way through index_reduce("prod") from
+ * reducer.identity() = 1, python/tiga/interop/torch/reducer_oracle.py:160-178).
+ * message: [E, F], one row per edge in CSR order. */
+ORC_API void orc_csr_product_fwd_f32(const int64_t *row_ptr, int64_t N,
+                                     const float *message, int64_t F, float *out) {
+#pragma omp parallel for schedule(dynamic, 256)
+  for (int64_t r = 0; r < N; ++r) {
+    float *o = out + r * F;
+    for (int64_t f = 0; f < F; ++f) o[f] = 1.0f;
+    for (int64_t e = row_ptr[r]; e < row_ptr[r + 1]; ++e)
+      for (int64_t f = 0; f < F; ++f) o[f] = o[f] * message[e * F + f];
+  }
+}
+
+/* d message[e,f] = dy[row,f] times the product of the OTHER messages of the
+ * row, taken in order (csr_segment_product_vjp, python/tiga/tensor/core.py:
+ * 1586-1598): zero-safe by construction, O(degree^2) per row. */
+ORC_API void orc_csr_product_vjp_f32(const int64_t *row_ptr, int64_t N,
+                                     const float *message, int64_t F,
+                                     const float *dy, float *d_message) {
+#pragma omp parallel for schedule(dynamic, 64)
+  for (int64_t r = 0; r < N; ++r)
+    for (int64_t e = row_ptr[r]; e < row_ptr[r + 1]; ++e)
+      for (int64_t f = 0; f < F; ++f) {
+        float product = dy[r * F + f];
+        for (int64_t other = row_ptr[r]; other < row_ptr[r + 1]; ++other)
+          if (other != e) product = product * message[other * F + f];
+        d_message[e * F + f] = product;
+      }
+}
+
+/* ------------------------------------------------------------------------ */
 /* Max reducer (user Reducer whose combine is tg.math.maximum)               */
 /* ------------------------------------------------------------------------ */
 

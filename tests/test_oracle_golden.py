@@ -182,3 +182,35 @@ def test_max_reducer_algebra(oracle):
     assert out[2, 0] == 2.0 and arg[2, 0] == 3          # first winner kept
     dx, dw = oracle.max_bwd(row_ptr, col, 3, np.ones((3, 2), np.float32), x, arg)
     assert dx[1, 0] == 1.0 and dx[2, 0] == 1.0 and dx[0, 0] == 0.0
+
+
+def test_product_reducer_known_answers_and_reference_fixtures(oracle):
+    """tg.prod(): the values the reference's tests assert (tests/python/test_builtin_reducers.py:44-59,
+    tests/python/test_message_passing_autograd.py:439-485) and the fixtures its Torch evaluator
+    produced (tests/golden/make_golden_programs.py): forward bit for bit (same left fold from 1),
+    cotangents within float32 rounding (Torch divides the row product by the message, the oracle
+    multiplies the other messages)."""
+    import os
+
+    row_ptr, col = np.array([0, 2, 2, 5]), np.array([0, 1, 0, 1, 2])
+    x = np.array([2.0, 3.0, 5.0], np.float32)
+    out = oracle.product_fwd(row_ptr, x[col])
+    assert out.tolist() == [6.0, 1.0, 30.0]
+    d_message = oracle.product_vjp(row_ptr, x[col], np.ones(3, np.float32))
+    assert np.bincount(col, weights=d_message, minlength=3).tolist() == [18.0, 12.0, 6.0]
+    edge = np.array([2.0, 0.0, 3.0, 4.0, 5.0], np.float32)
+    assert oracle.product_fwd([0, 3, 5], edge).tolist() == [0.0, 20.0]
+    assert oracle.product_vjp([0, 3, 5], edge, np.array([7.0, 11.0], np.float32)).tolist() == [0.0, 42.0, 0.0, 55.0, 44.0]
+
+    cases = dict(np.load(os.path.join(os.path.dirname(__file__), "golden", "program_cases.npz")))
+    row_ptr, col = cases["row_ptr"], cases["col"]
+    message = cases["prod_edge_in_x"]
+    np.testing.assert_array_equal(oracle.product_fwd(row_ptr, message), cases["prod_edge_out"])
+    np.testing.assert_allclose(oracle.product_vjp(row_ptr, message, cases["prod_edge_dy"]), cases["prod_edge_d_x"],
+                               rtol=2e-5, atol=1e-7)
+    x = cases["prod_src_in_x"]
+    np.testing.assert_array_equal(oracle.product_fwd(row_ptr, x[col]), cases["prod_src_out"])
+    d_message = oracle.product_vjp(row_ptr, x[col], cases["prod_src_dy"])
+    d_x = np.zeros_like(x)
+    np.add.at(d_x, col, d_message)
+    np.testing.assert_allclose(d_x, cases["prod_src_d_x"], rtol=1e-4, atol=1e-6)

@@ -244,7 +244,7 @@ class EdgeAlgebraFunction(torch.autograd.Function):
                                                    ep._pointers(rows), out.data_ptr(), ep._stream(device)),
                           "tgb_edge_algebra_fwd")
         ctx.graph, ctx.program, ctx.algebra, ctx.struct, ctx.rules = graph, program, algebra, struct, rules
-        ctx.width = width
+        ctx.width, ctx.edges = width, int(plan.num_edges)
         ctx.save_for_backward(*rows)
         ctx.shapes = [tuple(t.shape) for t in tensors]
         return out.reshape((graph.num_dst,) + feature_shape)
@@ -258,8 +258,7 @@ class EdgeAlgebraFunction(torch.autograd.Function):
         device = dy.device
         width = ctx.width
         dy = dy.detach().contiguous().reshape(graph.num_dst, width)
-        row_ptr, col_idx = graph.resolve_csr()
-        edges = int(col_idx.numel())
+        edges = ctx.edges
         grads: list[torch.Tensor | None] = [None] * len(rows)
         wanted = (ctypes.c_void_p * ep.MAX_OPERANDS)()
         param_partials = {}
