@@ -139,6 +139,21 @@ def test_capture_recognisers():
 
     assert cap.reducer_algebra(UserProduct()) == "prod"
 
+    # float keyword parameters of edge() are read at every call, unless Python itself consumed the value
+    from tiga import edge_program as ep
+
+    class Scaled(tg.MessagePassing):
+        def edge(self, src, dst, edge, scale, shift):
+            return (src.u - dst.u) * scale + shift * 2.0 + 0.25
+
+    consumed = set()
+    staged = cap.capture_edge(Scaled().edge, {"scale": 0.25, "shift": 0.25}, consumed)
+    assert consumed == {"shift"}                                  # shift * 2.0 happened in Python
+    program = ep.compile_expression(staged).literalised(frozenset(consumed))
+    assert program.constant_names == ("scale", None, None) and program.constants == (0.25, 0.5, 0.25)
+    assert program.rebound({"scale": 0.75}).constants == (0.75, 0.5, 0.25)
+    assert program.rebound({"scale": 0.75}).key() == program.key()
+
     # anything else is staged into step / combine / finalize register programs
     from tiga import algebra as alg
 

@@ -121,23 +121,67 @@ def call_region(method, positional, params):
     return method(*positional, **selected_params(method, params))
 
 
-def _stage_params(params: Mapping[str, Any]):
+class NamedScalar(float):
+    """A float keyword parameter as ``edge()`` sees it while it is staged.  It behaves like the
+    number; when it meets a staged expression it becomes a ``constant`` leaf that remembers which
+    parameter it came from, so a compiled program can take the parameter's value at every call
+    instead of baking it in.  Anything Python itself does with the number (arithmetic with other
+    numbers, comparisons, truth tests, conversions, hashing) is recorded in ``observed``: the value
+    has then shaped the staged program in a way nothing can re-bind."""
+
+    __slots__ = ("name", "observed")
+
+    def __new__(cls, value, name, observed):
+        self = super().__new__(cls, value)
+        self.name, self.observed = name, observed
+        return self
+
+
+def _install_observation() -> None:
+    def watch(dunder):
+        plain = getattr(float, dunder)
+
+        def method(self, *args):
+            if not any(isinstance(a, Expr) for a in args):
+                self.observed.add(self.name)
+            return plain(self, *args)
+
+        return method
+
+    for dunder in ("__add__", "__radd__", "__sub__", "__rsub__", "__mul__", "__rmul__", "__truediv__",
+                   "__rtruediv__", "__floordiv__", "__rfloordiv__", "__mod__", "__rmod__", "__pow__", "__rpow__",
+                   "__neg__", "__pos__", "__abs__", "__lt__", "__le__", "__gt__", "__ge__", "__eq__", "__ne__",
+                   "__bool__", "__int__", "__float__", "__round__", "__trunc__", "__floor__", "__ceil__",
+                   "__hash__", "__index__" if hasattr(float, "__index__") else "__hash__"):
+        setattr(NamedScalar, dunder, watch(dunder))
+
+
+_install_observation()
+
+
+def _stage_params(params: Mapping[str, Any], observed: set | None = None):
     staged = {}
     for name, value in params.items():
         is_tensor = type(value).__module__.split(".")[0] == "torch" and hasattr(value, "shape")
-        staged[name] = Expr("param", (name,)) if is_tensor else value
+        if is_tensor:
+            staged[name] = Expr("param", (name,))
+        elif observed is not None and type(value) is float:
+            staged[name] = NamedScalar(value, name, observed)
+        else:
+            staged[name] = value
     return staged
 
 
-def capture_edge(method, params: Mapping[str, Any]):
+def capture_edge(method, params: Mapping[str, Any], observed: set | None = None):
     """Run ``edge`` on symbolic fields; returns an Expr (one message), an OnlineSoftmaxItem, a
     ReducerCall of several Exprs (``self.reducer(m0, m1, ...)``), or None when the body leaves the
-    vocabulary."""
+    vocabulary.  With ``observed`` (a set), float parameters are staged as ``NamedScalar`` and the
+    names whose values Python itself consumed are added to the set."""
     from .reducer import OnlineSoftmaxItem, ReducerCall
 
     try:
         result = method(FieldNamespace("src"), FieldNamespace("dst"), FieldNamespace("edge"),
-                        **_stage_params(selected_params(method, params)))
+                        **_stage_params(selected_params(method, params), observed))
     except Exception:
         return None
     if isinstance(result, (Expr, OnlineSoftmaxItem)):

@@ -67,9 +67,33 @@ class EdgeProgram:
     rhs: tuple[int, ...]
     constants: tuple[float, ...]
     operands: tuple[Operand, ...]
+    # per constant: the float keyword parameter it is read from at every call, or None for a literal
+    constant_names: tuple[str | None, ...] = ()
 
     def key(self):
-        return (self.ops, self.lhs, self.rhs, self.constants, self.operands)
+        """Identity of the program: a constant read from a parameter counts by name, not by value."""
+        names = self.constant_names or (None,) * len(self.constants)
+        constants = tuple(("scalar", name) if name is not None else value
+                          for name, value in zip(names, self.constants))
+        return (self.ops, self.lhs, self.rhs, constants, self.operands)
+
+    def scalar_names(self) -> tuple[str, ...]:
+        return tuple(name for name in self.constant_names if name is not None)
+
+    def literalised(self, names) -> "EdgeProgram":
+        """The program with the constants of ``names`` frozen at their staged values."""
+        if not any(name in names for name in self.constant_names if name is not None):
+            return self
+        kept = tuple(None if name in names else name for name in self.constant_names)
+        return EdgeProgram(self.ops, self.lhs, self.rhs, self.constants, self.operands, kept)
+
+    def rebound(self, params) -> "EdgeProgram":
+        """The program with its parameter-fed constants taken from ``params`` (the current call)."""
+        if not any(name is not None for name in self.constant_names):
+            return self
+        constants = tuple(float(params[name]) if name is not None else value
+                          for name, value in zip(self.constant_names, self.constants))
+        return EdgeProgram(self.ops, self.lhs, self.rhs, constants, self.operands, self.constant_names)
 
 
 def compile_expression(expr) -> EdgeProgram | None:
@@ -84,7 +108,10 @@ def compile_expression(expr) -> EdgeProgram | None:
 def compile_expressions(roots) -> tuple[EdgeProgram, tuple[int, ...]] | None:
     """One register program for several staged expressions (the messages ``self.reducer(m0, m1, ...)``
     binds) and, per expression, the instruction that holds its value."""
+    from .capture import NamedScalar
+
     ops, lhs, rhs, constants, operands = [], [], [], [], []
+    constant_keys: list = []          # ("scalar", name) for a parameter-fed constant, else the literal's value
     memo: dict[int, int] = {}
 
     def emit(op, a=0, b=0):
@@ -109,10 +136,11 @@ def compile_expressions(roots) -> tuple[EdgeProgram, tuple[int, ...]] | None:
             value = node.args[0]
             if isinstance(value, bool) or not isinstance(value, (int, float)):
                 return None
-            value = float(value)
-            if value not in constants:
-                constants.append(value)
-            result = emit(OP_CONST, constants.index(value))
+            key = ("scalar", value.name) if isinstance(value, NamedScalar) else float(value)
+            if key not in constant_keys:
+                constant_keys.append(key)
+                constants.append(float.__float__(value) if isinstance(value, NamedScalar) else float(value))
+            result = emit(OP_CONST, constant_keys.index(key))
         elif node.op in _BINARY:
             a, b = visit(node.args[0]), visit(node.args[1])
             if a is None or b is None:
@@ -138,7 +166,8 @@ def compile_expressions(roots) -> tuple[EdgeProgram, tuple[int, ...]] | None:
         return None
     if not operands:
         return None
-    return EdgeProgram(tuple(ops), tuple(lhs), tuple(rhs), tuple(constants), tuple(operands)), tuple(slots)
+    names = tuple(key[1] if isinstance(key, tuple) else None for key in constant_keys)
+    return EdgeProgram(tuple(ops), tuple(lhs), tuple(rhs), tuple(constants), tuple(operands), names), tuple(slots)
 
 
 def _entity_shape(operand: Operand, tensor: torch.Tensor) -> tuple[int, ...]:

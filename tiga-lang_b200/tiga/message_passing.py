@@ -141,7 +141,7 @@ class _GuardedLaunch:
     (``_GuardedExecutable`` and the installed fast path,
     python/tiga/interop/torch/message_passing.py:974-1007, 3680-3797)."""
 
-    __slots__ = ("graph", "reducer", "bindings", "specs", "constants", "runner", "variant", "signature")
+    __slots__ = ("graph", "reducer", "bindings", "specs", "constants", "scalars", "runner", "variant", "signature")
 
     def __init__(self, graph, reducer, bindings, tensors, constants, runner, variant):
         self.graph = graph
@@ -153,7 +153,10 @@ class _GuardedLaunch:
         self.reducer = reducer
         self.bindings = tuple(bindings)            # (role, name) per tensor the runner takes
         self.specs = tuple(_tensor_spec(t) for t in tensors)
-        self.constants = dict(constants)           # non-tensor params the staged program absorbed
+        # float params the compiled program reads at every call (the runner takes their current values)
+        self.scalars = tuple(getattr(runner, "scalars", ()))
+        # the other non-tensor params: absorbed into the staged program, so they must compare equal
+        self.constants = {name: value for name, value in constants.items() if name not in self.scalars}
         self.runner = runner
         self.variant = variant
 
@@ -174,14 +177,19 @@ class _GuardedLaunch:
             for name, value in self.constants.items():
                 if params[name] != value:
                     return _MISS
+            for name in self.scalars:
+                if type(params[name]) not in (float, int):
+                    return _MISS
         except (KeyError, TypeError, AttributeError):
             return _MISS
         # only the parameters edge() takes are part of the staged program; node() may take others
-        if kernel._edge_parameter_count(params) != len(self.constants) + sum(
+        if kernel._edge_parameter_count(params) != len(self.constants) + len(self.scalars) + sum(
                 1 for role, _ in self.bindings if role == "param"):
             return _MISS
         if graph is not self.graph:
             self.runner.cell.graph = self.graph = graph
+        if self.scalars:
+            return self.runner(*tensors, scalars={name: params[name] for name in self.scalars})
         return self.runner(*tensors)
 
 
@@ -338,7 +346,9 @@ class MessagePassing(Kernel):
     def _specialise(self, graph, src, dst, edge, params):
         """Stage ``edge()``, recognise the program and return
         (bindings, tensors, constants, runner): `runner(*tensors)` launches the native kernels."""
-        staged = cap.capture_edge(self.edge, params)
+        consumed: set = set()           # float params whose value Python itself used while edge() was staged
+        staged = cap.capture_edge(self.edge, params, consumed)
+        self._baked_scalars = frozenset(consumed)
         if staged is None:
             raise NotImplementedError(
                 f"edge() of {type(self).__name__} leaves the staging vocabulary "
@@ -466,6 +476,7 @@ class MessagePassing(Kernel):
         program = ep.compile_expression(staged)
         if program is None:
             return None
+        program = program.literalised(self._baked_scalars)
         implicit = _implicit_edge_names(graph)
         _refuse_shadowing(implicit, edge)
         row_ptr, col_idx = graph.resolve_csr()
@@ -485,7 +496,7 @@ class MessagePassing(Kernel):
         reducer_id = {"sum": ep.REDUCE_SUM, "mean": ep.REDUCE_MEAN, "max": ep.REDUCE_MAX, "prod": ep.REDUCE_PROD}[kind]
         identity = float(self.reducer.identity()) if kind in ("sum", "max", "prod") else 0.0
 
-        def runner(*bound):
+        def runner(*bound, scalars=None):
             current = cell.graph
             provided = None
             operands = []
@@ -496,9 +507,11 @@ class MessagePassing(Kernel):
                     operands.append(provided[slot])
                 else:
                     operands.append(bound[slot])
-            return ep.EdgeProgramFunction.apply(current, program, reducer_id, identity, *operands)
+            bound_program = program if scalars is None else program.rebound(scalars)
+            return ep.EdgeProgramFunction.apply(current, bound_program, reducer_id, identity, *operands)
 
         runner.cell = cell
+        runner.scalars = program.scalar_names()
         probe_shapes = tuple(tuple(t.shape[1:]) if role != "param" else tuple(t.shape)
                              for (role, _), t in zip(bindings, tensors))
         self._record(
@@ -528,6 +541,7 @@ class MessagePassing(Kernel):
         if rules is None or compiled is None:
             return None
         program, message_slots = compiled
+        program = program.literalised(self._baked_scalars)
         implicit = _implicit_edge_names(graph)
         _refuse_shadowing(implicit, edge)
         row_ptr, col_idx = graph.resolve_csr()
@@ -545,7 +559,7 @@ class MessagePassing(Kernel):
             tensors.append(spaces[operand.role][operand.name])
         cell = SimpleNamespace(graph=graph)
 
-        def runner(*bound):
+        def runner(*bound, scalars=None):
             current = cell.graph
             provided = None
             operands = []
@@ -556,13 +570,15 @@ class MessagePassing(Kernel):
                     operands.append(provided[slot])
                 else:
                     operands.append(bound[slot])
+            bound_program = program if scalars is None else program.rebound(scalars)
             if scalars_broadcast:
                 rank = max(t.ndim - 1 for o, t in zip(program.operands, operands) if o.role != "param")
                 operands = [t.reshape(t.shape[0], *((1,) * rank)) if o.role != "param" and t.ndim == 1 and rank else t
                             for o, t in zip(program.operands, operands)]
-            return alg.EdgeAlgebraFunction.apply(current, program, message_slots, rules, *operands)
+            return alg.EdgeAlgebraFunction.apply(current, bound_program, message_slots, rules, *operands)
 
         runner.cell = cell
+        runner.scalars = program.scalar_names()
         probe_shapes = tuple(tuple(t.shape[1:]) if role != "param" else tuple(t.shape)
                              for (role, _), t in zip(bindings, tensors))
         self._record(
