@@ -355,7 +355,17 @@ def generic_program(args, device, bench):
             "forward_ms": round(fwd_ms, 4), "value": round(E / (ms * 1e-3) / 1e9, 4), "unit": bench.UNIT,
             "lowering": kernel.last_variant.lowering,
             "forward_algorithmic_frac": round(alg_fwd / (fwd_ms * 1e-3) / 1e9 / peak, 4), "peak_kind": f"of {kind}",
-            "note": "interpreted register program (no dedicated kernel): the correctness path", "clocks": clocks}
+            "note": ("edge expression compiled at run time into straight-line CUDA kernels (NVRTC, sm_100a)"
+                     if _edge_jit_active() else "register program run by the interpreting kernels"),
+            "clocks": clocks}
+
+
+def _edge_jit_active() -> bool:
+    from tiga import edge_jit
+
+    if not edge_jit.enabled():
+        return False
+    return any(module is not None for module in edge_jit._modules.values())
 
 
 def _binary_grid_snapshots(n, device, seed):

@@ -712,6 +712,70 @@ TGB_API int32_t tgb_edge_algebra_bwd_sources(const tgb_csr_plan *plan,
                                              const void *message_grads,
                                              void *const *grads, uint64_t stream);
 
+/* ---------------------------------------------------------------------------
+ * Runtime-compiled edge programs.  CUDA source generated for one staged edge
+ * expression (straight-line code in place of the interpreter loop of the
+ * tgb_edge_program kernels) is compiled for sm_100a by NVRTC and launched
+ * through the driver's module interface: the role of the reference's provider
+ * pipeline, which turns a captured UDF into generated kernel code compiled at
+ * run time and cached per specialisation (python/tiga/codegen/ttir.py:103-121
+ * of walkerchi/TIGA-lang; its compiler is Triton).
+ *   tgb_jit_build    compiles `source`; needs NVRTC (opened with dlopen) but no
+ *                    GPU.  The compiler's log is copied to `log` (may be null).
+ *   tgb_jit_launch   loads the module on the current device on first use and
+ *                    launches `kernel` (an extern "C" __global__ taking ONE
+ *                    by-value argument block, pointed to by `arguments`) with
+ *                    `grid` blocks of `block` threads on `stream`.
+ * ------------------------------------------------------------------------ */
+typedef struct tgb_jit_module tgb_jit_module;
+TGB_API int32_t tgb_jit_build(const char *source, tgb_jit_module **module,
+                              char *log, int64_t log_capacity);
+TGB_API int32_t tgb_jit_image_bytes(const tgb_jit_module *module, int64_t *bytes);
+TGB_API int32_t tgb_jit_launch(tgb_jit_module *module, const char *kernel,
+                               uint32_t grid, uint32_t block,
+                               const void *arguments, uint64_t stream);
+TGB_API void tgb_jit_destroy(tgb_jit_module *module);
+
+/* The argument block of the generated edge-program kernels (`fwd`, `fwd_long`,
+ * `bwd_rows`, `bwd_rows_long`, `bwd_sources`, `bwd_sources_long`); the
+ * generated source declares the same structure.  The library fills it from the
+ * plan and the call. */
+typedef struct tgb_jit_edge_args {
+  const float *in[TGB_EP_MAX_OPERANDS];
+  float *sink[TGB_EP_MAX_OPERANDS];
+  const void *ptr;          /* row pointers of the traversal */
+  const void *idx;          /* neighbour per entry */
+  const uint32_t *eid;      /* edge id per entry, or null: entry = edge */
+  const int32_t *order;     /* plan row order: the long rows first */
+  const void *degree_ptr;   /* forward row pointers (MEAN divides by the degree) */
+  const float *dy;
+  float *out;
+  float *saved_value;
+  int32_t *saved_index;
+  int64_t n_rows;
+  int64_t n_long;
+  int64_t split_threshold;
+  int32_t ptr_bits, idx_bits, degree_bits;
+  float identity;
+  float constants[TGB_EP_MAX_CONSTANTS];
+} tgb_jit_edge_args;
+
+/* tgb_edge_program_fwd / _bwd_rows / _bwd_sources with the kernels of a module
+ * generated for this program (same reducer, width, operand roles and moduli;
+ * the constants are read from `program` at every call).  source_major = 0:
+ * the destination-major pass, 1: the source-major pass. */
+TGB_API int32_t tgb_edge_program_jit_fwd(const tgb_csr_plan *plan, tgb_jit_module *module,
+                                         const tgb_edge_program *program,
+                                         const void *const *operands, int32_t reducer,
+                                         float identity, void *out, void *saved_value,
+                                         void *saved_index, uint64_t stream);
+TGB_API int32_t tgb_edge_program_jit_bwd(const tgb_csr_plan *plan, tgb_jit_module *module,
+                                         const tgb_edge_program *program,
+                                         const void *const *operands, int32_t reducer,
+                                         const void *dy, void *const *grads,
+                                         const void *saved_value, const void *saved_index,
+                                         int32_t source_major, uint64_t stream);
+
 /* out[c] = sum over r of partial[r, c] (float32, rows added in a fixed order:
  * strips of rows by one thread each, then the strips in order). */
 TGB_API int32_t tgb_column_sum(const void *partial, int64_t rows, int64_t cols,

@@ -154,6 +154,23 @@ def test_capture_recognisers():
     assert program.rebound({"scale": 0.75}).constants == (0.75, 0.5, 0.25)
     assert program.rebound({"scale": 0.75}).key() == program.key()
 
+    # the same program as generated CUDA source, compiled for sm_100a by the runtime compiler (no GPU needed)
+    from tiga import edge_jit
+
+    source = edge_jit.generate_source(program, 4, (0, 0), ep.REDUCE_SUM)
+    assert "value[2] = __fsub_rn(value[0], value[1]);" in source and "a.constants[0]" in source
+    try:
+        module = edge_jit.Module(source)
+    except edge_jit.CompilerUnavailable:
+        module = None
+    if module is not None:
+        import ctypes
+
+        size = ctypes.c_int64()
+        assert _native.lib().tgb_jit_image_bytes(module.handle, ctypes.byref(size)) == 0 and size.value > 1000
+        with pytest.raises(RuntimeError, match="did not compile"):
+            edge_jit.Module("this is not CUDA")
+
     # anything else is staged into step / combine / finalize register programs
     from tiga import algebra as alg
 

@@ -13,6 +13,8 @@
 //   backward (sources) rows = sources over the plan's transposed relation: cotangents of src operands
 // The interpreter costs ~10 instructions per program instruction; programs the library has a
 // dedicated kernel for (weighted sums, attention) never come here.
+#include <cstring>
+
 #include "tgb_common.cuh"
 
 namespace tgb {
@@ -589,6 +591,107 @@ extern "C" int32_t tgb_edge_program_bwd_sources(const tgb_csr_plan *plan, const 
                                                 void *const *grads, const void *saved_value,
                                                 const void *saved_index, uint64_t stream) {
   return backward(true, plan, program, operands, reducer, dy, grads, saved_value, saved_index, stream);
+}
+
+// ---- the same three passes through a module generated for the program (tiga/edge_jit.py) ---------
+namespace {
+
+void fill_walk(tgb_jit_edge_args *a, const Walk &w) {
+  a->ptr = w.ptr;
+  a->idx = w.idx;
+  a->eid = w.eid;
+  a->order = w.order;
+  a->n_rows = w.n_rows;
+  a->n_long = w.n_long;
+  a->split_threshold = w.split_threshold;
+  a->ptr_bits = w.ptr_bits;
+  a->idx_bits = w.idx_bits;
+}
+
+void fill_program(tgb_jit_edge_args *a, const tgb_csr_plan *plan, const tgb_edge_program *program,
+                  const void *const *operands) {
+  memset(a, 0, sizeof(*a));
+  for (int k = 0; k < program->num_operands; ++k) a->in[k] = static_cast<const float *>(operands[k]);
+  for (int c = 0; c < TGB_EP_MAX_CONSTANTS; ++c) a->constants[c] = program->constants[c];
+  a->degree_ptr = plan->fwd.ptr;
+  a->degree_bits = plan->fwd.ptr_bits;
+}
+
+}  // namespace
+
+extern "C" int32_t tgb_edge_program_jit_fwd(const tgb_csr_plan *plan, tgb_jit_module *module,
+                                            const tgb_edge_program *program, const void *const *operands,
+                                            int32_t reducer, float identity, void *out, void *saved_value,
+                                            void *saved_index, uint64_t stream) {
+  const int32_t status = check_program(plan, program, operands);
+  if (status != TGB_STATUS_OK) return status;
+  if (!module) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null module");
+  if (reducer < TGB_REDUCER_SUM || reducer > TGB_REDUCER_PROD) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "unknown reducer");
+  if (plan->num_dst == 0) return TGB_STATUS_OK;
+  if (!out) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null output");
+  if (saved_index && plan->num_edges >= ((int64_t)1 << 31))
+    TGB_FAIL(TGB_STATUS_UNSUPPORTED, "the saved entry index is 32 bits wide");
+  tgb_jit_edge_args a;
+  fill_program(&a, plan, program, operands);
+  const Walk w = forward_walk(plan);
+  fill_walk(&a, w);
+  a.identity = identity;
+  a.out = static_cast<float *>(out);
+  a.saved_value = reducer == TGB_REDUCER_PROD ? static_cast<float *>(saved_value) : nullptr;
+  a.saved_index = reducer == TGB_REDUCER_PROD || reducer == TGB_REDUCER_MAX ? static_cast<int32_t *>(saved_index)
+                                                                            : nullptr;
+  const int lanes = lanes_for_width(program->width);
+  int32_t rc = tgb_jit_launch(module, "fwd", (uint32_t)ceil_div(plan->num_dst * lanes, kThreads), kThreads, &a, stream);
+  if (rc == TGB_STATUS_OK && w.n_long > 0)
+    rc = tgb_jit_launch(module, "fwd_long", (uint32_t)w.n_long, kLongThreads, &a, stream);
+  return rc;
+}
+
+extern "C" int32_t tgb_edge_program_jit_bwd(const tgb_csr_plan *plan, tgb_jit_module *module,
+                                            const tgb_edge_program *program, const void *const *operands,
+                                            int32_t reducer, const void *dy, void *const *grads,
+                                            const void *saved_value, const void *saved_index,
+                                            int32_t source_major, uint64_t stream) {
+  const int32_t status = check_program(plan, program, operands);
+  if (status != TGB_STATUS_OK) return status;
+  if (!module) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null module");
+  if (reducer < TGB_REDUCER_SUM || reducer > TGB_REDUCER_PROD) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "unknown reducer");
+  if ((reducer == TGB_REDUCER_MAX || reducer == TGB_REDUCER_PROD) && !saved_index)
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "this reducer's reverse mode needs what the forward saved (saved_index)");
+  if (reducer == TGB_REDUCER_PROD && !saved_value)
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "the product reducer's reverse mode needs saved_value");
+  if (!dy || !grads) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null cotangent");
+  if (source_major && !(plan->flags & TGB_PLAN_TRANSPOSE))
+    TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "the source-major pass needs a plan with the transposed relation");
+  tgb_jit_edge_args a;
+  fill_program(&a, plan, program, operands);
+  bool any = false;
+  for (int k = 0; k < program->num_operands; ++k) {
+    if (!grads[k]) continue;
+    const int role = program->operand_role[k];
+    const bool mine = source_major ? role == TGB_EP_ROLE_SRC : role != TGB_EP_ROLE_SRC;
+    if (!mine) continue;
+    if (program->operand_modulus[k] > 1)
+      TGB_FAIL(TGB_STATUS_UNSUPPORTED, "operand %d broadcasts along trailing dimensions: no cotangent kernel", k);
+    a.sink[k] = static_cast<float *>(grads[k]);
+    any = true;
+  }
+  if (!any) return TGB_STATUS_OK;
+  Walk w = forward_walk(plan);
+  if (source_major) w = Walk{plan->bwd.ptr, plan->bwd.idx, plan->bwd.eid, plan->bwd.ptr_bits, plan->bwd.idx_bits,
+                             plan->num_src, plan->bwd.order, plan->bwd.n_long, kSplitThreshold};
+  if (w.n_rows == 0) return TGB_STATUS_OK;
+  fill_walk(&a, w);
+  a.dy = static_cast<const float *>(dy);
+  a.saved_value = const_cast<float *>(static_cast<const float *>(saved_value));
+  a.saved_index = const_cast<int32_t *>(static_cast<const int32_t *>(saved_index));
+  const int lanes = lanes_for_width(program->width);
+  const uint32_t blocks = (uint32_t)ceil_div(w.n_rows * lanes, kThreads);
+  int32_t rc = tgb_jit_launch(module, source_major ? "bwd_sources" : "bwd_rows", blocks, kThreads, &a, stream);
+  if (rc == TGB_STATUS_OK && w.n_long > 0)
+    rc = tgb_jit_launch(module, source_major ? "bwd_sources_long" : "bwd_rows_long", (uint32_t)w.n_long, kLongThreads,
+                        &a, stream);
+  return rc;
 }
 
 extern "C" int32_t tgb_column_sum(const void *partial, int64_t rows, int64_t cols, void *out, uint64_t stream) {

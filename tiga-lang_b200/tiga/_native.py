@@ -85,6 +85,12 @@ _SIGNATURES = {
     "tgb_edge_algebra_bwd_rows": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u64]),
     "tgb_edge_algebra_bwd_sources": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u64]),
     "tgb_column_sum": (_i32, [_vp, _i64, _i64, _vp, _u64]),
+    "tgb_jit_build": (_i32, [ctypes.c_char_p, ctypes.POINTER(_vp), ctypes.c_char_p, _i64]),
+    "tgb_jit_image_bytes": (_i32, [_vp, ctypes.POINTER(_i64)]),
+    "tgb_jit_launch": (_i32, [_vp, ctypes.c_char_p, ctypes.c_uint32, ctypes.c_uint32, _vp, _u64]),
+    "tgb_jit_destroy": (None, [_vp]),
+    "tgb_edge_program_jit_fwd": (_i32, [_vp, _vp, _vp, _vp, _i32, _f32, _vp, _vp, _vp, _u64]),
+    "tgb_edge_program_jit_bwd": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _u64]),
 }
 
 

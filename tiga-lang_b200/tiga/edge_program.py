@@ -272,13 +272,26 @@ class EdgeProgramFunction(torch.autograd.Function):
             saved_index = torch.empty((graph.num_dst, width), dtype=torch.int32, device=device)
         if wants_grad and reducer == REDUCE_PROD:
             saved_value = torch.empty((graph.num_dst, width), dtype=torch.float32, device=device)
+        # kernels generated and compiled for this program when the runtime compiler is there,
+        # the interpreting kernels otherwise (same arithmetic, same order of every sum)
+        from . import edge_jit
+
+        module = edge_jit.module_for(program, width, moduli, reducer) if edge_jit.enabled() else None
         with torch.cuda.device(device):
-            _native.check(lib.tgb_edge_program_fwd(plan.handle, ctypes.byref(struct), _pointers(rows), int(reducer),
-                                                   float(identity), out.data_ptr(),
-                                                   None if saved_value is None else saved_value.data_ptr(),
-                                                   None if saved_index is None else saved_index.data_ptr(),
-                                                   _stream(device)),
-                          "tgb_edge_program_fwd")
+            if module is not None:
+                _native.check(lib.tgb_edge_program_jit_fwd(
+                    plan.handle, module.handle, ctypes.byref(struct), _pointers(rows), int(reducer), float(identity),
+                    out.data_ptr(), None if saved_value is None else saved_value.data_ptr(),
+                    None if saved_index is None else saved_index.data_ptr(), _stream(device)),
+                    "tgb_edge_program_jit_fwd")
+            else:
+                _native.check(lib.tgb_edge_program_fwd(plan.handle, ctypes.byref(struct), _pointers(rows), int(reducer),
+                                                       float(identity), out.data_ptr(),
+                                                       None if saved_value is None else saved_value.data_ptr(),
+                                                       None if saved_index is None else saved_index.data_ptr(),
+                                                       _stream(device)),
+                              "tgb_edge_program_fwd")
+        ctx.module = module
         ctx.graph, ctx.program, ctx.reducer, ctx.struct = graph, program, reducer, struct
         ctx.moduli, ctx.width = moduli, width
         ctx.count = len(rows)
@@ -316,18 +329,29 @@ class EdgeProgramFunction(torch.autograd.Function):
                 else:
                     any_dst_major = True
         with torch.cuda.device(device):
+            module = ctx.module
             if any_dst_major:
                 plan = graph.native_plan(transpose=False)
-                _native.check(lib.tgb_edge_program_bwd_rows(plan.handle, ctypes.byref(struct), _pointers(rows),
-                                                            ctx.reducer, dy.data_ptr(), wanted, saved_value,
-                                                            saved_index, _stream(device)),
-                              "tgb_edge_program_bwd_rows")
+                if module is not None:
+                    _native.check(lib.tgb_edge_program_jit_bwd(
+                        plan.handle, module.handle, ctypes.byref(struct), _pointers(rows), ctx.reducer, dy.data_ptr(),
+                        wanted, saved_value, saved_index, 0, _stream(device)), "tgb_edge_program_jit_bwd")
+                else:
+                    _native.check(lib.tgb_edge_program_bwd_rows(plan.handle, ctypes.byref(struct), _pointers(rows),
+                                                                ctx.reducer, dy.data_ptr(), wanted, saved_value,
+                                                                saved_index, _stream(device)),
+                                  "tgb_edge_program_bwd_rows")
             if any_src_major:
                 plan = graph.native_plan(transpose=True)
-                _native.check(lib.tgb_edge_program_bwd_sources(plan.handle, ctypes.byref(struct), _pointers(rows),
-                                                               ctx.reducer, dy.data_ptr(), wanted, saved_value,
-                                                               saved_index, _stream(device)),
-                              "tgb_edge_program_bwd_sources")
+                if module is not None:
+                    _native.check(lib.tgb_edge_program_jit_bwd(
+                        plan.handle, module.handle, ctypes.byref(struct), _pointers(rows), ctx.reducer, dy.data_ptr(),
+                        wanted, saved_value, saved_index, 1, _stream(device)), "tgb_edge_program_jit_bwd")
+                else:
+                    _native.check(lib.tgb_edge_program_bwd_sources(plan.handle, ctypes.byref(struct), _pointers(rows),
+                                                                   ctx.reducer, dy.data_ptr(), wanted, saved_value,
+                                                                   saved_index, _stream(device)),
+                                  "tgb_edge_program_bwd_sources")
             for i, partial in param_partials.items():
                 total = torch.empty(partial.shape[1], dtype=torch.float32, device=device)
                 _native.check(lib.tgb_column_sum(partial.data_ptr(), partial.shape[0], partial.shape[1],
