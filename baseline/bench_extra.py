@@ -15,8 +15,10 @@ events on the launching stream and its own clock record):
                     so the no-reuse algorithmic bytes are close to the real DRAM bytes
 
   generic_program   R-MAT 2^20 nodes (config 2's graph), F = 16: `edge.weight * (src.u - dst.u)`, an edge
-                    expression no dedicated kernel covers, through the interpreting kernels, fwd + grads
-                    of both node fields and the edge weights
+                    expression no dedicated kernel covers, compiled at run time into straight-line CUDA
+                    kernels, fwd + grads of both node fields and the edge weights
+  user_algebra      the same graph, F = 16: a user-written reducer with a tuple state (stable weighted mean,
+                    two messages per edge) that no dedicated kernel folds, fwd + grads of both fields
   dynamic_radius    131 072 points in the unit cube on a binary coordinate grid, scalar features,
                     cutoff between two squared-distance levels (about 16 neighbours): every step copies
                     one of two coordinate snapshots into the live position tensor, searches the
@@ -368,6 +370,70 @@ def _edge_jit_active() -> bool:
     return any(module is not None for module in edge_jit._modules.values())
 
 
+def user_algebra(args, device, bench):
+    """A reducer no dedicated kernel folds: the user-written stable weighted mean of the reference's
+    tests (tuple state (maximum, denominator, numerator), two messages per edge) on config 2's graph."""
+    import tiga as tg
+    from baseline import synthetic as syn
+
+    scale, edge_factor, F = 20, 32, 16
+    row_ptr, col = syn.rmat_csr(scale, edge_factor, seed=args.seed, symmetrize=True, device=device)
+    N, E = row_ptr.numel() - 1, col.numel()
+    gen = torch.Generator(device=device).manual_seed(args.seed + 5)
+    score = torch.randn(N, 1, generator=gen, device=device).requires_grad_()
+    value = torch.randn(N, F, generator=gen, device=device).requires_grad_()
+    graph = tg.Graph.from_csr(row_ptr, col, num_src=N)
+    graph.native_plan(transpose=True)
+
+    class StableWeightedMean(tg.Reducer):
+        name = "user_stable_weighted_mean"
+        associative = commutative = True
+
+        def identity(self):
+            return -1.0e30, 0.0, 0.0
+
+        def lift(self, s, v):
+            return s, 1.0, v
+
+        def combine(self, left, right):
+            top = left[0].maximum(right[0])
+            keep_left, keep_right = (left[0] - top).exp(), (right[0] - top).exp()
+            return top, keep_left * left[1] + keep_right * right[1], keep_left * left[2] + keep_right * right[2]
+
+        def finalize(self, state):
+            return state[2] / state[1]
+
+    class Attention(tg.MessagePassing):
+        reducer = StableWeightedMean()
+
+        def edge(self, src, dst, edge):
+            return self.reducer(src.score, src.value)
+
+    kernel = Attention()
+    ones = torch.ones((N, F), device=device)
+
+    def step():
+        out = kernel(graph=graph, src={"score": score, "value": value}, dst={})
+        return torch.autograd.grad(out, (score, value), ones)
+
+    def forward_only():
+        with torch.no_grad():
+            return kernel(graph=graph, src={"score": score, "value": value}, dst={})
+
+    steps = _steps(args)
+    ms, clocks = bench.timed(step, steps, args.warmup, device.index or 0)
+    fwd_ms, _ = bench.timed(forward_only, steps, args.warmup, device.index or 0)
+    alg_fwd = E * (8 + 4 + 4 * F) + N * (8 + 4 * F)
+    peak, kind = bench.hbm_peak()
+    return {"workload": f"user reducer (stable weighted mean, tuple state of 3, 2 messages), rmat scale={scale} "
+                        f"edge_factor={edge_factor} F={F} fp32, fwd + grads of score and value",
+            "num_nodes": N, "num_edges": E, "steps": steps, "ms_per_step": round(ms, 4),
+            "forward_ms": round(fwd_ms, 4), "value": round(E / (ms * 1e-3) / 1e9, 4), "unit": bench.UNIT,
+            "lowering": kernel.last_variant.lowering,
+            "forward_algorithmic_frac": round(alg_fwd / (fwd_ms * 1e-3) / 1e9 / peak, 4), "peak_kind": f"of {kind}",
+            "clocks": clocks}
+
+
 def _binary_grid_snapshots(n, device, seed):
     """Two coordinate snapshots on a 1/1024 grid of the unit cube: float32 squared distances between
     grid points are exact, so no pair sits within rounding distance of the cutoff."""
@@ -484,6 +550,7 @@ WORKLOADS = {"weighted-sum": ("c1_weighted_sum", weighted_sum_c1), "gcn-layer": 
              "gcn-layer-max": ("c2_gcn_layer_max", gcn_layer_max), "gat": ("c3_gat", gat),
              "attention": ("c4_attention", attention), "l2-hostile": ("l2_hostile_sum", l2_hostile),
              "generic-program": ("generic_program", generic_program),
+             "user-algebra": ("user_algebra", user_algebra),
              "dynamic-radius": ("dynamic_radius", dynamic_radius), "dynamic-knn": ("dynamic_knn", dynamic_knn)}
 
 

@@ -80,7 +80,7 @@ def parse_args():
     p.add_argument("--cpu-sample-seconds", type=float, default=12.0)
     p.add_argument("--workload", default="halo-gcn",
                    choices=("halo-gcn", "gcn-layer", "gcn-layer-max", "weighted-sum", "gat", "attention", "l2-hostile",
-                            "generic-program", "dynamic-radius", "dynamic-knn"),
+                            "generic-program", "user-algebra", "dynamic-radius", "dynamic-knn"),
                    help="halo-gcn = the headline; the others print one of the `extra` sub-results alone (one GPU)")
     p.add_argument("--kernel-table", action="store_true",
                    help="after the timed run, print a per-kernel device-time table of two more steps to stderr")

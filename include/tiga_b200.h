@@ -758,6 +758,11 @@ typedef struct tgb_jit_edge_args {
   int32_t ptr_bits, idx_bits, degree_bits;
   float identity;
   float constants[TGB_EP_MAX_CONSTANTS];
+  /* user algebras only */
+  const float *seeds;       /* message cotangents [messages, E, width] (reverse passes) */
+  float *prefix;            /* state before each edge [E, arity, width] */
+  float *message_grads;     /* [messages, E, width] */
+  int64_t num_edges;
 } tgb_jit_edge_args;
 
 /* tgb_edge_program_fwd / _bwd_rows / _bwd_sources with the kernels of a module
@@ -774,6 +779,27 @@ TGB_API int32_t tgb_edge_program_jit_bwd(const tgb_csr_plan *plan, tgb_jit_modul
                                          const void *const *operands, int32_t reducer,
                                          const void *dy, void *const *grads,
                                          const void *saved_value, const void *saved_index,
+                                         int32_t source_major, uint64_t stream);
+
+/* The user-algebra passes (tgb_edge_algebra_fwd / _bwd_messages / _bwd_rows /
+ * _bwd_sources) through a module generated for the program AND the algebra:
+ * kernels `alg_fwd`, `alg_fwd_long`, `alg_bwd_messages`,
+ * `alg_bwd_messages_long`, and the four reverse passes seeded per edge from
+ * message_grads.  The regions are part of the generated source, so only the
+ * message count and state size are read from `algebra`. */
+TGB_API int32_t tgb_edge_algebra_jit_fwd(const tgb_csr_plan *plan, tgb_jit_module *module,
+                                         const tgb_edge_program *program,
+                                         const void *const *operands, void *out,
+                                         uint64_t stream);
+TGB_API int32_t tgb_edge_algebra_jit_bwd_messages(const tgb_csr_plan *plan, tgb_jit_module *module,
+                                                  const tgb_edge_program *program,
+                                                  const void *const *operands, const void *dy,
+                                                  void *prefix, void *message_grads,
+                                                  uint64_t stream);
+TGB_API int32_t tgb_edge_algebra_jit_bwd(const tgb_csr_plan *plan, tgb_jit_module *module,
+                                         const tgb_edge_program *program,
+                                         const void *const *operands,
+                                         const void *message_grads, void *const *grads,
                                          int32_t source_major, uint64_t stream);
 
 /* out[c] = sum over r of partial[r, c] (float32, rows added in a fixed order:

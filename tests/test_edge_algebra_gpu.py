@@ -222,3 +222,42 @@ def test_a_reducer_that_is_not_associative_is_refused():
 
     with pytest.raises(NotImplementedError, match="associative"):
         Kernel()(graph=small_graph(), src={"x": torch.ones(3, device="cuda")}, dst={})
+
+
+@pytest.mark.parametrize("kernel_class", (WeightedComposition, StableAttention))
+def test_generated_algebra_kernels_equal_the_interpreting_kernels(kernel_class, monkeypatch):
+    """The fold and its reverse sweep as runtime-compiled straight-line CUDA against the interpreter:
+    same graph (a 1 500-edge row, rows without edges), forward bit for bit, cotangents to rounding."""
+    n = 400
+    gen = torch.Generator().manual_seed(17)
+    hub = torch.randint(0, n, (1500,), generator=gen)
+    fan = torch.randint(0, n, (n - 1, 2), generator=gen)
+    degree = torch.full((n,), 2)
+    degree[0] = 1500
+    degree[9] = 0
+    row_ptr = torch.cat((torch.zeros(1, dtype=torch.int64), degree.cumsum(0)))
+    col = torch.cat((hub, fan[:8].reshape(-1), fan[9:].reshape(-1)))
+    assert col.numel() == int(row_ptr[-1])
+    edges = col.numel()
+    graph = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=n)
+    if kernel_class is WeightedComposition:
+        fields = {"scale": 1.0 + 0.01 * torch.randn(n, 3, generator=gen), "bias": torch.randn(n, 3, generator=gen),
+                  "y": torch.randn(n, 3, generator=gen), "w": torch.rand(edges, 1, generator=gen),
+                  "gain": torch.randn(3, generator=gen)}
+    else:
+        fields = {"score": torch.randn(n, 1, generator=gen), "value": torch.randn(n, 3, generator=gen)}
+    dy = torch.randn(n, 3, generator=gen).cuda()
+    results = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("TGB_EDGE_JIT", mode)
+        leaves = {name: t.clone().cuda().requires_grad_() for name, t in fields.items()}
+        if kernel_class is WeightedComposition:
+            out = kernel_class()(graph=graph, src={"scale": leaves["scale"], "bias": leaves["bias"]},
+                                 dst={"y": leaves["y"]}, edge={"w": leaves["w"]}, gain=leaves["gain"])
+        else:
+            out = kernel_class()(graph=graph, src=leaves, dst={})
+        cotangent = torch.where(torch.isfinite(out.detach()), dy, torch.zeros_like(dy))
+        results[mode] = (out.detach(), torch.autograd.grad(out, list(leaves.values()), cotangent))
+    assert torch.equal(torch.nan_to_num(results["1"][0], nan=7.0), torch.nan_to_num(results["0"][0], nan=7.0))
+    for a, b in zip(results["1"][1], results["0"][1]):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6 * float(b.abs().max()), equal_nan=True)

@@ -647,6 +647,16 @@ extern "C" int32_t tgb_edge_program_jit_fwd(const tgb_csr_plan *plan, tgb_jit_mo
   return rc;
 }
 
+namespace {
+
+// The reverse pass of a generated module over one traversal; `seeds` != null: message cotangents
+// per edge (user algebras) instead of a reducer rule.
+int32_t jit_reverse(const tgb_csr_plan *plan, tgb_jit_module *module, const tgb_edge_program *program,
+                    const void *const *operands, const void *dy, const void *seeds, void *const *grads,
+                    const void *saved_value, const void *saved_index, int32_t source_major, uint64_t stream);
+
+}  // namespace
+
 extern "C" int32_t tgb_edge_program_jit_bwd(const tgb_csr_plan *plan, tgb_jit_module *module,
                                             const tgb_edge_program *program, const void *const *operands,
                                             int32_t reducer, const void *dy, void *const *grads,
@@ -654,17 +664,29 @@ extern "C" int32_t tgb_edge_program_jit_bwd(const tgb_csr_plan *plan, tgb_jit_mo
                                             int32_t source_major, uint64_t stream) {
   const int32_t status = check_program(plan, program, operands);
   if (status != TGB_STATUS_OK) return status;
-  if (!module) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null module");
   if (reducer < TGB_REDUCER_SUM || reducer > TGB_REDUCER_PROD) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "unknown reducer");
   if ((reducer == TGB_REDUCER_MAX || reducer == TGB_REDUCER_PROD) && !saved_index)
     TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "this reducer's reverse mode needs what the forward saved (saved_index)");
   if (reducer == TGB_REDUCER_PROD && !saved_value)
     TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "the product reducer's reverse mode needs saved_value");
-  if (!dy || !grads) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null cotangent");
+  if (!dy) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null cotangent");
+  return jit_reverse(plan, module, program, operands, dy, nullptr, grads, saved_value, saved_index, source_major,
+                     stream);
+}
+
+namespace {
+
+int32_t jit_reverse(const tgb_csr_plan *plan, tgb_jit_module *module, const tgb_edge_program *program,
+                    const void *const *operands, const void *dy, const void *seeds, void *const *grads,
+                    const void *saved_value, const void *saved_index, int32_t source_major, uint64_t stream) {
+  if (!module) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null module");
+  if (!grads) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null cotangent table");
   if (source_major && !(plan->flags & TGB_PLAN_TRANSPOSE))
     TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "the source-major pass needs a plan with the transposed relation");
   tgb_jit_edge_args a;
   fill_program(&a, plan, program, operands);
+  a.seeds = static_cast<const float *>(seeds);
+  a.num_edges = plan->num_edges;
   bool any = false;
   for (int k = 0; k < program->num_operands; ++k) {
     if (!grads[k]) continue;
@@ -692,6 +714,66 @@ extern "C" int32_t tgb_edge_program_jit_bwd(const tgb_csr_plan *plan, tgb_jit_mo
     rc = tgb_jit_launch(module, source_major ? "bwd_sources_long" : "bwd_rows_long", (uint32_t)w.n_long, kLongThreads,
                         &a, stream);
   return rc;
+}
+
+}  // namespace
+
+extern "C" int32_t tgb_edge_algebra_jit_fwd(const tgb_csr_plan *plan, tgb_jit_module *module,
+                                            const tgb_edge_program *program, const void *const *operands, void *out,
+                                            uint64_t stream) {
+  const int32_t status = check_program(plan, program, operands);
+  if (status != TGB_STATUS_OK) return status;
+  if (!module) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null module");
+  if (plan->num_dst == 0) return TGB_STATUS_OK;
+  if (!out) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null output");
+  tgb_jit_edge_args a;
+  fill_program(&a, plan, program, operands);
+  const Walk w = forward_walk(plan);
+  fill_walk(&a, w);
+  a.out = static_cast<float *>(out);
+  a.num_edges = plan->num_edges;
+  const int lanes = lanes_for_width(program->width);
+  int32_t rc = tgb_jit_launch(module, "alg_fwd", (uint32_t)ceil_div(plan->num_dst * lanes, kThreads), kThreads, &a,
+                              stream);
+  if (rc == TGB_STATUS_OK && w.n_long > 0)
+    rc = tgb_jit_launch(module, "alg_fwd_long", (uint32_t)w.n_long, kLongThreads, &a, stream);
+  return rc;
+}
+
+extern "C" int32_t tgb_edge_algebra_jit_bwd_messages(const tgb_csr_plan *plan, tgb_jit_module *module,
+                                                     const tgb_edge_program *program, const void *const *operands,
+                                                     const void *dy, void *prefix, void *message_grads,
+                                                     uint64_t stream) {
+  const int32_t status = check_program(plan, program, operands);
+  if (status != TGB_STATUS_OK) return status;
+  if (!module) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null module");
+  if (plan->num_dst == 0 || plan->num_edges == 0) return TGB_STATUS_OK;
+  if (!dy || !prefix || !message_grads) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null pointer");
+  tgb_jit_edge_args a;
+  fill_program(&a, plan, program, operands);
+  const Walk w = forward_walk(plan);
+  fill_walk(&a, w);
+  a.dy = static_cast<const float *>(dy);
+  a.prefix = static_cast<float *>(prefix);
+  a.message_grads = static_cast<float *>(message_grads);
+  a.num_edges = plan->num_edges;
+  const int lanes = lanes_for_width(program->width);
+  int32_t rc = tgb_jit_launch(module, "alg_bwd_messages", (uint32_t)ceil_div(plan->num_dst * lanes, kThreads), kThreads,
+                              &a, stream);
+  if (rc == TGB_STATUS_OK && w.n_long > 0)
+    rc = tgb_jit_launch(module, "alg_bwd_messages_long", (uint32_t)w.n_long, kLongThreads, &a, stream);
+  return rc;
+}
+
+extern "C" int32_t tgb_edge_algebra_jit_bwd(const tgb_csr_plan *plan, tgb_jit_module *module,
+                                            const tgb_edge_program *program, const void *const *operands,
+                                            const void *message_grads, void *const *grads, int32_t source_major,
+                                            uint64_t stream) {
+  const int32_t status = check_program(plan, program, operands);
+  if (status != TGB_STATUS_OK) return status;
+  if (!message_grads) TGB_FAIL(TGB_STATUS_INVALID_ARGUMENT, "null message cotangents");
+  return jit_reverse(plan, module, program, operands, message_grads, message_grads, grads, nullptr, nullptr,
+                     source_major, stream);
 }
 
 extern "C" int32_t tgb_column_sum(const void *partial, int64_t rows, int64_t cols, void *out, uint64_t stream) {

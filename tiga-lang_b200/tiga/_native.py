@@ -91,6 +91,9 @@ _SIGNATURES = {
     "tgb_jit_destroy": (None, [_vp]),
     "tgb_edge_program_jit_fwd": (_i32, [_vp, _vp, _vp, _vp, _i32, _f32, _vp, _vp, _vp, _u64]),
     "tgb_edge_program_jit_bwd": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _u64]),
+    "tgb_edge_algebra_jit_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _u64]),
+    "tgb_edge_algebra_jit_bwd_messages": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64]),
+    "tgb_edge_algebra_jit_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _u64]),
 }
 
 

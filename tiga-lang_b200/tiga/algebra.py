@@ -239,10 +239,20 @@ class EdgeAlgebraFunction(torch.autograd.Function):
         plan = graph.native_plan(transpose=False)
         device = rows[0].device
         out = torch.empty((graph.num_dst, width), dtype=torch.float32, device=device)
+        # kernels generated for this program and this algebra when the runtime compiler is there
+        from . import edge_jit
+
+        module = edge_jit.module_for(program, width, moduli, 0, algebra, slots) if edge_jit.enabled() else None
         with torch.cuda.device(device):
-            _native.check(lib.tgb_edge_algebra_fwd(plan.handle, ctypes.byref(struct), ctypes.byref(rules),
-                                                   ep._pointers(rows), out.data_ptr(), ep._stream(device)),
-                          "tgb_edge_algebra_fwd")
+            if module is not None:
+                _native.check(lib.tgb_edge_algebra_jit_fwd(plan.handle, module.handle, ctypes.byref(struct),
+                                                           ep._pointers(rows), out.data_ptr(), ep._stream(device)),
+                              "tgb_edge_algebra_jit_fwd")
+            else:
+                _native.check(lib.tgb_edge_algebra_fwd(plan.handle, ctypes.byref(struct), ctypes.byref(rules),
+                                                       ep._pointers(rows), out.data_ptr(), ep._stream(device)),
+                              "tgb_edge_algebra_fwd")
+        ctx.module = module
         ctx.graph, ctx.program, ctx.algebra, ctx.struct, ctx.rules = graph, program, algebra, struct, rules
         ctx.width, ctx.edges = width, int(plan.num_edges)
         ctx.save_for_backward(*rows)
@@ -282,22 +292,36 @@ class EdgeAlgebraFunction(torch.autograd.Function):
         # every message of every edge
         prefix = torch.empty((max(edges, 1), algebra.arity, width), dtype=torch.float32, device=device)
         message_grads = torch.zeros((algebra.num_messages, max(edges, 1), width), dtype=torch.float32, device=device)
+        module = ctx.module
         with torch.cuda.device(device):
             plan = graph.native_plan(transpose=False)
-            _native.check(lib.tgb_edge_algebra_bwd_messages(plan.handle, ctypes.byref(struct), ctypes.byref(rules),
-                                                            ep._pointers(rows), dy.data_ptr(), prefix.data_ptr(),
-                                                            message_grads.data_ptr(), ep._stream(device)),
-                          "tgb_edge_algebra_bwd_messages")
+            if module is not None:
+                _native.check(lib.tgb_edge_algebra_jit_bwd_messages(
+                    plan.handle, module.handle, ctypes.byref(struct), ep._pointers(rows), dy.data_ptr(),
+                    prefix.data_ptr(), message_grads.data_ptr(), ep._stream(device)), "tgb_edge_algebra_jit_bwd_messages")
+            else:
+                _native.check(lib.tgb_edge_algebra_bwd_messages(plan.handle, ctypes.byref(struct), ctypes.byref(rules),
+                                                                ep._pointers(rows), dy.data_ptr(), prefix.data_ptr(),
+                                                                message_grads.data_ptr(), ep._stream(device)),
+                              "tgb_edge_algebra_bwd_messages")
             del prefix
-            if any_dst_major:
-                _native.check(lib.tgb_edge_algebra_bwd_rows(plan.handle, ctypes.byref(struct), ctypes.byref(rules),
-                                                            ep._pointers(rows), message_grads.data_ptr(), wanted,
-                                                            ep._stream(device)), "tgb_edge_algebra_bwd_rows")
-            if any_src_major:
-                plan = graph.native_plan(transpose=True)
-                _native.check(lib.tgb_edge_algebra_bwd_sources(plan.handle, ctypes.byref(struct), ctypes.byref(rules),
-                                                               ep._pointers(rows), message_grads.data_ptr(), wanted,
-                                                               ep._stream(device)), "tgb_edge_algebra_bwd_sources")
+            for source_major, wanted_pass in ((0, any_dst_major), (1, any_src_major)):
+                if not wanted_pass:
+                    continue
+                if source_major:
+                    plan = graph.native_plan(transpose=True)
+                if module is not None:
+                    _native.check(lib.tgb_edge_algebra_jit_bwd(
+                        plan.handle, module.handle, ctypes.byref(struct), ep._pointers(rows), message_grads.data_ptr(),
+                        wanted, source_major, ep._stream(device)), "tgb_edge_algebra_jit_bwd")
+                elif source_major:
+                    _native.check(lib.tgb_edge_algebra_bwd_sources(
+                        plan.handle, ctypes.byref(struct), ctypes.byref(rules), ep._pointers(rows),
+                        message_grads.data_ptr(), wanted, ep._stream(device)), "tgb_edge_algebra_bwd_sources")
+                else:
+                    _native.check(lib.tgb_edge_algebra_bwd_rows(
+                        plan.handle, ctypes.byref(struct), ctypes.byref(rules), ep._pointers(rows),
+                        message_grads.data_ptr(), wanted, ep._stream(device)), "tgb_edge_algebra_bwd_rows")
             for i, partial in param_partials.items():
                 total = torch.empty(partial.shape[1], dtype=torch.float32, device=device)
                 _native.check(lib.tgb_column_sum(partial.data_ptr(), partial.shape[0], partial.shape[1],

@@ -48,12 +48,17 @@ struct Args {
   i32 ptr_bits, idx_bits, degree_bits;
   float identity;
   float constants[16];
+  const float *seeds;
+  float *prefix;
+  float *message_grads;
+  i64 num_edges;
 };
 
 #define REDUCER_SUM 0
 #define REDUCER_MEAN 1
 #define REDUCER_MAX 2
 #define REDUCER_PROD 3
+#define REDUCER_SEEDED 4
 #define ROLE_SRC 0
 #define ROLE_DST 1
 #define ROLE_EDGE 2
@@ -201,7 +206,13 @@ __device__ __forceinline__ void reverse_pass(const Args &a) {
       const i64 src = SOURCE_MAJOR ? row : other, dst = SOURCE_MAJOR ? other : row;
 #pragma unroll
       for (int i = 0; i < N_INSTR; ++i) adjoint[i] = 0.0f;
-      if (live) {
+      if (live && REDUCER == REDUCER_SEEDED) {         // message cotangents handed over per edge (user algebras)
+        evaluate(a, src, dst, edge, f, value);
+#pragma unroll
+        for (int j = 0; j < N_MESSAGES; ++j)
+          adjoint[kMessageSlot[j]] += __ldg(a.seeds + ((i64)j * a.num_edges + edge) * WIDTH + f);
+        sweep_back(value, adjoint);
+      } else if (live) {
         evaluate(a, src, dst, edge, f, value);
         float g = __ldg(a.dy + dst * WIDTH + f);
         if (REDUCER == REDUCER_MEAN) {
@@ -301,6 +312,204 @@ extern "C" __global__ void __launch_bounds__(THREADS) bwd_sources(const __grid_c
 extern "C" __global__ void __launch_bounds__(LONG_THREADS) bwd_sources_long(const __grid_constant__ Args a) { reverse_pass<true, true>(a); }
 """
 
+_ALGEBRA_KERNELS = r"""
+#define MAX_ARGS (ARITY + (ARITY > N_MESSAGES ? ARITY : N_MESSAGES))
+
+__device__ __forceinline__ void fold_edge(const float *value, float *state) {
+  float args[MAX_ARGS], rv[N_STEP];
+#pragma unroll
+  for (int k = 0; k < ARITY; ++k) args[k] = state[k];
+#pragma unroll
+  for (int j = 0; j < N_MESSAGES; ++j) args[ARITY + j] = value[kMessageSlot[j]];
+  step_eval(args, rv);
+  step_out(rv, state);
+}
+
+struct RowSpan { i64 row, begin, end, degree, slice; };
+
+template <bool LONG>
+__device__ __forceinline__ bool row_span(const Args &a, RowSpan &span) {
+  constexpr int kGroups = (LONG ? LONG_THREADS : THREADS) / LANES;
+  const int group = threadIdx.x / LANES;
+  if (LONG) {
+    span.row = __ldg(a.order + blockIdx.x);
+  } else {
+    span.row = (i64)blockIdx.x * kGroups + group;
+    if (span.row >= a.n_rows) return false;
+  }
+  span.begin = load_index(a.ptr, a.ptr_bits, span.row);
+  span.end = load_index(a.ptr, a.ptr_bits, span.row + 1);
+  span.degree = span.end - span.begin;
+  span.slice = 0;
+  if (!LONG && span.degree > a.split_threshold) return false;
+  if (LONG) {
+    span.slice = (span.degree + kGroups - 1) / kGroups;
+    span.begin = span.begin + group * span.slice;
+    span.end = span.begin + span.slice < span.end ? span.begin + span.slice : span.end;
+  }
+  return true;
+}
+
+template <bool LONG>
+__device__ __forceinline__ void algebra_forward(const Args &a) {
+  constexpr int kGroups = (LONG ? LONG_THREADS : THREADS) / LANES;
+  __shared__ float part[LONG ? ARITY * LONG_THREADS : 1];
+  const int lane = threadIdx.x % LANES, group = threadIdx.x / LANES;
+  RowSpan span;
+  if (!row_span<LONG>(a, span)) return;
+  float value[N_INSTR], state[ARITY];
+  for (int f0 = 0; f0 < WIDTH; f0 += LANES) {
+    const int f = f0 + lane;
+    const bool live = f < WIDTH;
+#pragma unroll
+    for (int k = 0; k < ARITY; ++k) state[k] = identity_of(k);
+    if (live) {
+      for (i64 e = span.begin; e < span.end; ++e) {
+        evaluate(a, load_index(a.idx, a.idx_bits, e), span.row, e, f, value);
+        fold_edge(value, state);
+      }
+    }
+    if (LONG) {
+#pragma unroll
+      for (int k = 0; k < ARITY; ++k) part[k * LONG_THREADS + threadIdx.x] = state[k];
+      __syncthreads();
+      if (group == 0 && live) {
+#pragma unroll
+        for (int k = 0; k < ARITY; ++k) state[k] = identity_of(k);
+        for (int g = 0; g < kGroups && (i64)g * span.slice < span.degree; ++g) {
+          float args[2 * ARITY], rv[N_COMBINE];
+#pragma unroll
+          for (int k = 0; k < ARITY; ++k) {
+            args[k] = state[k];
+            args[ARITY + k] = part[k * LONG_THREADS + g * LANES + lane];
+          }
+          combine_eval(args, rv);
+          combine_out(rv, state);
+        }
+      }
+      __syncthreads();
+      if (group != 0) continue;
+    }
+    if (live) {
+      float rv[N_FINAL], result[1];
+      finalize_eval(state, rv);
+      finalize_out(rv, result);
+      a.out[span.row * WIDTH + f] = result[0];
+    }
+  }
+}
+
+template <bool LONG>
+__device__ __forceinline__ void algebra_messages(const Args &a) {
+  constexpr int kGroups = (LONG ? LONG_THREADS : THREADS) / LANES;
+  __shared__ float part[LONG ? ARITY * LONG_THREADS : 1];
+  __shared__ float joined[LONG ? ARITY * LONG_THREADS : 1];
+  const int lane = threadIdx.x % LANES, group = threadIdx.x / LANES;
+  RowSpan span;
+  if (!row_span<LONG>(a, span)) return;
+  float value[N_INSTR], state[ARITY], carried[ARITY];
+  for (int f0 = 0; f0 < WIDTH; f0 += LANES) {
+    const int f = f0 + lane;
+    const bool live = f < WIDTH;
+#pragma unroll
+    for (int k = 0; k < ARITY; ++k) state[k] = identity_of(k);
+    if (live) {
+      for (i64 e = span.begin; e < span.end; ++e) {
+#pragma unroll
+        for (int k = 0; k < ARITY; ++k) a.prefix[(e * ARITY + k) * WIDTH + f] = state[k];
+        evaluate(a, load_index(a.idx, a.idx_bits, e), span.row, e, f, value);
+        fold_edge(value, state);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < ARITY; ++k) carried[k] = 0.0f;
+    if (!LONG) {
+      if (live) {
+        float rv[N_FINAL], radj[N_FINAL];
+        const float g = __ldg(a.dy + span.row * WIDTH + f);
+        finalize_eval(state, rv);
+        finalize_seed(radj, &g);
+        finalize_back(rv, radj);
+        finalize_args(radj, carried);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < ARITY; ++k) part[k * LONG_THREADS + threadIdx.x] = state[k];
+      __syncthreads();
+      if (group == 0 && live) {
+        int used = 0;
+#pragma unroll
+        for (int k = 0; k < ARITY; ++k) state[k] = identity_of(k);
+        for (int g = 0; g < kGroups && (i64)g * span.slice < span.degree; ++g, ++used) {
+          float args[2 * ARITY], rv[N_COMBINE];
+#pragma unroll
+          for (int k = 0; k < ARITY; ++k) {
+            joined[k * LONG_THREADS + g * LANES + lane] = state[k];
+            args[k] = state[k];
+            args[ARITY + k] = part[k * LONG_THREADS + g * LANES + lane];
+          }
+          combine_eval(args, rv);
+          combine_out(rv, state);
+        }
+        {
+          float rv[N_FINAL], radj[N_FINAL];
+          const float g_row = __ldg(a.dy + span.row * WIDTH + f);
+          finalize_eval(state, rv);
+          finalize_seed(radj, &g_row);
+          finalize_back(rv, radj);
+          finalize_args(radj, carried);
+        }
+        for (int g = used - 1; g >= 0; --g) {
+          float args[2 * ARITY], rv[N_COMBINE], radj[N_COMBINE], arg_adjoint[2 * ARITY];
+#pragma unroll
+          for (int k = 0; k < ARITY; ++k) {
+            args[k] = joined[k * LONG_THREADS + g * LANES + lane];
+            args[ARITY + k] = part[k * LONG_THREADS + g * LANES + lane];
+          }
+          combine_eval(args, rv);
+          combine_seed(radj, carried);
+          combine_back(rv, radj);
+          combine_args(radj, arg_adjoint);
+#pragma unroll
+          for (int k = 0; k < ARITY; ++k) {
+            carried[k] = arg_adjoint[k];
+            part[k * LONG_THREADS + g * LANES + lane] = arg_adjoint[ARITY + k];
+          }
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < ARITY; ++k) carried[k] = part[k * LONG_THREADS + threadIdx.x];
+    }
+    if (live) {
+      for (i64 e = span.end - 1; e >= span.begin; --e) {
+        float args[MAX_ARGS], rv[N_STEP], radj[N_STEP], arg_adjoint[MAX_ARGS];
+        evaluate(a, load_index(a.idx, a.idx_bits, e), span.row, e, f, value);
+#pragma unroll
+        for (int k = 0; k < ARITY; ++k) args[k] = a.prefix[(e * ARITY + k) * WIDTH + f];
+#pragma unroll
+        for (int j = 0; j < N_MESSAGES; ++j) args[ARITY + j] = value[kMessageSlot[j]];
+        step_eval(args, rv);
+        step_seed(radj, carried);
+        step_back(rv, radj);
+        step_args(radj, arg_adjoint);
+#pragma unroll
+        for (int k = 0; k < ARITY; ++k) carried[k] = arg_adjoint[k];
+#pragma unroll
+        for (int j = 0; j < N_MESSAGES; ++j)
+          a.message_grads[((i64)j * a.num_edges + e) * WIDTH + f] = arg_adjoint[ARITY + j];
+      }
+    }
+    if (LONG) __syncthreads();
+  }
+}
+
+extern "C" __global__ void __launch_bounds__(THREADS) alg_fwd(const __grid_constant__ Args a) { algebra_forward<false>(a); }
+extern "C" __global__ void __launch_bounds__(LONG_THREADS) alg_fwd_long(const __grid_constant__ Args a) { algebra_forward<true>(a); }
+extern "C" __global__ void __launch_bounds__(THREADS) alg_bwd_messages(const __grid_constant__ Args a) { algebra_messages<false>(a); }
+extern "C" __global__ void __launch_bounds__(LONG_THREADS) alg_bwd_messages_long(const __grid_constant__ Args a) { algebra_messages<true>(a); }
+"""
+
 _BINARY = {ep.OP_ADD: "__fadd_rn({a}, {b})", ep.OP_SUB: "__fsub_rn({a}, {b})", ep.OP_MUL: "__fmul_rn({a}, {b})",
            ep.OP_DIV: "__fdiv_rn({a}, {b})", ep.OP_MAX: "maximum_nan({a}, {b})"}
 
@@ -312,63 +521,126 @@ def _lanes(width: int) -> int:
     return lanes
 
 
-def generate_source(program: ep.EdgeProgram, width: int, moduli, reducer: int) -> str:
-    """The CUDA source of the six kernels specialised for this program."""
+def _float_bits(value: float) -> str:
+    """The exact float32 as a CUDA expression."""
+    import struct
+
+    return f"__int_as_float(0x{struct.unpack('<I', struct.pack('<f', float(value)))[0]:08x})"
+
+
+def _forward_lines(ops, lhs, rhs, load, constant, target):
+    """One statement per instruction: ``target[i] = ...``."""
+    lines = []
+    for i, (op, a, b) in enumerate(zip(ops, lhs, rhs)):
+        if op == ep.OP_LOAD:
+            lines.append(f"  {target}[{i}] = {load(a)};")
+        elif op == ep.OP_CONST:
+            lines.append(f"  {target}[{i}] = {constant(a)};")
+        elif op in _BINARY:
+            lines.append(f"  {target}[{i}] = " + _BINARY[op].format(a=f"{target}[{a}]", b=f"{target}[{b}]") + ";")
+        elif op == ep.OP_EXP:
+            lines.append(f"  {target}[{i}] = expf({target}[{a}]);")
+        else:
+            lines.append(f"  {target}[{i}] = -{target}[{a}];")
+    return lines
+
+
+def _reverse_lines(ops, lhs, rhs, value, adjoint):
+    """The reverse sweep, last instruction first: pushes ``adjoint[i]`` down to the instruction's inputs."""
+    lines = []
+    for i in range(len(ops) - 1, -1, -1):
+        op, a, b = ops[i], lhs[i], rhs[i]
+        g = f"{adjoint}[{i}]"
+        if op == ep.OP_ADD:
+            lines.append(f"  {adjoint}[{a}] += {g}; {adjoint}[{b}] += {g};")
+        elif op == ep.OP_SUB:
+            lines.append(f"  {adjoint}[{a}] += {g}; {adjoint}[{b}] -= {g};")
+        elif op == ep.OP_MUL:
+            lines.append(f"  {{ const float gi = {g}; {adjoint}[{a}] += gi * {value}[{b}]; "
+                         f"{adjoint}[{b}] += gi * {value}[{a}]; }}")
+        elif op == ep.OP_DIV:
+            lines.append(f"  {{ const float q = {g} / {value}[{b}]; {adjoint}[{a}] += q; "
+                         f"{adjoint}[{b}] -= q * {value}[{i}]; }}")
+        elif op == ep.OP_MAX:
+            lines.append(f"  {{ const float gi = {g}, x = {value}[{a}], y = {value}[{b}]; "
+                         f"{adjoint}[{a}] += x > y ? gi : (x == y ? 0.5f * gi : 0.0f); "
+                         f"{adjoint}[{b}] += y > x ? gi : (x == y ? 0.5f * gi : 0.0f); }}")
+        elif op == ep.OP_EXP:
+            lines.append(f"  {adjoint}[{a}] += {g} * {value}[{i}];")
+        elif op == ep.OP_NEG:
+            lines.append(f"  {adjoint}[{a}] -= {g};")
+    return lines
+
+
+def _region_functions(name: str, region, n_args: int) -> str:
+    """eval / out / seed / back / args of one reducer region (tiga.algebra.Region)."""
+    n = len(region.ops)
+    forward = _forward_lines(region.ops, region.lhs, region.rhs, lambda a: f"args[{a}]",
+                             lambda c: _float_bits(region.constants[c]), "rv")
+    reverse = _reverse_lines(region.ops, region.lhs, region.rhs, "rv", "radj")
+    outs = [f"  out[{k}] = rv[{slot}];" for k, slot in enumerate(region.outs)]
+    seed = ["#pragma unroll", f"  for (int i = 0; i < {n}; ++i) radj[i] = 0.0f;"] + \
+           [f"  radj[{slot}] += out_adjoint[{k}];" for k, slot in enumerate(region.outs)]
+    gather = []
+    for argument in range(n_args):
+        loads = [i for i, (op, a) in enumerate(zip(region.ops, region.lhs)) if op == ep.OP_LOAD and a == argument]
+        gather.append(f"  arg_adjoint[{argument}] = " + (" + ".join(f"radj[{i}]" for i in loads) if loads else "0.0f") + ";")
+    return "\n".join([
+        f"__device__ __forceinline__ void {name}_eval(const float *args, float *rv) {{", *forward, "}",
+        f"__device__ __forceinline__ void {name}_out(const float *rv, float *out) {{", *outs, "}",
+        f"__device__ __forceinline__ void {name}_seed(float *radj, const float *out_adjoint) {{", *seed, "}",
+        f"__device__ __forceinline__ void {name}_back(const float *rv, float *radj) {{", *reverse, "}",
+        f"__device__ __forceinline__ void {name}_args(const float *radj, float *arg_adjoint) {{", *gather, "}"])
+
+
+def generate_source(program: ep.EdgeProgram, width: int, moduli, reducer: int, rules=None, message_slots=None) -> str:
+    """The CUDA source of the kernels specialised for this program: the six passes of a built-in
+    reducer, or -- with ``rules`` (a ``tiga.algebra.Algebra``) and the message slots -- the algebra fold,
+    its reverse sweep and the reverse passes seeded per edge."""
     n = len(program.ops)
     roles = [ep.ROLE_PARAM if o.role == "param" else ep._ROLES[o.role] for o in program.operands]
-    load_slot = {}
-    evaluate, sweep = [], []
-    for i, (op, a, b) in enumerate(zip(program.ops, program.lhs, program.rhs)):
-        if op == ep.OP_LOAD:
-            load_slot[a] = i
-            role, modulus = roles[a], int(moduli[a])
-            entity = {ep.ROLE_SRC: "src", ep.ROLE_DST: "dst", ep.ROLE_EDGE: "edge", ep.ROLE_PARAM: "0"}[role]
-            count = width if modulus == 0 else modulus
-            offset = "f" if modulus == 0 else ("0" if modulus == 1 else f"f % {modulus}")
-            evaluate.append(f"  value[{i}] = __ldg(a.in[{a}] + {entity} * {count} + {offset});")
-        elif op == ep.OP_CONST:
-            evaluate.append(f"  value[{i}] = a.constants[{a}];")
-        elif op in _BINARY:
-            evaluate.append(f"  value[{i}] = " + _BINARY[op].format(a=f"value[{a}]", b=f"value[{b}]") + ";")
-        elif op == ep.OP_EXP:
-            evaluate.append(f"  value[{i}] = expf(value[{a}]);")
-        else:
-            evaluate.append(f"  value[{i}] = -value[{a}];")
-    for i in range(n - 1, -1, -1):
-        op, a, b = program.ops[i], program.lhs[i], program.rhs[i]
-        g = f"adjoint[{i}]"
-        if op == ep.OP_ADD:
-            sweep.append(f"  adjoint[{a}] += {g}; adjoint[{b}] += {g};")
-        elif op == ep.OP_SUB:
-            sweep.append(f"  adjoint[{a}] += {g}; adjoint[{b}] -= {g};")
-        elif op == ep.OP_MUL:
-            sweep.append(f"  {{ const float gi = {g}; adjoint[{a}] += gi * value[{b}]; adjoint[{b}] += gi * value[{a}]; }}")
-        elif op == ep.OP_DIV:
-            sweep.append(f"  {{ const float q = {g} / value[{b}]; adjoint[{a}] += q; adjoint[{b}] -= q * value[{i}]; }}")
-        elif op == ep.OP_MAX:
-            sweep.append(f"  {{ const float gi = {g}, x = value[{a}], y = value[{b}]; "
-                         f"adjoint[{a}] += x > y ? gi : (x == y ? 0.5f * gi : 0.0f); "
-                         f"adjoint[{b}] += y > x ? gi : (x == y ? 0.5f * gi : 0.0f); }}")
-        elif op == ep.OP_EXP:
-            sweep.append(f"  adjoint[{a}] += {g} * value[{i}];")
-        elif op == ep.OP_NEG:
-            sweep.append(f"  adjoint[{a}] -= {g};")
+    load_slot = {a: i for i, (op, a) in enumerate(zip(program.ops, program.lhs)) if op == ep.OP_LOAD}
+
+    def load(a):
+        role, modulus = roles[a], int(moduli[a])
+        entity = {ep.ROLE_SRC: "src", ep.ROLE_DST: "dst", ep.ROLE_EDGE: "edge", ep.ROLE_PARAM: "0"}[role]
+        count = width if modulus == 0 else modulus
+        offset = "f" if modulus == 0 else ("0" if modulus == 1 else f"f % {modulus}")
+        return f"__ldg(a.in[{a}] + {entity} * {count} + {offset})"
+
+    evaluate = _forward_lines(program.ops, program.lhs, program.rhs, load, lambda c: f"a.constants[{c}]", "value")
+    sweep = _reverse_lines(program.ops, program.lhs, program.rhs, "value", "adjoint")
     count = len(program.operands)
+    slots = tuple(message_slots) if message_slots is not None else (n - 1,)
     table = lambda values: ", ".join(str(int(v)) for v in values)      # noqa: E731
-    defines = "\n".join([
+    defines = [
         f"#define WIDTH {int(width)}", f"#define LANES {_lanes(int(width))}", f"#define N_INSTR {n}",
-        f"#define N_OPERANDS {count}", f"#define REDUCER {int(reducer)}",
+        f"#define N_OPERANDS {count}", f"#define REDUCER {4 if rules is not None else int(reducer)}",
+        f"#define N_MESSAGES {len(slots)}",
         f"__device__ constexpr int kRole[N_OPERANDS] = {{{table(roles)}}};",
         f"__device__ constexpr int kModulus[N_OPERANDS] = {{{table(moduli)}}};",
         f"__device__ constexpr int kLoadSlot[N_OPERANDS] = {{{table(load_slot[k] for k in range(count))}}};",
+        f"__device__ constexpr int kMessageSlot[N_MESSAGES] = {{{table(slots)}}};",
         "#define constexpr_role_modulus(k) const int role = kRole[k], modulus = kModulus[k], load_slot = kLoadSlot[k]; "
         "(void)role; (void)modulus; (void)load_slot",
-    ])
-    functions = "\n".join([
+    ]
+    functions = [
         "__device__ __forceinline__ void evaluate(const Args &a, i64 src, i64 dst, i64 edge, int f, float *value) {",
         *evaluate, "}",
-        "__device__ __forceinline__ void sweep_back(const float *value, float *adjoint) {", *sweep, "}"])
-    return "\n".join([defines, _PRELUDE, functions, _KERNELS])
+        "__device__ __forceinline__ void sweep_back(const float *value, float *adjoint) {", *sweep, "}"]
+    parts = ["\n".join(defines), _PRELUDE, "\n".join(functions), _KERNELS]
+    if rules is not None:
+        arity = rules.arity
+        cases = " ".join(f"case {k}: return {_float_bits(v)};" for k, v in enumerate(rules.identity))
+        algebra = [
+            f"#define ARITY {arity}", f"#define N_STEP {len(rules.step.ops)}",
+            f"#define N_COMBINE {len(rules.combine.ops)}", f"#define N_FINAL {len(rules.finalize.ops)}",
+            f"__device__ __forceinline__ float identity_of(int k) {{ switch (k) {{ {cases} }} return 0.0f; }}",
+            _region_functions("step", rules.step, arity + rules.num_messages),
+            _region_functions("combine", rules.combine, 2 * arity),
+            _region_functions("finalize", rules.finalize, arity)]
+        parts += ["\n".join(algebra), _ALGEBRA_KERNELS]
+    return "\n".join(parts)
 
 
 class CompilerUnavailable(RuntimeError):
@@ -406,15 +678,17 @@ def enabled() -> bool:
     return os.environ.get("TGB_EDGE_JIT", "1") != "0"
 
 
-def module_for(program: ep.EdgeProgram, width: int, moduli, reducer: int) -> Module | None:
+def module_for(program: ep.EdgeProgram, width: int, moduli, reducer: int, rules=None,
+               message_slots=None) -> Module | None:
     """The module of this specialisation, compiled on first use; None when the runtime compiler is
     not available (the interpreting kernels then run the program)."""
-    key = (program.key(), int(width), tuple(int(m) for m in moduli), int(reducer))
+    key = (program.key(), int(width), tuple(int(m) for m in moduli), int(reducer),
+           None if rules is None else (rules.key(), tuple(message_slots)))
     with _lock:
         if key in _modules:
             return _modules[key]
     try:
-        module = Module(generate_source(program, width, moduli, reducer))
+        module = Module(generate_source(program, width, moduli, reducer, rules, message_slots))
     except CompilerUnavailable:
         module = None
     with _lock:
