@@ -725,7 +725,8 @@ TGB_API int32_t tgb_edge_algebra_bwd_sources(const tgb_csr_plan *plan,
  *   tgb_jit_launch   loads the module on the current device on first use and
  *                    launches `kernel` (an extern "C" __global__ taking ONE
  *                    by-value argument block, pointed to by `arguments`) with
- *                    `grid` blocks of `block` threads on `stream`.
+ *                    `grid` blocks of `block` threads on `stream`; block = 0:
+ *                    the block size the kernel declares (__launch_bounds__).
  * ------------------------------------------------------------------------ */
 typedef struct tgb_jit_module tgb_jit_module;
 TGB_API int32_t tgb_jit_build(const char *source, tgb_jit_module **module,

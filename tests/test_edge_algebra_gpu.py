@@ -227,7 +227,7 @@ def test_a_reducer_that_is_not_associative_is_refused():
 @pytest.mark.parametrize("kernel_class", (WeightedComposition, StableAttention))
 def test_generated_algebra_kernels_equal_the_interpreting_kernels(kernel_class, monkeypatch):
     """The fold and its reverse sweep as runtime-compiled straight-line CUDA against the interpreter:
-    same graph (a 1 500-edge row, rows without edges), forward bit for bit, cotangents to rounding."""
+    same graph (a 1 500-edge row, rows without edges), unsplit rows bit for bit, the rest to rounding."""
     n = 400
     gen = torch.Generator().manual_seed(17)
     hub = torch.randint(0, n, (1500,), generator=gen)
@@ -258,6 +258,10 @@ def test_generated_algebra_kernels_equal_the_interpreting_kernels(kernel_class, 
             out = kernel_class()(graph=graph, src=leaves, dst={})
         cotangent = torch.where(torch.isfinite(out.detach()), dy, torch.zeros_like(dy))
         results[mode] = (out.detach(), torch.autograd.grad(out, list(leaves.values()), cotangent))
-    assert torch.equal(torch.nan_to_num(results["1"][0], nan=7.0), torch.nan_to_num(results["0"][0], nan=7.0))
+    # rows below the split threshold are folded edge by edge by both: bit for bit; the long row is cut
+    # into more slices by the generated kernel (wider CTA), so its joins associate differently
+    generated, interpreted = (torch.nan_to_num(results[mode][0], nan=7.0) for mode in ("1", "0"))
+    assert torch.equal(generated[1:], interpreted[1:])
+    torch.testing.assert_close(generated[0], interpreted[0], rtol=1e-4, atol=1e-5 * float(interpreted[0].abs().max()))
     for a, b in zip(results["1"][1], results["0"][1]):
-        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6 * float(b.abs().max()), equal_nan=True)
+        torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5 * float(b.abs().max()), equal_nan=True)

@@ -643,7 +643,7 @@ extern "C" int32_t tgb_edge_program_jit_fwd(const tgb_csr_plan *plan, tgb_jit_mo
   const int lanes = lanes_for_width(program->width);
   int32_t rc = tgb_jit_launch(module, "fwd", (uint32_t)ceil_div(plan->num_dst * lanes, kThreads), kThreads, &a, stream);
   if (rc == TGB_STATUS_OK && w.n_long > 0)
-    rc = tgb_jit_launch(module, "fwd_long", (uint32_t)w.n_long, kLongThreads, &a, stream);
+    rc = tgb_jit_launch(module, "fwd_long", (uint32_t)w.n_long, 0, &a, stream);
   return rc;
 }
 
@@ -711,7 +711,7 @@ int32_t jit_reverse(const tgb_csr_plan *plan, tgb_jit_module *module, const tgb_
   const uint32_t blocks = (uint32_t)ceil_div(w.n_rows * lanes, kThreads);
   int32_t rc = tgb_jit_launch(module, source_major ? "bwd_sources" : "bwd_rows", blocks, kThreads, &a, stream);
   if (rc == TGB_STATUS_OK && w.n_long > 0)
-    rc = tgb_jit_launch(module, source_major ? "bwd_sources_long" : "bwd_rows_long", (uint32_t)w.n_long, kLongThreads,
+    rc = tgb_jit_launch(module, source_major ? "bwd_sources_long" : "bwd_rows_long", (uint32_t)w.n_long, 0,
                         &a, stream);
   return rc;
 }
@@ -736,7 +736,7 @@ extern "C" int32_t tgb_edge_algebra_jit_fwd(const tgb_csr_plan *plan, tgb_jit_mo
   int32_t rc = tgb_jit_launch(module, "alg_fwd", (uint32_t)ceil_div(plan->num_dst * lanes, kThreads), kThreads, &a,
                               stream);
   if (rc == TGB_STATUS_OK && w.n_long > 0)
-    rc = tgb_jit_launch(module, "alg_fwd_long", (uint32_t)w.n_long, kLongThreads, &a, stream);
+    rc = tgb_jit_launch(module, "alg_fwd_long", (uint32_t)w.n_long, 0, &a, stream);
   return rc;
 }
 
@@ -761,7 +761,7 @@ extern "C" int32_t tgb_edge_algebra_jit_bwd_messages(const tgb_csr_plan *plan, t
   int32_t rc = tgb_jit_launch(module, "alg_bwd_messages", (uint32_t)ceil_div(plan->num_dst * lanes, kThreads), kThreads,
                               &a, stream);
   if (rc == TGB_STATUS_OK && w.n_long > 0)
-    rc = tgb_jit_launch(module, "alg_bwd_messages_long", (uint32_t)w.n_long, kLongThreads, &a, stream);
+    rc = tgb_jit_launch(module, "alg_bwd_messages_long", (uint32_t)w.n_long, 0, &a, stream);
   return rc;
 }
 

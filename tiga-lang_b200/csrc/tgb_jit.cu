@@ -69,6 +69,7 @@ struct Driver {
   CUresult (*module_unload)(CUmodule) = nullptr;
   CUresult (*launch)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
                      void **, void **) = nullptr;
+  CUresult (*function_attribute)(int *, CUfunction_attribute, CUfunction) = nullptr;
   bool ok = false;
 };
 
@@ -88,7 +89,8 @@ const Driver *driver() {
     api.module_function = reinterpret_cast<decltype(api.module_function)>(load("cuModuleGetFunction"));
     api.module_unload = reinterpret_cast<decltype(api.module_unload)>(load("cuModuleUnload"));
     api.launch = reinterpret_cast<decltype(api.launch)>(load("cuLaunchKernel"));
-    api.ok = api.module_load && api.module_function && api.module_unload && api.launch;
+    api.function_attribute = reinterpret_cast<decltype(api.function_attribute)>(load("cuFuncGetAttribute"));
+    api.ok = api.module_load && api.module_function && api.module_unload && api.launch && api.function_attribute;
   });
   return api.ok ? &api : nullptr;
 }
@@ -178,6 +180,12 @@ extern "C" int32_t tgb_jit_launch(tgb_jit_module *module, const char *kernel, ui
     } else {
       function = found->second;
     }
+  }
+  if (block == 0) {     // the block size the kernel was compiled for (its __launch_bounds__)
+    int limit = 0;
+    const CUresult rc = api->function_attribute(&limit, CU_FUNC_ATTRIBUTE_MAX_THREADS_PER_BLOCK, function);
+    if (rc != CUDA_SUCCESS || limit < 32) TGB_FAIL(TGB_STATUS_INTERNAL, "cuFuncGetAttribute(%s) failed (%d)", kernel, (int)rc);
+    block = (uint32_t)limit;
   }
   // every generated kernel takes ONE by-value argument (its argument block)
   void *params[1] = {const_cast<void *>(arguments)};

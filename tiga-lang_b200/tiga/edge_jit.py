@@ -64,7 +64,6 @@ struct Args {
 #define ROLE_EDGE 2
 #define ROLE_PARAM 3
 #define THREADS 128
-#define LONG_THREADS 256
 
 __device__ __forceinline__ i64 load_index(const void *base, int bits, i64 i) {
   return bits == 64 ? __ldg(static_cast<const i64 *>(base) + i) : (i64)__ldg(static_cast<const i32 *>(base) + i);
@@ -617,6 +616,9 @@ def generate_source(program: ep.EdgeProgram, width: int, moduli, reducer: int, r
         f"#define WIDTH {int(width)}", f"#define LANES {_lanes(int(width))}", f"#define N_INSTR {n}",
         f"#define N_OPERANDS {count}", f"#define REDUCER {4 if rules is not None else int(reducer)}",
         f"#define N_MESSAGES {len(slots)}",
+        # one CTA per long row: the more lane groups, the shorter the slice each walks (the library
+        # launches the *_long kernels with the block size they declare)
+        f"#define LONG_THREADS {512 if rules is not None else 1024}",
         f"__device__ constexpr int kRole[N_OPERANDS] = {{{table(roles)}}};",
         f"__device__ constexpr int kModulus[N_OPERANDS] = {{{table(moduli)}}};",
         f"__device__ constexpr int kLoadSlot[N_OPERANDS] = {{{table(load_slot[k] for k in range(count))}}};",
