@@ -130,3 +130,31 @@ def test_while_loop_stops_on_its_condition():
     out = tg.control.while_loop(xa, lambda s: s.abs().max() < limit, grow, max_iterations=100)
     assert float(out.abs().max()) >= limit
     assert torch.equal(tg.control.while_loop(xa, lambda s: s.abs().max() < limit, grow, max_iterations=0), xa)
+
+
+def test_repeat_replays_a_runtime_compiled_edge_program():
+    """A loop body whose edge expression has no dedicated kernel: the generated kernels are launched
+    through the driver's module interface, which a CUDA-graph capture records like any other launch."""
+    class Flux(tg.MessagePassing):
+        reducer = tg.sum()
+
+        def edge(self, src, dst, edge, rate):
+            return edge.weight * (src.u - dst.u) * rate
+
+    row_ptr, col = syn.rmat_csr(9, 6, seed=3, symmetrize=True)
+    n = row_ptr.numel() - 1
+    graph = tg.Graph.from_csr(row_ptr.cuda(), col.cuda(), num_src=n)
+    gen = torch.Generator().manual_seed(2)
+    u0 = torch.randn(n, 4, generator=gen).cuda()
+    weight = (0.01 * torch.rand(col.numel(), 1, generator=gen)).cuda()
+    kernel = Flux()
+
+    def diffuse(state):
+        return state + kernel(graph=graph, src={"u": state}, dst={"u": state}, edge={"weight": weight}, rate=0.5)
+
+    want = u0
+    for _ in range(12):
+        want = diffuse(want)
+    got = tg.repeat(u0, diffuse, iterations=12, cuda_graph=True)
+    assert kernel.last_variant.lowering == "b200-generic-csr-scalar-reducer"
+    assert torch.equal(got, want)

@@ -70,6 +70,7 @@ struct Driver {
   CUresult (*launch)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
                      void **, void **) = nullptr;
   CUresult (*function_attribute)(int *, CUfunction_attribute, CUfunction) = nullptr;
+  CUresult (*current_context)(CUcontext *) = nullptr;
   bool ok = false;
 };
 
@@ -90,7 +91,9 @@ const Driver *driver() {
     api.module_unload = reinterpret_cast<decltype(api.module_unload)>(load("cuModuleUnload"));
     api.launch = reinterpret_cast<decltype(api.launch)>(load("cuLaunchKernel"));
     api.function_attribute = reinterpret_cast<decltype(api.function_attribute)>(load("cuFuncGetAttribute"));
-    api.ok = api.module_load && api.module_function && api.module_unload && api.launch && api.function_attribute;
+    api.current_context = reinterpret_cast<decltype(api.current_context)>(load("cuCtxGetCurrent"));
+    api.ok = api.module_load && api.module_function && api.module_unload && api.launch && api.function_attribute &&
+             api.current_context;
   });
   return api.ok ? &api : nullptr;
 }
@@ -161,7 +164,11 @@ extern "C" int32_t tgb_jit_launch(tgb_jit_module *module, const char *kernel, ui
   int device = 0;
   TGB_CUDA(cudaGetDevice(&device));
   if (device < 0 || device >= kMaxDevices) TGB_FAIL(TGB_STATUS_UNSUPPORTED, "device ordinal out of range");
-  TGB_CUDA(cudaFree(nullptr));          // binds the primary context to this thread (an autograd worker has none)
+  // A thread that has made no runtime call yet (an autograd worker) has no context bound; the
+  // no-op free binds the primary one.  Threads that have a context skip it, which also keeps the
+  // launch legal while a stream is being captured into a CUDA graph.
+  CUcontext current = nullptr;
+  if (api->current_context(&current) != CUDA_SUCCESS || current == nullptr) TGB_CUDA(cudaFree(nullptr));
   CUfunction function = nullptr;
   {
     std::lock_guard<std::mutex> guard(module->lock);
