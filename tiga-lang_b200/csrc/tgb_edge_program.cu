@@ -596,6 +596,16 @@ extern "C" int32_t tgb_edge_program_bwd_sources(const tgb_csr_plan *plan, const 
 // ---- the same three passes through a module generated for the program (tiga/edge_jit.py) ---------
 namespace {
 
+// The row-per-group kernel, then the kernel that gives every row above the split threshold a CTA of
+// its own (launched with the block size it declares).  Running the second on a forked stream beside
+// the first was measured: no gain, the long-row kernel is not a tail of a few CTAs.
+int32_t launch_pair(tgb_jit_module *module, const char *short_kernel, uint32_t short_grid, const char *long_kernel,
+                    int64_t n_long, const tgb_jit_edge_args *a, uint64_t stream) {
+  int32_t rc = tgb_jit_launch(module, short_kernel, short_grid, kThreads, a, stream);
+  if (rc == TGB_STATUS_OK && n_long > 0) rc = tgb_jit_launch(module, long_kernel, (uint32_t)n_long, 0, a, stream);
+  return rc;
+}
+
 void fill_walk(tgb_jit_edge_args *a, const Walk &w) {
   a->ptr = w.ptr;
   a->idx = w.idx;
@@ -641,10 +651,8 @@ extern "C" int32_t tgb_edge_program_jit_fwd(const tgb_csr_plan *plan, tgb_jit_mo
   a.saved_index = reducer == TGB_REDUCER_PROD || reducer == TGB_REDUCER_MAX ? static_cast<int32_t *>(saved_index)
                                                                             : nullptr;
   const int lanes = lanes_for_width(program->width);
-  int32_t rc = tgb_jit_launch(module, "fwd", (uint32_t)ceil_div(plan->num_dst * lanes, kThreads), kThreads, &a, stream);
-  if (rc == TGB_STATUS_OK && w.n_long > 0)
-    rc = tgb_jit_launch(module, "fwd_long", (uint32_t)w.n_long, 0, &a, stream);
-  return rc;
+  return launch_pair(module, "fwd", (uint32_t)ceil_div(plan->num_dst * lanes, kThreads), "fwd_long", w.n_long, &a,
+                     stream);
 }
 
 namespace {
@@ -709,11 +717,8 @@ int32_t jit_reverse(const tgb_csr_plan *plan, tgb_jit_module *module, const tgb_
   a.saved_index = const_cast<int32_t *>(static_cast<const int32_t *>(saved_index));
   const int lanes = lanes_for_width(program->width);
   const uint32_t blocks = (uint32_t)ceil_div(w.n_rows * lanes, kThreads);
-  int32_t rc = tgb_jit_launch(module, source_major ? "bwd_sources" : "bwd_rows", blocks, kThreads, &a, stream);
-  if (rc == TGB_STATUS_OK && w.n_long > 0)
-    rc = tgb_jit_launch(module, source_major ? "bwd_sources_long" : "bwd_rows_long", (uint32_t)w.n_long, 0,
-                        &a, stream);
-  return rc;
+  return launch_pair(module, source_major ? "bwd_sources" : "bwd_rows", blocks,
+                     source_major ? "bwd_sources_long" : "bwd_rows_long", w.n_long, &a, stream);
 }
 
 }  // namespace
@@ -733,11 +738,8 @@ extern "C" int32_t tgb_edge_algebra_jit_fwd(const tgb_csr_plan *plan, tgb_jit_mo
   a.out = static_cast<float *>(out);
   a.num_edges = plan->num_edges;
   const int lanes = lanes_for_width(program->width);
-  int32_t rc = tgb_jit_launch(module, "alg_fwd", (uint32_t)ceil_div(plan->num_dst * lanes, kThreads), kThreads, &a,
-                              stream);
-  if (rc == TGB_STATUS_OK && w.n_long > 0)
-    rc = tgb_jit_launch(module, "alg_fwd_long", (uint32_t)w.n_long, 0, &a, stream);
-  return rc;
+  return launch_pair(module, "alg_fwd", (uint32_t)ceil_div(plan->num_dst * lanes, kThreads), "alg_fwd_long", w.n_long,
+                     &a, stream);
 }
 
 extern "C" int32_t tgb_edge_algebra_jit_bwd_messages(const tgb_csr_plan *plan, tgb_jit_module *module,
@@ -758,11 +760,8 @@ extern "C" int32_t tgb_edge_algebra_jit_bwd_messages(const tgb_csr_plan *plan, t
   a.message_grads = static_cast<float *>(message_grads);
   a.num_edges = plan->num_edges;
   const int lanes = lanes_for_width(program->width);
-  int32_t rc = tgb_jit_launch(module, "alg_bwd_messages", (uint32_t)ceil_div(plan->num_dst * lanes, kThreads), kThreads,
-                              &a, stream);
-  if (rc == TGB_STATUS_OK && w.n_long > 0)
-    rc = tgb_jit_launch(module, "alg_bwd_messages_long", (uint32_t)w.n_long, 0, &a, stream);
-  return rc;
+  return launch_pair(module, "alg_bwd_messages", (uint32_t)ceil_div(plan->num_dst * lanes, kThreads),
+                     "alg_bwd_messages_long", w.n_long, &a, stream);
 }
 
 extern "C" int32_t tgb_edge_algebra_jit_bwd(const tgb_csr_plan *plan, tgb_jit_module *module,

@@ -98,7 +98,7 @@ __device__ __forceinline__ void forward_pass(const Args &a) {
   }
   i64 begin = load_index(a.ptr, a.ptr_bits, row), end = load_index(a.ptr, a.ptr_bits, row + 1);
   const i64 degree = end - begin;
-  if (!LONG && degree > a.split_threshold) return;
+  if (LONG != (degree > a.split_threshold)) return;      // the whole CTA of a long-row kernel leaves together
   if (LONG) {
     const i64 slice = (degree + kGroups - 1) / kGroups;
     begin = begin + group * slice;
@@ -182,7 +182,7 @@ __device__ __forceinline__ void reverse_pass(const Args &a) {
   }
   const unsigned mask = group_mask();
   i64 begin = load_index(a.ptr, a.ptr_bits, row), end = load_index(a.ptr, a.ptr_bits, row + 1);
-  if (!LONG && end - begin > a.split_threshold) return;
+  if (LONG != (end - begin > a.split_threshold)) return;
   if (LONG) {
     const i64 slice = (end - begin + kGroups - 1) / kGroups;
     begin = begin + group * slice;
@@ -340,7 +340,7 @@ __device__ __forceinline__ bool row_span(const Args &a, RowSpan &span) {
   span.end = load_index(a.ptr, a.ptr_bits, span.row + 1);
   span.degree = span.end - span.begin;
   span.slice = 0;
-  if (!LONG && span.degree > a.split_threshold) return false;
+  if (LONG != (span.degree > a.split_threshold)) return false;
   if (LONG) {
     span.slice = (span.degree + kGroups - 1) / kGroups;
     span.begin = span.begin + group * span.slice;
