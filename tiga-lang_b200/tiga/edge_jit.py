@@ -89,16 +89,18 @@ __device__ __forceinline__ void forward_pass(const Args &a) {
   __shared__ float part_masked[LONG ? LONG_THREADS : 1];
   __shared__ i32 part_mark[LONG ? LONG_THREADS : 1];
   const int lane = threadIdx.x % LANES, group = threadIdx.x / LANES;
+  // the plan's row order: the rows above the split threshold first (one CTA each), then the others
+  // bucketed by degree, so the lane groups of a CTA walk rows of similar length
   i64 row;
   if (LONG) {
     row = __ldg(a.order + blockIdx.x);
   } else {
-    row = (i64)blockIdx.x * kGroups + group;
-    if (row >= a.n_rows) return;
+    const i64 position = a.n_long + (i64)blockIdx.x * kGroups + group;
+    if (position >= a.n_rows) return;
+    row = __ldg(a.order + position);
   }
   i64 begin = load_index(a.ptr, a.ptr_bits, row), end = load_index(a.ptr, a.ptr_bits, row + 1);
   const i64 degree = end - begin;
-  if (LONG != (degree > a.split_threshold)) return;      // the whole CTA of a long-row kernel leaves together
   if (LONG) {
     const i64 slice = (degree + kGroups - 1) / kGroups;
     begin = begin + group * slice;
@@ -177,12 +179,12 @@ __device__ __forceinline__ void reverse_pass(const Args &a) {
   if (LONG) {
     row = __ldg(a.order + blockIdx.x);
   } else {
-    row = (i64)blockIdx.x * kGroups + group;
-    if (row >= a.n_rows) return;
+    const i64 position = a.n_long + (i64)blockIdx.x * kGroups + group;
+    if (position >= a.n_rows) return;
+    row = __ldg(a.order + position);
   }
   const unsigned mask = group_mask();
   i64 begin = load_index(a.ptr, a.ptr_bits, row), end = load_index(a.ptr, a.ptr_bits, row + 1);
-  if (LONG != (end - begin > a.split_threshold)) return;
   if (LONG) {
     const i64 slice = (end - begin + kGroups - 1) / kGroups;
     begin = begin + group * slice;
@@ -333,14 +335,14 @@ __device__ __forceinline__ bool row_span(const Args &a, RowSpan &span) {
   if (LONG) {
     span.row = __ldg(a.order + blockIdx.x);
   } else {
-    span.row = (i64)blockIdx.x * kGroups + group;
-    if (span.row >= a.n_rows) return false;
+    const i64 position = a.n_long + (i64)blockIdx.x * kGroups + group;
+    if (position >= a.n_rows) return false;
+    span.row = __ldg(a.order + position);
   }
   span.begin = load_index(a.ptr, a.ptr_bits, span.row);
   span.end = load_index(a.ptr, a.ptr_bits, span.row + 1);
   span.degree = span.end - span.begin;
   span.slice = 0;
-  if (LONG != (span.degree > a.split_threshold)) return false;
   if (LONG) {
     span.slice = (span.degree + kGroups - 1) / kGroups;
     span.begin = span.begin + group * span.slice;
