@@ -14,6 +14,14 @@ from baseline import synthetic as syn
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=("generated", "interpreted"))
+def kernels(request, monkeypatch):
+    """Every test runs twice: on the kernels compiled at run time for the program, and on the
+    interpreting kernels that take over when the runtime compiler is missing."""
+    monkeypatch.setenv("TGB_EDGE_JIT", "1" if request.param == "generated" else "0")
+    return request.param
+
+
 class StableWeightedMean(tg.Reducer):
     name = "deliberately_not_online_softmax"
     associative = True

@@ -178,13 +178,13 @@ k_edge_program_fwd(const __grid_constant__ tgb_edge_program p, Operands in, Walk
   int64_t row;
   if (LONG) {
     row = __ldg(w.order + blockIdx.x);
-  } else {
-    row = (int64_t)blockIdx.x * kGroups + group;
-    if (row >= w.n_rows) return;
+  } else {               // the rows below the split threshold, in the plan's bucket order
+    const int64_t position = w.n_long + (int64_t)blockIdx.x * kGroups + group;
+    if (position >= w.n_rows) return;
+    row = __ldg(w.order + position);
   }
   int64_t begin = load_index(w.ptr, w.ptr_bits, row), end = load_index(w.ptr, w.ptr_bits, row + 1);
   const int64_t degree = end - begin;
-  if (!LONG && degree > w.split_threshold) return;
   if (LONG) {
     const int64_t slice = (degree + kGroups - 1) / kGroups;
     begin = begin + group * slice;
@@ -271,12 +271,12 @@ k_edge_program_bwd(const __grid_constant__ tgb_edge_program p, Operands in, Sink
   if (LONG) {
     row = __ldg(w.order + blockIdx.x);
   } else {
-    row = (int64_t)blockIdx.x * kGroups + group;
-    if (row >= w.n_rows) return;
+    const int64_t position = w.n_long + (int64_t)blockIdx.x * kGroups + group;
+    if (position >= w.n_rows) return;
+    row = __ldg(w.order + position);
   }
   const unsigned mask = group_mask<LANES>();
   int64_t begin = load_index(w.ptr, w.ptr_bits, row), end = load_index(w.ptr, w.ptr_bits, row + 1);
-  if (!LONG && end - begin > w.split_threshold) return;
   if (LONG) {            // contiguous slices of the row's entries, one per lane group
     const int64_t slice = (end - begin + kGroups - 1) / kGroups;
     begin = begin + group * slice;
@@ -839,14 +839,14 @@ __device__ __forceinline__ bool row_span(const Walk &w, RowSpan *span) {
   if (LONG) {
     span->row = __ldg(w.order + blockIdx.x);
   } else {
-    span->row = (int64_t)blockIdx.x * kGroups + group;
-    if (span->row >= w.n_rows) return false;
+    const int64_t position = w.n_long + (int64_t)blockIdx.x * kGroups + group;
+    if (position >= w.n_rows) return false;
+    span->row = __ldg(w.order + position);
   }
   span->begin = load_index(w.ptr, w.ptr_bits, span->row);
   span->end = load_index(w.ptr, w.ptr_bits, span->row + 1);
   span->degree = span->end - span->begin;
   span->slice = 0;
-  if (!LONG && span->degree > w.split_threshold) return false;
   if (LONG) {
     span->slice = (span->degree + kGroups - 1) / kGroups;
     span->begin = span->begin + group * span->slice;
