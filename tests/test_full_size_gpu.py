@@ -242,3 +242,47 @@ def test_varlen_attention_configuration_full_size():
     rq, rk, rv = torch.autograd.grad(ref, (qs, ks, vs), dy[b:e, 3].float())
     for got, want in ((dq, rq), (dk, rk), (dv, rv)):
         assert torch.allclose(got[b:e, 3].float(), want, rtol=3e-2, atol=3e-2 * want.abs().max().item())
+
+
+def test_runtime_compiled_edge_program_against_the_dedicated_kernels_full_size():
+    """Two independent native paths at config 2's size: the flux `edge.weight * (src.u - dst.u)` through
+    the kernels generated for that expression, and the same sum written with the dedicated kernels,
+    `wsum(weight, u) - dst.u * wsum(weight, 1)`; forward and all three cotangents.  The graph has
+    10^5-edge rows (the generated long-row kernels) and rows without edges.
+    Tolerance: float32 sums over up to 10^5 terms added in different orders: 2e-4 of the row's
+    sum of magnitudes (measured spread is a few 1e-6)."""
+    device = torch.device("cuda")
+    row_ptr, col = syn.rmat_csr(20, 32, seed=20261125, symmetrize=True, device=device)
+    n, F = row_ptr.numel() - 1, 16
+    E = col.numel()
+    u = syn.normal((n, F), seed=3, device=device)
+    v = syn.normal((n, F), seed=4, device=device)
+    w = torch.rand(E, 1, device=device, generator=torch.Generator(device=device).manual_seed(5))
+    dy = syn.normal((n, F), seed=6, device=device)
+    graph = tg.Graph.from_csr(row_ptr, col, num_src=n)
+
+    class Flux(tg.MessagePassing):
+        reducer = tg.sum()
+
+        def edge(self, src, dst, edge):
+            return edge.weight * (src.u - dst.u)
+
+    ug, vg, wg = (t.clone().requires_grad_() for t in (u, v, w))
+    kernel = Flux()
+    out = kernel(graph=graph, src={"u": ug}, dst={"u": vg}, edge={"weight": wg})
+    assert kernel.last_variant.lowering == "b200-generic-csr-scalar-reducer"
+    grads = torch.autograd.grad(out, (ug, vg, wg), dy)
+
+    ud, vd, wd = (t.clone().requires_grad_() for t in (u, v, w))
+    gathered = WeightedSum()(graph=graph, src={"x": ud}, dst={}, edge={"weight": wd.reshape(-1)})
+    row_weight = WeightedSum()(graph=graph, src={"x": torch.ones(n, 1, device=device)}, dst={},
+                               edge={"weight": wd.reshape(-1)})
+    want = gathered - vd * row_weight
+    want_grads = torch.autograd.grad(want, (ud, vd, wd), dy)
+
+    magnitude = WeightedSum()(graph=graph, src={"x": u.abs()}, dst={}, edge={"weight": w.reshape(-1)}) \
+        + v.abs() * row_weight.detach()
+    assert torch.all((out.detach() - want.detach()).abs() <= 2e-4 * magnitude + 1e-5)
+    for got, ref in zip(grads, want_grads):
+        scale = float(ref.abs().max())
+        assert float((got - ref).abs().max()) <= 2e-4 * scale
