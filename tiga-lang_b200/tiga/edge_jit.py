@@ -666,6 +666,10 @@ class Module:
         self.source = source
 
     def __del__(self):
+        import sys
+
+        if sys is None or sys.is_finalizing():      # process exit releases the module with the context
+            return
         try:
             if self.handle:
                 _native.lib().tgb_jit_destroy(self.handle)
