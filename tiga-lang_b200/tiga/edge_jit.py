@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import sys
 import threading
 
 from . import _native
@@ -666,8 +667,6 @@ class Module:
         self.source = source
 
     def __del__(self):
-        import sys
-
         if sys is None or sys.is_finalizing():      # process exit releases the module with the context
             return
         try:
